@@ -1,0 +1,194 @@
+/*
+ * vetr.h — C ABI of the B200 (sm_100a) blending point rasterizer.
+ *
+ * This is the boundary a host program binds to: plain pointers and sizes, no C++ or tensor-library types.
+ * Every function replaces a piece of the reference's rasterizer (lfranke/VET, src/lib/rendering); the comment
+ * of each entry point cites what it stands in for.
+ *
+ * Conventions
+ *   - All pointers named *device* pointers below must point to memory of the context's GPU.
+ *   - Every call enqueues its work on the context's stream and returns without synchronising, unless stated.
+ *   - Return value: VETR_OK (0) or a negative vetr_status.  Nothing aborts the process or traps the device.
+ *     Conditions that can only be seen on the device (fragment buffer overflow) are recorded in a device
+ *     status word that vetr_read_status() copies back.
+ *   - A context is not thread-safe; distinct contexts are independent.  There is no process-global state.
+ */
+#ifndef VETR_H
+#define VETR_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VETR_MAX_LAYERS 5 /* RenderConstants.h:33 (max_layers) */
+#define VETR_MAX_VIEWS 8  /* views handled by one launch; larger batches are processed in groups */
+
+typedef enum vetr_status
+{
+    VETR_OK               = 0,
+    VETR_E_INVALID_ARG    = -1,
+    VETR_E_CUDA           = -2, /* a CUDA runtime call failed; vetr_last_cuda_error() has the code */
+    VETR_E_UNSUPPORTED    = -3, /* camera model / option the library does not implement */
+    VETR_E_LIST_OVERFLOW  = -4, /* more fragments than the key buffer holds (reported by vetr_read_status) */
+    VETR_E_TOO_LARGE      = -5  /* a size exceeds a fixed limit of the entry point */
+} vetr_status;
+
+/* Render modes: PointRendererCache::RenderMode, PointRenderer.h (FUZZY_DT = 0 and FUZZY_BLEND = 2 are not built). */
+#define VETR_MODE_FULL_BLEND 1
+#define VETR_MODE_BILINEAR_BLEND 3
+
+/* The RenderParams fields the kernels read: data/Settings.h:19-73, RenderConstants.h:36-60. */
+typedef struct vetr_params
+{
+    int32_t render_mode;               /* VETR_MODE_* */
+    int32_t num_layers;                /* 1..VETR_MAX_LAYERS */
+    int32_t num_channels;              /* 3 or 4 (RenderBackward.cu:2474-2492) */
+    int32_t drop_out_points_by_radius; /* bool */
+    float   drop_out_radius_threshold; /* 0.6 */
+    float   dist_cutoff;               /* 20 */
+    int32_t use_environment_map;       /* bool: no background term */
+    int32_t viewer_only;               /* bool: drop points whose confidence < stability_cutoff_value */
+    float   stability_cutoff_value;
+    int32_t debug_max_list_length;     /* <= 0: off */
+    int32_t need_point_gradient;       /* bool */
+    float   K_gradient_factor;         /* 0.5 */
+    float   distortion_gradient_factor;/* 0.005 */
+    float   output_background_mask_value;
+    int32_t background_alpha_to_point0;/* bool, default 1: the reference adds the background entry's alpha
+                                          gradient to descriptor 0's confidence gradient (RenderBackward.cu:1130,1157) */
+    int32_t keep_sorted_lists;         /* bool: write the sorted lists back (needed by vetr_backward / vetr_get_lists) */
+} vetr_params;
+
+/* ReducedImageInfo, data/SceneData.h:39-50. */
+typedef struct vetr_view
+{
+    int32_t w, h;
+    int32_t image_index;  /* row of poses_se3 */
+    int32_t camera_index; /* row of intrinsics */
+    int32_t camera_model; /* 0 = pinhole + distortion (the only model built) */
+    float   crop[5];      /* crop_transform: fx fy cx cy s */
+    float   rot[4];       /* crop_rotation, row-major 2x2 */
+} vetr_view;
+
+/* NeuralPointCloudCuda tensors, rendering/NeuralPointCloudCuda.h:81-106 (device pointers). */
+typedef struct vetr_cloud
+{
+    const float*   position; /* [n,4] xyz + drop-out radius, 16-byte aligned */
+    const int32_t* index;    /* [n]   point -> descriptor column */
+    int32_t        n;
+} vetr_cloud;
+
+/* NeuralPointTexture tensors, models/NeuralTexture.h:114-126 (device pointers). */
+typedef struct vetr_texture
+{
+    const float* texture;    /* [channels, n_tex] channel-major */
+    const float* confidence; /* [n_tex] */
+    const float* background; /* [channels] */
+    int32_t      n_tex;
+} vetr_texture;
+
+/* PoseModule / IntrinsicsModule tensors, data/NeuralStructure.h:30-34,56-59 (device pointers). */
+typedef struct vetr_cameras
+{
+    const double* poses_se3;  /* [n_img,8] world->camera: qx qy qz qw tx ty tz pad */
+    const float*  intrinsics; /* [n_cam,13] fx fy cx cy s k1 k2 k3 k4 k5 k6 p1 p2 */
+    int32_t       n_img, n_cam;
+} vetr_cameras;
+
+/*
+ * Per-pixel fragment lists of one forward call: what the reference keeps in LayerCuda::counting /
+ * scanned_counting / per_image_atomic_counters and in collections[b][l] (PointRenderer.h:66-110,
+ * PointRenderer.cu:796-822).  All views and levels live in ONE pixel space of n_views * P entries
+ * (P = pyramid pixels of a view; view-major, then level, then row-major) and ONE key buffer.
+ * Caller-owned device memory.
+ */
+typedef struct vetr_lists
+{
+    int32_t*  counts;   /* [n_views*P]  list length per pixel */
+    int32_t*  ends;     /* [n_views*P]  end offset (exclusive) of the pixel's list in keys; its start is ends - counts */
+    uint64_t* keys;     /* [capacity]   depth bits << 32 | point index, ascending inside each list after forward */
+    int64_t   capacity; /* entries of keys */
+    int32_t*  status;   /* [4] device words: {total fragments F, overflow flag, longest list, number of work items} */
+    int32_t*  items;    /* [items_capacity] work-item table written by the scan: first pixel of every run of pixels that
+                           one thread block of the blend / backward kernels processes (balanced by fragments) */
+    int64_t   items_capacity; /* >= vetr_item_table_entries(capacity, n_views*P) */
+} vetr_lists;
+
+typedef struct vetr_ctx vetr_ctx;
+
+/* Creates a context on `device` that enqueues on `cuda_stream` (a cudaStream_t; NULL = the legacy default stream).
+ * Replaces the process-global state of the reference (the __constant__ parameter blocks of RenderForward.cu:22-27 and
+ * the cached PointRendererCache, PointRenderer.h:112-248). Allocates a few KB of device scratch; synchronous. */
+int vetr_create(vetr_ctx** out, int device, void* cuda_stream);
+void vetr_destroy(vetr_ctx* ctx);
+int vetr_set_stream(vetr_ctx* ctx, void* cuda_stream);
+const char* vetr_strerror(int status);
+int vetr_last_cuda_error(const vetr_ctx* ctx);
+
+/* Pyramid pixels of one w x h view with num_layers levels (successive integer halving, PointRenderer.cu:351-381). */
+int64_t vetr_pyramid_pixels(int w, int h, int num_layers);
+
+/* Entries the work-item table of vetr_lists needs for a key buffer of `capacity` keys over `n_pixels_total` pixels. */
+int64_t vetr_item_table_entries(int64_t capacity, int64_t n_pixels_total);
+
+/* Upper bound of the number of fragments: n * num_layers * n_views (x4 in bilinear mode). */
+int64_t vetr_max_fragments(int n_points, int n_views, const vetr_params* params);
+
+/* Forward pass: CountingPrepassMulti + exclusive_scan + CollectMulti + SortMulti + BlendMulti / BlendMultiBilinear +
+ * CreateMask for all views and levels (BlendPointCloudForward, PointRenderer.cu:657-1069).
+ *   dropout    [n_views, n] float device array, 1 = point dropped (PointRenderer.cu:461-468), or NULL
+ *   out_color  num_layers device pointers, level l is [n_views, channels, h_l, w_l]
+ *   out_weight num_layers device pointers [n_views,1,h_l,w_l]: final transmittance (LayerCuda::weight), or NULL
+ *   out_mask   num_layers device pointers [n_views,1,h_l,w_l] (CreateMask, PointRenderer.cu:216-235), or NULL
+ *   out_depth  num_layers device pointers [n_views,1,h_l,w_l]: nearest depth, 100000 where empty (LayerCuda::depth), or NULL
+ * n_views <= VETR_MAX_VIEWS; all views share w and h. */
+int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* cloud, const vetr_texture* texture,
+                 const vetr_cameras* cameras, const vetr_view* views, int n_views, const float* dropout,
+                 const vetr_lists* lists, float* const* out_color, float* const* out_weight, float* const* out_mask,
+                 float* const* out_depth);
+
+/* Backward pass of the forward call that filled `lists`: BlendBackwards2 / BlendBackwardsBilinear for all views and
+ * levels (BlendPointCloudBackward, PointRenderer.cu:1111-1250; kernels RenderBackward.cu:1083-1513, 2893-3232).
+ * Gradients are ADDED to the caller's buffers as raw sums (the caller zero-fills; several calls may accumulate):
+ *   g_desc     [n_tex,4] point-major descriptor gradient (columns >= channels stay untouched)
+ *   g_conf     [n_tex]
+ *   g_points   [n,4] xyz gradient sum + hit count in .w, or NULL (out_gradient_points + out_gradient_points_count)
+ *   g_background [channels]
+ *   g_pose     [n_img,6] double, g_pose_count [n_img] float, or NULL
+ *   g_intr     [n_cam,13] float, g_intr_count [n_cam] float, or NULL
+ * out_color are the images the forward call wrote; grad_color their gradients (same shapes). */
+int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* cloud, const vetr_texture* texture,
+                  const vetr_cameras* cameras, const vetr_view* views, int n_views, const vetr_lists* lists,
+                  const float* const* out_color, const float* const* grad_color, float* g_desc, float* g_conf,
+                  float* g_points, float* g_background, double* g_pose, float* g_pose_count, float* g_intr,
+                  float* g_intr_count);
+
+/* Epilogue of the backward pass: converts the accumulation buffers into the tensors the reference returns
+ * (PointRenderer.cu:1251-1322): g_texture [channels,n_tex] channel-major (transpose of g_desc), and the count
+ * normalisation of NormalizeGradient / NormalizeGradientDevTensor (PointRenderer.cu:1072-1109): point gradients
+ * [n,4] divided by their hit count (.w is set to 0 afterwards, counts are written to g_points_count [n] if given),
+ * pose and intrinsics gradients divided by their counts.  Any pointer may be NULL to skip that part. */
+int vetr_finalize_gradients(vetr_ctx* ctx, int channels, int n_tex, const float* g_desc, float* g_texture, int n,
+                            float* g_points, float* g_points_count, int n_img, double* g_pose,
+                            const float* g_pose_count, int n_cam, float* g_intr, const float* g_intr_count);
+
+/* ApplyTangentToPose (PointRenderer.cu:1325-1349): poses[i] <- exp_se3(tangent[i]) * poses[i]; tangent[i] <- 0. */
+int vetr_apply_tangent(vetr_ctx* ctx, double* tangent /*[n,6]*/, double* poses_se3 /*[n,8]*/, int n);
+
+/* Copies the device status words of `lists` to the host (synchronises the stream).  Returns VETR_E_LIST_OVERFLOW
+ * if the last forward call produced more fragments than lists->capacity. */
+int vetr_read_status(vetr_ctx* ctx, const vetr_lists* lists, int64_t* total_fragments, int32_t* longest_list);
+
+/* Parity / debugging: unpacks one (view, level) of `lists` into the reference's collections layout [2,F_l] int32
+ * (row 0 depth bits, row 1 point index; PointRenderer.cu:817-818) and its scanned_counting [h_l*w_l].
+ * Synchronises.  out_collections may be NULL to query *n_fragments only. */
+int vetr_get_lists(vetr_ctx* ctx, const vetr_lists* lists, int w, int h, int num_layers, int n_views, int view,
+                   int layer, int32_t* out_collections, int32_t* out_scanned_counting, int64_t* n_fragments);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VETR_H */

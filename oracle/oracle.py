@@ -1,0 +1,160 @@
+"""ctypes front end of the CPU oracle (oracle/vet_oracle.cpp).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the CPU-baseline leg of the
+benchmark.  The product package never imports this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+class OParams(C.Structure):
+    _fields_ = [
+        ("render_mode", C.c_int), ("num_layers", C.c_int), ("num_channels", C.c_int),
+        ("drop_out_points_by_radius", C.c_int), ("drop_out_radius_threshold", C.c_float),
+        ("dist_cutoff", C.c_float), ("use_environment_map", C.c_int), ("viewer_only", C.c_int),
+        ("stability_cutoff_value", C.c_float), ("debug_max_list_length", C.c_int),
+        ("need_point_gradient", C.c_int), ("K_gradient_factor", C.c_float),
+        ("distortion_gradient_factor", C.c_float), ("output_background_mask", C.c_int),
+        ("output_background_mask_value", C.c_float), ("conf_grad_quadratic", C.c_int),
+        ("background_alpha_to_point0", C.c_int),
+    ]
+
+
+class OView(C.Structure):
+    _fields_ = [("w", C.c_int), ("h", C.c_int), ("image_index", C.c_int), ("camera_index", C.c_int),
+                ("camera_model", C.c_int), ("crop", C.c_float * 5), ("rot", C.c_float * 4)]
+
+
+def build(force: bool = False) -> str:
+    path = os.path.join(_HERE, "libvet_oracle.so")
+    src = os.path.join(_HERE, "vet_oracle.cpp")
+    if force or not os.path.exists(path) or os.path.getmtime(path) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "libvet_oracle.so"], stdout=subprocess.DEVNULL)
+    return path
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = C.CDLL(build())
+        _LIB.vo_create.restype = C.c_void_p
+        _LIB.vo_destroy.argtypes = [C.c_void_p]
+        _LIB.vo_forward.restype = C.c_int64
+        _LIB.vo_pixels_per_view.restype = C.c_int64
+        _LIB.vo_pixels_per_view.argtypes = [C.c_void_p]
+    return _LIB
+
+
+def default_params(**kw) -> dict:
+    p = dict(render_mode=1, num_layers=4, num_channels=4, drop_out_points_by_radius=1,
+             drop_out_radius_threshold=0.6, dist_cutoff=20.0, use_environment_map=0, viewer_only=0,
+             stability_cutoff_value=10000.0, debug_max_list_length=-1, need_point_gradient=1,
+             K_gradient_factor=0.5, distortion_gradient_factor=0.005, output_background_mask=0,
+             output_background_mask_value=0.0, conf_grad_quadratic=0, background_alpha_to_point0=1)
+    p.update(kw)
+    return p
+
+
+def level_sizes(w: int, h: int, L: int):
+    out = []
+    for _ in range(L):
+        out.append((w, h))
+        w //= 2
+        h //= 2
+    return out
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def _ptr_array(arrs):
+    if arrs is None:
+        return None
+    return (C.c_void_p * len(arrs))(*[a.ctypes.data for a in arrs])
+
+
+class Oracle:
+    """One forward (+ optional backward) of the rasterizer on the CPU."""
+
+    def __init__(self):
+        self._h = C.c_void_p(lib().vo_create())
+        self._keep = None
+
+    def __del__(self):
+        try:
+            lib().vo_destroy(self._h)
+        except Exception:
+            pass
+
+    def forward(self, scene, params: dict, dropout=None, views=None):
+        views = scene.views if views is None else views
+        B = len(views)
+        prm = OParams(**{k: v for k, v in params.items() if k in dict(OParams._fields_)})
+        L, Cn = prm.num_layers, scene.channels
+        prm.num_channels = Cn
+        ov = (OView * B)()
+        for i, v in enumerate(views):
+            ov[i] = OView(v.w, v.h, v.image_index, v.camera_index, v.camera_model, (C.c_float * 5)(*v.crop),
+                          (C.c_float * 4)(*v.rot))
+        sizes = level_sizes(views[0].w, views[0].h, L)
+        color = [np.zeros((B, Cn, h, w), np.float32) for (w, h) in sizes]
+        weight = [np.zeros((B, 1, h, w), np.float32) for (w, h) in sizes]
+        mask = [np.zeros((B, 1, h, w), np.float32) for (w, h) in sizes]
+        depth = [np.zeros((B, 1, h, w), np.float32) for (w, h) in sizes]
+        dro = None if dropout is None else np.ascontiguousarray(dropout, np.float32)
+        self._keep = (scene, prm, ov, dro, sizes, B)
+        F = lib().vo_forward(self._h, C.byref(prm), C.c_int(scene.n), _ptr(scene.position), _ptr(scene.index),
+                             C.c_int(scene.texture.shape[1]), _ptr(scene.texture), _ptr(scene.confidence),
+                             _ptr(scene.background), C.c_int(scene.poses.shape[0]), _ptr(scene.poses),
+                             C.c_int(scene.intrinsics.shape[0]), _ptr(scene.intrinsics), ov, C.c_int(B), _ptr(dro),
+                             _ptr_array(color), _ptr_array(weight), _ptr_array(mask), _ptr_array(depth))
+        if F < 0:
+            raise ValueError("oracle: invalid arguments")
+        self.F = int(F)
+        self.P = int(lib().vo_pixels_per_view(self._h))
+        return dict(color=color, weight=weight, mask=mask, depth=depth, F=self.F)
+
+    def lists(self):
+        """(counts [B*P] int32, keys [F] uint64) of the last forward; keys = depth bits << 32 | point id."""
+        B = self._keep[5]
+        counts = np.zeros(B * self.P, np.int32)
+        keys = np.zeros(self.F, np.uint64)
+        lib().vo_get_lists(self._h, _ptr(counts), _ptr(keys))
+        return counts, keys
+
+    def backward(self, grad_color, want_points=True, want_pose=True, want_intrinsics=True):
+        scene = self._keep[0]
+        Cn, nt, n = scene.channels, scene.texture.shape[1], scene.n
+        n_img, n_cam = scene.poses.shape[0], scene.intrinsics.shape[0]
+        g = [np.ascontiguousarray(x, np.float32) for x in grad_color]
+        out = dict(texture=np.zeros((Cn, nt)), confidence=np.zeros(nt), background=np.zeros(Cn))
+        if want_points:
+            out.update(points=np.zeros((n, 3)), points_count=np.zeros(n))
+        if want_pose:
+            out.update(pose=np.zeros((n_img, 6)), pose_count=np.zeros(n_img))
+        if want_intrinsics:
+            out.update(intrinsics=np.zeros((n_cam, 13)), intrinsics_count=np.zeros(n_cam))
+        lib().vo_backward(self._h, _ptr_array(g), _ptr(out["texture"]), _ptr(out["confidence"]),
+                          _ptr(out["background"]), _ptr(out.get("points")), _ptr(out.get("points_count")),
+                          _ptr(out.get("pose")), _ptr(out.get("pose_count")), _ptr(out.get("intrinsics")),
+                          _ptr(out.get("intrinsics_count")))
+        return out
+
+
+def apply_tangent(tangent: np.ndarray, poses: np.ndarray):
+    """In place: poses <- exp(tangent) * poses, tangent <- 0 (both float64)."""
+    assert tangent.dtype == np.float64 and poses.dtype == np.float64
+    lib().vo_apply_tangent(_ptr(tangent), _ptr(poses), C.c_int(poses.shape[0]))
+
+
+def threads() -> int:
+    return int(lib().vo_threads())

@@ -1,0 +1,851 @@
+// CPU oracle of VET's differentiable blending point rasterizer.
+//
+// TEST INFRASTRUCTURE ONLY.  This file is the checker for the CUDA library: it is linked by nothing
+// that ships.  It restates, on the CPU and in the same order of fp32 operations as the CUDA kernels
+// use for everything that decides a fragment's pixel and depth bits, the algorithm of the reference's
+// rasterizer:
+//
+//   projection            src/lib/rendering/PointRendererHelper.h:184-218, RenderForward.cu:117-158
+//   level loop / counting src/lib/rendering/RenderForward.cu:806-905
+//   scan + list sizes     src/lib/rendering/PointRenderer.cu:788-824
+//   collection            src/lib/rendering/RenderForward.cu:1011-1137
+//   per-pixel sort        src/lib/rendering/AlphaListSort.cu:601-703   (ascending depth)
+//   blend (mode 1)        src/lib/rendering/RenderForward.cu:1303-1357, PointBlending.h:90-129
+//   blend (mode 3)        src/lib/rendering/RenderForward.cu:1539-1644, PointBlending.h:12-44
+//   mask                  src/lib/rendering/PointRenderer.cu:216-235
+//   backward (mode 1)     src/lib/rendering/RenderBackward.cu:1083-1513
+//   backward (mode 3)     src/lib/rendering/RenderBackward.cu:2893-3232
+//   projection backward   src/lib/rendering/PointRendererHelper.h:317-372
+//   normalisation         src/lib/rendering/PointRenderer.cu:1072-1109,1251-1308
+//   tangent application   src/lib/rendering/PointRenderer.cu:1325-1349
+//
+// PARITY UNPINNED for the camera arithmetic: the reference takes TransformPoint, DivideByZ,
+// distortNormalizedPoint, IntrinsicsPinhole::normalizedToImage/scale, ImageView::distanceFromEdge and
+// Sophus::se3_expd from the saiga / Sophus libraries (git submodule External/saiga, no pinned commit,
+// directory empty in the reference snapshot), and ships no test or golden vector for this path.  Those
+// functions are restated here from their published definitions.  The blend algebra IS pinned: the
+// reference's own PointBlending.h is compiled (oracle/Makefile, target _ref) and compared with the
+// functions below by tests/test_oracle_ref_blend.py.
+//
+// Canonical list order: ascending (depth bits, point index).  The reference orders by depth only and
+// leaves equal depths in atomic arrival order; every order it can produce equals the canonical one up
+// to permutations inside runs of equal depth.
+//
+// Build: see oracle/Makefile (-O3 -fopenmp -ffp-contract=off: no fused multiply-add may be formed by
+// the compiler, so that the fp32 results of the projection match the CUDA build made with -fmad=false).
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#ifdef _OPENMP
+#    include <omp.h>
+#endif
+
+namespace
+{
+constexpr int kMaxLayers = 5;  // RenderConstants.h:33
+
+struct OParams  // mirrors the fields of RenderParams the kernels read (Settings.h:19-73)
+{
+    int render_mode;                  // 1 FULL_BLEND, 3 BILINEAR_BLEND (PointRenderer.h: RenderMode)
+    int num_layers;                   // 1..5
+    int num_channels;                 // 3 or 4
+    int drop_out_points_by_radius;    // bool
+    float drop_out_radius_threshold;  // 0.6
+    float dist_cutoff;                // 20
+    int use_environment_map;          // bool: skip the background term
+    int viewer_only;                  // bool: low-confidence discard (RenderForward.cu:168-176)
+    float stability_cutoff_value;     // 10000
+    int debug_max_list_length;        // -1
+    int need_point_gradient;          // bool
+    float K_gradient_factor;          // 0.5
+    float distortion_gradient_factor; // 0.005
+    int output_background_mask;       // bool
+    float output_background_mask_value;
+    int conf_grad_quadratic;          // oracle only: 1 = literal O(n^2) loop of RenderBackward.cu:1160-1178
+    int background_alpha_to_point0;   // quirk: RenderBackward.cu:1130,1157 (mode 1)
+};
+
+struct OView  // ReducedImageInfo, data/SceneData.h:39-50
+{
+    int w, h, image_index, camera_index, camera_model;
+    float crop[5];  // fx fy cx cy s
+    float rot[4];   // row-major 2x2
+};
+
+struct V2
+{
+    float x, y;
+};
+struct V3
+{
+    float x, y, z;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Camera arithmetic (restated from saiga / Sophus; op order is the contract shared with the kernels)
+
+struct Pose
+{
+    float q[4];  // x y z w
+    float t[3];
+};
+
+inline Pose load_pose(const double* p)  // Sophus::SE3d memory: quaternion xyzw, translation, pad; cast per use
+{
+    Pose r;
+    for (int i = 0; i < 4; ++i) r.q[i] = (float)p[i];
+    for (int i = 0; i < 3; ++i) r.t[i] = (float)p[4 + i];
+    return r;
+}
+
+inline V3 cross(V3 a, V3 b) { return {a.y * b.z - a.z * b.y, a.z * b.x - a.x * b.z, a.x * b.y - a.y * b.x}; }
+
+inline V3 rotate(const Pose& P, V3 v)  // Eigen quaternion _transformVector: v + w*uv + qv x uv, uv = 2 qv x v
+{
+    V3 qv{P.q[0], P.q[1], P.q[2]};
+    V3 uv = cross(qv, v);
+    uv    = {uv.x + uv.x, uv.y + uv.y, uv.z + uv.z};
+    V3 c  = cross(qv, uv);
+    float w = P.q[3];
+    return {v.x + w * uv.x + c.x, v.y + w * uv.y + c.y, v.z + w * uv.z + c.z};
+}
+
+inline V3 transform_point(const Pose& P, V3 p)
+{
+    V3 r = rotate(P, p);
+    return {r.x + P.t[0], r.y + P.t[1], r.z + P.t[2]};
+}
+
+inline void rotation_matrix(const Pose& P, float R[9])  // so3().matrix(), Eigen toRotationMatrix order
+{
+    float x = P.q[0], y = P.q[1], z = P.q[2], w = P.q[3];
+    float tx = 2 * x, ty = 2 * y, tz = 2 * z;
+    float twx = tx * w, twy = ty * w, twz = tz * w;
+    float txx = tx * x, txy = ty * x, txz = tz * x;
+    float tyy = ty * y, tyz = tz * y, tzz = tz * z;
+    R[0] = 1 - (tyy + tzz);
+    R[1] = txy - twz;
+    R[2] = txz + twy;
+    R[3] = txy + twz;
+    R[4] = 1 - (txx + tzz);
+    R[5] = tyz - twx;
+    R[6] = txz - twy;
+    R[7] = tyz + twx;
+    R[8] = 1 - (txx + tyy);
+}
+
+// OpenCV rational model, coefficients k1 k2 k3 k4 k5 k6 p1 p2; sentinel 100000 beyond the cutoff radius.
+inline V2 distort(V2 p, const float* d, float cutoff, float* J_p /*2x2*/, float* J_d /*2x8*/)
+{
+    float x = p.x, y = p.y;
+    float x2 = x * x, y2 = y * y, xy = x * y;
+    float r2 = x2 + y2;
+    if (r2 > cutoff * cutoff)
+    {
+        if (J_p) std::fill(J_p, J_p + 4, 0.f);
+        if (J_d) std::fill(J_d, J_d + 16, 0.f);
+        return {100000.f, 100000.f};
+    }
+    float r4 = r2 * r2, r6 = r4 * r2;
+    float k1 = d[0], k2 = d[1], k3 = d[2], k4 = d[3], k5 = d[4], k6 = d[5], p1 = d[6], p2 = d[7];
+    float num    = 1.f + k1 * r2 + k2 * r4 + k3 * r6;
+    float den    = 1.f + k4 * r2 + k5 * r4 + k6 * r6;
+    float radial = num / den;
+    float tx     = 2.f * p1 * xy + p2 * (r2 + 2.f * x2);
+    float ty     = 2.f * p2 * xy + p1 * (r2 + 2.f * y2);
+    V2 out{x * radial + tx, y * radial + ty};
+    if (J_p)
+    {
+        float dnum_dr2 = k1 + 2.f * k2 * r2 + 3.f * k3 * r4;
+        float dden_dr2 = k4 + 2.f * k5 * r2 + 3.f * k6 * r4;
+        float drad_dr2 = (dnum_dr2 * den - num * dden_dr2) / (den * den);
+        float drad_dx = drad_dr2 * 2.f * x, drad_dy = drad_dr2 * 2.f * y;
+        J_p[0] = radial + x * drad_dx + 2.f * p1 * y + p2 * (2.f * x + 4.f * x);
+        J_p[1] = x * drad_dy + 2.f * p1 * x + p2 * (2.f * y);
+        J_p[2] = y * drad_dx + 2.f * p2 * y + p1 * (2.f * x);
+        J_p[3] = radial + y * drad_dy + 2.f * p2 * x + p1 * (2.f * y + 4.f * y);
+    }
+    if (J_d)
+    {
+        float inv_den = 1.f / den;
+        float a       = -num / (den * den);
+        float jx[8]   = {x * r2 * inv_den, x * r4 * inv_den, x * r6 * inv_den, x * a * r2,
+                         x * a * r4,       x * a * r6,       2.f * xy,         r2 + 2.f * x2};
+        float jy[8]   = {y * r2 * inv_den, y * r4 * inv_den, y * r6 * inv_den, y * a * r2,
+                         y * a * r4,       y * a * r6,       r2 + 2.f * y2,    2.f * xy};
+        for (int i = 0; i < 8; ++i)
+        {
+            J_d[i]     = jx[i];
+            J_d[8 + i] = jy[i];
+        }
+    }
+    return out;
+}
+
+// IntrinsicsPinhole::normalizedToImage with coefficients fx fy cx cy s (data/SceneData.h:198-199)
+inline V2 k_apply(const float* K, V2 p) { return {K[0] * p.x + K[4] * p.y + K[2], K[1] * p.y + K[3]}; }
+
+struct Projected
+{
+    V2 ip;
+    float z;
+    float radius_px;
+};
+
+// ProjPoint, RenderForward.cu:117-158 (pinhole branch) on top of ProjectPointPinhole
+inline Projected project(const float* pos4, const Pose& V, const float* intr /*13*/, const OView& cam,
+                         float dist_cutoff)
+{
+    V3 vp   = transform_point(V, {pos4[0], pos4[1], pos4[2]});
+    float z = std::fmax(vp.z, 0.f);
+    V2 np{vp.x / vp.z, vp.y / vp.z};
+    V2 dp = distort(np, intr + 5, dist_cutoff, nullptr, nullptr);
+    if (dp.x == 100000.f) z = 0;
+    V2 ip = k_apply(intr, dp);
+    float radius_px = intr[0] * cam.crop[0] * pos4[3] / z;
+    ip = k_apply(cam.crop, ip);
+    float cx = (float)(cam.w / 2), cy = (float)(cam.h / 2);  // integer division, RenderForward.cu:156
+    float dx = ip.x - cx, dy = ip.y - cy;
+    ip = {cam.rot[0] * dx + cam.rot[1] * dy, cam.rot[2] * dx + cam.rot[3] * dy};
+    ip = {ip.x + cx, ip.y + cy};
+    return {ip, z, radius_px};
+}
+
+inline int round_half_even(float v)  // __float2int_rn; out-of-range and NaN go outside every image
+{
+    if (!(v > -1.0e9f && v < 1.0e9f)) return INT32_MIN;
+    return (int)std::nearbyintf(v);
+}
+inline int round_down(float v)  // __float2int_rd
+{
+    if (!(v > -1.0e9f && v < 1.0e9f)) return INT32_MIN;
+    return (int)std::floor(v);
+}
+
+// compute_blending_fac, PointBlending.h:12-44
+inline void blending_fac(V2 uv, float w[4], float J[8] /*4x2 or null*/)
+{
+    float sx = uv.x - std::floor(uv.x), sy = uv.y - std::floor(uv.y);
+    w[0] = (1 - sx) * (1 - sy);
+    w[1] = sx * (1 - sy);
+    w[2] = (1 - sx) * sy;
+    w[3] = sx * sy;
+    if (J)
+    {
+        J[0] = sy - 1;
+        J[1] = sx - 1;
+        J[2] = 1 - sy;
+        J[3] = -sx;
+        J[4] = -sy;
+        J[5] = 1 - sx;
+        J[6] = sy;
+        J[7] = sx;
+    }
+}
+
+// compute_blend / compute_new_alphadest, PointBlending.h:90-129.  nvcc contracts the reference's
+// `alpha_dest * alpha_s * color + color_dest` into one fused multiply-add; so do we, explicitly.
+inline float blend(float T, float a, float c, float dst) { return std::fmaf(T * a, c, dst); }
+inline float new_T(float T, float a) { return (1 - a) * T; }
+
+struct BackOut
+{
+    float g_point[3], g_pose[6], g_k[5], g_dis[8];
+};
+
+// ProjectPointPinholeBackward, PointRendererHelper.h:317-372
+inline bool project_backward(const float* pos4, V2 grad, const Pose& V, const float* intr, const float cropK[5],
+                             const float rot[4], float dist_cutoff, BackOut& o)
+{
+    std::memset(&o, 0, sizeof(o));
+    V3 vp = transform_point(V, {pos4[0], pos4[1], pos4[2]});
+    if (vp.z <= 0) return false;
+    float R[9];
+    rotation_matrix(V, R);  // J_point
+    // J_pose = [ I | -skew(vp) ]
+    float Jpose[18] = {1, 0, 0, 0,     vp.z,  -vp.y,   //
+                       0, 1, 0, -vp.z, 0,     vp.x,    //
+                       0, 0, 1, vp.y,  -vp.x, 0};
+    float iz = 1.f / vp.z;
+    float Jdiv[6] = {iz, 0, -vp.x * iz * iz, 0, iz, -vp.y * iz * iz};
+    V2 np{vp.x / vp.z, vp.y / vp.z};
+    float Jpd[4], Jdd[16];
+    V2 dp = distort(np, intr + 5, dist_cutoff, Jpd, Jdd);
+    float JpK1[4] = {intr[0], intr[4], 0, intr[1]};
+    float JkK1[10] = {dp.x, 0, 1, 0, dp.y,  //
+                      0, dp.y, 0, 1, 0};
+    float JpK2[4] = {cropK[0], cropK[4], 0, cropK[1]};
+
+    // grad_p_rot = rot^T grad
+    V2 g_rot{rot[0] * grad.x + rot[2] * grad.y, rot[1] * grad.x + rot[3] * grad.y};
+    V2 g_k2{JpK2[0] * g_rot.x + JpK2[2] * g_rot.y, JpK2[1] * g_rot.x + JpK2[3] * g_rot.y};
+    V2 g_k1{JpK1[0] * g_k2.x + JpK1[2] * g_k2.y, JpK1[1] * g_k2.x + JpK1[3] * g_k2.y};
+    V2 g_dis{Jpd[0] * g_k1.x + Jpd[2] * g_k1.y, Jpd[1] * g_k1.x + Jpd[3] * g_k1.y};
+    float g_view[3] = {Jdiv[0] * g_dis.x + Jdiv[3] * g_dis.y, Jdiv[1] * g_dis.x + Jdiv[4] * g_dis.y,
+                       Jdiv[2] * g_dis.x + Jdiv[5] * g_dis.y};
+    for (int k = 0; k < 3; ++k) o.g_point[k] = R[0 + k] * g_view[0] + R[3 + k] * g_view[1] + R[6 + k] * g_view[2];
+    for (int k = 0; k < 6; ++k)
+        o.g_pose[k] = Jpose[0 + k] * g_view[0] + Jpose[6 + k] * g_view[1] + Jpose[12 + k] * g_view[2];
+    for (int k = 0; k < 5; ++k) o.g_k[k] = JkK1[k] * g_k2.x + JkK1[5 + k] * g_k2.y;
+    for (int k = 0; k < 8; ++k) o.g_dis[k] = Jdd[k] * g_k1.x + Jdd[8 + k] * g_k1.y;
+    return true;
+}
+
+struct Level
+{
+    int w, h;
+    int64_t base;  // offset of this level inside one view's pyramid
+};
+
+struct Oracle
+{
+    OParams prm{};
+    int B = 0, L = 0, C = 0;
+    int64_t P = 0;  // pyramid pixels per view
+    Level lv[kMaxLayers]{};
+    std::vector<OView> views;
+    std::vector<int32_t> count;    // [B*P]
+    std::vector<int64_t> start;    // [B*P + 1] exclusive scan
+    std::vector<uint64_t> keys;    // [F] sorted per pixel: depth bits << 32 | point id
+    std::vector<float> uv;         // mode 3: [F,2] level-space ip of the fragment (per_point_data cols 1,2)
+    std::vector<uint8_t> corner;   // mode 3: [F] blend index (per_point_data col 3)
+    std::vector<std::vector<float>> out_color;  // per level [B,C,h,w]
+    // inputs kept for backward
+    int n = 0, n_tex = 0, n_img = 0, n_cam = 0;
+    const float* position = nullptr;
+    const int* index      = nullptr;
+    const float* texture  = nullptr;
+    const float* conf     = nullptr;
+    const float* bg       = nullptr;
+    const double* poses   = nullptr;
+    const float* intr     = nullptr;
+};
+
+void setup_levels(Oracle& o, int w, int h)
+{
+    int64_t base = 0;
+    for (int l = 0; l < o.L; ++l)
+    {
+        o.lv[l] = {w, h, base};
+        base += (int64_t)w * h;
+        w /= 2;  // PointRenderer.cu:378-380
+        h /= 2;
+    }
+    o.P = base;
+}
+
+// Visits every fragment of one point in one view in the order of the level loop.
+template <class F>
+inline void for_fragments(const Oracle& o, int b, int pid, const float* dropout, F&& f)
+{
+    const OParams& prm = o.prm;
+    if (dropout && dropout[(int64_t)b * o.n + pid] == 1.f) return;
+    int tex = o.index[pid];
+    if (prm.viewer_only && o.conf[tex] < prm.stability_cutoff_value) return;  // RenderForward.cu:168-176
+    const OView& cam = o.views[b];
+    Pose V           = load_pose(o.poses + 8 * cam.image_index);
+    Projected pr     = project(o.position + 4 * pid, V, o.intr + 13 * cam.camera_index, cam, prm.dist_cutoff);
+    if (pr.z == 0) return;
+    V2 ip        = pr.ip;
+    float radius = pr.radius_px;
+    uint32_t zb;
+    std::memcpy(&zb, &pr.z, 4);
+    for (int l = 0; l < o.L; ++l, radius *= 0.5f, ip = {ip.x * 0.5f, ip.y * 0.5f})
+    {
+        if (prm.drop_out_points_by_radius && radius < prm.drop_out_radius_threshold) break;
+        const Level& lv = o.lv[l];
+        if (prm.render_mode == 3)
+        {
+            int bx = round_down(ip.x), by = round_down(ip.y);
+            for (int yj = 0; yj <= 1; ++yj)
+                for (int xi = 0; xi <= 1; ++xi)
+                {
+                    int64_t x = (int64_t)bx + xi, y = (int64_t)by + yj;
+                    if (x < 0 || y < 0 || x >= lv.w || y >= lv.h) continue;
+                    f(l, (int)x, (int)y, zb, ip, yj * 2 + xi);
+                }
+        }
+        else
+        {
+            int x = round_half_even(ip.x), y = round_half_even(ip.y);
+            if (x < 0 || y < 0 || x >= lv.w || y >= lv.h) continue;
+            f(l, x, y, zb, ip, 0);
+        }
+    }
+}
+
+}  // namespace
+
+extern "C"
+{
+void* vo_create() { return new Oracle(); }
+void vo_destroy(void* h) { delete (Oracle*)h; }
+int vo_threads()
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+// Forward.  out_color[l] is [B,C,h_l,w_l]; out_weight[l], out_mask[l] (nullable), out_depth[l] (nullable) are
+// [B,1,h_l,w_l].  Returns the number of fragments F, or a negative value on invalid arguments.
+int64_t vo_forward(void* h, const OParams* prm, int n, const float* position, const int* index, int n_tex,
+                   const float* texture, const float* confidence, const float* background, int n_img,
+                   const double* poses, int n_cam, const float* intrinsics, const OView* views, int B,
+                   const float* dropout, float* const* out_color, float* const* out_weight, float* const* out_mask,
+                   float* const* out_depth)
+{
+    Oracle& o = *(Oracle*)h;
+    if (prm->num_layers < 1 || prm->num_layers > kMaxLayers || B < 1) return -1;
+    if (prm->render_mode != 1 && prm->render_mode != 3) return -1;
+    for (int b = 0; b < B; ++b)
+        if (views[b].camera_model != 0 || views[b].w != views[0].w || views[b].h != views[0].h) return -1;
+    o.prm = *prm;
+    o.B = B, o.L = prm->num_layers, o.C = prm->num_channels;
+    o.views.assign(views, views + B);
+    o.n = n, o.n_tex = n_tex, o.n_img = n_img, o.n_cam = n_cam;
+    o.position = position, o.index = index, o.texture = texture, o.conf = confidence, o.bg = background;
+    o.poses = poses, o.intr = intrinsics;
+    setup_levels(o, views[0].w, views[0].h);
+    const bool bilinear = prm->render_mode == 3;
+    const int64_t PT    = o.P * B;
+
+    // counting pass
+    o.count.assign(PT, 0);
+    for (int b = 0; b < B; ++b)
+    {
+        int32_t* cnt = o.count.data() + b * o.P;
+#pragma omp parallel for schedule(static)
+        for (int pid = 0; pid < n; ++pid)
+            for_fragments(o, b, pid, dropout, [&](int l, int x, int y, uint32_t, V2, int) {
+#pragma omp atomic
+                cnt[o.lv[l].base + (int64_t)y * o.lv[l].w + x] += 1;
+            });
+    }
+    // scan
+    o.start.resize(PT + 1);
+    int64_t acc = 0;
+    for (int64_t i = 0; i < PT; ++i)
+    {
+        o.start[i] = acc;
+        acc += o.count[i];
+    }
+    o.start[PT]     = acc;
+    const int64_t F = acc;
+    o.keys.resize(F);
+    if (bilinear)
+    {
+        o.uv.resize(2 * F);
+        o.corner.resize(F);
+    }
+    // collection pass (serial over points per view so that the cursor needs no atomics across the big arrays)
+    std::vector<int32_t> cursor(PT, 0);
+    std::vector<uint32_t> aux;  // mode 3: arrival slot -> (uv, corner) before sorting
+    std::vector<float> uv_unsorted;
+    std::vector<uint8_t> corner_unsorted;
+    if (bilinear)
+    {
+        uv_unsorted.resize(2 * F);
+        corner_unsorted.resize(F);
+    }
+    for (int b = 0; b < B; ++b)
+    {
+        const int64_t vb = b * o.P;
+#pragma omp parallel for schedule(static)
+        for (int pid = 0; pid < n; ++pid)
+            for_fragments(o, b, pid, dropout, [&](int l, int x, int y, uint32_t zb, V2 ip, int corner) {
+                int64_t g = vb + o.lv[l].base + (int64_t)y * o.lv[l].w + x;
+                int32_t pos;
+#pragma omp atomic capture
+                pos = cursor[g]++;
+                int64_t slot  = o.start[g] + pos;
+                o.keys[slot]  = ((uint64_t)zb << 32) | (uint32_t)pid;
+                if (bilinear)
+                {
+                    uv_unsorted[2 * slot]     = ip.x;
+                    uv_unsorted[2 * slot + 1] = ip.y;
+                    corner_unsorted[slot]     = (uint8_t)corner;
+                }
+            });
+    }
+    // sort every list by (depth bits, point id); mode 3 carries uv and corner along
+#pragma omp parallel
+    {
+        std::vector<std::pair<uint64_t, int64_t>> tmp;
+#pragma omp for schedule(dynamic, 4096)
+        for (int64_t g = 0; g < PT; ++g)
+        {
+            int64_t s = o.start[g], e = o.start[g + 1];
+            if (e - s == 0) continue;
+            if (!bilinear)
+            {
+                if (e - s > 1) std::sort(o.keys.begin() + s, o.keys.begin() + e);
+                continue;
+            }
+            tmp.clear();
+            for (int64_t i = s; i < e; ++i) tmp.push_back({o.keys[i], i});
+            std::sort(tmp.begin(), tmp.end());
+            for (int64_t i = s; i < e; ++i)
+            {
+                int64_t src       = tmp[i - s].second;
+                o.keys[i]         = tmp[i - s].first;
+                o.uv[2 * i]       = uv_unsorted[2 * src];
+                o.uv[2 * i + 1]   = uv_unsorted[2 * src + 1];
+                o.corner[i]       = corner_unsorted[src];
+            }
+        }
+    }
+    // blend
+    const int C = o.C;
+    o.out_color.resize(o.L);
+    for (int l = 0; l < o.L; ++l)
+    {
+        const Level& lv = o.lv[l];
+        const int64_t hw = (int64_t)lv.w * lv.h;
+        o.out_color[l].assign((size_t)B * C * hw, 0.f);
+#pragma omp parallel for schedule(dynamic, 64) collapse(2)
+        for (int b = 0; b < B; ++b)
+            for (int y = 0; y < lv.h; ++y)
+                for (int x = 0; x < lv.w; ++x)
+                {
+                    int64_t g  = b * o.P + lv.base + (int64_t)y * lv.w + x;
+                    int64_t s  = o.start[g];
+                    int cnt    = o.count[g];
+                    if (prm->debug_max_list_length > 0) cnt = std::min(prm->debug_max_list_length, cnt);
+                    float T    = 1.f;
+                    float c[4] = {0, 0, 0, 0};
+                    for (int i = 0; i < cnt; ++i)
+                    {
+                        int pid   = (int)(uint32_t)o.keys[s + i];
+                        int tex   = index[pid];
+                        float a   = confidence[tex];
+                        if (bilinear)
+                        {
+                            float w4[4];
+                            blending_fac({o.uv[2 * (s + i)], o.uv[2 * (s + i) + 1]}, w4, nullptr);
+                            a = w4[o.corner[s + i]] * a;
+                        }
+                        for (int ci = 0; ci < C; ++ci) c[ci] = blend(T, a, texture[(int64_t)ci * n_tex + tex], c[ci]);
+                        T = new_T(T, a);
+                        if (bilinear && T < 0.001f) break;
+                    }
+                    for (int ci = 0; ci < C; ++ci)
+                    {
+                        bool add_bg = !prm->use_environment_map && !(bilinear && !(T >= 0.001f));
+                        if (add_bg) c[ci] = blend(T, 1.f, background[ci], c[ci]);
+                        float v = c[ci];
+                        o.out_color[l][((int64_t)b * C + ci) * hw + (int64_t)y * lv.w + x] = v;
+                        if (out_color) out_color[l][((int64_t)b * C + ci) * hw + (int64_t)y * lv.w + x] = v;
+                    }
+                    int64_t pi = (int64_t)b * hw + (int64_t)y * lv.w + x;
+                    if (out_weight) out_weight[l][pi] = T;
+                    if (out_mask) out_mask[l][pi] = (T == 0.f) ? prm->output_background_mask_value : 1.f;
+                    if (out_depth)
+                    {
+                        float d = 100000.f;  // MAX_DEPTH_CONST; atomicMin of depth bits == first list entry
+                        if (o.count[g] > 0)
+                        {
+                            uint32_t zb = (uint32_t)(o.keys[s] >> 32);
+                            std::memcpy(&d, &zb, 4);
+                        }
+                        out_depth[l][pi] = d;
+                    }
+                }
+    }
+    return F;
+}
+
+int64_t vo_pixels_per_view(void* h) { return ((Oracle*)h)->P; }
+
+// Copies the per-pixel counts [B*P] and the sorted keys [F] of the last forward.
+void vo_get_lists(void* h, int32_t* counts, uint64_t* keys)
+{
+    Oracle& o = *(Oracle*)h;
+    if (counts) std::memcpy(counts, o.count.data(), o.count.size() * sizeof(int32_t));
+    if (keys) std::memcpy(keys, o.keys.data(), o.keys.size() * sizeof(uint64_t));
+}
+
+// Backward of the last forward.  grad_color[l] is [B,C,h_l,w_l].  All outputs are RAW SUMS in double
+// (each addend computed in fp32 exactly as the reference computes it, then accumulated in fp64 so that
+// the oracle carries no summation-order noise of its own):
+//   g_texture [C,n_tex], g_confidence [n_tex], g_background [C], g_points [n,3], g_points_count [n],
+//   g_pose [n_img,6], g_pose_count [n_img], g_intr [n_cam,13], g_intr_count [n_cam].  Nullable from g_points on.
+int vo_backward(void* h, const float* const* grad_color, double* g_texture, double* g_confidence,
+                double* g_background, double* g_points, double* g_points_count, double* g_pose, double* g_pose_count,
+                double* g_intr, double* g_intr_count)
+{
+    Oracle& o          = *(Oracle*)h;
+    const OParams& prm = o.prm;
+    const int C = o.C, B = o.B;
+    const bool bilinear = prm.render_mode == 3;
+    const int n_tex     = o.n_tex;
+    std::fill(g_texture, g_texture + (int64_t)C * n_tex, 0.0);
+    std::fill(g_confidence, g_confidence + n_tex, 0.0);
+    std::fill(g_background, g_background + C, 0.0);
+    if (g_points) std::fill(g_points, g_points + 3 * (int64_t)o.n, 0.0);
+    if (g_points_count) std::fill(g_points_count, g_points_count + o.n, 0.0);
+    if (g_pose) std::fill(g_pose, g_pose + 6 * o.n_img, 0.0);
+    if (g_pose_count) std::fill(g_pose_count, g_pose_count + o.n_img, 0.0);
+    if (g_intr) std::fill(g_intr, g_intr + 13 * o.n_cam, 0.0);
+    if (g_intr_count) std::fill(g_intr_count, g_intr_count + o.n_cam, 0.0);
+
+    std::vector<float> galpha;  // mode 3: gradient_sum_backwards row 0
+    if (bilinear) galpha.assign(o.keys.size(), 0.f);
+
+    for (int l = 0; l < o.L; ++l)
+    {
+        const Level& lv  = o.lv[l];
+        const int64_t hw = (int64_t)lv.w * lv.h;
+        float level_scale = 1.f;
+        for (int i = 0; i < l; ++i) level_scale *= 0.5f;  // powf(0.5f, layer) is exact
+        for (int b = 0; b < B; ++b)
+        {
+            const OView& cam = o.views[b];
+            const float* G   = grad_color[l] + (int64_t)b * C * hw;
+            const float* I   = o.out_color[l].data() + (int64_t)b * C * hw;
+            Pose V           = load_pose(o.poses + 8 * cam.image_index);
+            const float* K   = o.intr + 13 * cam.camera_index;
+            float crop2[5];
+            for (int k = 0; k < 5; ++k) crop2[k] = cam.crop[k] * level_scale;  // IntrinsicsPinhole::scale
+            // Serial over pixels: the accumulators are shared and this function is the checker, not the timed path.
+            for (int y = 0; y < lv.h; ++y)
+                for (int x = 0; x < lv.w; ++x)
+                {
+                    int64_t g = b * o.P + lv.base + (int64_t)y * lv.w + x;
+                    int64_t s = o.start[g];
+                    int cnt   = o.count[g];
+                    if (prm.debug_max_list_length > 0) cnt = std::min(prm.debug_max_list_length, cnt);
+                    float gin[4];
+                    for (int ci = 0; ci < C; ++ci) gin[ci] = G[ci * hw + (int64_t)y * lv.w + x];
+
+                    auto alpha_of = [&](int j) {
+                        int tex = o.index[(int)(uint32_t)o.keys[s + j]];
+                        float a = o.conf[tex];
+                        if (bilinear)
+                        {
+                            float w4[4];
+                            blending_fac({o.uv[2 * (s + j)], o.uv[2 * (s + j) + 1]}, w4, nullptr);
+                            a = w4[o.corner[s + j]] * a;
+                        }
+                        return a;
+                    };
+
+                    // (i) colour / alpha gradients: RenderBackward.cu:1118-1181 and :2936-3019
+                    {
+                        float T       = 1.f;
+                        const int cnt0 = cnt;
+                        int list_size = prm.use_environment_map ? cnt : cnt + 1;
+                        // O(n) form needs the per-entry weights first
+                        std::vector<float> Ti, ai, doti;
+                        int processed = 0;
+                        for (int i = 0; i < list_size; ++i)
+                        {
+                            bool fg  = i != cnt;
+                            int tex  = fg ? o.index[(int)(uint32_t)o.keys[s + i]] : 0;
+                            float a  = fg ? alpha_of(i) : 1.f;
+                            float col[4];
+                            for (int ci = 0; ci < C; ++ci) col[ci] = fg ? o.texture[(int64_t)ci * n_tex + tex] : o.bg[ci];
+                            float g_alpha = 0;
+                            for (int ci = 0; ci < C; ++ci)
+                            {
+                                float g_col = T * a * gin[ci];
+                                if (fg)
+                                    g_texture[(int64_t)ci * n_tex + tex] += (double)g_col;
+                                else
+                                    g_background[ci] += (double)g_col;
+                                g_alpha += col[ci] * gin[ci];
+                            }
+                            g_alpha *= T;
+                            if (!bilinear)
+                            {
+                                if (fg || prm.background_alpha_to_point0) g_confidence[tex] += (double)g_alpha;
+                            }
+                            else if (fg)
+                                galpha[s + i] += g_alpha;
+
+                            if (prm.conf_grad_quadratic)
+                            {
+                                for (int j = 0; j < i; ++j)
+                                {
+                                    float aj     = alpha_of(j);
+                                    float g_iter = 0;
+                                    for (int ci = 0; ci < C; ++ci)
+                                        g_iter -= (gin[ci] * col[ci] * T * a / (1 - aj + 1e-9f));
+                                    if (!bilinear)
+                                        g_confidence[o.index[(int)(uint32_t)o.keys[s + j]]] += (double)g_iter;
+                                    else
+                                        galpha[s + j] += g_iter;
+                                }
+                            }
+                            else
+                            {
+                                float dot = 0;
+                                for (int ci = 0; ci < C; ++ci) dot += gin[ci] * col[ci];
+                                Ti.push_back(T), ai.push_back(a), doti.push_back(dot);
+                            }
+                            processed = i + 1;
+                            T         = new_T(T, a);
+                            if (bilinear && T < 0.001f)
+                            {
+                                if (fg) cnt = i + 1;
+                                break;
+                            }
+                        }
+                        if (!prm.conf_grad_quadratic)
+                        {
+                            // d alpha_j -= S_j / (1 - alpha_j + eps),  S_j = sum_{i>j} T_i alpha_i (d_i . G)
+                            double S = 0;
+                            for (int j = processed - 1; j >= 0; --j)
+                            {
+                                if (j < cnt0)
+                                {
+                                    double sub = -S / (double)(1 - ai[j] + 1e-9f);
+                                    if (!bilinear)
+                                        g_confidence[o.index[(int)(uint32_t)o.keys[s + j]]] += sub;
+                                    else
+                                        galpha[s + j] += (float)sub;
+                                }
+                                S += (double)(Ti[j] * ai[j] * doti[j]);
+                            }
+                        }
+                    }
+
+                    // (ii) spatial gradients
+                    int dist_edge = std::min(std::min(x, lv.w - 1 - x), std::min(y, lv.h - 1 - y));
+                    if (!(dist_edge > 2)) continue;
+                    if (!bilinear && !prm.need_point_gradient) continue;
+                    for (int i = 0; i < cnt; ++i)
+                    {
+                        int pid = (int)(uint32_t)o.keys[s + i];
+                        int tex = o.index[pid];
+                        V2 dR;
+                        if (!bilinear)
+                        {
+                            float dx = 0, dy = 0;
+                            for (int ci = 0; ci < C; ++ci)
+                            {
+                                float Tp = o.texture[(int64_t)ci * n_tex + tex];
+                                auto at  = [&](const float* img, int xx, int yy) { return img[ci * hw + (int64_t)yy * lv.w + xx]; };
+                                float a0 = -(Tp - at(I, x - 1, y)) * at(G, x - 1, y);
+                                float a1 = (Tp - at(I, x + 1, y)) * at(G, x + 1, y);
+                                float b0 = -(Tp - at(I, x, y - 1)) * at(G, x, y - 1);
+                                float b1 = (Tp - at(I, x, y + 1)) * at(G, x, y + 1);
+                                dx += 0.5f * (a0 + a1);
+                                dy += 0.5f * (b0 + b1);
+                            }
+                            dR = {dx / (float)C, dy / (float)C};
+                        }
+                        else
+                        {
+                            float w4[4], J[8];
+                            blending_fac({o.uv[2 * (s + i)], o.uv[2 * (s + i) + 1]}, w4, J);
+                            int bi        = o.corner[s + i];
+                            float ga      = galpha[s + i];
+                            g_confidence[tex] += (double)(w4[bi] * ga);  // RenderBackward.cu:3076-3079
+                            if (!prm.need_point_gradient) continue;
+                            float single = o.conf[tex] * ga;
+                            dR = {J[2 * bi] * single, J[2 * bi + 1] * single};
+                        }
+                        BackOut bo;
+                        if (!project_backward(o.position + 4 * pid, dR, V, K, crop2, cam.rot, prm.dist_cutoff, bo)) continue;
+                        if (g_points)
+                        {
+                            for (int k = 0; k < 3; ++k) g_points[3 * (int64_t)pid + k] += (double)bo.g_point[k];
+                            g_points_count[pid] += 1.0;
+                        }
+                        if (g_pose)
+                        {
+                            for (int k = 0; k < 6; ++k) g_pose[6 * cam.image_index + k] += (double)bo.g_pose[k];
+                            g_pose_count[cam.image_index] += bilinear ? 1.0 : (double)(1.f / 1024.f);
+                        }
+                        if (g_intr)
+                        {
+                            bo.g_k[4] *= 0;
+                            for (int k = 0; k < 5; ++k) g_intr[13 * cam.camera_index + k] += (double)(prm.K_gradient_factor * bo.g_k[k]);
+                            bo.g_dis[2] *= 0.25f;
+                            for (int k = 3; k < 8; ++k) bo.g_dis[k] *= 0.1f;
+                            for (int k = 0; k < 8; ++k)
+                                g_intr[13 * cam.camera_index + 5 + k] += (double)(prm.distortion_gradient_factor * bo.g_dis[k]);
+                            g_intr_count[cam.camera_index] += (double)(1.f / 1024.f);
+                        }
+                    }
+                }
+        }
+    }
+    return 0;
+}
+
+// ApplyTangent, PointRenderer.cu:1325-1341: pose <- exp_se3(tangent) * pose, tangent <- 0, in double.
+// Tangent = (translation part, rotation part) as Sophus::SE3d::exp consumes it.
+void vo_apply_tangent(double* tangent, double* poses, int n)
+{
+    for (int i = 0; i < n; ++i)
+    {
+        double* t = tangent + 6 * i;
+        double* p = poses + 8 * i;
+        double ux = t[0], uy = t[1], uz = t[2], wx = t[3], wy = t[4], wz = t[5];
+        double th2 = wx * wx + wy * wy + wz * wz, th = std::sqrt(th2);
+        // SO3 exp -> quaternion
+        double imag, real;
+        if (th < 1e-10)
+        {
+            double th4 = th2 * th2;
+            imag = 0.5 - th2 / 48.0 + th4 / 3840.0;
+            real = 1.0 - th2 / 8.0 + th4 / 384.0;
+        }
+        else
+        {
+            imag = std::sin(0.5 * th) / th;
+            real = std::cos(0.5 * th);
+        }
+        double qe[4] = {imag * wx, imag * wy, imag * wz, real};
+        // V = I + a*Omega + b*Omega^2
+        double a, bb;
+        if (th < 1e-10)
+        {
+            a  = 0.5;
+            bb = 1.0 / 6.0;
+        }
+        else
+        {
+            a  = (1 - std::cos(th)) / th2;
+            bb = (th - std::sin(th)) / (th2 * th);
+        }
+        double O[9]  = {0, -wz, wy, wz, 0, -wx, -wy, wx, 0};
+        double O2[9];
+        for (int r = 0; r < 3; ++r)
+            for (int c = 0; c < 3; ++c) O2[3 * r + c] = O[3 * r] * O[c] + O[3 * r + 1] * O[3 + c] + O[3 * r + 2] * O[6 + c];
+        double u[3] = {ux, uy, uz}, te[3];
+        for (int r = 0; r < 3; ++r)
+        {
+            te[r] = u[r];
+            for (int c = 0; c < 3; ++c) te[r] += (a * O[3 * r + c] + bb * O2[3 * r + c]) * u[c];
+        }
+        // compose: q = qe * qp ; t = Re * tp + te
+        double x1 = qe[0], y1 = qe[1], z1 = qe[2], w1 = qe[3];
+        double x2 = p[0], y2 = p[1], z2 = p[2], w2 = p[3];
+        double q[4] = {w1 * x2 + x1 * w2 + y1 * z2 - z1 * y2, w1 * y2 - x1 * z2 + y1 * w2 + z1 * x2,
+                       w1 * z2 + x1 * y2 - y1 * x2 + z1 * w2, w1 * w2 - x1 * x2 - y1 * y2 - z1 * z2};
+        double nrm = std::sqrt(q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3]);
+        for (double& v : q) v /= nrm;
+        // rotate tp by qe
+        double tp[3] = {p[4], p[5], p[6]};
+        double cx = y1 * tp[2] - z1 * tp[1], cy = z1 * tp[0] - x1 * tp[2], cz = x1 * tp[1] - y1 * tp[0];
+        cx *= 2, cy *= 2, cz *= 2;
+        double rx = tp[0] + w1 * cx + (y1 * cz - z1 * cy);
+        double ry = tp[1] + w1 * cy + (z1 * cx - x1 * cz);
+        double rz = tp[2] + w1 * cz + (x1 * cy - y1 * cx);
+        p[0] = q[0], p[1] = q[1], p[2] = q[2], p[3] = q[3];
+        p[4] = rx + te[0], p[5] = ry + te[1], p[6] = rz + te[2];
+        for (int k = 0; k < 6; ++k) t[k] = 0;
+    }
+}
+}  // extern "C"

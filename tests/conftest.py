@@ -1,0 +1,23 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def rasterizer():
+    import torch
+    from vet_b200.render import Rasterizer
+
+    assert torch.cuda.is_available(), "gpu tests need a CUDA device"
+    r = Rasterizer(0)
+    yield r
+    r.close()

@@ -1,0 +1,179 @@
+"""CUDA library vs CPU oracle on identical seeded inputs, through the C ABI (vet_b200.render -> libvetr.so).
+
+Bar: per-pixel counts, fragment keys and their order bit-exact; images within 1e-5 relative (they are in fact
+bit-equal, the blend is evaluated in the same order with the same fused multiply-add); raw gradient sums within
+1e-5 relative with a floor of 1e-5 x the tensor's largest magnitude (fp32 atomic summation order is not defined).
+"""
+import numpy as np
+import pytest
+
+from tests import util
+from vet_b200 import scenes
+from vet_b200.render import default_params
+
+pytestmark = pytest.mark.gpu
+
+
+def _roundtrip(rast, scene, params, dropout=None, exact_images=True, grads="random"):
+    ora = util.run_oracle(scene, params, dropout=dropout)
+    g = util.random_grads(ora["fwd"]["color"], seed=3) if grads == "random" else util.l1_grads(ora["fwd"]["color"], seed=3)
+    ora = util.run_oracle(scene, params, grads=g, dropout=dropout)
+    gpu = util.run_gpu(rast, scene, params, grads=g, dropout=dropout)
+    util.compare_forward(gpu, ora, exact_images=exact_images)
+    util.compare_backward(gpu["bwd_raw"], ora["bwd"], scene.channels)
+    return gpu, ora
+
+
+@pytest.mark.parametrize("mode", [1, 3])
+@pytest.mark.parametrize("crop", [False, True])
+def test_tiny_scene(rasterizer, mode, crop):
+    sc = scenes.tiny_scene(n=3000, crop=crop)
+    _roundtrip(rasterizer, sc, default_params(render_mode=mode))
+
+
+@pytest.mark.parametrize("mode", [1, 3])
+def test_dense_lists_no_radius_dropout(rasterizer, mode):
+    """Every visible point reaches all levels: lists of hundreds of fragments at the coarse levels."""
+    sc = scenes.tiny_scene(n=40000, w=96, h=64, n_views=2, seed=11)
+    gpu, _ = _roundtrip(rasterizer, sc, default_params(render_mode=mode, drop_out_points_by_radius=0))
+    assert gpu["longest"] > 200
+
+
+@pytest.mark.parametrize("mode", [1, 3])
+def test_long_list_slow_path(rasterizer, mode):
+    """Lists beyond the shared-memory fast path (> 1024 fragments in one pixel)."""
+    sc = scenes.tiny_scene(n=30000, w=16, h=12, n_views=1, seed=5)
+    gpu, _ = _roundtrip(rasterizer, sc, default_params(render_mode=mode, drop_out_points_by_radius=0, num_layers=3))
+    assert gpu["longest"] > 2048 + 100
+
+
+def test_three_channels_env_map_and_truncation(rasterizer):
+    sc = scenes.tiny_scene(n=4000, channels=3, seed=21)
+    _roundtrip(rasterizer, sc, default_params(use_environment_map=1))
+    _roundtrip(rasterizer, sc, default_params(debug_max_list_length=3))
+    _roundtrip(rasterizer, sc, default_params(render_mode=3, debug_max_list_length=2, num_layers=2))
+
+
+def test_dropout_mask_and_viewer_discard(rasterizer):
+    sc = scenes.tiny_scene(n=3000, seed=31)
+    rng = np.random.default_rng(0)
+    dropout = (rng.uniform(size=(len(sc.views), sc.n)) < 0.25).astype(np.float32)
+    _roundtrip(rasterizer, sc, default_params(), dropout=dropout)
+    _roundtrip(rasterizer, sc, default_params(viewer_only=1, stability_cutoff_value=0.4))
+
+
+def test_flags_off(rasterizer):
+    sc = scenes.tiny_scene(n=3000, seed=41)
+    _roundtrip(rasterizer, sc, default_params(need_point_gradient=0))
+    _roundtrip(rasterizer, sc, default_params(background_alpha_to_point0=0))
+    _roundtrip(rasterizer, sc, default_params(render_mode=3, need_point_gradient=0))
+
+
+def test_distortion(rasterizer):
+    sc = scenes.tiny_scene(n=3000, seed=51, crop=True)
+    sc.intrinsics[0, 5:] = np.array([0.05, -0.02, 0.003, 0.01, 0.002, -0.001, 0.004, -0.003], np.float32)
+    sc.intrinsics[0, 4] = 0.01
+    _roundtrip(rasterizer, sc, default_params())
+    _roundtrip(rasterizer, sc, default_params(render_mode=3, dist_cutoff=0.5))
+
+
+def test_empty_and_degenerate(rasterizer):
+    sc = scenes.tiny_scene(n=64, w=8, h=8, n_views=1, seed=61)
+    sc.position[:, :3] += 100.0  # everything outside the frustum: all lists empty
+    gpu, ora = _roundtrip(rasterizer, sc, default_params())
+    assert gpu["F"] == 0
+    sc2 = scenes.tiny_scene(n=1, w=5, h=3, n_views=1, seed=62)
+    _roundtrip(rasterizer, sc2, default_params(num_layers=1))
+    _roundtrip(rasterizer, sc2, default_params(num_layers=5))
+
+
+def test_many_views_grouped(rasterizer):
+    """More views than one launch takes: the host mirror splits the batch."""
+    sc = scenes.tiny_scene(n=2000, w=40, h=30, n_views=11, seed=71)
+    ora = util.run_oracle(sc, default_params())
+    gpu = util.run_gpu(rasterizer, sc, default_params())
+    assert gpu["F"] == ora["F"]
+    for a, b in zip(gpu["fwd"]["color"], ora["fwd"]["color"]):
+        np.testing.assert_array_equal(a, b)
+
+
+def test_plumbing_config_l1(rasterizer):
+    """Configuration 1 of the benchmark set: 100k points, one 512x512 view, L1 loss against a seeded target."""
+    sc = scenes.config_plumbing()
+    _roundtrip(rasterizer, sc, default_params(), grads="l1")
+    _roundtrip(rasterizer, sc, default_params(render_mode=3), grads="l1")
+
+
+def test_key_buffer_overflow_is_reported(rasterizer):
+    from vet_b200 import _lib as L
+
+    sc = scenes.tiny_scene(n=3000, seed=81)
+    with pytest.raises(L.VetrError) as e:
+        util.run_gpu(rasterizer, sc, default_params(), capacity=100)
+    assert e.value.status == L.E_LIST_OVERFLOW
+
+
+def test_reference_layout_of_lists(rasterizer):
+    """vetr_get_lists: collections [2,F_l] (depth bits, point index) and scanned_counting per (view, layer)."""
+    import torch
+
+    sc = scenes.tiny_scene(n=3000, seed=91)
+    params = default_params()
+    ora = util.run_oracle(sc, params)
+    util.run_gpu(rasterizer, sc, params)
+    P = ora["counts"].size // len(sc.views)
+    starts = np.concatenate([[0], np.cumsum(ora["counts"])])
+    sizes = [(sc.views[0].w >> l, sc.views[0].h >> l) for l in range(4)]
+    base = 0
+    for layer, (w, h) in enumerate(sizes):
+        for view in range(len(sc.views)):
+            g0 = view * P + base
+            coll, scanned = rasterizer.lists_of(view, layer)
+            coll, scanned = coll.cpu().numpy(), scanned.cpu().numpy()
+            keys = ora["keys"][starts[g0]:starts[g0 + w * h]]
+            np.testing.assert_array_equal(coll[0].view(np.uint32), (keys >> np.uint64(32)).astype(np.uint32))
+            np.testing.assert_array_equal(coll[1].view(np.uint32), (keys & np.uint64(0xffffffff)).astype(np.uint32))
+            np.testing.assert_array_equal(scanned, starts[g0:g0 + w * h] - starts[g0])
+        base += w * h
+
+
+def test_apply_tangent(rasterizer):
+    import torch
+    from oracle import oracle as O
+
+    rng = np.random.default_rng(5)
+    n = 37
+    poses = scenes.orbit_poses(rng, n, 4.0)
+    tangent = rng.normal(scale=0.05, size=(n, 6))
+    tangent[0] = 0.0
+    tangent[1, 3:] = 1e-13
+    p_ref, t_ref = poses.copy(), tangent.copy()
+    O.apply_tangent(t_ref, p_ref)
+    p = torch.from_numpy(poses).cuda()
+    t = torch.from_numpy(tangent).cuda()
+    rasterizer.apply_tangent(t, p)
+    np.testing.assert_allclose(p.cpu().numpy(), p_ref, rtol=0, atol=1e-12)
+    assert float(t.abs().max()) == 0.0
+
+
+def test_finalize_matches_reference_normalisation(rasterizer):
+    import torch
+
+    sc = scenes.tiny_scene(n=3000, seed=101)
+    params = default_params()
+    ora = util.run_oracle(sc, params)
+    g = util.random_grads(ora["fwd"]["color"], seed=1)
+    ora = util.run_oracle(sc, params, grads=g)
+    util.run_gpu(rasterizer, sc, params)
+    raw = rasterizer.backward_raw([torch.from_numpy(x).cuda() for x in g])
+    fin = rasterizer.finalize({k: v.clone() for k, v in raw.items()})
+    torch.cuda.synchronize()
+    b = ora["bwd"]
+    util.assert_close("texture", fin["texture"].cpu().numpy(), b["texture"], 1e-5, 1e-5)
+    cnt = b["points_count"]
+    want = b["points"] / np.maximum(cnt, 1)[:, None]
+    util.assert_close("points", fin["points"].cpu().numpy()[:, :3], want, 1e-5, 1e-5)
+    want_pose = b["pose"] / np.where(b["pose_count"] > 0, b["pose_count"], 1)[:, None]
+    util.assert_close("pose", fin["pose"].cpu().numpy(), want_pose, 1e-5, 1e-5)
+    want_intr = b["intrinsics"] / np.where(b["intrinsics_count"] > 0, b["intrinsics_count"], 1)[:, None]
+    util.assert_close("intrinsics", fin["intrinsics"].cpu().numpy(), want_intr, 1e-5, 1e-5)

@@ -1,0 +1,114 @@
+"""Shared helpers of the parity tests: run the CPU oracle and the CUDA library on the same scene and compare."""
+from __future__ import annotations
+
+import numpy as np
+
+from oracle import oracle as O
+
+
+def oracle_params(params: dict) -> dict:
+    p = O.default_params()
+    for k in p:
+        if k in params:
+            p[k] = params[k]
+    p["output_background_mask"] = 1
+    return p
+
+
+def run_oracle(scene, params: dict, grads=None, dropout=None, quadratic=False):
+    o = O.Oracle()
+    p = oracle_params(params)
+    p["conf_grad_quadratic"] = int(quadratic)
+    fwd = o.forward(scene, p, dropout=dropout)
+    counts, keys = o.lists()
+    out = dict(fwd=fwd, counts=counts, keys=keys, F=fwd["F"])
+    if grads is not None:
+        out["bwd"] = o.backward(grads)
+    return out
+
+
+def run_gpu(rast, scene, params: dict, grads=None, dropout=None, capacity=None):
+    import torch
+    from vet_b200.render import scene_to_device
+
+    dev = rast.device
+    tensors = scene_to_device(scene, dev)
+    dro = None if dropout is None else torch.from_numpy(np.ascontiguousarray(dropout, np.float32)).to(dev)
+    fwd = rast.forward(*tensors, scene.views, params, dropout=dro, capacity=capacity, want_weight=True, want_mask=True,
+                       want_depth=True)
+    F, longest = rast.fragment_count()
+    groups = rast._saved["groups"]
+    counts = torch.cat([g[2].counts for g in groups]).cpu().numpy()
+    ends = [g[2].ends.cpu().numpy().astype(np.int64) for g in groups]
+    keys_parts = []
+    for g, e in zip(groups, ends):
+        n = int(e[-1]) if e.size else 0
+        keys_parts.append(g[2].keys[:n].cpu().numpy().view(np.uint64))
+    keys = np.concatenate(keys_parts) if keys_parts else np.zeros(0, np.uint64)
+    out = dict(fwd={k: (None if v is None else [t.cpu().numpy() for t in v]) for k, v in fwd.items()}, counts=counts,
+               keys=keys, F=F, longest=longest)
+    if grads is not None:
+        g = rast.backward_raw([torch.from_numpy(x).to(dev) for x in grads])
+        torch.cuda.synchronize()
+        out["bwd_raw"] = {k: v.cpu().numpy() for k, v in g.items()}
+    return out
+
+
+def l1_grads(color, seed=0):
+    """d(L1 loss vs a seeded U(0,1) target)/d(image) for every level: sign(out - target) / numel."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for c in color:
+        target = rng.uniform(0.0, 1.0, size=c.shape).astype(np.float32)
+        out.append((np.sign(c - target) / c.size).astype(np.float32))
+    return out
+
+
+def random_grads(color, seed=0):
+    rng = np.random.default_rng(seed)
+    return [rng.standard_normal(c.shape).astype(np.float32) for c in color]
+
+
+def assert_close(name, got, want, rtol=1e-5, floor_rel=1e-6):
+    """|got - want| <= rtol * max(|got|, |want|, floor) with floor = floor_rel * max|want| (summation-order noise
+    of fp32 atomics has no meaning relative to an element that cancels to ~0)."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    assert got.shape == want.shape, (name, got.shape, want.shape)
+    scale = np.maximum(np.abs(got), np.abs(want))
+    floor = floor_rel * (np.abs(want).max() if want.size else 0.0)
+    bound = rtol * np.maximum(scale, floor) if floor_rel < 1 else rtol * floor
+    err = np.abs(got - want)
+    bad = err > bound
+    if bad.any():
+        i = np.unravel_index(np.argmax(err - bound), err.shape)
+        raise AssertionError(f"{name}: {bad.sum()} of {bad.size} elements differ; worst at {i}: got {got[i]!r} "
+                             f"want {want[i]!r} (err {err[i]:.3e}, bound {bound[i] if np.ndim(bound) else bound:.3e})")
+
+
+def compare_forward(gpu, ora, exact_images=True):
+    assert gpu["F"] == ora["F"], (gpu["F"], ora["F"])
+    np.testing.assert_array_equal(gpu["counts"], ora["counts"])
+    np.testing.assert_array_equal(gpu["keys"], ora["keys"])
+    for name in ("color", "weight", "mask", "depth"):
+        for l, (a, b) in enumerate(zip(gpu["fwd"][name], ora["fwd"][name])):
+            if exact_images:
+                np.testing.assert_array_equal(a, b, err_msg=f"{name}[{l}]")
+            else:
+                assert_close(f"{name}[{l}]", a, b, rtol=1e-5, floor_rel=1e-6)
+
+
+def compare_backward(gpu_raw, ora_bwd, channels, rtol=1e-5, floor_rel=1e-5):
+    """Raw gradient sums; the oracle sums in fp64, the GPU with fp32 atomics in arbitrary order."""
+    assert_close("g_texture", gpu_raw["desc"][:, :channels].T, ora_bwd["texture"], rtol, floor_rel)
+    assert_close("g_confidence", gpu_raw["conf"], ora_bwd["confidence"], rtol, floor_rel)
+    assert_close("g_background", gpu_raw["background"], ora_bwd["background"], rtol, floor_rel)
+    if "points" in gpu_raw and "points" in ora_bwd:
+        np.testing.assert_array_equal(gpu_raw["points"][:, 3], ora_bwd["points_count"])
+        assert_close("g_points", gpu_raw["points"][:, :3], ora_bwd["points"], rtol, floor_rel)
+    if "pose" in gpu_raw and "pose" in ora_bwd:
+        assert_close("g_pose", gpu_raw["pose"], ora_bwd["pose"], rtol, floor_rel)
+        assert_close("g_pose_count", gpu_raw["pose_count"], ora_bwd["pose_count"], 1e-5, 1e-5)
+    if "intrinsics" in gpu_raw and "intrinsics" in ora_bwd:
+        assert_close("g_intrinsics", gpu_raw["intrinsics"], ora_bwd["intrinsics"], rtol, floor_rel)
+        assert_close("g_intrinsics_count", gpu_raw["intrinsics_count"], ora_bwd["intrinsics_count"], 1e-5, 1e-5)

@@ -1,0 +1,100 @@
+"""ctypes binding of libvetr.so (include/vetr.h).  There is no fallback: a missing library is an error."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libvetr.so")
+
+MAX_LAYERS = 5
+MAX_VIEWS = 8
+MODE_FULL_BLEND = 1
+MODE_BILINEAR_BLEND = 3
+
+OK, E_INVALID_ARG, E_CUDA, E_UNSUPPORTED, E_LIST_OVERFLOW, E_TOO_LARGE = 0, -1, -2, -3, -4, -5
+
+
+class Params(C.Structure):
+    _fields_ = [
+        ("render_mode", C.c_int32), ("num_layers", C.c_int32), ("num_channels", C.c_int32),
+        ("drop_out_points_by_radius", C.c_int32), ("drop_out_radius_threshold", C.c_float),
+        ("dist_cutoff", C.c_float), ("use_environment_map", C.c_int32), ("viewer_only", C.c_int32),
+        ("stability_cutoff_value", C.c_float), ("debug_max_list_length", C.c_int32),
+        ("need_point_gradient", C.c_int32), ("K_gradient_factor", C.c_float),
+        ("distortion_gradient_factor", C.c_float), ("output_background_mask_value", C.c_float),
+        ("background_alpha_to_point0", C.c_int32), ("keep_sorted_lists", C.c_int32),
+    ]
+
+
+class View(C.Structure):
+    _fields_ = [("w", C.c_int32), ("h", C.c_int32), ("image_index", C.c_int32), ("camera_index", C.c_int32),
+                ("camera_model", C.c_int32), ("crop", C.c_float * 5), ("rot", C.c_float * 4)]
+
+
+class Cloud(C.Structure):
+    _fields_ = [("position", C.c_void_p), ("index", C.c_void_p), ("n", C.c_int32)]
+
+
+class Texture(C.Structure):
+    _fields_ = [("texture", C.c_void_p), ("confidence", C.c_void_p), ("background", C.c_void_p), ("n_tex", C.c_int32)]
+
+
+class Cameras(C.Structure):
+    _fields_ = [("poses_se3", C.c_void_p), ("intrinsics", C.c_void_p), ("n_img", C.c_int32), ("n_cam", C.c_int32)]
+
+
+class Lists(C.Structure):
+    _fields_ = [("counts", C.c_void_p), ("ends", C.c_void_p), ("keys", C.c_void_p), ("capacity", C.c_int64),
+                ("status", C.c_void_p), ("items", C.c_void_p), ("items_capacity", C.c_int64)]
+
+
+EXPORTS = [
+    "vetr_create", "vetr_destroy", "vetr_set_stream", "vetr_strerror", "vetr_last_cuda_error", "vetr_pyramid_pixels",
+    "vetr_item_table_entries", "vetr_max_fragments", "vetr_forward", "vetr_backward", "vetr_finalize_gradients",
+    "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists",
+]
+
+_lib = None
+
+
+class VetrError(RuntimeError):
+    def __init__(self, status: int, where: str, cuda: int = 0):
+        self.status = status
+        msg = lib().vetr_strerror(status).decode()
+        super().__init__(f"{where}: {msg} (status {status}" + (f", cudaError {cuda})" if cuda else ")"))
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m vet_b200.build` "
+                               "(nvcc, sm_100a). There is no CPU or PyTorch fallback.")
+        L = C.CDLL(LIB_PATH)
+        L.vetr_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
+        L.vetr_destroy.argtypes = [C.c_void_p]
+        L.vetr_destroy.restype = None
+        L.vetr_set_stream.argtypes = [C.c_void_p, C.c_void_p]
+        L.vetr_strerror.argtypes = [C.c_int]
+        L.vetr_strerror.restype = C.c_char_p
+        L.vetr_last_cuda_error.argtypes = [C.c_void_p]
+        L.vetr_pyramid_pixels.argtypes = [C.c_int, C.c_int, C.c_int]
+        L.vetr_pyramid_pixels.restype = C.c_int64
+        L.vetr_item_table_entries.argtypes = [C.c_int64, C.c_int64]
+        L.vetr_item_table_entries.restype = C.c_int64
+        L.vetr_max_fragments.argtypes = [C.c_int, C.c_int, C.POINTER(Params)]
+        L.vetr_max_fragments.restype = C.c_int64
+        vp = C.c_void_p
+        L.vetr_forward.argtypes = [vp, C.POINTER(Params), C.POINTER(Cloud), C.POINTER(Texture), C.POINTER(Cameras),
+                                   C.POINTER(View), C.c_int, vp, C.POINTER(Lists), vp, vp, vp, vp]
+        L.vetr_backward.argtypes = [vp, C.POINTER(Params), C.POINTER(Cloud), C.POINTER(Texture), C.POINTER(Cameras),
+                                    C.POINTER(View), C.c_int, C.POINTER(Lists), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.vetr_finalize_gradients.argtypes = [vp, C.c_int, C.c_int, vp, vp, C.c_int, vp, vp, C.c_int, vp, vp, C.c_int,
+                                              vp, vp]
+        L.vetr_apply_tangent.argtypes = [vp, vp, vp, C.c_int]
+        L.vetr_read_status.argtypes = [vp, C.POINTER(Lists), C.POINTER(C.c_int64), C.POINTER(C.c_int32)]
+        L.vetr_get_lists.argtypes = [vp, C.POINTER(Lists), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp,
+                                     C.POINTER(C.c_int64)]
+        _lib = L
+    return _lib

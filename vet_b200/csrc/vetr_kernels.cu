@@ -1,0 +1,1558 @@
+// B200 (sm_100a) kernels and C ABI of the blending point rasterizer.  See include/vetr.h for the interface and the
+// reference functions each entry point replaces.
+//
+// Data layout in HBM
+//   pixel space : all views and all pyramid levels of a call form ONE array of PT = n_views * P pixels
+//                 (view-major, then level, then row-major).  counts[PT], ends[PT] (int32).
+//   key buffer  : one array of 64-bit keys, (depth bits << 32) | point index.  The list of pixel g is
+//                 keys[ends[g] - counts[g] .. ends[g]).  Lists of consecutive pixels are contiguous, so a CTA that
+//                 owns a run of pixels streams its fragments with coalesced loads.
+//   work items  : the pixel space is cut into runs of ~kQuantum units of work (1 per fragment, kPixelWork per pixel)
+//                 by the scan itself (item_start[]), so the persistent blend kernels are balanced by fragments, not
+//                 by pixels, and no host round trip is needed to size anything.
+//
+// Kernels (all HBM / L2-atomic bound; nothing here is a contraction, so no tensor cores)
+//   project_count_kernel   stream positions, project, per-level pixel, warp-aggregated count atomics
+//   scan_*                 three-phase exclusive scan of counts -> ends, total F, work-item table
+//   collect_kernel         re-project, warp-aggregated slot reservation, 8-byte key store
+//   sort_blend_kernel      per work item: stage keys in shared memory, rank-sort each list by (depth, index),
+//                          write sorted keys back, gather descriptors, blend front to back, write all outputs
+//   backward_kernel        per work item: stage sorted keys + gathered descriptors, O(n) transmittance / suffix
+//                          sweeps per pixel, then one thread per fragment: vector reductions to HBM
+//   finalize / tangent     small epilogues
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "../../include/vetr.h"
+#include "vetr_math.cuh"
+
+namespace vetr
+{
+constexpr int kThreads    = 256;   // CTA size of the item kernels
+constexpr int kQuantum    = 1024;  // units of work per item
+constexpr int kPixelWork  = 4;     // work units charged per pixel -> at most kQuantum / kPixelWork pixels per item
+constexpr int kMaxPixels  = kQuantum / kPixelWork;
+constexpr int kLongList   = kQuantum;      // lists longer than this take the slow path
+constexpr int kCap        = 2 * kQuantum;  // fragments staged per item (bound: kQuantum + kLongList)
+constexpr int kPointsPerThread = 4;
+constexpr int kScanTile   = 4096;  // elements per CTA in the scan (256 threads x 16)
+constexpr float kMaxDepth = 100000.f;  // MAX_DEPTH_CONST, RenderConstants.h:30
+
+struct ViewDev
+{
+    int image_index, camera_index;
+    float crop[5];
+    float rot[4];
+};
+
+struct Frame  // kernel parameter block (travels by value; no global or __constant__ state)
+{
+    int n_views, L, C, n, n_tex, w, h;
+    int mode, drop_by_radius, use_env, viewer_only, dbg_max_len, need_point_grad, bg_alpha_to_point0, keep_sorted;
+    float radius_threshold, dist_cutoff, stability_cutoff, k_grad_factor, dist_grad_factor, mask_value;
+    int lw[VETR_MAX_LAYERS], lh[VETR_MAX_LAYERS];
+    long long lbase[VETR_MAX_LAYERS];
+    long long P, PT;
+    ViewDev views[VETR_MAX_VIEWS];
+    const float4* position;
+    const int* index;
+    const float* texture;
+    const float* confidence;
+    const float* background;
+    const double* poses;
+    const float* intr;
+    const float* dropout;
+    int* counts;
+    int* ends;
+    unsigned long long* keys;
+    long long capacity;
+    int* status;      // {F, overflow, longest, number of work items}
+    int* item_start;  // [n_items + 1]
+};
+
+__device__ __forceinline__ Camera load_camera(const Frame& f, int b)
+{
+    Camera c;
+    const ViewDev& v = f.views[b];
+    const double* p  = f.poses + 8 * (long long)v.image_index;
+    c.V.qx = (float)p[0], c.V.qy = (float)p[1], c.V.qz = (float)p[2], c.V.qw = (float)p[3];
+    c.V.tx = (float)p[4], c.V.ty = (float)p[5], c.V.tz = (float)p[6];
+    const float* k = f.intr + 13 * (long long)v.camera_index;
+#pragma unroll
+    for (int i = 0; i < 5; ++i) c.K[i] = k[i];
+    bool hd = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+    {
+        c.dist[i] = k[5 + i];
+        hd |= c.dist[i] != 0.f;
+    }
+    c.has_dist = hd;
+#pragma unroll
+    for (int i = 0; i < 5; ++i) c.crop[i] = v.crop[i];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c.rot[i] = v.rot[i];
+    c.cx = (float)(f.w / 2);
+    c.cy = (float)(f.h / 2);
+    return c;
+}
+
+// Decodes a pixel of the global pixel space.
+struct PixelRef
+{
+    int view, level, x, y, w, h;
+};
+__device__ __forceinline__ PixelRef decode_pixel(const Frame& f, long long g)
+{
+    PixelRef r;
+    r.view      = (int)(g / f.P);
+    long long q = g - (long long)r.view * f.P;
+    int l       = 0;
+#pragma unroll
+    for (int i = 1; i < VETR_MAX_LAYERS; ++i)
+        if (i < f.L && q >= f.lbase[i]) l = i;
+    q -= f.lbase[l];
+    r.level = l;
+    r.w = f.lw[l], r.h = f.lh[l];
+    r.y = (int)(q / r.w);
+    r.x = (int)(q - (long long)r.y * r.w);
+    return r;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Pass 1 and 3: projection + counting / collection.  One point per thread and step, all lanes of a warp stay in
+// the level loop together so that equal pixels inside a warp can be merged into one atomic.
+
+template <bool kCollect>
+__global__ void __launch_bounds__(kThreads) project_kernel(const __grid_constant__ Frame f)
+{
+    const int b      = blockIdx.y;
+    const Camera cam = load_camera(f, b);
+    const unsigned lane = threadIdx.x & 31;
+    const long long vbase = (long long)b * f.P;
+    const bool bilinear   = f.mode == VETR_MODE_BILINEAR_BLEND;
+    const int base_point  = blockIdx.x * (kThreads * kPointsPerThread) + threadIdx.x;
+
+#pragma unroll 1
+    for (int it = 0; it < kPointsPerThread; ++it)
+    {
+        const int pid = base_point + it * kThreads;
+        bool alive    = pid < f.n;
+        float2 ip     = make_float2(0.f, 0.f);
+        float radius  = 0.f;
+        unsigned zb   = 0;
+        if (alive && f.dropout) alive = f.dropout[(long long)b * f.n + pid] != 1.f;
+        if (alive && f.viewer_only) alive = !(f.confidence[f.index[pid]] < f.stability_cutoff);
+        if (alive)
+        {
+            float4 pos   = __ldg(f.position + pid);
+            Projected pr = project_point(pos, cam, f.dist_cutoff);
+            alive        = pr.z != 0.f;  // also false for NaN-free zero; NaN z cannot occur (fmaxf)
+            ip           = pr.ip;
+            radius       = pr.radius_px;
+            zb           = __float_as_uint(pr.z);
+        }
+        if (!__any_sync(0xffffffffu, alive)) continue;
+
+#pragma unroll 1
+        for (int l = 0; l < f.L; ++l, radius *= 0.5f, ip.x *= 0.5f, ip.y *= 0.5f)
+        {
+            if (alive && f.drop_by_radius && radius < f.radius_threshold) alive = false;  // `break` of the reference
+            if (!__any_sync(0xffffffffu, alive)) break;
+            const int lw = f.lw[l], lh = f.lh[l];
+            const int ncorner = bilinear ? 4 : 1;
+            int bx, by;
+            if (bilinear)
+                bx = round_down(ip.x), by = round_down(ip.y);
+            else
+                bx = round_half_even(ip.x), by = round_half_even(ip.y);
+#pragma unroll 1
+            for (int cidx = 0; cidx < ncorner; ++cidx)
+            {
+                long long x = (long long)bx + (cidx & 1), y = (long long)by + (cidx >> 1);
+                bool valid  = alive && x >= 0 && y >= 0 && x < lw && y < lh;
+                // lanes without a fragment get a key no other lane can have
+                long long g = valid ? vbase + f.lbase[l] + y * lw + x : -1 - (long long)lane;
+                unsigned peers = __match_any_sync(0xffffffffu, g);
+                if (!valid) continue;
+                int leader = __ffs(peers) - 1;
+                int npeers = __popc(peers);
+                if (!kCollect)
+                {
+                    if (lane == (unsigned)leader) atomicAdd(f.counts + g, npeers);
+                }
+                else
+                {
+                    int slot0 = 0;
+                    if (lane == (unsigned)leader) slot0 = atomicAdd(f.ends + g, npeers);
+                    slot0     = __shfl_sync(peers, slot0, leader);
+                    int slot  = slot0 + __popc(peers & ((1u << lane) - 1));
+                    if ((unsigned long long)slot < (unsigned long long)f.capacity)
+                        f.keys[slot] = ((unsigned long long)zb << 32) | (unsigned)pid;
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Pass 2: exclusive scan of counts -> ends (start offsets until the collection pass has advanced them to the
+// list ends), total fragment count, longest list, and the work-item table.
+
+__global__ void __launch_bounds__(256) scan_tile_sums_kernel(const int* __restrict__ counts, long long n,
+                                                             long long* __restrict__ tile_sums, int* status)
+{
+    __shared__ long long s_sum[8];
+    __shared__ int s_max[8];
+    const long long base = (long long)blockIdx.x * kScanTile;
+    long long sum = 0;
+    int mx        = 0;
+    for (int i = threadIdx.x; i < kScanTile; i += 256)
+    {
+        long long g = base + i;
+        int c       = g < n ? counts[g] : 0;
+        sum += c;
+        mx = max(mx, c);
+    }
+    for (int o = 16; o > 0; o >>= 1)
+    {
+        sum += __shfl_down_sync(0xffffffffu, sum, o);
+        mx = max(mx, __shfl_down_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) s_sum[threadIdx.x >> 5] = sum, s_max[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        for (int i = 1; i < 8; ++i) sum += s_sum[i], mx = max(mx, s_max[i]);
+        tile_sums[blockIdx.x] = sum;
+        if (mx > 0) atomicMax(status + 2, mx);
+    }
+}
+
+// One CTA: exclusive scan of the tile sums in place; writes F, the overflow flag and the number of work items.
+__global__ void __launch_bounds__(1024) scan_spine_kernel(long long* tile_sums, int n_tiles, long long n_pixels,
+                                                          long long capacity, int* status, int* item_start)
+{
+    __shared__ long long s_warp[32];
+    __shared__ long long s_carry;
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    for (int base = 0; base < n_tiles; base += 1024)
+    {
+        int i         = base + threadIdx.x;
+        long long v   = i < n_tiles ? tile_sums[i] : 0;
+        long long inc = v;
+        for (int o = 1; o < 32; o <<= 1)
+        {
+            long long t = __shfl_up_sync(0xffffffffu, inc, o);
+            if ((threadIdx.x & 31) >= o) inc += t;
+        }
+        if ((threadIdx.x & 31) == 31) s_warp[threadIdx.x >> 5] = inc;
+        __syncthreads();
+        if (threadIdx.x < 32)
+        {
+            long long w = s_warp[threadIdx.x];
+            for (int o = 1; o < 32; o <<= 1)
+            {
+                long long t = __shfl_up_sync(0xffffffffu, w, o);
+                if (threadIdx.x >= o) w += t;
+            }
+            s_warp[threadIdx.x] = w;
+        }
+        __syncthreads();
+        long long carry  = s_carry;
+        long long before = carry + (threadIdx.x >= 32 ? s_warp[(threadIdx.x >> 5) - 1] : 0) + inc - v;
+        if (i < n_tiles) tile_sums[i] = before;
+        __syncthreads();
+        if (threadIdx.x == 1023) s_carry = carry + s_warp[31];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0)
+    {
+        long long F   = s_carry;
+        bool overflow = F > capacity || F > 0x7fffffffLL;
+        status[0]     = (int)(F > 0x7fffffffLL ? 0x7fffffffLL : F);
+        status[1]     = overflow ? 1 : 0;
+        long long work = F + (long long)kPixelWork * n_pixels;
+        int items      = overflow ? 0 : (int)((work + kQuantum - 1) / kQuantum);
+        status[3]      = items;
+        item_start[items] = (int)n_pixels;  // sentinel
+    }
+}
+
+// Writes the exclusive offsets and cuts the pixel space into work items: with work(p) = end(p) + kPixelWork*(p+1)
+// (strictly increasing), item k owns the pixels with k*Q < work(p) <= (k+1)*Q; pixel p opens every item k with
+// work(p-1) <= k*Q < work(p).
+__global__ void __launch_bounds__(256) scan_apply_kernel(const int* __restrict__ counts, long long n,
+                                                         const long long* __restrict__ tile_offsets,
+                                                         int* __restrict__ ends, const int* __restrict__ status,
+                                                         int* __restrict__ item_start)
+{
+    __shared__ int s_warp[8];
+    const long long base = (long long)blockIdx.x * kScanTile + threadIdx.x * 16;
+    int c[16];
+    int local = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+    {
+        long long g = base + i;
+        c[i]        = g < n ? counts[g] : 0;
+        local += c[i];
+    }
+    int inc = local;
+    for (int o = 1; o < 32; o <<= 1)
+    {
+        int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if ((threadIdx.x & 31) >= o) inc += t;
+    }
+    if ((threadIdx.x & 31) == 31) s_warp[threadIdx.x >> 5] = inc;
+    __syncthreads();
+    int warp_before = 0;
+    for (int i = 0; i < (int)(threadIdx.x >> 5); ++i) warp_before += s_warp[i];
+    long long run       = tile_offsets[blockIdx.x] + warp_before + inc - local;
+    const bool overflow = status[1] != 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+    {
+        long long g = base + i;
+        if (g < n)
+        {
+            ends[g] = (int)run;
+            if (!overflow)
+            {
+                long long w_prev = run + (long long)kPixelWork * g;                // work(g-1)
+                long long w_here = run + c[i] + (long long)kPixelWork * (g + 1);   // work(g)
+                for (long long k = (w_prev + kQuantum - 1) / kQuantum; k * kQuantum < w_here; ++k)
+                    item_start[k] = (int)g;
+            }
+        }
+        run += c[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Shared pieces of the two item kernels.
+
+struct ItemRange
+{
+    int lo, hi;           // pixels [lo, hi)
+    long long f0, f1;     // fragments [f0, f1)
+};
+
+__device__ __forceinline__ long long list_end(const Frame& f, long long g) { return g < 0 ? 0 : (long long)f.ends[g]; }
+
+// In-place ascending sort of a list in global memory by the whole CTA (lists longer than kLongList).  Sorting
+// network with all comparators pointing the same way, so that positions >= n behave as +infinity without padding.
+__device__ void sort_long_list(unsigned long long* keys, int n)
+{
+    int n2 = 1;
+    while (n2 < n) n2 <<= 1;
+    for (int k = 2; k <= n2; k <<= 1)
+    {
+        for (int j = k >> 1; j > 0; j >>= 1)
+        {
+            for (int i = threadIdx.x; i < n2; i += blockDim.x)
+            {
+                int partner = (j == (k >> 1)) ? (i ^ (k - 1)) : (i ^ j);
+                if (partner > i && partner < n)
+                {
+                    unsigned long long a = keys[i], b = keys[partner];
+                    if (a > b) keys[i] = b, keys[partner] = a;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// Alpha of a fragment: confidence (mode 1) or bilinear corner weight x confidence (mode 3).  For mode 3 the
+// level-space position is recomputed from the point (the reference stores it in per_point_data,
+// RenderForward.cu:1116-1127; recomputing with the same arithmetic gives the same bits).
+__device__ __forceinline__ float fragment_alpha(const Frame& f, const Camera& cam, const PixelRef& px, int pid, int tex,
+                                                float2* uv_out, int* corner_out)
+{
+    float a = __ldg(f.confidence + tex);
+    if (f.mode == VETR_MODE_BILINEAR_BLEND)
+    {
+        float4 pos   = __ldg(f.position + pid);
+        Projected pr = project_point(pos, cam, f.dist_cutoff);
+        float2 ip    = pr.ip;
+        for (int l = 0; l < px.level; ++l) ip.x *= 0.5f, ip.y *= 0.5f;
+        int bx = round_down(ip.x), by = round_down(ip.y);
+        int corner = (px.y - by) * 2 + (px.x - bx);
+        corner     = min(max(corner, 0), 3);
+        float w    = blending_fac(ip, corner, nullptr, nullptr);
+        if (uv_out) *uv_out = ip;
+        if (corner_out) *corner_out = corner;
+        a = w * a;
+    }
+    return a;
+}
+
+struct BlendSmem
+{
+    unsigned long long sorted[kCap];
+    union
+    {
+        unsigned long long unsorted[kCap];
+        float4 desc[kCap];
+    };
+    float alpha[kCap];
+    int seg_end[kMaxPixels + 1];
+    unsigned char seg_of[kCap];
+};
+
+// ---------------------------------------------------------------------------------------------------------
+// Pass 4: sort + blend.
+
+__device__ __forceinline__ void write_pixel(const Frame& f, float* const* out_color, float* const* out_weight,
+                                            float* const* out_mask, float* const* out_depth, const PixelRef& px,
+                                            const float c[4], float T, float depth)
+{
+    const long long hw = (long long)px.w * px.h;
+    const long long o  = (long long)px.y * px.w + px.x;
+    float* col         = out_color[px.level] + (long long)px.view * f.C * hw + o;
+    for (int ci = 0; ci < f.C; ++ci) col[ci * hw] = c[ci];
+    if (out_weight) out_weight[px.level][(long long)px.view * hw + o] = T;
+    if (out_mask) out_mask[px.level][(long long)px.view * hw + o] = (T == 0.f) ? f.mask_value : 1.f;
+    if (out_depth) out_depth[px.level][(long long)px.view * hw + o] = depth;
+}
+
+struct OutPtrs
+{
+    float* color[VETR_MAX_LAYERS];
+    float* weight[VETR_MAX_LAYERS];
+    float* mask[VETR_MAX_LAYERS];
+    float* depth[VETR_MAX_LAYERS];
+    int has_weight, has_mask, has_depth;
+};
+
+__global__ void __launch_bounds__(kThreads) sort_blend_kernel(const __grid_constant__ Frame f,
+                                                              const __grid_constant__ OutPtrs out)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    BlendSmem& s = *reinterpret_cast<BlendSmem*>(smem_raw);
+    __shared__ float s_fold[8];  // slow path: T and colour carried between blocks
+    const int tid     = threadIdx.x;
+    const int n_items = f.status[3];
+    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+    float* const* oc = out.color;
+    float* const* ow = out.has_weight ? out.weight : nullptr;
+    float* const* om = out.has_mask ? out.mask : nullptr;
+    float* const* od = out.has_depth ? out.depth : nullptr;
+
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x)
+    {
+        int lo = f.item_start[item], hi = f.item_start[item + 1];
+        if (lo >= hi) continue;
+        __syncthreads();  // shared memory of the previous item is free
+
+        // ---- slow path: a first pixel with a long list is handled alone, in blocks of kCap fragments
+        {
+            long long e0 = list_end(f, (long long)lo - 1), e1 = f.ends[lo];
+            int n_first  = (int)(e1 - e0);
+            if (n_first > kLongList)
+            {
+                sort_long_list(f.keys + e0, n_first);
+                __threadfence_block();
+                PixelRef px  = decode_pixel(f, lo);
+                Camera cam   = load_camera(f, px.view);
+                int cnt      = n_first;
+                if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
+                if (tid == 0)
+                {
+                    s_fold[0] = 1.f;
+                    s_fold[1] = s_fold[2] = s_fold[3] = s_fold[4] = 0.f;
+                    s_fold[5] = 0.f;  // stop flag
+                }
+                __syncthreads();
+                for (int blk = 0; blk < cnt; blk += kCap)
+                {
+                    int m = min(kCap, cnt - blk);
+                    for (int i = tid; i < m; i += kThreads)
+                    {
+                        int pid = (int)(unsigned)f.keys[e0 + blk + i];
+                        int tex = __ldg(f.index + pid);
+                        s.alpha[i] = fragment_alpha(f, cam, px, pid, tex, nullptr, nullptr);
+                        float4 d;
+                        d.x = __ldg(f.texture + tex);
+                        d.y = __ldg(f.texture + (long long)f.n_tex + tex);
+                        d.z = __ldg(f.texture + 2LL * f.n_tex + tex);
+                        d.w = f.C > 3 ? __ldg(f.texture + 3LL * f.n_tex + tex) : 0.f;
+                        s.desc[i] = d;
+                    }
+                    __syncthreads();
+                    if (tid == 0 && s_fold[5] == 0.f)
+                    {
+                        float T = s_fold[0];
+                        float c[4] = {s_fold[1], s_fold[2], s_fold[3], s_fold[4]};
+                        for (int i = 0; i < m; ++i)
+                        {
+                            float a = s.alpha[i];
+                            float4 d = s.desc[i];
+                            c[0] = vetr_blend(T, a, d.x, c[0]);
+                            c[1] = vetr_blend(T, a, d.y, c[1]);
+                            c[2] = vetr_blend(T, a, d.z, c[2]);
+                            c[3] = vetr_blend(T, a, d.w, c[3]);
+                            T    = vetr_new_T(T, a);
+                            if (bilinear && T < 0.001f)
+                            {
+                                s_fold[5] = 1.f;
+                                break;
+                            }
+                        }
+                        s_fold[0] = T;
+                        s_fold[1] = c[0], s_fold[2] = c[1], s_fold[3] = c[2], s_fold[4] = c[3];
+                    }
+                    __syncthreads();
+                }
+                if (tid == 0)
+                {
+                    float T    = s_fold[0];
+                    float c[4] = {s_fold[1], s_fold[2], s_fold[3], s_fold[4]};
+                    bool add_bg = !f.use_env && !(bilinear && !(T >= 0.001f));
+                    if (add_bg)
+                        for (int ci = 0; ci < f.C; ++ci) c[ci] = vetr_blend(T, 1.f, f.background[ci], c[ci]);
+                    float depth = __uint_as_float((unsigned)(f.keys[e0] >> 32));
+                    write_pixel(f, oc, ow, om, od, px, c, T, depth);
+                }
+                lo += 1;
+                __syncthreads();
+                if (lo >= hi) continue;
+            }
+        }
+
+        // ---- fast path
+        const long long f0 = list_end(f, (long long)lo - 1);
+        const int np       = hi - lo;
+        if (tid < np) s.seg_end[tid + 1] = (int)((long long)f.ends[lo + tid] - f0);
+        if (tid == 0) s.seg_end[0] = 0;
+        __syncthreads();
+        const int nf = s.seg_end[np];
+        for (int i = tid; i < nf; i += kThreads) s.unsorted[i] = f.keys[f0 + i];
+        __syncthreads();
+        // rank sort inside each list; keys are unique (distinct point indices), so ranks are a permutation
+        for (int i = tid; i < nf; i += kThreads)
+        {
+            int a = 0, b = np;  // find j with seg_end[j] <= i < seg_end[j+1]
+            while (b - a > 1)
+            {
+                int m = (a + b) >> 1;
+                if (s.seg_end[m] <= i)
+                    a = m;
+                else
+                    b = m;
+            }
+            const int ss = s.seg_end[a], se = s.seg_end[a + 1];
+            const unsigned long long key = s.unsorted[i];
+            int rank = 0;
+            for (int k = ss; k < se; ++k) rank += s.unsorted[k] < key;
+            s.sorted[ss + rank] = key;
+            s.seg_of[i]         = (unsigned char)a;  // position i belongs to list a both before and after sorting
+        }
+        __syncthreads();
+        // write back + gather
+        {
+            int cur_view = -1;
+            Camera cam;
+            for (int i = tid; i < nf; i += kThreads)
+            {
+                const unsigned long long key = s.sorted[i];
+                if (f.keep_sorted) f.keys[f0 + i] = key;
+                int pid = (int)(unsigned)key;
+                int tex = __ldg(f.index + pid);
+                float a;
+                if (bilinear)
+                {
+                    PixelRef px = decode_pixel(f, (long long)lo + s.seg_of[i]);
+                    if (px.view != cur_view) cam = load_camera(f, px.view), cur_view = px.view;
+                    a = fragment_alpha(f, cam, px, pid, tex, nullptr, nullptr);
+                }
+                else
+                    a = __ldg(f.confidence + tex);
+                s.alpha[i] = a;
+                float4 d;
+                d.x = __ldg(f.texture + tex);
+                d.y = __ldg(f.texture + (long long)f.n_tex + tex);
+                d.z = __ldg(f.texture + 2LL * f.n_tex + tex);
+                d.w = f.C > 3 ? __ldg(f.texture + 3LL * f.n_tex + tex) : 0.f;
+                s.desc[i] = d;  // overwrites `unsorted`, which is dead after the barrier above
+            }
+        }
+        __syncthreads();
+        // fold: one thread per pixel
+        if (tid < np)
+        {
+            const int ss = s.seg_end[tid], se = s.seg_end[tid + 1];
+            int cnt = se - ss;
+            if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
+            float T    = 1.f;
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int i = ss; i < ss + cnt; ++i)
+            {
+                float a  = s.alpha[i];
+                float4 d = s.desc[i];
+                c[0] = vetr_blend(T, a, d.x, c[0]);
+                c[1] = vetr_blend(T, a, d.y, c[1]);
+                c[2] = vetr_blend(T, a, d.z, c[2]);
+                c[3] = vetr_blend(T, a, d.w, c[3]);
+                T    = vetr_new_T(T, a);
+                if (bilinear && T < 0.001f) break;
+            }
+            bool add_bg = !f.use_env && !(bilinear && !(T >= 0.001f));
+            if (add_bg)
+                for (int ci = 0; ci < f.C; ++ci) c[ci] = vetr_blend(T, 1.f, f.background[ci], c[ci]);
+            float depth = se > ss ? __uint_as_float((unsigned)(s.sorted[ss] >> 32)) : kMaxDepth;
+            PixelRef px = decode_pixel(f, (long long)lo + tid);
+            write_pixel(f, oc, ow, om, od, px, c, T, depth);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Backward.
+
+struct BackPtrs
+{
+    const float* out_color[VETR_MAX_LAYERS];
+    const float* grad_color[VETR_MAX_LAYERS];
+    float4* g_desc;
+    float* g_conf;
+    float4* g_points;
+    float* g_background;
+    double* g_pose;
+    float* g_pose_count;
+    float* g_intr;
+    float* g_intr_count;
+};
+
+struct BackSmem
+{
+    unsigned long long keys[kCap];
+    float4 desc[kCap];
+    float alpha[kCap];
+    float dot[kCap];     // d_i . G  ->  replaced by the alpha gradient of the fragment
+    float trans[kCap];   // T_i ; NaN = fragment not blended (early termination / list truncation)
+    float4 grad[kMaxPixels];  // incoming gradient of the pixel
+    int seg_end[kMaxPixels + 1];
+    unsigned char seg_of[kCap];
+    double red[8][8];    // cross-warp reduction scratch
+};
+
+// Per-thread accumulators of the camera gradients of one view; flushed with atomics.
+struct CamAcc
+{
+    double pose[6];
+    float pose_count;
+    float intr[13];
+    float intr_count;
+    int view;
+    bool any;
+    __device__ void clear()
+    {
+        for (int k = 0; k < 6; ++k) pose[k] = 0.0;
+        for (int k = 0; k < 13; ++k) intr[k] = 0.f;
+        pose_count = intr_count = 0.f;
+        any        = false;
+    }
+};
+
+__device__ __forceinline__ void flush_cam(const Frame& f, const BackPtrs& bp, CamAcc& acc)
+{
+    if (!acc.any) return;
+    const ViewDev& v = f.views[acc.view];
+    if (bp.g_pose)
+    {
+        for (int k = 0; k < 6; ++k) atomicAdd(bp.g_pose + 6 * v.image_index + k, acc.pose[k]);
+        atomicAdd(bp.g_pose_count + v.image_index, acc.pose_count);
+    }
+    if (bp.g_intr)
+    {
+        for (int k = 0; k < 13; ++k) atomicAdd(bp.g_intr + 13 * v.camera_index + k, acc.intr[k]);
+        atomicAdd(bp.g_intr_count + v.camera_index, acc.intr_count);
+    }
+    acc.clear();
+}
+
+// Reduces the accumulators of all threads whose view equals `main_view` over the CTA and issues one set of
+// atomics; threads that hold another view flush on their own.
+__device__ void reduce_cam(const Frame& f, const BackPtrs& bp, CamAcc& acc, int main_view, BackSmem& s)
+{
+    if (acc.any && acc.view != main_view) flush_cam(f, bp, acc);
+    int any = __syncthreads_or(acc.any ? 1 : 0);
+    if (!any) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_values = 6 + 1 + (bp.g_intr ? 14 : 0);
+    for (int base = 0; base < n_values; base += 8)
+    {
+        for (int k = base; k < min(base + 8, n_values); ++k)
+        {
+            double v = 0.0;
+            if (acc.any)
+            {
+                if (k < 6)
+                    v = acc.pose[k];
+                else if (k == 6)
+                    v = acc.pose_count;
+                else if (k < 20)
+                    v = acc.intr[k - 7];
+                else
+                    v = acc.intr_count;
+            }
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+            if (lane == 0) s.red[warp][k - base] = v;
+        }
+        __syncthreads();
+        if (threadIdx.x < min(8, n_values - base))
+        {
+            int k    = base + threadIdx.x;
+            double v = 0.0;
+            for (int w = 0; w < kThreads / 32; ++w) v += s.red[w][threadIdx.x];
+            const ViewDev& vw = f.views[main_view];
+            if (k < 6)
+            {
+                if (bp.g_pose) atomicAdd(bp.g_pose + 6 * vw.image_index + k, v);
+            }
+            else if (k == 6)
+            {
+                if (bp.g_pose) atomicAdd(bp.g_pose_count + vw.image_index, (float)v);
+            }
+            else if (k < 20)
+                atomicAdd(bp.g_intr + 13 * vw.camera_index + (k - 7), (float)v);
+            else
+                atomicAdd(bp.g_intr_count + vw.camera_index, (float)v);
+        }
+        __syncthreads();
+    }
+    acc.clear();
+}
+
+__device__ __forceinline__ void red_add_v4(float4* addr, float4 v)
+{
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
+// Gradients of one blended fragment (descriptor, confidence, position, camera).  `galpha` is the gradient with
+// respect to the fragment's alpha, `Ta` = T_i * alpha_i.
+__device__ __forceinline__ void fragment_backward(const Frame& f, const BackPtrs& bp, const Camera& cam,
+                                                  const PixelRef& px, long long pixel_offset, int pid, float4 G,
+                                                  float4 d, float Ta, float galpha, CamAcc& acc)
+{
+    const int tex = __ldg(f.index + pid);
+    // descriptor gradient: T * alpha * G  (RenderBackward.cu:1149-1152)
+    float4 gd = make_float4(Ta * G.x, Ta * G.y, Ta * G.z, f.C > 3 ? Ta * G.w : 0.f);
+    red_add_v4(bp.g_desc + tex, gd);
+
+    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+    const int edge = min(min(px.x, px.w - 1 - px.x), min(px.y, px.h - 1 - px.y));  // ImageView::distanceFromEdge
+    const bool interior = edge > 2;
+    if (!bilinear) atomicAdd(bp.g_conf + tex, galpha);
+    if (!interior) return;
+    if (!bilinear && !f.need_point_grad) return;
+
+    float4 pos = __ldg(f.position + pid);
+    float2 dR;
+    if (!bilinear)
+    {
+        // approximate spatial gradient from the neighbouring pixels (RenderBackward.cu:1347-1374)
+        const long long hw = (long long)px.w * px.h;
+        const float* I = bp.out_color[px.level] + (long long)px.view * f.C * hw + pixel_offset;
+        const float* Gp = bp.grad_color[px.level] + (long long)px.view * f.C * hw + pixel_offset;
+        float dx = 0.f, dy = 0.f;
+        const float dv[4] = {d.x, d.y, d.z, d.w};
+        for (int ci = 0; ci < f.C; ++ci)
+        {
+            const float* Ic = I + ci * hw;
+            const float* Gc = Gp + ci * hw;
+            float Tp = dv[ci];
+            float a0 = -(Tp - __ldg(Ic - 1)) * __ldg(Gc - 1);
+            float a1 = (Tp - __ldg(Ic + 1)) * __ldg(Gc + 1);
+            float b0 = -(Tp - __ldg(Ic - px.w)) * __ldg(Gc - px.w);
+            float b1 = (Tp - __ldg(Ic + px.w)) * __ldg(Gc + px.w);
+            dx += 0.5f * (a0 + a1);
+            dy += 0.5f * (b0 + b1);
+        }
+        dR = make_float2(dx / (float)f.C, dy / (float)f.C);
+    }
+    else
+    {
+        Projected pr = project_point(pos, cam, f.dist_cutoff);
+        float2 ip    = pr.ip;
+        for (int l = 0; l < px.level; ++l) ip.x *= 0.5f, ip.y *= 0.5f;
+        int bx = round_down(ip.x), by = round_down(ip.y);
+        int corner = min(max((px.y - by) * 2 + (px.x - bx), 0), 3);
+        float jx, jy;
+        float w = blending_fac(ip, corner, &jx, &jy);
+        atomicAdd(bp.g_conf + tex, w * galpha);  // RenderBackward.cu:3076-3079
+        if (!f.need_point_grad) return;
+        float single = __ldg(f.confidence + tex) * galpha;
+        dR           = make_float2(jx * single, jy * single);
+    }
+    float scale = 1.f;
+    for (int l = 0; l < px.level; ++l) scale *= 0.5f;
+    float crop2[5];
+#pragma unroll
+    for (int k = 0; k < 5; ++k) crop2[k] = cam.crop[k] * scale;  // IntrinsicsPinhole::scale
+    BackOut bo;
+    if (!project_backward(pos, dR, cam, crop2, f.dist_cutoff, bp.g_intr != nullptr, bo)) return;
+    if (bp.g_points) red_add_v4(bp.g_points + pid, make_float4(bo.g_point[0], bo.g_point[1], bo.g_point[2], 1.f));
+    if (acc.any && acc.view != px.view) flush_cam(f, bp, acc);
+    acc.view = px.view;
+    acc.any  = true;
+    for (int k = 0; k < 6; ++k) acc.pose[k] += (double)bo.g_pose[k];
+    acc.pose_count += bilinear ? 1.f : (1.f / 1024.f);  // RenderBackward.cu:1425 vs :3144
+    if (bp.g_intr)
+    {
+        bo.g_k[4] *= 0.f;
+        for (int k = 0; k < 5; ++k) acc.intr[k] += f.k_grad_factor * bo.g_k[k];
+        bo.g_dis[2] *= 0.25f;
+        for (int k = 3; k < 8; ++k) bo.g_dis[k] *= 0.1f;
+        for (int k = 0; k < 8; ++k) acc.intr[5 + k] += f.dist_grad_factor * bo.g_dis[k];
+        acc.intr_count += 1.f / 1024.f;
+    }
+}
+
+__device__ __forceinline__ float4 load_grad(const Frame& f, const BackPtrs& bp, const PixelRef& px)
+{
+    const long long hw = (long long)px.w * px.h;
+    const float* G     = bp.grad_color[px.level] + (long long)px.view * f.C * hw + (long long)px.y * px.w + px.x;
+    float4 g;
+    g.x = __ldg(G);
+    g.y = __ldg(G + hw);
+    g.z = __ldg(G + 2 * hw);
+    g.w = f.C > 3 ? __ldg(G + 3 * hw) : 0.f;
+    return g;
+}
+
+__device__ __forceinline__ float dot4(float4 a, float4 b, int C)
+{
+    // same order as the reference's loop over channels (RenderBackward.cu:1146-1155)
+    float r = 0.f;
+    r += a.x * b.x;
+    r += a.y * b.y;
+    r += a.z * b.z;
+    if (C > 3) r += a.w * b.w;
+    return r;
+}
+
+__global__ void __launch_bounds__(kThreads) backward_kernel(const __grid_constant__ Frame f,
+                                                            const __grid_constant__ BackPtrs bp)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    BackSmem& s = *reinterpret_cast<BackSmem*>(smem_raw);
+    __shared__ float s_carry[4];  // slow path: {T at block start, S carried backwards, stop position, unused}
+    const int tid     = threadIdx.x;
+    const int n_items = f.status[3];
+    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+    float4 bgc = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
+
+    CamAcc acc;
+    acc.clear();
+    acc.view = 0;
+    // background colour gradient and the confidence gradient that the reference routes to descriptor 0
+    float bg_acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float p0_acc    = 0.f;
+
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x)
+    {
+        int lo = f.item_start[item], hi = f.item_start[item + 1];
+        if (lo >= hi) continue;
+        __syncthreads();
+
+        // ---- slow path: first pixel with a long list, blocks of kCap fragments, two sweeps
+        {
+            long long e0 = list_end(f, (long long)lo - 1), e1 = f.ends[lo];
+            int n_first  = (int)(e1 - e0);
+            if (n_first > kLongList)
+            {
+                PixelRef px = decode_pixel(f, lo);
+                Camera cam  = load_camera(f, px.view);
+                float4 G    = load_grad(f, bp, px);
+                int cnt     = n_first;
+                if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
+                const int n_blocks = (cnt + kCap - 1) / kCap;
+                // sweep 1 (forward): transmittance at the start of every block -> stored in seg_end[] (as float bits),
+                // which holds kMaxPixels+1 entries; longer lists are cut there (their tail has T ~ 0).
+                const int max_blocks = kMaxPixels;
+                const int used_blocks = min(n_blocks, max_blocks);
+                cnt = min(cnt, used_blocks * kCap);
+                if (tid == 0) s_carry[0] = 1.f, s_carry[2] = (float)cnt;
+                __syncthreads();
+                for (int blk = 0; blk < used_blocks; ++blk)
+                {
+                    int m = min(kCap, cnt - blk * kCap);
+                    for (int i = tid; i < m; i += kThreads)
+                    {
+                        int pid    = (int)(unsigned)f.keys[e0 + (long long)blk * kCap + i];
+                        int tex    = __ldg(f.index + pid);
+                        s.alpha[i] = fragment_alpha(f, cam, px, pid, tex, nullptr, nullptr);
+                    }
+                    __syncthreads();
+                    if (tid == 0)
+                    {
+                        float T = s_carry[0];
+                        s.seg_end[blk] = __float_as_int(T);
+                        int stop = (int)s_carry[2];
+                        for (int i = 0; i < m && blk * kCap + i < stop; ++i)
+                        {
+                            T = vetr_new_T(T, s.alpha[i]);
+                            if (bilinear && T < 0.001f) stop = blk * kCap + i + 1;
+                        }
+                        s_carry[0] = T;
+                        s_carry[2] = (float)stop;
+                    }
+                    __syncthreads();
+                }
+                const int eff_cnt  = (int)s_carry[2];            // fragments that were blended
+                const float T_end  = s_carry[0];
+                // background entry: reached unless a fragment ended the list early (mode 3)
+                const bool bg_term = !f.use_env && !(bilinear && !(T_end >= 0.001f));
+                if (tid == 0)
+                {
+                    float S = 0.f;
+                    if (bg_term)
+                    {
+                        float dotb = dot4(bgc, G, f.C);
+                        bg_acc[0] += T_end * 1.f * G.x, bg_acc[1] += T_end * 1.f * G.y, bg_acc[2] += T_end * 1.f * G.z;
+                        if (f.C > 3) bg_acc[3] += T_end * 1.f * G.w;
+                        if (!bilinear && f.bg_alpha_to_point0) p0_acc += dotb * T_end;
+                        S = T_end * 1.f * dotb;
+                    }
+                    s_carry[1] = S;
+                }
+                __syncthreads();
+                // sweep 2 (backward over blocks)
+                for (int blk = (eff_cnt + kCap - 1) / kCap - 1; blk >= 0; --blk)
+                {
+                    int m = min(kCap, eff_cnt - blk * kCap);
+                    for (int i = tid; i < m; i += kThreads)
+                    {
+                        unsigned long long key = f.keys[e0 + (long long)blk * kCap + i];
+                        int pid    = (int)(unsigned)key;
+                        int tex    = __ldg(f.index + pid);
+                        s.keys[i]  = key;
+                        s.alpha[i] = fragment_alpha(f, cam, px, pid, tex, nullptr, nullptr);
+                        float4 d;
+                        d.x = __ldg(f.texture + tex);
+                        d.y = __ldg(f.texture + (long long)f.n_tex + tex);
+                        d.z = __ldg(f.texture + 2LL * f.n_tex + tex);
+                        d.w = f.C > 3 ? __ldg(f.texture + 3LL * f.n_tex + tex) : 0.f;
+                        s.desc[i] = d;
+                        s.dot[i]  = dot4(d, G, f.C);
+                    }
+                    __syncthreads();
+                    if (tid == 0)
+                    {
+                        float T = __int_as_float(s.seg_end[blk]);
+                        for (int i = 0; i < m; ++i)
+                        {
+                            s.trans[i] = T;
+                            T          = vetr_new_T(T, s.alpha[i]);
+                        }
+                        float S = s_carry[1];
+                        for (int i = m - 1; i >= 0; --i)
+                        {
+                            float a = s.alpha[i], Ti = s.trans[i], dt = s.dot[i];
+                            s.dot[i] = Ti * dt - S / (1 - a + 1e-9f);
+                            S += Ti * a * dt;
+                        }
+                        s_carry[1] = S;
+                    }
+                    __syncthreads();
+                    const long long po = (long long)px.y * px.w + px.x;
+                    for (int i = tid; i < m; i += kThreads)
+                        fragment_backward(f, bp, cam, px, po, (int)(unsigned)s.keys[i], G, s.desc[i],
+                                          s.trans[i] * s.alpha[i], s.dot[i], acc);
+                    __syncthreads();
+                }
+                lo += 1;
+                if (lo >= hi)
+                {
+                    reduce_cam(f, bp, acc, px.view, s);
+                    continue;
+                }
+            }
+        }
+
+        // ---- fast path
+        const long long f0 = list_end(f, (long long)lo - 1);
+        const int np       = hi - lo;
+        if (tid < np)
+        {
+            s.seg_end[tid + 1] = (int)((long long)f.ends[lo + tid] - f0);
+            s.grad[tid]        = load_grad(f, bp, decode_pixel(f, (long long)lo + tid));
+        }
+        if (tid == 0) s.seg_end[0] = 0;
+        __syncthreads();
+        const int nf = s.seg_end[np];
+        {
+            int cur_view = -1;
+            Camera cam;
+            for (int i = tid; i < nf; i += kThreads)
+            {
+                int a = 0, b = np;
+                while (b - a > 1)
+                {
+                    int m = (a + b) >> 1;
+                    if (s.seg_end[m] <= i)
+                        a = m;
+                    else
+                        b = m;
+                }
+                s.seg_of[i] = (unsigned char)a;
+                const unsigned long long key = f.keys[f0 + i];
+                s.keys[i] = key;
+                int pid   = (int)(unsigned)key;
+                int tex   = __ldg(f.index + pid);
+                float al;
+                if (bilinear)
+                {
+                    PixelRef px = decode_pixel(f, (long long)lo + a);
+                    if (px.view != cur_view) cam = load_camera(f, px.view), cur_view = px.view;
+                    al = fragment_alpha(f, cam, px, pid, tex, nullptr, nullptr);
+                }
+                else
+                    al = __ldg(f.confidence + tex);
+                s.alpha[i] = al;
+                float4 d;
+                d.x = __ldg(f.texture + tex);
+                d.y = __ldg(f.texture + (long long)f.n_tex + tex);
+                d.z = __ldg(f.texture + 2LL * f.n_tex + tex);
+                d.w = f.C > 3 ? __ldg(f.texture + 3LL * f.n_tex + tex) : 0.f;
+                s.desc[i] = d;
+                s.dot[i]  = dot4(d, s.grad[a], f.C);
+            }
+        }
+        __syncthreads();
+        // per pixel: transmittance forward, suffix sum backward (O(n) form of RenderBackward.cu:1118-1181)
+        if (tid < np)
+        {
+            const int ss = s.seg_end[tid], se = s.seg_end[tid + 1];
+            int cnt = se - ss;
+            if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
+            float T = 1.f;
+            int eff = cnt;
+            for (int i = 0; i < cnt; ++i)
+            {
+                s.trans[ss + i] = T;
+                T               = vetr_new_T(T, s.alpha[ss + i]);
+                if (bilinear && T < 0.001f)
+                {
+                    eff = i + 1;
+                    break;
+                }
+            }
+            for (int i = ss + eff; i < se; ++i) s.trans[i] = __int_as_float(0x7fffffff);  // NaN marks: not blended, no gradient
+            bool bg_term = !f.use_env && !(bilinear && !(T >= 0.001f));
+            float4 G = s.grad[tid];
+            float S  = 0.f;
+            if (bg_term)
+            {
+                float dotb = dot4(bgc, G, f.C);
+                bg_acc[0] += T * 1.f * G.x, bg_acc[1] += T * 1.f * G.y, bg_acc[2] += T * 1.f * G.z;
+                if (f.C > 3) bg_acc[3] += T * 1.f * G.w;
+                if (!bilinear && f.bg_alpha_to_point0) p0_acc += dotb * T;
+                S = T * 1.f * dotb;
+            }
+            for (int i = ss + eff - 1; i >= ss; --i)
+            {
+                float a = s.alpha[i], Ti = s.trans[i], dt = s.dot[i];
+                s.dot[i] = Ti * dt - S / (1 - a + 1e-9f);
+                S += Ti * a * dt;
+            }
+        }
+        __syncthreads();
+        // per fragment: scatter
+        {
+            int cur_view = -1;
+            Camera cam;
+            for (int i = tid; i < nf; i += kThreads)
+            {
+                float Ti = s.trans[i];
+                if (Ti != Ti) continue;
+                int a       = s.seg_of[i];
+                PixelRef px = decode_pixel(f, (long long)lo + a);
+                if (px.view != cur_view) cam = load_camera(f, px.view), cur_view = px.view;
+                fragment_backward(f, bp, cam, px, (long long)px.y * px.w + px.x, (int)(unsigned)s.keys[i], s.grad[a],
+                                  s.desc[i], Ti * s.alpha[i], s.dot[i], acc);
+            }
+        }
+        int main_view = (int)((long long)lo / f.P);
+        reduce_cam(f, bp, acc, main_view, s);
+    }
+
+    // background gradient and the descriptor-0 confidence term: CTA reduction, one atomic per value
+    __syncthreads();
+    {
+        const int lane = tid & 31, warp = tid >> 5;
+        float v[5] = {bg_acc[0], bg_acc[1], bg_acc[2], bg_acc[3], p0_acc};
+        for (int k = 0; k < 5; ++k)
+        {
+            float x = v[k];
+            for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+            if (lane == 0) s.red[warp][k] = (double)x;
+        }
+        __syncthreads();
+        if (tid < 5)
+        {
+            float x = 0.f;
+            for (int w = 0; w < kThreads / 32; ++w) x += (float)s.red[w][tid];
+            if (x != 0.f)
+            {
+                if (tid < 4)
+                {
+                    if (tid < f.C) atomicAdd(bp.g_background + tid, x);
+                }
+                else
+                    atomicAdd(bp.g_conf + 0, x);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Epilogues.
+
+__global__ void transpose_desc_kernel(const float4* __restrict__ g_desc, float* __restrict__ g_texture, int n_tex, int C)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tex) return;
+    float4 v = g_desc[i];
+    g_texture[i] = v.x;
+    g_texture[(long long)n_tex + i] = v.y;
+    g_texture[2LL * n_tex + i] = v.z;
+    if (C > 3) g_texture[3LL * n_tex + i] = v.w;
+}
+
+// NormalizeGradient for points (PointRenderer.cu:1273-1280): divide by the hit count where it is positive.
+__global__ void normalize_points_kernel(float4* g_points, float* g_count, int n)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float4 v = g_points[i];
+    float c  = v.w;
+    if (g_count) g_count[i] = c;
+    if (c > 0) v.x = v.x / c, v.y = v.y / c, v.z = v.z / c;
+    v.w         = 0.f;
+    g_points[i] = v;
+}
+
+template <typename T, int N>
+__global__ void normalize_rows_kernel(T* g, const float* count, int n)  // NormalizeGradientDevTensor, :1092-1109
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float c = count[i];
+    if (c > 0)
+        for (int k = 0; k < N; ++k) g[(long long)i * N + k] = g[(long long)i * N + k] / c;
+}
+
+// ApplyTangent (PointRenderer.cu:1325-1341): pose <- exp_se3(t) * pose in double; tangent = (translation, rotation).
+__global__ void apply_tangent_kernel(double* tangent, double* poses, int n)
+{
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    double* t = tangent + 6 * idx;
+    double* p = poses + 8 * idx;
+    double ux = t[0], uy = t[1], uz = t[2], wx = t[3], wy = t[4], wz = t[5];
+    double th2 = wx * wx + wy * wy + wz * wz, th = sqrt(th2);
+    double imag, real, a, bb;
+    if (th < 1e-10)
+    {
+        double th4 = th2 * th2;
+        imag = 0.5 - th2 / 48.0 + th4 / 3840.0;
+        real = 1.0 - th2 / 8.0 + th4 / 384.0;
+        a    = 0.5;
+        bb   = 1.0 / 6.0;
+    }
+    else
+    {
+        imag = sin(0.5 * th) / th;
+        real = cos(0.5 * th);
+        a    = (1 - cos(th)) / th2;
+        bb   = (th - sin(th)) / (th2 * th);
+    }
+    double x1 = imag * wx, y1 = imag * wy, z1 = imag * wz, w1 = real;
+    double O[9] = {0, -wz, wy, wz, 0, -wx, -wy, wx, 0};
+    double u[3] = {ux, uy, uz}, te[3];
+    for (int r = 0; r < 3; ++r)
+    {
+        te[r] = u[r];
+        for (int c = 0; c < 3; ++c)
+        {
+            double o2 = O[3 * r] * O[c] + O[3 * r + 1] * O[3 + c] + O[3 * r + 2] * O[6 + c];
+            te[r] += (a * O[3 * r + c] + bb * o2) * u[c];
+        }
+    }
+    double x2 = p[0], y2 = p[1], z2 = p[2], w2 = p[3];
+    double q[4] = {w1 * x2 + x1 * w2 + y1 * z2 - z1 * y2, w1 * y2 - x1 * z2 + y1 * w2 + z1 * x2,
+                   w1 * z2 + x1 * y2 - y1 * x2 + z1 * w2, w1 * w2 - x1 * x2 - y1 * y2 - z1 * z2};
+    double nrm = sqrt(q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3]);
+    double tp[3] = {p[4], p[5], p[6]};
+    double cx = y1 * tp[2] - z1 * tp[1], cy = z1 * tp[0] - x1 * tp[2], cz = x1 * tp[1] - y1 * tp[0];
+    cx *= 2, cy *= 2, cz *= 2;
+    double rx = tp[0] + w1 * cx + (y1 * cz - z1 * cy);
+    double ry = tp[1] + w1 * cy + (z1 * cx - x1 * cz);
+    double rz = tp[2] + w1 * cz + (x1 * cy - y1 * cx);
+    for (int k = 0; k < 4; ++k) p[k] = q[k] / nrm;
+    p[4] = rx + te[0], p[5] = ry + te[1], p[6] = rz + te[2];
+    for (int k = 0; k < 6; ++k) t[k] = 0.0;
+}
+
+}  // namespace vetr
+
+// =========================================================================================================
+// C ABI
+
+using namespace vetr;
+
+struct vetr_ctx
+{
+    int device           = 0;
+    cudaStream_t stream  = nullptr;
+    int last_cuda        = 0;
+    int sm_count         = 148;
+    long long* tile_sums = nullptr;  // scan scratch
+    long long tile_cap   = 0;
+    int blend_ctas_per_sm = 1, back_ctas_per_sm = 1;
+};
+
+#define VETR_CUDA(ctx, call)                      \
+    do                                            \
+    {                                             \
+        cudaError_t e_ = (call);                  \
+        if (e_ != cudaSuccess)                    \
+        {                                         \
+            (ctx)->last_cuda = (int)e_;           \
+            return VETR_E_CUDA;                   \
+        }                                         \
+    } while (0)
+
+static int64_t pyramid(int w, int h, int L, int* lw, int* lh, long long* lbase)
+{
+    long long base = 0;
+    for (int l = 0; l < L; ++l)
+    {
+        if (lw) lw[l] = w, lh[l] = h, lbase[l] = base;
+        base += (long long)w * h;
+        w /= 2;
+        h /= 2;
+    }
+    return base;
+}
+
+extern "C" int64_t vetr_pyramid_pixels(int w, int h, int num_layers)
+{
+    if (w <= 0 || h <= 0 || num_layers < 1 || num_layers > VETR_MAX_LAYERS) return -1;
+    return pyramid(w, h, num_layers, nullptr, nullptr, nullptr);
+}
+
+extern "C" int64_t vetr_item_table_entries(int64_t capacity, int64_t n_pixels_total)
+{
+    if (capacity < 0 || n_pixels_total < 0) return -1;
+    int64_t cap = capacity < 0x7fffffffLL ? capacity : 0x7fffffffLL;
+    return (cap + (int64_t)kPixelWork * n_pixels_total + kQuantum - 1) / kQuantum + 2;
+}
+
+extern "C" int64_t vetr_max_fragments(int n_points, int n_views, const vetr_params* p)
+{
+    if (!p) return -1;
+    int64_t f = (int64_t)n_points * p->num_layers * n_views;
+    if (p->render_mode == VETR_MODE_BILINEAR_BLEND) f *= 4;
+    return f;
+}
+
+extern "C" const char* vetr_strerror(int status)
+{
+    switch (status)
+    {
+        case VETR_OK: return "ok";
+        case VETR_E_INVALID_ARG: return "invalid argument";
+        case VETR_E_CUDA: return "CUDA runtime error";
+        case VETR_E_UNSUPPORTED: return "unsupported camera model or option";
+        case VETR_E_LIST_OVERFLOW: return "fragment key buffer too small";
+        case VETR_E_TOO_LARGE: return "size exceeds a fixed limit";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int vetr_last_cuda_error(const vetr_ctx* ctx) { return ctx ? ctx->last_cuda : 0; }
+
+static int ensure_scratch(vetr_ctx* ctx, long long n_tiles)
+{
+    if (n_tiles > ctx->tile_cap)
+    {
+        if (ctx->tile_sums) cudaFree(ctx->tile_sums);
+        ctx->tile_sums = nullptr;
+        long long cap  = n_tiles + n_tiles / 4 + 16;
+        VETR_CUDA(ctx, cudaMalloc(&ctx->tile_sums, cap * sizeof(long long)));
+        ctx->tile_cap = cap;
+    }
+    return VETR_OK;
+}
+
+extern "C" int vetr_create(vetr_ctx** out, int device, void* cuda_stream)
+{
+    if (!out) return VETR_E_INVALID_ARG;
+    vetr_ctx* ctx = new (std::nothrow) vetr_ctx();
+    if (!ctx) return VETR_E_INVALID_ARG;
+    ctx->device = device;
+    ctx->stream = (cudaStream_t)cuda_stream;
+    cudaError_t e = cudaSetDevice(device);
+    cudaDeviceProp prop;
+    if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, device);
+    if (e == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(sort_blend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(BlendSmem));
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(BackSmem));
+    if (e == cudaSuccess)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->blend_ctas_per_sm, sort_blend_kernel, kThreads,
+                                                          sizeof(BlendSmem));
+    if (e == cudaSuccess)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->back_ctas_per_sm, backward_kernel, kThreads,
+                                                          sizeof(BackSmem));
+    if (e != cudaSuccess)
+    {
+        delete ctx;
+        *out = nullptr;
+        return VETR_E_CUDA;
+    }
+    if (ctx->blend_ctas_per_sm < 1) ctx->blend_ctas_per_sm = 1;
+    if (ctx->back_ctas_per_sm < 1) ctx->back_ctas_per_sm = 1;
+    *out = ctx;
+    return VETR_OK;
+}
+
+extern "C" void vetr_destroy(vetr_ctx* ctx)
+{
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->tile_sums) cudaFree(ctx->tile_sums);
+    delete ctx;
+}
+
+extern "C" int vetr_set_stream(vetr_ctx* ctx, void* cuda_stream)
+{
+    if (!ctx) return VETR_E_INVALID_ARG;
+    ctx->stream = (cudaStream_t)cuda_stream;
+    return VETR_OK;
+}
+
+static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_cloud* cloud, const vetr_texture* tex,
+                      const vetr_cameras* cams, const vetr_view* views, int n_views, const vetr_lists* lists)
+{
+    if (!ctx || !p || !cloud || !tex || !cams || !views || !lists) return VETR_E_INVALID_ARG;
+    if (n_views < 1 || n_views > VETR_MAX_VIEWS) return VETR_E_INVALID_ARG;
+    if (p->num_layers < 1 || p->num_layers > VETR_MAX_LAYERS) return VETR_E_INVALID_ARG;
+    if (p->num_channels != 3 && p->num_channels != 4) return VETR_E_INVALID_ARG;
+    if (p->render_mode != VETR_MODE_FULL_BLEND && p->render_mode != VETR_MODE_BILINEAR_BLEND) return VETR_E_UNSUPPORTED;
+    if (cloud->n < 0 || tex->n_tex < 1 || !cloud->position || !cloud->index || !tex->texture || !tex->confidence ||
+        !tex->background || !cams->poses_se3 || !cams->intrinsics)
+        return VETR_E_INVALID_ARG;
+    if (((uintptr_t)cloud->position & 15) != 0) return VETR_E_INVALID_ARG;
+    if (!lists->counts || !lists->ends || !lists->keys || !lists->status || lists->capacity < 0) return VETR_E_INVALID_ARG;
+    memset(&f, 0, sizeof(f));
+    f.n_views = n_views, f.L = p->num_layers, f.C = p->num_channels, f.n = cloud->n, f.n_tex = tex->n_tex;
+    f.w = views[0].w, f.h = views[0].h;
+    if (f.w <= 0 || f.h <= 0) return VETR_E_INVALID_ARG;
+    for (int b = 0; b < n_views; ++b)
+    {
+        const vetr_view& v = views[b];
+        if (v.w != f.w || v.h != f.h) return VETR_E_INVALID_ARG;
+        if (v.camera_model != 0) return VETR_E_UNSUPPORTED;
+        if (v.image_index < 0 || v.image_index >= cams->n_img || v.camera_index < 0 || v.camera_index >= cams->n_cam)
+            return VETR_E_INVALID_ARG;
+        f.views[b].image_index = v.image_index, f.views[b].camera_index = v.camera_index;
+        memcpy(f.views[b].crop, v.crop, sizeof(v.crop));
+        memcpy(f.views[b].rot, v.rot, sizeof(v.rot));
+    }
+    f.mode = p->render_mode, f.drop_by_radius = p->drop_out_points_by_radius, f.use_env = p->use_environment_map;
+    f.viewer_only = p->viewer_only, f.dbg_max_len = p->debug_max_list_length, f.need_point_grad = p->need_point_gradient;
+    f.bg_alpha_to_point0 = p->background_alpha_to_point0, f.keep_sorted = p->keep_sorted_lists;
+    f.radius_threshold = p->drop_out_radius_threshold, f.dist_cutoff = p->dist_cutoff;
+    f.stability_cutoff = p->stability_cutoff_value, f.k_grad_factor = p->K_gradient_factor;
+    f.dist_grad_factor = p->distortion_gradient_factor, f.mask_value = p->output_background_mask_value;
+    f.P  = pyramid(f.w, f.h, f.L, f.lw, f.lh, f.lbase);
+    f.PT = f.P * n_views;
+    if (f.PT > 0x7fffffffLL) return VETR_E_TOO_LARGE;
+    f.position = (const float4*)cloud->position, f.index = cloud->index;
+    f.texture = tex->texture, f.confidence = tex->confidence, f.background = tex->background;
+    f.poses = cams->poses_se3, f.intr = cams->intrinsics;
+    f.counts = lists->counts, f.ends = lists->ends, f.keys = (unsigned long long*)lists->keys;
+    f.capacity = lists->capacity, f.status = lists->status;
+    long long n_tiles = (f.PT + kScanTile - 1) / kScanTile;
+    if (!lists->items || lists->items_capacity < vetr_item_table_entries(lists->capacity, f.PT)) return VETR_E_INVALID_ARG;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    int rc = ensure_scratch(ctx, n_tiles);
+    if (rc != VETR_OK) return rc;
+    f.item_start = lists->items;
+    return VETR_OK;
+}
+
+extern "C" int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* cloud, const vetr_texture* texture,
+                            const vetr_cameras* cameras, const vetr_view* views, int n_views, const float* dropout,
+                            const vetr_lists* lists, float* const* out_color, float* const* out_weight,
+                            float* const* out_mask, float* const* out_depth)
+{
+    Frame f;
+    int rc = fill_frame(ctx, f, params, cloud, texture, cameras, views, n_views, lists);
+    if (rc != VETR_OK) return rc;
+    if (!out_color) return VETR_E_INVALID_ARG;
+    f.dropout = dropout;
+    OutPtrs out;
+    memset(&out, 0, sizeof(out));
+    out.has_weight = out_weight != nullptr, out.has_mask = out_mask != nullptr, out.has_depth = out_depth != nullptr;
+    for (int l = 0; l < f.L; ++l)
+    {
+        if (!out_color[l]) return VETR_E_INVALID_ARG;
+        out.color[l] = out_color[l];
+        if (out_weight) out.weight[l] = out_weight[l];
+        if (out_mask) out.mask[l] = out_mask[l];
+        if (out_depth) out.depth[l] = out_depth[l];
+    }
+    cudaStream_t st = ctx->stream;
+    VETR_CUDA(ctx, cudaMemsetAsync(f.counts, 0, f.PT * sizeof(int), st));
+    VETR_CUDA(ctx, cudaMemsetAsync(f.status, 0, 4 * sizeof(int), st));
+    const int point_ctas = (f.n + kThreads * kPointsPerThread - 1) / (kThreads * kPointsPerThread);
+    if (point_ctas > 0) project_kernel<false><<<dim3(point_ctas, n_views), kThreads, 0, st>>>(f);
+    const int n_tiles = (int)((f.PT + kScanTile - 1) / kScanTile);
+    scan_tile_sums_kernel<<<n_tiles, 256, 0, st>>>(f.counts, f.PT, ctx->tile_sums, f.status);
+    scan_spine_kernel<<<1, 1024, 0, st>>>(ctx->tile_sums, n_tiles, f.PT, f.capacity, f.status, f.item_start);
+    scan_apply_kernel<<<n_tiles, 256, 0, st>>>(f.counts, f.PT, ctx->tile_sums, f.ends, f.status, f.item_start);
+    if (point_ctas > 0) project_kernel<true><<<dim3(point_ctas, n_views), kThreads, 0, st>>>(f);
+    const int grid = ctx->sm_count * ctx->blend_ctas_per_sm;
+    sort_blend_kernel<<<grid, kThreads, sizeof(BlendSmem), st>>>(f, out);
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* cloud, const vetr_texture* texture,
+                             const vetr_cameras* cameras, const vetr_view* views, int n_views, const vetr_lists* lists,
+                             const float* const* out_color, const float* const* grad_color, float* g_desc, float* g_conf,
+                             float* g_points, float* g_background, double* g_pose, float* g_pose_count, float* g_intr,
+                             float* g_intr_count)
+{
+    Frame f;
+    int rc = fill_frame(ctx, f, params, cloud, texture, cameras, views, n_views, lists);
+    if (rc != VETR_OK) return rc;
+    if (!out_color || !grad_color || !g_desc || !g_conf || !g_background) return VETR_E_INVALID_ARG;
+    if ((g_pose != nullptr) != (g_pose_count != nullptr) || (g_intr != nullptr) != (g_intr_count != nullptr))
+        return VETR_E_INVALID_ARG;
+    if (((uintptr_t)g_desc & 15) != 0 || ((uintptr_t)g_points & 15) != 0) return VETR_E_INVALID_ARG;
+    BackPtrs bp;
+    memset(&bp, 0, sizeof(bp));
+    for (int l = 0; l < f.L; ++l)
+    {
+        if (!out_color[l] || !grad_color[l]) return VETR_E_INVALID_ARG;
+        bp.out_color[l] = out_color[l], bp.grad_color[l] = grad_color[l];
+    }
+    bp.g_desc = (float4*)g_desc, bp.g_conf = g_conf, bp.g_points = (float4*)g_points, bp.g_background = g_background;
+    bp.g_pose = g_pose, bp.g_pose_count = g_pose_count, bp.g_intr = g_intr, bp.g_intr_count = g_intr_count;
+    if (!f.need_point_grad && f.mode != VETR_MODE_BILINEAR_BLEND) bp.g_points = nullptr;
+    const int grid = ctx->sm_count * ctx->back_ctas_per_sm;
+    backward_kernel<<<grid, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+extern "C" int vetr_finalize_gradients(vetr_ctx* ctx, int channels, int n_tex, const float* g_desc, float* g_texture,
+                                       int n, float* g_points, float* g_points_count, int n_img, double* g_pose,
+                                       const float* g_pose_count, int n_cam, float* g_intr, const float* g_intr_count)
+{
+    if (!ctx) return VETR_E_INVALID_ARG;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t st = ctx->stream;
+    if (g_desc && g_texture && n_tex > 0)
+    {
+        if (channels != 3 && channels != 4) return VETR_E_INVALID_ARG;
+        transpose_desc_kernel<<<(n_tex + 255) / 256, 256, 0, st>>>((const float4*)g_desc, g_texture, n_tex, channels);
+    }
+    if (g_points && n > 0) normalize_points_kernel<<<(n + 255) / 256, 256, 0, st>>>((float4*)g_points, g_points_count, n);
+    if (g_pose && g_pose_count && n_img > 0)
+        normalize_rows_kernel<double, 6><<<(n_img + 127) / 128, 128, 0, st>>>(g_pose, g_pose_count, n_img);
+    if (g_intr && g_intr_count && n_cam > 0)
+        normalize_rows_kernel<float, 13><<<(n_cam + 127) / 128, 128, 0, st>>>(g_intr, g_intr_count, n_cam);
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+extern "C" int vetr_apply_tangent(vetr_ctx* ctx, double* tangent, double* poses_se3, int n)
+{
+    if (!ctx || !tangent || !poses_se3 || n < 0) return VETR_E_INVALID_ARG;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (n > 0) apply_tangent_kernel<<<(n + 127) / 128, 128, 0, ctx->stream>>>(tangent, poses_se3, n);
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+extern "C" int vetr_read_status(vetr_ctx* ctx, const vetr_lists* lists, int64_t* total_fragments, int32_t* longest_list)
+{
+    if (!ctx || !lists || !lists->status) return VETR_E_INVALID_ARG;
+    int h[4];
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    VETR_CUDA(ctx, cudaMemcpyAsync(h, lists->status, sizeof(h), cudaMemcpyDeviceToHost, ctx->stream));
+    VETR_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (total_fragments) *total_fragments = h[0];
+    if (longest_list) *longest_list = h[2];
+    return h[1] ? VETR_E_LIST_OVERFLOW : VETR_OK;
+}
+
+namespace vetr
+{
+__global__ void unpack_lists_kernel(const unsigned long long* keys, long long first, long long n, int* out)
+{
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    unsigned long long k = keys[first + i];
+    out[i]     = (int)(unsigned)(k >> 32);
+    out[n + i] = (int)(unsigned)k;
+}
+__global__ void local_offsets_kernel(const int* ends, const int* counts, long long g0, long long npix, long long first, int* out)
+{
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= npix) return;
+    out[i] = (int)((long long)ends[g0 + i] - counts[g0 + i] - first);
+}
+}  // namespace vetr
+
+extern "C" int vetr_get_lists(vetr_ctx* ctx, const vetr_lists* lists, int w, int h, int num_layers, int n_views, int view,
+                              int layer, int32_t* out_collections, int32_t* out_scanned_counting, int64_t* n_fragments)
+{
+    if (!ctx || !lists || num_layers < 1 || num_layers > VETR_MAX_LAYERS || view < 0 || view >= n_views || layer < 0 ||
+        layer >= num_layers)
+        return VETR_E_INVALID_ARG;
+    int lw[VETR_MAX_LAYERS], lh[VETR_MAX_LAYERS];
+    long long lbase[VETR_MAX_LAYERS];
+    long long P    = pyramid(w, h, num_layers, lw, lh, lbase);
+    long long g0   = (long long)view * P + lbase[layer];
+    long long npix = (long long)lw[layer] * lh[layer];
+    if (npix == 0)
+    {
+        if (n_fragments) *n_fragments = 0;
+        return VETR_OK;
+    }
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    int first_end, first_cnt, last_end;
+    VETR_CUDA(ctx, cudaMemcpyAsync(&first_end, lists->ends + g0, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VETR_CUDA(ctx, cudaMemcpyAsync(&first_cnt, lists->counts + g0, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VETR_CUDA(ctx, cudaMemcpyAsync(&last_end, lists->ends + g0 + npix - 1, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VETR_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    long long first = (long long)first_end - first_cnt;
+    long long n     = (long long)last_end - first;
+    if (n_fragments) *n_fragments = n;
+    if (out_collections && n > 0)
+        unpack_lists_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>((const unsigned long long*)lists->keys, first, n,
+                                                                                   out_collections);
+    if (out_scanned_counting)
+        local_offsets_kernel<<<(unsigned)((npix + 255) / 256), 256, 0, ctx->stream>>>(lists->ends, lists->counts, g0, npix, first,
+                                                                                      out_scanned_counting);
+    VETR_CUDA(ctx, cudaGetLastError());
+    VETR_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return VETR_OK;
+}

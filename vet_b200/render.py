@@ -1,0 +1,237 @@
+"""Host-side mirror of the reference's render operator on top of the C ABI.
+
+`Rasterizer` plays the role of PointRendererCache + BlendPointCloudForward / BlendPointCloudBackward
+(rendering/PointRenderer.h:112-248, PointRenderer.cu:657-1069, 1111-1323): it owns the per-call scratch
+(the reference caches it between calls and re-allocates when (C, N, L, B, h, w) changes, PointRenderer.cu:313-336),
+sequences forward and backward, and returns the tensors in the reference's layouts.  torch is used for device
+memory and streams only; all arithmetic happens in libvetr.so.  Batches larger than the library's per-launch view
+limit are processed in groups.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib as L
+
+
+def default_params(**kw) -> dict:
+    """RenderParams defaults the kernels read (data/Settings.h:27-73)."""
+    p = dict(render_mode=L.MODE_FULL_BLEND, num_layers=4, num_channels=4, drop_out_points_by_radius=1,
+             drop_out_radius_threshold=0.6, dist_cutoff=20.0, use_environment_map=0, viewer_only=0,
+             stability_cutoff_value=10000.0, debug_max_list_length=-1, need_point_gradient=1,
+             K_gradient_factor=0.5, distortion_gradient_factor=0.005, output_background_mask_value=0.0,
+             background_alpha_to_point0=1, keep_sorted_lists=1)
+    p.update(kw)
+    return p
+
+
+def level_sizes(w: int, h: int, num_layers: int):
+    out = []
+    for _ in range(num_layers):
+        out.append((w, h))
+        w //= 2
+        h //= 2
+    return out
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _ptr_array(ts: Optional[Sequence[torch.Tensor]]):
+    if ts is None:
+        return None
+    return (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+
+
+class FragmentLists:
+    """Device buffers of vetr_lists for one group of views."""
+
+    def __init__(self, device, n_pixels_total: int, capacity: int):
+        i32 = dict(dtype=torch.int32, device=device)
+        self.capacity = int(capacity)
+        self.counts = torch.empty(n_pixels_total, **i32)
+        self.ends = torch.empty(n_pixels_total, **i32)
+        self.keys = torch.empty(max(self.capacity, 1), dtype=torch.int64, device=device)
+        self.status = torch.zeros(4, **i32)
+        n_items = int(L.lib().vetr_item_table_entries(self.capacity, n_pixels_total))
+        self.items = torch.empty(n_items, **i32)
+        self.c = L.Lists(self.counts.data_ptr(), self.ends.data_ptr(), self.keys.data_ptr(), self.capacity,
+                         self.status.data_ptr(), self.items.data_ptr(), n_items)
+
+
+class Rasterizer:
+    """One context (device + stream).  Inputs are CUDA tensors in the reference's layouts."""
+
+    def __init__(self, device: int = 0, stream: Optional[torch.cuda.Stream] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("vet_b200.Rasterizer needs a CUDA device; there is no CPU path")
+        self.device = torch.device("cuda", device)
+        self._ctx = C.c_void_p()
+        st = C.c_void_p(stream.cuda_stream) if stream is not None else None
+        self._stream = stream
+        rc = L.lib().vetr_create(C.byref(self._ctx), device, st)
+        if rc != L.OK:
+            raise L.VetrError(rc, "vetr_create")
+        self._lists_cache = {}
+        self._saved = None
+
+    def close(self):
+        if self._ctx:
+            L.lib().vetr_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int, where: str):
+        if rc != L.OK:
+            raise L.VetrError(rc, where, L.lib().vetr_last_cuda_error(self._ctx))
+
+    # ---- helpers -----------------------------------------------------------------------------------------
+    def _views(self, views):
+        arr = (L.View * len(views))()
+        for i, v in enumerate(views):
+            arr[i] = L.View(v.w, v.h, v.image_index, v.camera_index, v.camera_model, (C.c_float * 5)(*v.crop),
+                            (C.c_float * 4)(*v.rot))
+        return arr
+
+    def _lists(self, slot: int, n_pixels_total: int, capacity: int) -> FragmentLists:
+        key = (slot, n_pixels_total)
+        cur = self._lists_cache.get(key)
+        if cur is None or cur.capacity < capacity:
+            cur = FragmentLists(self.device, n_pixels_total, capacity)
+            self._lists_cache[key] = cur
+        return cur
+
+    # ---- forward -----------------------------------------------------------------------------------------
+    def forward(self, position, index, texture, confidence, background, poses, intrinsics, views, params: dict,
+                dropout=None, capacity: Optional[int] = None, want_weight=True, want_mask=False, want_depth=False):
+        """Returns dict(color=[L x [B,C,h,w]], weight=..., mask=..., depth=...).  Keeps what backward() needs."""
+        lib = L.lib()
+        prm = L.Params(**{k: params[k] for k, _ in L.Params._fields_})
+        B, Cn, Ln = len(views), texture.shape[0], prm.num_layers
+        prm.num_channels = Cn
+        w, h = views[0].w, views[0].h
+        sizes = level_sizes(w, h, Ln)
+        P = int(lib.vetr_pyramid_pixels(w, h, Ln))
+        f32 = dict(dtype=torch.float32, device=self.device)
+        color = [torch.empty(B, Cn, hh, ww, **f32) for (ww, hh) in sizes]
+        weight = [torch.empty(B, 1, hh, ww, **f32) for (ww, hh) in sizes] if want_weight else None
+        mask = [torch.empty(B, 1, hh, ww, **f32) for (ww, hh) in sizes] if want_mask else None
+        depth = [torch.empty(B, 1, hh, ww, **f32) for (ww, hh) in sizes] if want_depth else None
+        cloud = L.Cloud(position.data_ptr(), index.data_ptr(), position.shape[0])
+        tex = L.Texture(texture.data_ptr(), confidence.data_ptr(), background.data_ptr(), texture.shape[1])
+        cams = L.Cameras(poses.data_ptr(), intrinsics.data_ptr(), poses.shape[0], intrinsics.shape[0])
+        groups = []
+        for gi, b0 in enumerate(range(0, B, L.MAX_VIEWS)):
+            b1 = min(B, b0 + L.MAX_VIEWS)
+            nb = b1 - b0
+            cap = capacity if capacity is not None else int(lib.vetr_max_fragments(position.shape[0], nb, C.byref(prm)))
+            lists = self._lists(gi, P * nb, cap)
+            varr = self._views(views[b0:b1])
+            sl = lambda ts: None if ts is None else [t[b0:b1] for t in ts]
+            dro = None if dropout is None else dropout[b0:b1]
+            rc = lib.vetr_forward(self._ctx, C.byref(prm), C.byref(cloud), C.byref(tex), C.byref(cams), varr, nb,
+                                  _ptr(dro), C.byref(lists.c), _ptr_array(sl(color)), _ptr_array(sl(weight)),
+                                  _ptr_array(sl(mask)), _ptr_array(sl(depth)))
+            self._check(rc, "vetr_forward")
+            groups.append((b0, b1, lists, varr))
+        self._saved = dict(prm=prm, cloud=cloud, tex=tex, cams=cams, groups=groups, color=color, P=P, sizes=sizes,
+                           tensors=(position, index, texture, confidence, background, poses, intrinsics, dropout))
+        return dict(color=color, weight=weight, mask=mask, depth=depth)
+
+    def fragment_count(self):
+        """(total fragments, longest list) of the last forward; synchronises. Raises on key-buffer overflow."""
+        total, longest = 0, 0
+        for (_, _, lists, _) in self._saved["groups"]:
+            t, m = C.c_int64(), C.c_int32()
+            self._check(L.lib().vetr_read_status(self._ctx, C.byref(lists.c), C.byref(t), C.byref(m)), "vetr_read_status")
+            total += t.value
+            longest = max(longest, m.value)
+        return total, longest
+
+    def lists_of(self, view: int, layer: int):
+        """Reference layout of one (view, layer): collections [2,F_l] int32 and scanned_counting [h_l*w_l] int32."""
+        s = self._saved
+        for (b0, b1, lists, varr) in s["groups"]:
+            if b0 <= view < b1:
+                w, h = s["sizes"][0]
+                n = C.c_int64()
+                args = (self._ctx, C.byref(lists.c), w, h, s["prm"].num_layers, b1 - b0, view - b0, layer)
+                self._check(L.lib().vetr_get_lists(*args, None, None, C.byref(n)), "vetr_get_lists")
+                lw, lh = s["sizes"][layer]
+                coll = torch.empty(2, max(n.value, 0), dtype=torch.int32, device=self.device)
+                scanned = torch.empty(lw * lh, dtype=torch.int32, device=self.device)
+                self._check(L.lib().vetr_get_lists(*args, _ptr(coll), _ptr(scanned), C.byref(n)), "vetr_get_lists")
+                return coll, scanned
+        raise IndexError(view)
+
+    # ---- backward ----------------------------------------------------------------------------------------
+    def backward_raw(self, grad_color, want_points=True, want_pose=True, want_intrinsics=True, accum=None):
+        """Raw gradient sums of the last forward: dict(desc [n_tex,4], conf [n_tex], points [n,4] (xyz sum, hit count),
+        background [C], pose [n_img,6] f64, pose_count, intrinsics [n_cam,13], intrinsics_count).
+        `accum` (a dict from an earlier call) accumulates further views into the same buffers."""
+        s = self._saved
+        lib = L.lib()
+        position, index, texture = s["tensors"][0], s["tensors"][1], s["tensors"][2]
+        poses, intrinsics = s["tensors"][5], s["tensors"][6]
+        n, n_tex, Cn = position.shape[0], texture.shape[1], texture.shape[0]
+        f32 = dict(dtype=torch.float32, device=self.device)
+        g = accum
+        if g is None:
+            g = dict(desc=torch.zeros(n_tex, 4, **f32), conf=torch.zeros(n_tex, **f32),
+                     background=torch.zeros(Cn, **f32))
+            if want_points:
+                g["points"] = torch.zeros(n, 4, **f32)
+            if want_pose:
+                g["pose"] = torch.zeros(poses.shape[0], 6, dtype=torch.float64, device=self.device)
+                g["pose_count"] = torch.zeros(poses.shape[0], **f32)
+            if want_intrinsics:
+                g["intrinsics"] = torch.zeros(intrinsics.shape[0], 13, **f32)
+                g["intrinsics_count"] = torch.zeros(intrinsics.shape[0], **f32)
+        grad_color = [x.contiguous() for x in grad_color]
+        for (b0, b1, lists, varr) in s["groups"]:
+            oc = [t[b0:b1] for t in s["color"]]
+            gc = [t[b0:b1] for t in grad_color]
+            rc = lib.vetr_backward(self._ctx, C.byref(s["prm"]), C.byref(s["cloud"]), C.byref(s["tex"]),
+                                   C.byref(s["cams"]), varr, b1 - b0, C.byref(lists.c), _ptr_array(oc), _ptr_array(gc),
+                                   _ptr(g["desc"]), _ptr(g["conf"]), _ptr(g.get("points")), _ptr(g["background"]),
+                                   _ptr(g.get("pose")), _ptr(g.get("pose_count")), _ptr(g.get("intrinsics")),
+                                   _ptr(g.get("intrinsics_count")))
+            self._check(rc, "vetr_backward")
+        return g
+
+    def finalize(self, g: dict):
+        """Raw sums -> the reference's return tensors (PointRenderer.cu:1251-1322): texture [C,n_tex], confidence
+        [1,n_tex], background [C], points [n,4] averaged by hit count, pose tangent and intrinsics averaged."""
+        n_tex = g["desc"].shape[0]
+        Cn = g["background"].shape[0]
+        g_texture = torch.empty(Cn, n_tex, dtype=torch.float32, device=self.device)
+        pts, pose, intr = g.get("points"), g.get("pose"), g.get("intrinsics")
+        rc = L.lib().vetr_finalize_gradients(
+            self._ctx, Cn, n_tex, _ptr(g["desc"]), _ptr(g_texture), 0 if pts is None else pts.shape[0], _ptr(pts), None,
+            0 if pose is None else pose.shape[0], _ptr(pose), _ptr(g.get("pose_count")),
+            0 if intr is None else intr.shape[0], _ptr(intr), _ptr(g.get("intrinsics_count")))
+        self._check(rc, "vetr_finalize_gradients")
+        return dict(texture=g_texture, confidence=g["conf"].view(1, -1), background=g["background"], points=pts,
+                    pose=pose, intrinsics=intr)
+
+    def apply_tangent(self, tangent: torch.Tensor, poses: torch.Tensor):
+        """ApplyTangentToPose (PointRenderer.cu:1343-1349), in place."""
+        assert tangent.dtype == torch.float64 and poses.dtype == torch.float64
+        assert tangent.is_contiguous() and poses.is_contiguous()
+        self._check(L.lib().vetr_apply_tangent(self._ctx, _ptr(tangent), _ptr(poses), poses.shape[0]), "vetr_apply_tangent")
+
+
+def scene_to_device(scene, device):
+    """numpy Scene (vet_b200.scenes) -> CUDA tensors in the order Rasterizer.forward takes them."""
+    t = lambda a: torch.from_numpy(a).to(device)
+    return (t(scene.position), t(scene.index), t(scene.texture), t(scene.confidence), t(scene.background),
+            t(scene.poses), t(scene.intrinsics))
