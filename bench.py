@@ -1,0 +1,387 @@
+#!/usr/bin/env python
+"""Benchmark of the blending point rasterizer: forward + backward frames/s at 1920x1080 with an 8M-point cloud.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--points M] [--views V]
+
+One step = one training batch of V views per GPU: forward (count, scan, collect, sort+blend), L1 gradient against
+a seeded target, backward, gradient epilogue; with N > 1 the point-parameter gradients (descriptor, confidence,
+position + hit count: 9 floats per point) are summed over the ranks with one NCCL all-reduce per step.  Views are
+sharded over the GPUs (weak scaling: V views per GPU and step), the cloud is replicated.
+
+The script prints ONE JSON line (rank 0).  `value` times the steps with inputs resident in HBM; `e2e` times the same
+steps with the per-step inputs (the target pyramid of every view) arriving from pinned host memory and the loss
+read back; `roofline` is the dominant kernel against the measured HBM copy bandwidth; `cpu_baseline` is the CPU
+oracle on the host cores on a bounded sample (one view of the same cloud).  `--impl reference` times that CPU
+oracle alone (the reference ships no CPU rasterizer and its CUDA sources need a library that is not available, so
+the oracle port is the reference arm).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "rasterizer fwd+bwd frames/s @1920x1080, 8M pts"
+UNIT = "frames/s"
+W, H, FOCAL, LAYERS, CHANNELS = 1920, 1080, 1200.0, 4, 4
+HBM_FALLBACK_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--points", type=int, default=8_000_000)
+    ap.add_argument("--views", type=int, default=4, help="views per GPU and step")
+    ap.add_argument("--mode", type=int, default=1, choices=[1, 3])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return HBM_FALLBACK_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def make_scene(n_points: int, n_views_total: int):
+    from vet_b200 import scenes
+
+    return scenes.config_planar(n_points, W, H, FOCAL, n_views=n_views_total, seed=2002, channels=CHANNELS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# -------------------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle on the host cores
+
+
+def cpu_oracle_run(scene, params, steps: int, warmup: int):
+    """Times forward + backward of ONE view per step with the CPU oracle.  Returns (seconds per step, threads)."""
+    from oracle import oracle as O
+
+    o = O.Oracle()
+    p = O.default_params(render_mode=params["render_mode"], num_layers=LAYERS)
+    times = []
+    for it in range(warmup + steps):
+        view = [scene.views[it % len(scene.views)]]
+        t0 = time.perf_counter()
+        fwd = o.forward(scene, p, views=view)
+        t1 = time.perf_counter()
+        rng = np.random.default_rng(it)  # seeded L1 target: input preparation, not timed
+        grads = [(np.sign(c - rng.uniform(0.0, 1.0, size=c.shape).astype(np.float32)) / c.size).astype(np.float32)
+                 for c in fwd["color"]]
+        t2 = time.perf_counter()
+        o.backward(grads)
+        t3 = time.perf_counter()
+        if it >= warmup:
+            times.append((t1 - t0) + (t3 - t2))
+    return float(np.mean(times)), O.threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    scene = make_scene(args.points, max(1, args.steps))
+    from vet_b200.render import default_params
+
+    steps, warmup = max(1, args.steps), min(args.warmup, 1)
+    sec, threads = cpu_oracle_run(scene, default_params(render_mode=args.mode), steps, warmup)
+    value = 1.0 / sec
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"headline: {args.points} planar-scene points, 1 view {W}x{H} f={FOCAL:g}, {LAYERS} levels, "
+                               f"mode {args.mode}, fwd+bwd, L1 vs seeded target", "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": "each step = forward+backward of ONE 1920x1080 view of the full cloud with the CPU "
+                                   "oracle (OpenMP, all host threads)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# -------------------------------------------------------------------------------------------------------------
+# our arm
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from vet_b200.render import Rasterizer, default_params, level_sizes, scene_to_device
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    V = args.views
+    params = default_params(render_mode=args.mode, num_layers=LAYERS, num_channels=CHANNELS)
+
+    # the cloud is replicated; every rank renders its own V views per step (view-sharded batch of world * V views)
+    scene = make_scene(args.points, world * V)
+    my_views = scene.views[rank * V:(rank + 1) * V]
+    tensors = scene_to_device(scene, dev)
+    position, index, texture, confidence, background, poses, intrinsics = tensors
+    n, n_tex = position.shape[0], texture.shape[1]
+    sizes = level_sizes(W, H, LAYERS)
+    P = sum(w * h for w, h in sizes)
+
+    stream = torch.cuda.current_stream(dev)
+    rast = Rasterizer(local_rank, stream=stream)
+
+    # seeded targets of the L1 loss, one pyramid per view: device copies for `value`, pinned host copies for `e2e`
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    targets_host = [torch.rand(V, CHANNELS, h, w, generator=gen).pin_memory() for (w, h) in sizes]
+    targets_dev = [t.to(dev) for t in targets_host]
+    numel = [float(t.numel()) for t in targets_host]
+    h2d_bytes = sum(t.numel() * 4 for t in targets_host)
+
+    # fused gradient buffer: [desc 4n_tex | points 4n | conf n_tex] floats -> one all-reduce
+    flat = torch.zeros(4 * n_tex + 4 * n + n_tex, dtype=torch.float32, device=dev)
+
+    def grad_views():
+        g = dict(desc=flat[:4 * n_tex].view(n_tex, 4), points=flat[4 * n_tex:4 * n_tex + 4 * n].view(n, 4),
+                 conf=flat[4 * n_tex + 4 * n:], background=torch.zeros(CHANNELS, device=dev),
+                 pose=torch.zeros(poses.shape[0], 6, dtype=torch.float64, device=dev),
+                 pose_count=torch.zeros(poses.shape[0], device=dev))
+        return g
+
+    def step(targets):
+        flat.zero_()
+        out = rast.forward(position, index, texture, confidence, background, poses, intrinsics, my_views, params,
+                           want_weight=True)
+        grads, loss = [], None
+        for l, (c, t) in enumerate(zip(out["color"], targets)):
+            d = c - t
+            grads.append(torch.sign(d) / numel[l])
+            term = d.abs().sum() / numel[l]
+            loss = term if loss is None else loss + term
+        g = rast.backward_raw(grads, want_intrinsics=False, accum=grad_views())
+        if world > 1:
+            dist.all_reduce(flat)
+            dist.all_reduce(g["pose"])
+            dist.all_reduce(g["pose_count"])
+        fin = rast.finalize(g)
+        return loss, fin
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- value: inputs resident in HBM
+    for _ in range(args.warmup):
+        step(targets_dev)
+    F_total, longest = rast.fragment_count()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = rast.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        loss, fin = step(targets_dev)
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = rast.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    frames = world * V * args.steps
+    value = frames / (ms_total * 1e-3)
+
+    # ---- e2e: per-step targets arrive from pinned host memory (prefetched on a copy stream), loss read back
+    e2e = None
+    if not args.no_e2e:
+        copy_stream = torch.cuda.Stream(dev)
+        bufs = [[torch.empty_like(t) for t in targets_dev] for _ in range(2)]
+        ready = [torch.cuda.Event() for _ in range(2)]
+        consumed = [torch.cuda.Event() for _ in range(2)]
+        loss_host = torch.zeros(1).pin_memory()
+
+        def prefetch(i):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(consumed[i % 2])
+                for dst, src in zip(bufs[i % 2], targets_host):
+                    dst.copy_(src, non_blocking=True)
+                ready[i % 2].record(copy_stream)
+
+        def e2e_run(k):
+            for ev in consumed:
+                ev.record(stream)
+            prefetch(0)
+            for i in range(k):
+                if i + 1 < k:
+                    prefetch(i + 1)
+                stream.wait_event(ready[i % 2])
+                loss, _ = step(bufs[i % 2])
+                consumed[i % 2].record(stream)
+                loss_host.copy_(loss.reshape(1), non_blocking=False)  # device -> host read of the step's result
+
+        e2e_run(min(2, args.warmup))
+        barrier()
+        t0 = time.perf_counter()
+        e0.record(stream)
+        e2e_run(args.steps)
+        e1.record(stream)
+        barrier()
+        wall = (time.perf_counter() - t0) * 1e3
+        t = torch.tensor([max(e0.elapsed_time(e1), 0.0), wall], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e = {"value": frames / (float(t[0].item()) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
+               "d2h_bytes_per_step": 4, "wall_ms_per_step": float(t[1].item()) / args.steps,
+               "note": "targets of the L1 loss copied from pinned host memory every step (double-buffered on a copy "
+                       "stream), loss scalar read back every step"}
+
+    # ---- per-kernel timing (CUDA events on the launching stream, outside the timed region) and roofline
+    rast.set_timing(True)
+    acc = {}
+    reps = 5
+    for _ in range(reps):
+        step(targets_dev)
+        for k, v in rast.timings().items():
+            acc[k] = acc.get(k, 0.0) + v / reps
+    rast.set_timing(False)
+    touched = int(torch.count_nonzero(fin["points"][:, :3].abs().sum(dim=1)).item()) if fin.get("points") is not None else 0
+    F, N, PT = F_total, n, P * V
+    # algorithmic bytes per launch (one launch = V views); N_t = points with a position gradient
+    kernel_bytes = {
+        "count": 16 * N * V + 4 * PT,                       # positions streamed once per view; counts written
+        "scan": 12 * PT,                                    # counts read twice, offsets written
+        "collect": 16 * N * V + 8 * F,                      # positions again; one 8-byte key per fragment
+        "sort_blend": 16 * F + 20 * F + 4 * PT + (4 * CHANNELS + 4) * PT,   # keys read + written back, descriptor and
+                                                                            # confidence gather, offsets, colour + weight
+        "backward": 8 * F + 20 * F + 16 * F + 4 * PT + 8 * CHANNELS * PT + 2 * 36 * touched,  # keys, gathers (descriptor,
+                                                            # confidence, position), offsets, gradient + forward image,
+                                                            # one read + one write of each touched gradient element
+        "finalize": 32 * n_tex + 32 * N,                    # transpose descriptor gradient, normalise point gradient
+    }
+    peak, peak_src = measured_peak()
+    kernels = {k: {"ms": acc.get(k, 0.0), "bytes": kernel_bytes[k],
+                   "gbs": (kernel_bytes[k] / (acc[k] * 1e-3) / 1e9) if acc.get(k, 0.0) > 0 else None} for k in kernel_bytes}
+    dominant = max(kernels, key=lambda k: kernels[k]["ms"])
+    whole_bytes = sum(kernel_bytes.values()) + 4 * flat.numel()  # + zero fill of the gradient buffer
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": kernels[dominant]["gbs"], "peak": peak, "unit": "GB/s",
+                "frac": (kernels[dominant]["gbs"] or 0.0) / peak, "traffic": TRAFFIC_BYTES_PER_FRAGMENT.get(dominant),
+                "peak_source": peak_src, "kernels": kernels,
+                "whole_step": {"algorithmic_bytes": whole_bytes,
+                               "achieved_gbs": whole_bytes * args.steps / (ms_total * 1e-3) / 1e9,
+                               "frac": whole_bytes * args.steps / (ms_total * 1e-3) / 1e9 / peak},
+                "counts": {"N": N, "N_touched": touched, "F": F, "pixels": PT, "views_per_launch": V,
+                           "longest_list": longest}}
+    if roofline["traffic"] is not None:
+        roofline["traffic"] = roofline["traffic"] * F
+
+    # ---- CPU baseline on the host cores (rank 0, N = 1 only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sec, threads = cpu_oracle_run(scene, params, steps=2, warmup=1)
+        cpu = {"value": 1.0 / sec, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": "2 timed steps after 1 warm-up; each step = forward+backward of ONE 1920x1080 view of the same "
+                         f"{N}-point cloud with the CPU oracle (OpenMP, all host threads)"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"headline: {N} planar-scene points replicated, {V} views {W}x{H} f={FOCAL:g} per GPU and "
+                                   f"step, {LAYERS} levels, mode {args.mode}, fwd+bwd, L1 vs seeded target"
+                                   + (", NCCL all-reduce of 9 floats per point" if world > 1 else ""),
+                       "views_per_gpu": V, "points": N, "l2": "inputs larger than L2 (cloud 128 MB + descriptors 160 MB + "
+                                                              "pyramids; gradient buffer 288 MB rewritten every step)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
+            "loss": float(loss.item()),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes per fragment of each kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum divided by
+# the fragments of the captured launch; see profiles/).  None = not captured yet.
+TRAFFIC_BYTES_PER_FRAGMENT = {}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

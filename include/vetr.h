@@ -188,6 +188,26 @@ int vetr_read_status(vetr_ctx* ctx, const vetr_lists* lists, int64_t* total_frag
 int vetr_get_lists(vetr_ctx* ctx, const vetr_lists* lists, int w, int h, int num_layers, int n_views, int view,
                    int layer, int32_t* out_collections, int32_t* out_scanned_counting, int64_t* n_fragments);
 
+/* Measurement hooks (the reference wraps every pass in a CudaTimerSystem scope, e.g. PointRenderer.cu:770,843,872,886).
+ * With timing enabled every kernel of vetr_forward / vetr_backward / vetr_finalize_gradients is bracketed by CUDA events
+ * on the context's stream.  vetr_get_timings() synchronises and returns the milliseconds of the most recent launch of each
+ * kernel, indexed by VETR_T_*; entries that did not run are 0. */
+enum
+{
+    VETR_T_COUNT = 0,    /* project + count */
+    VETR_T_SCAN,         /* the three scan kernels */
+    VETR_T_COLLECT,      /* project + collect */
+    VETR_T_SORT_BLEND,   /* sort + blend */
+    VETR_T_BACKWARD,     /* backward */
+    VETR_T_FINALIZE,     /* transpose + normalisation kernels */
+    VETR_T_N
+};
+int vetr_set_timing(vetr_ctx* ctx, int enable);
+int vetr_get_timings(vetr_ctx* ctx, float* out_ms /*[VETR_T_N]*/);
+
+/* Number of kernels this context has launched since it was created. */
+int64_t vetr_launch_count(const vetr_ctx* ctx);
+
 #ifdef __cplusplus
 }
 #endif

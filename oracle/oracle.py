@@ -50,6 +50,7 @@ def lib():
         _LIB.vo_forward.restype = C.c_int64
         _LIB.vo_pixels_per_view.restype = C.c_int64
         _LIB.vo_pixels_per_view.argtypes = [C.c_void_p]
+        _LIB.vo_set_abs_mode.argtypes = [C.c_void_p, C.c_int]
     return _LIB
 
 
@@ -131,7 +132,10 @@ class Oracle:
         lib().vo_get_lists(self._h, _ptr(counts), _ptr(keys))
         return counts, keys
 
-    def backward(self, grad_color, want_points=True, want_pose=True, want_intrinsics=True):
+    def backward(self, grad_color, want_points=True, want_pose=True, want_intrinsics=True, magnitudes=False):
+        """Raw gradient sums (fp64).  With `magnitudes`, the sums of |addend| instead: the scale against which the
+        rounding noise of an fp32 accumulation of the same addends has to be judged."""
+        lib().vo_set_abs_mode(self._h, C.c_int(1 if magnitudes else 0))
         scene = self._keep[0]
         Cn, nt, n = scene.channels, scene.texture.shape[1], scene.n
         n_img, n_cam = scene.poses.shape[0], scene.intrinsics.shape[0]
@@ -147,6 +151,7 @@ class Oracle:
                           _ptr(out["background"]), _ptr(out.get("points")), _ptr(out.get("points_count")),
                           _ptr(out.get("pose")), _ptr(out.get("pose_count")), _ptr(out.get("intrinsics")),
                           _ptr(out.get("intrinsics_count")))
+        lib().vo_set_abs_mode(self._h, C.c_int(0))
         return out
 
 

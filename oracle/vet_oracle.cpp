@@ -325,6 +325,7 @@ struct Oracle
     const float* bg       = nullptr;
     const double* poses   = nullptr;
     const float* intr     = nullptr;
+    bool abs_mode         = false;
 };
 
 void setup_levels(Oracle& o, int w, int h)
@@ -584,6 +585,12 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
 {
     Oracle& o          = *(Oracle*)h;
     const OParams& prm = o.prm;
+#define ACC(dst, v)                                                              \
+    do                                                                           \
+    {                                                                            \
+        double v_ = o.abs_mode ? std::fabs((double)(v)) : (double)(v);           \
+        _Pragma("omp atomic") (dst) += v_;                                       \
+    } while (0)
     const int C = o.C, B = o.B;
     const bool bilinear = prm.render_mode == 3;
     const int n_tex     = o.n_tex;
@@ -615,7 +622,9 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
             const float* K   = o.intr + 13 * cam.camera_index;
             float crop2[5];
             for (int k = 0; k < 5; ++k) crop2[k] = cam.crop[k] * level_scale;  // IntrinsicsPinhole::scale
-            // Serial over pixels: the accumulators are shared and this function is the checker, not the timed path.
+            // Rows in parallel; the shared fp64 accumulators are updated atomically (their summation order then
+            // varies from run to run at the 1e-16 level, far below what is compared).
+#pragma omp parallel for schedule(dynamic, 4)
             for (int y = 0; y < lv.h; ++y)
                 for (int x = 0; x < lv.w; ++x)
                 {
@@ -644,7 +653,8 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                         const int cnt0 = cnt;
                         int list_size = prm.use_environment_map ? cnt : cnt + 1;
                         // O(n) form needs the per-entry weights first
-                        std::vector<float> Ti, ai, doti;
+                        static thread_local std::vector<float> Ti, ai, doti;
+                        Ti.clear(), ai.clear(), doti.clear();
                         int processed = 0;
                         for (int i = 0; i < list_size; ++i)
                         {
@@ -658,18 +668,18 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                             {
                                 float g_col = T * a * gin[ci];
                                 if (fg)
-                                    g_texture[(int64_t)ci * n_tex + tex] += (double)g_col;
+                                    ACC(g_texture[(int64_t)ci * n_tex + tex], g_col);
                                 else
-                                    g_background[ci] += (double)g_col;
+                                    ACC(g_background[ci], g_col);
                                 g_alpha += col[ci] * gin[ci];
                             }
                             g_alpha *= T;
                             if (!bilinear)
                             {
-                                if (fg || prm.background_alpha_to_point0) g_confidence[tex] += (double)g_alpha;
+                                if (fg || prm.background_alpha_to_point0) ACC(g_confidence[tex], g_alpha);
                             }
                             else if (fg)
-                                galpha[s + i] += g_alpha;
+                                galpha[s + i] += o.abs_mode ? std::fabs(g_alpha) : g_alpha;
 
                             if (prm.conf_grad_quadratic)
                             {
@@ -680,9 +690,9 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                                     for (int ci = 0; ci < C; ++ci)
                                         g_iter -= (gin[ci] * col[ci] * T * a / (1 - aj + 1e-9f));
                                     if (!bilinear)
-                                        g_confidence[o.index[(int)(uint32_t)o.keys[s + j]]] += (double)g_iter;
+                                        ACC(g_confidence[o.index[(int)(uint32_t)o.keys[s + j]]], g_iter);
                                     else
-                                        galpha[s + j] += g_iter;
+                                        galpha[s + j] += o.abs_mode ? std::fabs(g_iter) : g_iter;
                                 }
                             }
                             else
@@ -709,11 +719,11 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                                 {
                                     double sub = -S / (double)(1 - ai[j] + 1e-9f);
                                     if (!bilinear)
-                                        g_confidence[o.index[(int)(uint32_t)o.keys[s + j]]] += sub;
+                                        ACC(g_confidence[o.index[(int)(uint32_t)o.keys[s + j]]], sub);
                                     else
-                                        galpha[s + j] += (float)sub;
+                                        galpha[s + j] += (float)(o.abs_mode ? std::fabs(sub) : sub);
                                 }
-                                S += (double)(Ti[j] * ai[j] * doti[j]);
+                                S += o.abs_mode ? std::fabs((double)(Ti[j] * ai[j] * doti[j])) : (double)(Ti[j] * ai[j] * doti[j]);
                             }
                         }
                     }
@@ -749,7 +759,7 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                             blending_fac({o.uv[2 * (s + i)], o.uv[2 * (s + i) + 1]}, w4, J);
                             int bi        = o.corner[s + i];
                             float ga      = galpha[s + i];
-                            g_confidence[tex] += (double)(w4[bi] * ga);  // RenderBackward.cu:3076-3079
+                            ACC(g_confidence[tex], w4[bi] * ga);  // RenderBackward.cu:3076-3079
                             if (!prm.need_point_gradient) continue;
                             float single = o.conf[tex] * ga;
                             dR = {J[2 * bi] * single, J[2 * bi + 1] * single};
@@ -758,30 +768,36 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                         if (!project_backward(o.position + 4 * pid, dR, V, K, crop2, cam.rot, prm.dist_cutoff, bo)) continue;
                         if (g_points)
                         {
-                            for (int k = 0; k < 3; ++k) g_points[3 * (int64_t)pid + k] += (double)bo.g_point[k];
-                            g_points_count[pid] += 1.0;
+                            for (int k = 0; k < 3; ++k) ACC(g_points[3 * (int64_t)pid + k], bo.g_point[k]);
+                            _Pragma("omp atomic") g_points_count[pid] += 1.0;
                         }
                         if (g_pose)
                         {
-                            for (int k = 0; k < 6; ++k) g_pose[6 * cam.image_index + k] += (double)bo.g_pose[k];
-                            g_pose_count[cam.image_index] += bilinear ? 1.0 : (double)(1.f / 1024.f);
+                            for (int k = 0; k < 6; ++k) ACC(g_pose[6 * cam.image_index + k], bo.g_pose[k]);
+                            _Pragma("omp atomic") g_pose_count[cam.image_index] += bilinear ? 1.0 : (double)(1.f / 1024.f);
                         }
                         if (g_intr)
                         {
                             bo.g_k[4] *= 0;
-                            for (int k = 0; k < 5; ++k) g_intr[13 * cam.camera_index + k] += (double)(prm.K_gradient_factor * bo.g_k[k]);
+                            for (int k = 0; k < 5; ++k) ACC(g_intr[13 * cam.camera_index + k], prm.K_gradient_factor * bo.g_k[k]);
                             bo.g_dis[2] *= 0.25f;
                             for (int k = 3; k < 8; ++k) bo.g_dis[k] *= 0.1f;
                             for (int k = 0; k < 8; ++k)
-                                g_intr[13 * cam.camera_index + 5 + k] += (double)(prm.distortion_gradient_factor * bo.g_dis[k]);
-                            g_intr_count[cam.camera_index] += (double)(1.f / 1024.f);
+                                ACC(g_intr[13 * cam.camera_index + 5 + k], prm.distortion_gradient_factor * bo.g_dis[k]);
+                            _Pragma("omp atomic") g_intr_count[cam.camera_index] += (double)(1.f / 1024.f);
                         }
                     }
                 }
         }
     }
+#undef ACC
     return 0;
 }
+
+// Magnitude shadow: with `on`, vo_backward accumulates |addend| instead of addend into every gradient sum (counts
+// are unchanged).  The result bounds the rounding noise an fp32 sum of the same addends can carry in any order.
+void vo_set_abs_mode(void* h, int on) { ((Oracle*)h)->abs_mode = on != 0; }
+
 
 // ApplyTangent, PointRenderer.cu:1325-1341: pose <- exp_se3(tangent) * pose, tangent <- 0, in double.
 // Tangent = (translation part, rotation part) as Sophus::SE3d::exp consumes it.

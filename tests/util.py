@@ -24,6 +24,7 @@ def run_oracle(scene, params: dict, grads=None, dropout=None, quadratic=False):
     out = dict(fwd=fwd, counts=counts, keys=keys, F=fwd["F"])
     if grads is not None:
         out["bwd"] = o.backward(grads)
+        out["bwd_mag"] = o.backward(grads, magnitudes=True)
     return out
 
 
@@ -98,17 +99,35 @@ def compare_forward(gpu, ora, exact_images=True):
                 assert_close(f"{name}[{l}]", a, b, rtol=1e-5, floor_rel=1e-6)
 
 
-def compare_backward(gpu_raw, ora_bwd, channels, rtol=1e-5, floor_rel=1e-5):
-    """Raw gradient sums; the oracle sums in fp64, the GPU with fp32 atomics in arbitrary order."""
-    assert_close("g_texture", gpu_raw["desc"][:, :channels].T, ora_bwd["texture"], rtol, floor_rel)
-    assert_close("g_confidence", gpu_raw["conf"], ora_bwd["confidence"], rtol, floor_rel)
-    assert_close("g_background", gpu_raw["background"], ora_bwd["background"], rtol, floor_rel)
-    if "points" in gpu_raw and "points" in ora_bwd:
-        np.testing.assert_array_equal(gpu_raw["points"][:, 3], ora_bwd["points_count"])
-        assert_close("g_points", gpu_raw["points"][:, :3], ora_bwd["points"], rtol, floor_rel)
-    if "pose" in gpu_raw and "pose" in ora_bwd:
-        assert_close("g_pose", gpu_raw["pose"], ora_bwd["pose"], rtol, floor_rel)
-        assert_close("g_pose_count", gpu_raw["pose_count"], ora_bwd["pose_count"], 1e-5, 1e-5)
-    if "intrinsics" in gpu_raw and "intrinsics" in ora_bwd:
-        assert_close("g_intrinsics", gpu_raw["intrinsics"], ora_bwd["intrinsics"], rtol, floor_rel)
-        assert_close("g_intrinsics_count", gpu_raw["intrinsics_count"], ora_bwd["intrinsics_count"], 1e-5, 1e-5)
+def assert_sum_close(name, got, want, magnitude, rtol=1e-5):
+    """For sums of many fp32 addends: |got - want| <= rtol * sum|addends| (+ one ulp-scale term of the value).
+    `magnitude` is the oracle's sum of |addend| for the same element."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    magnitude = np.asarray(magnitude, np.float64)
+    assert got.shape == want.shape == magnitude.shape, (name, got.shape, want.shape, magnitude.shape)
+    bound = rtol * np.maximum(magnitude, np.abs(want)) + 1e-30
+    err = np.abs(got - want)
+    bad = ~(err <= bound)
+    if bad.any():
+        i = np.unravel_index(np.argmax(np.where(bad, err / bound, 0)), err.shape)
+        raise AssertionError(f"{name}: {bad.sum()} of {bad.size} elements differ; worst at {i}: got {got[i]!r} "
+                             f"want {want[i]!r} (err {err[i]:.3e}, bound {bound[i]:.3e}, sum|addends| {magnitude[i]:.3e})")
+
+
+def compare_backward(gpu_raw, ora, channels, rtol=1e-5):
+    """Raw gradient sums.  The oracle sums in fp64; the GPU adds the same fp32 addends with atomics in an undefined
+    order, so each element is held to rtol x (sum of |addends| of that element)."""
+    b, m = ora["bwd"], ora["bwd_mag"]
+    assert_sum_close("g_texture", gpu_raw["desc"][:, :channels].T, b["texture"], m["texture"], rtol)
+    assert_sum_close("g_confidence", gpu_raw["conf"], b["confidence"], m["confidence"], rtol)
+    assert_sum_close("g_background", gpu_raw["background"], b["background"], m["background"], rtol)
+    if "points" in gpu_raw and "points" in b:
+        np.testing.assert_array_equal(gpu_raw["points"][:, 3], b["points_count"])
+        assert_sum_close("g_points", gpu_raw["points"][:, :3], b["points"], m["points"], rtol)
+    if "pose" in gpu_raw and "pose" in b:
+        assert_sum_close("g_pose", gpu_raw["pose"], b["pose"], m["pose"], rtol)
+        assert_sum_close("g_pose_count", gpu_raw["pose_count"], b["pose_count"], m["pose_count"], rtol)
+    if "intrinsics" in gpu_raw and "intrinsics" in b:
+        assert_sum_close("g_intrinsics", gpu_raw["intrinsics"], b["intrinsics"], m["intrinsics"], rtol)
+        assert_sum_close("g_intrinsics_count", gpu_raw["intrinsics_count"], b["intrinsics_count"], m["intrinsics_count"], rtol)

@@ -52,8 +52,10 @@ class Lists(C.Structure):
 EXPORTS = [
     "vetr_create", "vetr_destroy", "vetr_set_stream", "vetr_strerror", "vetr_last_cuda_error", "vetr_pyramid_pixels",
     "vetr_item_table_entries", "vetr_max_fragments", "vetr_forward", "vetr_backward", "vetr_finalize_gradients",
-    "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists",
+    "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists", "vetr_set_timing", "vetr_get_timings",
+    "vetr_launch_count",
 ]
+TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize"]
 
 _lib = None
 
@@ -96,5 +98,9 @@ def lib():
         L.vetr_read_status.argtypes = [vp, C.POINTER(Lists), C.POINTER(C.c_int64), C.POINTER(C.c_int32)]
         L.vetr_get_lists.argtypes = [vp, C.POINTER(Lists), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp,
                                      C.POINTER(C.c_int64)]
+        L.vetr_set_timing.argtypes = [vp, C.c_int]
+        L.vetr_get_timings.argtypes = [vp, C.POINTER(C.c_float)]
+        L.vetr_launch_count.argtypes = [vp]
+        L.vetr_launch_count.restype = C.c_int64
         _lib = L
     return _lib

@@ -1220,6 +1220,30 @@ struct vetr_ctx
     long long* tile_sums = nullptr;  // scan scratch
     long long tile_cap   = 0;
     int blend_ctas_per_sm = 1, back_ctas_per_sm = 1;
+    long long launches   = 0;
+    bool timing          = false;
+    cudaEvent_t ev[VETR_T_N][2] = {};
+    bool ev_used[VETR_T_N]      = {};
+};
+
+// Brackets the launches of one pass with events when timing is on, and counts kernels.
+struct PassScope
+{
+    vetr_ctx* c;
+    int id;
+    PassScope(vetr_ctx* ctx, int pass, int kernels) : c(ctx), id(pass)
+    {
+        c->launches += kernels;
+        if (c->timing) cudaEventRecord(c->ev[id][0], c->stream);
+    }
+    ~PassScope()
+    {
+        if (c->timing)
+        {
+            cudaEventRecord(c->ev[id][1], c->stream);
+            c->ev_used[id] = true;
+        }
+    }
 };
 
 #define VETR_CUDA(ctx, call)                      \
@@ -1334,8 +1358,38 @@ extern "C" void vetr_destroy(vetr_ctx* ctx)
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->tile_sums) cudaFree(ctx->tile_sums);
+    for (int i = 0; i < VETR_T_N; ++i)
+        for (int k = 0; k < 2; ++k)
+            if (ctx->ev[i][k]) cudaEventDestroy(ctx->ev[i][k]);
     delete ctx;
 }
+
+extern "C" int vetr_set_timing(vetr_ctx* ctx, int enable)
+{
+    if (!ctx) return VETR_E_INVALID_ARG;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (enable && !ctx->ev[0][0])
+        for (int i = 0; i < VETR_T_N; ++i)
+            for (int k = 0; k < 2; ++k) VETR_CUDA(ctx, cudaEventCreate(&ctx->ev[i][k]));
+    ctx->timing = enable != 0;
+    for (int i = 0; i < VETR_T_N; ++i) ctx->ev_used[i] = false;
+    return VETR_OK;
+}
+
+extern "C" int vetr_get_timings(vetr_ctx* ctx, float* out_ms)
+{
+    if (!ctx || !out_ms) return VETR_E_INVALID_ARG;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    VETR_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int i = 0; i < VETR_T_N; ++i)
+    {
+        out_ms[i] = 0.f;
+        if (ctx->ev_used[i]) VETR_CUDA(ctx, cudaEventElapsedTime(&out_ms[i], ctx->ev[i][0], ctx->ev[i][1]));
+    }
+    return VETR_OK;
+}
+
+extern "C" int64_t vetr_launch_count(const vetr_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
 extern "C" int vetr_set_stream(vetr_ctx* ctx, void* cuda_stream)
 {
@@ -1380,6 +1434,7 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     f.dist_grad_factor = p->distortion_gradient_factor, f.mask_value = p->output_background_mask_value;
     f.P  = pyramid(f.w, f.h, f.L, f.lw, f.lh, f.lbase);
     f.PT = f.P * n_views;
+    if (f.lw[f.L - 1] < 1 || f.lh[f.L - 1] < 1) return VETR_E_INVALID_ARG;  // the reference asserts w > 0 && h > 0 per level
     if (f.PT > 0x7fffffffLL) return VETR_E_TOO_LARGE;
     f.position = (const float4*)cloud->position, f.index = cloud->index;
     f.texture = tex->texture, f.confidence = tex->confidence, f.background = tex->background;
@@ -1420,14 +1475,28 @@ extern "C" int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr
     VETR_CUDA(ctx, cudaMemsetAsync(f.counts, 0, f.PT * sizeof(int), st));
     VETR_CUDA(ctx, cudaMemsetAsync(f.status, 0, 4 * sizeof(int), st));
     const int point_ctas = (f.n + kThreads * kPointsPerThread - 1) / (kThreads * kPointsPerThread);
-    if (point_ctas > 0) project_kernel<false><<<dim3(point_ctas, n_views), kThreads, 0, st>>>(f);
+    if (point_ctas > 0)
+    {
+        PassScope t(ctx, VETR_T_COUNT, 1);
+        project_kernel<false><<<dim3(point_ctas, n_views), kThreads, 0, st>>>(f);
+    }
     const int n_tiles = (int)((f.PT + kScanTile - 1) / kScanTile);
-    scan_tile_sums_kernel<<<n_tiles, 256, 0, st>>>(f.counts, f.PT, ctx->tile_sums, f.status);
-    scan_spine_kernel<<<1, 1024, 0, st>>>(ctx->tile_sums, n_tiles, f.PT, f.capacity, f.status, f.item_start);
-    scan_apply_kernel<<<n_tiles, 256, 0, st>>>(f.counts, f.PT, ctx->tile_sums, f.ends, f.status, f.item_start);
-    if (point_ctas > 0) project_kernel<true><<<dim3(point_ctas, n_views), kThreads, 0, st>>>(f);
-    const int grid = ctx->sm_count * ctx->blend_ctas_per_sm;
-    sort_blend_kernel<<<grid, kThreads, sizeof(BlendSmem), st>>>(f, out);
+    {
+        PassScope t(ctx, VETR_T_SCAN, 3);
+        scan_tile_sums_kernel<<<n_tiles, 256, 0, st>>>(f.counts, f.PT, ctx->tile_sums, f.status);
+        scan_spine_kernel<<<1, 1024, 0, st>>>(ctx->tile_sums, n_tiles, f.PT, f.capacity, f.status, f.item_start);
+        scan_apply_kernel<<<n_tiles, 256, 0, st>>>(f.counts, f.PT, ctx->tile_sums, f.ends, f.status, f.item_start);
+    }
+    if (point_ctas > 0)
+    {
+        PassScope t(ctx, VETR_T_COLLECT, 1);
+        project_kernel<true><<<dim3(point_ctas, n_views), kThreads, 0, st>>>(f);
+    }
+    {
+        PassScope t(ctx, VETR_T_SORT_BLEND, 1);
+        const int grid = ctx->sm_count * ctx->blend_ctas_per_sm;
+        sort_blend_kernel<<<grid, kThreads, sizeof(BlendSmem), st>>>(f, out);
+    }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }
@@ -1455,8 +1524,11 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
     bp.g_desc = (float4*)g_desc, bp.g_conf = g_conf, bp.g_points = (float4*)g_points, bp.g_background = g_background;
     bp.g_pose = g_pose, bp.g_pose_count = g_pose_count, bp.g_intr = g_intr, bp.g_intr_count = g_intr_count;
     if (!f.need_point_grad && f.mode != VETR_MODE_BILINEAR_BLEND) bp.g_points = nullptr;
-    const int grid = ctx->sm_count * ctx->back_ctas_per_sm;
-    backward_kernel<<<grid, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
+    {
+        PassScope t(ctx, VETR_T_BACKWARD, 1);
+        const int grid = ctx->sm_count * ctx->back_ctas_per_sm;
+        backward_kernel<<<grid, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
+    }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }
@@ -1468,6 +1540,9 @@ extern "C" int vetr_finalize_gradients(vetr_ctx* ctx, int channels, int n_tex, c
     if (!ctx) return VETR_E_INVALID_ARG;
     VETR_CUDA(ctx, cudaSetDevice(ctx->device));
     cudaStream_t st = ctx->stream;
+    const int n_kernels = (g_desc && g_texture && n_tex > 0) + (g_points && n > 0) + (g_pose && g_pose_count && n_img > 0) +
+                          (g_intr && g_intr_count && n_cam > 0);
+    PassScope t(ctx, VETR_T_FINALIZE, n_kernels);
     if (g_desc && g_texture && n_tex > 0)
     {
         if (channels != 3 && channels != 4) return VETR_E_INVALID_ARG;
@@ -1486,7 +1561,11 @@ extern "C" int vetr_apply_tangent(vetr_ctx* ctx, double* tangent, double* poses_
 {
     if (!ctx || !tangent || !poses_se3 || n < 0) return VETR_E_INVALID_ARG;
     VETR_CUDA(ctx, cudaSetDevice(ctx->device));
-    if (n > 0) apply_tangent_kernel<<<(n + 127) / 128, 128, 0, ctx->stream>>>(tangent, poses_se3, n);
+    if (n > 0)
+    {
+        ctx->launches += 1;
+        apply_tangent_kernel<<<(n + 127) / 128, 128, 0, ctx->stream>>>(tangent, poses_se3, n);
+    }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }

@@ -102,10 +102,10 @@ class Rasterizer:
                             (C.c_float * 4)(*v.rot))
         return arr
 
-    def _lists(self, slot: int, n_pixels_total: int, capacity: int) -> FragmentLists:
+    def _lists(self, slot: int, n_pixels_total: int, capacity: int, exact: bool = False) -> FragmentLists:
         key = (slot, n_pixels_total)
         cur = self._lists_cache.get(key)
-        if cur is None or cur.capacity < capacity:
+        if cur is None or cur.capacity < capacity or (exact and cur.capacity != capacity):
             cur = FragmentLists(self.device, n_pixels_total, capacity)
             self._lists_cache[key] = cur
         return cur
@@ -134,7 +134,7 @@ class Rasterizer:
             b1 = min(B, b0 + L.MAX_VIEWS)
             nb = b1 - b0
             cap = capacity if capacity is not None else int(lib.vetr_max_fragments(position.shape[0], nb, C.byref(prm)))
-            lists = self._lists(gi, P * nb, cap)
+            lists = self._lists(gi, P * nb, cap, exact=capacity is not None)
             varr = self._views(views[b0:b1])
             sl = lambda ts: None if ts is None else [t[b0:b1] for t in ts]
             dro = None if dropout is None else dropout[b0:b1]
@@ -222,6 +222,18 @@ class Rasterizer:
         self._check(rc, "vetr_finalize_gradients")
         return dict(texture=g_texture, confidence=g["conf"].view(1, -1), background=g["background"], points=pts,
                     pose=pose, intrinsics=intr)
+
+    def set_timing(self, enable: bool):
+        self._check(L.lib().vetr_set_timing(self._ctx, int(enable)), "vetr_set_timing")
+
+    def timings(self) -> dict:
+        """Milliseconds of the most recent launch of every pass (timing must be enabled); synchronises."""
+        ms = (C.c_float * len(L.TIMING_NAMES))()
+        self._check(L.lib().vetr_get_timings(self._ctx, ms), "vetr_get_timings")
+        return {k: float(ms[i]) for i, k in enumerate(L.TIMING_NAMES)}
+
+    def launch_count(self) -> int:
+        return int(L.lib().vetr_launch_count(self._ctx))
 
     def apply_tangent(self, tangent: torch.Tensor, poses: torch.Tensor):
         """ApplyTangentToPose (PointRenderer.cu:1343-1349), in place."""
