@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--mode", type=int, default=1, choices=[1, 3])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--prewarm", type=float, default=1.0, help="seconds of untimed load before the warm-up steps")
     return ap.parse_args()
 
 
@@ -75,27 +76,44 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.proc = None
         self.gpu_index = gpu_index
+        self.lines = []  # (arrival time, csv line)
+        self.thread = None
 
     def start(self):
+        """Starts sampling (every 50 ms) and waits for the first sample, so that short timed regions are covered."""
+        import threading
+
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                          "-lms", "50", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
+            return
 
-    def stop(self) -> dict:
+        def reader():
+            for line in self.proc.stdout:
+                self.lines.append((time.perf_counter(), line))
+
+        self.thread = threading.Thread(target=reader, daemon=True)
+        self.thread.start()
+        t0 = time.perf_counter()
+        while not self.lines and time.perf_counter() - t0 < 5.0:
+            time.sleep(0.01)
+
+    def stop(self, t_begin: float, t_end: float) -> dict:
+        """Summary of the samples that arrived while the timed region [t_begin, t_end] ran (all samples if none did)."""
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        time.sleep(0.06)
         self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except Exception:
-            self.proc.kill()
-            out = ""
+        if self.thread is not None:
+            self.thread.join(timeout=5)
+        inside = [l for (t, l) in self.lines if t_begin <= t <= t_end + 0.06]
+        lines = inside if inside else [l for (_, l) in self.lines]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
+        for line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
@@ -108,7 +126,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "samples_in_timed_region": len(inside)}
 
 
 # -------------------------------------------------------------------------------------------------------------
@@ -236,24 +254,31 @@ def run_ours(args):
         torch.cuda.synchronize(dev)
 
     # ---- value: inputs resident in HBM
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # bring the clocks up before the counted warm-up steps (a cold GPU needs a few hundred ms of load to boost)
+    t_pre = time.perf_counter()
+    while time.perf_counter() - t_pre < args.prewarm:
+        step(targets_dev)
+        torch.cuda.synchronize(dev)
     for _ in range(args.warmup):
         step(targets_dev)
     F_total, longest = rast.fragment_count()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     launches0 = rast.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_begin = time.perf_counter()
     e0.record(stream)
     for _ in range(args.steps):
         loss, fin = step(targets_dev)
     e1.record(stream)
     barrier()
+    t_end = time.perf_counter()
     ms = e0.elapsed_time(e1)
     launches = rast.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -5,7 +5,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libvetr.so")
+LIB_PATH = os.environ.get("VETR_LIB", os.path.join(_HERE, "libvetr.so"))  # VETR_LIB: a tuning variant of the library
 
 MAX_LAYERS = 5
 MAX_VIEWS = 8

@@ -1,7 +1,9 @@
 """Builds libvetr.so (the CUDA kernels + C ABI) in-tree with nvcc for sm_100a.
 
-nvcc cross-compiles without a GPU.  -fmad=false keeps every fp32 product and sum separately rounded, which the
-bit-exact fragment order depends on (see csrc/vetr_math.cuh).
+nvcc cross-compiles without a GPU.  The arithmetic that the bit-exact fragment order depends on is written with
+non-contracting intrinsics (see csrc/vetr_math.cuh); -fmad=false additionally keeps the per-fragment gradient
+arithmetic in the same rounding order as the CPU oracle, so that parity tests only have to allow for the order in
+which fp32 atomics sum.
 """
 from __future__ import annotations
 
@@ -25,11 +27,12 @@ def needs_build() -> bool:
     return any(os.path.getmtime(p) > t for p in SOURCES + HEADERS)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if force or needs_build():
-        cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + SOURCES
+def build(force: bool = False, verbose: bool = False, defines=(), out: str = LIB_PATH) -> str:
+    """`defines` (e.g. ["VETR_ITEM_THREADS=256"]) and `out` build tuning variants next to the default library."""
+    if force or out != LIB_PATH or needs_build():
+        cmd = [NVCC] + FLAGS + [f"-D{d}" for d in defines] + (["-Xptxas", "-v"] if verbose else []) + ["-o", out] + SOURCES
         subprocess.check_call(cmd)
-    return LIB_PATH
+    return out
 
 
 if __name__ == "__main__":

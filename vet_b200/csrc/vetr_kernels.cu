@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <new>
@@ -32,13 +33,29 @@
 
 namespace vetr
 {
-constexpr int kThreads    = 256;   // CTA size of the item kernels
-constexpr int kQuantum    = 1024;  // units of work per item
+#ifndef VETR_ITEM_THREADS
+#    define VETR_ITEM_THREADS 128
+#endif
+#ifndef VETR_QUANTUM
+#    define VETR_QUANTUM 512
+#endif
+#ifndef VETR_LONG_LIST
+#    define VETR_LONG_LIST 1024
+#endif
+#ifndef VETR_MIN_CTAS
+#    define VETR_MIN_CTAS 5
+#endif
+constexpr int kThreads    = VETR_ITEM_THREADS;  // CTA size of the item kernels
+constexpr int kQuantum    = VETR_QUANTUM;       // units of work per item
 constexpr int kPixelWork  = 4;     // work units charged per pixel -> at most kQuantum / kPixelWork pixels per item
 constexpr int kMaxPixels  = kQuantum / kPixelWork;
-constexpr int kLongList   = kQuantum;      // lists longer than this take the slow path
-constexpr int kCap        = 2 * kQuantum;  // fragments staged per item (bound: kQuantum + kLongList)
+constexpr int kLongList   = VETR_LONG_LIST;         // lists longer than this take the slow path
+constexpr int kCap        = kQuantum + kLongList;   // fragments staged per item (an item holds < kQuantum + its first list)
+constexpr int kMinCtas    = VETR_MIN_CTAS;          // resident CTAs per SM the item kernels are compiled for
+constexpr int kProjThreads     = 256;
 constexpr int kPointsPerThread = 4;
+static_assert(kMaxPixels <= kThreads, "one thread per pixel of an item");
+static_assert(kMaxPixels <= 256, "seg_of is a byte");
 constexpr int kScanTile   = 4096;  // elements per CTA in the scan (256 threads x 16)
 constexpr float kMaxDepth = 100000.f;  // MAX_DEPTH_CONST, RenderConstants.h:30
 
@@ -98,29 +115,8 @@ __device__ __forceinline__ Camera load_camera(const Frame& f, int b)
     for (int i = 0; i < 4; ++i) c.rot[i] = v.rot[i];
     c.cx = (float)(f.w / 2);
     c.cy = (float)(f.h / 2);
+    rotation_matrix(c.V, c.R);
     return c;
-}
-
-// Decodes a pixel of the global pixel space.
-struct PixelRef
-{
-    int view, level, x, y, w, h;
-};
-__device__ __forceinline__ PixelRef decode_pixel(const Frame& f, long long g)
-{
-    PixelRef r;
-    r.view      = (int)(g / f.P);
-    long long q = g - (long long)r.view * f.P;
-    int l       = 0;
-#pragma unroll
-    for (int i = 1; i < VETR_MAX_LAYERS; ++i)
-        if (i < f.L && q >= f.lbase[i]) l = i;
-    q -= f.lbase[l];
-    r.level = l;
-    r.w = f.lw[l], r.h = f.lh[l];
-    r.y = (int)(q / r.w);
-    r.x = (int)(q - (long long)r.y * r.w);
-    return r;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -128,71 +124,73 @@ __device__ __forceinline__ PixelRef decode_pixel(const Frame& f, long long g)
 // the level loop together so that equal pixels inside a warp can be merged into one atomic.
 
 template <bool kCollect>
-__global__ void __launch_bounds__(kThreads) project_kernel(const __grid_constant__ Frame f)
+__global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_constant__ Frame f)
 {
-    const int b      = blockIdx.y;
-    const Camera cam = load_camera(f, b);
-    const unsigned lane = threadIdx.x & 31;
-    const long long vbase = (long long)b * f.P;
-    const bool bilinear   = f.mode == VETR_MODE_BILINEAR_BLEND;
-    const int base_point  = blockIdx.x * (kThreads * kPointsPerThread) + threadIdx.x;
+    __shared__ Camera s_cam;
+    const int b = blockIdx.y;
+    if (threadIdx.x == 0) s_cam = load_camera(f, b);
+    __syncthreads();
+    const Camera& cam   = s_cam;
+    const int vbase     = b * (int)f.P;
+    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+    const int first     = blockIdx.x * (kProjThreads * kPointsPerThread) + threadIdx.x;
 
-#pragma unroll 1
+    float4 pos[kPointsPerThread];
+#pragma unroll
     for (int it = 0; it < kPointsPerThread; ++it)
     {
-        const int pid = base_point + it * kThreads;
-        bool alive    = pid < f.n;
-        float2 ip     = make_float2(0.f, 0.f);
-        float radius  = 0.f;
-        unsigned zb   = 0;
-        if (alive && f.dropout) alive = f.dropout[(long long)b * f.n + pid] != 1.f;
-        if (alive && f.viewer_only) alive = !(f.confidence[f.index[pid]] < f.stability_cutoff);
-        if (alive)
-        {
-            float4 pos   = __ldg(f.position + pid);
-            Projected pr = project_point(pos, cam, f.dist_cutoff);
-            alive        = pr.z != 0.f;  // also false for NaN-free zero; NaN z cannot occur (fmaxf)
-            ip           = pr.ip;
-            radius       = pr.radius_px;
-            zb           = __float_as_uint(pr.z);
-        }
-        if (!__any_sync(0xffffffffu, alive)) continue;
-
+        const int pid = first + it * kProjThreads;
+        pos[it]       = pid < f.n ? __ldg(f.position + pid) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int it = 0; it < kPointsPerThread; ++it)
+    {
+        const int pid = first + it * kProjThreads;
+        if (pid >= f.n) break;
+        if (f.dropout && f.dropout[(size_t)b * f.n + pid] == 1.f) continue;
+        if (f.viewer_only && f.confidence[f.index[pid]] < f.stability_cutoff) continue;
+        const Projected pr = project_point(pos[it], cam, f.dist_cutoff);
+        if (pr.z == 0.f) continue;
+        float2 ip     = pr.ip;
+        float radius  = pr.radius_px;
+        const unsigned long long key = ((unsigned long long)__float_as_uint(pr.z) << 32) | (unsigned)pid;
 #pragma unroll 1
         for (int l = 0; l < f.L; ++l, radius *= 0.5f, ip.x *= 0.5f, ip.y *= 0.5f)
         {
-            if (alive && f.drop_by_radius && radius < f.radius_threshold) alive = false;  // `break` of the reference
-            if (!__any_sync(0xffffffffu, alive)) break;
+            if (f.drop_by_radius && radius < f.radius_threshold) break;
             const int lw = f.lw[l], lh = f.lh[l];
-            const int ncorner = bilinear ? 4 : 1;
-            int bx, by;
-            if (bilinear)
-                bx = round_down(ip.x), by = round_down(ip.y);
-            else
-                bx = round_half_even(ip.x), by = round_half_even(ip.y);
-#pragma unroll 1
-            for (int cidx = 0; cidx < ncorner; ++cidx)
+            const int gbase = vbase + (int)f.lbase[l];
+            if (!bilinear)
             {
-                long long x = (long long)bx + (cidx & 1), y = (long long)by + (cidx >> 1);
-                bool valid  = alive && x >= 0 && y >= 0 && x < lw && y < lh;
-                // lanes without a fragment get a key no other lane can have
-                long long g = valid ? vbase + f.lbase[l] + y * lw + x : -1 - (long long)lane;
-                unsigned peers = __match_any_sync(0xffffffffu, g);
-                if (!valid) continue;
-                int leader = __ffs(peers) - 1;
-                int npeers = __popc(peers);
+                const int x = round_half_even(ip.x), y = round_half_even(ip.y);
+                if ((unsigned)x >= (unsigned)lw || (unsigned)y >= (unsigned)lh) continue;
+                const int g = gbase + y * lw + x;
                 if (!kCollect)
-                {
-                    if (lane == (unsigned)leader) atomicAdd(f.counts + g, npeers);
-                }
+                    atomicAdd(f.counts + g, 1);
                 else
                 {
-                    int slot0 = 0;
-                    if (lane == (unsigned)leader) slot0 = atomicAdd(f.ends + g, npeers);
-                    slot0     = __shfl_sync(peers, slot0, leader);
-                    int slot  = slot0 + __popc(peers & ((1u << lane) - 1));
-                    if ((unsigned long long)slot < (unsigned long long)f.capacity)
-                        f.keys[slot] = ((unsigned long long)zb << 32) | (unsigned)pid;
+                    const int slot = atomicAdd(f.ends + g, 1);
+                    if ((unsigned long long)slot < (unsigned long long)f.capacity) f.keys[slot] = key;
+                }
+            }
+            else
+            {
+                const int bx = round_down(ip.x), by = round_down(ip.y);
+#pragma unroll
+                for (int cidx = 0; cidx < 4; ++cidx)
+                {
+                    // bx, by may be INT32_MIN (unrepresentable position): the unsigned tests reject it before any use
+                    const int x = bx + (cidx & 1), y = by + (cidx >> 1);
+                    if (bx == INT32_MIN || by == INT32_MIN) continue;
+                    if ((unsigned)x >= (unsigned)lw || (unsigned)y >= (unsigned)lh) continue;
+                    const int g = gbase + y * lw + x;
+                    if (!kCollect)
+                        atomicAdd(f.counts + g, 1);
+                    else
+                    {
+                        const int slot = atomicAdd(f.ends + g, 1);
+                        if ((unsigned long long)slot < (unsigned long long)f.capacity) f.keys[slot] = key;
+                    }
                 }
             }
         }
@@ -335,15 +333,33 @@ __global__ void __launch_bounds__(256) scan_apply_kernel(const int* __restrict__
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Shared pieces of the two item kernels.
+// Shared pieces of the item kernels.
 
-struct ItemRange
+struct PixInfo  // decoded pixel of the global pixel space, 8 bytes
 {
-    int lo, hi;           // pixels [lo, hi)
-    long long f0, f1;     // fragments [f0, f1)
+    short x, y;
+    unsigned char level, view;
+    unsigned short pad;
 };
 
-__device__ __forceinline__ long long list_end(const Frame& f, long long g) { return g < 0 ? 0 : (long long)f.ends[g]; }
+__device__ __forceinline__ PixInfo decode_pixel(const Frame& f, unsigned g)
+{
+    PixInfo r;
+    const unsigned P = (unsigned)f.P;
+    unsigned view    = g / P;
+    unsigned q       = g - view * P;
+    int l            = 0;
+#pragma unroll
+    for (int i = 1; i < VETR_MAX_LAYERS; ++i)
+        if (i < f.L && q >= (unsigned)f.lbase[i]) l = i;
+    q -= (unsigned)f.lbase[l];
+    unsigned w = (unsigned)f.lw[l];
+    unsigned y = q / w;
+    r.x = (short)(q - y * w), r.y = (short)y, r.level = (unsigned char)l, r.view = (unsigned char)view, r.pad = 0;
+    return r;
+}
+
+__device__ __forceinline__ int list_end(const Frame& f, int g) { return g < 0 ? 0 : f.ends[g]; }
 
 // In-place ascending sort of a list in global memory by the whole CTA (lists longer than kLongList).  Sorting
 // network with all comparators pointing the same way, so that positions >= n behave as +infinity without padding.
@@ -369,29 +385,75 @@ __device__ void sort_long_list(unsigned long long* keys, int n)
     }
 }
 
-// Alpha of a fragment: confidence (mode 1) or bilinear corner weight x confidence (mode 3).  For mode 3 the
-// level-space position is recomputed from the point (the reference stores it in per_point_data,
-// RenderForward.cu:1116-1127; recomputing with the same arithmetic gives the same bits).
-__device__ __forceinline__ float fragment_alpha(const Frame& f, const Camera& cam, const PixelRef& px, int pid, int tex,
-                                                float2* uv_out, int* corner_out)
+// Mode 3: level-space image position of a point and the bilinear corner a pixel is of it.  The reference stores
+// both per fragment (per_point_data, RenderForward.cu:1116-1127); recomputing them with the same arithmetic gives
+// the same bits and saves 16 bytes per fragment of HBM traffic in each direction.
+__device__ __forceinline__ float2 level_position(const Frame& f, const Camera& cam, int pid, int level, float4* pos_out)
+{
+    float4 pos   = __ldg(f.position + pid);
+    Projected pr = project_point(pos, cam, f.dist_cutoff);
+    float2 ip    = pr.ip;
+    for (int l = 0; l < level; ++l) ip.x *= 0.5f, ip.y *= 0.5f;
+    if (pos_out) *pos_out = pos;
+    return ip;
+}
+__device__ __forceinline__ int corner_of(float2 ip, const PixInfo& px)
+{
+    int bx = round_down(ip.x), by = round_down(ip.y);
+    return min(max((px.y - by) * 2 + (px.x - bx), 0), 3);
+}
+
+// Alpha of a fragment: confidence (mode 1) or bilinear corner weight x confidence (mode 3).
+__device__ __forceinline__ float fragment_alpha(const Frame& f, const Camera& cam, const PixInfo& px, int pid, int tex)
 {
     float a = __ldg(f.confidence + tex);
     if (f.mode == VETR_MODE_BILINEAR_BLEND)
     {
-        float4 pos   = __ldg(f.position + pid);
-        Projected pr = project_point(pos, cam, f.dist_cutoff);
-        float2 ip    = pr.ip;
-        for (int l = 0; l < px.level; ++l) ip.x *= 0.5f, ip.y *= 0.5f;
-        int bx = round_down(ip.x), by = round_down(ip.y);
-        int corner = (px.y - by) * 2 + (px.x - bx);
-        corner     = min(max(corner, 0), 3);
-        float w    = blending_fac(ip, corner, nullptr, nullptr);
-        if (uv_out) *uv_out = ip;
-        if (corner_out) *corner_out = corner;
-        a = w * a;
+        float2 ip = level_position(f, cam, pid, px.level, nullptr);
+        a         = blending_fac(ip, corner_of(ip, px), nullptr, nullptr) * a;
     }
     return a;
 }
+
+__device__ __forceinline__ float4 load_descriptor(const Frame& f, int tex)
+{
+    float4 d;
+    d.x = __ldg(f.texture + tex);
+    d.y = __ldg(f.texture + (size_t)f.n_tex + tex);
+    d.z = __ldg(f.texture + 2 * (size_t)f.n_tex + tex);
+    d.w = f.C > 3 ? __ldg(f.texture + 3 * (size_t)f.n_tex + tex) : 0.f;
+    return d;
+}
+
+// First pixel of an item that the item kernels leave to the long-list kernels (0 or 1 pixels).
+__device__ __forceinline__ int long_prefix(const Frame& f, int lo)
+{
+    return (f.ends[lo] - list_end(f, lo - 1)) > kLongList ? 1 : 0;
+}
+
+struct OutPtrs
+{
+    float* color[VETR_MAX_LAYERS];
+    float* weight[VETR_MAX_LAYERS];
+    float* mask[VETR_MAX_LAYERS];
+    float* depth[VETR_MAX_LAYERS];
+};
+
+__device__ __forceinline__ void write_pixel(const Frame& f, const OutPtrs& out, const PixInfo& px, const float c[4], float T,
+                                            float depth)
+{
+    const int w = f.lw[px.level], h = f.lh[px.level];
+    const size_t hw = (size_t)w * h;
+    const size_t o  = (size_t)px.y * w + px.x;
+    float* col      = out.color[px.level] + (size_t)px.view * f.C * hw + o;
+    for (int ci = 0; ci < f.C; ++ci) col[ci * hw] = c[ci];
+    if (out.weight[0]) out.weight[px.level][(size_t)px.view * hw + o] = T;
+    if (out.mask[0]) out.mask[px.level][(size_t)px.view * hw + o] = (T == 0.f) ? f.mask_value : 1.f;
+    if (out.depth[0]) out.depth[px.level][(size_t)px.view * hw + o] = depth;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Pass 4: sort + blend.
 
 struct BlendSmem
 {
@@ -402,192 +464,86 @@ struct BlendSmem
         float4 desc[kCap];
     };
     float alpha[kCap];
-    int seg_end[kMaxPixels + 1];
+    int seg_end[2][kMaxPixels + 1];  // per-pixel arrays are double buffered: the next item fills the other half
+    PixInfo pix[2][kMaxPixels];      // while slow warps still fold the current one
     unsigned char seg_of[kCap];
+    Camera cam[VETR_MAX_VIEWS];
 };
 
-// ---------------------------------------------------------------------------------------------------------
-// Pass 4: sort + blend.
-
-__device__ __forceinline__ void write_pixel(const Frame& f, float* const* out_color, float* const* out_weight,
-                                            float* const* out_mask, float* const* out_depth, const PixelRef& px,
-                                            const float c[4], float T, float depth)
-{
-    const long long hw = (long long)px.w * px.h;
-    const long long o  = (long long)px.y * px.w + px.x;
-    float* col         = out_color[px.level] + (long long)px.view * f.C * hw + o;
-    for (int ci = 0; ci < f.C; ++ci) col[ci * hw] = c[ci];
-    if (out_weight) out_weight[px.level][(long long)px.view * hw + o] = T;
-    if (out_mask) out_mask[px.level][(long long)px.view * hw + o] = (T == 0.f) ? f.mask_value : 1.f;
-    if (out_depth) out_depth[px.level][(long long)px.view * hw + o] = depth;
-}
-
-struct OutPtrs
-{
-    float* color[VETR_MAX_LAYERS];
-    float* weight[VETR_MAX_LAYERS];
-    float* mask[VETR_MAX_LAYERS];
-    float* depth[VETR_MAX_LAYERS];
-    int has_weight, has_mask, has_depth;
-};
-
-__global__ void __launch_bounds__(kThreads) sort_blend_kernel(const __grid_constant__ Frame f,
-                                                              const __grid_constant__ OutPtrs out)
+__global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __grid_constant__ Frame f,
+                                                                        const __grid_constant__ OutPtrs out)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BlendSmem& s = *reinterpret_cast<BlendSmem*>(smem_raw);
-    __shared__ float s_fold[8];  // slow path: T and colour carried between blocks
     const int tid     = threadIdx.x;
     const int n_items = f.status[3];
     const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
-    float* const* oc = out.color;
-    float* const* ow = out.has_weight ? out.weight : nullptr;
-    float* const* om = out.has_mask ? out.mask : nullptr;
-    float* const* od = out.has_depth ? out.depth : nullptr;
+    if (tid < f.n_views) s.cam[tid] = load_camera(f, tid);
+    int buf = 0;
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x)
     {
-        int lo = f.item_start[item], hi = f.item_start[item + 1];
+        int lo = f.item_start[item];
+        const int hi = f.item_start[item + 1];
         if (lo >= hi) continue;
-        __syncthreads();  // shared memory of the previous item is free
-
-        // ---- slow path: a first pixel with a long list is handled alone, in blocks of kCap fragments
+        lo += long_prefix(f, lo);
+        if (lo >= hi) continue;
+        buf ^= 1;
+        int* seg_end       = s.seg_end[buf];
+        PixInfo* pix       = s.pix[buf];
+        const int f0 = list_end(f, lo - 1);
+        const int np = hi - lo;
+        if (tid < np)
         {
-            long long e0 = list_end(f, (long long)lo - 1), e1 = f.ends[lo];
-            int n_first  = (int)(e1 - e0);
-            if (n_first > kLongList)
-            {
-                sort_long_list(f.keys + e0, n_first);
-                __threadfence_block();
-                PixelRef px  = decode_pixel(f, lo);
-                Camera cam   = load_camera(f, px.view);
-                int cnt      = n_first;
-                if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
-                if (tid == 0)
-                {
-                    s_fold[0] = 1.f;
-                    s_fold[1] = s_fold[2] = s_fold[3] = s_fold[4] = 0.f;
-                    s_fold[5] = 0.f;  // stop flag
-                }
-                __syncthreads();
-                for (int blk = 0; blk < cnt; blk += kCap)
-                {
-                    int m = min(kCap, cnt - blk);
-                    for (int i = tid; i < m; i += kThreads)
-                    {
-                        int pid = (int)(unsigned)f.keys[e0 + blk + i];
-                        int tex = __ldg(f.index + pid);
-                        s.alpha[i] = fragment_alpha(f, cam, px, pid, tex, nullptr, nullptr);
-                        float4 d;
-                        d.x = __ldg(f.texture + tex);
-                        d.y = __ldg(f.texture + (long long)f.n_tex + tex);
-                        d.z = __ldg(f.texture + 2LL * f.n_tex + tex);
-                        d.w = f.C > 3 ? __ldg(f.texture + 3LL * f.n_tex + tex) : 0.f;
-                        s.desc[i] = d;
-                    }
-                    __syncthreads();
-                    if (tid == 0 && s_fold[5] == 0.f)
-                    {
-                        float T = s_fold[0];
-                        float c[4] = {s_fold[1], s_fold[2], s_fold[3], s_fold[4]};
-                        for (int i = 0; i < m; ++i)
-                        {
-                            float a = s.alpha[i];
-                            float4 d = s.desc[i];
-                            c[0] = vetr_blend(T, a, d.x, c[0]);
-                            c[1] = vetr_blend(T, a, d.y, c[1]);
-                            c[2] = vetr_blend(T, a, d.z, c[2]);
-                            c[3] = vetr_blend(T, a, d.w, c[3]);
-                            T    = vetr_new_T(T, a);
-                            if (bilinear && T < 0.001f)
-                            {
-                                s_fold[5] = 1.f;
-                                break;
-                            }
-                        }
-                        s_fold[0] = T;
-                        s_fold[1] = c[0], s_fold[2] = c[1], s_fold[3] = c[2], s_fold[4] = c[3];
-                    }
-                    __syncthreads();
-                }
-                if (tid == 0)
-                {
-                    float T    = s_fold[0];
-                    float c[4] = {s_fold[1], s_fold[2], s_fold[3], s_fold[4]};
-                    bool add_bg = !f.use_env && !(bilinear && !(T >= 0.001f));
-                    if (add_bg)
-                        for (int ci = 0; ci < f.C; ++ci) c[ci] = vetr_blend(T, 1.f, f.background[ci], c[ci]);
-                    float depth = __uint_as_float((unsigned)(f.keys[e0] >> 32));
-                    write_pixel(f, oc, ow, om, od, px, c, T, depth);
-                }
-                lo += 1;
-                __syncthreads();
-                if (lo >= hi) continue;
-            }
+            seg_end[tid + 1] = f.ends[lo + tid] - f0;
+            pix[tid]         = decode_pixel(f, (unsigned)(lo + tid));
         }
-
-        // ---- fast path
-        const long long f0 = list_end(f, (long long)lo - 1);
-        const int np       = hi - lo;
-        if (tid < np) s.seg_end[tid + 1] = (int)((long long)f.ends[lo + tid] - f0);
-        if (tid == 0) s.seg_end[0] = 0;
-        __syncthreads();
-        const int nf = s.seg_end[np];
+        if (tid == 0) seg_end[0] = 0;
+        __syncthreads();  // (a) per-pixel arrays ready; every warp has left the previous item's fold
+        const int nf = seg_end[np];
         for (int i = tid; i < nf; i += kThreads) s.unsorted[i] = f.keys[f0 + i];
-        __syncthreads();
+        __syncthreads();  // (b)
         // rank sort inside each list; keys are unique (distinct point indices), so ranks are a permutation
         for (int i = tid; i < nf; i += kThreads)
         {
-            int a = 0, b = np;  // find j with seg_end[j] <= i < seg_end[j+1]
-            while (b - a > 1)
+            int a = 0;  // largest a < np with seg_end[a] <= i
+#pragma unroll
+            for (int step = kMaxPixels / 2; step > 0; step >>= 1)
             {
-                int m = (a + b) >> 1;
-                if (s.seg_end[m] <= i)
-                    a = m;
-                else
-                    b = m;
+                const int m = a + step;
+                if (m < np && seg_end[m] <= i) a = m;
             }
-            const int ss = s.seg_end[a], se = s.seg_end[a + 1];
+            const int ss = seg_end[a], se = seg_end[a + 1];
             const unsigned long long key = s.unsorted[i];
             int rank = 0;
             for (int k = ss; k < se; ++k) rank += s.unsorted[k] < key;
             s.sorted[ss + rank] = key;
-            s.seg_of[i]         = (unsigned char)a;  // position i belongs to list a both before and after sorting
+            s.seg_of[i]         = (unsigned char)a;  // slot i belongs to list a before and after sorting
         }
-        __syncthreads();
-        // write back + gather
+        __syncthreads();  // (c)
+        // write back + gather (independent iterations: the loads of several fragments are in flight together)
+        for (int i = tid; i < nf; i += kThreads)
         {
-            int cur_view = -1;
-            Camera cam;
-            for (int i = tid; i < nf; i += kThreads)
+            const unsigned long long key = s.sorted[i];
+            if (f.keep_sorted) f.keys[f0 + i] = key;
+            const int pid = (int)(unsigned)key;
+            const int tex = __ldg(f.index + pid);
+            float a;
+            if (bilinear)
             {
-                const unsigned long long key = s.sorted[i];
-                if (f.keep_sorted) f.keys[f0 + i] = key;
-                int pid = (int)(unsigned)key;
-                int tex = __ldg(f.index + pid);
-                float a;
-                if (bilinear)
-                {
-                    PixelRef px = decode_pixel(f, (long long)lo + s.seg_of[i]);
-                    if (px.view != cur_view) cam = load_camera(f, px.view), cur_view = px.view;
-                    a = fragment_alpha(f, cam, px, pid, tex, nullptr, nullptr);
-                }
-                else
-                    a = __ldg(f.confidence + tex);
-                s.alpha[i] = a;
-                float4 d;
-                d.x = __ldg(f.texture + tex);
-                d.y = __ldg(f.texture + (long long)f.n_tex + tex);
-                d.z = __ldg(f.texture + 2LL * f.n_tex + tex);
-                d.w = f.C > 3 ? __ldg(f.texture + 3LL * f.n_tex + tex) : 0.f;
-                s.desc[i] = d;  // overwrites `unsorted`, which is dead after the barrier above
+                const PixInfo px = pix[s.seg_of[i]];
+                a                = fragment_alpha(f, s.cam[px.view], px, pid, tex);
             }
+            else
+                a = __ldg(f.confidence + tex);
+            s.alpha[i] = a;
+            s.desc[i]  = load_descriptor(f, tex);  // overwrites `unsorted`, dead since barrier (c)
         }
-        __syncthreads();
+        __syncthreads();  // (d)
         // fold: one thread per pixel
         if (tid < np)
         {
-            const int ss = s.seg_end[tid], se = s.seg_end[tid + 1];
+            const int ss = seg_end[tid], se = seg_end[tid + 1];
             int cnt = se - ss;
             if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
             float T    = 1.f;
@@ -607,8 +563,84 @@ __global__ void __launch_bounds__(kThreads) sort_blend_kernel(const __grid_const
             if (add_bg)
                 for (int ci = 0; ci < f.C; ++ci) c[ci] = vetr_blend(T, 1.f, f.background[ci], c[ci]);
             float depth = se > ss ? __uint_as_float((unsigned)(s.sorted[ss] >> 32)) : kMaxDepth;
-            PixelRef px = decode_pixel(f, (long long)lo + tid);
-            write_pixel(f, oc, ow, om, od, px, c, T, depth);
+            write_pixel(f, out, pix[tid], c, T, depth);
+        }
+    }
+}
+
+// Lists longer than kLongList: one CTA per list, sort in global memory, fold in blocks of kCap fragments.
+__global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_constant__ Frame f,
+                                                                   const __grid_constant__ OutPtrs out)
+{
+    if (f.status[2] <= kLongList) return;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    BlendSmem& s = *reinterpret_cast<BlendSmem*>(smem_raw);
+    __shared__ float s_fold[8];  // T, colour and the stop flag carried between blocks
+    const int tid       = threadIdx.x;
+    const int n_items   = f.status[3];
+    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x)
+    {
+        const int lo = f.item_start[item], hi = f.item_start[item + 1];
+        if (lo >= hi || !long_prefix(f, lo)) continue;
+        const int e0 = list_end(f, lo - 1);
+        const int n  = f.ends[lo] - e0;
+        __syncthreads();
+        sort_long_list(f.keys + e0, n);
+        const PixInfo px = decode_pixel(f, (unsigned)lo);
+        if (tid == 0) s.cam[0] = load_camera(f, px.view);
+        int cnt = n;
+        if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
+        if (tid == 0)
+        {
+            s_fold[0] = 1.f;
+            s_fold[1] = s_fold[2] = s_fold[3] = s_fold[4] = 0.f;
+            s_fold[5] = 0.f;
+        }
+        __syncthreads();
+        for (int blk = 0; blk < cnt; blk += kCap)
+        {
+            const int m = min(kCap, cnt - blk);
+            for (int i = tid; i < m; i += kThreads)
+            {
+                const int pid = (int)(unsigned)f.keys[e0 + blk + i];
+                const int tex = __ldg(f.index + pid);
+                s.alpha[i]    = fragment_alpha(f, s.cam[0], px, pid, tex);
+                s.desc[i]     = load_descriptor(f, tex);
+            }
+            __syncthreads();
+            if (tid == 0 && s_fold[5] == 0.f)
+            {
+                float T    = s_fold[0];
+                float c[4] = {s_fold[1], s_fold[2], s_fold[3], s_fold[4]};
+                for (int i = 0; i < m; ++i)
+                {
+                    float a  = s.alpha[i];
+                    float4 d = s.desc[i];
+                    c[0] = vetr_blend(T, a, d.x, c[0]);
+                    c[1] = vetr_blend(T, a, d.y, c[1]);
+                    c[2] = vetr_blend(T, a, d.z, c[2]);
+                    c[3] = vetr_blend(T, a, d.w, c[3]);
+                    T    = vetr_new_T(T, a);
+                    if (bilinear && T < 0.001f)
+                    {
+                        s_fold[5] = 1.f;
+                        break;
+                    }
+                }
+                s_fold[0] = T;
+                s_fold[1] = c[0], s_fold[2] = c[1], s_fold[3] = c[2], s_fold[4] = c[3];
+            }
+            __syncthreads();
+        }
+        if (tid == 0)
+        {
+            float T     = s_fold[0];
+            float c[4]  = {s_fold[1], s_fold[2], s_fold[3], s_fold[4]};
+            bool add_bg = !f.use_env && !(bilinear && !(T >= 0.001f));
+            if (add_bg)
+                for (int ci = 0; ci < f.C; ++ci) c[ci] = vetr_blend(T, 1.f, f.background[ci], c[ci]);
+            write_pixel(f, out, px, c, T, __uint_as_float((unsigned)(f.keys[e0] >> 32)));
         }
     }
 }
@@ -632,195 +664,162 @@ struct BackPtrs
 
 struct BackSmem
 {
-    unsigned long long keys[kCap];
-    float4 desc[kCap];
+    int pid[kCap];
+    int tex[kCap];
     float alpha[kCap];
     float dot[kCap];     // d_i . G  ->  replaced by the alpha gradient of the fragment
     float trans[kCap];   // T_i ; NaN = fragment not blended (early termination / list truncation)
-    float4 grad[kMaxPixels];  // incoming gradient of the pixel
-    int seg_end[kMaxPixels + 1];
+    float2 dR[kCap];     // mode 1: image-space gradient of the fragment's position; x = NaN: none
     unsigned char seg_of[kCap];
-    double red[8][8];    // cross-warp reduction scratch
+    float4 grad[2][kMaxPixels];      // incoming gradient of the pixel; per-pixel arrays are double buffered
+    int seg_end[2][kMaxPixels + 1];
+    PixInfo pix[2][kMaxPixels];
+    double red[kThreads / 32][8];    // cross-warp reduction scratch
+    Camera cam[VETR_MAX_VIEWS];
 };
 
-// Per-thread accumulators of the camera gradients of one view; flushed with atomics.
+// Gradient accumulation with fire-and-forget reductions.  The gradient buffers are never read by these kernels, so
+// the compiler may move other memory operations across them (no memory clobber).
+__device__ __forceinline__ void red_add_v4(float4* addr, float4 v)
+{
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w));
+}
+__device__ __forceinline__ void red_add(float* addr, float v)
+{
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v));
+}
+
+// Camera-gradient accumulators of one thread for the pixels of a single view: pose in double like the reference's
+// atomics (RenderBackward.cu:1423), the rest in float.
+template <bool kIntr>
 struct CamAcc
 {
     double pose[6];
     float pose_count;
-    float intr[13];
-    float intr_count;
-    int view;
-    bool any;
-    __device__ void clear()
+    float intr[kIntr ? 14 : 1];  // 13 gradients + count
+    __device__ __forceinline__ void clear()
     {
+#pragma unroll
         for (int k = 0; k < 6; ++k) pose[k] = 0.0;
-        for (int k = 0; k < 13; ++k) intr[k] = 0.f;
-        pose_count = intr_count = 0.f;
-        any        = false;
+        pose_count = 0.f;
+#pragma unroll
+        for (int k = 0; k < (kIntr ? 14 : 1); ++k) intr[k] = 0.f;
     }
 };
 
-__device__ __forceinline__ void flush_cam(const Frame& f, const BackPtrs& bp, CamAcc& acc)
+// Sums the accumulators over the CTA and adds the totals to the outputs of `view`: one atomic per value and
+// (CTA, view) instead of one per fragment.
+template <bool kIntr>
+__device__ void reduce_cam(const Frame& f, const BackPtrs& bp, CamAcc<kIntr>& acc, int view, BackSmem& s)
 {
-    if (!acc.any) return;
-    const ViewDev& v = f.views[acc.view];
-    if (bp.g_pose)
-    {
-        for (int k = 0; k < 6; ++k) atomicAdd(bp.g_pose + 6 * v.image_index + k, acc.pose[k]);
-        atomicAdd(bp.g_pose_count + v.image_index, acc.pose_count);
-    }
-    if (bp.g_intr)
-    {
-        for (int k = 0; k < 13; ++k) atomicAdd(bp.g_intr + 13 * v.camera_index + k, acc.intr[k]);
-        atomicAdd(bp.g_intr_count + v.camera_index, acc.intr_count);
-    }
-    acc.clear();
-}
-
-// Reduces the accumulators of all threads whose view equals `main_view` over the CTA and issues one set of
-// atomics; threads that hold another view flush on their own.
-__device__ void reduce_cam(const Frame& f, const BackPtrs& bp, CamAcc& acc, int main_view, BackSmem& s)
-{
-    if (acc.any && acc.view != main_view) flush_cam(f, bp, acc);
-    int any = __syncthreads_or(acc.any ? 1 : 0);
-    if (!any) return;
+    constexpr int kN = kIntr ? 21 : 7;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n_values = 6 + 1 + (bp.g_intr ? 14 : 0);
-    for (int base = 0; base < n_values; base += 8)
+    const ViewDev& vw = f.views[view];
+    for (int base = 0; base < kN; base += 8)
     {
-        for (int k = base; k < min(base + 8, n_values); ++k)
+        __syncthreads();
+        for (int k = base; k < min(base + 8, kN); ++k)
         {
-            double v = 0.0;
-            if (acc.any)
+            double x = k < 6 ? acc.pose[k] : (k == 6 ? (double)acc.pose_count : (double)acc.intr[kIntr ? k - 7 : 0]);
+            for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+            if (lane == 0) s.red[warp][k - base] = x;
+        }
+        __syncthreads();
+        const int k = base + threadIdx.x;
+        if (threadIdx.x < 8 && k < kN)
+        {
+            double x = 0.0;
+            for (int w = 0; w < kThreads / 32; ++w) x += s.red[w][threadIdx.x];
+            if (x != 0.0)
             {
                 if (k < 6)
-                    v = acc.pose[k];
+                    atomicAdd(bp.g_pose + 6 * vw.image_index + k, x);
                 else if (k == 6)
-                    v = acc.pose_count;
+                    atomicAdd(bp.g_pose_count + vw.image_index, (float)x);
                 else if (k < 20)
-                    v = acc.intr[k - 7];
+                    atomicAdd(bp.g_intr + 13 * vw.camera_index + (k - 7), (float)x);
                 else
-                    v = acc.intr_count;
+                    atomicAdd(bp.g_intr_count + vw.camera_index, (float)x);
             }
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
-            if (lane == 0) s.red[warp][k - base] = v;
         }
-        __syncthreads();
-        if (threadIdx.x < min(8, n_values - base))
-        {
-            int k    = base + threadIdx.x;
-            double v = 0.0;
-            for (int w = 0; w < kThreads / 32; ++w) v += s.red[w][threadIdx.x];
-            const ViewDev& vw = f.views[main_view];
-            if (k < 6)
-            {
-                if (bp.g_pose) atomicAdd(bp.g_pose + 6 * vw.image_index + k, v);
-            }
-            else if (k == 6)
-            {
-                if (bp.g_pose) atomicAdd(bp.g_pose_count + vw.image_index, (float)v);
-            }
-            else if (k < 20)
-                atomicAdd(bp.g_intr + 13 * vw.camera_index + (k - 7), (float)v);
-            else
-                atomicAdd(bp.g_intr_count + vw.camera_index, (float)v);
-        }
-        __syncthreads();
     }
     acc.clear();
 }
 
-__device__ __forceinline__ void red_add_v4(float4* addr, float4 v)
+// Spatial gradient of one fragment: image-space gradient dR -> point, pose and intrinsics gradients
+// (RenderBackward.cu:1380-1460 and :3097-3180).
+template <bool kIntr>
+__device__ __forceinline__ void spatial_backward(const Frame& f, const BackPtrs& bp, const Camera& cam, const PixInfo& px,
+                                                 int pid, float4 pos, float2 dR, CamAcc<kIntr>& acc)
 {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
-                 : "memory");
-}
-
-// Gradients of one blended fragment (descriptor, confidence, position, camera).  `galpha` is the gradient with
-// respect to the fragment's alpha, `Ta` = T_i * alpha_i.
-__device__ __forceinline__ void fragment_backward(const Frame& f, const BackPtrs& bp, const Camera& cam,
-                                                  const PixelRef& px, long long pixel_offset, int pid, float4 G,
-                                                  float4 d, float Ta, float galpha, CamAcc& acc)
-{
-    const int tex = __ldg(f.index + pid);
-    // descriptor gradient: T * alpha * G  (RenderBackward.cu:1149-1152)
-    float4 gd = make_float4(Ta * G.x, Ta * G.y, Ta * G.z, f.C > 3 ? Ta * G.w : 0.f);
-    red_add_v4(bp.g_desc + tex, gd);
-
-    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
-    const int edge = min(min(px.x, px.w - 1 - px.x), min(px.y, px.h - 1 - px.y));  // ImageView::distanceFromEdge
-    const bool interior = edge > 2;
-    if (!bilinear) atomicAdd(bp.g_conf + tex, galpha);
-    if (!interior) return;
-    if (!bilinear && !f.need_point_grad) return;
-
-    float4 pos = __ldg(f.position + pid);
-    float2 dR;
-    if (!bilinear)
-    {
-        // approximate spatial gradient from the neighbouring pixels (RenderBackward.cu:1347-1374)
-        const long long hw = (long long)px.w * px.h;
-        const float* I = bp.out_color[px.level] + (long long)px.view * f.C * hw + pixel_offset;
-        const float* Gp = bp.grad_color[px.level] + (long long)px.view * f.C * hw + pixel_offset;
-        float dx = 0.f, dy = 0.f;
-        const float dv[4] = {d.x, d.y, d.z, d.w};
-        for (int ci = 0; ci < f.C; ++ci)
-        {
-            const float* Ic = I + ci * hw;
-            const float* Gc = Gp + ci * hw;
-            float Tp = dv[ci];
-            float a0 = -(Tp - __ldg(Ic - 1)) * __ldg(Gc - 1);
-            float a1 = (Tp - __ldg(Ic + 1)) * __ldg(Gc + 1);
-            float b0 = -(Tp - __ldg(Ic - px.w)) * __ldg(Gc - px.w);
-            float b1 = (Tp - __ldg(Ic + px.w)) * __ldg(Gc + px.w);
-            dx += 0.5f * (a0 + a1);
-            dy += 0.5f * (b0 + b1);
-        }
-        dR = make_float2(dx / (float)f.C, dy / (float)f.C);
-    }
-    else
-    {
-        Projected pr = project_point(pos, cam, f.dist_cutoff);
-        float2 ip    = pr.ip;
-        for (int l = 0; l < px.level; ++l) ip.x *= 0.5f, ip.y *= 0.5f;
-        int bx = round_down(ip.x), by = round_down(ip.y);
-        int corner = min(max((px.y - by) * 2 + (px.x - bx), 0), 3);
-        float jx, jy;
-        float w = blending_fac(ip, corner, &jx, &jy);
-        atomicAdd(bp.g_conf + tex, w * galpha);  // RenderBackward.cu:3076-3079
-        if (!f.need_point_grad) return;
-        float single = __ldg(f.confidence + tex) * galpha;
-        dR           = make_float2(jx * single, jy * single);
-    }
     float scale = 1.f;
     for (int l = 0; l < px.level; ++l) scale *= 0.5f;
     float crop2[5];
 #pragma unroll
     for (int k = 0; k < 5; ++k) crop2[k] = cam.crop[k] * scale;  // IntrinsicsPinhole::scale
     BackOut bo;
-    if (!project_backward(pos, dR, cam, crop2, f.dist_cutoff, bp.g_intr != nullptr, bo)) return;
+    if (!project_backward(pos, dR, cam, crop2, f.dist_cutoff, kIntr, bo)) return;
     if (bp.g_points) red_add_v4(bp.g_points + pid, make_float4(bo.g_point[0], bo.g_point[1], bo.g_point[2], 1.f));
-    if (acc.any && acc.view != px.view) flush_cam(f, bp, acc);
-    acc.view = px.view;
-    acc.any  = true;
-    for (int k = 0; k < 6; ++k) acc.pose[k] += (double)bo.g_pose[k];
-    acc.pose_count += bilinear ? 1.f : (1.f / 1024.f);  // RenderBackward.cu:1425 vs :3144
-    if (bp.g_intr)
+    if (bp.g_pose)
+    {
+#pragma unroll
+        for (int k = 0; k < 6; ++k) acc.pose[k] += (double)bo.g_pose[k];
+        acc.pose_count += f.mode == VETR_MODE_BILINEAR_BLEND ? 1.f : (1.f / 1024.f);  // RenderBackward.cu:1425 vs :3144
+    }
+    if (kIntr)
     {
         bo.g_k[4] *= 0.f;
+#pragma unroll
         for (int k = 0; k < 5; ++k) acc.intr[k] += f.k_grad_factor * bo.g_k[k];
         bo.g_dis[2] *= 0.25f;
+#pragma unroll
         for (int k = 3; k < 8; ++k) bo.g_dis[k] *= 0.1f;
+#pragma unroll
         for (int k = 0; k < 8; ++k) acc.intr[5 + k] += f.dist_grad_factor * bo.g_dis[k];
-        acc.intr_count += 1.f / 1024.f;
+        acc.intr[kIntr ? 13 : 0] += 1.f / 1024.f;
     }
 }
 
-__device__ __forceinline__ float4 load_grad(const Frame& f, const BackPtrs& bp, const PixelRef& px)
+// Mode 1: approximate image-space gradient of a fragment from the neighbouring pixels (RenderBackward.cu:1347-1374).
+__device__ __forceinline__ float2 neighbour_gradient(const Frame& f, const BackPtrs& bp, const PixInfo& px, float4 d)
 {
-    const long long hw = (long long)px.w * px.h;
-    const float* G     = bp.grad_color[px.level] + (long long)px.view * f.C * hw + (long long)px.y * px.w + px.x;
+    const int w = f.lw[px.level], h = f.lh[px.level];
+    const int hw = w * h;
+    const int o  = (px.view * f.C) * hw + px.y * w + px.x;
+    const float* I  = bp.out_color[px.level] + o;
+    const float* Gp = bp.grad_color[px.level] + o;
+    float dx = 0.f, dy = 0.f;
+    const float dv[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+    for (int ci = 0; ci < 4; ++ci)
+    {
+        if (ci < f.C)
+        {
+            const float* Ic = I + ci * hw;
+            const float* Gc = Gp + ci * hw;
+            float Tp = dv[ci];
+            float a0 = -(Tp - __ldg(Ic - 1)) * __ldg(Gc - 1);
+            float a1 = (Tp - __ldg(Ic + 1)) * __ldg(Gc + 1);
+            float b0 = -(Tp - __ldg(Ic - w)) * __ldg(Gc - w);
+            float b1 = (Tp - __ldg(Ic + w)) * __ldg(Gc + w);
+            dx += 0.5f * (a0 + a1);
+            dy += 0.5f * (b0 + b1);
+        }
+    }
+    return make_float2(dx / (float)f.C, dy / (float)f.C);
+}
+
+__device__ __forceinline__ bool is_interior(const Frame& f, const PixInfo& px)  // ImageView::distanceFromEdge > 2
+{
+    const int w = f.lw[px.level], h = f.lh[px.level];
+    return min(min((int)px.x, w - 1 - px.x), min((int)px.y, h - 1 - px.y)) > 2;
+}
+
+__device__ __forceinline__ float4 load_grad(const Frame& f, const BackPtrs& bp, const PixInfo& px)
+{
+    const int w = f.lw[px.level], h = f.lh[px.level];
+    const int hw = w * h;
+    const float* G = bp.grad_color[px.level] + (px.view * f.C) * hw + px.y * w + px.x;
     float4 g;
     g.x = __ldg(G);
     g.y = __ldg(G + hw);
@@ -840,279 +839,340 @@ __device__ __forceinline__ float dot4(float4 a, float4 b, int C)
     return r;
 }
 
-__global__ void __launch_bounds__(kThreads) backward_kernel(const __grid_constant__ Frame f,
-                                                            const __grid_constant__ BackPtrs bp)
+// Stage A of a fragment (needs nothing from the sweeps, issues no atomics): gathers, d.G, and in mode 1 the
+// image-space gradient dR of the fragment's position.
+__device__ __forceinline__ void fragment_stage_a(const Frame& f, const BackPtrs& bp, BackSmem& s, const Camera& cam,
+                                                 const PixInfo& px, float4 G, int slot, int pid, bool blended)
+{
+    const int tex = __ldg(f.index + pid);
+    s.pid[slot]   = pid;
+    s.tex[slot]   = tex;
+    s.alpha[slot] = fragment_alpha(f, cam, px, pid, tex);
+    const float4 d = load_descriptor(f, tex);
+    s.dot[slot]    = dot4(d, G, f.C);
+    if (f.mode != VETR_MODE_BILINEAR_BLEND)
+    {
+        float2 dR = make_float2(__int_as_float(0x7fffffff), 0.f);
+        if (blended && f.need_point_grad && is_interior(f, px)) dR = neighbour_gradient(f, bp, px, d);
+        s.dR[slot] = dR;
+    }
+}
+
+// Stage B of a fragment (after the sweeps): every gradient the fragment contributes to.
+template <bool kIntr>
+__device__ __forceinline__ void fragment_stage_b(const Frame& f, const BackPtrs& bp, const Camera& cam, const PixInfo& px,
+                                                 float4 G, int pid, int tex, float Ta, float galpha, float2 dR,
+                                                 CamAcc<kIntr>& acc)
+{
+    // descriptor gradient: T * alpha * G  (RenderBackward.cu:1149-1152)
+    red_add_v4(bp.g_desc + tex, make_float4(Ta * G.x, Ta * G.y, Ta * G.z, f.C > 3 ? Ta * G.w : 0.f));
+    if (f.mode != VETR_MODE_BILINEAR_BLEND)
+    {
+        red_add(bp.g_conf + tex, galpha);
+        if (dR.x == dR.x) spatial_backward<kIntr>(f, bp, cam, px, pid, __ldg(f.position + pid), dR, acc);
+        return;
+    }
+    if (!is_interior(f, px)) return;  // the reference writes the mode-3 confidence gradient for interior pixels only
+    float4 pos;
+    float2 ip = level_position(f, cam, pid, px.level, &pos);
+    float jx, jy;
+    float w = blending_fac(ip, corner_of(ip, px), &jx, &jy);
+    red_add(bp.g_conf + tex, w * galpha);  // RenderBackward.cu:3076-3079
+    if (!f.need_point_grad) return;
+    float single = __ldg(f.confidence + tex) * galpha;
+    spatial_backward<kIntr>(f, bp, cam, px, pid, pos, make_float2(jx * single, jy * single), acc);
+}
+
+// Transmittance forward and suffix sum backward over one list held in shared memory: the O(n) form of the
+// reference's double loop (RenderBackward.cu:1118-1181).  Leaves T_i in trans[] and d(loss)/d(alpha_i) in dot[].
+__device__ __forceinline__ void sweep_list(const Frame& f, BackSmem& s, int ss, int se, float4 G, float4 bgc,
+                                           float bg_acc[4], float& p0_acc)
+{
+    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+    int cnt = se - ss;
+    if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
+    float T = 1.f;
+    int eff = cnt;
+    for (int i = 0; i < cnt; ++i)
+    {
+        s.trans[ss + i] = T;
+        T               = vetr_new_T(T, s.alpha[ss + i]);
+        if (bilinear && T < 0.001f)
+        {
+            eff = i + 1;
+            break;
+        }
+    }
+    for (int i = ss + eff; i < se; ++i) s.trans[i] = __int_as_float(0x7fffffff);  // NaN: not blended, no gradient
+    const bool bg_term = !f.use_env && !(bilinear && !(T >= 0.001f));
+    float S = 0.f;
+    if (bg_term)
+    {
+        float dotb = dot4(bgc, G, f.C);
+        bg_acc[0] += T * 1.f * G.x, bg_acc[1] += T * 1.f * G.y, bg_acc[2] += T * 1.f * G.z;
+        if (f.C > 3) bg_acc[3] += T * 1.f * G.w;
+        if (!bilinear && f.bg_alpha_to_point0) p0_acc += dotb * T;
+        S = T * 1.f * dotb;
+    }
+    for (int i = ss + eff - 1; i >= ss; --i)
+    {
+        float a = s.alpha[i], Ti = s.trans[i], dt = s.dot[i];
+        s.dot[i] = Ti * dt - S / (1 - a + 1e-9f);
+        S += Ti * a * dt;
+    }
+}
+
+// Background gradient and the confidence term the reference routes to descriptor 0: CTA reduction, one atomic each.
+__device__ __forceinline__ void reduce_background(const Frame& f, const BackPtrs& bp, BackSmem& s, const float bg_acc[4],
+                                                  float p0_acc)
+{
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float v[5] = {bg_acc[0], bg_acc[1], bg_acc[2], bg_acc[3], p0_acc};
+    for (int k = 0; k < 5; ++k)
+    {
+        float x = v[k];
+        for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+        if (lane == 0) s.red[warp][k] = (double)x;
+    }
+    __syncthreads();
+    if (threadIdx.x < 5)
+    {
+        float x = 0.f;
+        for (int w = 0; w < kThreads / 32; ++w) x += (float)s.red[w][threadIdx.x];
+        if (x != 0.f)
+        {
+            if (threadIdx.x < 4)
+            {
+                if ((int)threadIdx.x < f.C) atomicAdd(bp.g_background + threadIdx.x, x);
+            }
+            else
+                atomicAdd(bp.g_conf + 0, x);
+        }
+    }
+}
+
+#ifdef VETR_PHASE_TIMING
+__device__ unsigned long long g_phase_cycles[8];
+#    define PHASE_MARK(k)                                            \
+        do                                                           \
+        {                                                            \
+            if (threadIdx.x == 0)                                    \
+            {                                                        \
+                long long now_ = clock64();                          \
+                atomicAdd(&g_phase_cycles[k], (unsigned long long)(now_ - t_phase_)); \
+                t_phase_ = now_;                                     \
+            }                                                        \
+        } while (0)
+#else
+#    define PHASE_MARK(k)
+#endif
+
+template <bool kIntr>
+__global__ void __launch_bounds__(kThreads, kMinCtas) backward_kernel(const __grid_constant__ Frame f,
+                                                                      const __grid_constant__ BackPtrs bp)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BackSmem& s = *reinterpret_cast<BackSmem*>(smem_raw);
-    __shared__ float s_carry[4];  // slow path: {T at block start, S carried backwards, stop position, unused}
     const int tid     = threadIdx.x;
     const int n_items = f.status[3];
-    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
-    float4 bgc = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
+    const float4 bgc  = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
+    if (tid < f.n_views) s.cam[tid] = load_camera(f, tid);
 
-    CamAcc acc;
+    CamAcc<kIntr> acc;
     acc.clear();
-    acc.view = 0;
-    // background colour gradient and the confidence gradient that the reference routes to descriptor 0
+    int acc_view    = -1;  // view the accumulators belong to (items of a CTA come in view order)
+    float bg_acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float p0_acc    = 0.f;
+    const int P     = (int)f.P;
+    const bool want_cam = bp.g_pose != nullptr || kIntr;
+    int buf = 0;
+#ifdef VETR_PHASE_TIMING
+    long long t_phase_ = clock64();
+#endif
+
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x)
+    {
+        int lo_item = f.item_start[item];
+        const int hi_item = f.item_start[item + 1];
+        if (lo_item >= hi_item) continue;
+        lo_item += long_prefix(f, lo_item);
+        // a run of pixels of one view at a time, so that camera gradients belong to a single view
+        for (int lo = lo_item; lo < hi_item;)
+        {
+            const int view = lo / P;
+            const int hi   = min(hi_item, (view + 1) * P);
+            if (view != acc_view)
+            {
+                if (acc_view >= 0 && want_cam) reduce_cam<kIntr>(f, bp, acc, acc_view, s);
+                acc_view = view;
+            }
+            buf ^= 1;
+            int* seg_end  = s.seg_end[buf];
+            PixInfo* pix  = s.pix[buf];
+            float4* grad  = s.grad[buf];
+            const int f0 = list_end(f, lo - 1);
+            const int np = hi - lo;
+            if (tid < np)
+            {
+                seg_end[tid + 1] = f.ends[lo + tid] - f0;
+                const PixInfo px = decode_pixel(f, (unsigned)(lo + tid));
+                pix[tid]         = px;
+                grad[tid]        = load_grad(f, bp, px);
+            }
+            if (tid == 0) seg_end[0] = 0;
+            PHASE_MARK(0);
+            __syncthreads();  // (a) per-pixel arrays ready; every warp has left stage B of the previous run
+            PHASE_MARK(1);
+            const Camera& cam = s.cam[view];
+            const int nf = seg_end[np];
+            for (int i = tid; i < nf; i += kThreads)
+            {
+                int a = 0;  // largest a < np with seg_end[a] <= i
+#pragma unroll
+                for (int step = kMaxPixels / 2; step > 0; step >>= 1)
+                {
+                    const int m = a + step;
+                    if (m < np && seg_end[m] <= i) a = m;
+                }
+                s.seg_of[i] = (unsigned char)a;
+                const bool blended = f.dbg_max_len <= 0 || i - seg_end[a] < f.dbg_max_len;  // list truncation
+                fragment_stage_a(f, bp, s, cam, pix[a], grad[a], i, (int)(unsigned)f.keys[f0 + i], blended);
+            }
+            PHASE_MARK(2);
+            __syncthreads();  // (b)
+            PHASE_MARK(3);
+            if (tid < np) sweep_list(f, s, seg_end[tid], seg_end[tid + 1], grad[tid], bgc, bg_acc, p0_acc);
+            PHASE_MARK(4);
+            __syncthreads();  // (c)
+            PHASE_MARK(5);
+            for (int i = tid; i < nf; i += kThreads)
+            {
+                const float Ti = s.trans[i];
+                if (Ti != Ti) continue;
+                const int a = s.seg_of[i];
+                fragment_stage_b<kIntr>(f, bp, cam, pix[a], grad[a], s.pid[i], s.tex[i], Ti * s.alpha[i], s.dot[i], s.dR[i],
+                                        acc);
+            }
+            PHASE_MARK(6);
+            lo = hi;
+        }
+    }
+    if (acc_view >= 0 && want_cam) reduce_cam<kIntr>(f, bp, acc, acc_view, s);
+    reduce_background(f, bp, s, bg_acc, p0_acc);
+}
+
+// Lists longer than kLongList: one CTA per list, blocks of kCap fragments, a forward sweep that records the
+// transmittance at every block start and a backward sweep over the blocks that carries the suffix sum.
+template <bool kIntr>
+__global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_constant__ Frame f,
+                                                                 const __grid_constant__ BackPtrs bp)
+{
+    if (f.status[2] <= kLongList) return;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    BackSmem& s = *reinterpret_cast<BackSmem*>(smem_raw);
+    __shared__ float s_carry[4];      // {T, S, stop position}
+    __shared__ float s_block_T[256];  // transmittance at block starts; lists beyond 256 * kCap fragments are cut there
+    const int tid       = threadIdx.x;
+    const int n_items   = f.status[3];
+    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+    const float4 bgc    = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
+    CamAcc<kIntr> acc;
+    acc.clear();
     float bg_acc[4] = {0.f, 0.f, 0.f, 0.f};
     float p0_acc    = 0.f;
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x)
     {
-        int lo = f.item_start[item], hi = f.item_start[item + 1];
-        if (lo >= hi) continue;
+        const int lo = f.item_start[item], hi = f.item_start[item + 1];
+        if (lo >= hi || !long_prefix(f, lo)) continue;
+        const int e0 = list_end(f, lo - 1);
+        const int n  = f.ends[lo] - e0;
+        const PixInfo px = decode_pixel(f, (unsigned)lo);
         __syncthreads();
-
-        // ---- slow path: first pixel with a long list, blocks of kCap fragments, two sweeps
-        {
-            long long e0 = list_end(f, (long long)lo - 1), e1 = f.ends[lo];
-            int n_first  = (int)(e1 - e0);
-            if (n_first > kLongList)
-            {
-                PixelRef px = decode_pixel(f, lo);
-                Camera cam  = load_camera(f, px.view);
-                float4 G    = load_grad(f, bp, px);
-                int cnt     = n_first;
-                if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
-                const int n_blocks = (cnt + kCap - 1) / kCap;
-                // sweep 1 (forward): transmittance at the start of every block -> stored in seg_end[] (as float bits),
-                // which holds kMaxPixels+1 entries; longer lists are cut there (their tail has T ~ 0).
-                const int max_blocks = kMaxPixels;
-                const int used_blocks = min(n_blocks, max_blocks);
-                cnt = min(cnt, used_blocks * kCap);
-                if (tid == 0) s_carry[0] = 1.f, s_carry[2] = (float)cnt;
-                __syncthreads();
-                for (int blk = 0; blk < used_blocks; ++blk)
-                {
-                    int m = min(kCap, cnt - blk * kCap);
-                    for (int i = tid; i < m; i += kThreads)
-                    {
-                        int pid    = (int)(unsigned)f.keys[e0 + (long long)blk * kCap + i];
-                        int tex    = __ldg(f.index + pid);
-                        s.alpha[i] = fragment_alpha(f, cam, px, pid, tex, nullptr, nullptr);
-                    }
-                    __syncthreads();
-                    if (tid == 0)
-                    {
-                        float T = s_carry[0];
-                        s.seg_end[blk] = __float_as_int(T);
-                        int stop = (int)s_carry[2];
-                        for (int i = 0; i < m && blk * kCap + i < stop; ++i)
-                        {
-                            T = vetr_new_T(T, s.alpha[i]);
-                            if (bilinear && T < 0.001f) stop = blk * kCap + i + 1;
-                        }
-                        s_carry[0] = T;
-                        s_carry[2] = (float)stop;
-                    }
-                    __syncthreads();
-                }
-                const int eff_cnt  = (int)s_carry[2];            // fragments that were blended
-                const float T_end  = s_carry[0];
-                // background entry: reached unless a fragment ended the list early (mode 3)
-                const bool bg_term = !f.use_env && !(bilinear && !(T_end >= 0.001f));
-                if (tid == 0)
-                {
-                    float S = 0.f;
-                    if (bg_term)
-                    {
-                        float dotb = dot4(bgc, G, f.C);
-                        bg_acc[0] += T_end * 1.f * G.x, bg_acc[1] += T_end * 1.f * G.y, bg_acc[2] += T_end * 1.f * G.z;
-                        if (f.C > 3) bg_acc[3] += T_end * 1.f * G.w;
-                        if (!bilinear && f.bg_alpha_to_point0) p0_acc += dotb * T_end;
-                        S = T_end * 1.f * dotb;
-                    }
-                    s_carry[1] = S;
-                }
-                __syncthreads();
-                // sweep 2 (backward over blocks)
-                for (int blk = (eff_cnt + kCap - 1) / kCap - 1; blk >= 0; --blk)
-                {
-                    int m = min(kCap, eff_cnt - blk * kCap);
-                    for (int i = tid; i < m; i += kThreads)
-                    {
-                        unsigned long long key = f.keys[e0 + (long long)blk * kCap + i];
-                        int pid    = (int)(unsigned)key;
-                        int tex    = __ldg(f.index + pid);
-                        s.keys[i]  = key;
-                        s.alpha[i] = fragment_alpha(f, cam, px, pid, tex, nullptr, nullptr);
-                        float4 d;
-                        d.x = __ldg(f.texture + tex);
-                        d.y = __ldg(f.texture + (long long)f.n_tex + tex);
-                        d.z = __ldg(f.texture + 2LL * f.n_tex + tex);
-                        d.w = f.C > 3 ? __ldg(f.texture + 3LL * f.n_tex + tex) : 0.f;
-                        s.desc[i] = d;
-                        s.dot[i]  = dot4(d, G, f.C);
-                    }
-                    __syncthreads();
-                    if (tid == 0)
-                    {
-                        float T = __int_as_float(s.seg_end[blk]);
-                        for (int i = 0; i < m; ++i)
-                        {
-                            s.trans[i] = T;
-                            T          = vetr_new_T(T, s.alpha[i]);
-                        }
-                        float S = s_carry[1];
-                        for (int i = m - 1; i >= 0; --i)
-                        {
-                            float a = s.alpha[i], Ti = s.trans[i], dt = s.dot[i];
-                            s.dot[i] = Ti * dt - S / (1 - a + 1e-9f);
-                            S += Ti * a * dt;
-                        }
-                        s_carry[1] = S;
-                    }
-                    __syncthreads();
-                    const long long po = (long long)px.y * px.w + px.x;
-                    for (int i = tid; i < m; i += kThreads)
-                        fragment_backward(f, bp, cam, px, po, (int)(unsigned)s.keys[i], G, s.desc[i],
-                                          s.trans[i] * s.alpha[i], s.dot[i], acc);
-                    __syncthreads();
-                }
-                lo += 1;
-                if (lo >= hi)
-                {
-                    reduce_cam(f, bp, acc, px.view, s);
-                    continue;
-                }
-            }
-        }
-
-        // ---- fast path
-        const long long f0 = list_end(f, (long long)lo - 1);
-        const int np       = hi - lo;
-        if (tid < np)
-        {
-            s.seg_end[tid + 1] = (int)((long long)f.ends[lo + tid] - f0);
-            s.grad[tid]        = load_grad(f, bp, decode_pixel(f, (long long)lo + tid));
-        }
-        if (tid == 0) s.seg_end[0] = 0;
+        if (tid == 0) s.cam[0] = load_camera(f, px.view);
+        const float4 G = load_grad(f, bp, px);
+        int cnt = n;
+        if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
+        cnt = min(cnt, 256 * kCap);
+        const int n_blocks = (cnt + kCap - 1) / kCap;
+        if (tid == 0) s_carry[0] = 1.f, s_carry[2] = (float)cnt;
         __syncthreads();
-        const int nf = s.seg_end[np];
+        const Camera& cam = s.cam[0];
+        // sweep 1: transmittance at block starts and the position where a mode-3 list stops
+        for (int blk = 0; blk < n_blocks; ++blk)
         {
-            int cur_view = -1;
-            Camera cam;
-            for (int i = tid; i < nf; i += kThreads)
+            const int m = min(kCap, cnt - blk * kCap);
+            for (int i = tid; i < m; i += kThreads)
             {
-                int a = 0, b = np;
-                while (b - a > 1)
-                {
-                    int m = (a + b) >> 1;
-                    if (s.seg_end[m] <= i)
-                        a = m;
-                    else
-                        b = m;
-                }
-                s.seg_of[i] = (unsigned char)a;
-                const unsigned long long key = f.keys[f0 + i];
-                s.keys[i] = key;
-                int pid   = (int)(unsigned)key;
-                int tex   = __ldg(f.index + pid);
-                float al;
-                if (bilinear)
-                {
-                    PixelRef px = decode_pixel(f, (long long)lo + a);
-                    if (px.view != cur_view) cam = load_camera(f, px.view), cur_view = px.view;
-                    al = fragment_alpha(f, cam, px, pid, tex, nullptr, nullptr);
-                }
-                else
-                    al = __ldg(f.confidence + tex);
-                s.alpha[i] = al;
-                float4 d;
-                d.x = __ldg(f.texture + tex);
-                d.y = __ldg(f.texture + (long long)f.n_tex + tex);
-                d.z = __ldg(f.texture + 2LL * f.n_tex + tex);
-                d.w = f.C > 3 ? __ldg(f.texture + 3LL * f.n_tex + tex) : 0.f;
-                s.desc[i] = d;
-                s.dot[i]  = dot4(d, s.grad[a], f.C);
+                const int pid = (int)(unsigned)f.keys[e0 + blk * kCap + i];
+                s.alpha[i]    = fragment_alpha(f, cam, px, pid, __ldg(f.index + pid));
             }
+            __syncthreads();
+            if (tid == 0)
+            {
+                float T        = s_carry[0];
+                s_block_T[blk] = T;
+                int stop       = (int)s_carry[2];
+                for (int i = 0; i < m && blk * kCap + i < stop; ++i)
+                {
+                    T = vetr_new_T(T, s.alpha[i]);
+                    if (bilinear && T < 0.001f) stop = blk * kCap + i + 1;
+                }
+                s_carry[0] = T;
+                s_carry[2] = (float)stop;
+            }
+            __syncthreads();
         }
-        __syncthreads();
-        // per pixel: transmittance forward, suffix sum backward (O(n) form of RenderBackward.cu:1118-1181)
-        if (tid < np)
+        const int eff_cnt = (int)s_carry[2];
+        const float T_end = s_carry[0];
+        if (tid == 0)
         {
-            const int ss = s.seg_end[tid], se = s.seg_end[tid + 1];
-            int cnt = se - ss;
-            if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
-            float T = 1.f;
-            int eff = cnt;
-            for (int i = 0; i < cnt; ++i)
-            {
-                s.trans[ss + i] = T;
-                T               = vetr_new_T(T, s.alpha[ss + i]);
-                if (bilinear && T < 0.001f)
-                {
-                    eff = i + 1;
-                    break;
-                }
-            }
-            for (int i = ss + eff; i < se; ++i) s.trans[i] = __int_as_float(0x7fffffff);  // NaN marks: not blended, no gradient
-            bool bg_term = !f.use_env && !(bilinear && !(T >= 0.001f));
-            float4 G = s.grad[tid];
-            float S  = 0.f;
+            const bool bg_term = !f.use_env && !(bilinear && !(T_end >= 0.001f));
+            float S = 0.f;
             if (bg_term)
             {
                 float dotb = dot4(bgc, G, f.C);
-                bg_acc[0] += T * 1.f * G.x, bg_acc[1] += T * 1.f * G.y, bg_acc[2] += T * 1.f * G.z;
-                if (f.C > 3) bg_acc[3] += T * 1.f * G.w;
-                if (!bilinear && f.bg_alpha_to_point0) p0_acc += dotb * T;
-                S = T * 1.f * dotb;
+                bg_acc[0] += T_end * 1.f * G.x, bg_acc[1] += T_end * 1.f * G.y, bg_acc[2] += T_end * 1.f * G.z;
+                if (f.C > 3) bg_acc[3] += T_end * 1.f * G.w;
+                if (!bilinear && f.bg_alpha_to_point0) p0_acc += dotb * T_end;
+                S = T_end * 1.f * dotb;
             }
-            for (int i = ss + eff - 1; i >= ss; --i)
-            {
-                float a = s.alpha[i], Ti = s.trans[i], dt = s.dot[i];
-                s.dot[i] = Ti * dt - S / (1 - a + 1e-9f);
-                S += Ti * a * dt;
-            }
+            s_carry[1] = S;
         }
         __syncthreads();
-        // per fragment: scatter
+        // sweep 2: blocks back to front
+        for (int blk = (eff_cnt + kCap - 1) / kCap - 1; blk >= 0; --blk)
         {
-            int cur_view = -1;
-            Camera cam;
-            for (int i = tid; i < nf; i += kThreads)
+            const int m = min(kCap, eff_cnt - blk * kCap);
+            for (int i = tid; i < m; i += kThreads)
+                fragment_stage_a(f, bp, s, cam, px, G, i, (int)(unsigned)f.keys[e0 + blk * kCap + i], true);
+            __syncthreads();
+            if (tid == 0)
             {
-                float Ti = s.trans[i];
-                if (Ti != Ti) continue;
-                int a       = s.seg_of[i];
-                PixelRef px = decode_pixel(f, (long long)lo + a);
-                if (px.view != cur_view) cam = load_camera(f, px.view), cur_view = px.view;
-                fragment_backward(f, bp, cam, px, (long long)px.y * px.w + px.x, (int)(unsigned)s.keys[i], s.grad[a],
-                                  s.desc[i], Ti * s.alpha[i], s.dot[i], acc);
-            }
-        }
-        int main_view = (int)((long long)lo / f.P);
-        reduce_cam(f, bp, acc, main_view, s);
-    }
-
-    // background gradient and the descriptor-0 confidence term: CTA reduction, one atomic per value
-    __syncthreads();
-    {
-        const int lane = tid & 31, warp = tid >> 5;
-        float v[5] = {bg_acc[0], bg_acc[1], bg_acc[2], bg_acc[3], p0_acc};
-        for (int k = 0; k < 5; ++k)
-        {
-            float x = v[k];
-            for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
-            if (lane == 0) s.red[warp][k] = (double)x;
-        }
-        __syncthreads();
-        if (tid < 5)
-        {
-            float x = 0.f;
-            for (int w = 0; w < kThreads / 32; ++w) x += (float)s.red[w][tid];
-            if (x != 0.f)
-            {
-                if (tid < 4)
+                float T = s_block_T[blk];
+                for (int i = 0; i < m; ++i)
                 {
-                    if (tid < f.C) atomicAdd(bp.g_background + tid, x);
+                    s.trans[i] = T;
+                    T          = vetr_new_T(T, s.alpha[i]);
                 }
-                else
-                    atomicAdd(bp.g_conf + 0, x);
+                float S = s_carry[1];
+                for (int i = m - 1; i >= 0; --i)
+                {
+                    float a = s.alpha[i], Ti = s.trans[i], dt = s.dot[i];
+                    s.dot[i] = Ti * dt - S / (1 - a + 1e-9f);
+                    S += Ti * a * dt;
+                }
+                s_carry[1] = S;
             }
+            __syncthreads();
+            for (int i = tid; i < m; i += kThreads)
+                fragment_stage_b<kIntr>(f, bp, cam, px, G, s.pid[i], s.tex[i], s.trans[i] * s.alpha[i], s.dot[i], s.dR[i], acc);
+            __syncthreads();
         }
+        if (bp.g_pose != nullptr || kIntr) reduce_cam<kIntr>(f, bp, acc, px.view, s);
     }
+    reduce_background(f, bp, s, bg_acc, p0_acc);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -1331,16 +1391,17 @@ extern "C" int vetr_create(vetr_ctx** out, int device, void* cuda_stream)
     cudaDeviceProp prop;
     if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, device);
     if (e == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
+    const int blend_smem = (int)sizeof(BlendSmem), back_smem = (int)sizeof(BackSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(sort_blend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, blend_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(sort_blend_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, blend_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(sort_blend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(BlendSmem));
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->blend_ctas_per_sm, sort_blend_kernel, kThreads, blend_smem);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(BackSmem));
-    if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->blend_ctas_per_sm, sort_blend_kernel, kThreads,
-                                                          sizeof(BlendSmem));
-    if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->back_ctas_per_sm, backward_kernel, kThreads,
-                                                          sizeof(BackSmem));
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->back_ctas_per_sm, backward_kernel<false>, kThreads, back_smem);
     if (e != cudaSuccess)
     {
         delete ctx;
@@ -1391,6 +1452,20 @@ extern "C" int vetr_get_timings(vetr_ctx* ctx, float* out_ms)
 
 extern "C" int64_t vetr_launch_count(const vetr_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
+#ifdef VETR_PHASE_TIMING
+extern "C" int vetr_debug_phase_cycles(unsigned long long* out, int reset)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(g_phase_cycles));
+    if (reset)
+    {
+        unsigned long long z[8] = {};
+        cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z));
+    }
+    return 0;
+}
+#endif
+
 extern "C" int vetr_set_stream(vetr_ctx* ctx, void* cuda_stream)
 {
     if (!ctx) return VETR_E_INVALID_ARG;
@@ -1435,7 +1510,7 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     f.P  = pyramid(f.w, f.h, f.L, f.lw, f.lh, f.lbase);
     f.PT = f.P * n_views;
     if (f.lw[f.L - 1] < 1 || f.lh[f.L - 1] < 1) return VETR_E_INVALID_ARG;  // the reference asserts w > 0 && h > 0 per level
-    if (f.PT > 0x7fffffffLL) return VETR_E_TOO_LARGE;
+    if (f.PT > 0x7fffffffLL || (long long)f.lw[0] * f.lh[0] * f.C * n_views > 0x7fffffffLL) return VETR_E_TOO_LARGE;
     f.position = (const float4*)cloud->position, f.index = cloud->index;
     f.texture = tex->texture, f.confidence = tex->confidence, f.background = tex->background;
     f.poses = cams->poses_se3, f.intr = cams->intrinsics;
@@ -1462,11 +1537,11 @@ extern "C" int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr
     f.dropout = dropout;
     OutPtrs out;
     memset(&out, 0, sizeof(out));
-    out.has_weight = out_weight != nullptr, out.has_mask = out_mask != nullptr, out.has_depth = out_depth != nullptr;
     for (int l = 0; l < f.L; ++l)
     {
         if (!out_color[l]) return VETR_E_INVALID_ARG;
         out.color[l] = out_color[l];
+        if ((out_weight && !out_weight[l]) || (out_mask && !out_mask[l]) || (out_depth && !out_depth[l])) return VETR_E_INVALID_ARG;
         if (out_weight) out.weight[l] = out_weight[l];
         if (out_mask) out.mask[l] = out_mask[l];
         if (out_depth) out.depth[l] = out_depth[l];
@@ -1474,11 +1549,11 @@ extern "C" int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr
     cudaStream_t st = ctx->stream;
     VETR_CUDA(ctx, cudaMemsetAsync(f.counts, 0, f.PT * sizeof(int), st));
     VETR_CUDA(ctx, cudaMemsetAsync(f.status, 0, 4 * sizeof(int), st));
-    const int point_ctas = (f.n + kThreads * kPointsPerThread - 1) / (kThreads * kPointsPerThread);
+    const int point_ctas = (f.n + kProjThreads * kPointsPerThread - 1) / (kProjThreads * kPointsPerThread);
     if (point_ctas > 0)
     {
         PassScope t(ctx, VETR_T_COUNT, 1);
-        project_kernel<false><<<dim3(point_ctas, n_views), kThreads, 0, st>>>(f);
+        project_kernel<false><<<dim3(point_ctas, n_views), kProjThreads, 0, st>>>(f);
     }
     const int n_tiles = (int)((f.PT + kScanTile - 1) / kScanTile);
     {
@@ -1490,12 +1565,13 @@ extern "C" int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr
     if (point_ctas > 0)
     {
         PassScope t(ctx, VETR_T_COLLECT, 1);
-        project_kernel<true><<<dim3(point_ctas, n_views), kThreads, 0, st>>>(f);
+        project_kernel<true><<<dim3(point_ctas, n_views), kProjThreads, 0, st>>>(f);
     }
     {
-        PassScope t(ctx, VETR_T_SORT_BLEND, 1);
+        PassScope t(ctx, VETR_T_SORT_BLEND, 2);
         const int grid = ctx->sm_count * ctx->blend_ctas_per_sm;
         sort_blend_kernel<<<grid, kThreads, sizeof(BlendSmem), st>>>(f, out);
+        sort_blend_long_kernel<<<ctx->sm_count, kThreads, sizeof(BlendSmem), st>>>(f, out);
     }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
@@ -1525,9 +1601,18 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
     bp.g_pose = g_pose, bp.g_pose_count = g_pose_count, bp.g_intr = g_intr, bp.g_intr_count = g_intr_count;
     if (!f.need_point_grad && f.mode != VETR_MODE_BILINEAR_BLEND) bp.g_points = nullptr;
     {
-        PassScope t(ctx, VETR_T_BACKWARD, 1);
+        PassScope t(ctx, VETR_T_BACKWARD, 2);
         const int grid = ctx->sm_count * ctx->back_ctas_per_sm;
-        backward_kernel<<<grid, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
+        if (g_intr)
+        {
+            backward_kernel<true><<<grid, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
+            backward_long_kernel<true><<<ctx->sm_count, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
+        }
+        else
+        {
+            backward_kernel<false><<<grid, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
+            backward_long_kernel<false><<<ctx->sm_count, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
+        }
     }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;

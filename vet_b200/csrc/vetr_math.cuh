@@ -1,10 +1,12 @@
 // Camera arithmetic and blend algebra of the rasterizer kernels (device side).
 //
-// The translation unit that includes this header is compiled with -fmad=false: every product and sum below is
-// rounded separately, in the order written, so that the pixel and the depth bits of a fragment are a pure function
-// of the inputs and can be reproduced bit for bit by a CPU build made without floating-point contraction.  The one
-// deliberate fused multiply-add is the blend step (vetr_blend), where the reference's expression
+// Everything that decides a fragment's pixel, depth bits or forward alpha (the functions marked STRICT) is written
+// with the __f*_rn intrinsics, which the compiler never fuses into multiply-adds: every product and sum is rounded
+// separately, in the order written, so that those values are a pure function of the inputs and are reproduced bit
+// for bit by a CPU build made without floating-point contraction.  The one deliberate fused multiply-add of the
+// forward pass is the blend step (vetr_blend), where the reference's expression
 // `alpha_dest * alpha_s * color + color_dest` (PointBlending.h:90-114) is contracted by its own compiler.
+// The gradient arithmetic (Jacobians, sweeps) is ordinary fp32 and may be contracted.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -24,23 +26,29 @@ struct Camera  // everything a kernel needs to project into one view
     float crop[5];  // crop_transform fx fy cx cy s
     float rot[4];   // crop_rotation row-major
     float cx, cy;   // rotation centre (w/2, h/2) with integer division (RenderForward.cu:156)
+    float R[9];     // rotation matrix of V (backward only)
     bool has_dist;
 };
 
-__device__ __forceinline__ float3 cross3(float3 a, float3 b)
+#define VM(a, b) __fmul_rn((a), (b))
+#define VA(a, b) __fadd_rn((a), (b))
+#define VS(a, b) __fsub_rn((a), (b))
+
+__device__ __forceinline__ float3 cross3(float3 a, float3 b)  // STRICT
 {
-    return make_float3(a.y * b.z - a.z * b.y, a.z * b.x - a.x * b.z, a.x * b.y - a.y * b.x);
+    return make_float3(VS(VM(a.y, b.z), VM(a.z, b.y)), VS(VM(a.z, b.x), VM(a.x, b.z)), VS(VM(a.x, b.y), VM(a.y, b.x)));
 }
 
-// Eigen quaternion transform: v + w * uv + qv x uv with uv = 2 (qv x v); then the translation.
+// STRICT.  Eigen quaternion transform: v + w * uv + qv x uv with uv = 2 (qv x v); then the translation.
 __device__ __forceinline__ float3 transform_point(const Pose& P, float3 v)
 {
     float3 qv = make_float3(P.qx, P.qy, P.qz);
     float3 uv = cross3(qv, v);
-    uv        = make_float3(uv.x + uv.x, uv.y + uv.y, uv.z + uv.z);
+    uv        = make_float3(VA(uv.x, uv.x), VA(uv.y, uv.y), VA(uv.z, uv.z));
     float3 c  = cross3(qv, uv);
-    float3 r  = make_float3(v.x + P.qw * uv.x + c.x, v.y + P.qw * uv.y + c.y, v.z + P.qw * uv.z + c.z);
-    return make_float3(r.x + P.tx, r.y + P.ty, r.z + P.tz);
+    float3 r  = make_float3(VA(VA(v.x, VM(P.qw, uv.x)), c.x), VA(VA(v.y, VM(P.qw, uv.y)), c.y),
+                            VA(VA(v.z, VM(P.qw, uv.z)), c.z));
+    return make_float3(VA(r.x, P.tx), VA(r.y, P.ty), VA(r.z, P.tz));
 }
 
 __device__ __forceinline__ void rotation_matrix(const Pose& P, float R[9])
@@ -66,10 +74,11 @@ __device__ __forceinline__ void rotation_matrix(const Pose& P, float R[9])
 template <bool kJacobians>
 __device__ __forceinline__ float2 distort(float2 p, const float* d, float cutoff, float* J_p, float* J_d)
 {
+    // the value path is STRICT (it decides pixels); the Jacobians are not
     float x = p.x, y = p.y;
-    float x2 = x * x, y2 = y * y, xy = x * y;
-    float r2 = x2 + y2;
-    if (r2 > cutoff * cutoff)
+    float x2 = VM(x, x), y2 = VM(y, y), xy = VM(x, y);
+    float r2 = VA(x2, y2);
+    if (r2 > VM(cutoff, cutoff))
     {
         if (kJacobians)
         {
@@ -78,14 +87,14 @@ __device__ __forceinline__ float2 distort(float2 p, const float* d, float cutoff
         }
         return make_float2(100000.f, 100000.f);
     }
-    float r4 = r2 * r2, r6 = r4 * r2;
+    float r4 = VM(r2, r2), r6 = VM(r4, r2);
     float k1 = d[0], k2 = d[1], k3 = d[2], k4 = d[3], k5 = d[4], k6 = d[5], p1 = d[6], p2 = d[7];
-    float num    = 1.f + k1 * r2 + k2 * r4 + k3 * r6;
-    float den    = 1.f + k4 * r2 + k5 * r4 + k6 * r6;
+    float num    = VA(VA(VA(1.f, VM(k1, r2)), VM(k2, r4)), VM(k3, r6));
+    float den    = VA(VA(VA(1.f, VM(k4, r2)), VM(k5, r4)), VM(k6, r6));
     float radial = num / den;
-    float tx     = 2.f * p1 * xy + p2 * (r2 + 2.f * x2);
-    float ty     = 2.f * p2 * xy + p1 * (r2 + 2.f * y2);
-    float2 out   = make_float2(x * radial + tx, y * radial + ty);
+    float tx     = VA(VM(VM(2.f, p1), xy), VM(p2, VA(r2, VM(2.f, x2))));
+    float ty     = VA(VM(VM(2.f, p2), xy), VM(p1, VA(r2, VM(2.f, y2))));
+    float2 out   = make_float2(VA(VM(x, radial), tx), VA(VM(y, radial), ty));
     if (kJacobians)
     {
         float dnum_dr2 = k1 + 2.f * k2 * r2 + 3.f * k3 * r4;
@@ -108,10 +117,10 @@ __device__ __forceinline__ float2 distort(float2 p, const float* d, float cutoff
     return out;
 }
 
-// IntrinsicsPinhole::normalizedToImage, coefficient order fx fy cx cy s.
+// STRICT.  IntrinsicsPinhole::normalizedToImage, coefficient order fx fy cx cy s.
 __device__ __forceinline__ float2 k_apply(const float* K, float2 p)
 {
-    return make_float2(K[0] * p.x + K[4] * p.y + K[2], K[1] * p.y + K[3]);
+    return make_float2(VA(VA(VM(K[0], p.x), VM(K[4], p.y)), K[2]), VA(VM(K[1], p.y), K[3]));
 }
 
 struct Projected
@@ -121,20 +130,30 @@ struct Projected
     float radius_px;  // drop-out radius in level-0 pixels
 };
 
-// ProjPoint (RenderForward.cu:117-158, pinhole branch) over ProjectPointPinhole (PointRendererHelper.h:184-218).
+// STRICT.  ProjPoint (RenderForward.cu:117-158, pinhole branch) over ProjectPointPinhole (PointRendererHelper.h:184-218).
 __device__ __forceinline__ Projected project_point(const float4 pos, const Camera& cam, float dist_cutoff)
 {
     float3 vp = transform_point(cam.V, make_float3(pos.x, pos.y, pos.z));
     float z   = fmaxf(vp.z, 0.f);
     float2 np = make_float2(vp.x / vp.z, vp.y / vp.z);
-    float2 dp = distort<false>(np, cam.dist, dist_cutoff, nullptr, nullptr);
-    if (dp.x == 100000.f) z = 0.f;
+    float2 dp = np;
+    if (cam.has_dist)
+    {
+        dp = distort<false>(np, cam.dist, dist_cutoff, nullptr, nullptr);
+        if (dp.x == 100000.f) z = 0.f;
+    }
+    else
+    {
+        // all coefficients zero: the model returns its input bit for bit (radial = 1, tangential = 0); only the
+        // cutoff test remains
+        if (VA(VM(np.x, np.x), VM(np.y, np.y)) > VM(dist_cutoff, dist_cutoff)) z = 0.f;
+    }
     float2 ip       = k_apply(cam.K, dp);
-    float radius_px = cam.K[0] * cam.crop[0] * pos.w / z;
+    float radius_px = VM(VM(cam.K[0], cam.crop[0]), pos.w) / z;
     ip              = k_apply(cam.crop, ip);
-    float dx = ip.x - cam.cx, dy = ip.y - cam.cy;
-    ip = make_float2(cam.rot[0] * dx + cam.rot[1] * dy, cam.rot[2] * dx + cam.rot[3] * dy);
-    ip = make_float2(ip.x + cam.cx, ip.y + cam.cy);
+    float dx = VS(ip.x, cam.cx), dy = VS(ip.y, cam.cy);
+    ip = make_float2(VA(VM(cam.rot[0], dx), VM(cam.rot[1], dy)), VA(VM(cam.rot[2], dx), VM(cam.rot[3], dy)));
+    ip = make_float2(VA(ip.x, cam.cx), VA(ip.y, cam.cy));
     Projected r;
     r.ip        = ip;
     r.z         = z;
@@ -153,27 +172,27 @@ __device__ __forceinline__ int round_down(float v)  // __float2int_rd
     return __float2int_rd(v);
 }
 
-// compute_blending_fac, PointBlending.h:12-44: weight of corner `bi` (= 2*y_j + x_i) and its row of J_uv.
+// STRICT.  compute_blending_fac, PointBlending.h:12-44: weight of corner `bi` (= 2*y_j + x_i) and its row of J_uv.
 __device__ __forceinline__ float blending_fac(float2 uv, int bi, float* Jx, float* Jy)
 {
-    float sx = uv.x - floorf(uv.x), sy = uv.y - floorf(uv.y);
+    float sx = VS(uv.x, floorf(uv.x)), sy = VS(uv.y, floorf(uv.y));
     float w, jx, jy;
     if (bi == 0)
-        w = (1 - sx) * (1 - sy), jx = sy - 1, jy = sx - 1;
+        w = VM(VS(1.f, sx), VS(1.f, sy)), jx = sy - 1, jy = sx - 1;
     else if (bi == 1)
-        w = sx * (1 - sy), jx = 1 - sy, jy = -sx;
+        w = VM(sx, VS(1.f, sy)), jx = 1 - sy, jy = -sx;
     else if (bi == 2)
-        w = (1 - sx) * sy, jx = -sy, jy = 1 - sx;
+        w = VM(VS(1.f, sx), sy), jx = -sy, jy = 1 - sx;
     else
-        w = sx * sy, jx = sy, jy = sx;
+        w = VM(sx, sy), jx = sy, jy = sx;
     if (Jx) *Jx = jx;
     if (Jy) *Jy = jy;
     return w;
 }
 
 // compute_blend / compute_new_alphadest, PointBlending.h:90-129.
-__device__ __forceinline__ float vetr_blend(float T, float a, float c, float dst) { return __fmaf_rn(T * a, c, dst); }
-__device__ __forceinline__ float vetr_new_T(float T, float a) { return (1 - a) * T; }
+__device__ __forceinline__ float vetr_blend(float T, float a, float c, float dst) { return __fmaf_rn(VM(T, a), c, dst); }
+__device__ __forceinline__ float vetr_new_T(float T, float a) { return VM(VS(1.f, a), T); }
 
 struct BackOut
 {
@@ -186,8 +205,7 @@ __device__ __forceinline__ bool project_backward(const float4 pos, float2 grad, 
 {
     float3 vp = transform_point(cam.V, make_float3(pos.x, pos.y, pos.z));
     if (!(vp.z > 0)) return false;
-    float R[9];
-    rotation_matrix(cam.V, R);
+    const float* R = cam.R;
     float iz = 1.f / vp.z;
     float2 np = make_float2(vp.x / vp.z, vp.y / vp.z);
     float Jpd[4] = {1.f, 0.f, 0.f, 1.f}, Jdd[16];

@@ -121,6 +121,8 @@ class Rasterizer:
         w, h = views[0].w, views[0].h
         sizes = level_sizes(w, h, Ln)
         P = int(lib.vetr_pyramid_pixels(w, h, Ln))
+        if P <= 0:
+            raise L.VetrError(L.E_INVALID_ARG, "vetr_pyramid_pixels")
         f32 = dict(dtype=torch.float32, device=self.device)
         color = [torch.empty(B, Cn, hh, ww, **f32) for (ww, hh) in sizes]
         weight = [torch.empty(B, 1, hh, ww, **f32) for (ww, hh) in sizes] if want_weight else None
