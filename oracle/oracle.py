@@ -51,6 +51,11 @@ def lib():
         _LIB.vo_pixels_per_view.restype = C.c_int64
         _LIB.vo_pixels_per_view.argtypes = [C.c_void_p]
         _LIB.vo_set_abs_mode.argtypes = [C.c_void_p, C.c_int]
+        _LIB.vo_blend.restype = C.c_float
+        _LIB.vo_blend.argtypes = [C.c_float] * 4 + [C.c_int]
+        _LIB.vo_new_T.restype = C.c_float
+        _LIB.vo_new_T.argtypes = [C.c_float] * 2
+        _LIB.vo_blending_fac.argtypes = [C.c_float, C.c_float, C.c_void_p, C.c_void_p]
     return _LIB
 
 

@@ -794,6 +794,13 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
     return 0;
 }
 
+// The blend algebra on its own, for the comparison with the reference's PointBlending.h (compiled separately).
+// vo_blend evaluates the colour step without the fused multiply-add (as a CPU build of the reference does) when
+// `fused` is 0, and with it (as the CUDA build of the reference and this library do) when `fused` is 1.
+float vo_blend(float T, float a, float c, float dst, int fused) { return fused ? blend(T, a, c, dst) : T * a * c + dst; }
+float vo_new_T(float T, float a) { return new_T(T, a); }
+void vo_blending_fac(float u, float v, float* w4, float* J8) { blending_fac({u, v}, w4, J8); }
+
 // Magnitude shadow: with `on`, vo_backward accumulates |addend| instead of addend into every gradient sum (counts
 // are unchanged).  The result bounds the rounding noise an fp32 sum of the same addends can carry in any order.
 void vo_set_abs_mode(void* h, int on) { ((Oracle*)h)->abs_mode = on != 0; }

@@ -1,0 +1,70 @@
+"""The C ABI without a GPU: the library loads, exports every function include/vetr.h declares, and its host-only entry
+points behave.  No kernel is launched here."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from vet_b200 import _lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "vetr.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(vetr_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported():
+    names = declared_functions()
+    assert len(names) >= 15
+    lib = L.lib()
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+    assert sorted(L.EXPORTS) == [n for n in names], "vet_b200._lib.EXPORTS is out of step with include/vetr.h"
+
+
+def test_host_only_entry_points():
+    lib = L.lib()
+    assert lib.vetr_pyramid_pixels(1920, 1080, 4) == 1920 * 1080 + 960 * 540 + 480 * 270 + 240 * 135
+    assert lib.vetr_pyramid_pixels(5, 3, 2) == 15 + 2
+    assert lib.vetr_pyramid_pixels(0, 3, 2) == -1 and lib.vetr_pyramid_pixels(4, 4, 6) == -1
+    p = L.Params(render_mode=1, num_layers=4)
+    assert lib.vetr_max_fragments(1000, 3, C.byref(p)) == 12000
+    p.render_mode = 3
+    assert lib.vetr_max_fragments(1000, 3, C.byref(p)) == 48000
+    assert lib.vetr_item_table_entries(0, 0) >= 2
+    assert lib.vetr_item_table_entries(10**6, 10**6) > (10**6 + 4 * 10**6) // 1024
+    assert lib.vetr_strerror(0) == b"ok"
+    assert b"buffer" in lib.vetr_strerror(L.E_LIST_OVERFLOW)
+    assert lib.vetr_launch_count(None) == 0
+
+
+def test_struct_sizes_match_the_header():
+    # include/vetr.h: 16 four-byte fields; 5 ints + 9 floats; pointers + ints
+    assert C.sizeof(L.Params) == 64
+    assert C.sizeof(L.View) == 56
+    assert C.sizeof(L.Cloud) == 24 and C.sizeof(L.Texture) == 32 and C.sizeof(L.Cameras) == 24
+    assert C.sizeof(L.Lists) == 56
+
+
+def test_create_without_gpu_reports_cuda_error():
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    ctx = C.c_void_p()
+    assert L.lib().vetr_create(C.byref(ctx), 0, None) == L.E_CUDA
+    assert not ctx.value
+
+
+def test_host_mirror_refuses_to_run_without_cuda():
+    import torch
+    from vet_b200.render import Rasterizer
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        Rasterizer(0)
