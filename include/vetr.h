@@ -102,15 +102,19 @@ typedef struct vetr_cameras
  * Per-pixel fragment lists of one forward call: what the reference keeps in LayerCuda::counting /
  * scanned_counting / per_image_atomic_counters and in collections[b][l] (PointRenderer.h:66-110,
  * PointRenderer.cu:796-822).  All views and levels live in ONE pixel space of n_views * P entries
- * (P = pyramid pixels of a view; view-major, then level, then row-major) and ONE key buffer.
+ * (P = pyramid pixels of a view; view-major, then level, then row-major) and ONE fragment buffer.
  * Caller-owned device memory.
  */
 typedef struct vetr_lists
 {
     int32_t*  counts;   /* [n_views*P]  list length per pixel */
-    int32_t*  ends;     /* [n_views*P]  end offset (exclusive) of the pixel's list in keys; its start is ends - counts */
-    uint64_t* keys;     /* [capacity]   depth bits << 32 | point index, ascending inside each list after forward */
-    int64_t   capacity; /* entries of keys */
+    int32_t*  ends;     /* [n_views*P]  end offset (exclusive) of the pixel's list in frags; its start is ends - counts */
+    void*     frags;    /* [capacity] 32-byte fragment records, 32-byte aligned; ascending by key inside each list
+                           after forward.  Record: uint64 key = depth bits << 32 | point index; float alpha
+                           (confidence, or bilinear weight x confidence in mode 3); int32 descriptor index; float[4]
+                           descriptor.  Everything the blend needs of a fragment sits in one 32-byte sector, so the
+                           blend and the backward pass stream it instead of gathering through index -> descriptor. */
+    int64_t   capacity; /* records in frags */
     int32_t*  status;   /* [4] device words: {total fragments F, overflow flag, longest list, number of work items} */
     int32_t*  items;    /* [items_capacity] work-item table written by the scan: first pixel of every run of pixels that
                            one thread block of the blend / backward kernels processes (balanced by fragments) */

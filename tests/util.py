@@ -44,7 +44,7 @@ def run_gpu(rast, scene, params: dict, grads=None, dropout=None, capacity=None):
     keys_parts = []
     for g, e in zip(groups, ends):
         n = int(e[-1]) if e.size else 0
-        keys_parts.append(g[2].keys[:n].cpu().numpy().view(np.uint64))
+        keys_parts.append(g[2].frags[:n, 0].cpu().numpy().view(np.uint64))  # first 8 bytes of a record = key
     keys = np.concatenate(keys_parts) if keys_parts else np.zeros(0, np.uint64)
     out = dict(fwd={k: (None if v is None else [t.cpu().numpy() for t in v]) for k, v in fwd.items()}, counts=counts,
                keys=keys, F=F, longest=longest)

@@ -45,7 +45,7 @@ class Cameras(C.Structure):
 
 
 class Lists(C.Structure):
-    _fields_ = [("counts", C.c_void_p), ("ends", C.c_void_p), ("keys", C.c_void_p), ("capacity", C.c_int64),
+    _fields_ = [("counts", C.c_void_p), ("ends", C.c_void_p), ("frags", C.c_void_p), ("capacity", C.c_int64),
                 ("status", C.c_void_p), ("items", C.c_void_p), ("items_capacity", C.c_int64)]
 
 

@@ -40,10 +40,10 @@ namespace vetr
 #    define VETR_QUANTUM 512
 #endif
 #ifndef VETR_LONG_LIST
-#    define VETR_LONG_LIST 1024
+#    define VETR_LONG_LIST 512
 #endif
 #ifndef VETR_MIN_CTAS
-#    define VETR_MIN_CTAS 5
+#    define VETR_MIN_CTAS 6
 #endif
 constexpr int kThreads    = VETR_ITEM_THREADS;  // CTA size of the item kernels
 constexpr int kQuantum    = VETR_QUANTUM;       // units of work per item
@@ -85,11 +85,23 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
     const float* dropout;
     int* counts;
     int* ends;
-    unsigned long long* keys;
+    uint4* recs;  // 32-byte fragment records: [2i] = {point index, depth bits, alpha bits, descriptor index}, [2i+1] = descriptor
     long long capacity;
     int* status;      // {F, overflow, longest, number of work items}
     int* item_start;  // [n_items + 1]
 };
+
+// One fragment record = one 32-byte sector.
+__device__ __forceinline__ void store_record(const Frame& f, int slot, unsigned long long key, float alpha, int tex, float4 d)
+{
+    f.recs[2 * (size_t)slot]     = make_uint4((unsigned)key, (unsigned)(key >> 32), __float_as_uint(alpha), (unsigned)tex);
+    f.recs[2 * (size_t)slot + 1] = make_uint4(__float_as_uint(d.x), __float_as_uint(d.y), __float_as_uint(d.z), __float_as_uint(d.w));
+}
+__device__ __forceinline__ unsigned long long record_key(uint4 h) { return ((unsigned long long)h.y << 32) | h.x; }
+__device__ __forceinline__ float4 as_float4(uint4 v)
+{
+    return make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+}
 
 __device__ __forceinline__ Camera load_camera(const Frame& f, int b)
 {
@@ -154,6 +166,20 @@ __global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_cons
         float2 ip     = pr.ip;
         float radius  = pr.radius_px;
         const unsigned long long key = ((unsigned long long)__float_as_uint(pr.z) << 32) | (unsigned)pid;
+        // collection also stores what the blend needs of the point next to every key (coalesced loads here, one
+        // per point, instead of a dependent gather per fragment later)
+        int tex      = 0;
+        float conf   = 0.f;
+        float4 desc  = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (kCollect && !(f.drop_by_radius && radius < f.radius_threshold))
+        {
+            tex    = __ldg(f.index + pid);
+            conf   = __ldg(f.confidence + tex);
+            desc.x = __ldg(f.texture + tex);
+            desc.y = __ldg(f.texture + (size_t)f.n_tex + tex);
+            desc.z = __ldg(f.texture + 2 * (size_t)f.n_tex + tex);
+            desc.w = f.C > 3 ? __ldg(f.texture + 3 * (size_t)f.n_tex + tex) : 0.f;
+        }
 #pragma unroll 1
         for (int l = 0; l < f.L; ++l, radius *= 0.5f, ip.x *= 0.5f, ip.y *= 0.5f)
         {
@@ -170,7 +196,7 @@ __global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_cons
                 else
                 {
                     const int slot = atomicAdd(f.ends + g, 1);
-                    if ((unsigned long long)slot < (unsigned long long)f.capacity) f.keys[slot] = key;
+                    if ((unsigned long long)slot < (unsigned long long)f.capacity) store_record(f, slot, key, conf, tex, desc);
                 }
             }
             else
@@ -189,7 +215,8 @@ __global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_cons
                     else
                     {
                         const int slot = atomicAdd(f.ends + g, 1);
-                        if ((unsigned long long)slot < (unsigned long long)f.capacity) f.keys[slot] = key;
+                        if ((unsigned long long)slot < (unsigned long long)f.capacity)
+                            store_record(f, slot, key, blending_fac(ip, cidx, nullptr, nullptr) * conf, tex, desc);  // RenderForward.cu:1619
                     }
                 }
             }
@@ -361,10 +388,12 @@ __device__ __forceinline__ PixInfo decode_pixel(const Frame& f, unsigned g)
 
 __device__ __forceinline__ int list_end(const Frame& f, int g) { return g < 0 ? 0 : f.ends[g]; }
 
-// In-place ascending sort of a list in global memory by the whole CTA (lists longer than kLongList).  Sorting
-// network with all comparators pointing the same way, so that positions >= n behave as +infinity without padding.
-__device__ void sort_long_list(unsigned long long* keys, int n)
+// In-place ascending sort of a list (keys with their payload) in global memory by the whole CTA, for lists longer
+// than kLongList.  Sorting network with all comparators pointing the same way, so that positions >= n behave as
+// +infinity without padding.
+__device__ void sort_long_list(const Frame& f, int first, int n)
 {
+    uint4* recs = f.recs + 2 * (size_t)first;
     int n2 = 1;
     while (n2 < n) n2 <<= 1;
     for (int k = 2; k <= n2; k <<= 1)
@@ -376,8 +405,13 @@ __device__ void sort_long_list(unsigned long long* keys, int n)
                 int partner = (j == (k >> 1)) ? (i ^ (k - 1)) : (i ^ j);
                 if (partner > i && partner < n)
                 {
-                    unsigned long long a = keys[i], b = keys[partner];
-                    if (a > b) keys[i] = b, keys[partner] = a;
+                    uint4 a = recs[2 * i], b = recs[2 * partner];
+                    if (record_key(a) > record_key(b))
+                    {
+                        recs[2 * i] = b, recs[2 * partner] = a;
+                        uint4 da = recs[2 * i + 1], db = recs[2 * partner + 1];
+                        recs[2 * i + 1] = db, recs[2 * partner + 1] = da;
+                    }
                 }
             }
             __syncthreads();
@@ -386,8 +420,8 @@ __device__ void sort_long_list(unsigned long long* keys, int n)
 }
 
 // Mode 3: level-space image position of a point and the bilinear corner a pixel is of it.  The reference stores
-// both per fragment (per_point_data, RenderForward.cu:1116-1127); recomputing them with the same arithmetic gives
-// the same bits and saves 16 bytes per fragment of HBM traffic in each direction.
+// both per fragment (per_point_data, RenderForward.cu:1116-1127); the backward pass recomputes them with the same
+// arithmetic, which gives the same bits.
 __device__ __forceinline__ float2 level_position(const Frame& f, const Camera& cam, int pid, int level, float4* pos_out)
 {
     float4 pos   = __ldg(f.position + pid);
@@ -403,26 +437,34 @@ __device__ __forceinline__ int corner_of(float2 ip, const PixInfo& px)
     return min(max((px.y - by) * 2 + (px.x - bx), 0), 3);
 }
 
-// Alpha of a fragment: confidence (mode 1) or bilinear corner weight x confidence (mode 3).
-__device__ __forceinline__ float fragment_alpha(const Frame& f, const Camera& cam, const PixInfo& px, int pid, int tex)
+// Which list a staged fragment belongs to.  The thread that owns a pixel writes its index over the pixel's slots when
+// the list is short; the few long lists of an item are recorded separately and matched by range.  (A binary search
+// per fragment costs more instructions than everything else the sort does for it.)
+constexpr int kFillMax  = 32;
+constexpr int kMaxLong  = kCap / kFillMax + 1;
+struct SegTable
 {
-    float a = __ldg(f.confidence + tex);
-    if (f.mode == VETR_MODE_BILINEAR_BLEND)
+    unsigned char seg_of[kCap];
+    unsigned char long_pix[kMaxLong];
+    int n_long[2];  // alternating between consecutive items, so that the reset never races with a fill
+};
+__device__ __forceinline__ void seg_fill(SegTable& t, int parity, int pixel, int ss, int se)
+{
+    if (se - ss <= kFillMax)
+        for (int k = ss; k < se; ++k) t.seg_of[k] = (unsigned char)pixel;
+    else
+        t.long_pix[atomicAdd(&t.n_long[parity], 1)] = (unsigned char)pixel;
+}
+__device__ __forceinline__ int seg_lookup(const SegTable& t, int parity, const int* seg_end, int i)
+{
+    int a = t.seg_of[i];
+    const int nl = t.n_long[parity];
+    for (int k = 0; k < nl; ++k)
     {
-        float2 ip = level_position(f, cam, pid, px.level, nullptr);
-        a         = blending_fac(ip, corner_of(ip, px), nullptr, nullptr) * a;
+        const int p = t.long_pix[k];
+        if (i >= seg_end[p] && i < seg_end[p + 1]) a = p;
     }
     return a;
-}
-
-__device__ __forceinline__ float4 load_descriptor(const Frame& f, int tex)
-{
-    float4 d;
-    d.x = __ldg(f.texture + tex);
-    d.y = __ldg(f.texture + (size_t)f.n_tex + tex);
-    d.z = __ldg(f.texture + 2 * (size_t)f.n_tex + tex);
-    d.w = f.C > 3 ? __ldg(f.texture + 3 * (size_t)f.n_tex + tex) : 0.f;
-    return d;
 }
 
 // First pixel of an item that the item kernels leave to the long-list kernels (0 or 1 pixels).
@@ -443,31 +485,54 @@ __device__ __forceinline__ void write_pixel(const Frame& f, const OutPtrs& out, 
                                             float depth)
 {
     const int w = f.lw[px.level], h = f.lh[px.level];
-    const size_t hw = (size_t)w * h;
-    const size_t o  = (size_t)px.y * w + px.x;
-    float* col      = out.color[px.level] + (size_t)px.view * f.C * hw + o;
+    const int hw = w * h;
+    const int o  = px.y * w + px.x;
+    float* col   = out.color[px.level] + (px.view * f.C) * hw + o;
     for (int ci = 0; ci < f.C; ++ci) col[ci * hw] = c[ci];
-    if (out.weight[0]) out.weight[px.level][(size_t)px.view * hw + o] = T;
-    if (out.mask[0]) out.mask[px.level][(size_t)px.view * hw + o] = (T == 0.f) ? f.mask_value : 1.f;
-    if (out.depth[0]) out.depth[px.level][(size_t)px.view * hw + o] = depth;
+    if (out.weight[0]) out.weight[px.level][px.view * hw + o] = T;
+    if (out.mask[0]) out.mask[px.level][px.view * hw + o] = (T == 0.f) ? f.mask_value : 1.f;
+    if (out.depth[0]) out.depth[px.level][px.view * hw + o] = depth;
 }
+
+// Front-to-back fold of one list (BlendMulti / BlendMultiBilinear, RenderForward.cu:1320-1356, 1597-1639).
+struct Fold
+{
+    float T;
+    float c[4];
+    __device__ __forceinline__ void init()
+    {
+        T    = 1.f;
+        c[0] = c[1] = c[2] = c[3] = 0.f;
+    }
+    __device__ __forceinline__ void add(float a, float4 d)
+    {
+        c[0] = vetr_blend(T, a, d.x, c[0]);
+        c[1] = vetr_blend(T, a, d.y, c[1]);
+        c[2] = vetr_blend(T, a, d.z, c[2]);
+        c[3] = vetr_blend(T, a, d.w, c[3]);
+        T    = vetr_new_T(T, a);
+    }
+    __device__ __forceinline__ void background(const Frame& f)
+    {
+        const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+        if (!f.use_env && !(bilinear && !(T >= 0.001f)))
+            for (int ci = 0; ci < f.C; ++ci) c[ci] = vetr_blend(T, 1.f, f.background[ci], c[ci]);
+    }
+};
 
 // ---------------------------------------------------------------------------------------------------------
 // Pass 4: sort + blend.
 
 struct BlendSmem
 {
-    unsigned long long sorted[kCap];
-    union
-    {
-        unsigned long long unsorted[kCap];
-        float4 desc[kCap];
-    };
+    unsigned long long key[kCap];  // arrival order
+    float4 desc[kCap];
     float alpha[kCap];
-    int seg_end[2][kMaxPixels + 1];  // per-pixel arrays are double buffered: the next item fills the other half
-    PixInfo pix[2][kMaxPixels];      // while slow warps still fold the current one
-    unsigned char seg_of[kCap];
-    Camera cam[VETR_MAX_VIEWS];
+    int tex[kCap];
+    unsigned short perm[kCap];     // sorted position -> arrival slot
+    int seg_end[kMaxPixels + 1];
+    PixInfo pix[kMaxPixels];
+    SegTable seg;
 };
 
 __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __grid_constant__ Frame f,
@@ -478,8 +543,8 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
     const int tid     = threadIdx.x;
     const int n_items = f.status[3];
     const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
-    if (tid < f.n_views) s.cam[tid] = load_camera(f, tid);
-    int buf = 0;
+    if (tid == 0) s.seg.n_long[0] = s.seg.n_long[1] = 0;
+    int parity = 0;
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x)
     {
@@ -488,82 +553,65 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
         if (lo >= hi) continue;
         lo += long_prefix(f, lo);
         if (lo >= hi) continue;
-        buf ^= 1;
-        int* seg_end       = s.seg_end[buf];
-        PixInfo* pix       = s.pix[buf];
+        __syncthreads();  // every warp has left the previous item
+        parity ^= 1;
+        if (tid == 0) s.seg.n_long[parity ^ 1] = 0;
         const int f0 = list_end(f, lo - 1);
         const int np = hi - lo;
+        const int nf = f.ends[hi - 1] - f0;
         if (tid < np)
         {
-            seg_end[tid + 1] = f.ends[lo + tid] - f0;
-            pix[tid]         = decode_pixel(f, (unsigned)(lo + tid));
+            const int ss = list_end(f, lo + tid - 1) - f0, se = f.ends[lo + tid] - f0;
+            s.seg_end[tid + 1] = se;
+            s.pix[tid]         = decode_pixel(f, (unsigned)(lo + tid));
+            seg_fill(s.seg, parity, tid, ss, se);
         }
-        if (tid == 0) seg_end[0] = 0;
-        __syncthreads();  // (a) per-pixel arrays ready; every warp has left the previous item's fold
-        const int nf = seg_end[np];
-        for (int i = tid; i < nf; i += kThreads) s.unsorted[i] = f.keys[f0 + i];
-        __syncthreads();  // (b)
+        if (tid == 0) s.seg_end[0] = 0;
+        // stream keys and payload of the item (contiguous, coalesced)
+        for (int i = tid; i < nf; i += kThreads)
+        {
+            const uint4 h = f.recs[2 * (size_t)(f0 + i)];
+            s.desc[i]     = as_float4(f.recs[2 * (size_t)(f0 + i) + 1]);
+            s.key[i]      = record_key(h);
+            s.alpha[i]    = __uint_as_float(h.z);
+            s.tex[i]      = (int)h.w;
+        }
+        __syncthreads();
         // rank sort inside each list; keys are unique (distinct point indices), so ranks are a permutation
         for (int i = tid; i < nf; i += kThreads)
         {
-            int a = 0;  // largest a < np with seg_end[a] <= i
-#pragma unroll
-            for (int step = kMaxPixels / 2; step > 0; step >>= 1)
-            {
-                const int m = a + step;
-                if (m < np && seg_end[m] <= i) a = m;
-            }
-            const int ss = seg_end[a], se = seg_end[a + 1];
-            const unsigned long long key = s.unsorted[i];
+            const int a  = seg_lookup(s.seg, parity, s.seg_end, i);
+            const int ss = s.seg_end[a], se = s.seg_end[a + 1];
+            const unsigned long long key = s.key[i];
             int rank = 0;
-            for (int k = ss; k < se; ++k) rank += s.unsorted[k] < key;
-            s.sorted[ss + rank] = key;
-            s.seg_of[i]         = (unsigned char)a;  // slot i belongs to list a before and after sorting
+            for (int k = ss; k < se; ++k) rank += s.key[k] < key;
+            s.perm[ss + rank] = (unsigned short)i;
         }
-        __syncthreads();  // (c)
-        // write back + gather (independent iterations: the loads of several fragments are in flight together)
-        for (int i = tid; i < nf; i += kThreads)
-        {
-            const unsigned long long key = s.sorted[i];
-            if (f.keep_sorted) f.keys[f0 + i] = key;
-            const int pid = (int)(unsigned)key;
-            const int tex = __ldg(f.index + pid);
-            float a;
-            if (bilinear)
+        __syncthreads();
+        // write the sorted lists back for the backward pass
+        if (f.keep_sorted)
+            for (int r = tid; r < nf; r += kThreads)
             {
-                const PixInfo px = pix[s.seg_of[i]];
-                a                = fragment_alpha(f, s.cam[px.view], px, pid, tex);
+                const int u = s.perm[r];
+                store_record(f, f0 + r, s.key[u], s.alpha[u], s.tex[u], s.desc[u]);
             }
-            else
-                a = __ldg(f.confidence + tex);
-            s.alpha[i] = a;
-            s.desc[i]  = load_descriptor(f, tex);  // overwrites `unsorted`, dead since barrier (c)
-        }
-        __syncthreads();  // (d)
         // fold: one thread per pixel
         if (tid < np)
         {
-            const int ss = seg_end[tid], se = seg_end[tid + 1];
+            const int ss = s.seg_end[tid], se = s.seg_end[tid + 1];
             int cnt = se - ss;
             if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
-            float T    = 1.f;
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int i = ss; i < ss + cnt; ++i)
+            Fold fold;
+            fold.init();
+            for (int r = ss; r < ss + cnt; ++r)
             {
-                float a  = s.alpha[i];
-                float4 d = s.desc[i];
-                c[0] = vetr_blend(T, a, d.x, c[0]);
-                c[1] = vetr_blend(T, a, d.y, c[1]);
-                c[2] = vetr_blend(T, a, d.z, c[2]);
-                c[3] = vetr_blend(T, a, d.w, c[3]);
-                T    = vetr_new_T(T, a);
-                if (bilinear && T < 0.001f) break;
+                const int u = s.perm[r];
+                fold.add(s.alpha[u], s.desc[u]);
+                if (bilinear && fold.T < 0.001f) break;
             }
-            bool add_bg = !f.use_env && !(bilinear && !(T >= 0.001f));
-            if (add_bg)
-                for (int ci = 0; ci < f.C; ++ci) c[ci] = vetr_blend(T, 1.f, f.background[ci], c[ci]);
-            float depth = se > ss ? __uint_as_float((unsigned)(s.sorted[ss] >> 32)) : kMaxDepth;
-            write_pixel(f, out, pix[tid], c, T, depth);
+            fold.background(f);
+            float depth = se > ss ? __uint_as_float((unsigned)(s.key[s.perm[ss]] >> 32)) : kMaxDepth;
+            write_pixel(f, out, s.pix[tid], fold.c, fold.T, depth);
         }
     }
 }
@@ -586,9 +634,8 @@ __global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_
         const int e0 = list_end(f, lo - 1);
         const int n  = f.ends[lo] - e0;
         __syncthreads();
-        sort_long_list(f.keys + e0, n);
+        sort_long_list(f, e0, n);
         const PixInfo px = decode_pixel(f, (unsigned)lo);
-        if (tid == 0) s.cam[0] = load_camera(f, px.view);
         int cnt = n;
         if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
         if (tid == 0)
@@ -603,44 +650,36 @@ __global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_
             const int m = min(kCap, cnt - blk);
             for (int i = tid; i < m; i += kThreads)
             {
-                const int pid = (int)(unsigned)f.keys[e0 + blk + i];
-                const int tex = __ldg(f.index + pid);
-                s.alpha[i]    = fragment_alpha(f, s.cam[0], px, pid, tex);
-                s.desc[i]     = load_descriptor(f, tex);
+                s.alpha[i] = __uint_as_float(f.recs[2 * (size_t)(e0 + blk + i)].z);
+                s.desc[i]  = as_float4(f.recs[2 * (size_t)(e0 + blk + i) + 1]);
             }
             __syncthreads();
             if (tid == 0 && s_fold[5] == 0.f)
             {
-                float T    = s_fold[0];
-                float c[4] = {s_fold[1], s_fold[2], s_fold[3], s_fold[4]};
+                Fold fold;
+                fold.T = s_fold[0];
+                for (int k = 0; k < 4; ++k) fold.c[k] = s_fold[1 + k];
                 for (int i = 0; i < m; ++i)
                 {
-                    float a  = s.alpha[i];
-                    float4 d = s.desc[i];
-                    c[0] = vetr_blend(T, a, d.x, c[0]);
-                    c[1] = vetr_blend(T, a, d.y, c[1]);
-                    c[2] = vetr_blend(T, a, d.z, c[2]);
-                    c[3] = vetr_blend(T, a, d.w, c[3]);
-                    T    = vetr_new_T(T, a);
-                    if (bilinear && T < 0.001f)
+                    fold.add(s.alpha[i], s.desc[i]);
+                    if (bilinear && fold.T < 0.001f)
                     {
                         s_fold[5] = 1.f;
                         break;
                     }
                 }
-                s_fold[0] = T;
-                s_fold[1] = c[0], s_fold[2] = c[1], s_fold[3] = c[2], s_fold[4] = c[3];
+                s_fold[0] = fold.T;
+                for (int k = 0; k < 4; ++k) s_fold[1 + k] = fold.c[k];
             }
             __syncthreads();
         }
         if (tid == 0)
         {
-            float T     = s_fold[0];
-            float c[4]  = {s_fold[1], s_fold[2], s_fold[3], s_fold[4]};
-            bool add_bg = !f.use_env && !(bilinear && !(T >= 0.001f));
-            if (add_bg)
-                for (int ci = 0; ci < f.C; ++ci) c[ci] = vetr_blend(T, 1.f, f.background[ci], c[ci]);
-            write_pixel(f, out, px, c, T, __uint_as_float((unsigned)(f.keys[e0] >> 32)));
+            Fold fold;
+            fold.T = s_fold[0];
+            for (int k = 0; k < 4; ++k) fold.c[k] = s_fold[1 + k];
+            fold.background(f);
+            write_pixel(f, out, px, fold.c, fold.T, __uint_as_float(f.recs[2 * (size_t)e0].y));
         }
     }
 }
@@ -669,12 +708,11 @@ struct BackSmem
     float alpha[kCap];
     float dot[kCap];     // d_i . G  ->  replaced by the alpha gradient of the fragment
     float trans[kCap];   // T_i ; NaN = fragment not blended (early termination / list truncation)
-    float2 dR[kCap];     // mode 1: image-space gradient of the fragment's position; x = NaN: none
-    unsigned char seg_of[kCap];
-    float4 grad[2][kMaxPixels];      // incoming gradient of the pixel; per-pixel arrays are double buffered
-    int seg_end[2][kMaxPixels + 1];
-    PixInfo pix[2][kMaxPixels];
-    double red[kThreads / 32][8];    // cross-warp reduction scratch
+    float4 grad[kMaxPixels];  // incoming gradient of the pixel
+    int seg_end[kMaxPixels + 1];
+    PixInfo pix[kMaxPixels];
+    SegTable seg;
+    double red[kThreads / 32][8];  // cross-warp reduction scratch
     Camera cam[VETR_MAX_VIEWS];
 };
 
@@ -781,6 +819,8 @@ __device__ __forceinline__ void spatial_backward(const Frame& f, const BackPtrs&
 }
 
 // Mode 1: approximate image-space gradient of a fragment from the neighbouring pixels (RenderBackward.cu:1347-1374).
+// (Staging the neighbour values once per pixel in shared memory was measured slower: it serialises 36 loads in the
+// few threads that own pixels and costs occupancy; the per-fragment loads below hit L1.)
 __device__ __forceinline__ float2 neighbour_gradient(const Frame& f, const BackPtrs& bp, const PixInfo& px, float4 d)
 {
     const int w = f.lw[px.level], h = f.lh[px.level];
@@ -839,37 +879,37 @@ __device__ __forceinline__ float dot4(float4 a, float4 b, int C)
     return r;
 }
 
-// Stage A of a fragment (needs nothing from the sweeps, issues no atomics): gathers, d.G, and in mode 1 the
-// image-space gradient dR of the fragment's position.
+// Stage A of a fragment (needs nothing from the sweeps): streams the fragment's key and payload, computes d.G, and
+// in mode 1 its whole spatial gradient (which depends on the descriptor and the neighbouring pixels only).
+template <bool kIntr>
 __device__ __forceinline__ void fragment_stage_a(const Frame& f, const BackPtrs& bp, BackSmem& s, const Camera& cam,
-                                                 const PixInfo& px, float4 G, int slot, int pid, bool blended)
+                                                 const PixInfo& px, float4 G, int slot, int gslot, bool blended,
+                                                 CamAcc<kIntr>& acc)
 {
-    const int tex = __ldg(f.index + pid);
-    s.pid[slot]   = pid;
-    s.tex[slot]   = tex;
-    s.alpha[slot] = fragment_alpha(f, cam, px, pid, tex);
-    const float4 d = load_descriptor(f, tex);
+    const uint4 h  = f.recs[2 * (size_t)gslot];
+    const float4 d = as_float4(f.recs[2 * (size_t)gslot + 1]);
+    const int pid  = (int)h.x;
+    s.pid[slot]    = pid;
+    s.tex[slot]    = (int)h.w;
+    s.alpha[slot]  = __uint_as_float(h.z);
     s.dot[slot]    = dot4(d, G, f.C);
-    if (f.mode != VETR_MODE_BILINEAR_BLEND)
+    if (f.mode != VETR_MODE_BILINEAR_BLEND && blended && f.need_point_grad && is_interior(f, px))
     {
-        float2 dR = make_float2(__int_as_float(0x7fffffff), 0.f);
-        if (blended && f.need_point_grad && is_interior(f, px)) dR = neighbour_gradient(f, bp, px, d);
-        s.dR[slot] = dR;
+        const float4 pos = __ldg(f.position + pid);
+        spatial_backward<kIntr>(f, bp, cam, px, pid, pos, neighbour_gradient(f, bp, px, d), acc);
     }
 }
 
-// Stage B of a fragment (after the sweeps): every gradient the fragment contributes to.
+// Stage B of a fragment (after the sweeps): descriptor and confidence gradients, and in mode 3 the spatial gradient.
 template <bool kIntr>
 __device__ __forceinline__ void fragment_stage_b(const Frame& f, const BackPtrs& bp, const Camera& cam, const PixInfo& px,
-                                                 float4 G, int pid, int tex, float Ta, float galpha, float2 dR,
-                                                 CamAcc<kIntr>& acc)
+                                                 float4 G, int pid, int tex, float Ta, float galpha, CamAcc<kIntr>& acc)
 {
     // descriptor gradient: T * alpha * G  (RenderBackward.cu:1149-1152)
     red_add_v4(bp.g_desc + tex, make_float4(Ta * G.x, Ta * G.y, Ta * G.z, f.C > 3 ? Ta * G.w : 0.f));
     if (f.mode != VETR_MODE_BILINEAR_BLEND)
     {
         red_add(bp.g_conf + tex, galpha);
-        if (dR.x == dR.x) spatial_backward<kIntr>(f, bp, cam, px, pid, __ldg(f.position + pid), dR, acc);
         return;
     }
     if (!is_interior(f, px)) return;  // the reference writes the mode-3 confidence gradient for interior pixels only
@@ -954,15 +994,15 @@ __device__ __forceinline__ void reduce_background(const Frame& f, const BackPtrs
 
 #ifdef VETR_PHASE_TIMING
 __device__ unsigned long long g_phase_cycles[8];
-#    define PHASE_MARK(k)                                            \
-        do                                                           \
-        {                                                            \
-            if (threadIdx.x == 0)                                    \
-            {                                                        \
-                long long now_ = clock64();                          \
-                atomicAdd(&g_phase_cycles[k], (unsigned long long)(now_ - t_phase_)); \
-                t_phase_ = now_;                                     \
-            }                                                        \
+#    define PHASE_MARK(k)                                                                 \
+        do                                                                                \
+        {                                                                                 \
+            if (threadIdx.x == 0)                                                         \
+            {                                                                             \
+                long long now_ = clock64();                                               \
+                atomicAdd(&g_phase_cycles[k], (unsigned long long)(now_ - t_phase_));     \
+                t_phase_ = now_;                                                          \
+            }                                                                             \
         } while (0)
 #else
 #    define PHASE_MARK(k)
@@ -986,7 +1026,8 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) backward_kernel(const __gr
     float p0_acc    = 0.f;
     const int P     = (int)f.P;
     const bool want_cam = bp.g_pose != nullptr || kIntr;
-    int buf = 0;
+    if (tid == 0) s.seg.n_long[0] = s.seg.n_long[1] = 0;
+    int parity = 0;
 #ifdef VETR_PHASE_TIMING
     long long t_phase_ = clock64();
 #endif
@@ -1007,54 +1048,45 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) backward_kernel(const __gr
                 if (acc_view >= 0 && want_cam) reduce_cam<kIntr>(f, bp, acc, acc_view, s);
                 acc_view = view;
             }
-            buf ^= 1;
-            int* seg_end  = s.seg_end[buf];
-            PixInfo* pix  = s.pix[buf];
-            float4* grad  = s.grad[buf];
+            __syncthreads();  // every warp has left the previous run (and the cameras are loaded)
+            PHASE_MARK(0);
+            parity ^= 1;
+            if (tid == 0) s.seg.n_long[parity ^ 1] = 0;
             const int f0 = list_end(f, lo - 1);
             const int np = hi - lo;
             if (tid < np)
             {
-                seg_end[tid + 1] = f.ends[lo + tid] - f0;
-                const PixInfo px = decode_pixel(f, (unsigned)(lo + tid));
-                pix[tid]         = px;
-                grad[tid]        = load_grad(f, bp, px);
+                const int ss = list_end(f, lo + tid - 1) - f0, se = f.ends[lo + tid] - f0;
+                s.seg_end[tid + 1] = se;
+                const PixInfo px   = decode_pixel(f, (unsigned)(lo + tid));
+                s.pix[tid]         = px;
+                s.grad[tid]        = load_grad(f, bp, px);
+                seg_fill(s.seg, parity, tid, ss, se);
             }
-            if (tid == 0) seg_end[0] = 0;
-            PHASE_MARK(0);
-            __syncthreads();  // (a) per-pixel arrays ready; every warp has left stage B of the previous run
+            if (tid == 0) s.seg_end[0] = 0;
+            __syncthreads();
             PHASE_MARK(1);
             const Camera& cam = s.cam[view];
-            const int nf = seg_end[np];
+            const int nf = s.seg_end[np];
             for (int i = tid; i < nf; i += kThreads)
             {
-                int a = 0;  // largest a < np with seg_end[a] <= i
-#pragma unroll
-                for (int step = kMaxPixels / 2; step > 0; step >>= 1)
-                {
-                    const int m = a + step;
-                    if (m < np && seg_end[m] <= i) a = m;
-                }
-                s.seg_of[i] = (unsigned char)a;
-                const bool blended = f.dbg_max_len <= 0 || i - seg_end[a] < f.dbg_max_len;  // list truncation
-                fragment_stage_a(f, bp, s, cam, pix[a], grad[a], i, (int)(unsigned)f.keys[f0 + i], blended);
+                const int a = seg_lookup(s.seg, parity, s.seg_end, i);
+                const bool blended = f.dbg_max_len <= 0 || i - s.seg_end[a] < f.dbg_max_len;  // list truncation
+                fragment_stage_a<kIntr>(f, bp, s, cam, s.pix[a], s.grad[a], i, f0 + i, blended, acc);
             }
+            __syncthreads();
             PHASE_MARK(2);
-            __syncthreads();  // (b)
+            if (tid < np) sweep_list(f, s, s.seg_end[tid], s.seg_end[tid + 1], s.grad[tid], bgc, bg_acc, p0_acc);
+            __syncthreads();
             PHASE_MARK(3);
-            if (tid < np) sweep_list(f, s, seg_end[tid], seg_end[tid + 1], grad[tid], bgc, bg_acc, p0_acc);
-            PHASE_MARK(4);
-            __syncthreads();  // (c)
-            PHASE_MARK(5);
             for (int i = tid; i < nf; i += kThreads)
             {
                 const float Ti = s.trans[i];
                 if (Ti != Ti) continue;
-                const int a = s.seg_of[i];
-                fragment_stage_b<kIntr>(f, bp, cam, pix[a], grad[a], s.pid[i], s.tex[i], Ti * s.alpha[i], s.dot[i], s.dR[i],
-                                        acc);
+                const int a = seg_lookup(s.seg, parity, s.seg_end, i);
+                fragment_stage_b<kIntr>(f, bp, cam, s.pix[a], s.grad[a], s.pid[i], s.tex[i], Ti * s.alpha[i], s.dot[i], acc);
             }
-            PHASE_MARK(6);
+            PHASE_MARK(4);
             lo = hi;
         }
     }
@@ -1103,11 +1135,7 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
         for (int blk = 0; blk < n_blocks; ++blk)
         {
             const int m = min(kCap, cnt - blk * kCap);
-            for (int i = tid; i < m; i += kThreads)
-            {
-                const int pid = (int)(unsigned)f.keys[e0 + blk * kCap + i];
-                s.alpha[i]    = fragment_alpha(f, cam, px, pid, __ldg(f.index + pid));
-            }
+            for (int i = tid; i < m; i += kThreads) s.alpha[i] = __uint_as_float(f.recs[2 * (size_t)(e0 + blk * kCap + i)].z);
             __syncthreads();
             if (tid == 0)
             {
@@ -1146,7 +1174,7 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
         {
             const int m = min(kCap, eff_cnt - blk * kCap);
             for (int i = tid; i < m; i += kThreads)
-                fragment_stage_a(f, bp, s, cam, px, G, i, (int)(unsigned)f.keys[e0 + blk * kCap + i], true);
+                fragment_stage_a<kIntr>(f, bp, s, cam, px, G, i, e0 + blk * kCap + i, true, acc);
             __syncthreads();
             if (tid == 0)
             {
@@ -1167,7 +1195,7 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
             }
             __syncthreads();
             for (int i = tid; i < m; i += kThreads)
-                fragment_stage_b<kIntr>(f, bp, cam, px, G, s.pid[i], s.tex[i], s.trans[i] * s.alpha[i], s.dot[i], s.dR[i], acc);
+                fragment_stage_b<kIntr>(f, bp, cam, px, G, s.pid[i], s.tex[i], s.trans[i] * s.alpha[i], s.dot[i], acc);
             __syncthreads();
         }
         if (bp.g_pose != nullptr || kIntr) reduce_cam<kIntr>(f, bp, acc, px.view, s);
@@ -1485,7 +1513,9 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
         !tex->background || !cams->poses_se3 || !cams->intrinsics)
         return VETR_E_INVALID_ARG;
     if (((uintptr_t)cloud->position & 15) != 0) return VETR_E_INVALID_ARG;
-    if (!lists->counts || !lists->ends || !lists->keys || !lists->status || lists->capacity < 0) return VETR_E_INVALID_ARG;
+    if (!lists->counts || !lists->ends || !lists->frags || !lists->status || lists->capacity < 0 ||
+        ((uintptr_t)lists->frags & 31) != 0)
+        return VETR_E_INVALID_ARG;
     memset(&f, 0, sizeof(f));
     f.n_views = n_views, f.L = p->num_layers, f.C = p->num_channels, f.n = cloud->n, f.n_tex = tex->n_tex;
     f.w = views[0].w, f.h = views[0].h;
@@ -1514,7 +1544,7 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     f.position = (const float4*)cloud->position, f.index = cloud->index;
     f.texture = tex->texture, f.confidence = tex->confidence, f.background = tex->background;
     f.poses = cams->poses_se3, f.intr = cams->intrinsics;
-    f.counts = lists->counts, f.ends = lists->ends, f.keys = (unsigned long long*)lists->keys;
+    f.counts = lists->counts, f.ends = lists->ends, f.recs = (uint4*)lists->frags;
     f.capacity = lists->capacity, f.status = lists->status;
     long long n_tiles = (f.PT + kScanTile - 1) / kScanTile;
     if (!lists->items || lists->items_capacity < vetr_item_table_entries(lists->capacity, f.PT)) return VETR_E_INVALID_ARG;
@@ -1669,13 +1699,13 @@ extern "C" int vetr_read_status(vetr_ctx* ctx, const vetr_lists* lists, int64_t*
 
 namespace vetr
 {
-__global__ void unpack_lists_kernel(const unsigned long long* keys, long long first, long long n, int* out)
+__global__ void unpack_lists_kernel(const uint4* recs, long long first, long long n, int* out)
 {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    unsigned long long k = keys[first + i];
-    out[i]     = (int)(unsigned)(k >> 32);
-    out[n + i] = (int)(unsigned)k;
+    uint4 h    = recs[2 * (first + i)];
+    out[i]     = (int)h.y;
+    out[n + i] = (int)h.x;
 }
 __global__ void local_offsets_kernel(const int* ends, const int* counts, long long g0, long long npix, long long first, int* out)
 {
@@ -1711,7 +1741,7 @@ extern "C" int vetr_get_lists(vetr_ctx* ctx, const vetr_lists* lists, int w, int
     long long n     = (long long)last_end - first;
     if (n_fragments) *n_fragments = n;
     if (out_collections && n > 0)
-        unpack_lists_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>((const unsigned long long*)lists->keys, first, n,
+        unpack_lists_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>((const uint4*)lists->frags, first, n,
                                                                                    out_collections);
     if (out_scanned_counting)
         local_offsets_kernel<<<(unsigned)((npix + 255) / 256), 256, 0, ctx->stream>>>(lists->ends, lists->counts, g0, npix, first,

@@ -55,11 +55,11 @@ class FragmentLists:
         self.capacity = int(capacity)
         self.counts = torch.empty(n_pixels_total, **i32)
         self.ends = torch.empty(n_pixels_total, **i32)
-        self.keys = torch.empty(max(self.capacity, 1), dtype=torch.int64, device=device)
+        self.frags = torch.empty(max(self.capacity, 1), 4, dtype=torch.int64, device=device)  # 32-byte records
         self.status = torch.zeros(4, **i32)
         n_items = int(L.lib().vetr_item_table_entries(self.capacity, n_pixels_total))
         self.items = torch.empty(n_items, **i32)
-        self.c = L.Lists(self.counts.data_ptr(), self.ends.data_ptr(), self.keys.data_ptr(), self.capacity,
+        self.c = L.Lists(self.counts.data_ptr(), self.ends.data_ptr(), self.frags.data_ptr(), self.capacity,
                          self.status.data_ptr(), self.items.data_ptr(), n_items)
 
 
