@@ -230,15 +230,22 @@ def run_ours(args):
                  pose_count=torch.zeros(poses.shape[0], device=dev))
         return g
 
+    grad_bufs = [torch.empty(V, CHANNELS, h, w, device=dev) for (w, h) in sizes]
+    diff_bufs = [torch.empty(V, CHANNELS, h, w, device=dev) for (w, h) in sizes]
+
     def step(targets):
         flat.zero_()
         out = rast.forward(position, index, texture, confidence, background, poses, intrinsics, my_views, params,
                            want_weight=True)
+        # L1 loss against the target pyramid and its gradient sign(out - target) / numel (torch element-wise kernels on
+        # preallocated buffers: plumbing around the path, not part of it)
         grads, loss = [], None
         for l, (c, t) in enumerate(zip(out["color"], targets)):
-            d = c - t
-            grads.append(torch.sign(d) / numel[l])
-            term = d.abs().sum() / numel[l]
+            d = torch.sub(c, t, out=diff_bufs[l])
+            g = torch.sign(d, out=grad_bufs[l])
+            g.mul_(1.0 / numel[l])
+            grads.append(g)
+            term = d.abs_().sum() / numel[l]
             loss = term if loss is None else loss + term
         g = rast.backward_raw(grads, want_intrinsics=False, accum=grad_views())
         if world > 1:
@@ -270,13 +277,17 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t_begin = time.perf_counter()
+    step_events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     e0.record(stream)
-    for _ in range(args.steps):
+    step_events[0].record(stream)
+    for i in range(args.steps):
         loss, fin = step(targets_dev)
+        step_events[i + 1].record(stream)
     e1.record(stream)
     barrier()
     t_end = time.perf_counter()
     ms = e0.elapsed_time(e1)
+    step_ms = [step_events[i].elapsed_time(step_events[i + 1]) for i in range(args.steps)]
     launches = rast.launch_count() - launches0
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -359,15 +370,15 @@ def run_ours(args):
     dominant = max(kernels, key=lambda k: kernels[k]["ms"])
     whole_bytes = sum(kernel_bytes.values()) + 4 * flat.numel()  # + zero fill of the gradient buffer
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": kernels[dominant]["gbs"], "peak": peak, "unit": "GB/s",
-                "frac": (kernels[dominant]["gbs"] or 0.0) / peak, "traffic": TRAFFIC_BYTES_PER_FRAGMENT.get(dominant),
+                "frac": (kernels[dominant]["gbs"] or 0.0) / peak,
+                "traffic": (TRAFFIC_OVER_ALGORITHMIC[dominant] * kernel_bytes[dominant]
+                            if dominant in TRAFFIC_OVER_ALGORITHMIC else None),
                 "peak_source": peak_src, "kernels": kernels,
                 "whole_step": {"algorithmic_bytes": whole_bytes,
                                "achieved_gbs": whole_bytes * args.steps / (ms_total * 1e-3) / 1e9,
                                "frac": whole_bytes * args.steps / (ms_total * 1e-3) / 1e9 / peak},
                 "counts": {"N": N, "N_touched": touched, "F": F, "pixels": PT, "views_per_launch": V,
                            "longest_list": longest}}
-    if roofline["traffic"] is not None:
-        roofline["traffic"] = roofline["traffic"] * F
 
     # ---- CPU baseline on the host cores (rank 0, N = 1 only)
     cpu = None
@@ -388,16 +399,24 @@ def run_ours(args):
                        "views_per_gpu": V, "points": N, "l2": "inputs larger than L2 (cloud 128 MB + descriptors 160 MB + "
                                                               "pyramids; gradient buffer 288 MB rewritten every step)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
-            "loss": float(loss.item()),
+            "loss": float(loss.item()), "step_ms": [round(x, 3) for x in step_ms],
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-# DRAM bytes per fragment of each kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum divided by
-# the fragments of the captured launch; see profiles/).  None = not captured yet.
-TRAFFIC_BYTES_PER_FRAGMENT = {}
+# DRAM traffic of each kernel relative to its algorithmic bytes, from the ncu captures summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch of a small case: 2 M points, 1 view, 3.32 M fragments,
+# divided by the algorithmic bytes of that launch).  The full-size workload is too large to capture with --set full;
+# traffic is taken to grow in proportion to the algorithmic bytes.
+TRAFFIC_OVER_ALGORITHMIC = {
+    "backward": (308.475e6 + 49.129e6) / 310.5e6,
+    "sort_blend": (117.499e6 + 105.804e6) / 185.6e6,
+    "count": 42.537e6 / 43.0e6,
+    # the collection pass writes the whole 32-byte record (key + what the blend gathers), not only the 8-byte key
+    "collect": (91.797e6 + 83.952e6) / 58.6e6,
+}
 
 
 def main():

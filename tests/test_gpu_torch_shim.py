@@ -1,0 +1,100 @@
+"""The C++/libtorch operator surface (vet_b200/torch_shim: BlendPointCloud / PointRender autograd function) against the
+oracle, through torch autograd: what the reference's pipeline would see."""
+import os
+
+import numpy as np
+import pytest
+
+from tests import util
+from vet_b200 import scenes
+from vet_b200.render import default_params
+
+pytestmark = pytest.mark.gpu
+SHIM = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "vet_b200", "libvetr_torch.so")
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import torch
+
+    assert os.path.exists(SHIM), "build it with: python -m vet_b200.build --shim"
+    torch.ops.load_library(SHIM)
+    return torch.ops.vetr
+
+
+def _views(sc, dev):
+    import torch
+
+    vi = torch.tensor([[v.w, v.h, v.image_index, v.camera_index, v.camera_model] for v in sc.views], dtype=torch.int32)
+    vf = torch.tensor([list(v.crop) + list(v.rot) for v in sc.views], dtype=torch.float32)
+    return vi, vf
+
+
+@pytest.mark.parametrize("mode", [1, 3])
+def test_blend_point_cloud_forward_backward(ops, mode):
+    import torch
+
+    dev = torch.device("cuda", 0)
+    sc = scenes.tiny_scene(n=3000, n_views=3, seed=17, crop=True)
+    params = default_params(render_mode=mode)
+    ora = util.run_oracle(sc, params)
+    grads = util.random_grads(ora["fwd"]["color"], seed=8)
+    ora = util.run_oracle(sc, params, grads=grads)
+
+    t = lambda a, rg=False: torch.from_numpy(a).to(dev).requires_grad_(rg)
+    texture, background = t(sc.texture, True), t(sc.background, True)
+    position, confidence = t(sc.position, True), t(sc.confidence[None], True)
+    tangent = torch.zeros(sc.poses.shape[0], 6, dtype=torch.float64, device=dev, requires_grad=True)
+    intr = t(sc.intrinsics, True)
+    vi, vf = _views(sc, dev)
+    out = ops.blend_point_cloud(texture, background, position, t(sc.index[:, None]), t(sc.poses), tangent, intr, confidence,
+                                vi, vf, 4, mode, True, True, True, False, True)
+    assert len(out) == 12  # colour, depth, mask per level (RenderInfo.cpp:40-42 order)
+    for l in range(4):
+        np.testing.assert_array_equal(out[l].detach().cpu().numpy(), ora["fwd"]["color"][l])
+        np.testing.assert_array_equal(out[4 + l].detach().cpu().numpy(), ora["fwd"]["depth"][l])
+        np.testing.assert_array_equal(out[8 + l].detach().cpu().numpy(), ora["fwd"]["mask"][l])
+    loss = sum((o * torch.from_numpy(g).to(dev)).sum() for o, g in zip(out[:4], grads))
+    loss.backward()
+    b, m = ora["bwd"], ora["bwd_mag"]
+    util.assert_sum_close("texture.grad", texture.grad.cpu().numpy(), b["texture"], m["texture"])
+    util.assert_sum_close("confidence.grad", confidence.grad.cpu().numpy()[0], b["confidence"], m["confidence"])
+    util.assert_sum_close("background.grad", background.grad.cpu().numpy(), b["background"], m["background"])
+    cnt = np.maximum(b["points_count"], 1)[:, None]
+    util.assert_sum_close("points.grad", position.grad.cpu().numpy()[:, :3], b["points"] / cnt, m["points"] / cnt)
+    assert float(position.grad[:, 3].abs().max()) == 0.0
+    pc = np.where(b["pose_count"] > 0, b["pose_count"], 1)[:, None]
+    util.assert_sum_close("tangent.grad", tangent.grad.cpu().numpy(), b["pose"] / pc, m["pose"] / pc)
+    ic = np.where(b["intrinsics_count"] > 0, b["intrinsics_count"], 1)[:, None]
+    util.assert_sum_close("intrinsics.grad", intr.grad.cpu().numpy(), b["intrinsics"] / ic, m["intrinsics"] / ic)
+
+
+def test_undefined_gradients_for_inputs_without_grad(ops):
+    """PointRenderer.cu:272-300: no gradient tensors for inputs that do not require one."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    sc = scenes.tiny_scene(n=1000, n_views=1, seed=19)
+    t = lambda a, rg=False: torch.from_numpy(a).to(dev).requires_grad_(rg)
+    texture = t(sc.texture, True)
+    position, tangent, intr = t(sc.position), torch.zeros(1, 6, dtype=torch.float64, device=dev), t(sc.intrinsics)
+    vi, vf = _views(sc, dev)
+    out = ops.blend_point_cloud(texture, t(sc.background), position, t(sc.index[:, None]), t(sc.poses), tangent, intr,
+                                t(sc.confidence[None]), vi, vf, 4, 1, False, False, True, False, True)
+    assert len(out) == 4
+    sum(o.sum() for o in out).backward()
+    assert texture.grad is not None and position.grad is None and tangent.grad is None and intr.grad is None
+
+
+def test_apply_tangent_to_pose(ops):
+    import torch
+    from oracle import oracle as O
+
+    rng = np.random.default_rng(2)
+    poses = scenes.orbit_poses(rng, 4, 3.0)
+    tangent = rng.normal(scale=0.05, size=(4, 6))
+    p_ref, t_ref = poses.copy(), tangent.copy()
+    O.apply_tangent(t_ref, p_ref)
+    p, tg = torch.from_numpy(poses).cuda(), torch.from_numpy(tangent).cuda()
+    ops.apply_tangent_to_pose(tg, p)
+    np.testing.assert_allclose(p.cpu().numpy(), p_ref, atol=1e-12)

@@ -35,5 +35,32 @@ def build(force: bool = False, verbose: bool = False, defines=(), out: str = LIB
     return out
 
 
+SHIM_PATH = os.path.join(_HERE, "libvetr_torch.so")
+SHIM_SOURCES = [os.path.join(_HERE, "torch_shim", "vetr_torch.cpp")]
+SHIM_HEADERS = [os.path.join(_HERE, "torch_shim", "vetr_torch.h"), os.path.join(_HERE, "..", "include", "vetr.h")]
+
+
+def build_torch_shim(force: bool = False) -> str:
+    """Builds libvetr_torch.so: the C++/libtorch operator surface (host code only, g++) on top of libvetr.so."""
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    build()
+    if not force and os.path.exists(SHIM_PATH):
+        t = os.path.getmtime(SHIM_PATH)
+        if all(os.path.getmtime(p) <= t for p in SHIM_SOURCES + SHIM_HEADERS + [LIB_PATH]):
+            return SHIM_PATH
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["/usr/bin/g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-D_GLIBCXX_USE_CXX11_ABI=" + str(int(torch._C._GLIBCXX_USE_CXX11_ABI))]
+    for inc in ce.include_paths("cuda"):
+        cmd += ["-isystem", inc]
+    cmd += SHIM_SOURCES + ["-o", SHIM_PATH, "-L" + _HERE, "-lvetr", "-L" + torch_lib, "-ltorch", "-ltorch_cpu", "-lc10",
+                           "-ltorch_cuda", "-lc10_cuda", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
+    subprocess.check_call(cmd)
+    return SHIM_PATH
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--shim" in sys.argv:
+        print(build_torch_shim(force="--force" in sys.argv))

@@ -1,0 +1,353 @@
+// See vetr_torch.h.  Sequencing follows BlendPointCloudForward / BlendPointCloudBackward
+// (rendering/PointRenderer.cu:657-1069, 1111-1323); all arithmetic happens behind the C ABI.
+#include "vetr_torch.h"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <stdexcept>
+#include <string>
+
+namespace vetr_torch
+{
+namespace
+{
+void check(int status, const char* where)
+{
+    if (status != VETR_OK) throw std::runtime_error(std::string(where) + ": " + vetr_strerror(status));
+}
+
+vetr_params make_params(const NeuralRenderInfo& info)
+{
+    const RenderParams& p = info.params;
+    if (p.check_normal) throw std::runtime_error("vetr: check_normal is not supported");
+    vetr_params q{};
+    q.render_mode                  = p.render_mode;
+    q.num_layers                   = info.num_layers;
+    q.num_channels                 = p.num_texture_channels;
+    q.drop_out_points_by_radius    = p.drop_out_points_by_radius;
+    q.drop_out_radius_threshold    = p.drop_out_radius_threshold;
+    q.dist_cutoff                  = p.dist_cutoff;
+    q.use_environment_map          = p.use_environment_map;
+    q.viewer_only                  = p.viewer_only;
+    q.stability_cutoff_value       = p.stability_cutoff_value;
+    q.debug_max_list_length        = p.debug_max_list_length;
+    q.need_point_gradient          = p.need_point_gradient;
+    q.K_gradient_factor            = p.K_gradient_factor;
+    q.distortion_gradient_factor   = p.distortion_gradient_factor;
+    q.output_background_mask_value = p.output_background_mask_value;
+    q.background_alpha_to_point0   = 1;
+    q.keep_sorted_lists            = 1;
+    return q;
+}
+
+std::vector<vetr_view> make_views(const NeuralRenderInfo& info, int b0, int b1)
+{
+    std::vector<vetr_view> v;
+    for (int b = b0; b < b1; ++b)
+    {
+        const ReducedImageInfo& im = info.images[b];
+        vetr_view x{};
+        x.w = im.w, x.h = im.h, x.image_index = im.image_index, x.camera_index = im.camera_index;
+        x.camera_model = im.camera_model_type;
+        for (int i = 0; i < 5; ++i) x.crop[i] = im.crop_transform[i];
+        for (int i = 0; i < 4; ++i) x.rot[i] = im.crop_rotation[i];
+        v.push_back(x);
+    }
+    return v;
+}
+
+struct Inputs
+{
+    vetr_cloud cloud;
+    vetr_texture tex;
+    vetr_cameras cams;
+    torch::Tensor index, confidence;  // contiguous views kept alive
+};
+
+Inputs make_inputs(const RenderScene& s)
+{
+    TORCH_CHECK(s.t_position.is_cuda() && s.t_position.is_contiguous() && s.t_position.dtype() == torch::kFloat32);
+    TORCH_CHECK(s.texture.is_contiguous() && s.poses_se3.dtype() == torch::kFloat64 && s.poses_se3.is_contiguous());
+    Inputs in;
+    in.index      = s.t_index.reshape({-1}).contiguous();
+    in.confidence = s.confidence_value_of_point.reshape({-1}).contiguous();
+    in.cloud      = {s.t_position.data_ptr<float>(), in.index.data_ptr<int>(), (int)s.t_position.size(0)};
+    in.tex        = {s.texture.data_ptr<float>(), in.confidence.data_ptr<float>(), s.background_color.data_ptr<float>(),
+                     (int)s.texture.size(1)};
+    in.cams       = {s.poses_se3.data_ptr<double>(), s.intrinsics.data_ptr<float>(), (int)s.poses_se3.size(0),
+                     (int)s.intrinsics.size(0)};
+    return in;
+}
+
+struct GroupLists
+{
+    torch::Tensor counts, ends, frags, status, items;
+    vetr_lists c;
+};
+
+GroupLists alloc_lists(int64_t n_pixels, int64_t capacity, const torch::Device& dev)
+{
+    auto i32 = torch::TensorOptions().device(dev).dtype(torch::kInt32);
+    GroupLists g;
+    g.counts = torch::empty({n_pixels}, i32);
+    g.ends   = torch::empty({n_pixels}, i32);
+    g.frags  = torch::empty({std::max<int64_t>(capacity, 1), 4}, i32.dtype(torch::kInt64));
+    g.status = torch::zeros({4}, i32);
+    int64_t n_items = vetr_item_table_entries(capacity, n_pixels);
+    g.items  = torch::empty({n_items}, i32);
+    g.c = {g.counts.data_ptr<int>(), g.ends.data_ptr<int>(), g.frags.data_ptr(), capacity, g.status.data_ptr<int>(),
+           g.items.data_ptr<int>(), n_items};
+    return g;
+}
+
+std::vector<float*> level_ptrs(const std::vector<torch::Tensor>& t, int b0)
+{
+    std::vector<float*> p;
+    for (auto& x : t) p.push_back(x.data_ptr<float>() + (int64_t)b0 * x.stride(0));
+    return p;
+}
+}  // namespace
+
+PointRendererCache::~PointRendererCache()
+{
+    if (ctx_) vetr_destroy(ctx_);
+}
+
+vetr_ctx* PointRendererCache::context(int device)
+{
+    void* stream = (void*)at::cuda::getCurrentCUDAStream(device).stream();
+    if (!ctx_ || device_ != device)
+    {
+        if (ctx_) vetr_destroy(ctx_);
+        check(vetr_create(&ctx_, device, stream), "vetr_create");
+        device_ = device;
+    }
+    check(vetr_set_stream(ctx_, stream), "vetr_set_stream");
+    return ctx_;
+}
+
+std::vector<torch::Tensor> BlendPointCloud(NeuralRenderInfo* info)
+{
+    torch::intrusive_ptr<NeuralRenderInfo> render_data = torch::make_intrusive<NeuralRenderInfo>(*info);
+    TORCH_CHECK(render_data->scene, "BlendPointCloud: no scene");
+    RenderScene& s = *render_data->scene;
+    return torch::autograd::PointRender::apply(s.texture, s.background_color, s.t_position, s.tangent_poses, s.intrinsics,
+                                               s.confidence_value_of_point, s.dynamic_refinement_t,
+                                               torch::IValue(render_data));
+}
+
+void ApplyTangentToPose(torch::Tensor tangent, torch::Tensor pose)
+{
+    TORCH_CHECK(tangent.is_contiguous() && pose.is_contiguous() && tangent.dtype() == torch::kFloat64);
+    c10::cuda::CUDAGuard guard(pose.device());
+    vetr_ctx* ctx = nullptr;
+    check(vetr_create(&ctx, pose.device().index(), (void*)at::cuda::getCurrentCUDAStream().stream()), "vetr_create");
+    int rc = vetr_apply_tangent(ctx, tangent.data_ptr<double>(), pose.data_ptr<double>(), (int)tangent.size(0));
+    vetr_destroy(ctx);
+    check(rc, "vetr_apply_tangent");
+}
+}  // namespace vetr_torch
+
+namespace torch::autograd
+{
+using namespace vetr_torch;
+
+variable_list PointRender::forward(AutogradContext* ctx, Variable texture, Variable background_color, Variable points,
+                                   Variable pose_tangents, Variable intrinsics, Variable confidence,
+                                   Variable dynamic_refinement, IValue info_v)
+{
+    ctx->saved_data["render_info"] = info_v;
+    NeuralRenderInfo* info = info_v.toCustomClass<NeuralRenderInfo>().get();
+    TORCH_CHECK(info->cache, "NeuralRenderInfo::cache is not set");
+    PointRendererCache& cache = *info->cache;
+    RenderScene& s            = *info->scene;
+    const auto dev            = s.t_position.device();
+    c10::cuda::CUDAGuard guard(dev);
+    vetr_ctx* vc = cache.context(dev.index());
+
+    const int B = (int)info->images.size(), L = info->num_layers, C = info->params.num_texture_channels;
+    TORCH_CHECK(B > 0);
+    cache.num_batches = B;
+    cache.render_mode = (PointRendererCache::RenderMode)info->params.render_mode;
+    const vetr_params prm = make_params(*info);
+    Inputs in             = make_inputs(s);
+
+    auto f32 = torch::TensorOptions().device(dev).dtype(torch::kFloat32);
+    std::vector<torch::Tensor> color, weight, depth, mask;
+    cache.layers_cuda.resize(L);
+    int w = info->images.front().w, h = info->images.front().h;
+    for (int l = 0; l < L; ++l, w /= 2, h /= 2)
+    {
+        TORCH_CHECK(w > 0 && h > 0, "pyramid level of size 0");
+        color.push_back(torch::empty({B, C, h, w}, f32));
+        weight.push_back(torch::empty({B, 1, h, w}, f32));
+        depth.push_back(torch::empty({B, 1, h, w}, f32));
+        if (info->params.output_background_mask) mask.push_back(torch::empty({B, 1, h, w}, f32));
+        cache.layers_cuda[l].w = w, cache.layers_cuda[l].h = h;
+        cache.layers_cuda[l].weight = weight.back(), cache.layers_cuda[l].depth = depth.back();
+    }
+
+    // drop-out mask like PointRendererCache::InitializeData (PointRenderer.cu:461-468)
+    torch::Tensor dropout;
+    if (info->params.dropout > 0 && info->train)
+    {
+        dropout = torch::empty({B, s.t_position.size(0)}, f32).bernoulli_(info->params.dropout);
+        cache.dropout_points = dropout;
+    }
+
+    const int64_t P = vetr_pyramid_pixels(info->images.front().w, info->images.front().h, L);
+    std::vector<torch::Tensor> saved = {texture, background_color, points, intrinsics, confidence};
+    for (auto& c : color) saved.push_back(c);
+    int n_groups = 0;
+    for (int b0 = 0; b0 < B; b0 += VETR_MAX_VIEWS, ++n_groups)
+    {
+        const int b1 = std::min(B, b0 + VETR_MAX_VIEWS), nb = b1 - b0;
+        GroupLists g = alloc_lists(P * nb, vetr_max_fragments(in.cloud.n, nb, &prm), dev);
+        auto views   = make_views(*info, b0, b1);
+        auto pc = level_ptrs(color, b0), pw = level_ptrs(weight, b0), pd = level_ptrs(depth, b0), pm = level_ptrs(mask, b0);
+        check(vetr_forward(vc, &prm, &in.cloud, &in.tex, &in.cams, views.data(), nb,
+                           dropout.defined() ? dropout.data_ptr<float>() + (int64_t)b0 * dropout.stride(0) : nullptr, &g.c,
+                           pc.data(), pw.data(), mask.empty() ? nullptr : pm.data(), pd.data()),
+              "vetr_forward");
+        for (auto& t : {g.counts, g.ends, g.frags, g.status, g.items}) saved.push_back(t);
+    }
+    ctx->saved_data["n_groups"] = n_groups;
+    ctx->save_for_backward(saved);
+
+    variable_list out = color;
+    if (info->params.add_depth_to_network) out.insert(out.end(), depth.begin(), depth.end());
+    out.insert(out.end(), mask.begin(), mask.end());
+    return out;
+}
+
+variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_output)
+{
+    IValue info_v          = ctx->saved_data["render_info"];
+    NeuralRenderInfo* info = info_v.toCustomClass<NeuralRenderInfo>().get();
+    PointRendererCache& cache = *info->cache;
+    RenderScene& s            = *info->scene;
+    const auto dev            = s.t_position.device();
+    c10::cuda::CUDAGuard guard(dev);
+    vetr_ctx* vc = cache.context(dev.index());
+    const int B = (int)info->images.size(), L = info->num_layers, C = info->params.num_texture_channels;
+    const vetr_params prm = make_params(*info);
+    Inputs in             = make_inputs(s);
+    auto saved            = ctx->get_saved_variables();
+    const int n_groups    = (int)ctx->saved_data["n_groups"].toInt();
+    TORCH_CHECK((int)saved.size() == 5 + L + 5 * n_groups);
+
+    std::vector<torch::Tensor> color(saved.begin() + 5, saved.begin() + 5 + L), gcolor;
+    for (int l = 0; l < L; ++l)
+    {
+        TORCH_CHECK(grad_output[l].defined() && grad_output[l].dtype() == torch::kFloat32);
+        gcolor.push_back(grad_output[l].contiguous());
+    }
+    const int64_t n = s.t_position.size(0), n_tex = s.texture.size(1);
+    auto f32 = torch::TensorOptions().device(dev).dtype(torch::kFloat32);
+    // accumulation buffers (point-major) and the reference's output tensors
+    torch::Tensor g_desc = torch::zeros({n_tex, 4}, f32), g_conf = torch::zeros({1, n_tex}, f32);
+    torch::Tensor g_background = torch::zeros_like(s.background_color);
+    torch::Tensor g_points, g_pose, g_pose_count, g_intr, g_intr_count;
+    if (s.t_position.requires_grad()) g_points = torch::zeros({n, 4}, f32);
+    if (s.tangent_poses.requires_grad())
+    {
+        g_pose       = torch::zeros_like(s.tangent_poses);
+        g_pose_count = torch::zeros({s.tangent_poses.size(0)}, f32);
+    }
+    if (s.intrinsics.requires_grad())
+    {
+        g_intr       = torch::zeros_like(s.intrinsics);
+        g_intr_count = torch::zeros({s.intrinsics.size(0)}, f32);
+    }
+    for (int gi = 0, b0 = 0; gi < n_groups; ++gi, b0 += VETR_MAX_VIEWS)
+    {
+        const int b1 = std::min(B, b0 + VETR_MAX_VIEWS), nb = b1 - b0;
+        auto* t = &saved[5 + L + 5 * gi];
+        vetr_lists lists = {t[0].data_ptr<int>(), t[1].data_ptr<int>(), t[2].data_ptr(), t[2].size(0), t[3].data_ptr<int>(),
+                            t[4].data_ptr<int>(), t[4].size(0)};
+        auto views = make_views(*info, b0, b1);
+        auto pc = level_ptrs(color, b0), pg = level_ptrs(gcolor, b0);
+        std::vector<const float*> cpc(pc.begin(), pc.end()), cpg(pg.begin(), pg.end());
+        check(vetr_backward(vc, &prm, &in.cloud, &in.tex, &in.cams, views.data(), nb, &lists, cpc.data(), cpg.data(),
+                            g_desc.data_ptr<float>(), g_conf.data_ptr<float>(),
+                            g_points.defined() ? g_points.data_ptr<float>() : nullptr, g_background.data_ptr<float>(),
+                            g_pose.defined() ? g_pose.data_ptr<double>() : nullptr,
+                            g_pose.defined() ? g_pose_count.data_ptr<float>() : nullptr,
+                            g_intr.defined() ? g_intr.data_ptr<float>() : nullptr,
+                            g_intr.defined() ? g_intr_count.data_ptr<float>() : nullptr),
+              "vetr_backward");
+    }
+    torch::Tensor g_texture = torch::empty_like(s.texture);
+    check(vetr_finalize_gradients(vc, C, (int)n_tex, g_desc.data_ptr<float>(), g_texture.data_ptr<float>(), (int)n,
+                                  g_points.defined() ? g_points.data_ptr<float>() : nullptr, nullptr,
+                                  g_pose.defined() ? (int)g_pose.size(0) : 0,
+                                  g_pose.defined() ? g_pose.data_ptr<double>() : nullptr,
+                                  g_pose.defined() ? g_pose_count.data_ptr<float>() : nullptr,
+                                  g_intr.defined() ? (int)g_intr.size(0) : 0,
+                                  g_intr.defined() ? g_intr.data_ptr<float>() : nullptr,
+                                  g_intr.defined() ? g_intr_count.data_ptr<float>() : nullptr),
+          "vetr_finalize_gradients");
+    // order of BlendPointCloudBackward's return (PointRenderer.cu:1319-1322) + one empty gradient for the IValue
+    return {g_texture, g_background, g_points, g_pose, g_intr, g_conf.view_as(s.confidence_value_of_point), Variable(), Variable()};
+}
+}  // namespace torch::autograd
+
+// ---------------------------------------------------------------------------------------------------------
+// Python-visible entry for tests: builds a NeuralRenderInfo from plain arguments and calls BlendPointCloud.
+namespace
+{
+using namespace vetr_torch;
+
+std::vector<torch::Tensor> blend_point_cloud_op(torch::Tensor texture, torch::Tensor background, torch::Tensor position,
+                                                torch::Tensor index, torch::Tensor poses_se3, torch::Tensor tangent_poses,
+                                                torch::Tensor intrinsics, torch::Tensor confidence, torch::Tensor views_i,
+                                                torch::Tensor views_f, int64_t num_layers, int64_t render_mode,
+                                                bool output_mask, bool add_depth, bool drop_by_radius, bool use_env_map,
+                                                bool need_point_gradient)
+{
+    static PointRendererCache cache;  // lives as long as the process, like the reference's render-module member
+    auto scene = std::make_shared<RenderScene>();
+    scene->texture = texture, scene->background_color = background, scene->t_position = position, scene->t_index = index;
+    scene->poses_se3 = poses_se3, scene->tangent_poses = tangent_poses, scene->intrinsics = intrinsics;
+    scene->confidence_value_of_point = confidence;
+    scene->dynamic_refinement_t      = torch::zeros({1}, position.options());
+    NeuralRenderInfo info;
+    info.scene = scene.get();
+    auto vi = views_i.cpu().contiguous();  // [B,5] w h image_index camera_index model
+    auto vf = views_f.cpu().contiguous();  // [B,9] crop(5) rot(4)
+    for (int64_t b = 0; b < vi.size(0); ++b)
+    {
+        ReducedImageInfo im;
+        const int* pi   = vi.data_ptr<int>() + 5 * b;
+        const float* pf = vf.data_ptr<float>() + 9 * b;
+        im.w = pi[0], im.h = pi[1], im.image_index = pi[2], im.camera_index = pi[3], im.camera_model_type = pi[4];
+        for (int i = 0; i < 5; ++i) im.crop_transform[i] = pf[i];
+        for (int i = 0; i < 4; ++i) im.crop_rotation[i] = pf[5 + i];
+        info.images.push_back(im);
+    }
+    info.params.num_texture_channels      = (int)texture.size(0);
+    info.params.render_mode               = (int)render_mode;
+    info.params.dropout                   = 0.f;
+    info.params.output_background_mask    = output_mask;
+    info.params.add_depth_to_network      = add_depth;
+    info.params.drop_out_points_by_radius = drop_by_radius;
+    info.params.use_environment_map       = use_env_map;
+    info.params.need_point_gradient       = need_point_gradient;
+    info.num_layers = (int)num_layers;
+    info.cache      = &cache;
+    // the scene must outlive the autograd graph: keep it in a holder that the returned tensors do not own; tests call
+    // backward before the next forward, so a static slot is enough here
+    static std::shared_ptr<RenderScene> keep;
+    keep       = scene;
+    info.scene = keep.get();
+    return BlendPointCloud(&info);
+}
+}  // namespace
+
+TORCH_LIBRARY(vetr, m)
+{
+    m.class_<vetr_torch::NeuralRenderInfo>("NeuralRenderInfo").def(torch::init());
+    m.def("blend_point_cloud", &blend_point_cloud_op);
+    m.def("apply_tangent_to_pose", &vetr_torch::ApplyTangentToPose);
+}

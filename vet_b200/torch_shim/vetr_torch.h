@@ -1,0 +1,130 @@
+// C++/libtorch host side of the rasterizer: the reference's operator surface on top of the C ABI (include/vetr.h).
+//
+// Mirrors, with the same names, argument order and return layout:
+//   NeuralRenderInfo                      rendering/PointRenderer.h:23-34
+//   torch::autograd::PointRender          rendering/PointRenderer.h:39-47, rendering/RenderInfo.cpp:32-67
+//   BlendPointCloud(NeuralRenderInfo*)    rendering/PointRenderer.h:53,   rendering/RenderInfo.cpp:18-30
+//   ApplyTangentToPose(tangent, pose)     rendering/PointRenderer.h:64,   rendering/PointRenderer.cu:1343-1349
+//   PointRendererCache / LayerCuda        rendering/PointRenderer.h:66-248 (the members outside code reads:
+//                                         layers_cuda[i].weight / .depth, num_batches, render_mode)
+// The reference's NeuralScene / RenderParams / ReducedImageInfo come from parts of VET that need the saiga library;
+// the structs below carry exactly the fields the render operator reads from them, under the same names, so that the
+// reference's call site (models/Pipeline.cpp:133 via RenderModule.cpp:45-245) maps onto them one to one.
+#pragma once
+#include <torch/torch.h>
+
+#include <memory>
+#include <vector>
+
+#include "../../include/vetr.h"
+
+namespace vetr_torch
+{
+// data/SceneData.h:39-50
+struct ReducedImageInfo
+{
+    int w = 0, h = 0;
+    int image_index       = -1;
+    int camera_index      = -1;
+    int camera_model_type = 0;                    // CameraModel::PINHOLE_DISTORTION
+    float crop_transform[5] = {1, 1, 0, 0, 0};    // IntrinsicsPinholef: fx fy cx cy s
+    float crop_rotation[4]  = {1, 0, 0, 1};       // row-major 2x2
+};
+
+// data/Settings.h:19-73 (fields the operator reads)
+struct RenderParams
+{
+    bool check_normal               = false;
+    float dropout                   = 0.25f;
+    float drop_out_radius_threshold = 0.6f;
+    bool drop_out_points_by_radius  = true;
+    float distortion_gradient_factor = 0.005f;
+    float K_gradient_factor          = 0.5f;
+    int num_texture_channels         = 4;
+    float dist_cutoff                = 20.f;
+    bool output_background_mask      = false;
+    float output_background_mask_value = 0.f;
+    bool add_depth_to_network        = false;
+    float stability_cutoff_value     = 10000.f;
+    bool need_point_gradient         = true;
+    bool use_environment_map         = true;
+    int render_mode                  = 1;
+    bool viewer_only                 = false;
+    int debug_max_list_length        = -1;
+};
+
+// The tensors of NeuralScene the operator reads (data/NeuralScene.h:22-121): texture->texture,
+// texture->background_color, texture->confidence_value_of_point, point_cloud_cuda->t_position / t_index,
+// poses->poses_se3 / tangent_poses, intrinsics->intrinsics.
+struct RenderScene
+{
+    torch::Tensor texture;                    // [C,N] f32
+    torch::Tensor background_color;           // [C]
+    torch::Tensor confidence_value_of_point;  // [1,N]
+    torch::Tensor t_position;                 // [N,4]
+    torch::Tensor t_index;                    // [N,1] i32
+    torch::Tensor poses_se3;                  // [n,8] f64
+    torch::Tensor tangent_poses;              // [n,6] f64
+    torch::Tensor intrinsics;                 // [n_cam,13]
+    torch::Tensor dynamic_refinement_t;       // dummy [1] (models/Pipeline.cpp:128)
+};
+
+struct LayerCuda
+{
+    int w = 0, h = 0;
+    torch::Tensor depth;   // [B,1,h,w] nearest depth, 100000 where empty
+    torch::Tensor weight;  // [B,1,h,w] final transmittance
+};
+
+class PointRendererCache
+{
+   public:
+    ~PointRendererCache();
+    enum RenderMode
+    {
+        FUZZY_DT       = 0,
+        FULL_BLEND     = 1,
+        FUZZY_BLEND    = 2,
+        BILINEAR_BLEND = 3,
+    } render_mode = FULL_BLEND;
+    std::vector<LayerCuda> layers_cuda;
+    int num_batches = 0;
+    torch::Tensor dropout_points;  // [B,N] (1 = dropped), kept for inspection like the reference's member
+
+    vetr_ctx* context(int device);  // one C-ABI context per cache, created on first use on the current stream
+
+   private:
+    vetr_ctx* ctx_ = nullptr;
+    int device_    = -1;
+};
+
+class NeuralRenderInfo : public torch::CustomClassHolder
+{
+   public:
+    RenderScene* scene = nullptr;
+    std::vector<ReducedImageInfo> images;
+    RenderParams params;
+    int num_layers    = 4;
+    bool train        = true;
+    int current_epoch = 0;
+    PointRendererCache* cache = nullptr;
+};
+
+// Render the scene into a batch of images; every image is a pyramid of layers.  Returns num_layers colour tensors
+// [B,C,h_l,w_l], then num_layers depth tensors if add_depth_to_network, then num_layers masks [B,1,h_l,w_l] if
+// output_background_mask (rendering/RenderInfo.cpp:40-42, RenderModule.cpp:74-102).
+std::vector<torch::Tensor> BlendPointCloud(NeuralRenderInfo* info);
+
+void ApplyTangentToPose(torch::Tensor tangent, torch::Tensor pose);
+}  // namespace vetr_torch
+
+namespace torch::autograd
+{
+struct PointRender : public Function<PointRender>
+{
+    static variable_list forward(AutogradContext* ctx, Variable texture, Variable background_color, Variable points,
+                                 Variable pose_tangents, Variable intrinsics, Variable confidence,
+                                 Variable dynamic_refinement, IValue info);
+    static variable_list backward(AutogradContext* ctx, variable_list grad_output);
+};
+}  // namespace torch::autograd
