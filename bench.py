@@ -80,12 +80,12 @@ class ClockSampler:
         self.thread = None
 
     def start(self):
-        """Starts sampling (every 50 ms) and waits for the first sample, so that short timed regions are covered."""
+        """Starts sampling (every 200 ms) and waits for the first sample."""
         import threading
 
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "50", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -105,11 +105,11 @@ class ClockSampler:
         """Summary of the samples that arrived while the timed region [t_begin, t_end] ran (all samples if none did)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
-        time.sleep(0.06)
+        time.sleep(0.25)
         self.proc.terminate()
         if self.thread is not None:
             self.thread.join(timeout=5)
-        inside = [l for (t, l) in self.lines if t_begin <= t <= t_end + 0.06]
+        inside = [l for (t, l) in self.lines if t_begin <= t <= t_end + 0.25]
         lines = inside if inside else [l for (_, l) in self.lines]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -197,7 +197,9 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     V = args.views
     params = default_params(render_mode=args.mode, num_layers=LAYERS, num_channels=CHANNELS)
 
@@ -264,11 +266,21 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    # bring the clocks up before the counted warm-up steps (a cold GPU needs a few hundred ms of load to boost)
-    t_pre = time.perf_counter()
-    while time.perf_counter() - t_pre < args.prewarm:
+    # bring the clocks up before the counted warm-up steps (a cold GPU needs a few hundred ms of load to boost).  The
+    # number of these steps is agreed between the ranks: every step holds collectives, so all ranks must run the same count.
+    n_pre = 0
+    if args.prewarm > 0:
         step(targets_dev)
         torch.cuda.synchronize(dev)
+        t_pre = time.perf_counter()
+        step(targets_dev)
+        torch.cuda.synchronize(dev)
+        one = torch.tensor([time.perf_counter() - t_pre], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(one, op=dist.ReduceOp.MAX)
+        n_pre = int(min(500, max(1, args.prewarm / max(float(one.item()), 1e-4))))
+    for _ in range(n_pre):
+        step(targets_dev)
     for _ in range(args.warmup):
         step(targets_dev)
     F_total, longest = rast.fragment_count()
