@@ -192,6 +192,23 @@ int vetr_read_status(vetr_ctx* ctx, const vetr_lists* lists, int64_t* total_frag
 int vetr_get_lists(vetr_ctx* ctx, const vetr_lists* lists, int w, int h, int num_layers, int n_views, int view,
                    int layer, int32_t* out_collections, int32_t* out_scanned_counting, int64_t* n_fragments);
 
+/* The scan of the forward pass (per-pixel counts -> list offsets, total fragment count, longest list, work-item table)
+ * as a call of its own that allocates nothing.  It has no counterpart in the reference; it exists for hosts that cannot
+ * allocate device memory while they render (a frame loop that cannot take the device-wide stall of cudaMalloc, a process
+ * whose device memory was handed out once by an arena, a region where allocation is forbidden).  The scan's scratch, one
+ * partial sum per 4096 pixels, is a fixed 128 KB array inside the library image on every GPU that loads it.
+ *   limit       n_pixels <= 67 108 864 (16384 tiles); more returns VETR_E_TOO_LARGE
+ *   inputs      counts [n_pixels] int32 device array; capacity as in vetr_lists
+ *   outputs     ends [n_pixels] = exclusive scan of counts (the start of every list; vetr_forward's collection pass later
+ *               advances its copy to the list ends); status [4] = {total, overflow flag, longest list, work items};
+ *               items [items_capacity >= vetr_item_table_entries(capacity, n_pixels)]
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and should therefore come before
+ * any stream capture on that device; it is not safe to make that first call from two threads at once.  All calls share
+ * the one array: it is fully rewritten by every call (nothing needs clearing), the status words are zeroed by the call,
+ * and two calls whose kernels overlap on the GPU (different streams, same device) race.  Calls no cudaMalloc / cudaFree. */
+int vetr_scan_counts_static(int device, void* cuda_stream, const int32_t* counts, int64_t n_pixels, int64_t capacity,
+                            int32_t* ends, int32_t* status, int32_t* items, int64_t items_capacity);
+
 /* Measurement hooks (the reference wraps every pass in a CudaTimerSystem scope, e.g. PointRenderer.cu:770,843,872,886).
  * With timing enabled every kernel of vetr_forward / vetr_backward / vetr_finalize_gradients is bracketed by CUDA events
  * on the context's stream.  vetr_get_timings() synchronises and returns the milliseconds of the most recent launch of each

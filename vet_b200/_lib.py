@@ -53,7 +53,7 @@ EXPORTS = [
     "vetr_create", "vetr_destroy", "vetr_set_stream", "vetr_strerror", "vetr_last_cuda_error", "vetr_pyramid_pixels",
     "vetr_item_table_entries", "vetr_max_fragments", "vetr_forward", "vetr_backward", "vetr_finalize_gradients",
     "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists", "vetr_set_timing", "vetr_get_timings",
-    "vetr_launch_count",
+    "vetr_launch_count", "vetr_scan_counts_static",
 ]
 TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize"]
 
@@ -102,5 +102,6 @@ def lib():
         L.vetr_get_timings.argtypes = [vp, C.POINTER(C.c_float)]
         L.vetr_launch_count.argtypes = [vp]
         L.vetr_launch_count.restype = C.c_int64
+        L.vetr_scan_counts_static.argtypes = [C.c_int, vp, vp, C.c_int64, C.c_int64, vp, vp, vp, C.c_int64]
         _lib = L
     return _lib

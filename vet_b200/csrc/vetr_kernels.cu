@@ -1697,6 +1697,49 @@ extern "C" int vetr_read_status(vetr_ctx* ctx, const vetr_lists* lists, int64_t*
     return h[1] ? VETR_E_LIST_OVERFLOW : VETR_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Scan without any allocation.
+//
+// Some hosts must not allocate device memory while they render: an interactive viewer whose frame loop cannot afford
+// the device-wide stall of cudaMalloc / cudaFree, a process whose device memory is handed out once at start-up by an
+// arena it does not own, or code running inside a region where the driver forbids allocation.  For them the scan's
+// only scratch (one partial sum per tile of 4096 pixels) lives in a fixed array inside the library image instead of a
+// buffer grown on demand.  Every GPU that loads the library carries these 128 KB until the process exits.
+namespace vetr
+{
+constexpr int kStaticScanTiles = 16384;  // 16384 tiles x 4096 pixels = 67 108 864 pixels per call
+static __device__ __align__(256) long long g_static_tile_sums[kStaticScanTiles];
+}  // namespace vetr
+static long long* g_static_tile_ptr[64] = {};  // device address of the array above, per device ordinal
+
+extern "C" int vetr_scan_counts_static(int device, void* cuda_stream, const int32_t* counts, int64_t n_pixels,
+                                       int64_t capacity, int32_t* ends, int32_t* status, int32_t* items,
+                                       int64_t items_capacity)
+{
+    if (device < 0 || device >= 64 || !counts || !ends || !status || !items || n_pixels < 1 || capacity < 0)
+        return VETR_E_INVALID_ARG;
+    if (n_pixels > 0x7fffffffLL) return VETR_E_TOO_LARGE;
+    const long long n_tiles = (n_pixels + kScanTile - 1) / kScanTile;
+    if (n_tiles > kStaticScanTiles) return VETR_E_TOO_LARGE;  // more pixels than the fixed scratch covers
+    if (items_capacity < vetr_item_table_entries(capacity, n_pixels)) return VETR_E_INVALID_ARG;
+    if (cudaSetDevice(device) != cudaSuccess) return VETR_E_CUDA;
+    if (!g_static_tile_ptr[device])
+    {
+        // The array's name is only a handle on the host; kernels need its address on THIS device.
+        long long* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, g_static_tile_sums) != cudaSuccess || !p) return VETR_E_CUDA;
+        g_static_tile_ptr[device] = p;
+    }
+    long long* tile_sums = g_static_tile_ptr[device];
+    cudaStream_t st      = (cudaStream_t)cuda_stream;
+    // the status words are accumulated into (longest list is an atomic maximum): start them at zero
+    if (cudaMemsetAsync(status, 0, 4 * sizeof(int), st) != cudaSuccess) return VETR_E_CUDA;
+    scan_tile_sums_kernel<<<(int)n_tiles, 256, 0, st>>>(counts, n_pixels, tile_sums, status);
+    scan_spine_kernel<<<1, 1024, 0, st>>>(tile_sums, (int)n_tiles, n_pixels, capacity, status, items);
+    scan_apply_kernel<<<(int)n_tiles, 256, 0, st>>>(counts, n_pixels, tile_sums, ends, status, items);
+    return cudaGetLastError() == cudaSuccess ? VETR_OK : VETR_E_CUDA;
+}
+
 namespace vetr
 {
 __global__ void unpack_lists_kernel(const uint4* recs, long long first, long long n, int* out)
