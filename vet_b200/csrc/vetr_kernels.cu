@@ -40,10 +40,10 @@ namespace vetr
 #    define VETR_QUANTUM 512
 #endif
 #ifndef VETR_LONG_LIST
-#    define VETR_LONG_LIST 512
+#    define VETR_LONG_LIST 256
 #endif
 #ifndef VETR_MIN_CTAS
-#    define VETR_MIN_CTAS 6
+#    define VETR_MIN_CTAS 8
 #endif
 constexpr int kThreads    = VETR_ITEM_THREADS;  // CTA size of the item kernels
 constexpr int kQuantum    = VETR_QUANTUM;       // units of work per item
@@ -440,7 +440,7 @@ __device__ __forceinline__ int corner_of(float2 ip, const PixInfo& px)
 // Which list a staged fragment belongs to.  The thread that owns a pixel writes its index over the pixel's slots when
 // the list is short; the few long lists of an item are recorded separately and matched by range.  (A binary search
 // per fragment costs more instructions than everything else the sort does for it.)
-constexpr int kFillMax  = 32;
+constexpr int kFillMax  = 128;
 constexpr int kMaxLong  = kCap / kFillMax + 1;
 struct SegTable
 {
