@@ -33,11 +33,13 @@ typedef enum vetr_status
     VETR_E_CUDA           = -2, /* a CUDA runtime call failed; vetr_last_cuda_error() has the code */
     VETR_E_UNSUPPORTED    = -3, /* camera model / option the library does not implement */
     VETR_E_LIST_OVERFLOW  = -4, /* more fragments than the key buffer holds (reported by vetr_read_status) */
-    VETR_E_TOO_LARGE      = -5  /* a size exceeds a fixed limit of the entry point */
+    VETR_E_TOO_LARGE      = -5  /* a size exceeds a fixed limit of the entry point (vetr_read_status: a list longer than
+                                   3072 fragments met the mode-2 backward pass, which skipped that pixel) */
 } vetr_status;
 
-/* Render modes: PointRendererCache::RenderMode, PointRenderer.h (FUZZY_DT = 0 and FUZZY_BLEND = 2 are not built). */
+/* Render modes: PointRendererCache::RenderMode, PointRenderer.h (FUZZY_DT = 0 is not built). */
 #define VETR_MODE_FULL_BLEND 1
+#define VETR_MODE_FUZZY_BLEND 2
 #define VETR_MODE_BILINEAR_BLEND 3
 
 /* The RenderParams fields the kernels read: data/Settings.h:19-73, RenderConstants.h:36-60. */
@@ -60,6 +62,7 @@ typedef struct vetr_params
     int32_t background_alpha_to_point0;/* bool, default 1: the reference adds the background entry's alpha
                                           gradient to descriptor 0's confidence gradient (RenderBackward.cu:1130,1157) */
     int32_t keep_sorted_lists;         /* bool: write the sorted lists back (needed by vetr_backward / vetr_get_lists) */
+    float   depth_accept_blend;        /* 0.01: depth window of a fuzzy group, mode 2 (data/Settings.h:29) */
 } vetr_params;
 
 /* ReducedImageInfo, data/SceneData.h:39-50. */

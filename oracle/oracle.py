@@ -24,7 +24,7 @@ class OParams(C.Structure):
         ("need_point_gradient", C.c_int), ("K_gradient_factor", C.c_float),
         ("distortion_gradient_factor", C.c_float), ("output_background_mask", C.c_int),
         ("output_background_mask_value", C.c_float), ("conf_grad_quadratic", C.c_int),
-        ("background_alpha_to_point0", C.c_int),
+        ("background_alpha_to_point0", C.c_int), ("depth_accept_blend", C.c_float),
     ]
 
 
@@ -64,7 +64,8 @@ def default_params(**kw) -> dict:
              drop_out_radius_threshold=0.6, dist_cutoff=20.0, use_environment_map=0, viewer_only=0,
              stability_cutoff_value=10000.0, debug_max_list_length=-1, need_point_gradient=1,
              K_gradient_factor=0.5, distortion_gradient_factor=0.005, output_background_mask=0,
-             output_background_mask_value=0.0, conf_grad_quadratic=0, background_alpha_to_point0=1)
+             output_background_mask_value=0.0, conf_grad_quadratic=0, background_alpha_to_point0=1,
+             depth_accept_blend=0.01)
     p.update(kw)
     return p
 

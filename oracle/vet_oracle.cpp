@@ -11,9 +11,11 @@
 //   collection            src/lib/rendering/RenderForward.cu:1011-1137
 //   per-pixel sort        src/lib/rendering/AlphaListSort.cu:601-703   (ascending depth)
 //   blend (mode 1)        src/lib/rendering/RenderForward.cu:1303-1357, PointBlending.h:90-129
+//   blend (mode 2)        src/lib/rendering/RenderForward.cu:1393-1503
 //   blend (mode 3)        src/lib/rendering/RenderForward.cu:1539-1644, PointBlending.h:12-44
 //   mask                  src/lib/rendering/PointRenderer.cu:216-235
 //   backward (mode 1)     src/lib/rendering/RenderBackward.cu:1083-1513
+//   backward (mode 2)     src/lib/rendering/RenderBackward.cu:570-1080
 //   backward (mode 3)     src/lib/rendering/RenderBackward.cu:2893-3232
 //   projection backward   src/lib/rendering/PointRendererHelper.h:317-372
 //   normalisation         src/lib/rendering/PointRenderer.cu:1072-1109,1251-1308
@@ -52,7 +54,7 @@ constexpr int kMaxLayers = 5;  // RenderConstants.h:33
 
 struct OParams  // mirrors the fields of RenderParams the kernels read (Settings.h:19-73)
 {
-    int render_mode;                  // 1 FULL_BLEND, 3 BILINEAR_BLEND (PointRenderer.h: RenderMode)
+    int render_mode;                  // 1 FULL_BLEND, 2 FUZZY_BLEND, 3 BILINEAR_BLEND (PointRenderer.h: RenderMode)
     int num_layers;                   // 1..5
     int num_channels;                 // 3 or 4
     int drop_out_points_by_radius;    // bool
@@ -69,6 +71,7 @@ struct OParams  // mirrors the fields of RenderParams the kernels read (Settings
     float output_background_mask_value;
     int conf_grad_quadratic;          // oracle only: 1 = literal O(n^2) loop of RenderBackward.cu:1160-1178
     int background_alpha_to_point0;   // quirk: RenderBackward.cu:1130,1157 (mode 1)
+    float depth_accept_blend;         // 0.01, mode 2 (Settings.h:29)
 };
 
 struct OView  // ReducedImageInfo, data/SceneData.h:39-50
@@ -406,7 +409,7 @@ int64_t vo_forward(void* h, const OParams* prm, int n, const float* position, co
 {
     Oracle& o = *(Oracle*)h;
     if (prm->num_layers < 1 || prm->num_layers > kMaxLayers || B < 1) return -1;
-    if (prm->render_mode != 1 && prm->render_mode != 3) return -1;
+    if (prm->render_mode < 1 || prm->render_mode > 3) return -1;
     for (int b = 0; b < B; ++b)
         if (views[b].camera_model != 0 || views[b].w != views[0].w || views[b].h != views[0].h) return -1;
     o.prm = *prm;
@@ -523,6 +526,40 @@ int64_t vo_forward(void* h, const OParams* prm, int n, const float* position, co
                     if (prm->debug_max_list_length > 0) cnt = std::min(prm->debug_max_list_length, cnt);
                     float T    = 1.f;
                     float c[4] = {0, 0, 0, 0};
+                    if (prm->render_mode == 2)
+                    {
+                        // BlendMultiFuzzy, RenderForward.cu:1412-1492, transcribed literally: fragments within
+                        // depth_accept_blend of the FIRST depth are averaged; after that group the reference resets its
+                        // reference depth to -100000, so every later fragment is a group of its own.
+                        float last_min_d = 0.f, acc_conf = 0.f, acc_desc[4] = {0, 0, 0, 0};
+                        int n_acc = 0;
+                        auto accumulate = [&]() {
+                            float conf = acc_conf / float(n_acc);
+                            for (int ci = 0; ci < C; ++ci) c[ci] = blend(T, conf, acc_desc[ci] / float(n_acc), c[ci]);
+                            T = new_T(T, conf);
+                        };
+                        for (int i = 0; i < cnt; ++i)
+                        {
+                            uint32_t zb = (uint32_t)(o.keys[s + i] >> 32);
+                            float d;
+                            std::memcpy(&d, &zb, 4);
+                            int tex = index[(int)(uint32_t)o.keys[s + i]];
+                            if (last_min_d == 0.f) last_min_d = d;
+                            if (!(d - last_min_d < prm->depth_accept_blend))
+                            {
+                                accumulate();
+                                last_min_d = -100000.f;
+                                acc_conf   = 0.f;
+                                n_acc      = 0;
+                                for (int ci = 0; ci < C; ++ci) acc_desc[ci] = 0.f;
+                            }
+                            acc_conf += confidence[tex];
+                            for (int ci = 0; ci < C; ++ci) acc_desc[ci] += texture[(int64_t)ci * n_tex + tex];
+                            ++n_acc;
+                        }
+                        if (n_acc > 0) accumulate();
+                        cnt = 0;  // the plain loop below has nothing left to do
+                    }
                     for (int i = 0; i < cnt; ++i)
                     {
                         int pid   = (int)(uint32_t)o.keys[s + i];
@@ -647,7 +684,77 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                         return a;
                     };
 
+                    // (i) mode 2: BlendBackwardsFuzzy, RenderBackward.cu:603-749, transcribed literally.  Groups here are formed
+                    // against the first depth of EVERY group (unlike the forward pass) and the background is an entry of
+                    // depth 100000; the alpha gradient passed to earlier entries is not divided by their group size.
+                    if (prm.render_mode == 2)
+                    {
+                        const int list_size = prm.use_environment_map ? cnt : cnt + 1;
+                        float last_min_d = 0.f, acc_conf = 0.f, acc_desc[4] = {0, 0, 0, 0}, T = 1.f;
+                        int n_acc = 0, start = 0;
+                        static thread_local std::vector<float> group_conf;  // gradient_sum_backwards row C
+                        group_conf.assign(list_size, 0.f);
+                        auto tex_of = [&](int t) { return o.index[(int)(uint32_t)o.keys[s + t]]; };
+                        auto accumulate = [&]() {
+                            float inv_w = 1.f / float(n_acc);
+                            float conf  = acc_conf * inv_w;
+                            float colors[4], g_colors[4], g_alpha = 0;
+                            for (int ci = 0; ci < C; ++ci) colors[ci] = acc_desc[ci] * inv_w;
+                            for (int ci = 0; ci < C; ++ci)
+                            {
+                                g_colors[ci] = T * conf * gin[ci];
+                                g_alpha += colors[ci] * gin[ci];
+                            }
+                            g_alpha *= T;
+                            for (int t = start; t < start + n_acc; ++t)
+                            {
+                                bool fg = t != cnt;
+                                for (int ci = 0; ci < C; ++ci)
+                                {
+                                    if (fg)
+                                        ACC(g_texture[(int64_t)ci * n_tex + tex_of(t)], g_colors[ci] * inv_w);
+                                    else
+                                        ACC(g_background[ci], g_colors[ci] * inv_w);
+                                }
+                                if (fg)
+                                {
+                                    ACC(g_confidence[tex_of(t)], g_alpha * inv_w);
+                                    group_conf[t] = conf;
+                                }
+                            }
+                            for (int j = 0; j < start; ++j)
+                            {
+                                float g_iter = 0;
+                                for (int ci = 0; ci < C; ++ci) g_iter -= (gin[ci] * colors[ci] * T * conf / (1 - group_conf[j] + 1e-9f));
+                                ACC(g_confidence[tex_of(j)], g_iter);
+                            }
+                            T = new_T(T, conf);
+                        };
+                        for (int i = 0; i < list_size; ++i)
+                        {
+                            bool fg = i != cnt;
+                            float d = 100000.f;
+                            if (fg)
+                            {
+                                uint32_t zb = (uint32_t)(o.keys[s + i] >> 32);
+                                std::memcpy(&d, &zb, 4);
+                            }
+                            if (!(d - last_min_d < prm.depth_accept_blend))
+                            {
+                                if (i != 0) accumulate();
+                                acc_conf = 0.f, n_acc = 0;
+                                for (int ci = 0; ci < C; ++ci) acc_desc[ci] = 0.f;
+                                last_min_d = d;
+                                start      = i;
+                            }
+                            acc_conf += fg ? o.conf[tex_of(i)] : 1.f;
+                            for (int ci = 0; ci < C; ++ci) acc_desc[ci] += fg ? o.texture[(int64_t)ci * n_tex + tex_of(i)] : o.bg[ci];
+                            ++n_acc;
+                        }
+                        if (n_acc > 0) accumulate();
+                    }
                     // (i) colour / alpha gradients: RenderBackward.cu:1118-1181 and :2936-3019
+                    else
                     {
                         float T       = 1.f;
                         const int cnt0 = cnt;

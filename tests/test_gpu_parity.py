@@ -48,6 +48,36 @@ def test_long_list_slow_path(rasterizer, mode):
     assert gpu["longest"] > 2048 + 100
 
 
+@pytest.mark.parametrize("accept", [0.01, 0.2])
+def test_mode2_fuzzy_blend(rasterizer, accept):
+    """FUZZY_BLEND: depth-window groups; the reference groups differently in forward and backward, both reproduced."""
+    sc = scenes.tiny_scene(n=6000, n_views=2, seed=23, crop=True)
+    _roundtrip(rasterizer, sc, default_params(render_mode=2, depth_accept_blend=accept))
+    _roundtrip(rasterizer, sc, default_params(render_mode=2, depth_accept_blend=accept, use_environment_map=1))
+    _roundtrip(rasterizer, sc, default_params(render_mode=2, depth_accept_blend=accept, debug_max_list_length=3))
+
+
+def test_mode2_dense_and_long_lists(rasterizer):
+    from vet_b200 import _lib as L
+
+    sc = scenes.tiny_scene(n=40000, w=96, h=64, n_views=2, seed=11)
+    gpu, _ = _roundtrip(rasterizer, sc, default_params(render_mode=2, drop_out_points_by_radius=0, depth_accept_blend=0.02))
+    assert gpu["longest"] > 200
+    sc = scenes.tiny_scene(n=12000, w=16, h=12, n_views=1, seed=5)  # lists of 300 .. 1600: whole-list kernel
+    gpu, _ = _roundtrip(rasterizer, sc, default_params(render_mode=2, drop_out_points_by_radius=0, num_layers=3))
+    assert 256 < gpu["longest"] <= 3072
+    # beyond 3072 fragments in one list the mode-2 backward pass skips the pixel and says so
+    sc = scenes.tiny_scene(n=30000, w=16, h=12, n_views=1, seed=5)
+    params = default_params(render_mode=2, drop_out_points_by_radius=0, num_layers=3)
+    ora = util.run_oracle(sc, params)
+    gpu = util.run_gpu(rasterizer, sc, params, grads=util.random_grads(ora["fwd"]["color"]))
+    util.compare_forward(gpu, ora)  # the forward pass has no such limit
+    assert gpu["longest"] > 3072
+    with pytest.raises(L.VetrError) as e:
+        rasterizer.fragment_count()
+    assert e.value.status == L.E_TOO_LARGE
+
+
 def test_three_channels_env_map_and_truncation(rasterizer):
     sc = scenes.tiny_scene(n=4000, channels=3, seed=21)
     _roundtrip(rasterizer, sc, default_params(use_environment_map=1))
@@ -94,7 +124,7 @@ def test_invalid_arguments_are_refused(rasterizer):
     from vet_b200 import _lib as L
 
     sc = scenes.tiny_scene(n=10, w=5, h=3, n_views=1, seed=62)
-    for bad in (dict(num_layers=5), dict(num_layers=0), dict(render_mode=2), dict(render_mode=0)):
+    for bad in (dict(num_layers=5), dict(num_layers=0), dict(render_mode=4), dict(render_mode=0)):
         with pytest.raises(L.VetrError) as e:
             util.run_gpu(rasterizer, sc, default_params(**bad))
         assert e.value.status in (L.E_INVALID_ARG, L.E_UNSUPPORTED)

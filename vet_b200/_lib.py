@@ -10,6 +10,7 @@ LIB_PATH = os.environ.get("VETR_LIB", os.path.join(_HERE, "libvetr.so"))  # VETR
 MAX_LAYERS = 5
 MAX_VIEWS = 8
 MODE_FULL_BLEND = 1
+MODE_FUZZY_BLEND = 2
 MODE_BILINEAR_BLEND = 3
 
 OK, E_INVALID_ARG, E_CUDA, E_UNSUPPORTED, E_LIST_OVERFLOW, E_TOO_LARGE = 0, -1, -2, -3, -4, -5
@@ -24,6 +25,7 @@ class Params(C.Structure):
         ("need_point_gradient", C.c_int32), ("K_gradient_factor", C.c_float),
         ("distortion_gradient_factor", C.c_float), ("output_background_mask_value", C.c_float),
         ("background_alpha_to_point0", C.c_int32), ("keep_sorted_lists", C.c_int32),
+        ("depth_accept_blend", C.c_float),
     ]
 
 

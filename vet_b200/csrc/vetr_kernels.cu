@@ -70,7 +70,7 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
 {
     int n_views, L, C, n, n_tex, w, h;
     int mode, drop_by_radius, use_env, viewer_only, dbg_max_len, need_point_grad, bg_alpha_to_point0, keep_sorted;
-    float radius_threshold, dist_cutoff, stability_cutoff, k_grad_factor, dist_grad_factor, mask_value;
+    float radius_threshold, dist_cutoff, stability_cutoff, k_grad_factor, dist_grad_factor, mask_value, accept_blend;
     int lw[VETR_MAX_LAYERS], lh[VETR_MAX_LAYERS];
     long long lbase[VETR_MAX_LAYERS];
     long long P, PT;
@@ -520,6 +520,48 @@ struct Fold
     }
 };
 
+// Mode 2 (BlendMultiFuzzy, RenderForward.cu:1412-1492): fragments within depth_accept_blend of the list's FIRST depth
+// are averaged and blended as one; the reference then resets its reference depth to -100000, so every later fragment
+// is a group of its own.  Transcribed literally.
+struct FuzzyFold
+{
+    Fold fold;
+    float last_min_d, acc_conf, acc_desc[4];
+    int n_acc;
+    __device__ __forceinline__ void init()
+    {
+        fold.init();
+        last_min_d = acc_conf = 0.f;
+        acc_desc[0] = acc_desc[1] = acc_desc[2] = acc_desc[3] = 0.f;
+        n_acc       = 0;
+    }
+    __device__ __forceinline__ void flush()
+    {
+        const float n    = (float)n_acc;
+        const float conf = acc_conf / n;
+        fold.add(conf, make_float4(acc_desc[0] / n, acc_desc[1] / n, acc_desc[2] / n, acc_desc[3] / n));
+    }
+    __device__ __forceinline__ void add(float depth, float conf, float4 d, float accept)
+    {
+        if (last_min_d == 0.f) last_min_d = depth;
+        if (!(depth - last_min_d < accept))
+        {
+            flush();
+            last_min_d = -100000.f;
+            acc_conf   = 0.f;
+            n_acc      = 0;
+            acc_desc[0] = acc_desc[1] = acc_desc[2] = acc_desc[3] = 0.f;
+        }
+        acc_conf += conf;
+        acc_desc[0] += d.x, acc_desc[1] += d.y, acc_desc[2] += d.z, acc_desc[3] += d.w;
+        ++n_acc;
+    }
+    __device__ __forceinline__ void finish()
+    {
+        if (n_acc > 0) flush();
+    }
+};
+
 // ---------------------------------------------------------------------------------------------------------
 // Pass 4: sort + blend.
 
@@ -602,12 +644,27 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
             int cnt = se - ss;
             if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
             Fold fold;
-            fold.init();
-            for (int r = ss; r < ss + cnt; ++r)
+            if (f.mode == VETR_MODE_FUZZY_BLEND)
             {
-                const int u = s.perm[r];
-                fold.add(s.alpha[u], s.desc[u]);
-                if (bilinear && fold.T < 0.001f) break;
+                FuzzyFold ff;
+                ff.init();
+                for (int r = ss; r < ss + cnt; ++r)
+                {
+                    const int u = s.perm[r];
+                    ff.add(__uint_as_float((unsigned)(s.key[u] >> 32)), s.alpha[u], s.desc[u], f.accept_blend);
+                }
+                ff.finish();
+                fold = ff.fold;
+            }
+            else
+            {
+                fold.init();
+                for (int r = ss; r < ss + cnt; ++r)
+                {
+                    const int u = s.perm[r];
+                    fold.add(s.alpha[u], s.desc[u]);
+                    if (bilinear && fold.T < 0.001f) break;
+                }
             }
             fold.background(f);
             float depth = se > ss ? __uint_as_float((unsigned)(s.key[s.perm[ss]] >> 32)) : kMaxDepth;
@@ -623,7 +680,7 @@ __global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_
     if (f.status[2] <= kLongList) return;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BlendSmem& s = *reinterpret_cast<BlendSmem*>(smem_raw);
-    __shared__ float s_fold[8];  // T, colour and the stop flag carried between blocks
+    __shared__ float s_fold[16];  // carried between blocks: T, colour, stop flag; mode 2: reference depth, sums, count
     const int tid       = threadIdx.x;
     const int n_items   = f.status[3];
     const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
@@ -641,8 +698,7 @@ __global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_
         if (tid == 0)
         {
             s_fold[0] = 1.f;
-            s_fold[1] = s_fold[2] = s_fold[3] = s_fold[4] = 0.f;
-            s_fold[5] = 0.f;
+            for (int k = 1; k < 16; ++k) s_fold[k] = 0.f;
         }
         __syncthreads();
         for (int blk = 0; blk < cnt; blk += kCap)
@@ -650,34 +706,49 @@ __global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_
             const int m = min(kCap, cnt - blk);
             for (int i = tid; i < m; i += kThreads)
             {
-                s.alpha[i] = __uint_as_float(f.recs[2 * (size_t)(e0 + blk + i)].z);
-                s.desc[i]  = as_float4(f.recs[2 * (size_t)(e0 + blk + i) + 1]);
+                const uint4 h = f.recs[2 * (size_t)(e0 + blk + i)];
+                s.key[i]      = record_key(h);
+                s.alpha[i]    = __uint_as_float(h.z);
+                s.desc[i]     = as_float4(f.recs[2 * (size_t)(e0 + blk + i) + 1]);
             }
             __syncthreads();
             if (tid == 0 && s_fold[5] == 0.f)
             {
-                Fold fold;
-                fold.T = s_fold[0];
-                for (int k = 0; k < 4; ++k) fold.c[k] = s_fold[1 + k];
+                FuzzyFold ff;
+                ff.fold.T = s_fold[0];
+                for (int k = 0; k < 4; ++k) ff.fold.c[k] = s_fold[1 + k];
+                ff.last_min_d = s_fold[6], ff.acc_conf = s_fold[7], ff.n_acc = (int)s_fold[12];
+                for (int k = 0; k < 4; ++k) ff.acc_desc[k] = s_fold[8 + k];
                 for (int i = 0; i < m; ++i)
                 {
-                    fold.add(s.alpha[i], s.desc[i]);
-                    if (bilinear && fold.T < 0.001f)
+                    if (f.mode == VETR_MODE_FUZZY_BLEND)
+                        ff.add(__uint_as_float((unsigned)(s.key[i] >> 32)), s.alpha[i], s.desc[i], f.accept_blend);
+                    else
                     {
-                        s_fold[5] = 1.f;
-                        break;
+                        ff.fold.add(s.alpha[i], s.desc[i]);
+                        if (bilinear && ff.fold.T < 0.001f)
+                        {
+                            s_fold[5] = 1.f;
+                            break;
+                        }
                     }
                 }
-                s_fold[0] = fold.T;
-                for (int k = 0; k < 4; ++k) s_fold[1 + k] = fold.c[k];
+                s_fold[0] = ff.fold.T;
+                for (int k = 0; k < 4; ++k) s_fold[1 + k] = ff.fold.c[k];
+                s_fold[6] = ff.last_min_d, s_fold[7] = ff.acc_conf, s_fold[12] = (float)ff.n_acc;
+                for (int k = 0; k < 4; ++k) s_fold[8 + k] = ff.acc_desc[k];
             }
             __syncthreads();
         }
         if (tid == 0)
         {
-            Fold fold;
-            fold.T = s_fold[0];
-            for (int k = 0; k < 4; ++k) fold.c[k] = s_fold[1 + k];
+            FuzzyFold ff;
+            ff.fold.T = s_fold[0];
+            for (int k = 0; k < 4; ++k) ff.fold.c[k] = s_fold[1 + k];
+            ff.last_min_d = s_fold[6], ff.acc_conf = s_fold[7], ff.n_acc = (int)s_fold[12];
+            for (int k = 0; k < 4; ++k) ff.acc_desc[k] = s_fold[8 + k];
+            if (f.mode == VETR_MODE_FUZZY_BLEND) ff.finish();
+            Fold fold = ff.fold;
             fold.background(f);
             write_pixel(f, out, px, fold.c, fold.T, __uint_as_float(f.recs[2 * (size_t)e0].y));
         }
@@ -714,6 +785,15 @@ struct BackSmem
     SegTable seg;
     double red[kThreads / 32][8];  // cross-warp reduction scratch
     Camera cam[VETR_MAX_VIEWS];
+};
+
+// Mode 2 additionally needs every fragment's descriptor and depth (groups average them) and two group markers.
+struct BackSmemFuzzy : BackSmem
+{
+    float4 desc[kCap];
+    float depth[kCap];
+    float gv[kCap];               // at the first fragment of a group: sum_c G_c * colour_c * T * conf of that group
+    unsigned char gfirst[kCap];   // 1 = first fragment of its group
 };
 
 // Gradient accumulation with fire-and-forget reductions.  The gradient buffers are never read by these kernels, so
@@ -884,11 +964,12 @@ __device__ __forceinline__ float dot4(float4 a, float4 b, int C)
 template <bool kIntr>
 __device__ __forceinline__ void fragment_stage_a(const Frame& f, const BackPtrs& bp, BackSmem& s, const Camera& cam,
                                                  const PixInfo& px, float4 G, int slot, int gslot, bool blended,
-                                                 CamAcc<kIntr>& acc)
+                                                 CamAcc<kIntr>& acc, float4* desc_out = nullptr, float* depth_out = nullptr)
 {
     const uint4 h  = f.recs[2 * (size_t)gslot];
     const float4 d = as_float4(f.recs[2 * (size_t)gslot + 1]);
     const int pid  = (int)h.x;
+    if (desc_out) desc_out[slot] = d, depth_out[slot] = __uint_as_float(h.y);
     s.pid[slot]    = pid;
     s.tex[slot]    = (int)h.w;
     s.alpha[slot]  = __uint_as_float(h.z);
@@ -957,8 +1038,80 @@ __device__ __forceinline__ void sweep_list(const Frame& f, BackSmem& s, int ss, 
     for (int i = ss + eff - 1; i >= ss; --i)
     {
         float a = s.alpha[i], Ti = s.trans[i], dt = s.dot[i];
-        s.dot[i] = Ti * dt - S / (1 - a + 1e-9f);
+        s.dot[i]   = Ti * dt - S / (1 - a + 1e-9f);
+        s.trans[i] = Ti * a;  // from here on: the factor of G in the fragment's descriptor gradient
         S += Ti * a * dt;
+    }
+}
+
+// Mode 2 sweeps over one list (BlendBackwardsFuzzy, RenderBackward.cu:603-749) in O(n): groups are formed against the
+// first depth of every group, the background is an entry of depth 100000 (confidence 1, colour = background), a
+// group's descriptor / confidence gradients are shared equally by its fragments, and the term a later group passes to
+// the confidence of an earlier fragment uses that fragment's GROUP confidence and is not divided by the group size.
+// Leaves the factor of G of the descriptor gradient in trans[] (NaN = not blended) and the confidence gradient in dot[].
+__device__ __forceinline__ void sweep_list_fuzzy(const Frame& f, float* alpha, float* dot, float* trans, const float4* desc,
+                                                 const float* depth, float* gv, unsigned char* gfirst, int ss, int se,
+                                                 float4 G, float4 bgc, float bg_acc[4])
+{
+    int cnt = se - ss;
+    if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
+    for (int i = ss + cnt; i < se; ++i) trans[i] = __int_as_float(0x7fffffff);
+    const int list_size = f.use_env ? cnt : cnt + 1;
+    float last_min_d = 0.f, acc_conf = 0.f, T = 1.f, S_tail = 0.f;
+    float4 acc_desc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int n_acc = 0, start = 0;
+    auto close_group = [&]()
+    {
+        const float inv_w = 1.f / (float)n_acc;
+        const float conf  = acc_conf * inv_w;
+        const float4 col  = make_float4(acc_desc.x * inv_w, acc_desc.y * inv_w, acc_desc.z * inv_w, acc_desc.w * inv_w);
+        const float g_alpha = dot4(col, G, f.C) * T;
+        float v = 0.f;
+        v += G.x * col.x * T * conf;
+        v += G.y * col.y * T * conf;
+        v += G.z * col.z * T * conf;
+        if (f.C > 3) v += G.w * col.w * T * conf;
+        for (int t = start; t < start + n_acc; ++t)
+        {
+            if (t < cnt)
+            {
+                trans[ss + t]  = T * conf * inv_w;
+                dot[ss + t]    = g_alpha * inv_w;
+                alpha[ss + t]  = conf;  // the group's confidence, used below for earlier fragments
+                gfirst[ss + t] = t == start;
+                gv[ss + t]     = v;
+            }
+            else
+            {
+                bg_acc[0] += T * conf * G.x * inv_w, bg_acc[1] += T * conf * G.y * inv_w, bg_acc[2] += T * conf * G.z * inv_w;
+                if (f.C > 3) bg_acc[3] += T * conf * G.w * inv_w;
+            }
+        }
+        if (start >= cnt) S_tail = v;  // the group consists of the background entry alone
+        T = vetr_new_T(T, conf);
+    };
+    for (int i = 0; i < list_size; ++i)
+    {
+        const bool fg = i != cnt;
+        const float d = fg ? depth[ss + i] : kMaxDepth;
+        if (!(d - last_min_d < f.accept_blend))
+        {
+            if (i != 0) close_group();
+            acc_conf = 0.f, n_acc = 0, acc_desc = make_float4(0.f, 0.f, 0.f, 0.f);
+            last_min_d = d;
+            start      = i;
+        }
+        const float4 c = fg ? desc[ss + i] : bgc;
+        acc_conf += fg ? alpha[ss + i] : 1.f;
+        acc_desc.x += c.x, acc_desc.y += c.y, acc_desc.z += c.z, acc_desc.w += c.w;
+        ++n_acc;
+    }
+    if (n_acc > 0) close_group();
+    float S = S_tail;  // sum of v over the groups after the current one
+    for (int t = cnt - 1; t >= 0; --t)
+    {
+        dot[ss + t] -= S / (1 - alpha[ss + t] + 1e-9f);
+        if (gfirst[ss + t]) S += gv[ss + t];
     }
 }
 
@@ -1008,12 +1161,24 @@ __device__ unsigned long long g_phase_cycles[8];
 #    define PHASE_MARK(k)
 #endif
 
-template <bool kIntr>
-__global__ void __launch_bounds__(kThreads, kMinCtas) backward_kernel(const __grid_constant__ Frame f,
-                                                                      const __grid_constant__ BackPtrs bp)
+template <bool kFuzzy>
+struct BackSmemOf
 {
+    using type = BackSmem;
+};
+template <>
+struct BackSmemOf<true>
+{
+    using type = BackSmemFuzzy;
+};
+
+template <bool kIntr, bool kFuzzy>
+__global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kernel(const __grid_constant__ Frame f,
+                                                                                   const __grid_constant__ BackPtrs bp)
+{
+    using Smem = typename BackSmemOf<kFuzzy>::type;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    BackSmem& s = *reinterpret_cast<BackSmem*>(smem_raw);
+    Smem& s = *reinterpret_cast<Smem*>(smem_raw);
     const int tid     = threadIdx.x;
     const int n_items = f.status[3];
     const float4 bgc  = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
@@ -1072,11 +1237,21 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) backward_kernel(const __gr
             {
                 const int a = seg_lookup(s.seg, parity, s.seg_end, i);
                 const bool blended = f.dbg_max_len <= 0 || i - s.seg_end[a] < f.dbg_max_len;  // list truncation
-                fragment_stage_a<kIntr>(f, bp, s, cam, s.pix[a], s.grad[a], i, f0 + i, blended, acc);
+                if constexpr (kFuzzy)
+                    fragment_stage_a<kIntr>(f, bp, s, cam, s.pix[a], s.grad[a], i, f0 + i, blended, acc, s.desc, s.depth);
+                else
+                    fragment_stage_a<kIntr>(f, bp, s, cam, s.pix[a], s.grad[a], i, f0 + i, blended, acc);
             }
             __syncthreads();
             PHASE_MARK(2);
-            if (tid < np) sweep_list(f, s, s.seg_end[tid], s.seg_end[tid + 1], s.grad[tid], bgc, bg_acc, p0_acc);
+            if (tid < np)
+            {
+                if constexpr (kFuzzy)
+                    sweep_list_fuzzy(f, s.alpha, s.dot, s.trans, s.desc, s.depth, s.gv, s.gfirst, s.seg_end[tid], s.seg_end[tid + 1],
+                                     s.grad[tid], bgc, bg_acc);
+                else
+                    sweep_list(f, s, s.seg_end[tid], s.seg_end[tid + 1], s.grad[tid], bgc, bg_acc, p0_acc);
+            }
             __syncthreads();
             PHASE_MARK(3);
             for (int i = tid; i < nf; i += kThreads)
@@ -1084,7 +1259,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) backward_kernel(const __gr
                 const float Ti = s.trans[i];
                 if (Ti != Ti) continue;
                 const int a = seg_lookup(s.seg, parity, s.seg_end, i);
-                fragment_stage_b<kIntr>(f, bp, cam, s.pix[a], s.grad[a], s.pid[i], s.tex[i], Ti * s.alpha[i], s.dot[i], acc);
+                fragment_stage_b<kIntr>(f, bp, cam, s.pix[a], s.grad[a], s.pid[i], s.tex[i], Ti, s.dot[i], acc);
             }
             PHASE_MARK(4);
             lo = hi;
@@ -1188,19 +1363,126 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
                 for (int i = m - 1; i >= 0; --i)
                 {
                     float a = s.alpha[i], Ti = s.trans[i], dt = s.dot[i];
-                    s.dot[i] = Ti * dt - S / (1 - a + 1e-9f);
+                    s.dot[i]   = Ti * dt - S / (1 - a + 1e-9f);
+                    s.trans[i] = Ti * a;
                     S += Ti * a * dt;
                 }
                 s_carry[1] = S;
             }
             __syncthreads();
             for (int i = tid; i < m; i += kThreads)
-                fragment_stage_b<kIntr>(f, bp, cam, px, G, s.pid[i], s.tex[i], s.trans[i] * s.alpha[i], s.dot[i], acc);
+                fragment_stage_b<kIntr>(f, bp, cam, px, G, s.pid[i], s.tex[i], s.trans[i], s.dot[i], acc);
             __syncthreads();
         }
         if (bp.g_pose != nullptr || kIntr) reduce_cam<kIntr>(f, bp, acc, px.view, s);
     }
     reduce_background(f, bp, s, bg_acc, p0_acc);
+}
+
+// Mode 2, lists longer than kLongList: one CTA per list with the whole list staged (the group structure does not split
+// into blocks).  Lists beyond kFuzzyLongMax are skipped and flagged in the status word (the reference itself sorts only
+// the first 4096 fragments of a list, AlphaListSort.cu:289-290, so its result for such lists is not defined either).
+constexpr int kFuzzyLongMax = 3072;
+struct FuzzyLongSmem
+{
+    float4 desc[kFuzzyLongMax];
+    int pid[kFuzzyLongMax];
+    int tex[kFuzzyLongMax];
+    float alpha[kFuzzyLongMax];
+    float dot[kFuzzyLongMax];
+    float trans[kFuzzyLongMax];
+    float depth[kFuzzyLongMax];
+    float gv[kFuzzyLongMax];
+    unsigned char gfirst[kFuzzyLongMax];
+    double red[kThreads / 32][8];
+    Camera cam;
+};
+
+template <bool kIntr>
+__global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __grid_constant__ Frame f,
+                                                                       const __grid_constant__ BackPtrs bp)
+{
+    if (f.status[2] <= kLongList) return;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    FuzzyLongSmem& s = *reinterpret_cast<FuzzyLongSmem*>(smem_raw);
+    const int tid     = threadIdx.x;
+    const int n_items = f.status[3];
+    const float4 bgc  = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
+    CamAcc<kIntr> acc;
+    acc.clear();
+    float bg_acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x)
+    {
+        const int lo = f.item_start[item], hi = f.item_start[item + 1];
+        if (lo >= hi || !long_prefix(f, lo)) continue;
+        const int e0 = list_end(f, lo - 1);
+        const int n  = f.ends[lo] - e0;
+        if (n > kFuzzyLongMax)
+        {
+            if (tid == 0) atomicOr(f.status + 1, 2);
+            continue;
+        }
+        const PixInfo px = decode_pixel(f, (unsigned)lo);
+        __syncthreads();
+        if (tid == 0) s.cam = load_camera(f, px.view);
+        const float4 G = load_grad(f, bp, px);
+        __syncthreads();
+        const bool spatial = f.need_point_grad && is_interior(f, px);
+        for (int i = tid; i < n; i += kThreads)
+        {
+            const uint4 h  = f.recs[2 * (size_t)(e0 + i)];
+            const float4 d = as_float4(f.recs[2 * (size_t)(e0 + i) + 1]);
+            s.pid[i] = (int)h.x, s.tex[i] = (int)h.w, s.alpha[i] = __uint_as_float(h.z), s.depth[i] = __uint_as_float(h.y);
+            s.desc[i] = d;
+            const bool blended = f.dbg_max_len <= 0 || i < f.dbg_max_len;
+            if (spatial && blended)
+                spatial_backward<kIntr>(f, bp, s.cam, px, (int)h.x, __ldg(f.position + (int)h.x), neighbour_gradient(f, bp, px, d), acc);
+        }
+        __syncthreads();
+        if (tid == 0) sweep_list_fuzzy(f, s.alpha, s.dot, s.trans, s.desc, s.depth, s.gv, s.gfirst, 0, n, G, bgc, bg_acc);
+        __syncthreads();
+        for (int i = tid; i < n; i += kThreads)
+        {
+            const float coef = s.trans[i];
+            if (coef != coef) continue;
+            red_add_v4(bp.g_desc + s.tex[i], make_float4(coef * G.x, coef * G.y, coef * G.z, f.C > 3 ? coef * G.w : 0.f));
+            red_add(bp.g_conf + s.tex[i], s.dot[i]);
+        }
+        // camera gradients of this list's view
+        if (bp.g_pose != nullptr || kIntr)
+        {
+            constexpr int kN = kIntr ? 21 : 7;
+            const ViewDev& vw = f.views[px.view];
+            for (int k = 0; k < kN; ++k)
+            {
+                double x = k < 6 ? acc.pose[k] : (k == 6 ? (double)acc.pose_count : (double)acc.intr[kIntr ? k - 7 : 0]);
+                for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+                __syncthreads();
+                if ((tid & 31) == 0) s.red[tid >> 5][0] = x;
+                __syncthreads();
+                if (tid == 0)
+                {
+                    double t = 0.0;
+                    for (int w = 0; w < kThreads / 32; ++w) t += s.red[w][0];
+                    if (t != 0.0)
+                    {
+                        if (k < 6)
+                            atomicAdd(bp.g_pose + 6 * vw.image_index + k, t);
+                        else if (k == 6)
+                            atomicAdd(bp.g_pose_count + vw.image_index, (float)t);
+                        else if (k < 20)
+                            atomicAdd(bp.g_intr + 13 * vw.camera_index + (k - 7), (float)t);
+                        else
+                            atomicAdd(bp.g_intr_count + vw.camera_index, (float)t);
+                    }
+                }
+            }
+            acc.clear();
+        }
+    }
+    if (tid == 0)
+        for (int ci = 0; ci < f.C; ++ci)
+            if (bg_acc[ci] != 0.f) atomicAdd(bp.g_background + ci, bg_acc[ci]);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -1307,7 +1589,7 @@ struct vetr_ctx
     int sm_count         = 148;
     long long* tile_sums = nullptr;  // scan scratch
     long long tile_cap   = 0;
-    int blend_ctas_per_sm = 1, back_ctas_per_sm = 1;
+    int blend_ctas_per_sm = 1, back_ctas_per_sm = 1, fuzzy_ctas_per_sm = 1;
     long long launches   = 0;
     bool timing          = false;
     cudaEvent_t ev[VETR_T_N][2] = {};
@@ -1422,14 +1704,23 @@ extern "C" int vetr_create(vetr_ctx** out, int device, void* cuda_stream)
     const int blend_smem = (int)sizeof(BlendSmem), back_smem = (int)sizeof(BackSmem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(sort_blend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, blend_smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(sort_blend_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, blend_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
+    const int fuzzy_smem = (int)sizeof(BackSmemFuzzy), fuzzy_long_smem = (int)sizeof(FuzzyLongSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fuzzy_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fuzzy_smem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(backward_fuzzy_long_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fuzzy_long_smem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(backward_fuzzy_long_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fuzzy_long_smem);
+    if (e == cudaSuccess)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->fuzzy_ctas_per_sm, backward_kernel<false, true>, kThreads, fuzzy_smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
     if (e == cudaSuccess)
         e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->blend_ctas_per_sm, sort_blend_kernel, kThreads, blend_smem);
     if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->back_ctas_per_sm, backward_kernel<false>, kThreads, back_smem);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->back_ctas_per_sm, backward_kernel<false, false>, kThreads, back_smem);
     if (e != cudaSuccess)
     {
         delete ctx;
@@ -1438,6 +1729,7 @@ extern "C" int vetr_create(vetr_ctx** out, int device, void* cuda_stream)
     }
     if (ctx->blend_ctas_per_sm < 1) ctx->blend_ctas_per_sm = 1;
     if (ctx->back_ctas_per_sm < 1) ctx->back_ctas_per_sm = 1;
+    if (ctx->fuzzy_ctas_per_sm < 1) ctx->fuzzy_ctas_per_sm = 1;
     *out = ctx;
     return VETR_OK;
 }
@@ -1508,7 +1800,9 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     if (n_views < 1 || n_views > VETR_MAX_VIEWS) return VETR_E_INVALID_ARG;
     if (p->num_layers < 1 || p->num_layers > VETR_MAX_LAYERS) return VETR_E_INVALID_ARG;
     if (p->num_channels != 3 && p->num_channels != 4) return VETR_E_INVALID_ARG;
-    if (p->render_mode != VETR_MODE_FULL_BLEND && p->render_mode != VETR_MODE_BILINEAR_BLEND) return VETR_E_UNSUPPORTED;
+    if (p->render_mode != VETR_MODE_FULL_BLEND && p->render_mode != VETR_MODE_FUZZY_BLEND &&
+        p->render_mode != VETR_MODE_BILINEAR_BLEND)
+        return VETR_E_UNSUPPORTED;
     if (cloud->n < 0 || tex->n_tex < 1 || !cloud->position || !cloud->index || !tex->texture || !tex->confidence ||
         !tex->background || !cams->poses_se3 || !cams->intrinsics)
         return VETR_E_INVALID_ARG;
@@ -1537,6 +1831,7 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     f.radius_threshold = p->drop_out_radius_threshold, f.dist_cutoff = p->dist_cutoff;
     f.stability_cutoff = p->stability_cutoff_value, f.k_grad_factor = p->K_gradient_factor;
     f.dist_grad_factor = p->distortion_gradient_factor, f.mask_value = p->output_background_mask_value;
+    f.accept_blend = p->depth_accept_blend;
     f.P  = pyramid(f.w, f.h, f.L, f.lw, f.lh, f.lbase);
     f.PT = f.P * n_views;
     if (f.lw[f.L - 1] < 1 || f.lh[f.L - 1] < 1) return VETR_E_INVALID_ARG;  // the reference asserts w > 0 && h > 0 per level
@@ -1632,16 +1927,34 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
     if (!f.need_point_grad && f.mode != VETR_MODE_BILINEAR_BLEND) bp.g_points = nullptr;
     {
         PassScope t(ctx, VETR_T_BACKWARD, 2);
-        const int grid = ctx->sm_count * ctx->back_ctas_per_sm;
-        if (g_intr)
+        cudaStream_t st = ctx->stream;
+        if (f.mode == VETR_MODE_FUZZY_BLEND)
         {
-            backward_kernel<true><<<grid, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
-            backward_long_kernel<true><<<ctx->sm_count, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
+            const int grid = ctx->sm_count * ctx->fuzzy_ctas_per_sm;
+            if (g_intr)
+            {
+                backward_kernel<true, true><<<grid, kThreads, sizeof(BackSmemFuzzy), st>>>(f, bp);
+                backward_fuzzy_long_kernel<true><<<ctx->sm_count, kThreads, sizeof(FuzzyLongSmem), st>>>(f, bp);
+            }
+            else
+            {
+                backward_kernel<false, true><<<grid, kThreads, sizeof(BackSmemFuzzy), st>>>(f, bp);
+                backward_fuzzy_long_kernel<false><<<ctx->sm_count, kThreads, sizeof(FuzzyLongSmem), st>>>(f, bp);
+            }
         }
         else
         {
-            backward_kernel<false><<<grid, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
-            backward_long_kernel<false><<<ctx->sm_count, kThreads, sizeof(BackSmem), ctx->stream>>>(f, bp);
+            const int grid = ctx->sm_count * ctx->back_ctas_per_sm;
+            if (g_intr)
+            {
+                backward_kernel<true, false><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
+                backward_long_kernel<true><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
+            }
+            else
+            {
+                backward_kernel<false, false><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
+                backward_long_kernel<false><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
+            }
         }
     }
     VETR_CUDA(ctx, cudaGetLastError());
@@ -1694,7 +2007,8 @@ extern "C" int vetr_read_status(vetr_ctx* ctx, const vetr_lists* lists, int64_t*
     VETR_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (total_fragments) *total_fragments = h[0];
     if (longest_list) *longest_list = h[2];
-    return h[1] ? VETR_E_LIST_OVERFLOW : VETR_OK;
+    if (h[1] & 1) return VETR_E_LIST_OVERFLOW;
+    return (h[1] & 2) ? VETR_E_TOO_LARGE : VETR_OK;
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -23,7 +23,7 @@ def default_params(**kw) -> dict:
              drop_out_radius_threshold=0.6, dist_cutoff=20.0, use_environment_map=0, viewer_only=0,
              stability_cutoff_value=10000.0, debug_max_list_length=-1, need_point_gradient=1,
              K_gradient_factor=0.5, distortion_gradient_factor=0.005, output_background_mask_value=0.0,
-             background_alpha_to_point0=1, keep_sorted_lists=1)
+             background_alpha_to_point0=1, keep_sorted_lists=1, depth_accept_blend=0.01)
     p.update(kw)
     return p
 

@@ -38,6 +38,7 @@ vetr_params make_params(const NeuralRenderInfo& info)
     q.output_background_mask_value = p.output_background_mask_value;
     q.background_alpha_to_point0   = 1;
     q.keep_sorted_lists            = 1;
+    q.depth_accept_blend           = p.depth_accept_blend;
     return q;
 }
 
