@@ -37,7 +37,8 @@ typedef enum vetr_status
                                    3072 fragments met the mode-2 backward pass, which skipped that pixel) */
 } vetr_status;
 
-/* Render modes: PointRendererCache::RenderMode, PointRenderer.h (FUZZY_DT = 0 is not built). */
+/* Render modes: PointRendererCache::RenderMode, PointRenderer.h. */
+#define VETR_MODE_FUZZY_DT 0
 #define VETR_MODE_FULL_BLEND 1
 #define VETR_MODE_FUZZY_BLEND 2
 #define VETR_MODE_BILINEAR_BLEND 3
@@ -63,6 +64,8 @@ typedef struct vetr_params
                                           gradient to descriptor 0's confidence gradient (RenderBackward.cu:1130,1157) */
     int32_t keep_sorted_lists;         /* bool: write the sorted lists back (needed by vetr_backward / vetr_get_lists) */
     float   depth_accept_blend;        /* 0.01: depth window of a fuzzy group, mode 2 (data/Settings.h:29) */
+    float   depth_accept;              /* 0.01: relative depth window of the splat, mode 0 (data/Settings.h:28) */
+    int32_t ghost_gradients;           /* bool, mode 0: position gradients from dropped-out points instead (Settings.h:31) */
 } vetr_params;
 
 /* ReducedImageInfo, data/SceneData.h:39-50. */
@@ -157,8 +160,14 @@ int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* clo
                  const vetr_lists* lists, float* const* out_color, float* const* out_weight, float* const* out_mask,
                  float* const* out_depth);
 
-/* Backward pass of the forward call that filled `lists`: BlendBackwards2 / BlendBackwardsBilinear for all views and
+/* Mode 0 (FUZZY_DT: DepthPrepassMulti, RenderForwardMulti, CombineAndFill, RenderForward.cu:180-406, PointRenderer.cu:24-52)
+ * keeps no lists: vetr_forward uses lists->ends for the nearest depth of every pixel, lists->frags (capacity >= n_views*P)
+ * as accumulators and leaves the number of accepted points of every pixel in lists->counts; out_weight is that number.
+ *
+ * Backward pass of the forward call that filled `lists`: BlendBackwards2 / BlendBackwardsBilinear for all views and
  * levels (BlendPointCloudBackward, PointRenderer.cu:1111-1250; kernels RenderBackward.cu:1083-1513, 2893-3232).
+ * (mode 0: CombineAndFillBackward + RenderBackward, RenderBackward.cu:27-76, 131-474; `dropout` must be the mask given to
+ * vetr_forward, other modes ignore it).
  * Gradients are ADDED to the caller's buffers as raw sums (the caller zero-fills; several calls may accumulate):
  *   g_desc     [n_tex,4] point-major descriptor gradient (columns >= channels stay untouched)
  *   g_conf     [n_tex]
@@ -168,7 +177,7 @@ int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* clo
  *   g_intr     [n_cam,13] float, g_intr_count [n_cam] float, or NULL
  * out_color are the images the forward call wrote; grad_color their gradients (same shapes). */
 int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* cloud, const vetr_texture* texture,
-                  const vetr_cameras* cameras, const vetr_view* views, int n_views, const vetr_lists* lists,
+                  const vetr_cameras* cameras, const vetr_view* views, int n_views, const float* dropout, const vetr_lists* lists,
                   const float* const* out_color, const float* const* grad_color, float* g_desc, float* g_conf,
                   float* g_points, float* g_background, double* g_pose, float* g_pose_count, float* g_intr,
                   float* g_intr_count);

@@ -24,7 +24,8 @@ class OParams(C.Structure):
         ("need_point_gradient", C.c_int), ("K_gradient_factor", C.c_float),
         ("distortion_gradient_factor", C.c_float), ("output_background_mask", C.c_int),
         ("output_background_mask_value", C.c_float), ("conf_grad_quadratic", C.c_int),
-        ("background_alpha_to_point0", C.c_int), ("depth_accept_blend", C.c_float),
+        ("background_alpha_to_point0", C.c_int), ("depth_accept_blend", C.c_float), ("depth_accept", C.c_float),
+        ("ghost_gradients", C.c_int),
     ]
 
 
@@ -65,7 +66,7 @@ def default_params(**kw) -> dict:
              stability_cutoff_value=10000.0, debug_max_list_length=-1, need_point_gradient=1,
              K_gradient_factor=0.5, distortion_gradient_factor=0.005, output_background_mask=0,
              output_background_mask_value=0.0, conf_grad_quadratic=0, background_alpha_to_point0=1,
-             depth_accept_blend=0.01)
+             depth_accept_blend=0.01, depth_accept=0.01, ghost_gradients=0)
     p.update(kw)
     return p
 

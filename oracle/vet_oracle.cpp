@@ -11,6 +11,8 @@
 //   collection            src/lib/rendering/RenderForward.cu:1011-1137
 //   per-pixel sort        src/lib/rendering/AlphaListSort.cu:601-703   (ascending depth)
 //   blend (mode 1)        src/lib/rendering/RenderForward.cu:1303-1357, PointBlending.h:90-129
+//   mode 0 (FUZZY_DT)     src/lib/rendering/RenderForward.cu:180-406, PointRenderer.cu:24-52,
+//                         RenderBackward.cu:27-128, 131-474
 //   blend (mode 2)        src/lib/rendering/RenderForward.cu:1393-1503
 //   blend (mode 3)        src/lib/rendering/RenderForward.cu:1539-1644, PointBlending.h:12-44
 //   mask                  src/lib/rendering/PointRenderer.cu:216-235
@@ -54,7 +56,7 @@ constexpr int kMaxLayers = 5;  // RenderConstants.h:33
 
 struct OParams  // mirrors the fields of RenderParams the kernels read (Settings.h:19-73)
 {
-    int render_mode;                  // 1 FULL_BLEND, 2 FUZZY_BLEND, 3 BILINEAR_BLEND (PointRenderer.h: RenderMode)
+    int render_mode;                  // 0 FUZZY_DT, 1 FULL_BLEND, 2 FUZZY_BLEND, 3 BILINEAR_BLEND (PointRenderer.h: RenderMode)
     int num_layers;                   // 1..5
     int num_channels;                 // 3 or 4
     int drop_out_points_by_radius;    // bool
@@ -72,6 +74,8 @@ struct OParams  // mirrors the fields of RenderParams the kernels read (Settings
     int conf_grad_quadratic;          // oracle only: 1 = literal O(n^2) loop of RenderBackward.cu:1160-1178
     int background_alpha_to_point0;   // quirk: RenderBackward.cu:1130,1157 (mode 1)
     float depth_accept_blend;         // 0.01, mode 2 (Settings.h:29)
+    float depth_accept;               // 0.01, mode 0 (Settings.h:28)
+    int ghost_gradients;              // mode 0: position gradients from dropped-out points instead (Settings.h:31)
 };
 
 struct OView  // ReducedImageInfo, data/SceneData.h:39-50
@@ -203,7 +207,7 @@ struct Projected
 
 // ProjPoint, RenderForward.cu:117-158 (pinhole branch) on top of ProjectPointPinhole
 inline Projected project(const float* pos4, const Pose& V, const float* intr /*13*/, const OView& cam,
-                         float dist_cutoff)
+                         float dist_cutoff, bool apply_crop_rotation = true)
 {
     V3 vp   = transform_point(V, {pos4[0], pos4[1], pos4[2]});
     float z = std::fmax(vp.z, 0.f);
@@ -213,6 +217,7 @@ inline Projected project(const float* pos4, const Pose& V, const float* intr /*1
     V2 ip = k_apply(intr, dp);
     float radius_px = intr[0] * cam.crop[0] * pos4[3] / z;
     ip = k_apply(cam.crop, ip);
+    if (!apply_crop_rotation) return {ip, z, radius_px};  // mode 0's backward copy of ProjPoint, RenderBackward.cu:78-116
     float cx = (float)(cam.w / 2), cy = (float)(cam.h / 2);  // integer division, RenderForward.cu:156
     float dx = ip.x - cx, dy = ip.y - cy;
     ip = {cam.rot[0] * dx + cam.rot[1] * dy, cam.rot[2] * dx + cam.rot[3] * dy};
@@ -329,6 +334,10 @@ struct Oracle
     const double* poses   = nullptr;
     const float* intr     = nullptr;
     bool abs_mode         = false;
+    // mode 0
+    std::vector<float> depth0;     // [B*P] nearest depth (100000 where empty)
+    std::vector<float> weight0;    // [B*P] number of accepted points
+    std::vector<float> dropout;    // copy of the drop-out mask (the backward pass reads it)
 };
 
 void setup_levels(Oracle& o, int w, int h)
@@ -409,7 +418,7 @@ int64_t vo_forward(void* h, const OParams* prm, int n, const float* position, co
 {
     Oracle& o = *(Oracle*)h;
     if (prm->num_layers < 1 || prm->num_layers > kMaxLayers || B < 1) return -1;
-    if (prm->render_mode < 1 || prm->render_mode > 3) return -1;
+    if (prm->render_mode < 0 || prm->render_mode > 3) return -1;
     for (int b = 0; b < B; ++b)
         if (views[b].camera_model != 0 || views[b].w != views[0].w || views[b].h != views[0].h) return -1;
     o.prm = *prm;
@@ -421,6 +430,66 @@ int64_t vo_forward(void* h, const OParams* prm, int n, const float* position, co
     setup_levels(o, views[0].w, views[0].h);
     const bool bilinear = prm->render_mode == 3;
     const int64_t PT    = o.P * B;
+    o.dropout.clear();
+    if (dropout) o.dropout.assign(dropout, dropout + (int64_t)B * n);
+
+    if (prm->render_mode == 0)
+    {
+        // FUZZY_DT: DepthPrepassMulti (no drop-out test), RenderForwardMulti (drop-out test, depth test against the
+        // nearest depth), CombineAndFill.
+        const int C = prm->num_channels;
+        o.count.assign(PT, 0);
+        o.keys.clear();
+        o.depth0.assign(PT, 100000.f);
+        o.weight0.assign(PT, 0.f);
+        std::vector<double> accum((size_t)PT * C, 0.0);
+        for (int b = 0; b < B; ++b)
+            for (int pid = 0; pid < n; ++pid)
+                for_fragments(o, b, pid, nullptr, [&](int l, int x, int y, uint32_t zb, V2, int) {
+                    float z;
+                    std::memcpy(&z, &zb, 4);
+                    float& d = o.depth0[b * o.P + o.lv[l].base + (int64_t)y * o.lv[l].w + x];
+                    d = std::min(d, z);
+                });
+        int64_t F0 = 0;
+        for (int b = 0; b < B; ++b)
+            for (int pid = 0; pid < n; ++pid)
+                for_fragments(o, b, pid, dropout, [&](int l, int x, int y, uint32_t zb, V2, int) {
+                    float z;
+                    std::memcpy(&z, &zb, 4);
+                    int64_t g = b * o.P + o.lv[l].base + (int64_t)y * o.lv[l].w + x;
+                    if (z > o.depth0[g] * (prm->depth_accept + 1)) return;
+                    int tex = index[pid];
+                    for (int ci = 0; ci < C; ++ci) accum[(size_t)g * C + ci] += (double)texture[(int64_t)ci * n_tex + tex];
+                    o.weight0[g] += 1.f;
+                    o.count[g] += 1;
+                    ++F0;
+                });
+        o.out_color.resize(o.L);
+        for (int l = 0; l < o.L; ++l)
+        {
+            const Level& lv  = o.lv[l];
+            const int64_t hw = (int64_t)lv.w * lv.h;
+            o.out_color[l].assign((size_t)B * C * hw, 0.f);
+            for (int b = 0; b < B; ++b)
+                for (int64_t q = 0; q < hw; ++q)
+                {
+                    int64_t g = b * o.P + lv.base + q;
+                    float w   = o.weight0[g];
+                    for (int ci = 0; ci < C; ++ci)
+                    {
+                        float v = w == 0 ? background[ci] : (float)accum[(size_t)g * C + ci] / w;
+                        o.out_color[l][((int64_t)b * C + ci) * hw + q] = v;
+                        if (out_color) out_color[l][((int64_t)b * C + ci) * hw + q] = v;
+                    }
+                    if (out_weight) out_weight[l][b * hw + q] = w;
+                    if (out_mask) out_mask[l][b * hw + q] = (w == 0.f) ? prm->output_background_mask_value : 1.f;
+                    if (out_depth) out_depth[l][b * hw + q] = o.depth0[g];
+                }
+        }
+        o.start.assign(PT + 1, 0);
+        return F0;
+    }
 
     // counting pass
     o.count.assign(PT, 0);
@@ -640,6 +709,97 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
     if (g_pose_count) std::fill(g_pose_count, g_pose_count + o.n_img, 0.0);
     if (g_intr) std::fill(g_intr, g_intr + 13 * o.n_cam, 0.0);
     if (g_intr_count) std::fill(g_intr_count, g_intr_count + o.n_cam, 0.0);
+
+    if (prm.render_mode == 0)
+    {
+        // CombineAndFillBackward: the background receives the gradient of every empty pixel
+        for (int l = 0; l < o.L; ++l)
+        {
+            const Level& lv  = o.lv[l];
+            const int64_t hw = (int64_t)lv.w * lv.h;
+            for (int b = 0; b < B; ++b)
+                for (int64_t q = 0; q < hw; ++q)
+                    if (o.weight0[b * o.P + lv.base + q] == 0)
+                        for (int ci = 0; ci < C; ++ci) ACC(g_background[ci], grad_color[l][((int64_t)b * C + ci) * hw + q]);
+        }
+        // RenderBackward: one pass over the points per view; pixel positions come from the backward's own copy of the
+        // projection, which leaves out the crop rotation
+        for (int b = 0; b < B; ++b)
+        {
+            const OView& cam = o.views[b];
+            Pose V           = load_pose(o.poses + 8 * cam.image_index);
+            const float* K   = o.intr + 13 * cam.camera_index;
+            for (int pid = 0; pid < o.n; ++pid)
+            {
+                const bool drop_out = !o.dropout.empty() && o.dropout[(int64_t)b * o.n + pid] == 1.f;
+                Projected pr = project(o.position + 4 * pid, V, K, cam, prm.dist_cutoff, false);
+                if (pr.z == 0) continue;
+                const int tex = o.index[pid];
+                V2 ip = pr.ip;
+                float radius = pr.radius_px, scale = 1.f;
+                for (int l = 0; l < o.L; ++l, scale *= 0.5f, radius *= 0.5f, ip = {ip.x * 0.5f, ip.y * 0.5f})
+                {
+                    if (prm.drop_out_points_by_radius && radius < prm.drop_out_radius_threshold) continue;
+                    const Level& lv = o.lv[l];
+                    const int64_t hw = (int64_t)lv.w * lv.h;
+                    int x = round_half_even(ip.x), y = round_half_even(ip.y);
+                    if (x < 0 || y < 0 || x >= lv.w || y >= lv.h) continue;
+                    int64_t g = b * o.P + lv.base + (int64_t)y * lv.w + x;
+                    float w   = o.weight0[g];
+                    if (w == 0) continue;
+                    if (pr.z > o.depth0[g] * (prm.depth_accept + 1)) continue;
+                    const float* G = grad_color[l] + (int64_t)b * C * hw;
+                    const float* I = o.out_color[l].data() + (int64_t)b * C * hw;
+                    if (!drop_out)
+                    {
+                        float iw = 1.f / w;
+                        for (int ci = 0; ci < C; ++ci) ACC(g_texture[(int64_t)ci * n_tex + tex], iw * G[ci * hw + (int64_t)y * lv.w + x]);
+                    }
+                    bool point_grad = (prm.ghost_gradients && drop_out) | (!prm.ghost_gradients && !drop_out);
+                    int dist_edge   = std::min(std::min(x, lv.w - 1 - x), std::min(y, lv.h - 1 - y));
+                    if (!(point_grad && dist_edge > 2)) continue;
+                    float dx = 0, dy = 0;
+                    for (int ci = 0; ci < C; ++ci)
+                    {
+                        float Tp = o.texture[(int64_t)ci * n_tex + tex];
+                        auto at  = [&](const float* img, int xx, int yy) { return img[ci * hw + (int64_t)yy * lv.w + xx]; };
+                        float a0 = -((Tp - at(I, x - 1, y)) * at(G, x - 1, y));
+                        float a1 = (Tp - at(I, x + 1, y)) * at(G, x + 1, y);
+                        float b0 = -((Tp - at(I, x, y - 1)) * at(G, x, y - 1));
+                        float b1 = (Tp - at(I, x, y + 1)) * at(G, x, y + 1);
+                        dx += 0.5f * (a0 + a1);
+                        dy += 0.5f * (b0 + b1);
+                    }
+                    V2 dR{dx / (float)C, dy / (float)C};
+                    float crop2[5];
+                    for (int k = 0; k < 5; ++k) crop2[k] = cam.crop[k] * scale;
+                    BackOut bo;
+                    if (!project_backward(o.position + 4 * pid, dR, V, K, crop2, cam.rot, prm.dist_cutoff, bo)) continue;
+                    if (g_points)
+                    {
+                        for (int k = 0; k < 3; ++k) ACC(g_points[3 * (int64_t)pid + k], bo.g_point[k]);
+                        g_points_count[pid] += 1.0;
+                    }
+                    if (g_pose)
+                    {
+                        for (int k = 0; k < 6; ++k) ACC(g_pose[6 * cam.image_index + k], bo.g_pose[k]);
+                        g_pose_count[cam.image_index] += 1.0;  // RenderBackward.cu:379
+                    }
+                    if (g_intr)
+                    {
+                        bo.g_k[4] *= 0;
+                        for (int k = 0; k < 5; ++k) ACC(g_intr[13 * cam.camera_index + k], prm.K_gradient_factor * bo.g_k[k]);
+                        bo.g_dis[2] *= 0.25f;
+                        for (int k = 3; k < 8; ++k) bo.g_dis[k] *= 0.1f;
+                        for (int k = 0; k < 8; ++k)
+                            ACC(g_intr[13 * cam.camera_index + 5 + k], prm.distortion_gradient_factor * bo.g_dis[k]);
+                        g_intr_count[cam.camera_index] += (double)(1.f / 1024.f);
+                    }
+                }
+            }
+        }
+        return 0;
+    }
 
     std::vector<float> galpha;  // mode 3: gradient_sum_backwards row 0
     if (bilinear) galpha.assign(o.keys.size(), 0.f);

@@ -43,8 +43,8 @@ def test_host_only_entry_points():
 
 
 def test_struct_sizes_match_the_header():
-    # include/vetr.h: 17 four-byte fields; 5 ints + 9 floats; pointers + ints
-    assert C.sizeof(L.Params) == 68
+    # include/vetr.h: 19 four-byte fields; 5 ints + 9 floats; pointers + ints
+    assert C.sizeof(L.Params) == 76
     assert C.sizeof(L.View) == 56
     assert C.sizeof(L.Cloud) == 24 and C.sizeof(L.Texture) == 32 and C.sizeof(L.Cameras) == 24
     assert C.sizeof(L.Lists) == 56

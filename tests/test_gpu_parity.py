@@ -78,6 +78,39 @@ def test_mode2_dense_and_long_lists(rasterizer):
     assert e.value.status == L.E_TOO_LARGE
 
 
+def _mode0_roundtrip(rast, scene, params, dropout=None):
+    """Mode 0 sums descriptors with float atomics in an undefined order (as the reference does): images are compared
+    within 1e-5 of the largest descriptor magnitude instead of bit for bit; weights, depths and masks are exact."""
+    ora = util.run_oracle(scene, params, dropout=dropout)
+    g = util.random_grads(ora["fwd"]["color"], seed=3)
+    ora = util.run_oracle(scene, params, grads=g, dropout=dropout)
+    gpu = util.run_gpu(rast, scene, params, grads=g, dropout=dropout)
+    assert gpu["F"] == ora["F"]
+    np.testing.assert_array_equal(gpu["counts"], ora["counts"])
+    tol = 1e-5 * float(np.abs(scene.texture).max())
+    for l in range(len(ora["fwd"]["color"])):
+        np.testing.assert_allclose(gpu["fwd"]["color"][l], ora["fwd"]["color"][l], rtol=1e-5, atol=tol)
+        for name in ("weight", "mask", "depth"):
+            np.testing.assert_array_equal(gpu["fwd"][name][l], ora["fwd"][name][l], err_msg=name)
+    # the backward pass reads the forward image: give the oracle's gradients the same slack through the magnitudes
+    util.compare_backward(gpu["bwd_raw"], ora, scene.channels, rtol=2e-5)
+    return gpu, ora
+
+
+def test_mode0_fuzzy_depth_test(rasterizer):
+    """FUZZY_DT: nearest-depth pre-pass, depth-tested splat, combine; per-point backward."""
+    sc = scenes.tiny_scene(n=6000, n_views=2, seed=29)
+    _mode0_roundtrip(rasterizer, sc, default_params(render_mode=0))
+    _mode0_roundtrip(rasterizer, sc, default_params(render_mode=0, depth_accept=0.2, drop_out_points_by_radius=0))
+    sc3 = scenes.tiny_scene(n=4000, n_views=1, seed=30, channels=3, crop=True)  # crop rotation: the backward pass ignores it
+    _mode0_roundtrip(rasterizer, sc3, default_params(render_mode=0))
+    rng = np.random.default_rng(0)
+    dropout = (rng.uniform(size=(len(sc.views), sc.n)) < 0.3).astype(np.float32)
+    _mode0_roundtrip(rasterizer, sc, default_params(render_mode=0), dropout=dropout)
+    _mode0_roundtrip(rasterizer, sc, default_params(render_mode=0, ghost_gradients=1), dropout=dropout)
+    _mode0_roundtrip(rasterizer, sc, default_params(render_mode=0, viewer_only=1, stability_cutoff_value=0.4))
+
+
 def test_three_channels_env_map_and_truncation(rasterizer):
     sc = scenes.tiny_scene(n=4000, channels=3, seed=21)
     _roundtrip(rasterizer, sc, default_params(use_environment_map=1))
@@ -124,7 +157,7 @@ def test_invalid_arguments_are_refused(rasterizer):
     from vet_b200 import _lib as L
 
     sc = scenes.tiny_scene(n=10, w=5, h=3, n_views=1, seed=62)
-    for bad in (dict(num_layers=5), dict(num_layers=0), dict(render_mode=4), dict(render_mode=0)):
+    for bad in (dict(num_layers=5), dict(num_layers=0), dict(render_mode=4), dict(render_mode=-1)):
         with pytest.raises(L.VetrError) as e:
             util.run_gpu(rasterizer, sc, default_params(**bad))
         assert e.value.status in (L.E_INVALID_ARG, L.E_UNSUPPORTED)

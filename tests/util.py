@@ -43,7 +43,7 @@ def run_gpu(rast, scene, params: dict, grads=None, dropout=None, capacity=None):
     ends = [g[2].ends.cpu().numpy().astype(np.int64) for g in groups]
     keys_parts = []
     for g, e in zip(groups, ends):
-        n = int(e[-1]) if e.size else 0
+        n = int(e[-1]) if e.size and params.get("render_mode", 1) != 0 else 0
         keys_parts.append(g[2].frags[:n, 0].cpu().numpy().view(np.uint64))  # first 8 bytes of a record = key
     keys = np.concatenate(keys_parts) if keys_parts else np.zeros(0, np.uint64)
     out = dict(fwd={k: (None if v is None else [t.cpu().numpy() for t in v]) for k, v in fwd.items()}, counts=counts,

@@ -9,6 +9,7 @@ LIB_PATH = os.environ.get("VETR_LIB", os.path.join(_HERE, "libvetr.so"))  # VETR
 
 MAX_LAYERS = 5
 MAX_VIEWS = 8
+MODE_FUZZY_DT = 0
 MODE_FULL_BLEND = 1
 MODE_FUZZY_BLEND = 2
 MODE_BILINEAR_BLEND = 3
@@ -25,7 +26,7 @@ class Params(C.Structure):
         ("need_point_gradient", C.c_int32), ("K_gradient_factor", C.c_float),
         ("distortion_gradient_factor", C.c_float), ("output_background_mask_value", C.c_float),
         ("background_alpha_to_point0", C.c_int32), ("keep_sorted_lists", C.c_int32),
-        ("depth_accept_blend", C.c_float),
+        ("depth_accept_blend", C.c_float), ("depth_accept", C.c_float), ("ghost_gradients", C.c_int32),
     ]
 
 
@@ -93,7 +94,7 @@ def lib():
         L.vetr_forward.argtypes = [vp, C.POINTER(Params), C.POINTER(Cloud), C.POINTER(Texture), C.POINTER(Cameras),
                                    C.POINTER(View), C.c_int, vp, C.POINTER(Lists), vp, vp, vp, vp]
         L.vetr_backward.argtypes = [vp, C.POINTER(Params), C.POINTER(Cloud), C.POINTER(Texture), C.POINTER(Cameras),
-                                    C.POINTER(View), C.c_int, C.POINTER(Lists), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+                                    C.POINTER(View), C.c_int, vp, C.POINTER(Lists), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
         L.vetr_finalize_gradients.argtypes = [vp, C.c_int, C.c_int, vp, vp, C.c_int, vp, vp, C.c_int, vp, vp, C.c_int,
                                               vp, vp]
         L.vetr_apply_tangent.argtypes = [vp, vp, vp, C.c_int]

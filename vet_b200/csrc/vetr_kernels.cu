@@ -71,6 +71,8 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
     int n_views, L, C, n, n_tex, w, h;
     int mode, drop_by_radius, use_env, viewer_only, dbg_max_len, need_point_grad, bg_alpha_to_point0, keep_sorted;
     float radius_threshold, dist_cutoff, stability_cutoff, k_grad_factor, dist_grad_factor, mask_value, accept_blend;
+    float depth_accept;
+    int ghost;
     int lw[VETR_MAX_LAYERS], lh[VETR_MAX_LAYERS];
     long long lbase[VETR_MAX_LAYERS];
     long long P, PT;
@@ -467,6 +469,16 @@ __device__ __forceinline__ int seg_lookup(const SegTable& t, int parity, const i
     return a;
 }
 
+__device__ __forceinline__ float4 load_descriptor(const Frame& f, int tex)
+{
+    float4 d;
+    d.x = __ldg(f.texture + tex);
+    d.y = __ldg(f.texture + (size_t)f.n_tex + tex);
+    d.z = __ldg(f.texture + 2 * (size_t)f.n_tex + tex);
+    d.w = f.C > 3 ? __ldg(f.texture + 3 * (size_t)f.n_tex + tex) : 0.f;
+    return d;
+}
+
 // First pixel of an item that the item kernels leave to the long-list kernels (0 or 1 pixels).
 __device__ __forceinline__ int long_prefix(const Frame& f, int lo)
 {
@@ -828,7 +840,7 @@ struct CamAcc
 // Sums the accumulators over the CTA and adds the totals to the outputs of `view`: one atomic per value and
 // (CTA, view) instead of one per fragment.
 template <bool kIntr>
-__device__ void reduce_cam(const Frame& f, const BackPtrs& bp, CamAcc<kIntr>& acc, int view, BackSmem& s)
+__device__ void reduce_cam(const Frame& f, const BackPtrs& bp, CamAcc<kIntr>& acc, int view, double (*red)[8])
 {
     constexpr int kN = kIntr ? 21 : 7;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -840,14 +852,14 @@ __device__ void reduce_cam(const Frame& f, const BackPtrs& bp, CamAcc<kIntr>& ac
         {
             double x = k < 6 ? acc.pose[k] : (k == 6 ? (double)acc.pose_count : (double)acc.intr[kIntr ? k - 7 : 0]);
             for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
-            if (lane == 0) s.red[warp][k - base] = x;
+            if (lane == 0) red[warp][k - base] = x;
         }
         __syncthreads();
         const int k = base + threadIdx.x;
         if (threadIdx.x < 8 && k < kN)
         {
             double x = 0.0;
-            for (int w = 0; w < kThreads / 32; ++w) x += s.red[w][threadIdx.x];
+            for (int w = 0; w < (int)blockDim.x / 32; ++w) x += red[w][threadIdx.x];
             if (x != 0.0)
             {
                 if (k < 6)
@@ -882,7 +894,8 @@ __device__ __forceinline__ void spatial_backward(const Frame& f, const BackPtrs&
     {
 #pragma unroll
         for (int k = 0; k < 6; ++k) acc.pose[k] += (double)bo.g_pose[k];
-        acc.pose_count += f.mode == VETR_MODE_BILINEAR_BLEND ? 1.f : (1.f / 1024.f);  // RenderBackward.cu:1425 vs :3144
+        // RenderBackward.cu:379 (mode 0) and :3144 (mode 3) count 1 per hit, :993 and :1425 (modes 2, 1) count 1/1024
+        acc.pose_count += (f.mode == VETR_MODE_BILINEAR_BLEND || f.mode == VETR_MODE_FUZZY_DT) ? 1.f : (1.f / 1024.f);
     }
     if (kIntr)
     {
@@ -1210,7 +1223,7 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
             const int hi   = min(hi_item, (view + 1) * P);
             if (view != acc_view)
             {
-                if (acc_view >= 0 && want_cam) reduce_cam<kIntr>(f, bp, acc, acc_view, s);
+                if (acc_view >= 0 && want_cam) reduce_cam<kIntr>(f, bp, acc, acc_view, s.red);
                 acc_view = view;
             }
             __syncthreads();  // every warp has left the previous run (and the cameras are loaded)
@@ -1265,7 +1278,7 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
             lo = hi;
         }
     }
-    if (acc_view >= 0 && want_cam) reduce_cam<kIntr>(f, bp, acc, acc_view, s);
+    if (acc_view >= 0 && want_cam) reduce_cam<kIntr>(f, bp, acc, acc_view, s.red);
     reduce_background(f, bp, s, bg_acc, p0_acc);
 }
 
@@ -1374,7 +1387,7 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
                 fragment_stage_b<kIntr>(f, bp, cam, px, G, s.pid[i], s.tex[i], s.trans[i], s.dot[i], acc);
             __syncthreads();
         }
-        if (bp.g_pose != nullptr || kIntr) reduce_cam<kIntr>(f, bp, acc, px.view, s);
+        if (bp.g_pose != nullptr || kIntr) reduce_cam<kIntr>(f, bp, acc, px.view, s.red);
     }
     reduce_background(f, bp, s, bg_acc, p0_acc);
 }
@@ -1483,6 +1496,177 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
     if (tid == 0)
         for (int ci = 0; ci < f.C; ++ci)
             if (bg_acc[ci] != 0.f) atomicAdd(bp.g_background + ci, bg_acc[ci]);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Mode 0 (FUZZY_DT): no lists.  Per pixel: nearest depth (int bits, in `ends`), accumulators in the fragment buffer
+// (record g: float4 descriptor sum, then the number of accepted points as a float), count of accepted points (`counts`).
+
+__global__ void fill_int_kernel(int* p, int v, long long n)
+{
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
+// kPass 0: DepthPrepassMulti (RenderForward.cu:180-308; no drop-out test).  kPass 1: RenderForwardMulti (:312-406).
+template <int kPass>
+__global__ void __launch_bounds__(kProjThreads) fuzzy_dt_point_kernel(const __grid_constant__ Frame f)
+{
+    __shared__ Camera s_cam;
+    const int b = blockIdx.y;
+    if (threadIdx.x == 0) s_cam = load_camera(f, b);
+    __syncthreads();
+    const Camera& cam = s_cam;
+    const int vbase   = b * (int)f.P;
+    const int pid     = blockIdx.x * kProjThreads + threadIdx.x;
+    if (pid >= f.n) return;
+    const int tex = __ldg(f.index + pid);
+    if (f.viewer_only && f.confidence[tex] < f.stability_cutoff) return;
+    if (kPass == 1 && f.dropout && f.dropout[(size_t)b * f.n + pid] == 1.f) return;
+    const Projected pr = project_point(__ldg(f.position + pid), cam, f.dist_cutoff);
+    if (pr.z == 0.f) return;
+    float2 ip    = pr.ip;
+    float radius = pr.radius_px;
+    float4 desc  = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (kPass == 1)
+    {
+        desc.x = __ldg(f.texture + tex);
+        desc.y = __ldg(f.texture + (size_t)f.n_tex + tex);
+        desc.z = __ldg(f.texture + 2 * (size_t)f.n_tex + tex);
+        desc.w = f.C > 3 ? __ldg(f.texture + 3 * (size_t)f.n_tex + tex) : 0.f;
+    }
+    for (int l = 0; l < f.L; ++l, radius *= 0.5f, ip.x *= 0.5f, ip.y *= 0.5f)
+    {
+        if (f.drop_by_radius && radius < f.radius_threshold) break;
+        const int lw = f.lw[l], lh = f.lh[l];
+        const int x = round_half_even(ip.x), y = round_half_even(ip.y);
+        if ((unsigned)x >= (unsigned)lw || (unsigned)y >= (unsigned)lh) continue;
+        const int g = vbase + (int)f.lbase[l] + y * lw + x;
+        if (kPass == 0)
+            atomicMin(f.ends + g, __float_as_int(pr.z));  // z > 0: integer order = float order
+        else
+        {
+            const float image_depth = __int_as_float(f.ends[g]);
+            if (pr.z > image_depth * (f.depth_accept + 1)) continue;
+            red_add_v4(reinterpret_cast<float4*>(f.recs + 2 * (size_t)g), desc);
+            red_add(reinterpret_cast<float*>(f.recs + 2 * (size_t)g + 1), 1.f);
+        }
+    }
+}
+
+// CombineAndFill (PointRenderer.cu:24-52) + CreateMask + depth output, one thread per pixel of the pixel space.
+__global__ void __launch_bounds__(256) fuzzy_dt_combine_kernel(const __grid_constant__ Frame f, const __grid_constant__ OutPtrs out)
+{
+    __shared__ int s_sum[8], s_max[8];
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    int n_acc = 0;
+    if (g < f.PT)
+    {
+        const float4 acc = as_float4(f.recs[2 * (size_t)g]);
+        const float w    = __uint_as_float(f.recs[2 * (size_t)g + 1].x);
+        n_acc            = (int)w;
+        f.counts[g]      = n_acc;
+        float c[4];
+        if (w == 0.f)
+            c[0] = f.background[0], c[1] = f.background[1], c[2] = f.background[2], c[3] = f.C > 3 ? f.background[3] : 0.f;
+        else
+            c[0] = acc.x / w, c[1] = acc.y / w, c[2] = acc.z / w, c[3] = acc.w / w;
+        write_pixel(f, out, decode_pixel(f, (unsigned)g), c, w, __int_as_float(f.ends[g]));
+    }
+    int sum = n_acc, mx = n_acc;
+    for (int o = 16; o > 0; o >>= 1)
+    {
+        sum += __shfl_down_sync(0xffffffffu, sum, o);
+        mx = max(mx, __shfl_down_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) s_sum[threadIdx.x >> 5] = sum, s_max[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        for (int i = 1; i < 8; ++i) sum += s_sum[i], mx = max(mx, s_max[i]);
+        if (sum) atomicAdd(f.status + 0, sum);
+        if (mx) atomicMax(f.status + 2, mx);
+    }
+}
+
+// CombineAndFillBackward (RenderBackward.cu:27-76): the background colour receives the gradient of every empty pixel.
+__global__ void __launch_bounds__(256) fuzzy_dt_background_kernel(const __grid_constant__ Frame f,
+                                                                   const __grid_constant__ BackPtrs bp)
+{
+    __shared__ float s_red[8][4];
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < f.PT; g += (long long)gridDim.x * blockDim.x)
+        if (f.counts[g] == 0)
+        {
+            const float4 G = load_grad(f, bp, decode_pixel(f, (unsigned)g));
+            v[0] += G.x, v[1] += G.y, v[2] += G.z, v[3] += G.w;
+        }
+    for (int k = 0; k < 4; ++k)
+    {
+        float x = v[k];
+        for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+        if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5][k] = x;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < f.C)
+    {
+        float x = 0.f;
+        for (int w = 0; w < 8; ++w) x += s_red[w][threadIdx.x];
+        if (x != 0.f) atomicAdd(bp.g_background + threadIdx.x, x);
+    }
+}
+
+// RenderBackward (RenderBackward.cu:131-474): one thread per point and view.  Pixel positions come from the backward's own
+// copy of the projection, which leaves out the crop rotation (RenderBackward.cu:78-116).
+template <bool kIntr>
+__global__ void __launch_bounds__(kProjThreads) fuzzy_dt_backward_kernel(const __grid_constant__ Frame f,
+                                                                         const __grid_constant__ BackPtrs bp)
+{
+    __shared__ Camera s_cam;
+    __shared__ double s_red[kProjThreads / 32][8];
+    const int b = blockIdx.y;
+    if (threadIdx.x == 0) s_cam = load_camera(f, b);
+    __syncthreads();
+    const Camera& cam = s_cam;
+    const int vbase   = b * (int)f.P;
+    const int pid     = blockIdx.x * kProjThreads + threadIdx.x;
+    CamAcc<kIntr> acc;
+    acc.clear();
+    if (pid < f.n)
+    {
+        const bool drop_out = f.dropout && f.dropout[(size_t)b * f.n + pid] == 1.f;
+        const float4 pos    = __ldg(f.position + pid);
+        const Projected pr  = project_point(pos, cam, f.dist_cutoff, false);
+        if (pr.z != 0.f)
+        {
+            const int tex = __ldg(f.index + pid);
+            float2 ip     = pr.ip;
+            float radius  = pr.radius_px;
+            for (int l = 0; l < f.L; ++l, radius *= 0.5f, ip.x *= 0.5f, ip.y *= 0.5f)
+            {
+                if (f.drop_by_radius && radius < f.radius_threshold) continue;
+                const int lw = f.lw[l], lh = f.lh[l];
+                const int x = round_half_even(ip.x), y = round_half_even(ip.y);
+                if ((unsigned)x >= (unsigned)lw || (unsigned)y >= (unsigned)lh) continue;
+                const int g   = vbase + (int)f.lbase[l] + y * lw + x;
+                const float w = (float)f.counts[g];
+                if (w == 0.f) continue;
+                if (pr.z > __int_as_float(f.ends[g]) * (f.depth_accept + 1)) continue;
+                PixInfo px;
+                px.x = (short)x, px.y = (short)y, px.level = (unsigned char)l, px.view = (unsigned char)b, px.pad = 0;
+                if (!drop_out)
+                {
+                    const float iw = 1.f / w;
+                    const float4 G = load_grad(f, bp, px);
+                    red_add_v4(bp.g_desc + tex, make_float4(iw * G.x, iw * G.y, iw * G.z, f.C > 3 ? iw * G.w : 0.f));
+                }
+                const bool point_grad = (f.ghost && drop_out) | (!f.ghost && !drop_out);
+                if (!(point_grad && is_interior(f, px))) continue;
+                spatial_backward<kIntr>(f, bp, cam, px, pid, pos, neighbour_gradient(f, bp, px, load_descriptor(f, tex)), acc);
+            }
+        }
+    }
+    if (bp.g_pose != nullptr || kIntr) reduce_cam<kIntr>(f, bp, acc, b, s_red);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -1626,6 +1810,13 @@ struct PassScope
             return VETR_E_CUDA;                   \
         }                                         \
     } while (0)
+
+static int __float_as_int_host(float v)
+{
+    int i;
+    memcpy(&i, &v, 4);
+    return i;
+}
 
 static int64_t pyramid(int w, int h, int L, int* lw, int* lh, long long* lbase)
 {
@@ -1800,9 +1991,7 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     if (n_views < 1 || n_views > VETR_MAX_VIEWS) return VETR_E_INVALID_ARG;
     if (p->num_layers < 1 || p->num_layers > VETR_MAX_LAYERS) return VETR_E_INVALID_ARG;
     if (p->num_channels != 3 && p->num_channels != 4) return VETR_E_INVALID_ARG;
-    if (p->render_mode != VETR_MODE_FULL_BLEND && p->render_mode != VETR_MODE_FUZZY_BLEND &&
-        p->render_mode != VETR_MODE_BILINEAR_BLEND)
-        return VETR_E_UNSUPPORTED;
+    if (p->render_mode < VETR_MODE_FUZZY_DT || p->render_mode > VETR_MODE_BILINEAR_BLEND) return VETR_E_UNSUPPORTED;
     if (cloud->n < 0 || tex->n_tex < 1 || !cloud->position || !cloud->index || !tex->texture || !tex->confidence ||
         !tex->background || !cams->poses_se3 || !cams->intrinsics)
         return VETR_E_INVALID_ARG;
@@ -1831,7 +2020,7 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     f.radius_threshold = p->drop_out_radius_threshold, f.dist_cutoff = p->dist_cutoff;
     f.stability_cutoff = p->stability_cutoff_value, f.k_grad_factor = p->K_gradient_factor;
     f.dist_grad_factor = p->distortion_gradient_factor, f.mask_value = p->output_background_mask_value;
-    f.accept_blend = p->depth_accept_blend;
+    f.accept_blend = p->depth_accept_blend, f.depth_accept = p->depth_accept, f.ghost = p->ghost_gradients;
     f.P  = pyramid(f.w, f.h, f.L, f.lw, f.lh, f.lbase);
     f.PT = f.P * n_views;
     if (f.lw[f.L - 1] < 1 || f.lh[f.L - 1] < 1) return VETR_E_INVALID_ARG;  // the reference asserts w > 0 && h > 0 per level
@@ -1872,6 +2061,29 @@ extern "C" int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr
         if (out_depth) out.depth[l] = out_depth[l];
     }
     cudaStream_t st = ctx->stream;
+    if (f.mode == VETR_MODE_FUZZY_DT)
+    {
+        if (f.capacity < f.PT) return VETR_E_INVALID_ARG;  // the fragment buffer holds one accumulator record per pixel
+        VETR_CUDA(ctx, cudaMemsetAsync(f.status, 0, 4 * sizeof(int), st));
+        VETR_CUDA(ctx, cudaMemsetAsync(f.recs, 0, (size_t)f.PT * 32, st));
+        const int ctas = (f.n + kProjThreads - 1) / kProjThreads;
+        {
+            PassScope t(ctx, VETR_T_COUNT, 2 + (ctas > 0));
+            fill_int_kernel<<<(unsigned)((f.PT + 255) / 256), 256, 0, st>>>(f.ends, __float_as_int_host(kMaxDepth), f.PT);
+            if (ctas > 0) fuzzy_dt_point_kernel<0><<<dim3(ctas, n_views), kProjThreads, 0, st>>>(f);
+        }
+        if (ctas > 0)
+        {
+            PassScope t(ctx, VETR_T_COLLECT, 1);
+            fuzzy_dt_point_kernel<1><<<dim3(ctas, n_views), kProjThreads, 0, st>>>(f);
+        }
+        {
+            PassScope t(ctx, VETR_T_SORT_BLEND, 1);
+            fuzzy_dt_combine_kernel<<<(unsigned)((f.PT + 255) / 256), 256, 0, st>>>(f, out);
+        }
+        VETR_CUDA(ctx, cudaGetLastError());
+        return VETR_OK;
+    }
     VETR_CUDA(ctx, cudaMemsetAsync(f.counts, 0, f.PT * sizeof(int), st));
     VETR_CUDA(ctx, cudaMemsetAsync(f.status, 0, 4 * sizeof(int), st));
     const int point_ctas = (f.n + kProjThreads * kPointsPerThread - 1) / (kProjThreads * kPointsPerThread);
@@ -1903,8 +2115,9 @@ extern "C" int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr
 }
 
 extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* cloud, const vetr_texture* texture,
-                             const vetr_cameras* cameras, const vetr_view* views, int n_views, const vetr_lists* lists,
-                             const float* const* out_color, const float* const* grad_color, float* g_desc, float* g_conf,
+                             const vetr_cameras* cameras, const vetr_view* views, int n_views, const float* dropout,
+                             const vetr_lists* lists, const float* const* out_color, const float* const* grad_color,
+                             float* g_desc, float* g_conf,
                              float* g_points, float* g_background, double* g_pose, float* g_pose_count, float* g_intr,
                              float* g_intr_count)
 {
@@ -1924,7 +2137,24 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
     }
     bp.g_desc = (float4*)g_desc, bp.g_conf = g_conf, bp.g_points = (float4*)g_points, bp.g_background = g_background;
     bp.g_pose = g_pose, bp.g_pose_count = g_pose_count, bp.g_intr = g_intr, bp.g_intr_count = g_intr_count;
-    if (!f.need_point_grad && f.mode != VETR_MODE_BILINEAR_BLEND) bp.g_points = nullptr;
+    if (!f.need_point_grad && f.mode != VETR_MODE_BILINEAR_BLEND && f.mode != VETR_MODE_FUZZY_DT) bp.g_points = nullptr;
+    f.dropout = dropout;
+    if (f.mode == VETR_MODE_FUZZY_DT)
+    {
+        PassScope t(ctx, VETR_T_BACKWARD, 2);
+        cudaStream_t st = ctx->stream;
+        fuzzy_dt_background_kernel<<<ctx->sm_count * 4, 256, 0, st>>>(f, bp);
+        const int ctas = (f.n + kProjThreads - 1) / kProjThreads;
+        if (ctas > 0)
+        {
+            if (g_intr)
+                fuzzy_dt_backward_kernel<true><<<dim3(ctas, n_views), kProjThreads, 0, st>>>(f, bp);
+            else
+                fuzzy_dt_backward_kernel<false><<<dim3(ctas, n_views), kProjThreads, 0, st>>>(f, bp);
+        }
+        VETR_CUDA(ctx, cudaGetLastError());
+        return VETR_OK;
+    }
     {
         PassScope t(ctx, VETR_T_BACKWARD, 2);
         cudaStream_t st = ctx->stream;

@@ -131,7 +131,8 @@ struct Projected
 };
 
 // STRICT.  ProjPoint (RenderForward.cu:117-158, pinhole branch) over ProjectPointPinhole (PointRendererHelper.h:184-218).
-__device__ __forceinline__ Projected project_point(const float4 pos, const Camera& cam, float dist_cutoff)
+__device__ __forceinline__ Projected project_point(const float4 pos, const Camera& cam, float dist_cutoff,
+                                                   bool apply_crop_rotation = true)
 {
     float3 vp = transform_point(cam.V, make_float3(pos.x, pos.y, pos.z));
     float z   = fmaxf(vp.z, 0.f);
@@ -151,9 +152,12 @@ __device__ __forceinline__ Projected project_point(const float4 pos, const Camer
     float2 ip       = k_apply(cam.K, dp);
     float radius_px = VM(VM(cam.K[0], cam.crop[0]), pos.w) / z;
     ip              = k_apply(cam.crop, ip);
-    float dx = VS(ip.x, cam.cx), dy = VS(ip.y, cam.cy);
-    ip = make_float2(VA(VM(cam.rot[0], dx), VM(cam.rot[1], dy)), VA(VM(cam.rot[2], dx), VM(cam.rot[3], dy)));
-    ip = make_float2(VA(ip.x, cam.cx), VA(ip.y, cam.cy));
+    if (apply_crop_rotation)  // mode 0's backward pass projects without it (RenderBackward.cu:78-116)
+    {
+        float dx = VS(ip.x, cam.cx), dy = VS(ip.y, cam.cy);
+        ip = make_float2(VA(VM(cam.rot[0], dx), VM(cam.rot[1], dy)), VA(VM(cam.rot[2], dx), VM(cam.rot[3], dy)));
+        ip = make_float2(VA(ip.x, cam.cx), VA(ip.y, cam.cy));
+    }
     Projected r;
     r.ip        = ip;
     r.z         = z;

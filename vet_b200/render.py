@@ -23,7 +23,8 @@ def default_params(**kw) -> dict:
              drop_out_radius_threshold=0.6, dist_cutoff=20.0, use_environment_map=0, viewer_only=0,
              stability_cutoff_value=10000.0, debug_max_list_length=-1, need_point_gradient=1,
              K_gradient_factor=0.5, distortion_gradient_factor=0.005, output_background_mask_value=0.0,
-             background_alpha_to_point0=1, keep_sorted_lists=1, depth_accept_blend=0.01)
+             background_alpha_to_point0=1, keep_sorted_lists=1, depth_accept_blend=0.01,
+             depth_accept=0.01, ghost_gradients=0)
     p.update(kw)
     return p
 
@@ -202,8 +203,10 @@ class Rasterizer:
         for (b0, b1, lists, varr) in s["groups"]:
             oc = [t[b0:b1] for t in s["color"]]
             gc = [t[b0:b1] for t in grad_color]
+            dro = s["tensors"][7]
             rc = lib.vetr_backward(self._ctx, C.byref(s["prm"]), C.byref(s["cloud"]), C.byref(s["tex"]),
-                                   C.byref(s["cams"]), varr, b1 - b0, C.byref(lists.c), _ptr_array(oc), _ptr_array(gc),
+                                   C.byref(s["cams"]), varr, b1 - b0, _ptr(None if dro is None else dro[b0:b1]),
+                                   C.byref(lists.c), _ptr_array(oc), _ptr_array(gc),
                                    _ptr(g["desc"]), _ptr(g["conf"]), _ptr(g.get("points")), _ptr(g["background"]),
                                    _ptr(g.get("pose")), _ptr(g.get("pose_count")), _ptr(g.get("intrinsics")),
                                    _ptr(g.get("intrinsics_count")))

@@ -39,6 +39,8 @@ vetr_params make_params(const NeuralRenderInfo& info)
     q.background_alpha_to_point0   = 1;
     q.keep_sorted_lists            = 1;
     q.depth_accept_blend           = p.depth_accept_blend;
+    q.depth_accept                 = p.depth_accept;
+    q.ghost_gradients              = p.ghost_gradients;
     return q;
 }
 
@@ -270,7 +272,10 @@ variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_out
         auto views = make_views(*info, b0, b1);
         auto pc = level_ptrs(color, b0), pg = level_ptrs(gcolor, b0);
         std::vector<const float*> cpc(pc.begin(), pc.end()), cpg(pg.begin(), pg.end());
-        check(vetr_backward(vc, &prm, &in.cloud, &in.tex, &in.cams, views.data(), nb, &lists, cpc.data(), cpg.data(),
+        const bool has_dropout = cache.dropout_points.defined() && info->params.dropout > 0 && info->train;
+        check(vetr_backward(vc, &prm, &in.cloud, &in.tex, &in.cams, views.data(), nb,
+                            has_dropout ? cache.dropout_points.data_ptr<float>() + (int64_t)b0 * cache.dropout_points.stride(0) : nullptr,
+                            &lists, cpc.data(), cpg.data(),
                             g_desc.data_ptr<float>(), g_conf.data_ptr<float>(),
                             g_points.defined() ? g_points.data_ptr<float>() : nullptr, g_background.data_ptr<float>(),
                             g_pose.defined() ? g_pose.data_ptr<double>() : nullptr,

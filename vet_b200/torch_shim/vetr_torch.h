@@ -36,7 +36,9 @@ struct RenderParams
 {
     bool check_normal               = false;
     float dropout                   = 0.25f;
+    float depth_accept              = 0.01f;
     float depth_accept_blend        = 0.01f;
+    bool ghost_gradients            = false;
     float drop_out_radius_threshold = 0.6f;
     bool drop_out_points_by_radius  = true;
     float distortion_gradient_factor = 0.005f;
