@@ -92,8 +92,9 @@ def _mode0_roundtrip(rast, scene, params, dropout=None):
         np.testing.assert_allclose(gpu["fwd"]["color"][l], ora["fwd"]["color"][l], rtol=1e-5, atol=tol)
         for name in ("weight", "mask", "depth"):
             np.testing.assert_array_equal(gpu["fwd"][name][l], ora["fwd"][name][l], err_msg=name)
-    # the backward pass reads the forward image: give the oracle's gradients the same slack through the magnitudes
-    util.compare_backward(gpu["bwd_raw"], ora, scene.channels, rtol=2e-5)
+    # the backward pass reads the forward image, which here differs from the oracle's in the last bits: an addend
+    # (T - I) * G inherits that difference relative to |I * G|, not to its own size, hence the floor per tensor
+    util.compare_backward(gpu["bwd_raw"], ora, scene.channels, rtol=2e-5, floor_rel=1e-6)
     return gpu, ora
 
 

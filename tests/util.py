@@ -99,7 +99,7 @@ def compare_forward(gpu, ora, exact_images=True):
                 assert_close(f"{name}[{l}]", a, b, rtol=1e-5, floor_rel=1e-6)
 
 
-def assert_sum_close(name, got, want, magnitude, rtol=1e-5):
+def assert_sum_close(name, got, want, magnitude, rtol=1e-5, floor_rel=0.0):
     """For sums of many fp32 addends: |got - want| <= rtol * sum|addends| (+ one ulp-scale term of the value).
     `magnitude` is the oracle's sum of |addend| for the same element."""
     got = np.asarray(got, np.float64)
@@ -107,6 +107,8 @@ def assert_sum_close(name, got, want, magnitude, rtol=1e-5):
     magnitude = np.asarray(magnitude, np.float64)
     assert got.shape == want.shape == magnitude.shape, (name, got.shape, want.shape, magnitude.shape)
     bound = rtol * np.maximum(magnitude, np.abs(want)) + 1e-30
+    if floor_rel:
+        bound = bound + floor_rel * (np.abs(want).max() if want.size else 0.0)
     err = np.abs(got - want)
     bad = ~(err <= bound)
     if bad.any():
@@ -115,10 +117,12 @@ def assert_sum_close(name, got, want, magnitude, rtol=1e-5):
                              f"want {want[i]!r} (err {err[i]:.3e}, bound {bound[i]:.3e}, sum|addends| {magnitude[i]:.3e})")
 
 
-def compare_backward(gpu_raw, ora, channels, rtol=1e-5):
+def compare_backward(gpu_raw, ora, channels, rtol=1e-5, floor_rel=0.0):
     """Raw gradient sums.  The oracle sums in fp64; the GPU adds the same fp32 addends with atomics in an undefined
     order, so each element is held to rtol x (sum of |addends| of that element)."""
     b, m = ora["bwd"], ora["bwd_mag"]
+    import functools
+    assert_sum_close = functools.partial(globals()["assert_sum_close"], floor_rel=floor_rel)
     assert_sum_close("g_texture", gpu_raw["desc"][:, :channels].T, b["texture"], m["texture"], rtol)
     assert_sum_close("g_confidence", gpu_raw["conf"], b["confidence"], m["confidence"], rtol)
     assert_sum_close("g_background", gpu_raw["background"], b["background"], m["background"], rtol)

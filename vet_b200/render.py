@@ -79,6 +79,8 @@ class Rasterizer:
             raise L.VetrError(rc, "vetr_create")
         self._lists_cache = {}
         self._saved = None
+        self._cur_stream = 0 if stream is None else stream.cuda_stream
+        self._sync_stream()
 
     def close(self):
         if self._ctx:
@@ -90,6 +92,15 @@ class Rasterizer:
             self.close()
         except Exception:
             pass
+
+    def _sync_stream(self):
+        """Without an explicit stream the context follows torch's current stream (also the capture stream of
+        torch.cuda.graph, so a whole step of forward + backward can be recorded into a CUDA graph and replayed)."""
+        if self._stream is None:
+            cur = torch.cuda.current_stream(self.device).cuda_stream
+            if cur != self._cur_stream:
+                self._check(L.lib().vetr_set_stream(self._ctx, C.c_void_p(cur)), "vetr_set_stream")
+                self._cur_stream = cur
 
     def _check(self, rc: int, where: str):
         if rc != L.OK:
@@ -116,6 +127,7 @@ class Rasterizer:
                 dropout=None, capacity: Optional[int] = None, want_weight=True, want_mask=False, want_depth=False):
         """Returns dict(color=[L x [B,C,h,w]], weight=..., mask=..., depth=...).  Keeps what backward() needs."""
         lib = L.lib()
+        self._sync_stream()
         prm = L.Params(**{k: params[k] for k, _ in L.Params._fields_})
         B, Cn, Ln = len(views), texture.shape[0], prm.num_layers
         prm.num_channels = Cn
@@ -183,6 +195,7 @@ class Rasterizer:
         `accum` (a dict from an earlier call) accumulates further views into the same buffers."""
         s = self._saved
         lib = L.lib()
+        self._sync_stream()
         position, index, texture = s["tensors"][0], s["tensors"][1], s["tensors"][2]
         poses, intrinsics = s["tensors"][5], s["tensors"][6]
         n, n_tex, Cn = position.shape[0], texture.shape[1], texture.shape[0]
@@ -216,6 +229,7 @@ class Rasterizer:
     def finalize(self, g: dict):
         """Raw sums -> the reference's return tensors (PointRenderer.cu:1251-1322): texture [C,n_tex], confidence
         [1,n_tex], background [C], points [n,4] averaged by hit count, pose tangent and intrinsics averaged."""
+        self._sync_stream()
         n_tex = g["desc"].shape[0]
         Cn = g["background"].shape[0]
         g_texture = torch.empty(Cn, n_tex, dtype=torch.float32, device=self.device)
@@ -244,6 +258,7 @@ class Rasterizer:
         """ApplyTangentToPose (PointRenderer.cu:1343-1349), in place."""
         assert tangent.dtype == torch.float64 and poses.dtype == torch.float64
         assert tangent.is_contiguous() and poses.is_contiguous()
+        self._sync_stream()
         self._check(L.lib().vetr_apply_tangent(self._ctx, _ptr(tangent), _ptr(poses), poses.shape[0]), "vetr_apply_tangent")
 
 
