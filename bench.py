@@ -236,7 +236,8 @@ def run_ours(args):
     grad_bufs = [torch.empty(V, CHANNELS, h, w, device=dev) for (w, h) in sizes]
     diff_bufs = [torch.empty(V, CHANNELS, h, w, device=dev) for (w, h) in sizes]
 
-    def step(targets):
+    def compute(targets):
+        """Everything of a step up to the gradient sums of this rank."""
         flat.zero_()
         out = rast.forward(position, index, texture, confidence, background, poses, intrinsics, my_views, params,
                            want_weight=True)
@@ -251,20 +252,28 @@ def run_ours(args):
             term = d.abs_().sum() / numel[l]
             loss = term if loss is None else loss + term
         g = rast.backward_raw(grads, want_intrinsics=False, accum=grad_views())
+        return loss, g
+
+    def exchange(g):
+        """The one exchange step of view-sharded data parallelism: sum the gradient buffers over the ranks."""
         if world > 1:
             dist.all_reduce(flat)
             dist.all_reduce(g["pose"])
             dist.all_reduce(g["pose_count"])
-        fin = rast.finalize(g)
-        return loss, fin
+
+    def step(targets):
+        loss, g = compute(targets)
+        exchange(g)
+        return loss, rast.finalize(g)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    # ---- the whole step as one CUDA graph: ~60 kernel launches (library + loss + epilogue + all-reduce) replayed with one
-    # call, so that the host's launch cost is off the critical path.  Falls back to plain launches if capture fails.
+    # ---- the step as CUDA graphs: ~60 kernel launches (library + loss + epilogue) replayed with two calls, so that the
+    # host's launch cost is off the critical path.  The all-reduce stays an ordinary NCCL call between the two graphs.
+    # Falls back to plain launches if capture fails.
     eager_step = step
     static_targets = [torch.empty_like(t) for t in targets_dev]
     graph_info = {"used": False}
@@ -275,9 +284,11 @@ def run_ours(args):
             for _ in range(2):  # sizes every scratch buffer (nothing may be allocated by the library during capture)
                 eager_step(static_targets)
             torch.cuda.synchronize(dev)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                graph_out = eager_step(static_targets)
+            graph_a, graph_b = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_a):
+                loss_static, g_static = compute(static_targets)
+            with torch.cuda.graph(graph_b, pool=graph_a.pool()):
+                fin_static = rast.finalize(g_static)
             torch.cuda.synchronize(dev)
 
             def step(targets):
@@ -285,8 +296,10 @@ def run_ours(args):
                     for dst, src in zip(static_targets, targets):
                         if dst.data_ptr() != src.data_ptr():
                             dst.copy_(src, non_blocking=True)
-                graph.replay()
-                return graph_out
+                graph_a.replay()
+                exchange(g_static)
+                graph_b.replay()
+                return loss_static, fin_static
 
             graph_info["used"] = True
         except Exception as e:  # noqa: BLE001
