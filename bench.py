@@ -420,9 +420,12 @@ def run_ours(args):
         "collect": 16 * N * V + 8 * F,                      # positions again; one 8-byte key per fragment
         "sort_blend": 16 * F + 20 * F + 4 * PT + (4 * CHANNELS + 4) * PT,   # keys read + written back, descriptor and
                                                                             # confidence gather, offsets, colour + weight
-        "backward": 8 * F + 20 * F + 16 * F + 4 * PT + 8 * CHANNELS * PT + 2 * 36 * touched,  # keys, gathers (descriptor,
-                                                            # confidence, position), offsets, gradient + forward image,
-                                                            # one read + one write of each touched gradient element
+        # the backward step's bytes (keys, descriptor / confidence / position of every fragment, offsets, gradient +
+        # forward image, one read + one write of each touched gradient element) split over its two kernels: the position
+        # part belongs to the per-point pass.  The image-space gradients the first kernel parks for the second one are
+        # not algorithmic bytes.
+        "backward": 8 * F + 20 * F + 4 * PT + 8 * CHANNELS * PT + 2 * 20 * touched,
+        "point_backward": 16 * F + 2 * 16 * touched,
         "finalize": 32 * n_tex + 32 * N,                    # transpose descriptor gradient, normalise point gradient
     }
     peak, peak_src = measured_peak()

@@ -125,6 +125,14 @@ typedef struct vetr_lists
     int32_t*  items;    /* [items_capacity] work-item table written by the scan: first pixel of every run of pixels that
                            one thread block of the blend / backward kernels processes (balanced by fragments) */
     int64_t   items_capacity; /* >= vetr_item_table_entries(capacity, n_views*P) */
+    uint8_t*  level_mask;  /* [n_views*n] written by vetr_forward when not NULL: bit l set = the point has a fragment on
+                              pyramid level l of that view */
+    float*    point_grad;  /* [n_views*num_layers*n*2] scratch of vetr_backward: image-space gradient of every fragment,
+                              indexed by (view, level, point).  The position / pose / intrinsics gradients of modes 1 and 2
+                              are then formed in one coalesced pass over the points (every fragment's term computed exactly
+                              as in ProjectPointPinholeBackward, summed per point in a fixed order, no atomics on g_points).
+                              Both arrays are required by vetr_backward in modes 1 and 2 when need_point_gradient is set;
+                              level_mask must be the one the forward call wrote.  Neither needs initialising. */
 } vetr_lists;
 
 typedef struct vetr_ctx vetr_ctx;
@@ -233,6 +241,7 @@ enum
     VETR_T_SORT_BLEND,   /* sort + blend */
     VETR_T_BACKWARD,     /* backward */
     VETR_T_FINALIZE,     /* transpose + normalisation kernels */
+    VETR_T_POINT_BACKWARD, /* per-point pass of the backward step (modes 1 and 2) */
     VETR_T_N
 };
 int vetr_set_timing(vetr_ctx* ctx, int enable);

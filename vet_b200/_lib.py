@@ -49,7 +49,8 @@ class Cameras(C.Structure):
 
 class Lists(C.Structure):
     _fields_ = [("counts", C.c_void_p), ("ends", C.c_void_p), ("frags", C.c_void_p), ("capacity", C.c_int64),
-                ("status", C.c_void_p), ("items", C.c_void_p), ("items_capacity", C.c_int64)]
+                ("status", C.c_void_p), ("items", C.c_void_p), ("items_capacity", C.c_int64),
+                ("level_mask", C.c_void_p), ("point_grad", C.c_void_p)]
 
 
 EXPORTS = [
@@ -58,7 +59,7 @@ EXPORTS = [
     "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists", "vetr_set_timing", "vetr_get_timings",
     "vetr_launch_count", "vetr_scan_counts_static",
 ]
-TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize"]
+TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize", "point_backward"]
 
 _lib = None
 

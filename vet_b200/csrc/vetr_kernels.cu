@@ -53,7 +53,11 @@ constexpr int kLongList   = VETR_LONG_LIST;         // lists longer than this ta
 constexpr int kCap        = kQuantum + kLongList;   // fragments staged per item (an item holds < kQuantum + its first list)
 constexpr int kMinCtas    = VETR_MIN_CTAS;          // resident CTAs per SM the item kernels are compiled for
 constexpr int kProjThreads     = 256;
-constexpr int kPointsPerThread = 4;
+#ifndef VETR_COLLECT_POINTS
+#    define VETR_COLLECT_POINTS 2
+#endif
+constexpr int kPointsPerThread = 4;                      // count pass
+constexpr int kCollectPoints   = VETR_COLLECT_POINTS;    // collection pass (its slots and payload live in registers)
 static_assert(kMaxPixels <= kThreads, "one thread per pixel of an item");
 static_assert(kMaxPixels <= 256, "seg_of is a byte");
 constexpr int kScanTile   = 4096;  // elements per CTA in the scan (256 threads x 16)
@@ -91,6 +95,8 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
     long long capacity;
     int* status;      // {F, overflow, longest, number of work items}
     int* item_start;  // [n_items + 1]
+    unsigned char* level_mask;  // [n_views * n]: levels of the view on which the point has a fragment (written by collect)
+    float2* point_grad;         // [(view * L + level) * n + point]: image-space gradient of that fragment (backward scratch)
 };
 
 // One fragment record = one 32-byte sector.
@@ -134,10 +140,19 @@ __device__ __forceinline__ Camera load_camera(const Frame& f, int b)
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Pass 1 and 3: projection + counting / collection.  One point per thread and step, all lanes of a warp stay in
-// the level loop together so that equal pixels inside a warp can be merged into one atomic.
+// Pass 1 and 3: projection + counting / collection.  kPts points per thread.  Modes 1 and 2 run in three sweeps over
+// the thread's points so that independent memory operations are in flight together: (1) project and find the pixel of
+// every (point, level), (2) issue ALL count reductions / slot reservations, (3) load the payload and store the records.
+// (The slot reservation is an atomic with a return value: with one in flight per thread the kernel waits on it.)
 
-template <bool kCollect>
+__device__ __forceinline__ bool point_is_live(const Frame& f, int b, int pid)
+{
+    if (f.dropout && f.dropout[(size_t)b * f.n + pid] == 1.f) return false;
+    if (f.viewer_only && f.confidence[f.index[pid]] < f.stability_cutoff) return false;
+    return true;
+}
+
+template <bool kCollect, int kPts>
 __global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_constant__ Frame f)
 {
     __shared__ Camera s_cam;
@@ -147,29 +162,103 @@ __global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_cons
     const Camera& cam   = s_cam;
     const int vbase     = b * (int)f.P;
     const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
-    const int first     = blockIdx.x * (kProjThreads * kPointsPerThread) + threadIdx.x;
+    const int first     = blockIdx.x * (kProjThreads * kPts) + threadIdx.x;
 
-    float4 pos[kPointsPerThread];
+    float4 pos[kPts];
 #pragma unroll
-    for (int it = 0; it < kPointsPerThread; ++it)
+    for (int it = 0; it < kPts; ++it)
     {
         const int pid = first + it * kProjThreads;
         pos[it]       = pid < f.n ? __ldg(f.position + pid) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+
+    if (!bilinear)
+    {
+        int g[kPts][VETR_MAX_LAYERS];  // pixel of (point, level) in the global pixel space, then its record slot; -1 = none
+        unsigned zbits[kPts];
 #pragma unroll
-    for (int it = 0; it < kPointsPerThread; ++it)
+        for (int it = 0; it < kPts; ++it)
+        {
+            const int pid = first + it * kProjThreads;
+#pragma unroll
+            for (int l = 0; l < VETR_MAX_LAYERS; ++l) g[it][l] = -1;
+            zbits[it] = 0;
+            if (pid >= f.n || !point_is_live(f, b, pid)) continue;
+            const Projected pr = project_point(pos[it], cam, f.dist_cutoff);
+            if (pr.z == 0.f) continue;
+            zbits[it]    = __float_as_uint(pr.z);
+            float2 ip    = pr.ip;
+            float radius = pr.radius_px;
+            bool alive   = true;
+#pragma unroll
+            for (int l = 0; l < VETR_MAX_LAYERS; ++l)
+            {
+                if (l >= f.L || (f.drop_by_radius && radius < f.radius_threshold)) alive = false;
+                if (alive)
+                {
+                    const int lw = f.lw[l], lh = f.lh[l];
+                    const int x = round_half_even(ip.x), y = round_half_even(ip.y);
+                    if ((unsigned)x < (unsigned)lw && (unsigned)y < (unsigned)lh) g[it][l] = vbase + (int)f.lbase[l] + y * lw + x;
+                }
+                radius *= 0.5f, ip.x *= 0.5f, ip.y *= 0.5f;
+            }
+        }
+        if constexpr (!kCollect)
+        {
+#pragma unroll
+            for (int it = 0; it < kPts; ++it)
+#pragma unroll
+                for (int l = 0; l < VETR_MAX_LAYERS; ++l)
+                    if (g[it][l] >= 0) atomicAdd(f.counts + g[it][l], 1);
+            return;
+        }
+        else
+        {
+#pragma unroll
+            for (int it = 0; it < kPts; ++it)
+#pragma unroll
+                for (int l = 0; l < VETR_MAX_LAYERS; ++l)
+                    if (g[it][l] >= 0) g[it][l] = atomicAdd(f.ends + g[it][l], 1);
+        // what the blend needs of the point travels next to every key (coalesced loads here, one per point, instead of
+        // a dependent gather per fragment later)
+#pragma unroll
+        for (int it = 0; it < kPts; ++it)
+        {
+            const int pid = first + it * kProjThreads;
+            if (pid >= f.n) break;
+            unsigned bits = 0;
+#pragma unroll
+            for (int l = 0; l < VETR_MAX_LAYERS; ++l) bits |= g[it][l] >= 0 ? 1u << l : 0u;
+            if (f.level_mask) f.level_mask[(size_t)b * f.n + pid] = (unsigned char)bits;
+            if (!bits) continue;
+            const int tex   = __ldg(f.index + pid);
+            const float conf = __ldg(f.confidence + tex);
+            float4 desc;
+            desc.x = __ldg(f.texture + tex);
+            desc.y = __ldg(f.texture + (size_t)f.n_tex + tex);
+            desc.z = __ldg(f.texture + 2 * (size_t)f.n_tex + tex);
+            desc.w = f.C > 3 ? __ldg(f.texture + 3 * (size_t)f.n_tex + tex) : 0.f;
+            const unsigned long long key = ((unsigned long long)zbits[it] << 32) | (unsigned)pid;
+#pragma unroll
+            for (int l = 0; l < VETR_MAX_LAYERS; ++l)
+                if (g[it][l] >= 0 && (long long)g[it][l] < f.capacity) store_record(f, g[it][l], key, conf, tex, desc);
+        }
+        }
+        return;
+    }
+
+    // mode 3: every (point, level) touches the four pixels around its position
+#pragma unroll
+    for (int it = 0; it < kPts; ++it)
     {
         const int pid = first + it * kProjThreads;
         if (pid >= f.n) break;
-        if (f.dropout && f.dropout[(size_t)b * f.n + pid] == 1.f) continue;
-        if (f.viewer_only && f.confidence[f.index[pid]] < f.stability_cutoff) continue;
+        if (!point_is_live(f, b, pid)) continue;
         const Projected pr = project_point(pos[it], cam, f.dist_cutoff);
         if (pr.z == 0.f) continue;
         float2 ip     = pr.ip;
         float radius  = pr.radius_px;
         const unsigned long long key = ((unsigned long long)__float_as_uint(pr.z) << 32) | (unsigned)pid;
-        // collection also stores what the blend needs of the point next to every key (coalesced loads here, one
-        // per point, instead of a dependent gather per fragment later)
         int tex      = 0;
         float conf   = 0.f;
         float4 desc  = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -188,39 +277,27 @@ __global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_cons
             if (f.drop_by_radius && radius < f.radius_threshold) break;
             const int lw = f.lw[l], lh = f.lh[l];
             const int gbase = vbase + (int)f.lbase[l];
-            if (!bilinear)
+            const int bx = round_down(ip.x), by = round_down(ip.y);
+            if (bx == INT32_MIN || by == INT32_MIN) continue;  // unrepresentable position
+            int slot[4];
+#pragma unroll
+            for (int cidx = 0; cidx < 4; ++cidx)
             {
-                const int x = round_half_even(ip.x), y = round_half_even(ip.y);
+                const int x = bx + (cidx & 1), y = by + (cidx >> 1);
+                slot[cidx]  = -1;
                 if ((unsigned)x >= (unsigned)lw || (unsigned)y >= (unsigned)lh) continue;
                 const int g = gbase + y * lw + x;
                 if (!kCollect)
                     atomicAdd(f.counts + g, 1);
                 else
-                {
-                    const int slot = atomicAdd(f.ends + g, 1);
-                    if ((unsigned long long)slot < (unsigned long long)f.capacity) store_record(f, slot, key, conf, tex, desc);
-                }
+                    slot[cidx] = atomicAdd(f.ends + g, 1);
             }
-            else
+            if (kCollect)
             {
-                const int bx = round_down(ip.x), by = round_down(ip.y);
 #pragma unroll
                 for (int cidx = 0; cidx < 4; ++cidx)
-                {
-                    // bx, by may be INT32_MIN (unrepresentable position): the unsigned tests reject it before any use
-                    const int x = bx + (cidx & 1), y = by + (cidx >> 1);
-                    if (bx == INT32_MIN || by == INT32_MIN) continue;
-                    if ((unsigned)x >= (unsigned)lw || (unsigned)y >= (unsigned)lh) continue;
-                    const int g = gbase + y * lw + x;
-                    if (!kCollect)
-                        atomicAdd(f.counts + g, 1);
-                    else
-                    {
-                        const int slot = atomicAdd(f.ends + g, 1);
-                        if ((unsigned long long)slot < (unsigned long long)f.capacity)
-                            store_record(f, slot, key, blending_fac(ip, cidx, nullptr, nullptr) * conf, tex, desc);  // RenderForward.cu:1619
-                    }
-                }
+                    if (slot[cidx] >= 0 && (long long)slot[cidx] < f.capacity)
+                        store_record(f, slot[cidx], key, blending_fac(ip, cidx, nullptr, nullptr) * conf, tex, desc);  // RenderForward.cu:1619
             }
         }
     }
@@ -574,6 +651,23 @@ struct FuzzyFold
     }
 };
 
+// Optional instrumentation: cycles one thread of every CTA spends between the marks of an item kernel.
+#ifdef VETR_PHASE_TIMING
+__device__ unsigned long long g_phase_cycles[16];
+#    define PHASE_MARK(k)                                                                 \
+        do                                                                                \
+        {                                                                                 \
+            if (threadIdx.x == 0)                                                         \
+            {                                                                             \
+                long long now_ = clock64();                                               \
+                atomicAdd(&g_phase_cycles[k], (unsigned long long)(now_ - t_phase_));     \
+                t_phase_ = now_;                                                          \
+            }                                                                             \
+        } while (0)
+#else
+#    define PHASE_MARK(k)
+#endif
+
 // ---------------------------------------------------------------------------------------------------------
 // Pass 4: sort + blend.
 
@@ -599,6 +693,9 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
     const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
     if (tid == 0) s.seg.n_long[0] = s.seg.n_long[1] = 0;
     int parity = 0;
+#ifdef VETR_PHASE_TIMING
+    long long t_phase_ = clock64();
+#endif
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x)
     {
@@ -608,6 +705,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
         lo += long_prefix(f, lo);
         if (lo >= hi) continue;
         __syncthreads();  // every warp has left the previous item
+        PHASE_MARK(8);
         parity ^= 1;
         if (tid == 0) s.seg.n_long[parity ^ 1] = 0;
         const int f0 = list_end(f, lo - 1);
@@ -631,6 +729,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
             s.tex[i]      = (int)h.w;
         }
         __syncthreads();
+        PHASE_MARK(9);
         // rank sort inside each list; keys are unique (distinct point indices), so ranks are a permutation
         for (int i = tid; i < nf; i += kThreads)
         {
@@ -642,6 +741,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
             s.perm[ss + rank] = (unsigned short)i;
         }
         __syncthreads();
+        PHASE_MARK(10);
         // write the sorted lists back for the backward pass
         if (f.keep_sorted)
             for (int r = tid; r < nf; r += kThreads)
@@ -649,6 +749,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
                 const int u = s.perm[r];
                 store_record(f, f0 + r, s.key[u], s.alpha[u], s.tex[u], s.desc[u]);
             }
+        PHASE_MARK(11);
         // fold: one thread per pixel
         if (tid < np)
         {
@@ -682,6 +783,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
             float depth = se > ss ? __uint_as_float((unsigned)(s.key[s.perm[ss]] >> 32)) : kMaxDepth;
             write_pixel(f, out, s.pix[tid], fold.c, fold.T, depth);
         }
+        PHASE_MARK(12);
     }
 }
 
@@ -879,17 +981,15 @@ __device__ void reduce_cam(const Frame& f, const BackPtrs& bp, CamAcc<kIntr>& ac
 // Spatial gradient of one fragment: image-space gradient dR -> point, pose and intrinsics gradients
 // (RenderBackward.cu:1380-1460 and :3097-3180).
 template <bool kIntr>
-__device__ __forceinline__ void spatial_backward(const Frame& f, const BackPtrs& bp, const Camera& cam, const PixInfo& px,
-                                                 int pid, float4 pos, float2 dR, CamAcc<kIntr>& acc)
+__device__ __forceinline__ void spatial_terms(const Frame& f, const BackPtrs& bp, const Camera& cam, int level,
+                                              const PointJac& jac, float2 dR, CamAcc<kIntr>& acc, BackOut& bo)
 {
     float scale = 1.f;
-    for (int l = 0; l < px.level; ++l) scale *= 0.5f;
+    for (int l = 0; l < level; ++l) scale *= 0.5f;
     float crop2[5];
 #pragma unroll
     for (int k = 0; k < 5; ++k) crop2[k] = cam.crop[k] * scale;  // IntrinsicsPinhole::scale
-    BackOut bo;
-    if (!project_backward(pos, dR, cam, crop2, f.dist_cutoff, kIntr, bo)) return;
-    if (bp.g_points) red_add_v4(bp.g_points + pid, make_float4(bo.g_point[0], bo.g_point[1], bo.g_point[2], 1.f));
+    project_backward_apply(jac, dR, cam, crop2, kIntr, bo);
     if (bp.g_pose)
     {
 #pragma unroll
@@ -909,6 +1009,17 @@ __device__ __forceinline__ void spatial_backward(const Frame& f, const BackPtrs&
         for (int k = 0; k < 8; ++k) acc.intr[5 + k] += f.dist_grad_factor * bo.g_dis[k];
         acc.intr[kIntr ? 13 : 0] += 1.f / 1024.f;
     }
+}
+
+template <bool kIntr>
+__device__ __forceinline__ void spatial_backward(const Frame& f, const BackPtrs& bp, const Camera& cam, const PixInfo& px,
+                                                 int pid, float4 pos, float2 dR, CamAcc<kIntr>& acc)
+{
+    PointJac jac;
+    if (!project_backward_prepare(pos, cam, f.dist_cutoff, kIntr, jac)) return;
+    BackOut bo;
+    spatial_terms<kIntr>(f, bp, cam, px.level, jac, dR, acc, bo);
+    if (bp.g_points) red_add_v4(bp.g_points + pid, make_float4(bo.g_point[0], bo.g_point[1], bo.g_point[2], 1.f));
 }
 
 // Mode 1: approximate image-space gradient of a fragment from the neighbouring pixels (RenderBackward.cu:1347-1374).
@@ -972,12 +1083,17 @@ __device__ __forceinline__ float dot4(float4 a, float4 b, int C)
     return r;
 }
 
+// Image-space gradient of a fragment that takes no part in the position gradient (border pixel, cut-off list).
+constexpr int kNoGradientBits = 0x7fffffff;
+
 // Stage A of a fragment (needs nothing from the sweeps): streams the fragment's key and payload, computes d.G, and
-// in mode 1 its whole spatial gradient (which depends on the descriptor and the neighbouring pixels only).
-template <bool kIntr>
-__device__ __forceinline__ void fragment_stage_a(const Frame& f, const BackPtrs& bp, BackSmem& s, const Camera& cam,
-                                                 const PixInfo& px, float4 G, int slot, int gslot, bool blended,
-                                                 CamAcc<kIntr>& acc, float4* desc_out = nullptr, float* depth_out = nullptr)
+// in modes 1 and 2 its image-space gradient (which depends on the descriptor and the neighbouring pixels only).  That
+// gradient is parked under (view, level, point); point_backward_kernel turns it into position / camera gradients with
+// coalesced position loads and without atomics, instead of a position gather per fragment here.
+template <bool kBilinear>
+__device__ __forceinline__ void fragment_stage_a(const Frame& f, const BackPtrs& bp, BackSmem& s, const PixInfo& px, float4 G,
+                                                 int slot, int gslot, bool blended, float4* desc_out = nullptr,
+                                                 float* depth_out = nullptr)
 {
     const uint4 h  = f.recs[2 * (size_t)gslot];
     const float4 d = as_float4(f.recs[2 * (size_t)gslot + 1]);
@@ -987,21 +1103,22 @@ __device__ __forceinline__ void fragment_stage_a(const Frame& f, const BackPtrs&
     s.tex[slot]    = (int)h.w;
     s.alpha[slot]  = __uint_as_float(h.z);
     s.dot[slot]    = dot4(d, G, f.C);
-    if (f.mode != VETR_MODE_BILINEAR_BLEND && blended && f.need_point_grad && is_interior(f, px))
+    if (!kBilinear && f.need_point_grad)
     {
-        const float4 pos = __ldg(f.position + pid);
-        spatial_backward<kIntr>(f, bp, cam, px, pid, pos, neighbour_gradient(f, bp, px, d), acc);
+        float2 dR = make_float2(__int_as_float(kNoGradientBits), 0.f);
+        if (blended && is_interior(f, px)) dR = neighbour_gradient(f, bp, px, d);
+        f.point_grad[((size_t)px.view * f.L + px.level) * f.n + pid] = dR;
     }
 }
 
 // Stage B of a fragment (after the sweeps): descriptor and confidence gradients, and in mode 3 the spatial gradient.
-template <bool kIntr>
+template <bool kIntr, bool kBilinear>
 __device__ __forceinline__ void fragment_stage_b(const Frame& f, const BackPtrs& bp, const Camera& cam, const PixInfo& px,
                                                  float4 G, int pid, int tex, float Ta, float galpha, CamAcc<kIntr>& acc)
 {
     // descriptor gradient: T * alpha * G  (RenderBackward.cu:1149-1152)
     red_add_v4(bp.g_desc + tex, make_float4(Ta * G.x, Ta * G.y, Ta * G.z, f.C > 3 ? Ta * G.w : 0.f));
-    if (f.mode != VETR_MODE_BILINEAR_BLEND)
+    if (!kBilinear)
     {
         red_add(bp.g_conf + tex, galpha);
         return;
@@ -1158,21 +1275,6 @@ __device__ __forceinline__ void reduce_background(const Frame& f, const BackPtrs
     }
 }
 
-#ifdef VETR_PHASE_TIMING
-__device__ unsigned long long g_phase_cycles[8];
-#    define PHASE_MARK(k)                                                                 \
-        do                                                                                \
-        {                                                                                 \
-            if (threadIdx.x == 0)                                                         \
-            {                                                                             \
-                long long now_ = clock64();                                               \
-                atomicAdd(&g_phase_cycles[k], (unsigned long long)(now_ - t_phase_));     \
-                t_phase_ = now_;                                                          \
-            }                                                                             \
-        } while (0)
-#else
-#    define PHASE_MARK(k)
-#endif
 
 template <bool kFuzzy>
 struct BackSmemOf
@@ -1185,17 +1287,20 @@ struct BackSmemOf<true>
     using type = BackSmemFuzzy;
 };
 
-template <bool kIntr, bool kFuzzy>
+// kBilinear: mode 3, whose position / camera gradients are formed per fragment after the sweeps (stage B) and summed
+// per thread block and view; modes 1 and 2 leave them to point_backward_kernel.
+template <bool kIntr, bool kFuzzy, bool kBilinear>
 __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kernel(const __grid_constant__ Frame f,
                                                                                    const __grid_constant__ BackPtrs bp)
 {
+    static_assert(!(kFuzzy && kBilinear) && (kBilinear || !kIntr), "camera gradients are formed here in mode 3 only");
     using Smem = typename BackSmemOf<kFuzzy>::type;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Smem& s = *reinterpret_cast<Smem*>(smem_raw);
     const int tid     = threadIdx.x;
     const int n_items = f.status[3];
     const float4 bgc  = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
-    if (tid < f.n_views) s.cam[tid] = load_camera(f, tid);
+    if (kBilinear && tid < f.n_views) s.cam[tid] = load_camera(f, tid);
 
     CamAcc<kIntr> acc;
     acc.clear();
@@ -1203,7 +1308,7 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
     float bg_acc[4] = {0.f, 0.f, 0.f, 0.f};
     float p0_acc    = 0.f;
     const int P     = (int)f.P;
-    const bool want_cam = bp.g_pose != nullptr || kIntr;
+    const bool want_cam = kBilinear && (bp.g_pose != nullptr || kIntr);
     if (tid == 0) s.seg.n_long[0] = s.seg.n_long[1] = 0;
     int parity = 0;
 #ifdef VETR_PHASE_TIMING
@@ -1251,9 +1356,9 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
                 const int a = seg_lookup(s.seg, parity, s.seg_end, i);
                 const bool blended = f.dbg_max_len <= 0 || i - s.seg_end[a] < f.dbg_max_len;  // list truncation
                 if constexpr (kFuzzy)
-                    fragment_stage_a<kIntr>(f, bp, s, cam, s.pix[a], s.grad[a], i, f0 + i, blended, acc, s.desc, s.depth);
+                    fragment_stage_a<false>(f, bp, s, s.pix[a], s.grad[a], i, f0 + i, blended, s.desc, s.depth);
                 else
-                    fragment_stage_a<kIntr>(f, bp, s, cam, s.pix[a], s.grad[a], i, f0 + i, blended, acc);
+                    fragment_stage_a<kBilinear>(f, bp, s, s.pix[a], s.grad[a], i, f0 + i, blended);
             }
             __syncthreads();
             PHASE_MARK(2);
@@ -1272,7 +1377,7 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
                 const float Ti = s.trans[i];
                 if (Ti != Ti) continue;
                 const int a = seg_lookup(s.seg, parity, s.seg_end, i);
-                fragment_stage_b<kIntr>(f, bp, cam, s.pix[a], s.grad[a], s.pid[i], s.tex[i], Ti, s.dot[i], acc);
+                fragment_stage_b<kIntr, kBilinear>(f, bp, cam, s.pix[a], s.grad[a], s.pid[i], s.tex[i], Ti, s.dot[i], acc);
             }
             PHASE_MARK(4);
             lo = hi;
@@ -1284,10 +1389,11 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
 
 // Lists longer than kLongList: one CTA per list, blocks of kCap fragments, a forward sweep that records the
 // transmittance at every block start and a backward sweep over the blocks that carries the suffix sum.
-template <bool kIntr>
+template <bool kIntr, bool kBilinear>
 __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_constant__ Frame f,
                                                                  const __grid_constant__ BackPtrs bp)
 {
+    static_assert(kBilinear || !kIntr, "camera gradients are formed here in mode 3 only");
     if (f.status[2] <= kLongList) return;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BackSmem& s = *reinterpret_cast<BackSmem*>(smem_raw);
@@ -1295,7 +1401,7 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
     __shared__ float s_block_T[256];  // transmittance at block starts; lists beyond 256 * kCap fragments are cut there
     const int tid       = threadIdx.x;
     const int n_items   = f.status[3];
-    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+    constexpr bool bilinear = kBilinear;
     const float4 bgc    = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
     CamAcc<kIntr> acc;
     acc.clear();
@@ -1310,7 +1416,7 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
         const int n  = f.ends[lo] - e0;
         const PixInfo px = decode_pixel(f, (unsigned)lo);
         __syncthreads();
-        if (tid == 0) s.cam[0] = load_camera(f, px.view);
+        if (kBilinear && tid == 0) s.cam[0] = load_camera(f, px.view);
         const float4 G = load_grad(f, bp, px);
         int cnt = n;
         if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
@@ -1362,7 +1468,7 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
         {
             const int m = min(kCap, eff_cnt - blk * kCap);
             for (int i = tid; i < m; i += kThreads)
-                fragment_stage_a<kIntr>(f, bp, s, cam, px, G, i, e0 + blk * kCap + i, true, acc);
+                fragment_stage_a<kBilinear>(f, bp, s, px, G, i, e0 + blk * kCap + i, true);
             __syncthreads();
             if (tid == 0)
             {
@@ -1384,10 +1490,15 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
             }
             __syncthreads();
             for (int i = tid; i < m; i += kThreads)
-                fragment_stage_b<kIntr>(f, bp, cam, px, G, s.pid[i], s.tex[i], s.trans[i], s.dot[i], acc);
+                fragment_stage_b<kIntr, kBilinear>(f, bp, cam, px, G, s.pid[i], s.tex[i], s.trans[i], s.dot[i], acc);
             __syncthreads();
         }
-        if (bp.g_pose != nullptr || kIntr) reduce_cam<kIntr>(f, bp, acc, px.view, s.red);
+        // fragments behind the cut take no part in the position gradient
+        if (!kBilinear && f.need_point_grad)
+            for (int i = eff_cnt + tid; i < n; i += kThreads)
+                f.point_grad[((size_t)px.view * f.L + px.level) * f.n + (int)f.recs[2 * (size_t)(e0 + i)].x] =
+                    make_float2(__int_as_float(kNoGradientBits), 0.f);
+        if (kBilinear && (bp.g_pose != nullptr || kIntr)) reduce_cam<kIntr>(f, bp, acc, px.view, s.red);
     }
     reduce_background(f, bp, s, bg_acc, p0_acc);
 }
@@ -1407,11 +1518,8 @@ struct FuzzyLongSmem
     float depth[kFuzzyLongMax];
     float gv[kFuzzyLongMax];
     unsigned char gfirst[kFuzzyLongMax];
-    double red[kThreads / 32][8];
-    Camera cam;
 };
 
-template <bool kIntr>
 __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __grid_constant__ Frame f,
                                                                        const __grid_constant__ BackPtrs bp)
 {
@@ -1421,8 +1529,6 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
     const int tid     = threadIdx.x;
     const int n_items = f.status[3];
     const float4 bgc  = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
-    CamAcc<kIntr> acc;
-    acc.clear();
     float bg_acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int item = blockIdx.x; item < n_items; item += gridDim.x)
     {
@@ -1436,11 +1542,9 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
             continue;
         }
         const PixInfo px = decode_pixel(f, (unsigned)lo);
-        __syncthreads();
-        if (tid == 0) s.cam = load_camera(f, px.view);
         const float4 G = load_grad(f, bp, px);
-        __syncthreads();
-        const bool spatial = f.need_point_grad && is_interior(f, px);
+        __syncthreads();  // every warp has left the previous list
+        const bool spatial = is_interior(f, px);
         for (int i = tid; i < n; i += kThreads)
         {
             const uint4 h  = f.recs[2 * (size_t)(e0 + i)];
@@ -1448,8 +1552,9 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
             s.pid[i] = (int)h.x, s.tex[i] = (int)h.w, s.alpha[i] = __uint_as_float(h.z), s.depth[i] = __uint_as_float(h.y);
             s.desc[i] = d;
             const bool blended = f.dbg_max_len <= 0 || i < f.dbg_max_len;
-            if (spatial && blended)
-                spatial_backward<kIntr>(f, bp, s.cam, px, (int)h.x, __ldg(f.position + (int)h.x), neighbour_gradient(f, bp, px, d), acc);
+            if (f.need_point_grad)
+                f.point_grad[((size_t)px.view * f.L + px.level) * f.n + (int)h.x] =
+                    spatial && blended ? neighbour_gradient(f, bp, px, d) : make_float2(__int_as_float(kNoGradientBits), 0.f);
         }
         __syncthreads();
         if (tid == 0) sweep_list_fuzzy(f, s.alpha, s.dot, s.trans, s.desc, s.depth, s.gv, s.gfirst, 0, n, G, bgc, bg_acc);
@@ -1461,41 +1566,92 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
             red_add_v4(bp.g_desc + s.tex[i], make_float4(coef * G.x, coef * G.y, coef * G.z, f.C > 3 ? coef * G.w : 0.f));
             red_add(bp.g_conf + s.tex[i], s.dot[i]);
         }
-        // camera gradients of this list's view
-        if (bp.g_pose != nullptr || kIntr)
-        {
-            constexpr int kN = kIntr ? 21 : 7;
-            const ViewDev& vw = f.views[px.view];
-            for (int k = 0; k < kN; ++k)
-            {
-                double x = k < 6 ? acc.pose[k] : (k == 6 ? (double)acc.pose_count : (double)acc.intr[kIntr ? k - 7 : 0]);
-                for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
-                __syncthreads();
-                if ((tid & 31) == 0) s.red[tid >> 5][0] = x;
-                __syncthreads();
-                if (tid == 0)
-                {
-                    double t = 0.0;
-                    for (int w = 0; w < kThreads / 32; ++w) t += s.red[w][0];
-                    if (t != 0.0)
-                    {
-                        if (k < 6)
-                            atomicAdd(bp.g_pose + 6 * vw.image_index + k, t);
-                        else if (k == 6)
-                            atomicAdd(bp.g_pose_count + vw.image_index, (float)t);
-                        else if (k < 20)
-                            atomicAdd(bp.g_intr + 13 * vw.camera_index + (k - 7), (float)t);
-                        else
-                            atomicAdd(bp.g_intr_count + vw.camera_index, (float)t);
-                    }
-                }
-            }
-            acc.clear();
-        }
     }
     if (tid == 0)
         for (int ci = 0; ci < f.C; ++ci)
             if (bg_acc[ci] != 0.f) atomicAdd(bp.g_background + ci, bg_acc[ci]);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Modes 1 and 2: position, pose and intrinsics gradients, one pass over the points.  Every fragment's term is
+// ProjectPointPinholeBackward of the image-space gradient that stage A parked for it, evaluated with the arithmetic
+// of the per-fragment form (so each addend has the reference's bits); a point's terms are summed in registers in a
+// fixed order (view, level) and added to g_points by the one thread that owns the point.  Positions, masks and
+// parked gradients are read coalesced; camera gradients are summed per thread block and view.
+
+#ifndef VETR_POINT_BACK_POINTS
+#    define VETR_POINT_BACK_POINTS 2
+#endif
+constexpr int kPointBackPoints = VETR_POINT_BACK_POINTS;
+
+template <bool kIntr>
+__global__ void __launch_bounds__(kProjThreads) point_backward_kernel(const __grid_constant__ Frame f,
+                                                                      const __grid_constant__ BackPtrs bp)
+{
+    __shared__ Camera s_cam[VETR_MAX_VIEWS];
+    __shared__ double s_red[kProjThreads / 32][8];
+    if (f.status[1] != 0) return;  // overflow / skipped list: some fragments never parked a gradient
+    if (threadIdx.x < f.n_views) s_cam[threadIdx.x] = load_camera(f, threadIdx.x);
+    __syncthreads();
+    const int first     = blockIdx.x * (kProjThreads * kPointBackPoints) + threadIdx.x;
+    const bool want_cam = bp.g_pose != nullptr || kIntr;
+    float4 pos[kPointBackPoints], gp[kPointBackPoints];
+#pragma unroll
+    for (int it = 0; it < kPointBackPoints; ++it)
+    {
+        const int pid = first + it * kProjThreads;
+        pos[it]       = pid < f.n ? __ldg(f.position + pid) : make_float4(0.f, 0.f, 0.f, 0.f);
+        gp[it]        = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int b = 0; b < f.n_views; ++b)
+    {
+        CamAcc<kIntr> acc;
+        acc.clear();
+        unsigned mask[kPointBackPoints];
+#pragma unroll
+        for (int it = 0; it < kPointBackPoints; ++it)
+        {
+            const int pid = first + it * kProjThreads;
+            mask[it]      = pid < f.n ? f.level_mask[(size_t)b * f.n + pid] : 0u;
+        }
+        bool any = false;
+#pragma unroll
+        for (int it = 0; it < kPointBackPoints; ++it)
+        {
+            const int pid = first + it * kProjThreads;
+            if (!mask[it]) continue;
+            float2 dR[VETR_MAX_LAYERS];
+#pragma unroll
+            for (int l = 0; l < VETR_MAX_LAYERS; ++l)
+                if (mask[it] >> l & 1u) dR[l] = f.point_grad[((size_t)b * f.L + l) * f.n + pid];
+            PointJac jac;
+            if (!project_backward_prepare(pos[it], s_cam[b], f.dist_cutoff, kIntr, jac)) continue;
+#pragma unroll
+            for (int l = 0; l < VETR_MAX_LAYERS; ++l)
+            {
+                if (!(mask[it] >> l & 1u) || __float_as_int(dR[l].x) == kNoGradientBits) continue;
+                BackOut bo;
+                spatial_terms<kIntr>(f, bp, s_cam[b], l, jac, dR[l], acc, bo);
+                gp[it].x += bo.g_point[0], gp[it].y += bo.g_point[1], gp[it].z += bo.g_point[2], gp[it].w += 1.f;
+                any = true;
+            }
+        }
+        if (want_cam && __syncthreads_or(any)) reduce_cam<kIntr>(f, bp, acc, b, s_red);
+    }
+    if (bp.g_points)
+    {
+#pragma unroll
+        for (int it = 0; it < kPointBackPoints; ++it)
+        {
+            const int pid = first + it * kProjThreads;
+            if (pid < f.n && gp[it].w != 0.f)
+            {
+                float4 cur = bp.g_points[pid];
+                cur.x += gp[it].x, cur.y += gp[it].y, cur.z += gp[it].z, cur.w += gp[it].w;
+                bp.g_points[pid] = cur;
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -1773,7 +1929,7 @@ struct vetr_ctx
     int sm_count         = 148;
     long long* tile_sums = nullptr;  // scan scratch
     long long tile_cap   = 0;
-    int blend_ctas_per_sm = 1, back_ctas_per_sm = 1, fuzzy_ctas_per_sm = 1;
+    int blend_ctas_per_sm = 1, back_ctas_per_sm = 1, fuzzy_ctas_per_sm = 1, bilinear_ctas_per_sm = 1;
     long long launches   = 0;
     bool timing          = false;
     cudaEvent_t ev[VETR_T_N][2] = {};
@@ -1896,22 +2052,23 @@ extern "C" int vetr_create(vetr_ctx** out, int device, void* cuda_stream)
     if (e == cudaSuccess) e = cudaFuncSetAttribute(sort_blend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, blend_smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(sort_blend_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, blend_smem);
     const int fuzzy_smem = (int)sizeof(BackSmemFuzzy), fuzzy_long_smem = (int)sizeof(FuzzyLongSmem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fuzzy_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fuzzy_smem);
+    const auto smem_attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, false, false>, smem_attr, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, false, true>, smem_attr, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<true, false, true>, smem_attr, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, true, false>, smem_attr, fuzzy_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_fuzzy_long_kernel, smem_attr, fuzzy_long_smem);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(backward_fuzzy_long_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fuzzy_long_smem);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(backward_fuzzy_long_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fuzzy_long_smem);
-    if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->fuzzy_ctas_per_sm, backward_kernel<false, true>, kThreads, fuzzy_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, back_smem);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->fuzzy_ctas_per_sm, backward_kernel<false, true, false>, kThreads, fuzzy_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<false, false>, smem_attr, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<false, true>, smem_attr, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<true, true>, smem_attr, back_smem);
     if (e == cudaSuccess)
         e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->blend_ctas_per_sm, sort_blend_kernel, kThreads, blend_smem);
     if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->back_ctas_per_sm, backward_kernel<false, false>, kThreads, back_smem);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->back_ctas_per_sm, backward_kernel<false, false, false>, kThreads, back_smem);
+    if (e == cudaSuccess)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->bilinear_ctas_per_sm, backward_kernel<false, false, true>, kThreads, back_smem);
     if (e != cudaSuccess)
     {
         delete ctx;
@@ -1921,6 +2078,7 @@ extern "C" int vetr_create(vetr_ctx** out, int device, void* cuda_stream)
     if (ctx->blend_ctas_per_sm < 1) ctx->blend_ctas_per_sm = 1;
     if (ctx->back_ctas_per_sm < 1) ctx->back_ctas_per_sm = 1;
     if (ctx->fuzzy_ctas_per_sm < 1) ctx->fuzzy_ctas_per_sm = 1;
+    if (ctx->bilinear_ctas_per_sm < 1) ctx->bilinear_ctas_per_sm = 1;
     *out = ctx;
     return VETR_OK;
 }
@@ -1970,7 +2128,7 @@ extern "C" int vetr_debug_phase_cycles(unsigned long long* out, int reset)
     cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(g_phase_cycles));
     if (reset)
     {
-        unsigned long long z[8] = {};
+        unsigned long long z[16] = {};
         cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z));
     }
     return 0;
@@ -2036,6 +2194,8 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     int rc = ensure_scratch(ctx, n_tiles);
     if (rc != VETR_OK) return rc;
     f.item_start = lists->items;
+    f.level_mask = lists->level_mask;
+    f.point_grad = (float2*)lists->point_grad;
     return VETR_OK;
 }
 
@@ -2090,7 +2250,7 @@ extern "C" int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr
     if (point_ctas > 0)
     {
         PassScope t(ctx, VETR_T_COUNT, 1);
-        project_kernel<false><<<dim3(point_ctas, n_views), kProjThreads, 0, st>>>(f);
+        project_kernel<false, kPointsPerThread><<<dim3(point_ctas, n_views), kProjThreads, 0, st>>>(f);
     }
     const int n_tiles = (int)((f.PT + kScanTile - 1) / kScanTile);
     {
@@ -2102,7 +2262,8 @@ extern "C" int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr
     if (point_ctas > 0)
     {
         PassScope t(ctx, VETR_T_COLLECT, 1);
-        project_kernel<true><<<dim3(point_ctas, n_views), kProjThreads, 0, st>>>(f);
+        const int ctas = (f.n + kProjThreads * kCollectPoints - 1) / (kProjThreads * kCollectPoints);
+        project_kernel<true, kCollectPoints><<<dim3(ctas, n_views), kProjThreads, 0, st>>>(f);
     }
     {
         PassScope t(ctx, VETR_T_SORT_BLEND, 2);
@@ -2155,37 +2316,49 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
         VETR_CUDA(ctx, cudaGetLastError());
         return VETR_OK;
     }
+    const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+    // modes 1 and 2: position / camera gradients come from the per-point pass over the gradients stage A parks
+    const bool point_pass = !bilinear && f.need_point_grad && (bp.g_points || g_pose || g_intr);
+    if (!bilinear && !point_pass) f.need_point_grad = 0;
+    if (point_pass && (!f.level_mask || !f.point_grad)) return VETR_E_INVALID_ARG;
     {
         PassScope t(ctx, VETR_T_BACKWARD, 2);
         cudaStream_t st = ctx->stream;
         if (f.mode == VETR_MODE_FUZZY_BLEND)
         {
             const int grid = ctx->sm_count * ctx->fuzzy_ctas_per_sm;
+            backward_kernel<false, true, false><<<grid, kThreads, sizeof(BackSmemFuzzy), st>>>(f, bp);
+            backward_fuzzy_long_kernel<<<ctx->sm_count, kThreads, sizeof(FuzzyLongSmem), st>>>(f, bp);
+        }
+        else if (bilinear)
+        {
+            const int grid = ctx->sm_count * ctx->bilinear_ctas_per_sm;
             if (g_intr)
             {
-                backward_kernel<true, true><<<grid, kThreads, sizeof(BackSmemFuzzy), st>>>(f, bp);
-                backward_fuzzy_long_kernel<true><<<ctx->sm_count, kThreads, sizeof(FuzzyLongSmem), st>>>(f, bp);
+                backward_kernel<true, false, true><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
+                backward_long_kernel<true, true><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
             }
             else
             {
-                backward_kernel<false, true><<<grid, kThreads, sizeof(BackSmemFuzzy), st>>>(f, bp);
-                backward_fuzzy_long_kernel<false><<<ctx->sm_count, kThreads, sizeof(FuzzyLongSmem), st>>>(f, bp);
+                backward_kernel<false, false, true><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
+                backward_long_kernel<false, true><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
             }
         }
         else
         {
             const int grid = ctx->sm_count * ctx->back_ctas_per_sm;
-            if (g_intr)
-            {
-                backward_kernel<true, false><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
-                backward_long_kernel<true><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
-            }
-            else
-            {
-                backward_kernel<false, false><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
-                backward_long_kernel<false><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
-            }
+            backward_kernel<false, false, false><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
+            backward_long_kernel<false, false><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
         }
+    }
+    if (point_pass && f.n > 0)
+    {
+        PassScope t(ctx, VETR_T_POINT_BACKWARD, 1);
+        const int ctas = (f.n + kProjThreads * kPointBackPoints - 1) / (kProjThreads * kPointBackPoints);
+        if (g_intr)
+            point_backward_kernel<true><<<ctas, kProjThreads, 0, ctx->stream>>>(f, bp);
+        else
+            point_backward_kernel<false><<<ctas, kProjThreads, 0, ctx->stream>>>(f, bp);
     }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;

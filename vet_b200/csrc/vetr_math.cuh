@@ -203,27 +203,45 @@ struct BackOut
     float g_point[3], g_pose[6], g_k[5], g_dis[8];
 };
 
-// ProjectPointPinholeBackward, PointRendererHelper.h:317-372.  `cropK` is crop_transform.scale(0.5^level).
-__device__ __forceinline__ bool project_backward(const float4 pos, float2 grad, const Camera& cam, const float cropK[5],
-                                                 float dist_cutoff, bool want_intrinsics, BackOut& o)
+// ProjectPointPinholeBackward, PointRendererHelper.h:317-372, in two steps: what depends on the point and the camera
+// only (computed once per point and view), and the chain of transposed Jacobians applied to one image-space gradient.
+// `cropK` is crop_transform.scale(0.5^level).
+struct PointJac
 {
-    float3 vp = transform_point(cam.V, make_float3(pos.x, pos.y, pos.z));
-    if (!(vp.z > 0)) return false;
+    float3 vp;
+    float iz, gzx, gzy;  // 1/z and the z column of the division's Jacobian
+    float2 dp;
+    float Jpd[4], Jdd[16];
+};
+
+__device__ __forceinline__ bool project_backward_prepare(const float4 pos, const Camera& cam, float dist_cutoff,
+                                                         bool want_intrinsics, PointJac& j)
+{
+    j.vp = transform_point(cam.V, make_float3(pos.x, pos.y, pos.z));
+    if (!(j.vp.z > 0)) return false;
+    j.iz = 1.f / j.vp.z;
+    float2 np = make_float2(j.vp.x / j.vp.z, j.vp.y / j.vp.z);
+    j.Jpd[0] = 1.f, j.Jpd[1] = 0.f, j.Jpd[2] = 0.f, j.Jpd[3] = 1.f;
+    j.dp = np;
+    if (cam.has_dist || want_intrinsics) j.dp = distort<true>(np, cam.dist, dist_cutoff, j.Jpd, j.Jdd);
+    j.gzx = -j.vp.x * j.iz * j.iz;
+    j.gzy = -j.vp.y * j.iz * j.iz;
+    return true;
+}
+
+__device__ __forceinline__ void project_backward_apply(const PointJac& j, float2 grad, const Camera& cam, const float cropK[5],
+                                                       bool want_intrinsics, BackOut& o)
+{
     const float* R = cam.R;
-    float iz = 1.f / vp.z;
-    float2 np = make_float2(vp.x / vp.z, vp.y / vp.z);
-    float Jpd[4] = {1.f, 0.f, 0.f, 1.f}, Jdd[16];
-    float2 dp = np;
-    if (cam.has_dist || want_intrinsics)
-        dp = distort<true>(np, cam.dist, dist_cutoff, Jpd, Jdd);
+    const float3 vp = j.vp;
     // grad_p_rot = rot^T grad ; grad_p_k2 = J_p_K2^T grad_p_rot ; then J_p_K1^T, J_p_dis^T, J_div^T
     float2 g_rot = make_float2(cam.rot[0] * grad.x + cam.rot[2] * grad.y, cam.rot[1] * grad.x + cam.rot[3] * grad.y);
     float2 g_k2  = make_float2(cropK[0] * g_rot.x + 0.f * g_rot.y, cropK[4] * g_rot.x + cropK[1] * g_rot.y);
     float2 g_k1  = make_float2(cam.K[0] * g_k2.x + 0.f * g_k2.y, cam.K[4] * g_k2.x + cam.K[1] * g_k2.y);
-    float2 g_dis = make_float2(Jpd[0] * g_k1.x + Jpd[2] * g_k1.y, Jpd[1] * g_k1.x + Jpd[3] * g_k1.y);
-    float gv0 = iz * g_dis.x + 0.f * g_dis.y;
-    float gv1 = 0.f * g_dis.x + iz * g_dis.y;
-    float gv2 = (-vp.x * iz * iz) * g_dis.x + (-vp.y * iz * iz) * g_dis.y;
+    float2 g_dis = make_float2(j.Jpd[0] * g_k1.x + j.Jpd[2] * g_k1.y, j.Jpd[1] * g_k1.x + j.Jpd[3] * g_k1.y);
+    float gv0 = j.iz * g_dis.x + 0.f * g_dis.y;
+    float gv1 = 0.f * g_dis.x + j.iz * g_dis.y;
+    float gv2 = j.gzx * g_dis.x + j.gzy * g_dis.y;
     for (int k = 0; k < 3; ++k) o.g_point[k] = R[0 + k] * gv0 + R[3 + k] * gv1 + R[6 + k] * gv2;
     // J_pose = [ I | -skew(vp) ]
     o.g_pose[0] = gv0;
@@ -234,13 +252,21 @@ __device__ __forceinline__ bool project_backward(const float4 pos, float2 grad, 
     o.g_pose[5] = (-vp.y) * gv0 + vp.x * gv1 + 0.f * gv2;
     if (want_intrinsics)
     {
-        o.g_k[0] = dp.x * g_k2.x;
-        o.g_k[1] = dp.y * g_k2.y;
+        o.g_k[0] = j.dp.x * g_k2.x;
+        o.g_k[1] = j.dp.y * g_k2.y;
         o.g_k[2] = g_k2.x;
         o.g_k[3] = g_k2.y;
-        o.g_k[4] = dp.y * g_k2.x;
-        for (int k = 0; k < 8; ++k) o.g_dis[k] = Jdd[k] * g_k1.x + Jdd[8 + k] * g_k1.y;
+        o.g_k[4] = j.dp.y * g_k2.x;
+        for (int k = 0; k < 8; ++k) o.g_dis[k] = j.Jdd[k] * g_k1.x + j.Jdd[8 + k] * g_k1.y;
     }
+}
+
+__device__ __forceinline__ bool project_backward(const float4 pos, float2 grad, const Camera& cam, const float cropK[5],
+                                                 float dist_cutoff, bool want_intrinsics, BackOut& o)
+{
+    PointJac j;
+    if (!project_backward_prepare(pos, cam, dist_cutoff, want_intrinsics, j)) return false;
+    project_backward_apply(j, grad, cam, cropK, want_intrinsics, o);
     return true;
 }
 

@@ -61,7 +61,21 @@ class FragmentLists:
         n_items = int(L.lib().vetr_item_table_entries(self.capacity, n_pixels_total))
         self.items = torch.empty(n_items, **i32)
         self.c = L.Lists(self.counts.data_ptr(), self.ends.data_ptr(), self.frags.data_ptr(), self.capacity,
-                         self.status.data_ptr(), self.items.data_ptr(), n_items)
+                         self.status.data_ptr(), self.items.data_ptr(), n_items, None, None)
+        self.level_mask = None
+        self.point_grad = None
+
+    def ensure_level_mask(self, n_entries: int):
+        """[n_views*n] bytes written by the forward pass (which levels of a view hold a fragment of a point)."""
+        if self.level_mask is None or self.level_mask.numel() < n_entries:
+            self.level_mask = torch.empty(max(n_entries, 1), dtype=torch.uint8, device=self.counts.device)
+            self.c.level_mask = self.level_mask.data_ptr()
+
+    def ensure_point_grad(self, n_floats: int):
+        """[n_views*num_layers*n*2] floats of backward scratch (image-space gradient per fragment)."""
+        if self.point_grad is None or self.point_grad.numel() < n_floats:
+            self.point_grad = torch.empty(max(n_floats, 1), dtype=torch.float32, device=self.counts.device)
+            self.c.point_grad = self.point_grad.data_ptr()
 
 
 class Rasterizer:
@@ -150,6 +164,8 @@ class Rasterizer:
             nb = b1 - b0
             cap = capacity if capacity is not None else int(lib.vetr_max_fragments(position.shape[0], nb, C.byref(prm)))
             lists = self._lists(gi, P * nb, cap, exact=capacity is not None)
+            if prm.render_mode in (1, 2) and prm.need_point_gradient:
+                lists.ensure_level_mask(nb * position.shape[0])
             varr = self._views(views[b0:b1])
             sl = lambda ts: None if ts is None else [t[b0:b1] for t in ts]
             dro = None if dropout is None else dropout[b0:b1]
@@ -217,6 +233,8 @@ class Rasterizer:
             oc = [t[b0:b1] for t in s["color"]]
             gc = [t[b0:b1] for t in grad_color]
             dro = s["tensors"][7]
+            if lists.level_mask is not None:
+                lists.ensure_point_grad((b1 - b0) * s["prm"].num_layers * n * 2)
             rc = lib.vetr_backward(self._ctx, C.byref(s["prm"]), C.byref(s["cloud"]), C.byref(s["tex"]),
                                    C.byref(s["cams"]), varr, b1 - b0, _ptr(None if dro is None else dro[b0:b1]),
                                    C.byref(lists.c), _ptr_array(oc), _ptr_array(gc),

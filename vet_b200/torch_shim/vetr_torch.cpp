@@ -85,11 +85,11 @@ Inputs make_inputs(const RenderScene& s)
 
 struct GroupLists
 {
-    torch::Tensor counts, ends, frags, status, items;
+    torch::Tensor counts, ends, frags, status, items, level_mask;
     vetr_lists c;
 };
 
-GroupLists alloc_lists(int64_t n_pixels, int64_t capacity, const torch::Device& dev)
+GroupLists alloc_lists(int64_t n_pixels, int64_t capacity, int64_t mask_entries, const torch::Device& dev)
 {
     auto i32 = torch::TensorOptions().device(dev).dtype(torch::kInt32);
     GroupLists g;
@@ -99,8 +99,9 @@ GroupLists alloc_lists(int64_t n_pixels, int64_t capacity, const torch::Device& 
     g.status = torch::zeros({4}, i32);
     int64_t n_items = vetr_item_table_entries(capacity, n_pixels);
     g.items  = torch::empty({n_items}, i32);
+    g.level_mask = torch::empty({std::max<int64_t>(mask_entries, 1)}, i32.dtype(torch::kUInt8));
     g.c = {g.counts.data_ptr<int>(), g.ends.data_ptr<int>(), g.frags.data_ptr(), capacity, g.status.data_ptr<int>(),
-           g.items.data_ptr<int>(), n_items};
+           g.items.data_ptr<int>(), n_items, g.level_mask.data_ptr<uint8_t>(), nullptr};
     return g;
 }
 
@@ -206,14 +207,17 @@ variable_list PointRender::forward(AutogradContext* ctx, Variable texture, Varia
     for (int b0 = 0; b0 < B; b0 += VETR_MAX_VIEWS, ++n_groups)
     {
         const int b1 = std::min(B, b0 + VETR_MAX_VIEWS), nb = b1 - b0;
-        GroupLists g = alloc_lists(P * nb, vetr_max_fragments(in.cloud.n, nb, &prm), dev);
+        const bool point_pass = (prm.render_mode == VETR_MODE_FULL_BLEND || prm.render_mode == VETR_MODE_FUZZY_BLEND) &&
+                                prm.need_point_gradient;
+        GroupLists g = alloc_lists(P * nb, vetr_max_fragments(in.cloud.n, nb, &prm),
+                                   point_pass ? (int64_t)nb * in.cloud.n : 0, dev);
         auto views   = make_views(*info, b0, b1);
         auto pc = level_ptrs(color, b0), pw = level_ptrs(weight, b0), pd = level_ptrs(depth, b0), pm = level_ptrs(mask, b0);
         check(vetr_forward(vc, &prm, &in.cloud, &in.tex, &in.cams, views.data(), nb,
                            dropout.defined() ? dropout.data_ptr<float>() + (int64_t)b0 * dropout.stride(0) : nullptr, &g.c,
                            pc.data(), pw.data(), mask.empty() ? nullptr : pm.data(), pd.data()),
               "vetr_forward");
-        for (auto& t : {g.counts, g.ends, g.frags, g.status, g.items}) saved.push_back(t);
+        for (auto& t : {g.counts, g.ends, g.frags, g.status, g.items, g.level_mask}) saved.push_back(t);
     }
     ctx->saved_data["n_groups"] = n_groups;
     ctx->save_for_backward(saved);
@@ -238,7 +242,7 @@ variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_out
     Inputs in             = make_inputs(s);
     auto saved            = ctx->get_saved_variables();
     const int n_groups    = (int)ctx->saved_data["n_groups"].toInt();
-    TORCH_CHECK((int)saved.size() == 5 + L + 5 * n_groups);
+    TORCH_CHECK((int)saved.size() == 5 + L + 6 * n_groups);
 
     std::vector<torch::Tensor> color(saved.begin() + 5, saved.begin() + 5 + L), gcolor;
     for (int l = 0; l < L; ++l)
@@ -266,9 +270,14 @@ variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_out
     for (int gi = 0, b0 = 0; gi < n_groups; ++gi, b0 += VETR_MAX_VIEWS)
     {
         const int b1 = std::min(B, b0 + VETR_MAX_VIEWS), nb = b1 - b0;
-        auto* t = &saved[5 + L + 5 * gi];
+        auto* t = &saved[5 + L + 6 * gi];
+        // scratch of the per-point pass that forms the position / pose / intrinsics gradients of modes 1 and 2
+        torch::Tensor point_grad;
+        if ((prm.render_mode == VETR_MODE_FULL_BLEND || prm.render_mode == VETR_MODE_FUZZY_BLEND) && prm.need_point_gradient)
+            point_grad = torch::empty({(int64_t)nb * L * n * 2}, f32);
         vetr_lists lists = {t[0].data_ptr<int>(), t[1].data_ptr<int>(), t[2].data_ptr(), t[2].size(0), t[3].data_ptr<int>(),
-                            t[4].data_ptr<int>(), t[4].size(0)};
+                            t[4].data_ptr<int>(), t[4].size(0), t[5].data_ptr<uint8_t>(),
+                            point_grad.defined() ? point_grad.data_ptr<float>() : nullptr};
         auto views = make_views(*info, b0, b1);
         auto pc = level_ptrs(color, b0), pg = level_ptrs(gcolor, b0);
         std::vector<const float*> cpc(pc.begin(), pc.end()), cpg(pg.begin(), pg.end());
