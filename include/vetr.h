@@ -133,6 +133,9 @@ typedef struct vetr_lists
                               as in ProjectPointPinholeBackward, summed per point in a fixed order, no atomics on g_points).
                               Both arrays are required by vetr_backward in modes 1 and 2 when need_point_gradient is set;
                               level_mask must be the one the forward call wrote.  Neither needs initialising. */
+    float*    pixel_scratch; /* [n_views*P*8] 16-byte aligned scratch of vetr_backward in modes 1-3: channel-interleaved
+                                copies of out_color and grad_color over the pixel space (eight 16-byte loads fetch all
+                                neighbour values of a fragment).  Needs no initialising. */
 } vetr_lists;
 
 typedef struct vetr_ctx vetr_ctx;

@@ -47,7 +47,7 @@ def test_struct_sizes_match_the_header():
     assert C.sizeof(L.Params) == 76
     assert C.sizeof(L.View) == 56
     assert C.sizeof(L.Cloud) == 24 and C.sizeof(L.Texture) == 32 and C.sizeof(L.Cameras) == 24
-    assert C.sizeof(L.Lists) == 72
+    assert C.sizeof(L.Lists) == 80
 
 
 def test_create_without_gpu_reports_cuda_error():

@@ -50,7 +50,8 @@ class Cameras(C.Structure):
 class Lists(C.Structure):
     _fields_ = [("counts", C.c_void_p), ("ends", C.c_void_p), ("frags", C.c_void_p), ("capacity", C.c_int64),
                 ("status", C.c_void_p), ("items", C.c_void_p), ("items_capacity", C.c_int64),
-                ("level_mask", C.c_void_p), ("point_grad", C.c_void_p)]
+                ("level_mask", C.c_void_p), ("point_grad", C.c_void_p),
+                ("pixel_scratch", C.c_void_p)]
 
 
 EXPORTS = [

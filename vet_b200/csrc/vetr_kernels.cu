@@ -97,6 +97,8 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
     int* item_start;  // [n_items + 1]
     unsigned char* level_mask;  // [n_views * n]: levels of the view on which the point has a fragment (written by collect)
     float2* point_grad;         // [(view * L + level) * n + point]: image-space gradient of that fragment (backward scratch)
+    float4* img4;               // [PT] forward image, channels interleaved, indexed like counts[] (backward scratch)
+    float4* grad4;              // [PT] its incoming gradient
 };
 
 // One fragment record = one 32-byte sector.
@@ -445,7 +447,7 @@ struct PixInfo  // decoded pixel of the global pixel space, 8 bytes
 {
     short x, y;
     unsigned char level, view;
-    unsigned short pad;
+    unsigned short interior;  // ImageView::distanceFromEdge > 2: the pixel takes part in the position gradient
 };
 
 __device__ __forceinline__ PixInfo decode_pixel(const Frame& f, unsigned g)
@@ -461,7 +463,9 @@ __device__ __forceinline__ PixInfo decode_pixel(const Frame& f, unsigned g)
     q -= (unsigned)f.lbase[l];
     unsigned w = (unsigned)f.lw[l];
     unsigned y = q / w;
-    r.x = (short)(q - y * w), r.y = (short)y, r.level = (unsigned char)l, r.view = (unsigned char)view, r.pad = 0;
+    r.x = (short)(q - y * w), r.y = (short)y, r.level = (unsigned char)l, r.view = (unsigned char)view;
+    const int h = f.lh[l];
+    r.interior  = min(min((int)r.x, (int)w - 1 - r.x), min((int)r.y, h - 1 - r.y)) > 2;
     return r;
 }
 
@@ -1022,54 +1026,54 @@ __device__ __forceinline__ void spatial_backward(const Frame& f, const BackPtrs&
     if (bp.g_points) red_add_v4(bp.g_points + pid, make_float4(bo.g_point[0], bo.g_point[1], bo.g_point[2], 1.f));
 }
 
-// Mode 1: approximate image-space gradient of a fragment from the neighbouring pixels (RenderBackward.cu:1347-1374).
-// (Staging the neighbour values once per pixel in shared memory was measured slower: it serialises 36 loads in the
-// few threads that own pixels and costs occupancy; the per-fragment loads below hit L1.)
-__device__ __forceinline__ float2 neighbour_gradient(const Frame& f, const BackPtrs& bp, const PixInfo& px, float4 d)
+// Modes 1 and 2: approximate image-space gradient of a fragment from the neighbouring pixels
+// (RenderBackward.cu:1347-1374).  `g` is the pixel in the global pixel space; the images are the channel-interleaved
+// copies pack_images_kernel makes, so the eight neighbour values of all channels are eight 16-byte loads.
+__device__ __forceinline__ float2 neighbour_gradient(const Frame& f, int g, int w, float4 d)
 {
-    const int w = f.lw[px.level], h = f.lh[px.level];
-    const int hw = w * h;
-    const int o  = (px.view * f.C) * hw + px.y * w + px.x;
-    const float* I  = bp.out_color[px.level] + o;
-    const float* Gp = bp.grad_color[px.level] + o;
-    float dx = 0.f, dy = 0.f;
+    const float4* I  = f.img4 + g;
+    const float4* Gp = f.grad4 + g;
+    const float4 il = __ldg(I - 1), ir = __ldg(I + 1), iu = __ldg(I - w), id = __ldg(I + w);
+    const float4 gl = __ldg(Gp - 1), gr = __ldg(Gp + 1), gu = __ldg(Gp - w), gd = __ldg(Gp + w);
     const float dv[4] = {d.x, d.y, d.z, d.w};
+    const float Il[4] = {il.x, il.y, il.z, il.w}, Ir[4] = {ir.x, ir.y, ir.z, ir.w};
+    const float Iu[4] = {iu.x, iu.y, iu.z, iu.w}, Id[4] = {id.x, id.y, id.z, id.w};
+    const float Gl[4] = {gl.x, gl.y, gl.z, gl.w}, Gr[4] = {gr.x, gr.y, gr.z, gr.w};
+    const float Gu[4] = {gu.x, gu.y, gu.z, gu.w}, Gd[4] = {gd.x, gd.y, gd.z, gd.w};
+    float dx = 0.f, dy = 0.f;
 #pragma unroll
     for (int ci = 0; ci < 4; ++ci)
     {
         if (ci < f.C)
         {
-            const float* Ic = I + ci * hw;
-            const float* Gc = Gp + ci * hw;
             float Tp = dv[ci];
-            float a0 = -(Tp - __ldg(Ic - 1)) * __ldg(Gc - 1);
-            float a1 = (Tp - __ldg(Ic + 1)) * __ldg(Gc + 1);
-            float b0 = -(Tp - __ldg(Ic - w)) * __ldg(Gc - w);
-            float b1 = (Tp - __ldg(Ic + w)) * __ldg(Gc + w);
+            float a0 = -(Tp - Il[ci]) * Gl[ci];
+            float a1 = (Tp - Ir[ci]) * Gr[ci];
+            float b0 = -(Tp - Iu[ci]) * Gu[ci];
+            float b1 = (Tp - Id[ci]) * Gd[ci];
             dx += 0.5f * (a0 + a1);
             dy += 0.5f * (b0 + b1);
         }
     }
-    return make_float2(dx / (float)f.C, dy / (float)f.C);
+    // x / 4 and x * 0.25 round alike
+    return f.C == 4 ? make_float2(dx * 0.25f, dy * 0.25f) : make_float2(dx / (float)f.C, dy / (float)f.C);
 }
 
-__device__ __forceinline__ bool is_interior(const Frame& f, const PixInfo& px)  // ImageView::distanceFromEdge > 2
-{
-    const int w = f.lw[px.level], h = f.lh[px.level];
-    return min(min((int)px.x, w - 1 - px.x), min((int)px.y, h - 1 - px.y)) > 2;
-}
+__device__ __forceinline__ float4 load_grad(const Frame& f, int g) { return __ldg(f.grad4 + g); }
 
-__device__ __forceinline__ float4 load_grad(const Frame& f, const BackPtrs& bp, const PixInfo& px)
+// Channel-interleaved copies of the forward image and of its gradient over the global pixel space (the caller's
+// tensors are planar [view, channel, y, x] per level).
+__global__ void __launch_bounds__(256) pack_images_kernel(const __grid_constant__ Frame f, const __grid_constant__ BackPtrs bp)
 {
-    const int w = f.lw[px.level], h = f.lh[px.level];
-    const int hw = w * h;
-    const float* G = bp.grad_color[px.level] + (px.view * f.C) * hw + px.y * w + px.x;
-    float4 g;
-    g.x = __ldg(G);
-    g.y = __ldg(G + hw);
-    g.z = __ldg(G + 2 * hw);
-    g.w = f.C > 3 ? __ldg(G + 3 * hw) : 0.f;
-    return g;
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= f.PT) return;
+    const PixInfo px = decode_pixel(f, (unsigned)g);
+    const int w = f.lw[px.level], hw = w * f.lh[px.level];
+    const int o = (px.view * f.C) * hw + px.y * w + px.x;
+    const float* I = bp.out_color[px.level] + o;
+    const float* G = bp.grad_color[px.level] + o;
+    f.img4[g]  = make_float4(__ldg(I), __ldg(I + hw), __ldg(I + 2 * hw), f.C > 3 ? __ldg(I + 3 * hw) : 0.f);
+    f.grad4[g] = make_float4(__ldg(G), __ldg(G + hw), __ldg(G + 2 * hw), f.C > 3 ? __ldg(G + 3 * hw) : 0.f);
 }
 
 __device__ __forceinline__ float dot4(float4 a, float4 b, int C)
@@ -1091,8 +1095,8 @@ constexpr int kNoGradientBits = 0x7fffffff;
 // gradient is parked under (view, level, point); point_backward_kernel turns it into position / camera gradients with
 // coalesced position loads and without atomics, instead of a position gather per fragment here.
 template <bool kBilinear>
-__device__ __forceinline__ void fragment_stage_a(const Frame& f, const BackPtrs& bp, BackSmem& s, const PixInfo& px, float4 G,
-                                                 int slot, int gslot, bool blended, float4* desc_out = nullptr,
+__device__ __forceinline__ void fragment_stage_a(const Frame& f, BackSmem& s, int g, const PixInfo& px, float4 G, int slot,
+                                                 int gslot, bool blended, float4* desc_out = nullptr,
                                                  float* depth_out = nullptr)
 {
     const uint4 h  = f.recs[2 * (size_t)gslot];
@@ -1106,7 +1110,7 @@ __device__ __forceinline__ void fragment_stage_a(const Frame& f, const BackPtrs&
     if (!kBilinear && f.need_point_grad)
     {
         float2 dR = make_float2(__int_as_float(kNoGradientBits), 0.f);
-        if (blended && is_interior(f, px)) dR = neighbour_gradient(f, bp, px, d);
+        if (blended && px.interior) dR = neighbour_gradient(f, g, f.lw[px.level], d);
         f.point_grad[((size_t)px.view * f.L + px.level) * f.n + pid] = dR;
     }
 }
@@ -1123,7 +1127,7 @@ __device__ __forceinline__ void fragment_stage_b(const Frame& f, const BackPtrs&
         red_add(bp.g_conf + tex, galpha);
         return;
     }
-    if (!is_interior(f, px)) return;  // the reference writes the mode-3 confidence gradient for interior pixels only
+    if (!px.interior) return;  // the reference writes the mode-3 confidence gradient for interior pixels only
     float4 pos;
     float2 ip = level_position(f, cam, pid, px.level, &pos);
     float jx, jy;
@@ -1343,7 +1347,7 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
                 s.seg_end[tid + 1] = se;
                 const PixInfo px   = decode_pixel(f, (unsigned)(lo + tid));
                 s.pix[tid]         = px;
-                s.grad[tid]        = load_grad(f, bp, px);
+                s.grad[tid]        = load_grad(f, lo + tid);
                 seg_fill(s.seg, parity, tid, ss, se);
             }
             if (tid == 0) s.seg_end[0] = 0;
@@ -1356,9 +1360,9 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
                 const int a = seg_lookup(s.seg, parity, s.seg_end, i);
                 const bool blended = f.dbg_max_len <= 0 || i - s.seg_end[a] < f.dbg_max_len;  // list truncation
                 if constexpr (kFuzzy)
-                    fragment_stage_a<false>(f, bp, s, s.pix[a], s.grad[a], i, f0 + i, blended, s.desc, s.depth);
+                    fragment_stage_a<false>(f, s, lo + a, s.pix[a], s.grad[a], i, f0 + i, blended, s.desc, s.depth);
                 else
-                    fragment_stage_a<kBilinear>(f, bp, s, s.pix[a], s.grad[a], i, f0 + i, blended);
+                    fragment_stage_a<kBilinear>(f, s, lo + a, s.pix[a], s.grad[a], i, f0 + i, blended);
             }
             __syncthreads();
             PHASE_MARK(2);
@@ -1417,7 +1421,7 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
         const PixInfo px = decode_pixel(f, (unsigned)lo);
         __syncthreads();
         if (kBilinear && tid == 0) s.cam[0] = load_camera(f, px.view);
-        const float4 G = load_grad(f, bp, px);
+        const float4 G = load_grad(f, lo);
         int cnt = n;
         if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
         cnt = min(cnt, 256 * kCap);
@@ -1468,7 +1472,7 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
         {
             const int m = min(kCap, eff_cnt - blk * kCap);
             for (int i = tid; i < m; i += kThreads)
-                fragment_stage_a<kBilinear>(f, bp, s, px, G, i, e0 + blk * kCap + i, true);
+                fragment_stage_a<kBilinear>(f, s, lo, px, G, i, e0 + blk * kCap + i, true);
             __syncthreads();
             if (tid == 0)
             {
@@ -1542,9 +1546,9 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
             continue;
         }
         const PixInfo px = decode_pixel(f, (unsigned)lo);
-        const float4 G = load_grad(f, bp, px);
+        const float4 G = load_grad(f, lo);
         __syncthreads();  // every warp has left the previous list
-        const bool spatial = is_interior(f, px);
+        const bool spatial = px.interior;
         for (int i = tid; i < n; i += kThreads)
         {
             const uint4 h  = f.recs[2 * (size_t)(e0 + i)];
@@ -1554,7 +1558,7 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
             const bool blended = f.dbg_max_len <= 0 || i < f.dbg_max_len;
             if (f.need_point_grad)
                 f.point_grad[((size_t)px.view * f.L + px.level) * f.n + (int)h.x] =
-                    spatial && blended ? neighbour_gradient(f, bp, px, d) : make_float2(__int_as_float(kNoGradientBits), 0.f);
+                    spatial && blended ? neighbour_gradient(f, lo, f.lw[px.level], d) : make_float2(__int_as_float(kNoGradientBits), 0.f);
         }
         __syncthreads();
         if (tid == 0) sweep_list_fuzzy(f, s.alpha, s.dot, s.trans, s.desc, s.depth, s.gv, s.gfirst, 0, n, G, bgc, bg_acc);
@@ -1658,6 +1662,48 @@ __global__ void __launch_bounds__(kProjThreads) point_backward_kernel(const __gr
 // Mode 0 (FUZZY_DT): no lists.  Per pixel: nearest depth (int bits, in `ends`), accumulators in the fragment buffer
 // (record g: float4 descriptor sum, then the number of accepted points as a float), count of accepted points (`counts`).
 
+// Mode 0 reads the caller's planar images directly (its backward pass is point-parallel: one fragment per point).
+__device__ __forceinline__ float2 neighbour_gradient_planar(const Frame& f, const BackPtrs& bp, const PixInfo& px, float4 d)
+{
+    const int w = f.lw[px.level], h = f.lh[px.level];
+    const int hw = w * h;
+    const int o  = (px.view * f.C) * hw + px.y * w + px.x;
+    const float* I  = bp.out_color[px.level] + o;
+    const float* Gp = bp.grad_color[px.level] + o;
+    float dx = 0.f, dy = 0.f;
+    const float dv[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+    for (int ci = 0; ci < 4; ++ci)
+    {
+        if (ci < f.C)
+        {
+            const float* Ic = I + ci * hw;
+            const float* Gc = Gp + ci * hw;
+            float Tp = dv[ci];
+            float a0 = -(Tp - __ldg(Ic - 1)) * __ldg(Gc - 1);
+            float a1 = (Tp - __ldg(Ic + 1)) * __ldg(Gc + 1);
+            float b0 = -(Tp - __ldg(Ic - w)) * __ldg(Gc - w);
+            float b1 = (Tp - __ldg(Ic + w)) * __ldg(Gc + w);
+            dx += 0.5f * (a0 + a1);
+            dy += 0.5f * (b0 + b1);
+        }
+    }
+    return make_float2(dx / (float)f.C, dy / (float)f.C);
+}
+
+__device__ __forceinline__ float4 load_grad_planar(const Frame& f, const BackPtrs& bp, const PixInfo& px)
+{
+    const int w = f.lw[px.level], h = f.lh[px.level];
+    const int hw = w * h;
+    const float* G = bp.grad_color[px.level] + (px.view * f.C) * hw + px.y * w + px.x;
+    float4 g;
+    g.x = __ldg(G);
+    g.y = __ldg(G + hw);
+    g.z = __ldg(G + 2 * hw);
+    g.w = f.C > 3 ? __ldg(G + 3 * hw) : 0.f;
+    return g;
+}
+
 __global__ void fill_int_kernel(int* p, int v, long long n)
 {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1754,7 +1800,7 @@ __global__ void __launch_bounds__(256) fuzzy_dt_background_kernel(const __grid_c
     for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < f.PT; g += (long long)gridDim.x * blockDim.x)
         if (f.counts[g] == 0)
         {
-            const float4 G = load_grad(f, bp, decode_pixel(f, (unsigned)g));
+            const float4 G = load_grad_planar(f, bp, decode_pixel(f, (unsigned)g));
             v[0] += G.x, v[1] += G.y, v[2] += G.z, v[3] += G.w;
         }
     for (int k = 0; k < 4; ++k)
@@ -1809,16 +1855,17 @@ __global__ void __launch_bounds__(kProjThreads) fuzzy_dt_backward_kernel(const _
                 if (w == 0.f) continue;
                 if (pr.z > __int_as_float(f.ends[g]) * (f.depth_accept + 1)) continue;
                 PixInfo px;
-                px.x = (short)x, px.y = (short)y, px.level = (unsigned char)l, px.view = (unsigned char)b, px.pad = 0;
+                px.x = (short)x, px.y = (short)y, px.level = (unsigned char)l, px.view = (unsigned char)b;
+                px.interior = min(min(x, f.lw[l] - 1 - x), min(y, f.lh[l] - 1 - y)) > 2;
                 if (!drop_out)
                 {
                     const float iw = 1.f / w;
-                    const float4 G = load_grad(f, bp, px);
+                    const float4 G = load_grad_planar(f, bp, px);
                     red_add_v4(bp.g_desc + tex, make_float4(iw * G.x, iw * G.y, iw * G.z, f.C > 3 ? iw * G.w : 0.f));
                 }
                 const bool point_grad = (f.ghost && drop_out) | (!f.ghost && !drop_out);
-                if (!(point_grad && is_interior(f, px))) continue;
-                spatial_backward<kIntr>(f, bp, cam, px, pid, pos, neighbour_gradient(f, bp, px, load_descriptor(f, tex)), acc);
+                if (!(point_grad && px.interior)) continue;
+                spatial_backward<kIntr>(f, bp, cam, px, pid, pos, neighbour_gradient_planar(f, bp, px, load_descriptor(f, tex)), acc);
             }
         }
     }
@@ -2196,6 +2243,8 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     f.item_start = lists->items;
     f.level_mask = lists->level_mask;
     f.point_grad = (float2*)lists->point_grad;
+    f.img4       = (float4*)lists->pixel_scratch;
+    f.grad4      = f.img4 ? f.img4 + f.PT : nullptr;
     return VETR_OK;
 }
 
@@ -2321,9 +2370,11 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
     const bool point_pass = !bilinear && f.need_point_grad && (bp.g_points || g_pose || g_intr);
     if (!bilinear && !point_pass) f.need_point_grad = 0;
     if (point_pass && (!f.level_mask || !f.point_grad)) return VETR_E_INVALID_ARG;
+    if (!f.img4 || ((uintptr_t)f.img4 & 15) != 0) return VETR_E_INVALID_ARG;
     {
-        PassScope t(ctx, VETR_T_BACKWARD, 2);
+        PassScope t(ctx, VETR_T_BACKWARD, 3);
         cudaStream_t st = ctx->stream;
+        pack_images_kernel<<<(unsigned)((f.PT + 255) / 256), 256, 0, st>>>(f, bp);
         if (f.mode == VETR_MODE_FUZZY_BLEND)
         {
             const int grid = ctx->sm_count * ctx->fuzzy_ctas_per_sm;

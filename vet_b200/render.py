@@ -61,9 +61,17 @@ class FragmentLists:
         n_items = int(L.lib().vetr_item_table_entries(self.capacity, n_pixels_total))
         self.items = torch.empty(n_items, **i32)
         self.c = L.Lists(self.counts.data_ptr(), self.ends.data_ptr(), self.frags.data_ptr(), self.capacity,
-                         self.status.data_ptr(), self.items.data_ptr(), n_items, None, None)
+                         self.status.data_ptr(), self.items.data_ptr(), n_items, None, None, None)
         self.level_mask = None
         self.point_grad = None
+        self.pixel_scratch = None
+        self.n_pixels_total = n_pixels_total
+
+    def ensure_pixel_scratch(self):
+        """[n_pixels*8] floats of backward scratch (channel-interleaved forward image and its gradient)."""
+        if self.pixel_scratch is None:
+            self.pixel_scratch = torch.empty(max(self.n_pixels_total, 1) * 8, dtype=torch.float32, device=self.counts.device)
+            self.c.pixel_scratch = self.pixel_scratch.data_ptr()
 
     def ensure_level_mask(self, n_entries: int):
         """[n_views*n] bytes written by the forward pass (which levels of a view hold a fragment of a point)."""
@@ -233,6 +241,7 @@ class Rasterizer:
             oc = [t[b0:b1] for t in s["color"]]
             gc = [t[b0:b1] for t in grad_color]
             dro = s["tensors"][7]
+            lists.ensure_pixel_scratch()
             if lists.level_mask is not None:
                 lists.ensure_point_grad((b1 - b0) * s["prm"].num_layers * n * 2)
             rc = lib.vetr_backward(self._ctx, C.byref(s["prm"]), C.byref(s["cloud"]), C.byref(s["tex"]),

@@ -101,7 +101,7 @@ GroupLists alloc_lists(int64_t n_pixels, int64_t capacity, int64_t mask_entries,
     g.items  = torch::empty({n_items}, i32);
     g.level_mask = torch::empty({std::max<int64_t>(mask_entries, 1)}, i32.dtype(torch::kUInt8));
     g.c = {g.counts.data_ptr<int>(), g.ends.data_ptr<int>(), g.frags.data_ptr(), capacity, g.status.data_ptr<int>(),
-           g.items.data_ptr<int>(), n_items, g.level_mask.data_ptr<uint8_t>(), nullptr};
+           g.items.data_ptr<int>(), n_items, g.level_mask.data_ptr<uint8_t>(), nullptr, nullptr};
     return g;
 }
 
@@ -275,9 +275,10 @@ variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_out
         torch::Tensor point_grad;
         if ((prm.render_mode == VETR_MODE_FULL_BLEND || prm.render_mode == VETR_MODE_FUZZY_BLEND) && prm.need_point_gradient)
             point_grad = torch::empty({(int64_t)nb * L * n * 2}, f32);
+        torch::Tensor pixel_scratch = torch::empty({std::max<int64_t>(t[0].size(0), 1) * 8}, f32);
         vetr_lists lists = {t[0].data_ptr<int>(), t[1].data_ptr<int>(), t[2].data_ptr(), t[2].size(0), t[3].data_ptr<int>(),
                             t[4].data_ptr<int>(), t[4].size(0), t[5].data_ptr<uint8_t>(),
-                            point_grad.defined() ? point_grad.data_ptr<float>() : nullptr};
+                            point_grad.defined() ? point_grad.data_ptr<float>() : nullptr, pixel_scratch.data_ptr<float>()};
         auto views = make_views(*info, b0, b1);
         auto pc = level_ptrs(color, b0), pg = level_ptrs(gcolor, b0);
         std::vector<const float*> cpc(pc.begin(), pc.end()), cpg(pg.begin(), pg.end());
