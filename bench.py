@@ -48,6 +48,10 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--prewarm", type=float, default=1.0, help="seconds of untimed load before the warm-up steps")
+    ap.add_argument("--views-mode", choices=["same", "distinct"], default="same",
+                    help="N > 1: every rank renders the same V camera poses (identical per-GPU work), or V poses of its own")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="N > 1: how the ranks' gradient buffers are summed (one kernel over peer memory, or NCCL all-reduce)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     return ap.parse_args()
 
@@ -205,8 +209,14 @@ def run_ours(args):
     params = default_params(render_mode=args.mode, num_layers=LAYERS, num_channels=CHANNELS)
 
     # the cloud is replicated; every rank renders its own V views per step (view-sharded batch of world * V views)
-    scene = make_scene(args.points, world * V)
-    my_views = scene.views[rank * V:(rank + 1) * V]
+    if args.views_mode == "same":
+        # weak scaling with identical per-GPU work: every rank renders the same V camera poses (against its own seeded
+        # targets), so the step time at N GPUs differs from N = 1 by the exchange alone, not by which views a rank drew
+        scene = make_scene(args.points, V)
+        my_views = scene.views
+    else:
+        scene = make_scene(args.points, world * V)
+        my_views = scene.views[rank * V:(rank + 1) * V]
     tensors = scene_to_device(scene, dev)
     position, index, texture, confidence, background, poses, intrinsics = tensors
     n, n_tex = position.shape[0], texture.shape[1]
@@ -223,8 +233,17 @@ def run_ours(args):
     numel = [float(t.numel()) for t in targets_host]
     h2d_bytes = sum(t.numel() * 4 for t in targets_host)
 
-    # fused gradient buffer: [desc 4n_tex | points 4n | conf n_tex] floats -> one all-reduce
-    flat = torch.zeros(4 * n_tex + 4 * n + n_tex, dtype=torch.float32, device=dev)
+    # fused gradient buffer: [desc 4n_tex | points 4n | conf n_tex] floats.  N > 1: it lives in symmetric memory and the
+    # sum over the ranks + the epilogue is one kernel over NVLink peer memory (vet_b200.dist.PeerExchange);
+    # --exchange nccl selects an NCCL all-reduce of the buffer followed by the epilogue kernels instead.
+    peer = None
+    exchange_kind = "none" if world == 1 else args.exchange
+    if world > 1 and args.exchange == "peer":
+        from vet_b200.dist import PeerExchange
+        peer = PeerExchange(rast, n, n_tex, CHANNELS, dev)
+        flat = peer.raw
+    else:
+        flat = torch.zeros(4 * n_tex + 4 * n + n_tex, dtype=torch.float32, device=dev)
 
     def grad_views():
         g = dict(desc=flat[:4 * n_tex].view(n_tex, 4), points=flat[4 * n_tex:4 * n_tex + 4 * n].view(n, 4),
@@ -256,15 +275,18 @@ def run_ours(args):
 
     def exchange(g):
         """The one exchange step of view-sharded data parallelism: sum the gradient buffers over the ranks."""
+        if peer is not None:
+            return peer.run(g)  # sum + epilogue in one kernel; returns the finished gradients
         if world > 1:
             dist.all_reduce(flat)
             dist.all_reduce(g["pose"])
             dist.all_reduce(g["pose_count"])
+        return None
 
     def step(targets):
         loss, g = compute(targets)
-        exchange(g)
-        return loss, rast.finalize(g)
+        fin = exchange(g)
+        return loss, (fin if fin is not None else rast.finalize(g))
 
     def barrier():
         if world > 1:
@@ -287,8 +309,9 @@ def run_ours(args):
             graph_a, graph_b = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph_a):
                 loss_static, g_static = compute(static_targets)
-            with torch.cuda.graph(graph_b, pool=graph_a.pool()):
-                fin_static = rast.finalize(g_static)
+            if peer is None:
+                with torch.cuda.graph(graph_b, pool=graph_a.pool()):
+                    fin_static = rast.finalize(g_static)
             torch.cuda.synchronize(dev)
 
             def step(targets):
@@ -297,7 +320,9 @@ def run_ours(args):
                         if dst.data_ptr() != src.data_ptr():
                             dst.copy_(src, non_blocking=True)
                 graph_a.replay()
-                exchange(g_static)
+                fin = exchange(g_static)
+                if fin is not None:
+                    return loss_static, fin
                 graph_b.replay()
                 return loss_static, fin_static
 
@@ -357,6 +382,23 @@ def run_ours(args):
     ms_total = float(t.item())
     frames = world * V * args.steps
     value = frames / (ms_total * 1e-3)
+    # per-rank load (the step time is the max over the ranks): fragments of the rank's views, ms of its compute graph
+    per_rank = None
+    if world > 1:
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        c0.record(stream)
+        for _ in range(3):
+            if graph_info["used"]:
+                graph_a.replay()
+            else:
+                compute(static_targets)
+        c1.record(stream)
+        torch.cuda.synchronize(dev)
+        mine = torch.tensor([float(F_total), c0.elapsed_time(c1) / 3], dtype=torch.float64, device=dev)
+        allr = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        per_rank = [{"fragments": int(t[0].item()), "compute_ms": round(float(t[1].item()), 3)} for t in allr]
 
     # ---- e2e: per-step targets arrive from pinned host memory (prefetched on a copy stream), loss read back
     e2e = None
@@ -428,6 +470,11 @@ def run_ours(args):
         "point_backward": 16 * F + 2 * 16 * touched,
         "finalize": 32 * n_tex + 32 * N,                    # transpose descriptor gradient, normalise point gradient
     }
+    if peer is not None:
+        # the rank reads its 1/world slice of every rank's 36-byte-per-point raw sums and writes the finished slice to
+        # every rank: 2 x 36 bytes per point cross this GPU's links or HBM either way
+        kernel_bytes["exchange"] = 2 * 36 * N
+        kernel_bytes.pop("finalize")
     peak, peak_src = measured_peak()
     kernels = {k: {"ms": acc.get(k, 0.0), "bytes": kernel_bytes[k],
                    "gbs": (kernel_bytes[k] / (acc[k] * 1e-3) / 1e9) if acc.get(k, 0.0) > 0 else None} for k in kernel_bytes}
@@ -459,11 +506,11 @@ def run_ours(args):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"headline: {N} planar-scene points replicated, {V} views {W}x{H} f={FOCAL:g} per GPU and "
                                    f"step, {LAYERS} levels, mode {args.mode}, fwd+bwd, L1 vs seeded target"
-                                   + (", NCCL all-reduce of 9 floats per point" if world > 1 else ""),
-                       "views_per_gpu": V, "points": N, "l2": "inputs larger than L2 (cloud 128 MB + descriptors 160 MB + "
+                                   + (f", gradients of 9 floats per point summed over the ranks ({exchange_kind})" if world > 1 else ""),
+                       "views_per_gpu": V, "views_mode": args.views_mode if world > 1 else None, "points": N, "l2": "inputs larger than L2 (cloud 128 MB + descriptors 160 MB + "
                                                               "pyramids; gradient buffer 288 MB rewritten every step)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
-            "loss": float(loss.item()), "step_ms": [round(x, 3) for x in step_ms], "cuda_graph": graph_info,
+            "loss": float(loss.item()), "step_ms": [round(x, 3) for x in step_ms], "cuda_graph": graph_info, "exchange": exchange_kind, "per_rank": per_rank,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -202,6 +202,30 @@ int vetr_finalize_gradients(vetr_ctx* ctx, int channels, int n_tex, const float*
                             float* g_points, float* g_points_count, int n_img, double* g_pose,
                             const float* g_pose_count, int n_cam, float* g_intr, const float* g_intr_count);
 
+/* View-sharded training on several GPUs of one node (the reference is single-GPU; this has no counterpart there).
+ * Every rank keeps its raw gradient sums of a step in ONE buffer, [descriptor gradient n_tex*4 | position gradient +
+ * hit count n*4 | confidence gradient n_tex] floats (vetr_exchange_raw_floats), in memory its peers can address
+ * (CUDA peer access: IPC or VMM mappings; torch's symmetric memory gives such pointers).  vetr_exchange_finalize is
+ * the sum over the ranks and vetr_finalize_gradients in one kernel over that peer memory: the rank reduces its 1/world
+ * slice of every rank's raw buffer and stores the finished slice (texture gradient [channels, n_tex], position
+ * gradient [n,4] averaged by hit count, confidence gradient [n_tex]; vetr_exchange_out_floats, position segment at
+ * channels*n_tex rounded up to 4 floats) into every rank's output buffer.  It moves the bytes of a reduce-scatter plus
+ * an all-gather and replaces NCCL all-reduce + the epilogue kernels.
+ * Ordering is the caller's: the kernel must start after the backward kernels of ALL ranks have finished and its
+ * outputs may be read after the exchange kernels of ALL ranks have finished - enqueue a collective on the same stream
+ * before and after it (the all-reduce of the pose gradients and of their counts serve).  The kernel itself waits on
+ * nothing.  world = 1 is allowed (a local epilogue). */
+#define VETR_MAX_RANKS 16
+typedef struct vetr_exchange
+{
+    int32_t rank, world;
+    const float* raw[VETR_MAX_RANKS]; /* raw[k]: rank k's raw buffer as seen from this rank, 16-byte aligned */
+    float*       out[VETR_MAX_RANKS]; /* out[k]: rank k's output buffer as seen from this rank, 16-byte aligned */
+} vetr_exchange;
+int64_t vetr_exchange_raw_floats(int n_tex, int n);
+int64_t vetr_exchange_out_floats(int channels, int n_tex, int n);
+int vetr_exchange_finalize(vetr_ctx* ctx, const vetr_exchange* ex, int channels, int n_tex, int n);
+
 /* ApplyTangentToPose (PointRenderer.cu:1325-1349): poses[i] <- exp_se3(tangent[i]) * poses[i]; tangent[i] <- 0. */
 int vetr_apply_tangent(vetr_ctx* ctx, double* tangent /*[n,6]*/, double* poses_se3 /*[n,8]*/, int n);
 
@@ -245,6 +269,7 @@ enum
     VETR_T_BACKWARD,     /* backward */
     VETR_T_FINALIZE,     /* transpose + normalisation kernels */
     VETR_T_POINT_BACKWARD, /* per-point pass of the backward step (modes 1 and 2) */
+    VETR_T_EXCHANGE,     /* vetr_exchange_finalize */
     VETR_T_N
 };
 int vetr_set_timing(vetr_ctx* ctx, int enable);

@@ -54,13 +54,21 @@ class Lists(C.Structure):
                 ("pixel_scratch", C.c_void_p)]
 
 
+MAX_RANKS = 16
+
+
+class Exchange(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("raw", C.c_void_p * MAX_RANKS), ("out", C.c_void_p * MAX_RANKS)]
+
+
 EXPORTS = [
     "vetr_create", "vetr_destroy", "vetr_set_stream", "vetr_strerror", "vetr_last_cuda_error", "vetr_pyramid_pixels",
     "vetr_item_table_entries", "vetr_max_fragments", "vetr_forward", "vetr_backward", "vetr_finalize_gradients",
     "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists", "vetr_set_timing", "vetr_get_timings",
-    "vetr_launch_count", "vetr_scan_counts_static",
+    "vetr_launch_count", "vetr_scan_counts_static", "vetr_exchange_raw_floats", "vetr_exchange_out_floats",
+    "vetr_exchange_finalize",
 ]
-TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize", "point_backward"]
+TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize", "point_backward", "exchange"]
 
 _lib = None
 
@@ -108,5 +116,10 @@ def lib():
         L.vetr_launch_count.argtypes = [vp]
         L.vetr_launch_count.restype = C.c_int64
         L.vetr_scan_counts_static.argtypes = [C.c_int, vp, vp, C.c_int64, C.c_int64, vp, vp, vp, C.c_int64]
+        L.vetr_exchange_raw_floats.argtypes = [C.c_int, C.c_int]
+        L.vetr_exchange_raw_floats.restype = C.c_int64
+        L.vetr_exchange_out_floats.argtypes = [C.c_int, C.c_int, C.c_int]
+        L.vetr_exchange_out_floats.restype = C.c_int64
+        L.vetr_exchange_finalize.argtypes = [vp, C.POINTER(Exchange), C.c_int, C.c_int, C.c_int]
         _lib = L
     return _lib

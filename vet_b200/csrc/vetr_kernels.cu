@@ -1961,6 +1961,96 @@ __global__ void apply_tangent_kernel(double* tangent, double* poses, int n)
     for (int k = 0; k < 6; ++k) t[k] = 0.0;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Multi-GPU epilogue: sum of the raw gradient buffers of all ranks + the count normalisation + the channel-major
+// transpose, in one kernel over peer memory.  Every rank owns one contiguous slice of each of the three segments
+// (descriptor, position, confidence gradients): it reads that slice from every rank's raw buffer (peer loads over
+// NVLink, summed in rank order, so every rank ends up with the same bits), finalises it and stores the result into
+// every rank's output buffer (peer stores).  The kernel waits on nothing: the caller orders it after the backward
+// kernels of ALL ranks and orders the consumers after the exchange kernels of ALL ranks (a collective on the same
+// stream before and after, e.g. the all-reduce of the pose gradients and of their counts).
+
+struct ExchangeArgs
+{
+    int rank, world, C, n_tex, n;
+    long long out_points, out_conf;  // float offsets of the position / confidence segments in the output buffers
+    const float* raw[VETR_MAX_RANKS];
+    float* out[VETR_MAX_RANKS];
+};
+
+__device__ __forceinline__ void slice_of(long long count, int rank, int world, long long& lo, long long& hi)
+{
+    lo = count * rank / world;
+    hi = count * (rank + 1) / world;
+}
+
+// Sum over the ranks of element i of a segment that starts `offset` floats into every raw buffer.  The kExchangeUnroll
+// elements a thread handles per step are loaded from all ranks before the first is used (peer loads have microseconds
+// of latency: bytes in flight are what fills the links).
+constexpr int kExchangeUnroll = 4;
+
+template <typename T>
+__device__ __forceinline__ T add_vec(T a, T b);
+template <>
+__device__ __forceinline__ float4 add_vec(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+template <>
+__device__ __forceinline__ float add_vec(float a, float b) { return a + b; }
+
+template <typename T, typename Store>
+__device__ __forceinline__ void exchange_segment(const ExchangeArgs& a, long long offset, long long count, Store store)
+{
+    const long long gtid   = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long lo, hi;
+    slice_of(count, a.rank, a.world, lo, hi);
+    for (long long base = lo + gtid; base < hi; base += stride * kExchangeUnroll)
+    {
+        T v[kExchangeUnroll];
+#pragma unroll
+        for (int u = 0; u < kExchangeUnroll; ++u) v[u] = T();
+        for (int k = 0; k < a.world; ++k)
+        {
+            const T* src = reinterpret_cast<const T*>(a.raw[k] + offset);
+            T x[kExchangeUnroll];
+#pragma unroll
+            for (int u = 0; u < kExchangeUnroll; ++u)
+                if (base + u * stride < hi) x[u] = __ldcg(src + base + u * stride);
+#pragma unroll
+            for (int u = 0; u < kExchangeUnroll; ++u)
+                if (base + u * stride < hi) v[u] = add_vec(v[u], x[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kExchangeUnroll; ++u)
+            if (base + u * stride < hi) store(base + u * stride, v[u]);
+    }
+}
+
+__global__ void __launch_bounds__(256) exchange_finalize_kernel(const __grid_constant__ ExchangeArgs a)
+{
+    // descriptor gradient [n_tex] float4 -> texture gradient [C, n_tex]
+    exchange_segment<float4>(a, 0, a.n_tex, [&](long long t, float4 v) {
+        for (int k = 0; k < a.world; ++k)
+        {
+            float* o = a.out[k];
+            o[t] = v.x;
+            o[(long long)a.n_tex + t] = v.y;
+            o[2LL * a.n_tex + t] = v.z;
+            if (a.C > 3) o[3LL * a.n_tex + t] = v.w;
+        }
+    });
+    // position gradient sums with the hit count in .w -> average (NormalizeGradient, PointRenderer.cu:1273-1280)
+    exchange_segment<float4>(a, 4LL * a.n_tex, a.n, [&](long long i, float4 v) {
+        if (v.w > 0) v.x = v.x / v.w, v.y = v.y / v.w, v.z = v.z / v.w;
+        v.w = 0.f;
+        for (int k = 0; k < a.world; ++k) reinterpret_cast<float4*>(a.out[k] + a.out_points)[i] = v;
+    });
+    // confidence gradient
+    exchange_segment<float>(a, 4LL * a.n_tex + 4LL * a.n, a.n_tex, [&](long long t, float v) {
+        for (int k = 0; k < a.world; ++k) a.out[k][a.out_conf + t] = v;
+    });
+    __threadfence_system();  // the peer stores are performed before the kernel counts as finished
+}
+
 }  // namespace vetr
 
 // =========================================================================================================
@@ -2435,6 +2525,42 @@ extern "C" int vetr_finalize_gradients(vetr_ctx* ctx, int channels, int n_tex, c
         normalize_rows_kernel<double, 6><<<(n_img + 127) / 128, 128, 0, st>>>(g_pose, g_pose_count, n_img);
     if (g_intr && g_intr_count && n_cam > 0)
         normalize_rows_kernel<float, 13><<<(n_cam + 127) / 128, 128, 0, st>>>(g_intr, g_intr_count, n_cam);
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+extern "C" int64_t vetr_exchange_raw_floats(int n_tex, int n)
+{
+    if (n_tex < 0 || n < 0) return -1;
+    return 5LL * n_tex + 4LL * n;
+}
+
+static long long exchange_out_points(int channels, int n_tex) { return ((long long)channels * n_tex + 3) / 4 * 4; }
+
+extern "C" int64_t vetr_exchange_out_floats(int channels, int n_tex, int n)
+{
+    if ((channels != 3 && channels != 4) || n_tex < 0 || n < 0) return -1;
+    return exchange_out_points(channels, n_tex) + 4LL * n + n_tex;
+}
+
+extern "C" int vetr_exchange_finalize(vetr_ctx* ctx, const vetr_exchange* ex, int channels, int n_tex, int n)
+{
+    if (!ctx || !ex || (channels != 3 && channels != 4) || n_tex < 1 || n < 0) return VETR_E_INVALID_ARG;
+    if (ex->world < 1 || ex->world > VETR_MAX_RANKS || ex->rank < 0 || ex->rank >= ex->world) return VETR_E_INVALID_ARG;
+    ExchangeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.rank = ex->rank, a.world = ex->world, a.C = channels, a.n_tex = n_tex, a.n = n;
+    a.out_points = exchange_out_points(channels, n_tex);
+    a.out_conf   = a.out_points + 4LL * n;
+    for (int k = 0; k < ex->world; ++k)
+    {
+        if (!ex->raw[k] || !ex->out[k] || ((uintptr_t)ex->raw[k] & 15) != 0 || ((uintptr_t)ex->out[k] & 15) != 0)
+            return VETR_E_INVALID_ARG;
+        a.raw[k] = ex->raw[k], a.out[k] = ex->out[k];
+    }
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    PassScope t(ctx, VETR_T_EXCHANGE, 1);
+    exchange_finalize_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(a);
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }

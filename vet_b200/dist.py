@@ -12,6 +12,7 @@ and their counts (double / float, a few hundred bytes) are reduced separately.
 """
 from __future__ import annotations
 
+import ctypes as C
 from typing import List, Optional
 
 import torch
@@ -28,9 +29,12 @@ def shard_views(n_views_total: int, rank: int, world: int) -> List[int]:
 class GradientBuffer:
     """Fused accumulation buffer for the point-parameter gradients of one step."""
 
-    def __init__(self, n: int, n_tex: int, device):
+    def __init__(self, n: int, n_tex: int, device, flat: Optional[torch.Tensor] = None):
         self.n, self.n_tex = n, n_tex
-        self.flat = torch.zeros(4 * n_tex + 4 * n + n_tex, dtype=torch.float32, device=device)
+        if flat is None:
+            flat = torch.zeros(4 * n_tex + 4 * n + n_tex, dtype=torch.float32, device=device)
+        assert flat.numel() == 4 * n_tex + 4 * n + n_tex and flat.dtype == torch.float32 and flat.is_contiguous()
+        self.flat = flat
         self.desc = self.flat[: 4 * n_tex].view(n_tex, 4)
         self.points = self.flat[4 * n_tex: 4 * n_tex + 4 * n].view(n, 4)
         self.conf = self.flat[4 * n_tex + 4 * n:]
@@ -59,3 +63,70 @@ def allreduce_gradients(buf: GradientBuffer, g: dict, group: Optional[dist.Proce
         if g.get(key) is not None:
             works.append(dist.all_reduce(g[key], group=group, async_op=async_op))
     return works if async_op else []
+
+
+class PeerExchange:
+    """Sum over the ranks + epilogue of the point-parameter gradients in ONE kernel over NVLink peer memory
+    (vetr_exchange_finalize) instead of an NCCL all-reduce followed by the epilogue kernels.
+
+    The raw buffer (what backward accumulates into) and the result buffer of every rank are allocated as torch
+    symmetric memory, so that every rank holds a pointer to every other rank's copy.  `run` enqueues, on the current
+    stream: all-reduce(pose gradient) -> the exchange kernel -> all-reduce(pose count, background).  The two small
+    NCCL collectives are needed anyway and are what orders the kernel after all ranks' backward kernels and its
+    consumers after all ranks' exchange kernels; the kernel itself waits on nothing.
+    """
+
+    def __init__(self, rast, n: int, n_tex: int, channels: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        from . import _lib as L
+
+        self.rast, self.n, self.n_tex, self.channels = rast, n, n_tex, channels
+        self.group = group if group is not None else dist.group.WORLD
+        lib = L.lib()
+        raw_floats = int(lib.vetr_exchange_raw_floats(n_tex, n))
+        out_floats = int(lib.vetr_exchange_out_floats(channels, n_tex, n))
+        self.raw = symm.empty(raw_floats, dtype=torch.float32, device=device)
+        self.out = symm.empty(out_floats, dtype=torch.float32, device=device)
+        self.raw.zero_()
+        h_raw = symm.rendezvous(self.raw, self.group)
+        h_out = symm.rendezvous(self.out, self.group)
+        self.rank, self.world = h_raw.rank, h_raw.world_size
+        self.c = L.Exchange()
+        self.c.rank, self.c.world = self.rank, self.world
+        for k in range(self.world):
+            self.c.raw[k] = int(h_raw.buffer_ptrs[k])
+            self.c.out[k] = int(h_out.buffer_ptrs[k])
+        self._handles = (h_raw, h_out)
+        self.buffer = GradientBuffer(n, n_tex, device, flat=self.raw)
+        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+        p0 = (channels * n_tex + 3) // 4 * 4
+        self.texture = self.out[: channels * n_tex].view(channels, n_tex)
+        self.points = self.out[p0: p0 + 4 * n].view(n, 4)
+        self.confidence = self.out[p0 + 4 * n:].view(1, n_tex)
+
+    def run(self, g: dict) -> dict:
+        """g: the dict backward accumulated into (its desc / points / conf are views of self.buffer).  Returns the
+        finished gradients (views of the result buffer, the same on every rank) plus the reduced small tensors."""
+        from . import _lib as L
+
+        first = g.get("pose") if g.get("pose") is not None else self._token
+        dist.all_reduce(first, group=self.group)
+        self.rast._sync_stream()
+        rc = L.lib().vetr_exchange_finalize(self.rast._ctx, self.c, self.channels, self.n_tex, self.n)
+        self.rast._check(rc, "vetr_exchange_finalize")
+        second = g.get("pose_count") if g.get("pose_count") is not None else self._token
+        dist.all_reduce(second, group=self.group)
+        for key in ("background", "intrinsics", "intrinsics_count"):
+            if g.get(key) is not None:
+                dist.all_reduce(g[key], group=self.group)
+        # count normalisation of the small camera gradients (the point-parameter part is already finished)
+        pose, intr = g.get("pose"), g.get("intrinsics")
+        if pose is not None or intr is not None:
+            ptr = lambda t: None if t is None else C.c_void_p(t.data_ptr())
+            rc = L.lib().vetr_finalize_gradients(
+                self.rast._ctx, self.channels, 0, None, None, 0, None, None,
+                0 if pose is None else pose.shape[0], ptr(pose), ptr(g.get("pose_count")),
+                0 if intr is None else intr.shape[0], ptr(intr), ptr(g.get("intrinsics_count")))
+            self.rast._check(rc, "vetr_finalize_gradients")
+        return dict(texture=self.texture, points=self.points, confidence=self.confidence, background=g.get("background"),
+                    pose=pose, intrinsics=intr)
