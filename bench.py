@@ -522,11 +522,12 @@ def run_ours(args):
 # divided by the algorithmic bytes of that launch).  The full-size workload is too large to capture with --set full;
 # traffic is taken to grow in proportion to the algorithmic bytes.
 TRAFFIC_OVER_ALGORITHMIC = {
-    "backward": (308.475e6 + 49.129e6) / 310.5e6,
-    "sort_blend": (117.499e6 + 105.804e6) / 185.6e6,
-    "count": 42.537e6 / 43.0e6,
+    "backward": (237.271e6 + 34.819e6) / 228.388e6,
+    "point_backward": (79.188e6 + 2.561e6) / 82.153e6,
+    "sort_blend": (117.402e6 + 104.202e6) / 185.585e6,
+    "count": 42.554e6 / 43.016e6,
     # the collection pass writes the whole 32-byte record (key + what the blend gathers), not only the 8-byte key
-    "collect": (91.797e6 + 83.952e6) / 58.6e6,
+    "collect": (67.186e6 + 86.907e6) / 58.553e6,
 }
 
 

@@ -43,7 +43,7 @@ namespace vetr
 #    define VETR_LONG_LIST 256
 #endif
 #ifndef VETR_MIN_CTAS
-#    define VETR_MIN_CTAS 8
+#    define VETR_MIN_CTAS 10
 #endif
 constexpr int kThreads    = VETR_ITEM_THREADS;  // CTA size of the item kernels
 constexpr int kQuantum    = VETR_QUANTUM;       // units of work per item
