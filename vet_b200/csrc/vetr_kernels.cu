@@ -78,6 +78,7 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
     float depth_accept;
     int ghost;
     int lw[VETR_MAX_LAYERS], lh[VETR_MAX_LAYERS];
+    float inv_lw[VETR_MAX_LAYERS];
     long long lbase[VETR_MAX_LAYERS];
     long long P, PT;
     ViewDev views[VETR_MAX_VIEWS];
@@ -450,20 +451,35 @@ struct PixInfo  // decoded pixel of the global pixel space, 8 bytes
     unsigned short interior;  // ImageView::distanceFromEdge > 2: the pixel takes part in the position gradient
 };
 
-__device__ __forceinline__ PixInfo decode_pixel(const Frame& f, unsigned g)
+// View, level and offset inside the level of pixel g, without divisions (a run of comparisons each).
+__device__ __forceinline__ void locate_pixel(const Frame& f, unsigned g, int& view, int& level, unsigned& offset)
 {
-    PixInfo r;
     const unsigned P = (unsigned)f.P;
-    unsigned view    = g / P;
-    unsigned q       = g - view * P;
-    int l            = 0;
+    int v = 0;
+#pragma unroll
+    for (int i = 1; i < VETR_MAX_VIEWS; ++i)
+        if (i < f.n_views && g >= i * P) v = i;
+    unsigned q = g - v * P;
+    int l      = 0;
 #pragma unroll
     for (int i = 1; i < VETR_MAX_LAYERS; ++i)
         if (i < f.L && q >= (unsigned)f.lbase[i]) l = i;
-    q -= (unsigned)f.lbase[l];
-    unsigned w = (unsigned)f.lw[l];
-    unsigned y = q / w;
-    r.x = (short)(q - y * w), r.y = (short)y, r.level = (unsigned char)l, r.view = (unsigned char)view;
+    view = v, level = l, offset = q - (unsigned)f.lbase[l];
+}
+
+__device__ __forceinline__ PixInfo decode_pixel(const Frame& f, unsigned g)
+{
+    PixInfo r;
+    int view, l;
+    unsigned q;
+    locate_pixel(f, g, view, l, q);
+    const unsigned w = (unsigned)f.lw[l];
+    // row = q / w: float estimate, then one correction step either way (exact: the estimate is off by at most one)
+    unsigned y = (unsigned)__float2int_rz(__fmul_rn((float)q, f.inv_lw[l]));
+    int x      = (int)(q - y * w);
+    if (x < 0) x += (int)w, --y;
+    if (x >= (int)w) x -= (int)w, ++y;
+    r.x = (short)x, r.y = (short)y, r.level = (unsigned char)l, r.view = (unsigned char)view;
     const int h = f.lh[l];
     r.interior  = min(min((int)r.x, (int)w - 1 - r.x), min((int)r.y, h - 1 - r.y)) > 2;
     return r;
@@ -574,17 +590,21 @@ struct OutPtrs
     float* depth[VETR_MAX_LAYERS];
 };
 
-__device__ __forceinline__ void write_pixel(const Frame& f, const OutPtrs& out, const PixInfo& px, const float c[4], float T,
-                                            float depth)
+// Outputs of pixel g of the global pixel space (planar [view, channel, y, x] tensors per level: the offset inside the
+// level is the row-major pixel offset, so rows and columns are not needed).
+__device__ __forceinline__ void write_pixel(const Frame& f, const OutPtrs& out, unsigned g, const float c[4], float T, float depth)
 {
-    const int w = f.lw[px.level], h = f.lh[px.level];
-    const int hw = w * h;
-    const int o  = px.y * w + px.x;
-    float* col   = out.color[px.level] + (px.view * f.C) * hw + o;
-    for (int ci = 0; ci < f.C; ++ci) col[ci * hw] = c[ci];
-    if (out.weight[0]) out.weight[px.level][px.view * hw + o] = T;
-    if (out.mask[0]) out.mask[px.level][px.view * hw + o] = (T == 0.f) ? f.mask_value : 1.f;
-    if (out.depth[0]) out.depth[px.level][px.view * hw + o] = depth;
+    int view, level;
+    unsigned o;
+    locate_pixel(f, g, view, level, o);
+    const int hw = f.lw[level] * f.lh[level];
+    float* col   = out.color[level] + (size_t)(view * f.C) * hw + o;
+    col[0] = c[0], col[hw] = c[1], col[2 * hw] = c[2];
+    if (f.C > 3) col[3 * hw] = c[3];
+    const size_t po = (size_t)view * hw + o;
+    if (out.weight[0]) out.weight[level][po] = T;
+    if (out.mask[0]) out.mask[level][po] = (T == 0.f) ? f.mask_value : 1.f;
+    if (out.depth[0]) out.depth[level][po] = depth;
 }
 
 // Front-to-back fold of one list (BlendMulti / BlendMultiBilinear, RenderForward.cu:1320-1356, 1597-1639).
@@ -605,11 +625,14 @@ struct Fold
         c[3] = vetr_blend(T, a, d.w, c[3]);
         T    = vetr_new_T(T, a);
     }
-    __device__ __forceinline__ void background(const Frame& f)
+    __device__ __forceinline__ void background(const Frame& f, const float bg[4])
     {
         const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
         if (!f.use_env && !(bilinear && !(T >= 0.001f)))
-            for (int ci = 0; ci < f.C; ++ci) c[ci] = vetr_blend(T, 1.f, f.background[ci], c[ci]);
+        {
+            c[0] = vetr_blend(T, 1.f, bg[0], c[0]), c[1] = vetr_blend(T, 1.f, bg[1], c[1]), c[2] = vetr_blend(T, 1.f, bg[2], c[2]);
+            if (f.C > 3) c[3] = vetr_blend(T, 1.f, bg[3], c[3]);
+        }
     }
 };
 
@@ -683,7 +706,6 @@ struct BlendSmem
     int tex[kCap];
     unsigned short perm[kCap];     // sorted position -> arrival slot
     int seg_end[kMaxPixels + 1];
-    PixInfo pix[kMaxPixels];
     SegTable seg;
 };
 
@@ -695,6 +717,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
     const int tid     = threadIdx.x;
     const int n_items = f.status[3];
     const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
+    const float bg[4]   = {f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f};
     if (tid == 0) s.seg.n_long[0] = s.seg.n_long[1] = 0;
     int parity = 0;
 #ifdef VETR_PHASE_TIMING
@@ -719,7 +742,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
         {
             const int ss = list_end(f, lo + tid - 1) - f0, se = f.ends[lo + tid] - f0;
             s.seg_end[tid + 1] = se;
-            s.pix[tid]         = decode_pixel(f, (unsigned)(lo + tid));
             seg_fill(s.seg, parity, tid, ss, se);
         }
         if (tid == 0) s.seg_end[0] = 0;
@@ -783,9 +805,9 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
                     if (bilinear && fold.T < 0.001f) break;
                 }
             }
-            fold.background(f);
+            fold.background(f, bg);
             float depth = se > ss ? __uint_as_float((unsigned)(s.key[s.perm[ss]] >> 32)) : kMaxDepth;
-            write_pixel(f, out, s.pix[tid], fold.c, fold.T, depth);
+            write_pixel(f, out, (unsigned)(lo + tid), fold.c, fold.T, depth);
         }
         PHASE_MARK(12);
     }
@@ -810,7 +832,6 @@ __global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_
         const int n  = f.ends[lo] - e0;
         __syncthreads();
         sort_long_list(f, e0, n);
-        const PixInfo px = decode_pixel(f, (unsigned)lo);
         int cnt = n;
         if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
         if (tid == 0)
@@ -867,8 +888,9 @@ __global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_
             for (int k = 0; k < 4; ++k) ff.acc_desc[k] = s_fold[8 + k];
             if (f.mode == VETR_MODE_FUZZY_BLEND) ff.finish();
             Fold fold = ff.fold;
-            fold.background(f);
-            write_pixel(f, out, px, fold.c, fold.T, __uint_as_float(f.recs[2 * (size_t)e0].y));
+            const float bg[4] = {f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f};
+            fold.background(f, bg);
+            write_pixel(f, out, (unsigned)lo, fold.c, fold.T, __uint_as_float(f.recs[2 * (size_t)e0].y));
         }
     }
 }
@@ -1773,7 +1795,7 @@ __global__ void __launch_bounds__(256) fuzzy_dt_combine_kernel(const __grid_cons
             c[0] = f.background[0], c[1] = f.background[1], c[2] = f.background[2], c[3] = f.C > 3 ? f.background[3] : 0.f;
         else
             c[0] = acc.x / w, c[1] = acc.y / w, c[2] = acc.z / w, c[3] = acc.w / w;
-        write_pixel(f, out, decode_pixel(f, (unsigned)g), c, w, __int_as_float(f.ends[g]));
+        write_pixel(f, out, (unsigned)g, c, w, __int_as_float(f.ends[g]));
     }
     int sum = n_acc, mx = n_acc;
     for (int o = 16; o > 0; o >>= 1)
@@ -2319,6 +2341,7 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     f.P  = pyramid(f.w, f.h, f.L, f.lw, f.lh, f.lbase);
     f.PT = f.P * n_views;
     if (f.lw[f.L - 1] < 1 || f.lh[f.L - 1] < 1) return VETR_E_INVALID_ARG;  // the reference asserts w > 0 && h > 0 per level
+    for (int l = 0; l < f.L; ++l) f.inv_lw[l] = 1.f / (float)f.lw[l];
     if (f.PT > 0x7fffffffLL || (long long)f.lw[0] * f.lh[0] * f.C * n_views > 0x7fffffffLL) return VETR_E_TOO_LARGE;
     f.position = (const float4*)cloud->position, f.index = cloud->index;
     f.texture = tex->texture, f.confidence = tex->confidence, f.background = tex->background;
