@@ -50,8 +50,11 @@ def parse_args():
     ap.add_argument("--prewarm", type=float, default=1.0, help="seconds of untimed load before the warm-up steps")
     ap.add_argument("--views-mode", choices=["same", "distinct"], default="same",
                     help="N > 1: every rank renders the same V camera poses (identical per-GPU work), or V poses of its own")
-    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
-                    help="N > 1: how the ranks' gradient buffers are summed (one kernel over peer memory, or NCCL all-reduce)")
+    ap.add_argument("--exchange", choices=["auto", "multicast", "peer", "nccl"], default="auto",
+                    help="N > 1: how the ranks' gradient buffers are summed: one kernel over peer memory, either through the "
+                         "NVSwitch multicast object (the switch adds; falls back to peer where there is none) or with plain "
+                         "peer loads / stores; auto = peer for 2 ranks, multicast for more; nccl = NCCL all-reduce + "
+                         "epilogue kernels")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     return ap.parse_args()
 
@@ -238,9 +241,11 @@ def run_ours(args):
     # --exchange nccl selects an NCCL all-reduce of the buffer followed by the epilogue kernels instead.
     peer = None
     exchange_kind = "none" if world == 1 else args.exchange
-    if world > 1 and args.exchange == "peer":
+    if world > 1 and args.exchange != "nccl":
         from vet_b200.dist import PeerExchange
-        peer = PeerExchange(rast, n, n_tex, CHANNELS, dev)
+        peer = PeerExchange(rast, n, n_tex, CHANNELS, dev,
+                            multicast=None if args.exchange == "auto" else args.exchange == "multicast")
+        exchange_kind = "multicast" if peer.multicast else "peer"
         flat = peer.raw
     else:
         flat = torch.zeros(4 * n_tex + 4 * n + n_tex, dtype=torch.float32, device=dev)

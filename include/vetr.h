@@ -221,6 +221,10 @@ typedef struct vetr_exchange
     int32_t rank, world;
     const float* raw[VETR_MAX_RANKS]; /* raw[k]: rank k's raw buffer as seen from this rank, 16-byte aligned */
     float*       out[VETR_MAX_RANKS]; /* out[k]: rank k's output buffer as seen from this rank, 16-byte aligned */
+    const float* raw_multicast;       /* optional: address of the NVSwitch multicast object bound to all ranks' raw buffers */
+    float*       out_multicast;       /* (and output buffers).  Both or neither.  When given, the sum is done by the switch
+                                         (multimem.ld_reduce) and the results are stored to all ranks at once (multimem.st):
+                                         the rank moves 1/world of the bytes.  fp32 sums in the switch's order. */
 } vetr_exchange;
 int64_t vetr_exchange_raw_floats(int n_tex, int n);
 int64_t vetr_exchange_out_floats(int channels, int n_tex, int n);

@@ -32,13 +32,22 @@ def main():
     gen = torch.Generator(device="cpu").manual_seed(100 + rank)
     grads = [torch.randn(c.shape, generator=gen).to(dev) for c in out["color"]]
 
-    # path 1: one kernel over peer memory
-    peer = PeerExchange(rast, n, n_tex, ch, dev)
-    for it in range(2):  # twice: the buffers are reused step after step
-        peer.buffer.zero_()
-        g1 = rast.backward_raw(grads, want_intrinsics=False, accum=peer.buffer.as_accum(ch, poses.shape[0]))
-        r1 = peer.run(g1)
-    tex1, pts1, conf1, pose1 = (r1[k].clone() for k in ("texture", "points", "confidence", "pose"))
+    # path 1: one kernel over peer memory; first with plain peer loads / stores, then through the NVSwitch multicast
+    # object where the platform has one
+    results = []
+    for multicast in (False, True):
+        peer = PeerExchange(rast, n, n_tex, ch, dev, multicast=multicast)
+        if multicast and not peer.multicast:
+            if rank == 0:
+                print("no multicast object on this platform: multimem path not run", flush=True)
+            break
+        for it in range(2):  # twice: the buffers are reused step after step
+            peer.buffer.zero_()
+            g1 = rast.backward_raw(grads, want_intrinsics=False, accum=peer.buffer.as_accum(ch, poses.shape[0]))
+            r1 = peer.run(g1)
+        results.append(tuple(r1[k].clone() for k in ("texture", "points", "confidence", "pose")))
+        if rank == 0:
+            print("exchange ran with multicast =", peer.multicast, flush=True)
 
     # path 2: NCCL all-reduce of the fused buffer + the epilogue kernels
     buf = GradientBuffer(n, n_tex, dev)
@@ -53,17 +62,17 @@ def main():
         err = np.abs(a - b).max() / scale
         assert err < 1e-5, (what, err)  # the two paths add the ranks' float sums in different orders
 
-    close(tex1, r2["texture"], "texture")
-    close(pts1, r2["points"], "points")
-    close(conf1, r2["confidence"], "confidence")
-    close(pose1, r2["pose"], "pose")
-    assert int(torch.count_nonzero(pts1).item()) > 0 and int(torch.count_nonzero(tex1).item()) > 0
-
-    # every rank holds the same bits
-    for t in (tex1, pts1, conf1):
-        ref = t.clone()
-        dist.broadcast(ref, src=0)
-        assert torch.equal(ref, t)
+    for tex1, pts1, conf1, pose1 in results:
+        close(tex1, r2["texture"], "texture")
+        close(pts1, r2["points"], "points")
+        close(conf1, r2["confidence"], "confidence")
+        close(pose1, r2["pose"], "pose")
+        assert int(torch.count_nonzero(pts1).item()) > 0 and int(torch.count_nonzero(tex1).item()) > 0
+        # every rank holds the same bits
+        for t in (tex1, pts1, conf1):
+            ref = t.clone()
+            dist.broadcast(ref, src=0)
+            assert torch.equal(ref, t)
     dist.barrier()
     if rank == 0:
         print("PEER_EXCHANGE_OK", flush=True)

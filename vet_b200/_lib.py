@@ -58,7 +58,8 @@ MAX_RANKS = 16
 
 
 class Exchange(C.Structure):
-    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("raw", C.c_void_p * MAX_RANKS), ("out", C.c_void_p * MAX_RANKS)]
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("raw", C.c_void_p * MAX_RANKS), ("out", C.c_void_p * MAX_RANKS),
+                ("raw_multicast", C.c_void_p), ("out_multicast", C.c_void_p)]
 
 
 EXPORTS = [

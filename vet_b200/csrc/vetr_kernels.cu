@@ -1998,6 +1998,8 @@ struct ExchangeArgs
     long long out_points, out_conf;  // float offsets of the position / confidence segments in the output buffers
     const float* raw[VETR_MAX_RANKS];
     float* out[VETR_MAX_RANKS];
+    const float* raw_mc;  // multicast address of the raw buffers (NVLink SHARP), or nullptr
+    float* out_mc;        // multicast address of the output buffers
 };
 
 __device__ __forceinline__ void slice_of(long long count, int rank, int world, long long& lo, long long& hi)
@@ -2045,6 +2047,62 @@ __device__ __forceinline__ void exchange_segment(const ExchangeArgs& a, long lon
         for (int u = 0; u < kExchangeUnroll; ++u)
             if (base + u * stride < hi) store(base + u * stride, v[u]);
     }
+}
+
+// The same exchange through the NVSwitch multicast object that spans all ranks' buffers: multimem.ld_reduce returns the
+// sum over the ranks of one address (the switch fetches and adds), multimem.st stores to all ranks at once.  The SM
+// issues 1/world of the loads and stores of the plain form.
+__device__ __forceinline__ float4 multimem_sum_v4(const float* mc)
+{
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ float multimem_sum(const float* mc)
+{
+    float v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.f32 %0, [%1];" : "=f"(v) : "l"(mc) : "memory");
+    return v;
+}
+__device__ __forceinline__ void multimem_store_v4(float* mc, float4 v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void multimem_store(float* mc, float v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc), "f"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(256) exchange_finalize_multicast_kernel(const __grid_constant__ ExchangeArgs a)
+{
+    const long long gtid   = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long lo, hi;
+    slice_of(a.n_tex, a.rank, a.world, lo, hi);
+    for (long long t = lo + gtid; t < hi; t += stride)
+    {
+        const float4 v = multimem_sum_v4(a.raw_mc + 4 * t);
+        multimem_store(a.out_mc + t, v.x);
+        multimem_store(a.out_mc + (long long)a.n_tex + t, v.y);
+        multimem_store(a.out_mc + 2LL * a.n_tex + t, v.z);
+        if (a.C > 3) multimem_store(a.out_mc + 3LL * a.n_tex + t, v.w);
+    }
+    slice_of(a.n, a.rank, a.world, lo, hi);
+    for (long long i = lo + gtid; i < hi; i += stride)
+    {
+        float4 v = multimem_sum_v4(a.raw_mc + 4LL * a.n_tex + 4 * i);
+        if (v.w > 0) v.x = v.x / v.w, v.y = v.y / v.w, v.z = v.z / v.w;
+        v.w = 0.f;
+        multimem_store_v4(a.out_mc + a.out_points + 4 * i, v);
+    }
+    slice_of(a.n_tex, a.rank, a.world, lo, hi);
+    for (long long t = lo + gtid; t < hi; t += stride)
+        multimem_store(a.out_mc + a.out_conf + t, multimem_sum(a.raw_mc + 4LL * a.n_tex + 4LL * a.n + t));
+    __threadfence_system();
 }
 
 __global__ void __launch_bounds__(256) exchange_finalize_kernel(const __grid_constant__ ExchangeArgs a)
@@ -2581,9 +2639,15 @@ extern "C" int vetr_exchange_finalize(vetr_ctx* ctx, const vetr_exchange* ex, in
             return VETR_E_INVALID_ARG;
         a.raw[k] = ex->raw[k], a.out[k] = ex->out[k];
     }
+    if ((ex->raw_multicast != nullptr) != (ex->out_multicast != nullptr)) return VETR_E_INVALID_ARG;
+    if (((uintptr_t)ex->raw_multicast & 15) != 0 || ((uintptr_t)ex->out_multicast & 15) != 0) return VETR_E_INVALID_ARG;
+    a.raw_mc = ex->raw_multicast, a.out_mc = ex->out_multicast;
     VETR_CUDA(ctx, cudaSetDevice(ctx->device));
     PassScope t(ctx, VETR_T_EXCHANGE, 1);
-    exchange_finalize_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(a);
+    if (a.raw_mc)
+        exchange_finalize_multicast_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(a);
+    else
+        exchange_finalize_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(a);
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }

@@ -76,7 +76,7 @@ class PeerExchange:
     consumers after all ranks' exchange kernels; the kernel itself waits on nothing.
     """
 
-    def __init__(self, rast, n: int, n_tex: int, channels: int, device, group=None):
+    def __init__(self, rast, n: int, n_tex: int, channels: int, device, group=None, multicast: Optional[bool] = None):
         import torch.distributed._symmetric_memory as symm
         from . import _lib as L
 
@@ -96,6 +96,15 @@ class PeerExchange:
         for k in range(self.world):
             self.c.raw[k] = int(h_raw.buffer_ptrs[k])
             self.c.out[k] = int(h_out.buffer_ptrs[k])
+        # NVSwitch multicast objects over both buffers (0 where the platform has none): the sum then happens in the switch
+        mc_raw, mc_out = int(getattr(h_raw, "multicast_ptr", 0) or 0), int(getattr(h_out, "multicast_ptr", 0) or 0)
+        if multicast is None:
+            # measured on 8 x B200: with 2 ranks plain peer loads / stores are faster (0.44 vs 0.76 ms for 8 M points), with
+            # 8 ranks the switch-side sum is (0.64 vs 0.85 ms)
+            multicast = self.world > 2
+        self.multicast = bool(multicast and self.world > 1 and mc_raw and mc_out)
+        if self.multicast:
+            self.c.raw_multicast, self.c.out_multicast = mc_raw, mc_out
         self._handles = (h_raw, h_out)
         self.buffer = GradientBuffer(n, n_tex, device, flat=self.raw)
         self._token = torch.zeros(1, dtype=torch.float32, device=device)

@@ -188,6 +188,7 @@ class Rasterizer:
 
     def fragment_count(self):
         """(total fragments, longest list) of the last forward; synchronises. Raises on key-buffer overflow."""
+        self._sync_stream()
         total, longest = 0, 0
         for (_, _, lists, _) in self._saved["groups"]:
             t, m = C.c_int64(), C.c_int32()
@@ -199,6 +200,7 @@ class Rasterizer:
     def lists_of(self, view: int, layer: int):
         """Reference layout of one (view, layer): collections [2,F_l] int32 and scanned_counting [h_l*w_l] int32."""
         s = self._saved
+        self._sync_stream()
         for (b0, b1, lists, varr) in s["groups"]:
             if b0 <= view < b1:
                 w, h = s["sizes"][0]
@@ -270,11 +272,13 @@ class Rasterizer:
                     pose=pose, intrinsics=intr)
 
     def set_timing(self, enable: bool):
+        self._sync_stream()
         self._check(L.lib().vetr_set_timing(self._ctx, int(enable)), "vetr_set_timing")
 
     def timings(self) -> dict:
         """Milliseconds of the most recent launch of every pass (timing must be enabled); synchronises."""
         ms = (C.c_float * len(L.TIMING_NAMES))()
+        self._sync_stream()
         self._check(L.lib().vetr_get_timings(self._ctx, ms), "vetr_get_timings")
         return {k: float(ms[i]) for i, k in enumerate(L.TIMING_NAMES)}
 
