@@ -4,9 +4,11 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--points M] [--views V]
 
 One step = one training batch of V views per GPU: forward (count, scan, collect, sort+blend), L1 gradient against
-a seeded target, backward, gradient epilogue; with N > 1 the point-parameter gradients (descriptor, confidence,
-position + hit count: 9 floats per point) are summed over the ranks with one NCCL all-reduce per step.  Views are
-sharded over the GPUs (weak scaling: V views per GPU and step), the cloud is replicated.
+a seeded target, backward (per-fragment kernel + per-point pass), gradient epilogue; with N > 1 the point-parameter
+gradients (descriptor, confidence, position + hit count: 9 floats per point) are summed over the ranks and finished by
+one kernel over NVLink peer memory (--exchange nccl: NCCL all-reduce + epilogue kernels).  Views are sharded over the
+GPUs (weak scaling: V views per GPU and step; by default every rank renders the same V poses so that the per-GPU work is
+identical), the cloud is replicated.  The compute part of the step is replayed as a CUDA graph.
 
 The script prints ONE JSON line (rank 0).  `value` times the steps with inputs resident in HBM; `e2e` times the same
 steps with the per-step inputs (the target pyramid of every view) arriving from pinned host memory and the loss
