@@ -230,6 +230,19 @@ int64_t vetr_exchange_raw_floats(int n_tex, int n);
 int64_t vetr_exchange_out_floats(int channels, int n_tex, int n);
 int vetr_exchange_finalize(vetr_ctx* ctx, const vetr_exchange* ex, int channels, int n_tex, int n);
 
+/* Error-grid rasterisation: PointRendererCache::FillSceneGridWithLoss -> FillSceneGridWithLossRasterize
+ * (RenderForward.cu:639-791; called per image from train.cpp:1077 before the tomography's point spawning).  For every
+ * cell of the scene grid whose eight box corners lie in front of the camera of `view`, the pixels of its projected box
+ * (the twelve triangles of its faces, inside the image minus a 32-pixel border) add sum_c |loss_img[c,y,x]| to
+ * cell_value and 1 to cell_access_count.  Both arrays are accumulated into (the caller zeroes them per epoch and
+ * divides afterwards, NeuralPointCloudCuda.h:42-52).
+ *   cell_bb_min, cell_bb_len [n_cells,3] float (t_cell_bb_min, t_cell_bb_length); loss_img [channels, view->h, view->w]
+ *   cell_value [n_cells] float; cell_access_count [n_cells] int32.
+ * Counts are exact; values are float sums in no fixed order (as in the reference). */
+int vetr_grid_loss(vetr_ctx* ctx, const vetr_cameras* cameras, const vetr_view* view, float dist_cutoff, int n_cells,
+                   const float* cell_bb_min, const float* cell_bb_len, const float* loss_img, int channels,
+                   float* cell_value, int32_t* cell_access_count);
+
 /* ApplyTangentToPose (PointRenderer.cu:1325-1349): poses[i] <- exp_se3(tangent[i]) * poses[i]; tangent[i] <- 0. */
 int vetr_apply_tangent(vetr_ctx* ctx, double* tangent /*[n,6]*/, double* poses_se3 /*[n,8]*/, int n);
 

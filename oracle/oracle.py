@@ -170,3 +170,23 @@ def apply_tangent(tangent: np.ndarray, poses: np.ndarray):
 
 def threads() -> int:
     return int(lib().vo_threads())
+
+
+def grid_loss(scene, view, bb_min, bb_len, loss_img, dist_cutoff: float = 20.0):
+    """FillSceneGridWithLossRasterize on the CPU: returns (value [n_cells] f32, access count [n_cells] i32)."""
+    bb_min = np.ascontiguousarray(bb_min, np.float32)
+    bb_len = np.ascontiguousarray(bb_len, np.float32)
+    loss_img = np.ascontiguousarray(loss_img, np.float32)
+    n = bb_min.shape[0]
+    ch, h, w = loss_img.shape
+    value = np.zeros(n, np.float32)
+    count = np.zeros(n, np.int32)
+    ov = OView(view.w, view.h, view.image_index, view.camera_index, view.camera_model, (C.c_float * 5)(*view.crop),
+               (C.c_float * 4)(*view.rot))
+    f = lib().vo_grid_loss
+    f.restype = C.c_int
+    rc = f(_ptr(scene.poses), _ptr(scene.intrinsics), C.byref(ov), C.c_float(dist_cutoff), C.c_int(n), _ptr(bb_min),
+           _ptr(bb_len), _ptr(loss_img), C.c_int(ch), C.c_int(h), C.c_int(w), _ptr(value), _ptr(count))
+    if rc != 0:
+        raise ValueError("oracle: invalid arguments")
+    return value, count

@@ -1138,4 +1138,73 @@ void vo_apply_tangent(double* tangent, double* poses, int n)
         for (int k = 0; k < 6; ++k) t[k] = 0;
     }
 }
+// Error-grid rasterisation, FillSceneGridWithLossRasterize (RenderForward.cu:639-791): every cell of the scene grid
+// whose eight corners are in front of the camera collects the L1 loss of the pixels its projected box covers (32-pixel
+// border excluded): value += sum over channels of |loss|, access count += 1 per pixel.  The reference adds with float
+// atomics in no fixed order; here the value of a cell is summed in double (compare with a relative tolerance), the
+// count is exact.
+static inline float tri_sign(V2 p1, V2 p2, V2 p3) { return (p1.x - p3.x) * (p2.y - p3.y) - (p2.x - p3.x) * (p1.y - p3.y); }
+static inline bool point_in_triangle(V2 pt, V2 v1, V2 v2, V2 v3)
+{
+    float d1 = tri_sign(pt, v1, v2), d2 = tri_sign(pt, v2, v3), d3 = tri_sign(pt, v3, v1);
+    bool has_neg = (d1 < 0) || (d2 < 0) || (d3 < 0);
+    bool has_pos = (d1 > 0) || (d2 > 0) || (d3 > 0);
+    return !(has_neg && has_pos);
+}
+
+int vo_grid_loss(const double* poses, const float* intrinsics, const OView* view, float dist_cutoff, int n_cells,
+                 const float* bb_min, const float* bb_len, const float* loss_img, int channels, int h, int w,
+                 float* cell_value, int* cell_count)
+{
+    if (!poses || !intrinsics || !view || n_cells < 0 || channels < 1) return -1;
+    const Pose V      = load_pose(poses + 8 * (int64_t)view->image_index);
+    const float* intr = intrinsics + 13 * (int64_t)view->camera_index;
+    static const float fac[8][3]  = {{0, 0, 0}, {1, 0, 0}, {0, 1, 0}, {0, 0, 1}, {1, 1, 0}, {1, 0, 1}, {0, 1, 1}, {1, 1, 1}};
+    static const int tris[12][3]  = {{0, 1, 4}, {0, 4, 2}, {1, 5, 7}, {1, 7, 4}, {5, 3, 6}, {5, 6, 7},
+                                     {3, 0, 6}, {0, 6, 2}, {3, 0, 5}, {0, 5, 1}, {2, 4, 6}, {4, 6, 7}};
+    const float border = 32.f;
+#pragma omp parallel for schedule(dynamic, 16)
+    for (int c = 0; c < n_cells; ++c)
+    {
+        V2 pp[8];
+        bool behind = false;
+        for (int i = 0; i < 8; ++i)
+        {
+            float pos4[4] = {bb_min[3 * c] + bb_len[3 * c] * fac[i][0], bb_min[3 * c + 1] + bb_len[3 * c + 1] * fac[i][1],
+                             bb_min[3 * c + 2] + bb_len[3 * c + 2] * fac[i][2], 0.f};
+            Projected pr = project(pos4, V, intr, *view, dist_cutoff);
+            if (pr.z <= 0) behind = true;
+            pp[i] = pr.ip;
+        }
+        if (behind) continue;
+        V2 mx{-10000000.f, -10000000.f}, mn{10000000.f, 10000000.f};
+        for (int i = 0; i < 8; ++i)
+        {
+            mx.x = std::fmax(pp[i].x, mx.x), mx.y = std::fmax(pp[i].y, mx.y);
+            mn.x = std::fmin(pp[i].x, mn.x), mn.y = std::fmin(pp[i].y, mn.y);
+        }
+        if (mx.x < border || mn.x >= (float)w - border || mx.y < border || mn.y >= (float)h - border) continue;
+        mn.x = std::fmax(mn.x, border), mn.y = std::fmax(mn.y, border);
+        mx.x = std::fmin(mx.x, (float)w - border), mx.y = std::fmin(mx.y, (float)h - border);
+        const int y_size = (int)(mx.y - mn.y), x_size = (int)(mx.x - mn.x);
+        double sum = 0.0;
+        int hits   = 0;
+        for (int64_t xy = 0; xy < (int64_t)y_size * x_size; ++xy)
+        {
+            const int x_c = (int)((float)(int)(xy % x_size) + mn.x);
+            const int y_c = (int)((float)(int)(xy / x_size) + mn.y);
+            bool in = false;
+            for (int t = 0; t < 12 && !in; ++t)
+                in = point_in_triangle({(float)x_c, (float)y_c}, pp[tris[t][0]], pp[tris[t][1]], pp[tris[t][2]]);
+            if (!in) continue;
+            float g = 0.f;
+            for (int i = 0; i < channels; ++i) g += std::fabs(loss_img[((int64_t)i * h + y_c) * w + x_c]);
+            sum += (double)g;
+            ++hits;
+        }
+        cell_value[c] += (float)sum;
+        cell_count[c] += hits;
+    }
+    return 0;
+}
 }  // extern "C"

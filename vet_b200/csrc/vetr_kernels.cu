@@ -2131,6 +2131,118 @@ __global__ void __launch_bounds__(256) exchange_finalize_kernel(const __grid_con
     __threadfence_system();  // the peer stores are performed before the kernel counts as finished
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Error-grid rasterisation (FillSceneGridWithLossRasterize, RenderForward.cu:639-791): the step between a training
+// epoch and the point spawning.  One warp per grid cell: eight lanes project the corners of the cell's box, all lanes
+// walk the pixels of its screen rectangle (32-pixel border excluded), test them against the twelve triangles of the
+// box and add up the L1 loss.  The reference issues two global atomics per covered pixel; here a lane sums in
+// registers and the warp adds once per cell.
+
+struct GridArgs
+{
+    const float* bb_min;
+    const float* bb_len;
+    const float* loss;
+    float* value;
+    int* count;
+    int n_cells, channels, h, w, view;
+};
+
+__device__ __forceinline__ float tri_sign(float2 p1, float2 p2, float2 p3)
+{
+    return VS(VM(VS(p1.x, p3.x), VS(p2.y, p3.y)), VM(VS(p2.x, p3.x), VS(p1.y, p3.y)));
+}
+__device__ __forceinline__ bool point_in_triangle(float2 pt, float2 v1, float2 v2, float2 v3)
+{
+    const float d1 = tri_sign(pt, v1, v2), d2 = tri_sign(pt, v2, v3), d3 = tri_sign(pt, v3, v1);
+    const bool has_neg = (d1 < 0) || (d2 < 0) || (d3 < 0);
+    const bool has_pos = (d1 > 0) || (d2 > 0) || (d3 > 0);
+    return !(has_neg && has_pos);
+}
+
+constexpr int kGridWarps = 4;
+
+__global__ void __launch_bounds__(32 * kGridWarps) grid_loss_kernel(const __grid_constant__ Frame f, const __grid_constant__ GridArgs a)
+{
+    __shared__ Camera s_cam;
+    __shared__ float2 s_pp[kGridWarps][8];
+    if (threadIdx.x == 0) s_cam = load_camera(f, a.view);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float border = 32.f;
+    for (int c = blockIdx.x * kGridWarps + warp; c < a.n_cells; c += gridDim.x * kGridWarps)
+    {
+        bool behind = false;
+        if (lane < 8)
+        {
+            // corner order of the reference: (0,0,0) (1,0,0) (0,1,0) (0,0,1) (1,1,0) (1,0,1) (0,1,1) (1,1,1)
+            const float fx = (lane == 1 || lane == 4 || lane == 5 || lane == 7) ? 1.f : 0.f;
+            const float fy = (lane == 2 || lane == 4 || lane == 6 || lane == 7) ? 1.f : 0.f;
+            const float fz = (lane == 3 || lane == 5 || lane == 6 || lane == 7) ? 1.f : 0.f;
+            const float4 pos = make_float4(VA(a.bb_min[3 * c], VM(a.bb_len[3 * c], fx)), VA(a.bb_min[3 * c + 1], VM(a.bb_len[3 * c + 1], fy)),
+                                           VA(a.bb_min[3 * c + 2], VM(a.bb_len[3 * c + 2], fz)), 0.f);
+            const Projected pr = project_point(pos, s_cam, f.dist_cutoff);
+            behind         = pr.z <= 0.f;  // one corner behind the camera: the whole cell is ignored
+            s_pp[warp][lane] = pr.ip;
+        }
+        behind = __any_sync(0xffffffffu, behind);
+        __syncwarp();
+        float sum = 0.f;
+        int hits  = 0;
+        if (!behind)
+        {
+            float2 pp[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pp[i] = s_pp[warp][i];
+            float2 mx = make_float2(-10000000.f, -10000000.f), mn = make_float2(10000000.f, 10000000.f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+            {
+                mx.x = fmaxf(pp[i].x, mx.x), mx.y = fmaxf(pp[i].y, mx.y);
+                mn.x = fminf(pp[i].x, mn.x), mn.y = fminf(pp[i].y, mn.y);
+            }
+            const float W = (float)a.w, H = (float)a.h;
+            if (!(mx.x < border || mn.x >= VS(W, border) || mx.y < border || mn.y >= VS(H, border)))
+            {
+                mn.x = fmaxf(mn.x, border), mn.y = fmaxf(mn.y, border);
+                mx.x = fminf(mx.x, VS(W, border)), mx.y = fminf(mx.y, VS(H, border));
+                const int y_size = (int)VS(mx.y, mn.y), x_size = (int)VS(mx.x, mn.x);
+                const long long total = (long long)y_size * x_size;
+                for (long long xy = lane; xy < total; xy += 32)
+                {
+                    const int x_c = (int)VA((float)(int)(xy % x_size), mn.x);
+                    const int y_c = (int)VA((float)(int)(xy / x_size), mn.y);
+                    const float2 pt = make_float2((float)x_c, (float)y_c);
+                    bool in = false;
+                    // faces of the box as pairs of triangles (RenderForward.cu:676-677)
+                    in |= point_in_triangle(pt, pp[0], pp[1], pp[4]) || point_in_triangle(pt, pp[0], pp[4], pp[2]);
+                    in |= point_in_triangle(pt, pp[1], pp[5], pp[7]) || point_in_triangle(pt, pp[1], pp[7], pp[4]);
+                    in |= point_in_triangle(pt, pp[5], pp[3], pp[6]) || point_in_triangle(pt, pp[5], pp[6], pp[7]);
+                    in |= point_in_triangle(pt, pp[3], pp[0], pp[6]) || point_in_triangle(pt, pp[0], pp[6], pp[2]);
+                    in |= point_in_triangle(pt, pp[3], pp[0], pp[5]) || point_in_triangle(pt, pp[0], pp[5], pp[1]);
+                    in |= point_in_triangle(pt, pp[2], pp[4], pp[6]) || point_in_triangle(pt, pp[4], pp[6], pp[7]);
+                    if (!in) continue;
+                    float g = 0.f;
+                    for (int i = 0; i < a.channels; ++i) g += fabsf(__ldg(a.loss + ((long long)i * a.h + y_c) * a.w + x_c));
+                    sum += g;
+                    ++hits;
+                }
+            }
+        }
+        for (int o = 16; o > 0; o >>= 1)
+        {
+            sum += __shfl_down_sync(0xffffffffu, sum, o);
+            hits += __shfl_down_sync(0xffffffffu, hits, o);
+        }
+        if (lane == 0 && hits > 0)
+        {
+            atomicAdd(a.value + c, sum);
+            atomicAdd(a.count + c, hits);
+        }
+        __syncwarp();  // the corner slots are reused by the warp's next cell
+    }
+}
+
 }  // namespace vetr
 
 // =========================================================================================================
@@ -2648,6 +2760,38 @@ extern "C" int vetr_exchange_finalize(vetr_ctx* ctx, const vetr_exchange* ex, in
         exchange_finalize_multicast_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(a);
     else
         exchange_finalize_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(a);
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+extern "C" int vetr_grid_loss(vetr_ctx* ctx, const vetr_cameras* cams, const vetr_view* view, float dist_cutoff, int n_cells,
+                              const float* cell_bb_min, const float* cell_bb_len, const float* loss_img, int channels,
+                              float* cell_value, int32_t* cell_access_count)
+{
+    if (!ctx || !cams || !view || !cams->poses_se3 || !cams->intrinsics || n_cells < 0 || channels < 1) return VETR_E_INVALID_ARG;
+    if (n_cells > 0 && (!cell_bb_min || !cell_bb_len || !loss_img || !cell_value || !cell_access_count)) return VETR_E_INVALID_ARG;
+    if (view->w <= 0 || view->h <= 0) return VETR_E_INVALID_ARG;
+    if (view->camera_model != 0) return VETR_E_UNSUPPORTED;
+    if (view->image_index < 0 || view->image_index >= cams->n_img || view->camera_index < 0 || view->camera_index >= cams->n_cam)
+        return VETR_E_INVALID_ARG;
+    if ((long long)channels * view->w * view->h > 0x7fffffffLL) return VETR_E_TOO_LARGE;
+    Frame f;
+    memset(&f, 0, sizeof(f));
+    f.n_views = 1, f.w = view->w, f.h = view->h, f.dist_cutoff = dist_cutoff;
+    f.views[0].image_index = view->image_index, f.views[0].camera_index = view->camera_index;
+    memcpy(f.views[0].crop, view->crop, sizeof(view->crop));
+    memcpy(f.views[0].rot, view->rot, sizeof(view->rot));
+    f.poses = cams->poses_se3, f.intr = cams->intrinsics;
+    GridArgs a;
+    a.bb_min = cell_bb_min, a.bb_len = cell_bb_len, a.loss = loss_img, a.value = cell_value, a.count = cell_access_count;
+    a.n_cells = n_cells, a.channels = channels, a.h = view->h, a.w = view->w, a.view = 0;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (n_cells > 0)
+    {
+        ctx->launches += 1;
+        const int ctas = min((n_cells + kGridWarps - 1) / kGridWarps, ctx->sm_count * 16);
+        grid_loss_kernel<<<ctas, 32 * kGridWarps, 0, ctx->stream>>>(f, a);
+    }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }

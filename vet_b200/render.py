@@ -271,6 +271,22 @@ class Rasterizer:
         return dict(texture=g_texture, confidence=g["conf"].view(1, -1), background=g["background"], points=pts,
                     pose=pose, intrinsics=intr)
 
+    def grid_loss(self, poses, intrinsics, view, cell_bb_min, cell_bb_len, loss_img, cell_value, cell_access_count,
+                  dist_cutoff: float = 20.0):
+        """FillSceneGridWithLoss (RenderForward.cu:761-791): adds the L1 loss under every grid cell's projected box to
+        cell_value [n_cells] f32 and the number of covered pixels to cell_access_count [n_cells] i32 (both CUDA, in place)."""
+        assert cell_bb_min.dtype == torch.float32 and cell_bb_len.dtype == torch.float32 and loss_img.dtype == torch.float32
+        assert cell_value.dtype == torch.float32 and cell_access_count.dtype == torch.int32
+        assert all(t.is_contiguous() for t in (cell_bb_min, cell_bb_len, loss_img, cell_value, cell_access_count))
+        assert loss_img.shape[1] == view.h and loss_img.shape[2] == view.w
+        self._sync_stream()
+        cams = L.Cameras(poses.data_ptr(), intrinsics.data_ptr(), poses.shape[0], intrinsics.shape[0])
+        v = self._views([view])
+        rc = L.lib().vetr_grid_loss(self._ctx, C.byref(cams), v, dist_cutoff, cell_bb_min.shape[0], _ptr(cell_bb_min),
+                                    _ptr(cell_bb_len), _ptr(loss_img), loss_img.shape[0], _ptr(cell_value),
+                                    _ptr(cell_access_count))
+        self._check(rc, "vetr_grid_loss")
+
     def set_timing(self, enable: bool):
         self._sync_stream()
         self._check(L.lib().vetr_set_timing(self._ctx, int(enable)), "vetr_set_timing")
