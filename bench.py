@@ -498,6 +498,30 @@ def run_ours(args):
                 "counts": {"N": N, "N_touched": touched, "F": F, "pixels": PT, "views_per_launch": V,
                            "longest_list": longest}}
 
+    # ---- the path's next row, measured beside the headline: error-grid rasterisation of one view's loss image over a
+    # 128^3 grid around the scene (FillSceneGridWithLoss; one launch per training image at the end of an epoch)
+    next_rows = None
+    if rank == 0 and world == 1:
+        cells = 128
+        ax = torch.linspace(-10.0, 10.0, cells + 1, device=dev)[:-1]
+        gx, gy, gz = torch.meshgrid(ax, ax, ax, indexing="ij")
+        bb_min = torch.stack([gx, gy, gz], dim=-1).reshape(-1, 3).contiguous()
+        bb_len = torch.full_like(bb_min, 20.0 / cells)
+        loss_img = torch.rand(3, H, W, device=dev)
+        cell_value = torch.zeros(bb_min.shape[0], device=dev)
+        cell_count = torch.zeros(bb_min.shape[0], dtype=torch.int32, device=dev)
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for it in range(4):
+            if it == 1:
+                g0.record(stream)
+            rast.grid_loss(poses, intrinsics, my_views[0], bb_min, bb_len, loss_img, cell_value, cell_count)
+        g1.record(stream)
+        torch.cuda.synchronize(dev)
+        next_rows = {"grid_loss": {"ms": g0.elapsed_time(g1) / 3, "cells": int(bb_min.shape[0]),
+                                   "covered_pixels_per_launch": int(cell_count.sum().item()) // 4,
+                                   "workload": f"{cells}^3 cells over a 20-unit box, one {W}x{H} view, 3-channel loss image"}}
+        del bb_min, bb_len, loss_img, cell_value, cell_count
+
     # ---- CPU baseline on the host cores (rank 0, N = 1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -517,7 +541,7 @@ def run_ours(args):
                        "views_per_gpu": V, "views_mode": args.views_mode if world > 1 else None, "points": N, "l2": "inputs larger than L2 (cloud 128 MB + descriptors 160 MB + "
                                                               "pyramids; gradient buffer 288 MB rewritten every step)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
-            "loss": float(loss.item()), "step_ms": [round(x, 3) for x in step_ms], "cuda_graph": graph_info, "exchange": exchange_kind, "per_rank": per_rank,
+            "loss": float(loss.item()), "step_ms": [round(x, 3) for x in step_ms], "cuda_graph": graph_info, "exchange": exchange_kind, "per_rank": per_rank, "next_rows": next_rows,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

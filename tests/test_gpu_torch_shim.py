@@ -98,3 +98,32 @@ def test_apply_tangent_to_pose(ops):
     p, tg = torch.from_numpy(poses).cuda(), torch.from_numpy(tangent).cuda()
     ops.apply_tangent_to_pose(tg, p)
     np.testing.assert_allclose(p.cpu().numpy(), p_ref, atol=1e-12)
+
+
+def test_fill_scene_grid_with_loss(ops):
+    """PointRendererCache::FillSceneGridWithLoss through the libtorch surface, against the CPU restatement."""
+    import torch
+
+    from oracle import oracle as O
+
+    dev = torch.device("cuda", 0)
+    w, h = 320, 240
+    sc = scenes.config_planar(100, w, h, 230.0, n_views=2, seed=4)
+    rng = np.random.default_rng(9)
+    bb_min = rng.uniform(-8, 8, size=(1500, 3)).astype(np.float32)
+    bb_len = rng.uniform(0.3, 2.0, size=(1500, 3)).astype(np.float32)
+    loss = rng.standard_normal((3, h, w)).astype(np.float32)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    value = torch.zeros(1500, 1, device=dev)
+    count = torch.zeros(1500, 1, dtype=torch.int32, device=dev)
+    ref_v, ref_c = np.zeros(1500), np.zeros(1500, np.int64)
+    for k, v in enumerate(sc.views):
+        vi = torch.tensor([v.w, v.h, v.image_index, v.camera_index, v.camera_model], dtype=torch.int32)
+        vf = torch.tensor(list(v.crop) + list(v.rot), dtype=torch.float32)
+        ops.fill_scene_grid_with_loss(t(sc.poses), t(sc.intrinsics), vi, vf, t(bb_min), t(bb_len), value, count, t(loss))
+        rv, rc = O.grid_loss(sc, v, bb_min, bb_len, loss)
+        ref_v += rv
+        ref_c += rc
+    assert ref_c.sum() > 1000
+    np.testing.assert_array_equal(count.cpu().numpy()[:, 0].astype(np.int64), ref_c)
+    np.testing.assert_allclose(value.cpu().numpy()[:, 0], ref_v, rtol=1e-5)

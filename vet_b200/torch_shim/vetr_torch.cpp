@@ -131,6 +131,35 @@ vetr_ctx* PointRendererCache::context(int device)
     return ctx_;
 }
 
+void PointRendererCache::FillSceneGridWithLoss(int batch, RenderScene& s, const std::vector<ReducedImageInfo>& images,
+                                               torch::Tensor loss_img, float dist_cutoff)
+{
+    TORCH_CHECK(batch >= 0 && batch < (int)images.size(), "FillSceneGridWithLoss: batch index out of range");
+    TORCH_CHECK(s.t_cell_bb_min.defined() && s.t_cell_bb_length.defined() && s.t_cell_value.defined() &&
+                    s.t_cell_access_count.defined(),
+                "FillSceneGridWithLoss: the scene has no grid");
+    TORCH_CHECK(loss_img.dim() == 3 && loss_img.dtype() == torch::kFloat32, "loss image must be [C,h,w] float");
+    TORCH_CHECK(s.t_cell_value.dtype() == torch::kFloat32 && s.t_cell_access_count.dtype() == torch::kInt32);
+    TORCH_CHECK(s.t_cell_value.is_contiguous() && s.t_cell_access_count.is_contiguous(), "grid tensors must be contiguous");
+    const auto dev = s.t_cell_bb_min.device();
+    c10::cuda::CUDAGuard guard(dev);
+    vetr_ctx* vc = context(dev.index());
+    const ReducedImageInfo& im = images[batch];
+    TORCH_CHECK(loss_img.size(1) == im.h && loss_img.size(2) == im.w, "loss image does not match the view");
+    vetr_view v{};
+    v.w = im.w, v.h = im.h, v.image_index = im.image_index, v.camera_index = im.camera_index;
+    v.camera_model = im.camera_model_type;
+    for (int i = 0; i < 5; ++i) v.crop[i] = im.crop_transform[i];
+    for (int i = 0; i < 4; ++i) v.rot[i] = im.crop_rotation[i];
+    torch::Tensor bb_min = s.t_cell_bb_min.contiguous(), bb_len = s.t_cell_bb_length.contiguous(), loss = loss_img.contiguous();
+    torch::Tensor poses = s.poses_se3.contiguous(), intr = s.intrinsics.contiguous();
+    vetr_cameras cams{poses.data_ptr<double>(), intr.data_ptr<float>(), (int)poses.size(0), (int)intr.size(0)};
+    check(vetr_grid_loss(vc, &cams, &v, dist_cutoff, (int)bb_min.size(0), bb_min.data_ptr<float>(), bb_len.data_ptr<float>(),
+                         loss.data_ptr<float>(), (int)loss.size(0), s.t_cell_value.data_ptr<float>(),
+                         s.t_cell_access_count.data_ptr<int>()),
+          "vetr_grid_loss");
+}
+
 std::vector<torch::Tensor> BlendPointCloud(NeuralRenderInfo* info)
 {
     torch::intrusive_ptr<NeuralRenderInfo> render_data = torch::make_intrusive<NeuralRenderInfo>(*info);
@@ -359,10 +388,32 @@ std::vector<torch::Tensor> blend_point_cloud_op(torch::Tensor texture, torch::Te
     info.scene = keep.get();
     return BlendPointCloud(&info);
 }
+
+// FillSceneGridWithLoss for one view given as the same integer / float rows as blend_point_cloud's views
+void fill_scene_grid_with_loss_op(torch::Tensor poses_se3, torch::Tensor intrinsics, torch::Tensor view_i, torch::Tensor view_f,
+                                  torch::Tensor cell_bb_min, torch::Tensor cell_bb_length, torch::Tensor cell_value,
+                                  torch::Tensor cell_access_count, torch::Tensor loss_img)
+{
+    static PointRendererCache cache;
+    RenderScene scene;
+    scene.poses_se3 = poses_se3, scene.intrinsics = intrinsics;
+    scene.t_cell_bb_min = cell_bb_min, scene.t_cell_bb_length = cell_bb_length;
+    scene.t_cell_value = cell_value, scene.t_cell_access_count = cell_access_count;
+    auto vi = view_i.cpu().contiguous();
+    auto vf = view_f.cpu().contiguous();
+    ReducedImageInfo im;
+    const int* pi   = vi.data_ptr<int>();
+    const float* pf = vf.data_ptr<float>();
+    im.w = pi[0], im.h = pi[1], im.image_index = pi[2], im.camera_index = pi[3], im.camera_model_type = pi[4];
+    for (int i = 0; i < 5; ++i) im.crop_transform[i] = pf[i];
+    for (int i = 0; i < 4; ++i) im.crop_rotation[i] = pf[5 + i];
+    cache.FillSceneGridWithLoss(0, scene, {im}, loss_img);
+}
 }  // namespace
 
 TORCH_LIBRARY(vetr, m)
 {
+    m.def("fill_scene_grid_with_loss", &fill_scene_grid_with_loss_op);
     m.class_<vetr_torch::NeuralRenderInfo>("NeuralRenderInfo").def(torch::init());
     m.def("blend_point_cloud", &blend_point_cloud_op);
     m.def("apply_tangent_to_pose", &vetr_torch::ApplyTangentToPose);

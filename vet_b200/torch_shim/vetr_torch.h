@@ -70,6 +70,10 @@ struct RenderScene
     torch::Tensor tangent_poses;              // [n,6] f64
     torch::Tensor intrinsics;                 // [n_cam,13]
     torch::Tensor dynamic_refinement_t;       // dummy [1] (models/Pipeline.cpp:128)
+    // scene grid of the error tomography (NeuralPointCloudCuda.h:100-106); only FillSceneGridWithLoss reads them
+    torch::Tensor t_cell_bb_min, t_cell_bb_length;  // [n_cells,3] f32
+    torch::Tensor t_cell_value;                     // [n_cells,1] f32
+    torch::Tensor t_cell_access_count;              // [n_cells,1] i32
 };
 
 struct LayerCuda
@@ -95,6 +99,12 @@ class PointRendererCache
     torch::Tensor dropout_points;  // [B,N] (1 = dropped), kept for inspection like the reference's member
 
     vetr_ctx* context(int device);  // one C-ABI context per cache, created on first use on the current stream
+
+    // PointRendererCache::FillSceneGridWithLoss (RenderForward.cu:761-791, called from train.cpp:1077): adds the loss image
+    // of images[batch] ([C,h,w]) to the grid cells of `scene` that its camera sees.  Enqueued on the current stream; the
+    // reference synchronises the device afterwards, this does not.
+    void FillSceneGridWithLoss(int batch, RenderScene& scene, const std::vector<ReducedImageInfo>& images,
+                               torch::Tensor loss_img, float dist_cutoff = 20.f);
 
    private:
     vetr_ctx* ctx_ = nullptr;
