@@ -258,3 +258,54 @@ def test_finalize_matches_reference_normalisation(rasterizer):
     util.assert_sum_close("pose", fin["pose"].cpu().numpy(), b["pose"] / pc, m["pose"] / pc)
     ic = np.where(b["intrinsics_count"] > 0, b["intrinsics_count"], 1)[:, None]
     util.assert_sum_close("intrinsics", fin["intrinsics"].cpu().numpy(), b["intrinsics"] / ic, m["intrinsics"] / ic)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+def test_committed_fixture(rasterizer, mode):
+    """The CUDA path against tests/golden/oracle_tiny.npz alone (no oracle run): lists, images, raw gradient sums."""
+    import os
+
+    data = np.load(os.path.join(os.path.dirname(__file__), "golden", "oracle_tiny.npz"))
+    sc = scenes.tiny_scene(n=400, w=24, h=16, n_views=2, seed=77, crop=True)
+    params = default_params(render_mode=mode, num_layers=3)
+    grads = [data[f"grad_m{mode}_l{l}"] for l in range(3)]
+    gpu = util.run_gpu(rasterizer, sc, params, grads=grads)
+    if mode != 0:
+        np.testing.assert_array_equal(gpu["counts"], data[f"counts_m{mode}"])
+        np.testing.assert_array_equal(gpu["keys"], data[f"keys_m{mode}"])
+    for l in range(3):
+        if mode == 0:  # float atomics in no fixed order, in the reference too
+            util.assert_close(f"color[{l}]", gpu["fwd"]["color"][l], data[f"color_m{mode}_l{l}"], rtol=1e-5, floor_rel=1e-6)
+        else:
+            np.testing.assert_array_equal(gpu["fwd"]["color"][l], data[f"color_m{mode}_l{l}"])
+        np.testing.assert_array_equal(gpu["fwd"]["weight"][l], data[f"weight_m{mode}_l{l}"])
+        np.testing.assert_array_equal(gpu["fwd"]["depth"][l], data[f"depth_m{mode}_l{l}"])
+    raw = gpu["bwd_raw"]
+    rtol = 2e-5 if mode == 0 else 1e-5
+    floor = 1e-6 if mode == 0 else 0.0
+    chk = lambda name, got, key: util.assert_sum_close(name, got, data[f"bwd_m{mode}_{key}"], data[f"mag_m{mode}_{key}"], rtol,
+                                                       floor_rel=floor)
+    chk("g_texture", raw["desc"][:, :4].T, "texture")
+    chk("g_confidence", raw["conf"], "confidence")
+    chk("g_background", raw["background"], "background")
+    chk("g_points", raw["points"][:, :3], "points")
+    chk("g_pose", raw["pose"], "pose")
+    chk("g_intrinsics", raw["intrinsics"], "intrinsics")
+
+
+def test_committed_fixture_grid_loss(rasterizer):
+    import os
+
+    import torch
+
+    data = np.load(os.path.join(os.path.dirname(__file__), "golden", "oracle_tiny.npz"))
+    sc = scenes.tiny_scene(n=4, w=160, h=128, n_views=2, seed=78, crop=True)
+    dev = rasterizer.device
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    value = torch.zeros(200, device=dev)
+    count = torch.zeros(200, dtype=torch.int32, device=dev)
+    for v in sc.views:
+        rasterizer.grid_loss(t(sc.poses), t(sc.intrinsics), v, t(data["grid_bb_min"]), t(data["grid_bb_len"]),
+                             t(data["grid_loss_img"]), value, count)
+    np.testing.assert_array_equal(count.cpu().numpy().astype(np.int64), data["grid_count"])
+    np.testing.assert_allclose(value.cpu().numpy(), data["grid_value"], rtol=1e-5)

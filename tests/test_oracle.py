@@ -230,18 +230,30 @@ def test_apply_tangent_is_the_se3_exponential():
 
 
 def test_golden_fixture():
-    """Freezes the oracle: counts, keys and images of a tiny scene in both modes (tests/golden/make_golden.py)."""
+    """Freezes the oracle: counts, keys, images and gradient sums of a tiny scene in all four modes, and the error-grid
+    sums (tests/golden/make_golden.py)."""
     data = np.load(GOLDEN)
-    for mode in (1, 3):
+    for mode in (0, 1, 2, 3):
         sc = scenes.tiny_scene(n=400, w=24, h=16, n_views=2, seed=77, crop=True)
         o = O.Oracle()
         r = o.forward(sc, O.default_params(render_mode=mode, num_layers=3))
-        counts, keys = o.lists()
-        np.testing.assert_array_equal(counts, data[f"counts_m{mode}"])
-        np.testing.assert_array_equal(keys, data[f"keys_m{mode}"])
+        if mode != 0:
+            counts, keys = o.lists()
+            np.testing.assert_array_equal(counts, data[f"counts_m{mode}"])
+            np.testing.assert_array_equal(keys, data[f"keys_m{mode}"])
         for l in range(3):
             np.testing.assert_array_equal(r["color"][l], data[f"color_m{mode}_l{l}"])
+            np.testing.assert_array_equal(r["weight"][l], data[f"weight_m{mode}_l{l}"])
+            np.testing.assert_array_equal(r["depth"][l], data[f"depth_m{mode}_l{l}"])
         g = [data[f"grad_m{mode}_l{l}"] for l in range(3)]
         b = o.backward(g)
         for k in ("texture", "confidence", "background", "points", "pose", "intrinsics"):
             np.testing.assert_allclose(b[k], data[f"bwd_m{mode}_{k}"], rtol=1e-12, atol=1e-14)
+    sc = scenes.tiny_scene(n=4, w=160, h=128, n_views=2, seed=78, crop=True)
+    value, count = np.zeros(200, np.float64), np.zeros(200, np.int64)
+    for v in sc.views:
+        gv, gc = O.grid_loss(sc, v, data["grid_bb_min"], data["grid_bb_len"], data["grid_loss_img"])
+        value += gv
+        count += gc
+    np.testing.assert_array_equal(count, data["grid_count"])
+    np.testing.assert_allclose(value, data["grid_value"], rtol=1e-12)

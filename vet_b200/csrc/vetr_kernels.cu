@@ -47,7 +47,10 @@ namespace vetr
 #endif
 constexpr int kThreads    = VETR_ITEM_THREADS;  // CTA size of the item kernels
 constexpr int kQuantum    = VETR_QUANTUM;       // units of work per item
-constexpr int kPixelWork  = 4;     // work units charged per pixel -> at most kQuantum / kPixelWork pixels per item
+#ifndef VETR_PIXEL_WORK
+#    define VETR_PIXEL_WORK 4
+#endif
+constexpr int kPixelWork  = VETR_PIXEL_WORK;     // work units charged per pixel -> at most kQuantum / kPixelWork pixels per item
 constexpr int kMaxPixels  = kQuantum / kPixelWork;
 constexpr int kLongList   = VETR_LONG_LIST;         // lists longer than this take the slow path
 constexpr int kCap        = kQuantum + kLongList;   // fragments staged per item (an item holds < kQuantum + its first list)
@@ -58,6 +61,7 @@ constexpr int kProjThreads     = 256;
 #endif
 constexpr int kPointsPerThread = 4;                      // count pass
 constexpr int kCollectPoints   = VETR_COLLECT_POINTS;    // collection pass (its slots and payload live in registers)
+static_assert(kQuantum % kPixelWork == 0, "an item of kQuantum work units holds at most kQuantum / kPixelWork pixels");
 static_assert(kMaxPixels <= kThreads, "one thread per pixel of an item");
 static_assert(kMaxPixels <= 256, "seg_of is a byte");
 constexpr int kScanTile   = 4096;  // elements per CTA in the scan (256 threads x 16)
