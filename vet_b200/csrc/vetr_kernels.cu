@@ -2012,126 +2012,145 @@ __device__ __forceinline__ void slice_of(long long count, int rank, int world, l
     hi = count * (rank + 1) / world;
 }
 
-// Sum over the ranks of element i of a segment that starts `offset` floats into every raw buffer.  The kExchangeUnroll
-// elements a thread handles per step are loaded from all ranks before the first is used (peer loads have microseconds
-// of latency: bytes in flight are what fills the links).
-constexpr int kExchangeUnroll = 4;
+// Every access is 16 bytes per lane and contiguous across a warp: few large requests cross a link (and the switch)
+// faster than many small ones.  kMulticast: the accesses go through the NVSwitch multicast object that spans all
+// ranks' buffers - multimem.ld_reduce returns the sum over the ranks of one address (the switch fetches and adds),
+// multimem.st stores to all ranks at once - so the SM issues 1/world of the loads and stores.
 
-template <typename T>
-__device__ __forceinline__ T add_vec(T a, T b);
-template <>
-__device__ __forceinline__ float4 add_vec(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
-template <>
-__device__ __forceinline__ float add_vec(float a, float b) { return a + b; }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
 
-template <typename T, typename Store>
-__device__ __forceinline__ void exchange_segment(const ExchangeArgs& a, long long offset, long long count, Store store)
+// sum over the ranks of the float4 at float offset `at` of the raw buffers (rank order 0, 1, ... in the plain form)
+template <bool kMulticast>
+__device__ __forceinline__ float4 rank_sum4(const ExchangeArgs& a, long long at)
 {
-    const long long gtid   = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    long long lo, hi;
-    slice_of(count, a.rank, a.world, lo, hi);
-    for (long long base = lo + gtid; base < hi; base += stride * kExchangeUnroll)
+    if constexpr (kMulticast)
     {
-        T v[kExchangeUnroll];
-#pragma unroll
-        for (int u = 0; u < kExchangeUnroll; ++u) v[u] = T();
-        for (int k = 0; k < a.world; ++k)
-        {
-            const T* src = reinterpret_cast<const T*>(a.raw[k] + offset);
-            T x[kExchangeUnroll];
-#pragma unroll
-            for (int u = 0; u < kExchangeUnroll; ++u)
-                if (base + u * stride < hi) x[u] = __ldcg(src + base + u * stride);
-#pragma unroll
-            for (int u = 0; u < kExchangeUnroll; ++u)
-                if (base + u * stride < hi) v[u] = add_vec(v[u], x[u]);
-        }
-#pragma unroll
-        for (int u = 0; u < kExchangeUnroll; ++u)
-            if (base + u * stride < hi) store(base + u * stride, v[u]);
+        float4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                     : "l"(a.raw_mc + at)
+                     : "memory");
+        return v;
+    }
+    else
+    {
+        float4 v = __ldcg(reinterpret_cast<const float4*>(a.raw[0] + at));
+        for (int k = 1; k < a.world; ++k) v = add4(v, __ldcg(reinterpret_cast<const float4*>(a.raw[k] + at)));
+        return v;
     }
 }
 
-// The same exchange through the NVSwitch multicast object that spans all ranks' buffers: multimem.ld_reduce returns the
-// sum over the ranks of one address (the switch fetches and adds), multimem.st stores to all ranks at once.  The SM
-// issues 1/world of the loads and stores of the plain form.
-__device__ __forceinline__ float4 multimem_sum_v4(const float* mc)
+// store one float4 at float offset `at` of every rank's output buffer
+template <bool kMulticast>
+__device__ __forceinline__ void rank_store4(const ExchangeArgs& a, long long at, float4 v)
 {
-    float4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "l"(mc)
-                 : "memory");
+    if constexpr (kMulticast)
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.out_mc + at), "f"(v.x), "f"(v.y),
+                     "f"(v.z), "f"(v.w)
+                     : "memory");
+    else
+        for (int k = 0; k < a.world; ++k) *reinterpret_cast<float4*>(a.out[k] + at) = v;
+}
+
+// scalar forms for the few elements that do not fill a 16-byte group (plain peer accesses in both variants)
+__device__ __forceinline__ float rank_sum1(const ExchangeArgs& a, long long at)
+{
+    float v = __ldcg(a.raw[0] + at);
+    for (int k = 1; k < a.world; ++k) v += __ldcg(a.raw[k] + at);
     return v;
 }
-__device__ __forceinline__ float multimem_sum(const float* mc)
+__device__ __forceinline__ void rank_store1(const ExchangeArgs& a, long long at, float v)
 {
-    float v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.f32 %0, [%1];" : "=f"(v) : "l"(mc) : "memory");
-    return v;
-}
-__device__ __forceinline__ void multimem_store_v4(float* mc, float4 v)
-{
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
-                 : "memory");
-}
-__device__ __forceinline__ void multimem_store(float* mc, float v)
-{
-    asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc), "f"(v) : "memory");
+    for (int k = 0; k < a.world; ++k) a.out[k][at] = v;
 }
 
-__global__ void __launch_bounds__(256) exchange_finalize_multicast_kernel(const __grid_constant__ ExchangeArgs a)
+constexpr int kExchangeWarps = 8;
+
+template <bool kMulticast>
+__global__ void __launch_bounds__(32 * kExchangeWarps) exchange_finalize_kernel(const __grid_constant__ ExchangeArgs a)
 {
-    const long long gtid   = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long stride = (long long)gridDim.x * blockDim.x;
+    __shared__ float4 s_tile[kExchangeWarps][2][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long gtid    = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride  = (long long)gridDim.x * blockDim.x;
+    const long long gwarp   = (long long)blockIdx.x * kExchangeWarps + warp;
+    const long long n_warps = (long long)gridDim.x * kExchangeWarps;
+    const long long n_tex   = a.n_tex;
+    const long long raw_points = 4 * n_tex, raw_conf = 4 * n_tex + 4LL * a.n;
     long long lo, hi;
-    slice_of(a.n_tex, a.rank, a.world, lo, hi);
-    for (long long t = lo + gtid; t < hi; t += stride)
-    {
-        const float4 v = multimem_sum_v4(a.raw_mc + 4 * t);
-        multimem_store(a.out_mc + t, v.x);
-        multimem_store(a.out_mc + (long long)a.n_tex + t, v.y);
-        multimem_store(a.out_mc + 2LL * a.n_tex + t, v.z);
-        if (a.C > 3) multimem_store(a.out_mc + 3LL * a.n_tex + t, v.w);
-    }
-    slice_of(a.n, a.rank, a.world, lo, hi);
-    for (long long i = lo + gtid; i < hi; i += stride)
-    {
-        float4 v = multimem_sum_v4(a.raw_mc + 4LL * a.n_tex + 4 * i);
-        if (v.w > 0) v.x = v.x / v.w, v.y = v.y / v.w, v.z = v.z / v.w;
-        v.w = 0.f;
-        multimem_store_v4(a.out_mc + a.out_points + 4 * i, v);
-    }
-    slice_of(a.n_tex, a.rank, a.world, lo, hi);
-    for (long long t = lo + gtid; t < hi; t += stride)
-        multimem_store(a.out_mc + a.out_conf + t, multimem_sum(a.raw_mc + 4LL * a.n_tex + 4LL * a.n + t));
-    __threadfence_system();
-}
 
-__global__ void __launch_bounds__(256) exchange_finalize_kernel(const __grid_constant__ ExchangeArgs a)
-{
-    // descriptor gradient [n_tex] float4 -> texture gradient [C, n_tex]
-    exchange_segment<float4>(a, 0, a.n_tex, [&](long long t, float4 v) {
-        for (int k = 0; k < a.world; ++k)
+    // descriptor gradient [n_tex] float4 -> texture gradient [C, n_tex].  A warp takes 32 texels (one coalesced float4
+    // load per lane), turns them by 90 degrees in shared memory and stores 4 texels x 1 channel per lane, i.e. a
+    // 128-byte run in each channel row.  Rows start at c * n_tex floats: 16-byte aligned only if n_tex % 4 == 0.
+    const long long tiles = (n_tex & 3) == 0 ? n_tex / 32 : 0;
+    slice_of(tiles, a.rank, a.world, lo, hi);
+    const int c = lane >> 3, q = lane & 7;
+    for (long long tile = lo + gwarp; tile < hi; tile += 2 * n_warps)
+    {
+        const bool second = tile + n_warps < hi;
+        const float4 v0 = rank_sum4<kMulticast>(a, 4 * (tile * 32 + lane));
+        float4 v1       = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (second) v1 = rank_sum4<kMulticast>(a, 4 * ((tile + n_warps) * 32 + lane));
+        s_tile[warp][0][lane] = v0;
+        s_tile[warp][1][lane] = v1;
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
         {
-            float* o = a.out[k];
-            o[t] = v.x;
-            o[(long long)a.n_tex + t] = v.y;
-            o[2LL * a.n_tex + t] = v.z;
-            if (a.C > 3) o[3LL * a.n_tex + t] = v.w;
+            if (u == 1 && !second) break;
+            const float* tf = reinterpret_cast<const float*>(s_tile[warp][u]);
+            const float4 o  = make_float4(tf[(4 * q) * 4 + c], tf[(4 * q + 1) * 4 + c], tf[(4 * q + 2) * 4 + c], tf[(4 * q + 3) * 4 + c]);
+            if (c < a.C) rank_store4<kMulticast>(a, c * n_tex + (tile + u * n_warps) * 32 + 4 * q, o);
         }
-    });
+        __syncwarp();
+    }
+    // texels that do not fill a tile (all of them if the rows are not 16-byte aligned), one by one
+    {
+        const long long first = tiles * 32;
+        slice_of(n_tex - first, a.rank, a.world, lo, hi);
+        for (long long t = first + lo + gtid; t < first + hi; t += stride)
+        {
+            const float4 v = rank_sum4<false>(a, 4 * t);
+            rank_store1(a, t, v.x), rank_store1(a, n_tex + t, v.y), rank_store1(a, 2 * n_tex + t, v.z);
+            if (a.C > 3) rank_store1(a, 3 * n_tex + t, v.w);
+        }
+    }
+
     // position gradient sums with the hit count in .w -> average (NormalizeGradient, PointRenderer.cu:1273-1280)
-    exchange_segment<float4>(a, 4LL * a.n_tex, a.n, [&](long long i, float4 v) {
-        if (v.w > 0) v.x = v.x / v.w, v.y = v.y / v.w, v.z = v.z / v.w;
-        v.w = 0.f;
-        for (int k = 0; k < a.world; ++k) reinterpret_cast<float4*>(a.out[k] + a.out_points)[i] = v;
-    });
-    // confidence gradient
-    exchange_segment<float>(a, 4LL * a.n_tex + 4LL * a.n, a.n_tex, [&](long long t, float v) {
-        for (int k = 0; k < a.world; ++k) a.out[k][a.out_conf + t] = v;
-    });
+    slice_of(a.n, a.rank, a.world, lo, hi);
+    for (long long base = lo + gtid; base < hi; base += stride * 4)
+    {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (base + u * stride < hi) v[u] = rank_sum4<kMulticast>(a, raw_points + 4 * (base + u * stride));
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            if (base + u * stride >= hi) continue;
+            float4 r = v[u];
+            if (r.w > 0) r.x = r.x / r.w, r.y = r.y / r.w, r.z = r.z / r.w;
+            r.w = 0.f;
+            rank_store4<kMulticast>(a, a.out_points + 4 * (base + u * stride), r);
+        }
+    }
+
+    // confidence gradient, four texels per access (every segment offset is a multiple of 4 floats); the last rank also
+    // takes the n_tex % 4 texels that are left over
+    const long long groups = n_tex / 4;
+    slice_of(groups, a.rank, a.world, lo, hi);
+    for (long long base = lo + gtid; base < hi; base += stride * 4)
+    {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (base + u * stride < hi) v[u] = rank_sum4<kMulticast>(a, raw_conf + 4 * (base + u * stride));
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (base + u * stride < hi) rank_store4<kMulticast>(a, a.out_conf + 4 * (base + u * stride), v[u]);
+    }
+    if (a.rank == a.world - 1)
+        for (long long t = 4 * groups + gtid; t < n_tex; t += stride) rank_store1(a, a.out_conf + t, rank_sum1(a, raw_conf + t));
     __threadfence_system();  // the peer stores are performed before the kernel counts as finished
 }
 
@@ -2761,9 +2780,9 @@ extern "C" int vetr_exchange_finalize(vetr_ctx* ctx, const vetr_exchange* ex, in
     VETR_CUDA(ctx, cudaSetDevice(ctx->device));
     PassScope t(ctx, VETR_T_EXCHANGE, 1);
     if (a.raw_mc)
-        exchange_finalize_multicast_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(a);
+        exchange_finalize_kernel<true><<<ctx->sm_count * 4, 32 * kExchangeWarps, 0, ctx->stream>>>(a);
     else
-        exchange_finalize_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(a);
+        exchange_finalize_kernel<false><<<ctx->sm_count * 4, 32 * kExchangeWarps, 0, ctx->stream>>>(a);
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }
