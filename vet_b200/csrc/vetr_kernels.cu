@@ -742,6 +742,9 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
         const int f0 = list_end(f, lo - 1);
         const int np = hi - lo;
         const int nf = f.ends[hi - 1] - f0;
+        // the thread's first record is requested before the per-pixel set-up, each further one before the previous is stored
+        uint4 h_next = make_uint4(0, 0, 0, 0), d_next = h_next;
+        if (tid < nf) h_next = f.recs[2 * (size_t)(f0 + tid)], d_next = f.recs[2 * (size_t)(f0 + tid) + 1];
         if (tid < np)
         {
             const int ss = list_end(f, lo + tid - 1) - f0, se = f.ends[lo + tid] - f0;
@@ -752,8 +755,10 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
         // stream keys and payload of the item (contiguous, coalesced)
         for (int i = tid; i < nf; i += kThreads)
         {
-            const uint4 h = f.recs[2 * (size_t)(f0 + i)];
-            s.desc[i]     = as_float4(f.recs[2 * (size_t)(f0 + i) + 1]);
+            const uint4 h = h_next, d = d_next;
+            if (i + kThreads < nf)
+                h_next = f.recs[2 * (size_t)(f0 + i + kThreads)], d_next = f.recs[2 * (size_t)(f0 + i + kThreads) + 1];
+            s.desc[i]     = as_float4(d);
             s.key[i]      = record_key(h);
             s.alpha[i]    = __uint_as_float(h.z);
             s.tex[i]      = (int)h.w;
@@ -1055,34 +1060,48 @@ __device__ __forceinline__ void spatial_backward(const Frame& f, const BackPtrs&
 // Modes 1 and 2: approximate image-space gradient of a fragment from the neighbouring pixels
 // (RenderBackward.cu:1347-1374).  `g` is the pixel in the global pixel space; the images are the channel-interleaved
 // copies pack_images_kernel makes, so the eight neighbour values of all channels are eight 16-byte loads.
+struct Neighbours
+{
+    float4 il, ir, iu, id, gl, gr, gu, gd;  // forward image and its gradient left / right / above / below the pixel
+    __device__ __forceinline__ void load(const Frame& f, int g, int w)
+    {
+        const float4* I  = f.img4 + g;
+        const float4* Gp = f.grad4 + g;
+        il = __ldg(I - 1), ir = __ldg(I + 1), iu = __ldg(I - w), id = __ldg(I + w);
+        gl = __ldg(Gp - 1), gr = __ldg(Gp + 1), gu = __ldg(Gp - w), gd = __ldg(Gp + w);
+    }
+    __device__ __forceinline__ float2 gradient(const Frame& f, float4 d) const
+    {
+        const float dv[4] = {d.x, d.y, d.z, d.w};
+        const float Il[4] = {il.x, il.y, il.z, il.w}, Ir[4] = {ir.x, ir.y, ir.z, ir.w};
+        const float Iu[4] = {iu.x, iu.y, iu.z, iu.w}, Id[4] = {id.x, id.y, id.z, id.w};
+        const float Gl[4] = {gl.x, gl.y, gl.z, gl.w}, Gr[4] = {gr.x, gr.y, gr.z, gr.w};
+        const float Gu[4] = {gu.x, gu.y, gu.z, gu.w}, Gd[4] = {gd.x, gd.y, gd.z, gd.w};
+        float dx = 0.f, dy = 0.f;
+#pragma unroll
+        for (int ci = 0; ci < 4; ++ci)
+        {
+            if (ci < f.C)
+            {
+                float Tp = dv[ci];
+                float a0 = -(Tp - Il[ci]) * Gl[ci];
+                float a1 = (Tp - Ir[ci]) * Gr[ci];
+                float b0 = -(Tp - Iu[ci]) * Gu[ci];
+                float b1 = (Tp - Id[ci]) * Gd[ci];
+                dx += 0.5f * (a0 + a1);
+                dy += 0.5f * (b0 + b1);
+            }
+        }
+        // x / 4 and x * 0.25 round alike
+        return f.C == 4 ? make_float2(dx * 0.25f, dy * 0.25f) : make_float2(dx / (float)f.C, dy / (float)f.C);
+    }
+};
+
 __device__ __forceinline__ float2 neighbour_gradient(const Frame& f, int g, int w, float4 d)
 {
-    const float4* I  = f.img4 + g;
-    const float4* Gp = f.grad4 + g;
-    const float4 il = __ldg(I - 1), ir = __ldg(I + 1), iu = __ldg(I - w), id = __ldg(I + w);
-    const float4 gl = __ldg(Gp - 1), gr = __ldg(Gp + 1), gu = __ldg(Gp - w), gd = __ldg(Gp + w);
-    const float dv[4] = {d.x, d.y, d.z, d.w};
-    const float Il[4] = {il.x, il.y, il.z, il.w}, Ir[4] = {ir.x, ir.y, ir.z, ir.w};
-    const float Iu[4] = {iu.x, iu.y, iu.z, iu.w}, Id[4] = {id.x, id.y, id.z, id.w};
-    const float Gl[4] = {gl.x, gl.y, gl.z, gl.w}, Gr[4] = {gr.x, gr.y, gr.z, gr.w};
-    const float Gu[4] = {gu.x, gu.y, gu.z, gu.w}, Gd[4] = {gd.x, gd.y, gd.z, gd.w};
-    float dx = 0.f, dy = 0.f;
-#pragma unroll
-    for (int ci = 0; ci < 4; ++ci)
-    {
-        if (ci < f.C)
-        {
-            float Tp = dv[ci];
-            float a0 = -(Tp - Il[ci]) * Gl[ci];
-            float a1 = (Tp - Ir[ci]) * Gr[ci];
-            float b0 = -(Tp - Iu[ci]) * Gu[ci];
-            float b1 = (Tp - Id[ci]) * Gd[ci];
-            dx += 0.5f * (a0 + a1);
-            dy += 0.5f * (b0 + b1);
-        }
-    }
-    // x / 4 and x * 0.25 round alike
-    return f.C == 4 ? make_float2(dx * 0.25f, dy * 0.25f) : make_float2(dx / (float)f.C, dy / (float)f.C);
+    Neighbours nb;
+    nb.load(f, g, w);
+    return nb.gradient(f, d);
 }
 
 __device__ __forceinline__ float4 load_grad(const Frame& f, int g) { return __ldg(f.grad4 + g); }
@@ -1122,11 +1141,10 @@ constexpr int kNoGradientBits = 0x7fffffff;
 // coalesced position loads and without atomics, instead of a position gather per fragment here.
 template <bool kBilinear>
 __device__ __forceinline__ void fragment_stage_a(const Frame& f, BackSmem& s, int g, const PixInfo& px, float4 G, int slot,
-                                                 int gslot, bool blended, float4* desc_out = nullptr,
+                                                 uint4 h, uint4 payload, bool blended, float4* desc_out = nullptr,
                                                  float* depth_out = nullptr)
 {
-    const uint4 h  = f.recs[2 * (size_t)gslot];
-    const float4 d = as_float4(f.recs[2 * (size_t)gslot + 1]);
+    const float4 d = as_float4(payload);
     const int pid  = (int)h.x;
     if (desc_out) desc_out[slot] = d, depth_out[slot] = __uint_as_float(h.y);
     s.pid[slot]    = pid;
@@ -1383,12 +1401,15 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
             const int nf = s.seg_end[np];
             for (int i = tid; i < nf; i += kThreads)
             {
+                // Measured slower, both times through registers (spills, or one resident CTA less): requesting the next
+                // record before working on this one; requesting the eight neighbour values together with the record.
+                const uint4 h = f.recs[2 * (size_t)(f0 + i)], d = f.recs[2 * (size_t)(f0 + i) + 1];
                 const int a = seg_lookup(s.seg, parity, s.seg_end, i);
                 const bool blended = f.dbg_max_len <= 0 || i - s.seg_end[a] < f.dbg_max_len;  // list truncation
                 if constexpr (kFuzzy)
-                    fragment_stage_a<false>(f, s, lo + a, s.pix[a], s.grad[a], i, f0 + i, blended, s.desc, s.depth);
+                    fragment_stage_a<false>(f, s, lo + a, s.pix[a], s.grad[a], i, h, d, blended, s.desc, s.depth);
                 else
-                    fragment_stage_a<kBilinear>(f, s, lo + a, s.pix[a], s.grad[a], i, f0 + i, blended);
+                    fragment_stage_a<kBilinear>(f, s, lo + a, s.pix[a], s.grad[a], i, h, d, blended);
             }
             __syncthreads();
             PHASE_MARK(2);
@@ -1498,7 +1519,8 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
         {
             const int m = min(kCap, eff_cnt - blk * kCap);
             for (int i = tid; i < m; i += kThreads)
-                fragment_stage_a<kBilinear>(f, s, lo, px, G, i, e0 + blk * kCap + i, true);
+                fragment_stage_a<kBilinear>(f, s, lo, px, G, i, f.recs[2 * (size_t)(e0 + blk * kCap + i)],
+                                            f.recs[2 * (size_t)(e0 + blk * kCap + i) + 1], true);
             __syncthreads();
             if (tid == 0)
             {
