@@ -4,22 +4,32 @@
 // Data layout in HBM
 //   pixel space : all views and all pyramid levels of a call form ONE array of PT = n_views * P pixels
 //                 (view-major, then level, then row-major).  counts[PT], ends[PT] (int32).
-//   key buffer  : one array of 64-bit keys, (depth bits << 32) | point index.  The list of pixel g is
-//                 keys[ends[g] - counts[g] .. ends[g]).  Lists of consecutive pixels are contiguous, so a CTA that
-//                 owns a run of pixels streams its fragments with coalesced loads.
+//   records     : one 32-byte record per fragment = one DRAM sector: 64-bit key (depth bits << 32 | point index),
+//                 alpha, descriptor index, descriptor.  The list of pixel g is recs[ends[g] - counts[g] .. ends[g]).
+//                 Lists of consecutive pixels are contiguous, so a CTA that owns a run of pixels streams its fragments
+//                 with coalesced loads.
 //   work items  : the pixel space is cut into runs of ~kQuantum units of work (1 per fragment, kPixelWork per pixel)
-//                 by the scan itself (item_start[]), so the persistent blend kernels are balanced by fragments, not
+//                 by the scan itself (item_start[]), so the persistent item kernels are balanced by fragments, not
 //                 by pixels, and no host round trip is needed to size anything.
+//   backward    : level_mask[n_views * n] (which levels hold a fragment of a point), point_grad[(view, level, point)]
+//                 (image-space gradient parked per fragment), img4 / grad4[PT] (channel-interleaved image copies).
 //
-// Kernels (all HBM / L2-atomic bound; nothing here is a contraction, so no tensor cores)
-//   project_count_kernel   stream positions, project, per-level pixel, warp-aggregated count atomics
-//   scan_*                 three-phase exclusive scan of counts -> ends, total F, work-item table
-//   collect_kernel         re-project, warp-aggregated slot reservation, 8-byte key store
-//   sort_blend_kernel      per work item: stage keys in shared memory, rank-sort each list by (depth, index),
-//                          write sorted keys back, gather descriptors, blend front to back, write all outputs
-//   backward_kernel        per work item: stage sorted keys + gathered descriptors, O(n) transmittance / suffix
-//                          sweeps per pixel, then one thread per fragment: vector reductions to HBM
-//   finalize / tangent     small epilogues
+// Kernels (nothing here is a contraction, so no tensor cores)
+//   project_kernel<count>    stream positions, strict-fp32 projection, per-level pixel, one reduction per fragment
+//   scan_*                   three-phase exclusive scan of counts -> ends, total F, longest list, work-item table
+//   project_kernel<collect>  re-project, reserve all slots of a thread's points, then store the 32-byte records
+//   sort_blend_kernel        per work item: stage records in shared memory, rank-sort each list by (depth, index),
+//                            write the sorted records back, blend front to back, write all outputs (+ _long variant)
+//   pack_images_kernel       channel-interleaved copies of the forward image and its gradient
+//   backward_kernel          per work item: stream sorted records, image-space gradient of each fragment (parked for
+//                            the per-point pass), O(n) transmittance / suffix sweeps per pixel, vector reductions of
+//                            descriptor / confidence gradients (+ _long variants; mode 3 forms its spatial gradient here)
+//   point_backward_kernel    modes 1, 2: one thread per point over all views: projection Jacobians per fragment,
+//                            position gradient written once, camera gradients reduced per CTA and view
+//   fuzzy_dt_*               mode 0 (no lists): depth pre-pass, splat, combine, per-point backward
+//   exchange_finalize_kernel multi-GPU: sum over ranks + epilogue over NVLink peer memory (plain or multicast)
+//   grid_loss_kernel         error-grid rasterisation (one warp per grid cell)
+//   transpose / normalize / apply_tangent   small epilogues
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
