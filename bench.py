@@ -11,8 +11,8 @@ GPUs (weak scaling: V views per GPU and step; by default every rank renders the 
 identical), the cloud is replicated.  The compute part of the step is replayed as a CUDA graph.
 
 The script prints ONE JSON line (rank 0).  `value` times the steps with inputs resident in HBM; `e2e` times the same
-steps with the per-step inputs (the target pyramid of every view) arriving from pinned host memory and the loss
-read back; `roofline` is the dominant kernel against the measured HBM copy bandwidth; `cpu_baseline` is the CPU
+steps with the per-step inputs (an 8-bit target image per view) arriving from pinned host memory, the target pyramid
+built on the device and the loss read back; `roofline` is the dominant kernel against the measured HBM copy bandwidth; `cpu_baseline` is the CPU
 oracle on the host cores on a bounded sample (one view of the same cloud).  `--impl reference` times that CPU
 oracle alone (the reference ships no CPU rasterizer and its CUDA sources need a library that is not available, so
 the oracle port is the reference arm).
@@ -233,12 +233,21 @@ def run_ours(args):
     stream = torch.cuda.current_stream(dev)
     rast = Rasterizer(local_rank)  # follows torch's current stream, so a step can be captured into a CUDA graph
 
-    # seeded targets of the L1 loss, one pyramid per view: device copies for `value`, pinned host copies for `e2e`
+    # seeded targets of the L1 loss: one 8-bit image per view, as a training loop holds its photographs; the target of a
+    # coarser pyramid level is the 2x2 average of the finer one, built on the device.  `value` uses a resident pyramid,
+    # `e2e` receives the 8-bit images from pinned host memory every step and builds the pyramid inside the timed region.
     gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
-    targets_host = [torch.rand(V, CHANNELS, h, w, generator=gen).pin_memory() for (w, h) in sizes]
-    targets_dev = [t.to(dev) for t in targets_host]
-    numel = [float(t.numel()) for t in targets_host]
-    h2d_bytes = sum(t.numel() * 4 for t in targets_host)
+    targets_host = (torch.rand(V, CHANNELS, H, W, generator=gen) * 255.0).to(torch.uint8).pin_memory()
+
+    def build_targets(u8, out):
+        torch.mul(u8, 1.0 / 255.0, out=out[0])  # one kernel: 8-bit in, fp32 out
+        for l in range(1, len(out)):
+            torch.ops.aten.avg_pool2d.out(out[l - 1], [2, 2], [2, 2], [0, 0], False, True, None, out=out[l])
+
+    targets_dev = [torch.empty(V, CHANNELS, h, w, device=dev) for (w, h) in sizes]
+    build_targets(targets_host.to(dev), targets_dev)
+    numel = [float(t.numel()) for t in targets_dev]
+    h2d_bytes = targets_host.numel()
 
     # fused gradient buffer: [desc 4n_tex | points 4n | conf n_tex] floats.  N > 1: it lives in symmetric memory and the
     # sum over the ranks + the epilogue is one kernel over NVLink peer memory (vet_b200.dist.PeerExchange);
@@ -306,12 +315,10 @@ def run_ours(args):
     # host's launch cost is off the critical path.  The all-reduce stays an ordinary NCCL call between the two graphs.
     # Falls back to plain launches if capture fails.
     eager_step = step
-    static_targets = [torch.empty_like(t) for t in targets_dev]
+    static_targets = [t.clone() for t in targets_dev]
     graph_info = {"used": False}
     if not args.no_graph:
         try:
-            for dst, src in zip(static_targets, targets_dev):
-                dst.copy_(src)
             for _ in range(2):  # sizes every scratch buffer (nothing may be allocated by the library during capture)
                 eager_step(static_targets)
             torch.cuda.synchronize(dev)
@@ -413,16 +420,16 @@ def run_ours(args):
     e2e = None
     if not args.no_e2e:
         copy_stream = torch.cuda.Stream(dev)
-        bufs = [[torch.empty_like(t) for t in targets_dev] for _ in range(2)]
+        bufs = [torch.empty_like(targets_host, device=dev) for _ in range(2)]
         ready = [torch.cuda.Event() for _ in range(2)]
         consumed = [torch.cuda.Event() for _ in range(2)]
-        loss_host = torch.zeros(1).pin_memory()
+        loss_host = torch.zeros(2).pin_memory()
+        loss_read = [torch.cuda.Event() for _ in range(2)]
 
         def prefetch(i):
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(consumed[i % 2])
-                for dst, src in zip(bufs[i % 2], targets_host):
-                    dst.copy_(src, non_blocking=True)
+                bufs[i % 2].copy_(targets_host, non_blocking=True)
                 ready[i % 2].record(copy_stream)
 
         def e2e_run(k):
@@ -433,9 +440,16 @@ def run_ours(args):
                 if i + 1 < k:
                     prefetch(i + 1)
                 stream.wait_event(ready[i % 2])
-                loss, _ = step(bufs[i % 2])
+                build_targets(bufs[i % 2], static_targets)
                 consumed[i % 2].record(stream)
-                loss_host.copy_(loss.reshape(1), non_blocking=False)  # device -> host read of the step's result
+                loss, _ = step(static_targets)
+                # device -> host read of the step's result: asynchronous, and the host waits for the PREVIOUS step's value
+                # before it goes on, so it never runs more than one step ahead and every loss has arrived at the end
+                loss_host[i % 2:i % 2 + 1].copy_(loss.reshape(1), non_blocking=True)
+                loss_read[i % 2].record(stream)
+                if i > 0:
+                    loss_read[(i - 1) % 2].synchronize()
+            loss_read[(k - 1) % 2].synchronize()
 
         e2e_run(min(2, args.warmup))
         barrier()
@@ -450,8 +464,8 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e = {"value": frames / (float(t[0].item()) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
                "d2h_bytes_per_step": 4, "wall_ms_per_step": float(t[1].item()) / args.steps,
-               "note": "targets of the L1 loss copied from pinned host memory every step (double-buffered on a copy "
-                       "stream), loss scalar read back every step"}
+               "note": "the views' 8-bit target images copied from pinned host memory every step (double-buffered on a copy "
+                       "stream), target pyramid built on the device, loss scalar read back every step"}
 
     # ---- per-kernel timing (CUDA events on the launching stream, outside the timed region) and roofline
     rast.set_timing(True)
