@@ -57,6 +57,7 @@ def parse_args():
                          "NVSwitch multicast object (the switch adds; falls back to peer where there is none) or with plain "
                          "peer loads / stores; auto = peer for 2 ranks, multicast for more; nccl = NCCL all-reduce + "
                          "epilogue kernels")
+    ap.add_argument("--torch-loss", action="store_true", help="form the L1 loss and its gradient with torch element-wise kernels")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     return ap.parse_args()
 
@@ -272,22 +273,27 @@ def run_ours(args):
 
     grad_bufs = [torch.empty(V, CHANNELS, h, w, device=dev) for (w, h) in sizes]
     diff_bufs = [torch.empty(V, CHANNELS, h, w, device=dev) for (w, h) in sizes]
+    loss_buf = torch.zeros((), device=dev)
 
     def compute(targets):
         """Everything of a step up to the gradient sums of this rank."""
         flat.zero_()
         out = rast.forward(position, index, texture, confidence, background, poses, intrinsics, my_views, params,
                            want_weight=True)
-        # L1 loss against the target pyramid and its gradient sign(out - target) / numel (torch element-wise kernels on
-        # preallocated buffers: plumbing around the path, not part of it)
-        grads, loss = [], None
-        for l, (c, t) in enumerate(zip(out["color"], targets)):
-            d = torch.sub(c, t, out=diff_bufs[l])
-            g = torch.sign(d, out=grad_bufs[l])
-            g.mul_(1.0 / numel[l])
-            grads.append(g)
-            term = d.abs_().sum() / numel[l]
-            loss = term if loss is None else loss + term
+        # L1 loss against the target pyramid and its gradient sign(out - target) / numel: one launch for all levels
+        # (plumbing around the path, not part of it; --torch-loss forms it with torch's element-wise kernels instead)
+        if args.torch_loss:
+            grads, loss = [], None
+            for l, (c, t) in enumerate(zip(out["color"], targets)):
+                d = torch.sub(c, t, out=diff_bufs[l])
+                g = torch.sign(d, out=grad_bufs[l])
+                g.mul_(1.0 / numel[l])
+                grads.append(g)
+                term = d.abs_().sum() / numel[l]
+                loss = term if loss is None else loss + term
+        else:
+            grads, loss = grad_bufs, loss_buf
+            rast.l1_loss_grad(out["color"], targets, grad_bufs, loss_buf)
         g = rast.backward_raw(grads, want_intrinsics=False, accum=grad_views())
         return loss, g
 

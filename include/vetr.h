@@ -243,6 +243,14 @@ int vetr_grid_loss(vetr_ctx* ctx, const vetr_cameras* cameras, const vetr_view* 
                    const float* cell_bb_min, const float* cell_bb_len, const float* loss_img, int channels,
                    float* cell_value, int32_t* cell_access_count);
 
+/* L1 loss of an output pyramid against a target pyramid and its gradient, one launch for all levels:
+ *   loss = sum_l mean |image_l - target_l| (written to the device scalar `loss`), grad_l = sign(image_l - target_l) / numel_l.
+ * No counterpart in the reference's rasterizer: its training loop forms this term with libtorch element-wise operators
+ * between PointRender's forward and backward; the benchmark's step does the same with this call.
+ * image, target, grad: num_levels device pointers (16-byte aligned) of numel[l] floats each. */
+int vetr_l1_loss_grad(vetr_ctx* ctx, int num_levels, const float* const* image, const float* const* target,
+                      float* const* grad, const int64_t* numel, float* loss);
+
 /* ApplyTangentToPose (PointRenderer.cu:1325-1349): poses[i] <- exp_se3(tangent[i]) * poses[i]; tangent[i] <- 0. */
 int vetr_apply_tangent(vetr_ctx* ctx, double* tangent /*[n,6]*/, double* poses_se3 /*[n,8]*/, int n);
 

@@ -309,3 +309,22 @@ def test_committed_fixture_grid_loss(rasterizer):
                              t(data["grid_loss_img"]), value, count)
     np.testing.assert_array_equal(count.cpu().numpy().astype(np.int64), data["grid_count"])
     np.testing.assert_allclose(value.cpu().numpy(), data["grid_value"], rtol=1e-5)
+
+
+def test_l1_loss_grad(rasterizer):
+    """The one-launch L1 loss + gradient against torch's element-wise operators (odd sizes: unaligned level tails)."""
+    import torch
+
+    dev = rasterizer.device
+    gen = torch.Generator(device="cpu").manual_seed(2)
+    shapes = [(2, 3, 7, 9), (2, 3, 3, 4), (1, 1, 1, 1), (2, 4, 16, 16)]
+    images = [torch.rand(s, generator=gen).to(dev) for s in shapes]
+    targets = [torch.rand(s, generator=gen).to(dev) for s in shapes]
+    targets[0][0, 0, 0, :3] = images[0][0, 0, 0, :3]  # exact zeros: sign(0) = 0
+    grads = [torch.full_like(t, float("nan")) for t in images]
+    loss = torch.full((), float("nan"), device=dev)
+    rasterizer.l1_loss_grad(images, targets, grads, loss)
+    want = sum((i - t).abs().mean() for i, t in zip(images, targets))
+    assert abs(loss.item() - want.item()) <= 1e-5 * want.item()
+    for i, t, g in zip(images, targets, grads):
+        assert torch.equal(g, torch.sign(i - t) * (1.0 / i.numel()))

@@ -67,7 +67,7 @@ EXPORTS = [
     "vetr_item_table_entries", "vetr_max_fragments", "vetr_forward", "vetr_backward", "vetr_finalize_gradients",
     "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists", "vetr_set_timing", "vetr_get_timings",
     "vetr_launch_count", "vetr_scan_counts_static", "vetr_exchange_raw_floats", "vetr_exchange_out_floats",
-    "vetr_exchange_finalize", "vetr_grid_loss",
+    "vetr_exchange_finalize", "vetr_grid_loss", "vetr_l1_loss_grad",
 ]
 TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize", "point_backward", "exchange"]
 
@@ -122,6 +122,7 @@ def lib():
         L.vetr_exchange_out_floats.argtypes = [C.c_int, C.c_int, C.c_int]
         L.vetr_exchange_out_floats.restype = C.c_int64
         L.vetr_exchange_finalize.argtypes = [vp, C.POINTER(Exchange), C.c_int, C.c_int, C.c_int]
+        L.vetr_l1_loss_grad.argtypes = [vp, C.c_int, vp, vp, vp, C.POINTER(C.c_int64), vp]
         L.vetr_grid_loss.argtypes = [vp, C.POINTER(Cameras), C.POINTER(View), C.c_float, C.c_int, vp, vp, vp, C.c_int, vp, vp]
         _lib = L
     return _lib

@@ -2298,6 +2298,72 @@ __global__ void __launch_bounds__(32 * kGridWarps) grid_loss_kernel(const __grid
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// L1 loss of the whole output pyramid against a target pyramid and its gradient, in one launch (what a training step
+// does between the forward and the backward pass; with library element-wise kernels it is seven launches per level).
+
+struct L1Args
+{
+    const float* image[VETR_MAX_LAYERS];
+    const float* target[VETR_MAX_LAYERS];
+    float* grad[VETR_MAX_LAYERS];
+    long long end[VETR_MAX_LAYERS];  // running element count: level l covers [end[l-1], end[l])
+    float inv_numel[VETR_MAX_LAYERS];
+    int levels;
+    float* loss;
+};
+
+__global__ void __launch_bounds__(256) l1_loss_grad_kernel(const __grid_constant__ L1Args a)
+{
+    __shared__ float s_part[8];
+    const long long total  = a.end[a.levels - 1];
+    const long long stride = (long long)gridDim.x * blockDim.x * 4;
+    float sum = 0.f;
+    // four consecutive elements per thread where they lie in one level and are 16-byte aligned, else one by one
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < total; i += stride)
+    {
+        int l = 0;
+#pragma unroll
+        for (int k = 1; k < VETR_MAX_LAYERS; ++k)
+            if (k < a.levels && i >= a.end[k - 1]) l = k;
+        const long long base = l ? a.end[l - 1] : 0, j = i - base, n = a.end[l] - base;
+        const float w = a.inv_numel[l];
+        if (j + 4 <= n && ((j & 3) == 0))
+        {
+            const float4 x = __ldg(reinterpret_cast<const float4*>(a.image[l] + j));
+            const float4 t = __ldg(reinterpret_cast<const float4*>(a.target[l] + j));
+            const float d[4] = {x.x - t.x, x.y - t.y, x.z - t.z, x.w - t.w};
+            float g[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) g[k] = d[k] > 0.f ? w : (d[k] < 0.f ? -w : 0.f), sum += fabsf(d[k]) * w;
+            *reinterpret_cast<float4*>(a.grad[l] + j) = make_float4(g[0], g[1], g[2], g[3]);
+        }
+        else
+        {
+            for (long long e = i; e < min(i + 4, total); ++e)
+            {
+                int le = 0;
+#pragma unroll
+                for (int k = 1; k < VETR_MAX_LAYERS; ++k)
+                    if (k < a.levels && e >= a.end[k - 1]) le = k;
+                const long long je = e - (le ? a.end[le - 1] : 0);
+                const float d = a.image[le][je] - a.target[le][je], we = a.inv_numel[le];
+                a.grad[le][je] = d > 0.f ? we : (d < 0.f ? -we : 0.f);
+                sum += fabsf(d) * we;
+            }
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        float t = 0.f;
+        for (int k = 0; k < 8; ++k) t += s_part[k];
+        atomicAdd(a.loss, t);
+    }
+}
+
 }  // namespace vetr
 
 // =========================================================================================================
@@ -2847,6 +2913,32 @@ extern "C" int vetr_grid_loss(vetr_ctx* ctx, const vetr_cameras* cams, const vet
         const int ctas = min((n_cells + kGridWarps - 1) / kGridWarps, ctx->sm_count * 16);
         grid_loss_kernel<<<ctas, 32 * kGridWarps, 0, ctx->stream>>>(f, a);
     }
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+extern "C" int vetr_l1_loss_grad(vetr_ctx* ctx, int num_levels, const float* const* image, const float* const* target,
+                                 float* const* grad, const int64_t* numel, float* loss)
+{
+    if (!ctx || num_levels < 1 || num_levels > VETR_MAX_LAYERS || !image || !target || !grad || !numel || !loss)
+        return VETR_E_INVALID_ARG;
+    L1Args a;
+    memset(&a, 0, sizeof(a));
+    long long run = 0;
+    for (int l = 0; l < num_levels; ++l)
+    {
+        if (!image[l] || !target[l] || !grad[l] || numel[l] < 1) return VETR_E_INVALID_ARG;
+        if ((((uintptr_t)image[l] | (uintptr_t)target[l] | (uintptr_t)grad[l]) & 15) != 0) return VETR_E_INVALID_ARG;
+        a.image[l] = image[l], a.target[l] = target[l], a.grad[l] = grad[l];
+        run += numel[l];
+        a.end[l]       = run;
+        a.inv_numel[l] = 1.f / (float)numel[l];
+    }
+    a.levels = num_levels, a.loss = loss;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    VETR_CUDA(ctx, cudaMemsetAsync(loss, 0, sizeof(float), ctx->stream));
+    ctx->launches += 1;
+    l1_loss_grad_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(a);
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }

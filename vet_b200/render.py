@@ -287,6 +287,14 @@ class Rasterizer:
                                     _ptr(cell_access_count))
         self._check(rc, "vetr_grid_loss")
 
+    def l1_loss_grad(self, images, targets, grads, loss):
+        """loss (device scalar) = sum over levels of mean |image - target|; grads[l] = sign(image - target) / numel, one launch."""
+        self._sync_stream()
+        n = len(images)
+        numel = (C.c_int64 * n)(*[t.numel() for t in images])
+        rc = L.lib().vetr_l1_loss_grad(self._ctx, n, _ptr_array(images), _ptr_array(targets), _ptr_array(grads), numel, _ptr(loss))
+        self._check(rc, "vetr_l1_loss_grad")
+
     def set_timing(self, enable: bool):
         self._sync_stream()
         self._check(L.lib().vetr_set_timing(self._ctx, int(enable)), "vetr_set_timing")
