@@ -832,7 +832,44 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
     }
 }
 
-// Lists longer than kLongList: one CTA per list, sort in global memory, fold in blocks of kCap fragments.
+// Lists longer than kLongList: one CTA per list.  Up to kLongSortMax fragments the whole list is staged in shared memory,
+// rank-sorted there and written back in order (the reference's <= 4096 bucket is a CTA-wide shared-memory sort as well,
+// AlphaListSort.cu:601-703); longer lists are sorted in global memory.  The fold runs in blocks of kCap fragments.
+constexpr int kLongSortMax = 2048;
+struct LongSortSmem
+{
+    uint4 rec[2 * kLongSortMax];
+    unsigned long long key[kLongSortMax];
+    unsigned short perm[kLongSortMax];
+};
+constexpr size_t kLongBlendSmem = sizeof(LongSortSmem) > sizeof(BlendSmem) ? sizeof(LongSortSmem) : sizeof(BlendSmem);
+
+__device__ void sort_long_list_shared(const Frame& f, LongSortSmem& ls, int first, int n)
+{
+    uint4* recs = f.recs + 2 * (size_t)first;
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+    {
+        const uint4 h = recs[2 * i];
+        ls.rec[2 * i] = h, ls.rec[2 * i + 1] = recs[2 * i + 1];
+        ls.key[i]     = record_key(h);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+    {
+        const unsigned long long key = ls.key[i];
+        int rank = 0;
+        for (int k = 0; k < n; ++k) rank += ls.key[k] < key;
+        ls.perm[rank] = (unsigned short)i;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < n; r += blockDim.x)
+    {
+        const int u = ls.perm[r];
+        recs[2 * r] = ls.rec[2 * u], recs[2 * r + 1] = ls.rec[2 * u + 1];
+    }
+    __syncthreads();  // the fold below reads the sorted records back and reuses this shared memory
+}
+
 __global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_constant__ Frame f,
                                                                    const __grid_constant__ OutPtrs out)
 {
@@ -850,7 +887,10 @@ __global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_
         const int e0 = list_end(f, lo - 1);
         const int n  = f.ends[lo] - e0;
         __syncthreads();
-        sort_long_list(f, e0, n);
+        if (n <= kLongSortMax)
+            sort_long_list_shared(f, *reinterpret_cast<LongSortSmem*>(smem_raw), e0, n);
+        else
+            sort_long_list(f, e0, n);
         int cnt = n;
         if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
         if (tid == 0)
@@ -2500,7 +2540,7 @@ extern "C" int vetr_create(vetr_ctx** out, int device, void* cuda_stream)
     if (e == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
     const int blend_smem = (int)sizeof(BlendSmem), back_smem = (int)sizeof(BackSmem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(sort_blend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, blend_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(sort_blend_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, blend_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(sort_blend_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLongBlendSmem);
     const int fuzzy_smem = (int)sizeof(BackSmemFuzzy), fuzzy_long_smem = (int)sizeof(FuzzyLongSmem);
     const auto smem_attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
     if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, false, false>, smem_attr, back_smem);
@@ -2722,7 +2762,7 @@ extern "C" int vetr_forward(vetr_ctx* ctx, const vetr_params* params, const vetr
         PassScope t(ctx, VETR_T_SORT_BLEND, 2);
         const int grid = ctx->sm_count * ctx->blend_ctas_per_sm;
         sort_blend_kernel<<<grid, kThreads, sizeof(BlendSmem), st>>>(f, out);
-        sort_blend_long_kernel<<<ctx->sm_count, kThreads, sizeof(BlendSmem), st>>>(f, out);
+        sort_blend_long_kernel<<<ctx->sm_count * 2, kThreads, kLongBlendSmem, st>>>(f, out);
     }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
