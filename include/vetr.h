@@ -127,12 +127,16 @@ typedef struct vetr_lists
     int64_t   items_capacity; /* >= vetr_item_table_entries(capacity, n_views*P) */
     uint8_t*  level_mask;  /* [n_views*n] written by vetr_forward when not NULL: bit l set = the point has a fragment on
                               pyramid level l of that view */
-    float*    point_grad;  /* [n_views*num_layers*n*2] scratch of vetr_backward: image-space gradient of every fragment,
-                              indexed by (view, level, point).  The position / pose / intrinsics gradients of modes 1 and 2
-                              are then formed in one coalesced pass over the points (every fragment's term computed exactly
-                              as in ProjectPointPinholeBackward, summed per point in a fixed order, no atomics on g_points).
-                              Both arrays are required by vetr_backward in modes 1 and 2 when need_point_gradient is set;
-                              level_mask must be the one the forward call wrote.  Neither needs initialising. */
+    float*    point_grad;  /* 16-byte aligned scratch of vetr_backward, indexed by (view, level, point): modes 1 and 2
+                              [n_views*num_layers*n*2], the image-space gradient of the point's fragment on that level;
+                              mode 3 [n_views*num_layers*n*4], the alpha gradient of its four bilinear fragments.  The
+                              position / pose / intrinsics gradients (and mode 3's confidence gradient) are then formed
+                              in one coalesced pass over the points: every fragment's term computed exactly as in
+                              ProjectPointPinholeBackward, summed per point in a fixed order, no atomics on g_points.
+                              Both arrays are required by vetr_backward in mode 3, and in modes 1 and 2 when
+                              need_point_gradient is set; level_mask must be the one the forward call wrote.  Neither
+                              needs initialising.  Mode 3 keeps a fragment's corner in the two top bits of the record's
+                              descriptor index, so n_tex must stay below 2^30 there. */
     float*    pixel_scratch; /* [n_views*P*8] 16-byte aligned scratch of vetr_backward in modes 1-3: channel-interleaved
                                 copies of out_color and grad_color over the pixel space (eight 16-byte loads fetch all
                                 neighbour values of a fragment).  Needs no initialising. */

@@ -116,6 +116,10 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
     float4* grad4;              // [PT] its incoming gradient
 };
 
+// Mode 3 keeps the bilinear corner of a fragment in the two top bits of the record's descriptor index.
+constexpr int kCornerShift = 30;
+constexpr int kTexMask     = (1 << kCornerShift) - 1;
+
 // One fragment record = one 32-byte sector.
 __device__ __forceinline__ void store_record(const Frame& f, int slot, unsigned long long key, float alpha, int tex, float4 d)
 {
@@ -264,15 +268,22 @@ __global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_cons
         return;
     }
 
-    // mode 3: every (point, level) touches the four pixels around its position
+    // mode 3: every (point, level) touches the four pixels around its position.  The record's descriptor index carries
+    // the corner (0..3) in its two top bits: the backward pass files a fragment's result under (point, level, corner).
 #pragma unroll
     for (int it = 0; it < kPts; ++it)
     {
         const int pid = first + it * kProjThreads;
         if (pid >= f.n) break;
-        if (!point_is_live(f, b, pid)) continue;
-        const Projected pr = project_point(pos[it], cam, f.dist_cutoff);
-        if (pr.z == 0.f) continue;
+        unsigned level_bits = 0;
+        Projected pr;
+        pr.z = 0.f;
+        if (point_is_live(f, b, pid)) pr = project_point(pos[it], cam, f.dist_cutoff);
+        if (pr.z == 0.f)
+        {
+            if (kCollect && f.level_mask) f.level_mask[(size_t)b * f.n + pid] = 0;
+            continue;
+        }
         float2 ip     = pr.ip;
         float radius  = pr.radius_px;
         const unsigned long long key = ((unsigned long long)__float_as_uint(pr.z) << 32) | (unsigned)pid;
@@ -313,10 +324,16 @@ __global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_cons
             {
 #pragma unroll
                 for (int cidx = 0; cidx < 4; ++cidx)
-                    if (slot[cidx] >= 0 && (long long)slot[cidx] < f.capacity)
-                        store_record(f, slot[cidx], key, blending_fac(ip, cidx, nullptr, nullptr) * conf, tex, desc);  // RenderForward.cu:1619
+                {
+                    if (slot[cidx] < 0) continue;
+                    level_bits |= 1u << l;
+                    if ((long long)slot[cidx] < f.capacity)
+                        store_record(f, slot[cidx], key, blending_fac(ip, cidx, nullptr, nullptr) * conf,  // RenderForward.cu:1619
+                                     tex | (cidx << kCornerShift), desc);
+                }
             }
         }
+        if (kCollect && f.level_mask) f.level_mask[(size_t)b * f.n + pid] = (unsigned char)level_bits;
     }
 }
 
@@ -530,24 +547,6 @@ __device__ void sort_long_list(const Frame& f, int first, int n)
             __syncthreads();
         }
     }
-}
-
-// Mode 3: level-space image position of a point and the bilinear corner a pixel is of it.  The reference stores
-// both per fragment (per_point_data, RenderForward.cu:1116-1127); the backward pass recomputes them with the same
-// arithmetic, which gives the same bits.
-__device__ __forceinline__ float2 level_position(const Frame& f, const Camera& cam, int pid, int level, float4* pos_out)
-{
-    float4 pos   = __ldg(f.position + pid);
-    Projected pr = project_point(pos, cam, f.dist_cutoff);
-    float2 ip    = pr.ip;
-    for (int l = 0; l < level; ++l) ip.x *= 0.5f, ip.y *= 0.5f;
-    if (pos_out) *pos_out = pos;
-    return ip;
-}
-__device__ __forceinline__ int corner_of(float2 ip, const PixInfo& px)
-{
-    int bx = round_down(ip.x), by = round_down(ip.y);
-    return min(max((px.y - by) * 2 + (px.x - bx), 0), 3);
 }
 
 // Which list a staged fragment belongs to.  The thread that owns a pixel writes its index over the pixel's slots when
@@ -983,7 +982,6 @@ struct BackSmem
     PixInfo pix[kMaxPixels];
     SegTable seg;
     double red[kThreads / 32][8];  // cross-warp reduction scratch
-    Camera cam[VETR_MAX_VIEWS];
 };
 
 // Mode 2 additionally needs every fragment's descriptor and depth (groups average them) and two group markers.
@@ -1209,27 +1207,26 @@ __device__ __forceinline__ void fragment_stage_a(const Frame& f, BackSmem& s, in
     }
 }
 
-// Stage B of a fragment (after the sweeps): descriptor and confidence gradients, and in mode 3 the spatial gradient.
-template <bool kIntr, bool kBilinear>
-__device__ __forceinline__ void fragment_stage_b(const Frame& f, const BackPtrs& bp, const Camera& cam, const PixInfo& px,
-                                                 float4 G, int pid, int tex, float Ta, float galpha, CamAcc<kIntr>& acc)
+// Stage B of a fragment (after the sweeps): the descriptor gradient, and the confidence gradient - directly in modes 1
+// and 2; in mode 3 it is weighted by the bilinear weight of the fragment's corner, which needs the point's projection, so
+// the fragment's alpha gradient is parked under (view, level, point, corner) for point_backward_kernel (the reference
+// writes it for interior pixels only, RenderBackward.cu:3053).  `blended` = false: the list ended before this fragment.
+template <bool kBilinear>
+__device__ __forceinline__ void fragment_stage_b(const Frame& f, const BackPtrs& bp, const PixInfo& px, float4 G, int pid,
+                                                 int tex_word, float Ta, float galpha, bool blended)
 {
+    if (kBilinear)
+    {
+        const int corner  = (unsigned)tex_word >> kCornerShift;
+        float* parked     = reinterpret_cast<float*>(f.point_grad);
+        const size_t slot = ((((size_t)px.view * f.L + px.level) * f.n + pid) << 2) + corner;
+        parked[slot]      = blended && px.interior ? galpha : __int_as_float(kNoGradientBits);
+        if (!blended) return;
+    }
+    const int tex = kBilinear ? tex_word & kTexMask : tex_word;
     // descriptor gradient: T * alpha * G  (RenderBackward.cu:1149-1152)
     red_add_v4(bp.g_desc + tex, make_float4(Ta * G.x, Ta * G.y, Ta * G.z, f.C > 3 ? Ta * G.w : 0.f));
-    if (!kBilinear)
-    {
-        red_add(bp.g_conf + tex, galpha);
-        return;
-    }
-    if (!px.interior) return;  // the reference writes the mode-3 confidence gradient for interior pixels only
-    float4 pos;
-    float2 ip = level_position(f, cam, pid, px.level, &pos);
-    float jx, jy;
-    float w = blending_fac(ip, corner_of(ip, px), &jx, &jy);
-    red_add(bp.g_conf + tex, w * galpha);  // RenderBackward.cu:3076-3079
-    if (!f.need_point_grad) return;
-    float single = __ldg(f.confidence + tex) * galpha;
-    spatial_backward<kIntr>(f, bp, cam, px, pid, pos, make_float2(jx * single, jy * single), acc);
+    if (!kBilinear) red_add(bp.g_conf + tex, galpha);
 }
 
 // Transmittance forward and suffix sum backward over one list held in shared memory: the O(n) form of the
@@ -1385,28 +1382,20 @@ struct BackSmemOf<true>
     using type = BackSmemFuzzy;
 };
 
-// kBilinear: mode 3, whose position / camera gradients are formed per fragment after the sweeps (stage B) and summed
-// per thread block and view; modes 1 and 2 leave them to point_backward_kernel.
-template <bool kIntr, bool kFuzzy, bool kBilinear>
+// Position / camera gradients are left to point_backward_kernel in every mode.
+template <bool kFuzzy, bool kBilinear>
 __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kernel(const __grid_constant__ Frame f,
                                                                                    const __grid_constant__ BackPtrs bp)
 {
-    static_assert(!(kFuzzy && kBilinear) && (kBilinear || !kIntr), "camera gradients are formed here in mode 3 only");
+    static_assert(!(kFuzzy && kBilinear), "mode 2 and mode 3 exclude each other");
     using Smem = typename BackSmemOf<kFuzzy>::type;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Smem& s = *reinterpret_cast<Smem*>(smem_raw);
     const int tid     = threadIdx.x;
     const int n_items = f.status[3];
     const float4 bgc  = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
-    if (kBilinear && tid < f.n_views) s.cam[tid] = load_camera(f, tid);
-
-    CamAcc<kIntr> acc;
-    acc.clear();
-    int acc_view    = -1;  // view the accumulators belong to (items of a CTA come in view order)
     float bg_acc[4] = {0.f, 0.f, 0.f, 0.f};
     float p0_acc    = 0.f;
-    const int P     = (int)f.P;
-    const bool want_cam = kBilinear && (bp.g_pose != nullptr || kIntr);
     if (tid == 0) s.seg.n_long[0] = s.seg.n_long[1] = 0;
     int parity = 0;
 #ifdef VETR_PHASE_TIMING
@@ -1415,21 +1404,13 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x)
     {
-        int lo_item = f.item_start[item];
-        const int hi_item = f.item_start[item + 1];
-        if (lo_item >= hi_item) continue;
-        lo_item += long_prefix(f, lo_item);
-        // a run of pixels of one view at a time, so that camera gradients belong to a single view
-        for (int lo = lo_item; lo < hi_item;)
+        int lo = f.item_start[item];
+        const int hi = f.item_start[item + 1];
+        if (lo >= hi) continue;
+        lo += long_prefix(f, lo);
+        if (lo >= hi) continue;
         {
-            const int view = lo / P;
-            const int hi   = min(hi_item, (view + 1) * P);
-            if (view != acc_view)
-            {
-                if (acc_view >= 0 && want_cam) reduce_cam<kIntr>(f, bp, acc, acc_view, s.red);
-                acc_view = view;
-            }
-            __syncthreads();  // every warp has left the previous run (and the cameras are loaded)
+            __syncthreads();  // every warp has left the previous item
             PHASE_MARK(0);
             parity ^= 1;
             if (tid == 0) s.seg.n_long[parity ^ 1] = 0;
@@ -1447,7 +1428,6 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
             if (tid == 0) s.seg_end[0] = 0;
             __syncthreads();
             PHASE_MARK(1);
-            const Camera& cam = s.cam[view];
             const int nf = s.seg_end[np];
             for (int i = tid; i < nf; i += kThreads)
             {
@@ -1475,26 +1455,24 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
             PHASE_MARK(3);
             for (int i = tid; i < nf; i += kThreads)
             {
-                const float Ti = s.trans[i];
-                if (Ti != Ti) continue;
+                const float Ti     = s.trans[i];
+                const bool blended = Ti == Ti;  // NaN: the list ended before this fragment
+                if (!kBilinear && !blended) continue;
                 const int a = seg_lookup(s.seg, parity, s.seg_end, i);
-                fragment_stage_b<kIntr, kBilinear>(f, bp, cam, s.pix[a], s.grad[a], s.pid[i], s.tex[i], Ti, s.dot[i], acc);
+                fragment_stage_b<kBilinear>(f, bp, s.pix[a], s.grad[a], s.pid[i], s.tex[i], Ti, s.dot[i], blended);
             }
             PHASE_MARK(4);
-            lo = hi;
         }
     }
-    if (acc_view >= 0 && want_cam) reduce_cam<kIntr>(f, bp, acc, acc_view, s.red);
     reduce_background(f, bp, s, bg_acc, p0_acc);
 }
 
 // Lists longer than kLongList: one CTA per list, blocks of kCap fragments, a forward sweep that records the
 // transmittance at every block start and a backward sweep over the blocks that carries the suffix sum.
-template <bool kIntr, bool kBilinear>
+template <bool kBilinear>
 __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_constant__ Frame f,
                                                                  const __grid_constant__ BackPtrs bp)
 {
-    static_assert(kBilinear || !kIntr, "camera gradients are formed here in mode 3 only");
     if (f.status[2] <= kLongList) return;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BackSmem& s = *reinterpret_cast<BackSmem*>(smem_raw);
@@ -1504,8 +1482,6 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
     const int n_items   = f.status[3];
     constexpr bool bilinear = kBilinear;
     const float4 bgc    = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
-    CamAcc<kIntr> acc;
-    acc.clear();
     float bg_acc[4] = {0.f, 0.f, 0.f, 0.f};
     float p0_acc    = 0.f;
 
@@ -1517,7 +1493,6 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
         const int n  = f.ends[lo] - e0;
         const PixInfo px = decode_pixel(f, (unsigned)lo);
         __syncthreads();
-        if (kBilinear && tid == 0) s.cam[0] = load_camera(f, px.view);
         const float4 G = load_grad(f, lo);
         int cnt = n;
         if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
@@ -1525,7 +1500,6 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
         const int n_blocks = (cnt + kCap - 1) / kCap;
         if (tid == 0) s_carry[0] = 1.f, s_carry[2] = (float)cnt;
         __syncthreads();
-        const Camera& cam = s.cam[0];
         // sweep 1: transmittance at block starts and the position where a mode-3 list stops
         for (int blk = 0; blk < n_blocks; ++blk)
         {
@@ -1592,15 +1566,19 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
             }
             __syncthreads();
             for (int i = tid; i < m; i += kThreads)
-                fragment_stage_b<kIntr, kBilinear>(f, bp, cam, px, G, s.pid[i], s.tex[i], s.trans[i], s.dot[i], acc);
+                fragment_stage_b<kBilinear>(f, bp, px, G, s.pid[i], s.tex[i], s.trans[i], s.dot[i], true);
             __syncthreads();
         }
-        // fragments behind the cut take no part in the position gradient
-        if (!kBilinear && f.need_point_grad)
+        // fragments behind the cut take no part in the position gradient (mode 3: nor in the confidence gradient)
+        if (kBilinear || f.need_point_grad)
             for (int i = eff_cnt + tid; i < n; i += kThreads)
-                f.point_grad[((size_t)px.view * f.L + px.level) * f.n + (int)f.recs[2 * (size_t)(e0 + i)].x] =
-                    make_float2(__int_as_float(kNoGradientBits), 0.f);
-        if (kBilinear && (bp.g_pose != nullptr || kIntr)) reduce_cam<kIntr>(f, bp, acc, px.view, s.red);
+            {
+                const uint4 h = f.recs[2 * (size_t)(e0 + i)];
+                if (kBilinear)
+                    fragment_stage_b<kBilinear>(f, bp, px, G, (int)h.x, (int)h.w, 0.f, 0.f, false);
+                else
+                    f.point_grad[((size_t)px.view * f.L + px.level) * f.n + (int)h.x] = make_float2(__int_as_float(kNoGradientBits), 0.f);
+            }
     }
     reduce_background(f, bp, s, bg_acc, p0_acc);
 }
@@ -1675,28 +1653,34 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Modes 1 and 2: position, pose and intrinsics gradients, one pass over the points.  Every fragment's term is
-// ProjectPointPinholeBackward of the image-space gradient that stage A parked for it, evaluated with the arithmetic
-// of the per-fragment form (so each addend has the reference's bits); a point's terms are summed in registers in a
-// fixed order (view, level) and added to g_points by the one thread that owns the point.  Positions, masks and
-// parked gradients are read coalesced; camera gradients are summed per thread block and view.
+// Position, pose and intrinsics gradients (and the confidence gradient of mode 3), one pass over the points.
+//
+// Modes 1 and 2: every fragment's term is ProjectPointPinholeBackward of the image-space gradient that stage A parked
+// for it.  Mode 3: the fragment's alpha gradient was parked under (view, level, point, corner); here the point is
+// projected once per view exactly as the forward pass did (same bits), which gives the corner weights and their
+// Jacobians (compute_blending_fac) of all its fragments: confidence gradient += w * g_alpha, image-space gradient =
+// J_uv * confidence * g_alpha (RenderBackward.cu:3076-3180).  In every mode a fragment's term is evaluated with the
+// arithmetic of the per-fragment form (each addend has the reference's bits); a point's terms are summed in registers
+// in a fixed order and added to g_points by the one thread that owns the point.  Positions, masks and parked values are
+// read coalesced; camera gradients are summed per thread block and view.
 
 #ifndef VETR_POINT_BACK_POINTS
 #    define VETR_POINT_BACK_POINTS 2
 #endif
 constexpr int kPointBackPoints = VETR_POINT_BACK_POINTS;
 
-template <bool kIntr>
+template <bool kIntr, bool kBilinear>
 __global__ void __launch_bounds__(kProjThreads) point_backward_kernel(const __grid_constant__ Frame f,
                                                                       const __grid_constant__ BackPtrs bp)
 {
     __shared__ Camera s_cam[VETR_MAX_VIEWS];
     __shared__ double s_red[kProjThreads / 32][8];
-    if (f.status[1] != 0) return;  // overflow / skipped list: some fragments never parked a gradient
+    if (f.status[1] != 0) return;  // overflow / skipped list: some fragments never parked a value
     if (threadIdx.x < f.n_views) s_cam[threadIdx.x] = load_camera(f, threadIdx.x);
     __syncthreads();
     const int first     = blockIdx.x * (kProjThreads * kPointBackPoints) + threadIdx.x;
     const bool want_cam = bp.g_pose != nullptr || kIntr;
+    const bool spatial  = f.need_point_grad != 0;
     float4 pos[kPointBackPoints], gp[kPointBackPoints];
 #pragma unroll
     for (int it = 0; it < kPointBackPoints; ++it)
@@ -1722,20 +1706,63 @@ __global__ void __launch_bounds__(kProjThreads) point_backward_kernel(const __gr
         {
             const int pid = first + it * kProjThreads;
             if (!mask[it]) continue;
-            float2 dR[VETR_MAX_LAYERS];
-#pragma unroll
-            for (int l = 0; l < VETR_MAX_LAYERS; ++l)
-                if (mask[it] >> l & 1u) dR[l] = f.point_grad[((size_t)b * f.L + l) * f.n + pid];
-            PointJac jac;
-            if (!project_backward_prepare(pos[it], s_cam[b], f.dist_cutoff, kIntr, jac)) continue;
-#pragma unroll
-            for (int l = 0; l < VETR_MAX_LAYERS; ++l)
+            if constexpr (!kBilinear)
             {
-                if (!(mask[it] >> l & 1u) || __float_as_int(dR[l].x) == kNoGradientBits) continue;
-                BackOut bo;
-                spatial_terms<kIntr>(f, bp, s_cam[b], l, jac, dR[l], acc, bo);
-                gp[it].x += bo.g_point[0], gp[it].y += bo.g_point[1], gp[it].z += bo.g_point[2], gp[it].w += 1.f;
-                any = true;
+                float2 dR[VETR_MAX_LAYERS];
+#pragma unroll
+                for (int l = 0; l < VETR_MAX_LAYERS; ++l)
+                    if (mask[it] >> l & 1u) dR[l] = f.point_grad[((size_t)b * f.L + l) * f.n + pid];
+                PointJac jac;
+                if (!project_backward_prepare(pos[it], s_cam[b], f.dist_cutoff, kIntr, jac)) continue;
+#pragma unroll
+                for (int l = 0; l < VETR_MAX_LAYERS; ++l)
+                {
+                    if (!(mask[it] >> l & 1u) || __float_as_int(dR[l].x) == kNoGradientBits) continue;
+                    BackOut bo;
+                    spatial_terms<kIntr>(f, bp, s_cam[b], l, jac, dR[l], acc, bo);
+                    gp[it].x += bo.g_point[0], gp[it].y += bo.g_point[1], gp[it].z += bo.g_point[2], gp[it].w += 1.f;
+                    any = true;
+                }
+            }
+            else
+            {
+                const float* parked = reinterpret_cast<const float*>(f.point_grad);
+                float4 ga[VETR_MAX_LAYERS];  // the four corners' alpha gradients of every level
+#pragma unroll
+                for (int l = 0; l < VETR_MAX_LAYERS; ++l)
+                    if (mask[it] >> l & 1u) ga[l] = *reinterpret_cast<const float4*>(parked + ((((size_t)b * f.L + l) * f.n + pid) << 2));
+                const int tex    = __ldg(f.index + pid);
+                const float conf = __ldg(f.confidence + tex);
+                const Projected pr = project_point(pos[it], s_cam[b], f.dist_cutoff);
+                PointJac jac;
+                const bool jac_ok = spatial && project_backward_prepare(pos[it], s_cam[b], f.dist_cutoff, kIntr, jac);
+                float2 ip   = pr.ip;
+                float gconf = 0.f;
+#pragma unroll
+                for (int l = 0; l < VETR_MAX_LAYERS; ++l, ip.x *= 0.5f, ip.y *= 0.5f)
+                {
+                    if (!(mask[it] >> l & 1u)) continue;
+                    const int bx = round_down(ip.x), by = round_down(ip.y);
+                    const float gl[4] = {ga[l].x, ga[l].y, ga[l].z, ga[l].w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                    {
+                        // the same in-image test as the collection pass: corners outside never became fragments
+                        const int x = bx + (c & 1), y = by + (c >> 1);
+                        if ((unsigned)x >= (unsigned)f.lw[l] || (unsigned)y >= (unsigned)f.lh[l]) continue;
+                        if (__float_as_int(gl[c]) == kNoGradientBits) continue;
+                        float jx, jy;
+                        const float w = blending_fac(ip, c, &jx, &jy);
+                        gconf += w * gl[c];  // RenderBackward.cu:3076-3079
+                        if (!jac_ok) continue;
+                        const float single = conf * gl[c];
+                        BackOut bo;
+                        spatial_terms<kIntr>(f, bp, s_cam[b], l, jac, make_float2(jx * single, jy * single), acc, bo);
+                        gp[it].x += bo.g_point[0], gp[it].y += bo.g_point[1], gp[it].z += bo.g_point[2], gp[it].w += 1.f;
+                        any = true;
+                    }
+                }
+                if (gconf != 0.f) red_add(bp.g_conf + tex, gconf);
             }
         }
         if (want_cam && __syncthreads_or(any)) reduce_cam<kIntr>(f, bp, acc, b, s_red);
@@ -2543,22 +2570,20 @@ extern "C" int vetr_create(vetr_ctx** out, int device, void* cuda_stream)
     if (e == cudaSuccess) e = cudaFuncSetAttribute(sort_blend_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLongBlendSmem);
     const int fuzzy_smem = (int)sizeof(BackSmemFuzzy), fuzzy_long_smem = (int)sizeof(FuzzyLongSmem);
     const auto smem_attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, false, false>, smem_attr, back_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, false, true>, smem_attr, back_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<true, false, true>, smem_attr, back_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, true, false>, smem_attr, fuzzy_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, false>, smem_attr, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<false, true>, smem_attr, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_kernel<true, false>, smem_attr, fuzzy_smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_fuzzy_long_kernel, smem_attr, fuzzy_long_smem);
     if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->fuzzy_ctas_per_sm, backward_kernel<false, true, false>, kThreads, fuzzy_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<false, false>, smem_attr, back_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<false, true>, smem_attr, back_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<true, true>, smem_attr, back_smem);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->fuzzy_ctas_per_sm, backward_kernel<true, false>, kThreads, fuzzy_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<false>, smem_attr, back_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(backward_long_kernel<true>, smem_attr, back_smem);
     if (e == cudaSuccess)
         e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->blend_ctas_per_sm, sort_blend_kernel, kThreads, blend_smem);
     if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->back_ctas_per_sm, backward_kernel<false, false, false>, kThreads, back_smem);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->back_ctas_per_sm, backward_kernel<false, false>, kThreads, back_smem);
     if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->bilinear_ctas_per_sm, backward_kernel<false, false, true>, kThreads, back_smem);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctx->bilinear_ctas_per_sm, backward_kernel<false, true>, kThreads, back_smem);
     if (e != cudaSuccess)
     {
         delete ctx;
@@ -2810,10 +2835,13 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
         return VETR_OK;
     }
     const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
-    // modes 1 and 2: position / camera gradients come from the per-point pass over the gradients stage A parks
-    const bool point_pass = !bilinear && f.need_point_grad && (bp.g_points || g_pose || g_intr);
-    if (!bilinear && !point_pass) f.need_point_grad = 0;
-    if (point_pass && (!f.level_mask || !f.point_grad)) return VETR_E_INVALID_ARG;
+    // position / camera gradients (and mode 3's confidence gradient) come from the per-point pass over what the
+    // per-fragment kernel parks
+    const bool spatial    = f.need_point_grad && (bp.g_points || g_pose || g_intr);
+    const bool point_pass = bilinear || spatial;
+    if (!spatial) f.need_point_grad = 0;
+    if (point_pass && (!f.level_mask || !f.point_grad || ((uintptr_t)f.point_grad & 15) != 0)) return VETR_E_INVALID_ARG;
+    if (bilinear && f.n_tex > kTexMask) return VETR_E_TOO_LARGE;
     if (!f.img4 || ((uintptr_t)f.img4 & 15) != 0) return VETR_E_INVALID_ARG;
     {
         PassScope t(ctx, VETR_T_BACKWARD, 3);
@@ -2822,38 +2850,41 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
         if (f.mode == VETR_MODE_FUZZY_BLEND)
         {
             const int grid = ctx->sm_count * ctx->fuzzy_ctas_per_sm;
-            backward_kernel<false, true, false><<<grid, kThreads, sizeof(BackSmemFuzzy), st>>>(f, bp);
+            backward_kernel<true, false><<<grid, kThreads, sizeof(BackSmemFuzzy), st>>>(f, bp);
             backward_fuzzy_long_kernel<<<ctx->sm_count, kThreads, sizeof(FuzzyLongSmem), st>>>(f, bp);
         }
         else if (bilinear)
         {
             const int grid = ctx->sm_count * ctx->bilinear_ctas_per_sm;
-            if (g_intr)
-            {
-                backward_kernel<true, false, true><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
-                backward_long_kernel<true, true><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
-            }
-            else
-            {
-                backward_kernel<false, false, true><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
-                backward_long_kernel<false, true><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
-            }
+            backward_kernel<false, true><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
+            backward_long_kernel<true><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
         }
         else
         {
             const int grid = ctx->sm_count * ctx->back_ctas_per_sm;
-            backward_kernel<false, false, false><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
-            backward_long_kernel<false, false><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
+            backward_kernel<false, false><<<grid, kThreads, sizeof(BackSmem), st>>>(f, bp);
+            backward_long_kernel<false><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
         }
     }
     if (point_pass && f.n > 0)
     {
         PassScope t(ctx, VETR_T_POINT_BACKWARD, 1);
         const int ctas = (f.n + kProjThreads * kPointBackPoints - 1) / (kProjThreads * kPointBackPoints);
-        if (g_intr)
-            point_backward_kernel<true><<<ctas, kProjThreads, 0, ctx->stream>>>(f, bp);
+        cudaStream_t st = ctx->stream;
+        if (bilinear)
+        {
+            if (g_intr)
+                point_backward_kernel<true, true><<<ctas, kProjThreads, 0, st>>>(f, bp);
+            else
+                point_backward_kernel<false, true><<<ctas, kProjThreads, 0, st>>>(f, bp);
+        }
         else
-            point_backward_kernel<false><<<ctas, kProjThreads, 0, ctx->stream>>>(f, bp);
+        {
+            if (g_intr)
+                point_backward_kernel<true, false><<<ctas, kProjThreads, 0, st>>>(f, bp);
+            else
+                point_backward_kernel<false, false><<<ctas, kProjThreads, 0, st>>>(f, bp);
+        }
     }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;

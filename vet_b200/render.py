@@ -172,7 +172,7 @@ class Rasterizer:
             nb = b1 - b0
             cap = capacity if capacity is not None else int(lib.vetr_max_fragments(position.shape[0], nb, C.byref(prm)))
             lists = self._lists(gi, P * nb, cap, exact=capacity is not None)
-            if prm.render_mode in (1, 2) and prm.need_point_gradient:
+            if prm.render_mode == 3 or (prm.render_mode in (1, 2) and prm.need_point_gradient):
                 lists.ensure_level_mask(nb * position.shape[0])
             varr = self._views(views[b0:b1])
             sl = lambda ts: None if ts is None else [t[b0:b1] for t in ts]
@@ -244,8 +244,9 @@ class Rasterizer:
             gc = [t[b0:b1] for t in grad_color]
             dro = s["tensors"][7]
             lists.ensure_pixel_scratch()
-            if lists.level_mask is not None:
-                lists.ensure_point_grad((b1 - b0) * s["prm"].num_layers * n * 2)
+            if lists.level_mask is not None:  # 2 floats per (view, level, point), 4 (one per bilinear corner) in mode 3
+                per = 4 if s["prm"].render_mode == 3 else 2
+                lists.ensure_point_grad((b1 - b0) * s["prm"].num_layers * n * per)
             rc = lib.vetr_backward(self._ctx, C.byref(s["prm"]), C.byref(s["cloud"]), C.byref(s["tex"]),
                                    C.byref(s["cams"]), varr, b1 - b0, _ptr(None if dro is None else dro[b0:b1]),
                                    C.byref(lists.c), _ptr_array(oc), _ptr_array(gc),

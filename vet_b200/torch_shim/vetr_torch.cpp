@@ -236,8 +236,9 @@ variable_list PointRender::forward(AutogradContext* ctx, Variable texture, Varia
     for (int b0 = 0; b0 < B; b0 += VETR_MAX_VIEWS, ++n_groups)
     {
         const int b1 = std::min(B, b0 + VETR_MAX_VIEWS), nb = b1 - b0;
-        const bool point_pass = (prm.render_mode == VETR_MODE_FULL_BLEND || prm.render_mode == VETR_MODE_FUZZY_BLEND) &&
-                                prm.need_point_gradient;
+        const bool point_pass = prm.render_mode == VETR_MODE_BILINEAR_BLEND ||
+                                ((prm.render_mode == VETR_MODE_FULL_BLEND || prm.render_mode == VETR_MODE_FUZZY_BLEND) &&
+                                 prm.need_point_gradient);
         GroupLists g = alloc_lists(P * nb, vetr_max_fragments(in.cloud.n, nb, &prm),
                                    point_pass ? (int64_t)nb * in.cloud.n : 0, dev);
         auto views   = make_views(*info, b0, b1);
@@ -302,7 +303,9 @@ variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_out
         auto* t = &saved[5 + L + 6 * gi];
         // scratch of the per-point pass that forms the position / pose / intrinsics gradients of modes 1 and 2
         torch::Tensor point_grad;
-        if ((prm.render_mode == VETR_MODE_FULL_BLEND || prm.render_mode == VETR_MODE_FUZZY_BLEND) && prm.need_point_gradient)
+        if (prm.render_mode == VETR_MODE_BILINEAR_BLEND)
+            point_grad = torch::empty({(int64_t)nb * L * n * 4}, f32);  // one value per bilinear corner
+        else if ((prm.render_mode == VETR_MODE_FULL_BLEND || prm.render_mode == VETR_MODE_FUZZY_BLEND) && prm.need_point_gradient)
             point_grad = torch::empty({(int64_t)nb * L * n * 2}, f32);
         torch::Tensor pixel_scratch = torch::empty({std::max<int64_t>(t[0].size(0), 1) * 8}, f32);
         vetr_lists lists = {t[0].data_ptr<int>(), t[1].data_ptr<int>(), t[2].data_ptr(), t[2].size(0), t[3].data_ptr<int>(),
