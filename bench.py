@@ -544,6 +544,34 @@ def run_ours(args):
                                    "workload": f"{cells}^3 cells over a 20-unit box, one {W}x{H} view, 3-channel loss image"}}
         del bb_min, bb_len, loss_img, cell_value, cell_count
 
+        # the same step in mode 3 (bilinear splats: four fragments per point and level; the mode the reference's shipped
+        # configuration trains with), a few launches without graph replay, reported beside the headline
+        if args.mode == 1:
+            p3 = default_params(render_mode=3, num_layers=LAYERS, num_channels=CHANNELS)
+            rast._lists_cache.clear()
+            torch.cuda.empty_cache()
+            m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps3 = 3
+            for it in range(reps3 + 1):
+                if it == 1:
+                    m0.record(stream)
+                out3 = rast.forward(position, index, texture, confidence, background, poses, intrinsics, my_views, p3,
+                                    want_weight=True)
+                rast.l1_loss_grad(out3["color"], targets_dev, grad_bufs, loss_buf)
+                flat.zero_()
+                g3 = rast.backward_raw(grad_bufs, want_intrinsics=False, accum=grad_views())
+                rast.finalize(g3)
+            m1.record(stream)
+            torch.cuda.synchronize(dev)
+            F3, longest3 = rast.fragment_count()
+            ms3 = m0.elapsed_time(m1) / reps3
+            next_rows["mode3"] = {"ms_per_step": ms3, "frames_per_s": V / (ms3 * 1e-3), "fragments": F3,
+                                  "longest_list": longest3, "workload": "the headline step in render mode 3"}
+            del out3, g3
+            rast._lists_cache.clear()
+            rast._saved = None
+            torch.cuda.empty_cache()
+
     # ---- CPU baseline on the host cores (rank 0, N = 1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
