@@ -57,6 +57,9 @@ def parse_args():
                          "NVSwitch multicast object (the switch adds; falls back to peer where there is none) or with plain "
                          "peer loads / stores; auto = peer for 2 ranks, multicast for more; nccl = NCCL all-reduce + "
                          "epilogue kernels")
+    ap.add_argument("--overlap", action="store_true",
+                    help="N > 1: run the per-point pass of the backward step beside the exchange of the descriptor / confidence "
+                         "segments (measured no faster at N = 2: the extra collective and launches cost what the overlap saves)")
     ap.add_argument("--torch-loss", action="store_true", help="form the L1 loss and its gradient with torch element-wise kernels")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     return ap.parse_args()
@@ -264,6 +267,8 @@ def run_ours(args):
     else:
         flat = torch.zeros(4 * n_tex + 4 * n + n_tex, dtype=torch.float32, device=dev)
 
+    overlap = peer is not None and args.overlap
+
     def grad_views():
         g = dict(desc=flat[:4 * n_tex].view(n_tex, 4), points=flat[4 * n_tex:4 * n_tex + 4 * n].view(n, 4),
                  conf=flat[4 * n_tex + 4 * n:], background=torch.zeros(CHANNELS, device=dev),
@@ -294,13 +299,15 @@ def run_ours(args):
         else:
             grads, loss = grad_bufs, loss_buf
             rast.l1_loss_grad(out["color"], targets, grad_bufs, loss_buf)
-        g = rast.backward_raw(grads, want_intrinsics=False, accum=grad_views())
+        # N > 1 with the peer-memory exchange: only the per-fragment kernels here; the per-point pass runs in exchange(),
+        # beside the exchange of the segments that are already final
+        g = rast.backward_raw(grads, want_intrinsics=False, accum=grad_views(), phases=1 if overlap else 3)
         return loss, g
 
     def exchange(g):
         """The one exchange step of view-sharded data parallelism: sum the gradient buffers over the ranks."""
-        if peer is not None:
-            return peer.run(g)  # sum + epilogue in one kernel; returns the finished gradients
+        if peer is not None:  # sum + epilogue in one kernel over peer memory; returns the finished gradients
+            return peer.run_overlapped(grad_bufs, g, bilinear=args.mode == 3) if overlap else peer.run(g)
         if world > 1:
             dist.all_reduce(flat)
             dist.all_reduce(g["pose"])
@@ -591,7 +598,7 @@ def run_ours(args):
                        "views_per_gpu": V, "views_mode": args.views_mode if world > 1 else None, "points": N, "l2": "inputs larger than L2 (cloud 128 MB + descriptors 160 MB + "
                                                               "pyramids; gradient buffer 288 MB rewritten every step)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
-            "loss": float(loss.item()), "step_ms": [round(x, 3) for x in step_ms], "cuda_graph": graph_info, "exchange": exchange_kind, "per_rank": per_rank, "next_rows": next_rows,
+            "loss": float(loss.item()), "step_ms": [round(x, 3) for x in step_ms], "cuda_graph": graph_info, "exchange": exchange_kind + ("+overlap" if overlap else ""), "per_rank": per_rank, "next_rows": next_rows,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -197,6 +197,18 @@ int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* cl
                   float* g_points, float* g_background, double* g_pose, float* g_pose_count, float* g_intr,
                   float* g_intr_count);
 
+/* The same in two calls, for hosts that start exchanging the descriptor / confidence gradients while the position
+ * gradients are still being formed: VETR_BACKWARD_FRAGMENTS enqueues the per-fragment kernels (afterwards g_desc,
+ * g_background and, in modes 1 and 2, g_conf are final), VETR_BACKWARD_POINTS the per-point pass (g_points, g_pose,
+ * g_intr; in mode 3 also g_conf).  vetr_backward is both.  Mode 0 does everything in the first phase. */
+#define VETR_BACKWARD_FRAGMENTS 1
+#define VETR_BACKWARD_POINTS 2
+int vetr_backward_phase(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* cloud, const vetr_texture* texture,
+                        const vetr_cameras* cameras, const vetr_view* views, int n_views, const float* dropout,
+                        const vetr_lists* lists, const float* const* out_color, const float* const* grad_color,
+                        float* g_desc, float* g_conf, float* g_points, float* g_background, double* g_pose,
+                        float* g_pose_count, float* g_intr, float* g_intr_count, int phases);
+
 /* Epilogue of the backward pass: converts the accumulation buffers into the tensors the reference returns
  * (PointRenderer.cu:1251-1322): g_texture [channels,n_tex] channel-major (transpose of g_desc), and the count
  * normalisation of NormalizeGradient / NormalizeGradientDevTensor (PointRenderer.cu:1072-1109): point gradients
@@ -233,6 +245,15 @@ typedef struct vetr_exchange
 int64_t vetr_exchange_raw_floats(int n_tex, int n);
 int64_t vetr_exchange_out_floats(int channels, int n_tex, int n);
 int vetr_exchange_finalize(vetr_ctx* ctx, const vetr_exchange* ex, int channels, int n_tex, int n);
+/* One or two of the three segments only (VETR_SEG_* bits), on a grid of ctas_per_sm (1..8) thread blocks per SM: lets a
+ * host run the descriptor / confidence part on a second stream beside vetr_backward_phase(VETR_BACKWARD_POINTS), with a
+ * small grid so that both kernels are resident, and the position part afterwards.  Each part needs the ordering
+ * described above with respect to the kernels that produce its segment. */
+#define VETR_SEG_DESC 1
+#define VETR_SEG_POINTS 2
+#define VETR_SEG_CONF 4
+int vetr_exchange_finalize_part(vetr_ctx* ctx, const vetr_exchange* ex, int channels, int n_tex, int n, int segments,
+                                int ctas_per_sm);
 
 /* Error-grid rasterisation: PointRendererCache::FillSceneGridWithLoss -> FillSceneGridWithLossRasterize
  * (RenderForward.cu:639-791; called per image from train.cpp:1077 before the tomography's point spawning).  For every

@@ -46,6 +46,11 @@ def main():
             g1 = rast.backward_raw(grads, want_intrinsics=False, accum=peer.buffer.as_accum(ch, poses.shape[0]))
             r1 = peer.run(g1)
         results.append(tuple(r1[k].clone() for k in ("texture", "points", "confidence", "pose")))
+        # the same with the per-point pass beside the exchange of the descriptor / confidence segments
+        peer.buffer.zero_()
+        g1 = rast.backward_raw(grads, want_intrinsics=False, accum=peer.buffer.as_accum(ch, poses.shape[0]), phases=1)
+        r1 = peer.run_overlapped(grads, g1)
+        results.append(tuple(r1[k].clone() for k in ("texture", "points", "confidence", "pose")))
         if rank == 0:
             print("exchange ran with multicast =", peer.multicast, flush=True)
 

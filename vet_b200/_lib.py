@@ -67,8 +67,10 @@ EXPORTS = [
     "vetr_item_table_entries", "vetr_max_fragments", "vetr_forward", "vetr_backward", "vetr_finalize_gradients",
     "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists", "vetr_set_timing", "vetr_get_timings",
     "vetr_launch_count", "vetr_scan_counts_static", "vetr_exchange_raw_floats", "vetr_exchange_out_floats",
-    "vetr_exchange_finalize", "vetr_grid_loss", "vetr_l1_loss_grad",
+    "vetr_exchange_finalize", "vetr_grid_loss", "vetr_l1_loss_grad", "vetr_backward_phase", "vetr_exchange_finalize_part",
 ]
+BACKWARD_FRAGMENTS, BACKWARD_POINTS = 1, 2
+SEG_DESC, SEG_POINTS, SEG_CONF = 1, 2, 4
 TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize", "point_backward", "exchange"]
 
 _lib = None
@@ -106,6 +108,7 @@ def lib():
                                    C.POINTER(View), C.c_int, vp, C.POINTER(Lists), vp, vp, vp, vp]
         L.vetr_backward.argtypes = [vp, C.POINTER(Params), C.POINTER(Cloud), C.POINTER(Texture), C.POINTER(Cameras),
                                     C.POINTER(View), C.c_int, vp, C.POINTER(Lists), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.vetr_backward_phase.argtypes = L.vetr_backward.argtypes + [C.c_int]
         L.vetr_finalize_gradients.argtypes = [vp, C.c_int, C.c_int, vp, vp, C.c_int, vp, vp, C.c_int, vp, vp, C.c_int,
                                               vp, vp]
         L.vetr_apply_tangent.argtypes = [vp, vp, vp, C.c_int]
@@ -122,6 +125,7 @@ def lib():
         L.vetr_exchange_out_floats.argtypes = [C.c_int, C.c_int, C.c_int]
         L.vetr_exchange_out_floats.restype = C.c_int64
         L.vetr_exchange_finalize.argtypes = [vp, C.POINTER(Exchange), C.c_int, C.c_int, C.c_int]
+        L.vetr_exchange_finalize_part.argtypes = [vp, C.POINTER(Exchange), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
         L.vetr_l1_loss_grad.argtypes = [vp, C.c_int, vp, vp, vp, C.POINTER(C.c_int64), vp]
         L.vetr_grid_loss.argtypes = [vp, C.POINTER(Cameras), C.POINTER(View), C.c_float, C.c_int, vp, vp, vp, C.c_int, vp, vp]
         _lib = L

@@ -2103,6 +2103,7 @@ struct ExchangeArgs
     float* out[VETR_MAX_RANKS];
     const float* raw_mc;  // multicast address of the raw buffers (NVLink SHARP), or nullptr
     float* out_mc;        // multicast address of the output buffers
+    int segments;         // VETR_SEG_* bits: which of the three segments this launch handles
 };
 
 __device__ __forceinline__ void slice_of(long long count, int rank, int world, long long& lo, long long& hi)
@@ -2183,6 +2184,7 @@ __global__ void __launch_bounds__(32 * kExchangeWarps) exchange_finalize_kernel(
     // 128-byte run in each channel row.  Rows start at c * n_tex floats: 16-byte aligned only if n_tex % 4 == 0.
     const long long tiles = (n_tex & 3) == 0 ? n_tex / 32 : 0;
     slice_of(tiles, a.rank, a.world, lo, hi);
+    if (!(a.segments & VETR_SEG_DESC)) hi = lo;
     const int c = lane >> 3, q = lane & 7;
     for (long long tile = lo + gwarp; tile < hi; tile += 2 * n_warps)
     {
@@ -2207,6 +2209,7 @@ __global__ void __launch_bounds__(32 * kExchangeWarps) exchange_finalize_kernel(
     {
         const long long first = tiles * 32;
         slice_of(n_tex - first, a.rank, a.world, lo, hi);
+        if (!(a.segments & VETR_SEG_DESC)) hi = lo;
         for (long long t = first + lo + gtid; t < first + hi; t += stride)
         {
             const float4 v = rank_sum4<false>(a, 4 * t);
@@ -2217,6 +2220,7 @@ __global__ void __launch_bounds__(32 * kExchangeWarps) exchange_finalize_kernel(
 
     // position gradient sums with the hit count in .w -> average (NormalizeGradient, PointRenderer.cu:1273-1280)
     slice_of(a.n, a.rank, a.world, lo, hi);
+    if (!(a.segments & VETR_SEG_POINTS)) hi = lo;
     for (long long base = lo + gtid; base < hi; base += stride * 4)
     {
         float4 v[4];
@@ -2238,6 +2242,7 @@ __global__ void __launch_bounds__(32 * kExchangeWarps) exchange_finalize_kernel(
     // takes the n_tex % 4 texels that are left over
     const long long groups = n_tex / 4;
     slice_of(groups, a.rank, a.world, lo, hi);
+    if (!(a.segments & VETR_SEG_CONF)) hi = lo;
     for (long long base = lo + gtid; base < hi; base += stride * 4)
     {
         float4 v[4];
@@ -2248,7 +2253,7 @@ __global__ void __launch_bounds__(32 * kExchangeWarps) exchange_finalize_kernel(
         for (int u = 0; u < 4; ++u)
             if (base + u * stride < hi) rank_store4<kMulticast>(a, a.out_conf + 4 * (base + u * stride), v[u]);
     }
-    if (a.rank == a.world - 1)
+    if (a.rank == a.world - 1 && (a.segments & VETR_SEG_CONF))
         for (long long t = 4 * groups + gtid; t < n_tex; t += stride) rank_store1(a, a.out_conf + t, rank_sum1(a, raw_conf + t));
     __threadfence_system();  // the peer stores are performed before the kernel counts as finished
 }
@@ -2800,6 +2805,19 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
                              float* g_points, float* g_background, double* g_pose, float* g_pose_count, float* g_intr,
                              float* g_intr_count)
 {
+    return vetr_backward_phase(ctx, params, cloud, texture, cameras, views, n_views, dropout, lists, out_color, grad_color,
+                               g_desc, g_conf, g_points, g_background, g_pose, g_pose_count, g_intr, g_intr_count,
+                               VETR_BACKWARD_FRAGMENTS | VETR_BACKWARD_POINTS);
+}
+
+extern "C" int vetr_backward_phase(vetr_ctx* ctx, const vetr_params* params, const vetr_cloud* cloud,
+                                   const vetr_texture* texture, const vetr_cameras* cameras, const vetr_view* views,
+                                   int n_views, const float* dropout, const vetr_lists* lists,
+                                   const float* const* out_color, const float* const* grad_color, float* g_desc,
+                                   float* g_conf, float* g_points, float* g_background, double* g_pose,
+                                   float* g_pose_count, float* g_intr, float* g_intr_count, int phases)
+{
+    if ((phases & ~(VETR_BACKWARD_FRAGMENTS | VETR_BACKWARD_POINTS)) != 0 || phases == 0) return VETR_E_INVALID_ARG;
     Frame f;
     int rc = fill_frame(ctx, f, params, cloud, texture, cameras, views, n_views, lists);
     if (rc != VETR_OK) return rc;
@@ -2820,6 +2838,7 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
     f.dropout = dropout;
     if (f.mode == VETR_MODE_FUZZY_DT)
     {
+        if (!(phases & VETR_BACKWARD_FRAGMENTS)) return VETR_OK;  // mode 0 has one phase
         PassScope t(ctx, VETR_T_BACKWARD, 2);
         cudaStream_t st = ctx->stream;
         fuzzy_dt_background_kernel<<<ctx->sm_count * 4, 256, 0, st>>>(f, bp);
@@ -2843,6 +2862,7 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
     if (point_pass && (!f.level_mask || !f.point_grad || ((uintptr_t)f.point_grad & 15) != 0)) return VETR_E_INVALID_ARG;
     if (bilinear && f.n_tex > kTexMask) return VETR_E_TOO_LARGE;
     if (!f.img4 || ((uintptr_t)f.img4 & 15) != 0) return VETR_E_INVALID_ARG;
+    if (phases & VETR_BACKWARD_FRAGMENTS)
     {
         PassScope t(ctx, VETR_T_BACKWARD, 3);
         cudaStream_t st = ctx->stream;
@@ -2866,7 +2886,7 @@ extern "C" int vetr_backward(vetr_ctx* ctx, const vetr_params* params, const vet
             backward_long_kernel<false><<<ctx->sm_count, kThreads, sizeof(BackSmem), st>>>(f, bp);
         }
     }
-    if (point_pass && f.n > 0)
+    if ((phases & VETR_BACKWARD_POINTS) && point_pass && f.n > 0)
     {
         PassScope t(ctx, VETR_T_POINT_BACKWARD, 1);
         const int ctas = (f.n + kProjThreads * kPointBackPoints - 1) / (kProjThreads * kPointBackPoints);
@@ -2930,7 +2950,15 @@ extern "C" int64_t vetr_exchange_out_floats(int channels, int n_tex, int n)
 
 extern "C" int vetr_exchange_finalize(vetr_ctx* ctx, const vetr_exchange* ex, int channels, int n_tex, int n)
 {
+    return vetr_exchange_finalize_part(ctx, ex, channels, n_tex, n, VETR_SEG_DESC | VETR_SEG_POINTS | VETR_SEG_CONF, 4);
+}
+
+extern "C" int vetr_exchange_finalize_part(vetr_ctx* ctx, const vetr_exchange* ex, int channels, int n_tex, int n,
+                                           int segments, int ctas_per_sm)
+{
     if (!ctx || !ex || (channels != 3 && channels != 4) || n_tex < 1 || n < 0) return VETR_E_INVALID_ARG;
+    if (segments <= 0 || (segments & ~(VETR_SEG_DESC | VETR_SEG_POINTS | VETR_SEG_CONF)) != 0) return VETR_E_INVALID_ARG;
+    if (ctas_per_sm < 1 || ctas_per_sm > 8) return VETR_E_INVALID_ARG;
     if (ex->world < 1 || ex->world > VETR_MAX_RANKS || ex->rank < 0 || ex->rank >= ex->world) return VETR_E_INVALID_ARG;
     ExchangeArgs a;
     memset(&a, 0, sizeof(a));
@@ -2946,12 +2974,13 @@ extern "C" int vetr_exchange_finalize(vetr_ctx* ctx, const vetr_exchange* ex, in
     if ((ex->raw_multicast != nullptr) != (ex->out_multicast != nullptr)) return VETR_E_INVALID_ARG;
     if (((uintptr_t)ex->raw_multicast & 15) != 0 || ((uintptr_t)ex->out_multicast & 15) != 0) return VETR_E_INVALID_ARG;
     a.raw_mc = ex->raw_multicast, a.out_mc = ex->out_multicast;
+    a.segments = segments;
     VETR_CUDA(ctx, cudaSetDevice(ctx->device));
     PassScope t(ctx, VETR_T_EXCHANGE, 1);
     if (a.raw_mc)
-        exchange_finalize_kernel<true><<<ctx->sm_count * 4, 32 * kExchangeWarps, 0, ctx->stream>>>(a);
+        exchange_finalize_kernel<true><<<ctx->sm_count * ctas_per_sm, 32 * kExchangeWarps, 0, ctx->stream>>>(a);
     else
-        exchange_finalize_kernel<false><<<ctx->sm_count * 4, 32 * kExchangeWarps, 0, ctx->stream>>>(a);
+        exchange_finalize_kernel<false><<<ctx->sm_count * ctas_per_sm, 32 * kExchangeWarps, 0, ctx->stream>>>(a);
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }

@@ -108,30 +108,33 @@ class PeerExchange:
         self._handles = (h_raw, h_out)
         self.buffer = GradientBuffer(n, n_tex, device, flat=self.raw)
         self._token = torch.zeros(1, dtype=torch.float32, device=device)
+        self._side = None
         p0 = (channels * n_tex + 3) // 4 * 4
         self.texture = self.out[: channels * n_tex].view(channels, n_tex)
         self.points = self.out[p0: p0 + 4 * n].view(n, 4)
         self.confidence = self.out[p0 + 4 * n:].view(1, n_tex)
 
-    def run(self, g: dict) -> dict:
-        """g: the dict backward accumulated into (its desc / points / conf are views of self.buffer).  Returns the
-        finished gradients (views of the result buffer, the same on every rank) plus the reduced small tensors."""
+    def _launch(self, segments: int, ctas_per_sm: int):
         from . import _lib as L
 
-        first = g.get("pose") if g.get("pose") is not None else self._token
-        dist.all_reduce(first, group=self.group)
         self.rast._sync_stream()
-        rc = L.lib().vetr_exchange_finalize(self.rast._ctx, self.c, self.channels, self.n_tex, self.n)
-        self.rast._check(rc, "vetr_exchange_finalize")
+        rc = L.lib().vetr_exchange_finalize_part(self.rast._ctx, self.c, self.channels, self.n_tex, self.n, segments, ctas_per_sm)
+        self.rast._check(rc, "vetr_exchange_finalize_part")
+
+    def _finish(self, g: dict) -> dict:
+        """The collective that orders the consumers after all ranks' exchange kernels (and reduces the hit counts of the
+        pose gradients), the small remaining reductions and the count normalisation of the camera gradients."""
+        from . import _lib as L
+
         second = g.get("pose_count") if g.get("pose_count") is not None else self._token
         dist.all_reduce(second, group=self.group)
         for key in ("background", "intrinsics", "intrinsics_count"):
             if g.get(key) is not None:
                 dist.all_reduce(g[key], group=self.group)
-        # count normalisation of the small camera gradients (the point-parameter part is already finished)
         pose, intr = g.get("pose"), g.get("intrinsics")
         if pose is not None or intr is not None:
             ptr = lambda t: None if t is None else C.c_void_p(t.data_ptr())
+            self.rast._sync_stream()
             rc = L.lib().vetr_finalize_gradients(
                 self.rast._ctx, self.channels, 0, None, None, 0, None, None,
                 0 if pose is None else pose.shape[0], ptr(pose), ptr(g.get("pose_count")),
@@ -139,3 +142,39 @@ class PeerExchange:
             self.rast._check(rc, "vetr_finalize_gradients")
         return dict(texture=self.texture, points=self.points, confidence=self.confidence, background=g.get("background"),
                     pose=pose, intrinsics=intr)
+
+    def run(self, g: dict) -> dict:
+        """g: the dict backward accumulated into (its desc / points / conf are views of self.buffer).  Returns the
+        finished gradients (views of the result buffer, the same on every rank) plus the reduced small tensors."""
+        first = g.get("pose") if g.get("pose") is not None else self._token
+        dist.all_reduce(first, group=self.group)
+        self._launch(7, 4)
+        return self._finish(g)
+
+    def run_overlapped(self, grad_color, g: dict, bilinear: bool = False) -> dict:
+        """Second half of a backward step whose per-fragment kernels (Rasterizer.backward_raw(..., phases=1)) are already
+        enqueued: the exchange of the segments those kernels finished (descriptor gradient, and the confidence gradient
+        except in mode 3) runs on a side stream with one thread block per SM BESIDE the per-point pass, the rest after it.
+
+            main stream:  all-reduce(token) -> per-point pass -> all-reduce(pose) -> exchange(rest) -> join -> all-reduce(count)
+            side stream:        wait        -> exchange(descriptor [, confidence])
+        """
+        from . import _lib as L
+
+        if self._side is None:
+            self._side = torch.cuda.Stream(self.raw.device)
+            self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+        main = torch.cuda.current_stream(self.raw.device)
+        early = L.SEG_DESC | (0 if bilinear else L.SEG_CONF)
+        dist.all_reduce(self._token, group=self.group)  # every rank's per-fragment kernels have finished
+        self._fork.record(main)
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(self._fork)
+            self._launch(early, 1)
+            self._join.record(self._side)
+        self.rast.backward_raw(grad_color, want_intrinsics=g.get("intrinsics") is not None, accum=g, phases=2)
+        first = g.get("pose") if g.get("pose") is not None else self._token
+        dist.all_reduce(first, group=self.group)        # every rank's per-point pass has finished
+        self._launch(7 & ~early, 4)
+        main.wait_event(self._join)
+        return self._finish(g)

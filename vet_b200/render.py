@@ -215,10 +215,12 @@ class Rasterizer:
         raise IndexError(view)
 
     # ---- backward ----------------------------------------------------------------------------------------
-    def backward_raw(self, grad_color, want_points=True, want_pose=True, want_intrinsics=True, accum=None):
+    def backward_raw(self, grad_color, want_points=True, want_pose=True, want_intrinsics=True, accum=None, phases=3):
         """Raw gradient sums of the last forward: dict(desc [n_tex,4], conf [n_tex], points [n,4] (xyz sum, hit count),
         background [C], pose [n_img,6] f64, pose_count, intrinsics [n_cam,13], intrinsics_count).
-        `accum` (a dict from an earlier call) accumulates further views into the same buffers."""
+        `accum` (a dict from an earlier call) accumulates further views into the same buffers.
+        `phases`: 1 = the per-fragment kernels only, 2 = the per-point pass only (with the `accum` of the first call and the
+        same `grad_color`), 3 = both (vetr_backward_phase)."""
         s = self._saved
         lib = L.lib()
         self._sync_stream()
@@ -247,13 +249,13 @@ class Rasterizer:
             if lists.level_mask is not None:  # 2 floats per (view, level, point), 4 (one per bilinear corner) in mode 3
                 per = 4 if s["prm"].render_mode == 3 else 2
                 lists.ensure_point_grad((b1 - b0) * s["prm"].num_layers * n * per)
-            rc = lib.vetr_backward(self._ctx, C.byref(s["prm"]), C.byref(s["cloud"]), C.byref(s["tex"]),
-                                   C.byref(s["cams"]), varr, b1 - b0, _ptr(None if dro is None else dro[b0:b1]),
-                                   C.byref(lists.c), _ptr_array(oc), _ptr_array(gc),
-                                   _ptr(g["desc"]), _ptr(g["conf"]), _ptr(g.get("points")), _ptr(g["background"]),
-                                   _ptr(g.get("pose")), _ptr(g.get("pose_count")), _ptr(g.get("intrinsics")),
-                                   _ptr(g.get("intrinsics_count")))
-            self._check(rc, "vetr_backward")
+            rc = lib.vetr_backward_phase(self._ctx, C.byref(s["prm"]), C.byref(s["cloud"]), C.byref(s["tex"]),
+                                         C.byref(s["cams"]), varr, b1 - b0, _ptr(None if dro is None else dro[b0:b1]),
+                                         C.byref(lists.c), _ptr_array(oc), _ptr_array(gc),
+                                         _ptr(g["desc"]), _ptr(g["conf"]), _ptr(g.get("points")), _ptr(g["background"]),
+                                         _ptr(g.get("pose")), _ptr(g.get("pose_count")), _ptr(g.get("intrinsics")),
+                                         _ptr(g.get("intrinsics_count")), phases)
+            self._check(rc, "vetr_backward_phase")
         return g
 
     def finalize(self, g: dict):
