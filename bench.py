@@ -49,6 +49,7 @@ def parse_args():
     ap.add_argument("--mode", type=int, default=1, choices=[1, 3])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-next-rows", action="store_true", help="skip the measurements reported beside the headline (grid loss, mode 3)")
     ap.add_argument("--prewarm", type=float, default=1.0, help="seconds of untimed load before the warm-up steps")
     ap.add_argument("--views-mode", choices=["same", "distinct"], default="same",
                     help="N > 1: every rank renders the same V camera poses (identical per-GPU work), or V poses of its own")
@@ -530,7 +531,7 @@ def run_ours(args):
     # ---- the path's next row, measured beside the headline: error-grid rasterisation of one view's loss image over a
     # 128^3 grid around the scene (FillSceneGridWithLoss; one launch per training image at the end of an epoch)
     next_rows = None
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.no_next_rows:
         cells = 128
         ax = torch.linspace(-10.0, 10.0, cells + 1, device=dev)[:-1]
         gx, gy, gz = torch.meshgrid(ax, ax, ax, indexing="ij")

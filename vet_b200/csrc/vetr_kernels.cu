@@ -595,6 +595,41 @@ __device__ __forceinline__ int long_prefix(const Frame& f, int lo)
     return (f.ends[lo] - list_end(f, lo - 1)) > kLongList ? 1 : 0;
 }
 
+// Work items whose first pixel holds a long list, for the kernels that take one such list per CTA.  Testing an item costs
+// four dependent loads (two table entries, two list ends), and only a few items in a thousand qualify, so the threads of
+// a CTA test one item each and the CTA then works through the hits: next() is called by all threads and returns the same
+// pixel to all of them.  CTA b owns the items b, b + gridDim.x, ... (long lists cluster at the coarse levels, i.e. in
+// consecutive items: the stride spreads them over the CTAs).
+struct LongItemScan
+{
+    int base, k, n;  // base: index of the next batch among the CTA's own items
+    __device__ __forceinline__ LongItemScan() : base(0), k(0), n(0) {}
+    __device__ bool next(const Frame& f, int n_items, int* s_hits, int* s_count, int& lo)
+    {
+        for (;;)
+        {
+            if (k < n)
+            {
+                lo = s_hits[k++];
+                return true;
+            }
+            __syncthreads();  // every thread has taken the last hit of the previous batch
+            if ((long long)blockIdx.x + (long long)base * gridDim.x >= n_items) return false;
+            if (threadIdx.x == 0) *s_count = 0;
+            __syncthreads();
+            const long long item = (long long)blockIdx.x + (long long)(base + threadIdx.x) * gridDim.x;
+            if (item < n_items)
+            {
+                const int first = f.item_start[item], last = f.item_start[item + 1];
+                if (first < last && long_prefix(f, first)) s_hits[atomicAdd(s_count, 1)] = first;
+            }
+            __syncthreads();
+            n = *s_count, k = 0;
+            base += blockDim.x;
+        }
+    }
+};
+
 struct OutPtrs
 {
     float* color[VETR_MAX_LAYERS];
@@ -879,10 +914,11 @@ __global__ void __launch_bounds__(kThreads) sort_blend_long_kernel(const __grid_
     const int tid       = threadIdx.x;
     const int n_items   = f.status[3];
     const bool bilinear = f.mode == VETR_MODE_BILINEAR_BLEND;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x)
+    __shared__ int s_long_hits[kThreads], s_long_count;
+    LongItemScan scan;
+    int lo;
+    while (scan.next(f, n_items, s_long_hits, &s_long_count, lo))
     {
-        const int lo = f.item_start[item], hi = f.item_start[item + 1];
-        if (lo >= hi || !long_prefix(f, lo)) continue;
         const int e0 = list_end(f, lo - 1);
         const int n  = f.ends[lo] - e0;
         __syncthreads();
@@ -1485,10 +1521,11 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
     float bg_acc[4] = {0.f, 0.f, 0.f, 0.f};
     float p0_acc    = 0.f;
 
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x)
+    __shared__ int s_long_hits[kThreads], s_long_count;
+    LongItemScan scan;
+    int lo;
+    while (scan.next(f, n_items, s_long_hits, &s_long_count, lo))
     {
-        const int lo = f.item_start[item], hi = f.item_start[item + 1];
-        if (lo >= hi || !long_prefix(f, lo)) continue;
         const int e0 = list_end(f, lo - 1);
         const int n  = f.ends[lo] - e0;
         const PixInfo px = decode_pixel(f, (unsigned)lo);
@@ -1610,10 +1647,11 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
     const int n_items = f.status[3];
     const float4 bgc  = make_float4(f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f);
     float bg_acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x)
+    __shared__ int s_long_hits[kThreads], s_long_count;
+    LongItemScan scan;
+    int lo;
+    while (scan.next(f, n_items, s_long_hits, &s_long_count, lo))
     {
-        const int lo = f.item_start[item], hi = f.item_start[item + 1];
-        if (lo >= hi || !long_prefix(f, lo)) continue;
         const int e0 = list_end(f, lo - 1);
         const int n  = f.ends[lo] - e0;
         if (n > kFuzzyLongMax)
