@@ -611,12 +611,12 @@ def run_ours(args):
 # divided by the algorithmic bytes of that launch).  The full-size workload is too large to capture with --set full;
 # traffic is taken to grow in proportion to the algorithmic bytes.
 TRAFFIC_OVER_ALGORITHMIC = {
-    "backward": (237.271e6 + 34.819e6) / 228.388e6,
-    "point_backward": (79.188e6 + 2.561e6) / 82.153e6,
-    "sort_blend": (117.402e6 + 104.202e6) / 185.585e6,
-    "count": 42.554e6 / 43.016e6,
+    "backward": (238.468e6 + 35.511e6) / 228.388e6,
+    "point_backward": (79.187e6 + 2.127e6) / 82.153e6,
+    "sort_blend": (117.412e6 + 103.904e6) / 185.585e6,
+    "count": 42.547e6 / 43.016e6,
     # the collection pass writes the whole 32-byte record (key + what the blend gathers), not only the 8-byte key
-    "collect": (67.186e6 + 86.907e6) / 58.553e6,
+    "collect": (67.285e6 + 85.086e6) / 58.553e6,
 }
 
 
