@@ -328,3 +328,31 @@ def test_l1_loss_grad(rasterizer):
     assert abs(loss.item() - want.item()) <= 1e-5 * want.item()
     for i, t, g in zip(images, targets, grads):
         assert torch.equal(g, torch.sign(i - t) * (1.0 / i.numel()))
+
+
+@pytest.mark.parametrize("mode", [1, 3])
+def test_backward_in_two_phases(rasterizer, mode):
+    """vetr_backward_phase: the per-fragment kernels and the per-point pass as two calls give what one call gives."""
+    import torch
+
+    sc = scenes.tiny_scene(n=3000, n_views=2, seed=31, crop=True)
+    params = default_params(render_mode=mode)
+    dev = rasterizer.device
+    from vet_b200.render import scene_to_device
+
+    tensors = scene_to_device(sc, dev)
+    out = rasterizer.forward(*tensors, sc.views, params)
+    gen = torch.Generator(device="cpu").manual_seed(4)
+    grads = [torch.randn(c.shape, generator=gen).to(dev) for c in out["color"]]
+    whole = rasterizer.backward_raw(grads)
+    first = rasterizer.backward_raw(grads, phases=1)
+    if mode == 1:  # nothing of the position / camera gradients exists after the first phase
+        assert float(first["points"].abs().sum()) == 0.0 and float(first["pose"].abs().sum()) == 0.0
+        assert torch.equal(first["desc"], whole["desc"]) or torch.allclose(first["desc"], whole["desc"], rtol=1e-4, atol=1e-6)
+    both = rasterizer.backward_raw(grads, accum=first, phases=2)
+    torch.cuda.synchronize()
+    assert torch.equal(both["points"], whole["points"])  # one owner per point, fixed summation order
+    assert torch.equal(both["pose_count"], whole["pose_count"])
+    assert torch.allclose(both["pose"], whole["pose"], rtol=1e-9, atol=1e-12)  # f64 atomics over thread blocks
+    for k in ("desc", "conf", "background", "intrinsics"):
+        assert torch.allclose(both[k], whole[k], rtol=1e-4, atol=1e-6), k  # float atomics in no fixed order
