@@ -1707,8 +1707,11 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
 #endif
 constexpr int kPointBackPoints = VETR_POINT_BACK_POINTS;
 
+#ifndef VETR_POINT_BACK_CTAS
+#    define VETR_POINT_BACK_CTAS 4
+#endif
 template <bool kIntr, bool kBilinear>
-__global__ void __launch_bounds__(kProjThreads) point_backward_kernel(const __grid_constant__ Frame f,
+__global__ void __launch_bounds__(kProjThreads, VETR_POINT_BACK_CTAS) point_backward_kernel(const __grid_constant__ Frame f,
                                                                       const __grid_constant__ BackPtrs bp)
 {
     __shared__ Camera s_cam[VETR_MAX_VIEWS];
