@@ -261,8 +261,18 @@ def run_ours(args):
     exchange_kind = "none" if world == 1 else args.exchange
     if world > 1 and args.exchange != "nccl":
         from vet_b200.dist import PeerExchange
-        peer = PeerExchange(rast, n, n_tex, CHANNELS, dev,
-                            multicast=None if args.exchange == "auto" else args.exchange == "multicast")
+        why = None
+        try:
+            peer = PeerExchange(rast, n, n_tex, CHANNELS, dev,
+                                multicast=None if args.exchange == "auto" else args.exchange == "multicast")
+        except Exception as e:  # noqa: BLE001  (no symmetric memory on this platform)
+            why = repr(e)[:160]
+        ok = torch.tensor([0.0 if peer is None else 1.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)  # all ranks take the same path
+        if ok.item() < 1.0:
+            peer = None
+            exchange_kind = "nccl (peer memory unavailable" + (": " + why if why else " on another rank") + ")"
+    if peer is not None:
         exchange_kind = "multicast" if peer.multicast else "peer"
         flat = peer.raw
     else:
