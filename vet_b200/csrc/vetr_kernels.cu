@@ -2329,85 +2329,144 @@ __device__ __forceinline__ bool point_in_triangle(float2 pt, float2 v1, float2 v
 }
 
 constexpr int kGridWarps = 4;
+constexpr int kGridChunk = 4096;             // pixels of a cell's screen rectangle one warp walks
+constexpr int kGridQueueCap = 4 * 1024 * 1024;  // (cell, chunk) pairs handed to the second kernel
 
-__global__ void __launch_bounds__(32 * kGridWarps) grid_loss_kernel(const __grid_constant__ Frame f, const __grid_constant__ GridArgs a)
+// Screen rectangle of a cell: the eight projected corners (left in pp[]) and the clamped bounding rectangle.
+// Returns the number of pixels to test (0: cell ignored).  Called by a whole warp; s_pp is the warp's staging row.
+__device__ __forceinline__ long long grid_cell_rectangle(const Frame& f, const GridArgs& a, const Camera& cam, int c, int lane,
+                                                         float2* s_pp, float2 pp[8], float2& mn, int& x_size)
+{
+    const float border = 32.f;
+    bool behind = false;
+    if (lane < 8)
+    {
+        // corner order of the reference: (0,0,0) (1,0,0) (0,1,0) (0,0,1) (1,1,0) (1,0,1) (0,1,1) (1,1,1)
+        const float fx = (lane == 1 || lane == 4 || lane == 5 || lane == 7) ? 1.f : 0.f;
+        const float fy = (lane == 2 || lane == 4 || lane == 6 || lane == 7) ? 1.f : 0.f;
+        const float fz = (lane == 3 || lane == 5 || lane == 6 || lane == 7) ? 1.f : 0.f;
+        const float4 pos = make_float4(VA(a.bb_min[3 * c], VM(a.bb_len[3 * c], fx)), VA(a.bb_min[3 * c + 1], VM(a.bb_len[3 * c + 1], fy)),
+                                       VA(a.bb_min[3 * c + 2], VM(a.bb_len[3 * c + 2], fz)), 0.f);
+        const Projected pr = project_point(pos, cam, f.dist_cutoff);
+        behind      = pr.z <= 0.f;  // one corner behind the camera: the whole cell is ignored
+        s_pp[lane]  = pr.ip;
+    }
+    behind = __any_sync(0xffffffffu, behind);
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pp[i] = s_pp[i];
+    __syncwarp();  // the staging row is free for the warp's next cell
+    if (behind) return 0;
+    float2 mx = make_float2(-10000000.f, -10000000.f);
+    mn        = make_float2(10000000.f, 10000000.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+    {
+        mx.x = fmaxf(pp[i].x, mx.x), mx.y = fmaxf(pp[i].y, mx.y);
+        mn.x = fminf(pp[i].x, mn.x), mn.y = fminf(pp[i].y, mn.y);
+    }
+    const float W = (float)a.w, H = (float)a.h;
+    if (mx.x < border || mn.x >= VS(W, border) || mx.y < border || mn.y >= VS(H, border)) return 0;
+    mn.x = fmaxf(mn.x, border), mn.y = fmaxf(mn.y, border);
+    mx.x = fminf(mx.x, VS(W, border)), mx.y = fminf(mx.y, VS(H, border));
+    const int y_size = (int)VS(mx.y, mn.y);
+    x_size           = (int)VS(mx.x, mn.x);
+    return (long long)y_size * x_size;
+}
+
+// Pixels [first, last) of a cell's rectangle, one per lane and step; adds the warp's totals to the cell.
+__device__ __forceinline__ void grid_cell_pixels(const GridArgs& a, int c, int lane, const float2 pp[8], float2 mn, int x_size,
+                                                 long long first, long long last)
+{
+    float sum = 0.f;
+    int hits  = 0;
+    for (long long xy = first + lane; xy < last; xy += 32)
+    {
+        const int x_c = (int)VA((float)(int)(xy % x_size), mn.x);
+        const int y_c = (int)VA((float)(int)(xy / x_size), mn.y);
+        const float2 pt = make_float2((float)x_c, (float)y_c);
+        bool in = false;
+        // faces of the box as pairs of triangles (RenderForward.cu:676-677)
+        in |= point_in_triangle(pt, pp[0], pp[1], pp[4]) || point_in_triangle(pt, pp[0], pp[4], pp[2]);
+        in |= point_in_triangle(pt, pp[1], pp[5], pp[7]) || point_in_triangle(pt, pp[1], pp[7], pp[4]);
+        in |= point_in_triangle(pt, pp[5], pp[3], pp[6]) || point_in_triangle(pt, pp[5], pp[6], pp[7]);
+        in |= point_in_triangle(pt, pp[3], pp[0], pp[6]) || point_in_triangle(pt, pp[0], pp[6], pp[2]);
+        in |= point_in_triangle(pt, pp[3], pp[0], pp[5]) || point_in_triangle(pt, pp[0], pp[5], pp[1]);
+        in |= point_in_triangle(pt, pp[2], pp[4], pp[6]) || point_in_triangle(pt, pp[4], pp[6], pp[7]);
+        if (!in) continue;
+        float g = 0.f;
+        for (int i = 0; i < a.channels; ++i) g += fabsf(__ldg(a.loss + ((long long)i * a.h + y_c) * a.w + x_c));
+        sum += g;
+        ++hits;
+    }
+    for (int o = 16; o > 0; o >>= 1)
+    {
+        sum += __shfl_down_sync(0xffffffffu, sum, o);
+        hits += __shfl_down_sync(0xffffffffu, hits, o);
+    }
+    if (lane == 0 && hits > 0)
+    {
+        atomicAdd(a.value + c, sum);
+        atomicAdd(a.count + c, hits);
+    }
+}
+
+// First kernel: one warp per cell.  Rectangles of up to kGridChunk pixels are walked right away; larger ones (a cell next
+// to the camera covers 10^5 pixels, a distant one 10) are cut into chunks that go to a queue, so that the second kernel
+// can spread them over all SMs.  If the queue is full the warp walks the whole rectangle itself.
+__global__ void __launch_bounds__(32 * kGridWarps) grid_loss_kernel(const __grid_constant__ Frame f, const __grid_constant__ GridArgs a,
+                                                                     int2* queue, int* queue_count)
 {
     __shared__ Camera s_cam;
     __shared__ float2 s_pp[kGridWarps][8];
     if (threadIdx.x == 0) s_cam = load_camera(f, a.view);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float border = 32.f;
     for (int c = blockIdx.x * kGridWarps + warp; c < a.n_cells; c += gridDim.x * kGridWarps)
     {
-        bool behind = false;
-        if (lane < 8)
+        float2 pp[8], mn;
+        int x_size;
+        const long long total = grid_cell_rectangle(f, a, s_cam, c, lane, s_pp[warp], pp, mn, x_size);
+        if (total <= 0) continue;
+        if (total > kGridChunk)
         {
-            // corner order of the reference: (0,0,0) (1,0,0) (0,1,0) (0,0,1) (1,1,0) (1,0,1) (0,1,1) (1,1,1)
-            const float fx = (lane == 1 || lane == 4 || lane == 5 || lane == 7) ? 1.f : 0.f;
-            const float fy = (lane == 2 || lane == 4 || lane == 6 || lane == 7) ? 1.f : 0.f;
-            const float fz = (lane == 3 || lane == 5 || lane == 6 || lane == 7) ? 1.f : 0.f;
-            const float4 pos = make_float4(VA(a.bb_min[3 * c], VM(a.bb_len[3 * c], fx)), VA(a.bb_min[3 * c + 1], VM(a.bb_len[3 * c + 1], fy)),
-                                           VA(a.bb_min[3 * c + 2], VM(a.bb_len[3 * c + 2], fz)), 0.f);
-            const Projected pr = project_point(pos, s_cam, f.dist_cutoff);
-            behind         = pr.z <= 0.f;  // one corner behind the camera: the whole cell is ignored
-            s_pp[warp][lane] = pr.ip;
-        }
-        behind = __any_sync(0xffffffffu, behind);
-        __syncwarp();
-        float sum = 0.f;
-        int hits  = 0;
-        if (!behind)
-        {
-            float2 pp[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) pp[i] = s_pp[warp][i];
-            float2 mx = make_float2(-10000000.f, -10000000.f), mn = make_float2(10000000.f, 10000000.f);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
+            const int chunks = (int)((total + kGridChunk - 1) / kGridChunk);
+            int base = 0;
+            if (lane == 0) base = atomicAdd(queue_count, chunks);
+            base = __shfl_sync(0xffffffffu, base, 0);
+            if (base + chunks <= kGridQueueCap)
             {
-                mx.x = fmaxf(pp[i].x, mx.x), mx.y = fmaxf(pp[i].y, mx.y);
-                mn.x = fminf(pp[i].x, mn.x), mn.y = fminf(pp[i].y, mn.y);
+                for (int k = lane; k < chunks; k += 32) queue[base + k] = make_int2(c, k);
+                continue;
             }
-            const float W = (float)a.w, H = (float)a.h;
-            if (!(mx.x < border || mn.x >= VS(W, border) || mx.y < border || mn.y >= VS(H, border)))
-            {
-                mn.x = fmaxf(mn.x, border), mn.y = fmaxf(mn.y, border);
-                mx.x = fminf(mx.x, VS(W, border)), mx.y = fminf(mx.y, VS(H, border));
-                const int y_size = (int)VS(mx.y, mn.y), x_size = (int)VS(mx.x, mn.x);
-                const long long total = (long long)y_size * x_size;
-                for (long long xy = lane; xy < total; xy += 32)
-                {
-                    const int x_c = (int)VA((float)(int)(xy % x_size), mn.x);
-                    const int y_c = (int)VA((float)(int)(xy / x_size), mn.y);
-                    const float2 pt = make_float2((float)x_c, (float)y_c);
-                    bool in = false;
-                    // faces of the box as pairs of triangles (RenderForward.cu:676-677)
-                    in |= point_in_triangle(pt, pp[0], pp[1], pp[4]) || point_in_triangle(pt, pp[0], pp[4], pp[2]);
-                    in |= point_in_triangle(pt, pp[1], pp[5], pp[7]) || point_in_triangle(pt, pp[1], pp[7], pp[4]);
-                    in |= point_in_triangle(pt, pp[5], pp[3], pp[6]) || point_in_triangle(pt, pp[5], pp[6], pp[7]);
-                    in |= point_in_triangle(pt, pp[3], pp[0], pp[6]) || point_in_triangle(pt, pp[0], pp[6], pp[2]);
-                    in |= point_in_triangle(pt, pp[3], pp[0], pp[5]) || point_in_triangle(pt, pp[0], pp[5], pp[1]);
-                    in |= point_in_triangle(pt, pp[2], pp[4], pp[6]) || point_in_triangle(pt, pp[4], pp[6], pp[7]);
-                    if (!in) continue;
-                    float g = 0.f;
-                    for (int i = 0; i < a.channels; ++i) g += fabsf(__ldg(a.loss + ((long long)i * a.h + y_c) * a.w + x_c));
-                    sum += g;
-                    ++hits;
-                }
-            }
+            // no room for all chunks: whatever part of the reservation lies inside the queue is marked unused, and the warp
+            // walks the whole rectangle itself
+            for (int k = lane; k < chunks && base + k < kGridQueueCap; k += 32) queue[base + k] = make_int2(-1, 0);
         }
-        for (int o = 16; o > 0; o >>= 1)
-        {
-            sum += __shfl_down_sync(0xffffffffu, sum, o);
-            hits += __shfl_down_sync(0xffffffffu, hits, o);
-        }
-        if (lane == 0 && hits > 0)
-        {
-            atomicAdd(a.value + c, sum);
-            atomicAdd(a.count + c, hits);
-        }
-        __syncwarp();  // the corner slots are reused by the warp's next cell
+        grid_cell_pixels(a, c, lane, pp, mn, x_size, 0, total);
+    }
+}
+
+// Second kernel: one warp per queued (cell, chunk).
+__global__ void __launch_bounds__(32 * kGridWarps) grid_loss_chunk_kernel(const __grid_constant__ Frame f, const __grid_constant__ GridArgs a,
+                                                                           const int2* queue, const int* queue_count)
+{
+    __shared__ Camera s_cam;
+    __shared__ float2 s_pp[kGridWarps][8];
+    if (threadIdx.x == 0) s_cam = load_camera(f, a.view);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // reservations past the capacity were never written: those cells were walked by the first kernel
+    const int n = min(*queue_count, kGridQueueCap);
+    for (int e = blockIdx.x * kGridWarps + warp; e < n; e += gridDim.x * kGridWarps)
+    {
+        const int2 q = queue[e];
+        if (q.x < 0) continue;
+        float2 pp[8], mn;
+        int x_size;
+        const long long total = grid_cell_rectangle(f, a, s_cam, q.x, lane, s_pp[warp], pp, mn, x_size);
+        const long long first = (long long)q.y * kGridChunk;
+        grid_cell_pixels(a, q.x, lane, pp, mn, x_size, first, min(first + kGridChunk, total));
     }
 }
 
@@ -2492,6 +2551,8 @@ struct vetr_ctx
     int sm_count         = 148;
     long long* tile_sums = nullptr;  // scan scratch
     long long tile_cap   = 0;
+    int2* grid_queue     = nullptr;  // (cell, chunk) queue of vetr_grid_loss, allocated by its first call
+    int* grid_queue_count = nullptr;
     int blend_ctas_per_sm = 1, back_ctas_per_sm = 1, fuzzy_ctas_per_sm = 1, bilinear_ctas_per_sm = 1;
     long long launches   = 0;
     bool timing          = false;
@@ -2649,6 +2710,7 @@ extern "C" void vetr_destroy(vetr_ctx* ctx)
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->tile_sums) cudaFree(ctx->tile_sums);
+    if (ctx->grid_queue) cudaFree(ctx->grid_queue);
     for (int i = 0; i < VETR_T_N; ++i)
         for (int k = 0; k < 2; ++k)
             if (ctx->ev[i][k]) cudaEventDestroy(ctx->ev[i][k]);
@@ -3050,9 +3112,16 @@ extern "C" int vetr_grid_loss(vetr_ctx* ctx, const vetr_cameras* cams, const vet
     VETR_CUDA(ctx, cudaSetDevice(ctx->device));
     if (n_cells > 0)
     {
-        ctx->launches += 1;
+        if (!ctx->grid_queue)
+        {
+            VETR_CUDA(ctx, cudaMalloc(&ctx->grid_queue, (size_t)kGridQueueCap * sizeof(int2) + 256));
+            ctx->grid_queue_count = reinterpret_cast<int*>(ctx->grid_queue + kGridQueueCap);
+        }
+        VETR_CUDA(ctx, cudaMemsetAsync(ctx->grid_queue_count, 0, sizeof(int), ctx->stream));
+        ctx->launches += 2;
         const int ctas = min((n_cells + kGridWarps - 1) / kGridWarps, ctx->sm_count * 16);
-        grid_loss_kernel<<<ctas, 32 * kGridWarps, 0, ctx->stream>>>(f, a);
+        grid_loss_kernel<<<ctas, 32 * kGridWarps, 0, ctx->stream>>>(f, a, ctx->grid_queue, ctx->grid_queue_count);
+        grid_loss_chunk_kernel<<<ctx->sm_count * 16, 32 * kGridWarps, 0, ctx->stream>>>(f, a, ctx->grid_queue, ctx->grid_queue_count);
     }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
