@@ -32,7 +32,7 @@ typedef enum vetr_status
     VETR_E_INVALID_ARG    = -1,
     VETR_E_CUDA           = -2, /* a CUDA runtime call failed; vetr_last_cuda_error() has the code */
     VETR_E_UNSUPPORTED    = -3, /* camera model / option the library does not implement */
-    VETR_E_LIST_OVERFLOW  = -4, /* more fragments than the key buffer holds (reported by vetr_read_status) */
+    VETR_E_LIST_OVERFLOW  = -4, /* more fragments than the fragment buffer holds (reported by vetr_read_status) */
     VETR_E_TOO_LARGE      = -5  /* a size exceeds a fixed limit of the entry point (vetr_read_status: a list longer than
                                    3072 fragments met the mode-2 backward pass, which skipped that pixel) */
 } vetr_status;
@@ -156,7 +156,7 @@ int vetr_last_cuda_error(const vetr_ctx* ctx);
 /* Pyramid pixels of one w x h view with num_layers levels (successive integer halving, PointRenderer.cu:351-381). */
 int64_t vetr_pyramid_pixels(int w, int h, int num_layers);
 
-/* Entries the work-item table of vetr_lists needs for a key buffer of `capacity` keys over `n_pixels_total` pixels. */
+/* Entries the work-item table of vetr_lists needs for a fragment buffer of `capacity` records over `n_pixels_total` pixels. */
 int64_t vetr_item_table_entries(int64_t capacity, int64_t n_pixels_total);
 
 /* Upper bound of the number of fragments: n * num_layers * n_views (x4 in bilinear mode). */

@@ -2640,7 +2640,7 @@ extern "C" const char* vetr_strerror(int status)
         case VETR_E_INVALID_ARG: return "invalid argument";
         case VETR_E_CUDA: return "CUDA runtime error";
         case VETR_E_UNSUPPORTED: return "unsupported camera model or option";
-        case VETR_E_LIST_OVERFLOW: return "fragment key buffer too small";
+        case VETR_E_LIST_OVERFLOW: return "fragment buffer too small";
         case VETR_E_TOO_LARGE: return "size exceeds a fixed limit";
         default: return "unknown status";
     }

@@ -2,7 +2,8 @@
 
 The reference has no multi-GPU code.  A training batch shards by view: the cloud, descriptors and cameras are
 replicated, rank r renders the views {v : v mod world == r}, and the only exchange per step is the sum of the
-point-parameter gradients.  They live in ONE fused fp32 buffer so that one all-reduce moves them:
+point-parameter gradients.  They live in ONE fused fp32 buffer, so that one exchange moves them - PeerExchange: the sum
+over the ranks and the epilogue as one kernel over NVLink peer memory; allreduce_gradients: one NCCL all-reduce:
 
     [ descriptor gradient  n_tex x 4 | position gradient + hit count  n x 4 | confidence gradient  n_tex ]
 
