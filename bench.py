@@ -58,6 +58,7 @@ def parse_args():
                          "NVSwitch multicast object (the switch adds; falls back to peer where there is none) or with plain "
                          "peer loads / stores; auto = peer for 2 ranks, multicast for more; nccl = NCCL all-reduce + "
                          "epilogue kernels")
+    ap.add_argument("--exchange-ctas", type=int, default=4, help="N > 1: thread blocks per SM of the exchange kernel (1..8)")
     ap.add_argument("--overlap", action="store_true",
                     help="N > 1: run the per-point pass of the backward step beside the exchange of the descriptor / confidence "
                          "segments (measured no faster at N = 2: the extra collective and launches cost what the overlap saves)")
@@ -273,6 +274,7 @@ def run_ours(args):
             peer = None
             exchange_kind = "nccl (peer memory unavailable" + (": " + why if why else " on another rank") + ")"
     if peer is not None:
+        peer.ctas_per_sm = args.exchange_ctas
         exchange_kind = "multicast" if peer.multicast else "peer"
         flat = peer.raw
     else:

@@ -110,6 +110,7 @@ class PeerExchange:
         self.buffer = GradientBuffer(n, n_tex, device, flat=self.raw)
         self._token = torch.zeros(1, dtype=torch.float32, device=device)
         self._side = None
+        self.ctas_per_sm = 4  # thread blocks per SM of the exchange kernel (1..8)
         p0 = (channels * n_tex + 3) // 4 * 4
         self.texture = self.out[: channels * n_tex].view(channels, n_tex)
         self.points = self.out[p0: p0 + 4 * n].view(n, 4)
@@ -149,7 +150,7 @@ class PeerExchange:
         finished gradients (views of the result buffer, the same on every rank) plus the reduced small tensors."""
         first = g.get("pose") if g.get("pose") is not None else self._token
         dist.all_reduce(first, group=self.group)
-        self._launch(7, 4)
+        self._launch(7, self.ctas_per_sm)
         return self._finish(g)
 
     def run_overlapped(self, grad_color, g: dict, bilinear: bool = False) -> dict:
