@@ -113,7 +113,7 @@ typedef struct vetr_cameras
  */
 typedef struct vetr_lists
 {
-    int32_t*  counts;   /* [n_views*P]  list length per pixel */
+    int32_t*  counts;   /* [n_views*P]  list length per pixel (P = vetr_pyramid_pixels) */
     int32_t*  ends;     /* [n_views*P]  end offset (exclusive) of the pixel's list in frags; its start is ends - counts */
     void*     frags;    /* [capacity] 32-byte fragment records, 32-byte aligned; ascending by key inside each list
                            after forward.  Record: uint64 key = depth bits << 32 | point index; float alpha
@@ -153,7 +153,11 @@ int vetr_set_stream(vetr_ctx* ctx, void* cuda_stream);
 const char* vetr_strerror(int status);
 int vetr_last_cuda_error(const vetr_ctx* ctx);
 
-/* Pyramid pixels of one w x h view with num_layers levels (successive integer halving, PointRenderer.cu:351-381). */
+/* Size of the pixel space of one w x h view with num_layers levels (successive integer halving, PointRenderer.cu:351-381):
+ * the sum over the levels of w_l * (h_l rounded up to a multiple of 8).  The pixel space orders the pixels of a level in
+ * bands of eight rows, column by column inside a band (offset = (y / 8) * 8 w_l + 8 x + y % 8), so that the fragments
+ * of neighbouring points land near each other in the fragment buffer; the rows that pad the last band hold no fragments.
+ * counts / ends of vetr_lists are indexed like this; the images stay plain [view, channel, y, x] tensors. */
 int64_t vetr_pyramid_pixels(int w, int h, int num_layers);
 
 /* Entries the work-item table of vetr_lists needs for a fragment buffer of `capacity` records over `n_pixels_total` pixels. */

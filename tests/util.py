@@ -28,6 +28,20 @@ def run_oracle(scene, params: dict, grads=None, dropout=None, quadratic=False):
     return out
 
 
+def row_major_order(w: int, h: int, levels: int, n_views: int) -> np.ndarray:
+    """Pixel-space index of every (view, level, y, x) in row-major order: level l starts after the padded levels before
+    it, and inside a level offset(x, y) = (y // 8) * 8 w + 8 x + y % 8 (vetr_kernels.cu: pixel_offset)."""
+    per_view, base = [], 0
+    for _ in range(levels):
+        y, x = np.meshgrid(np.arange(h), np.arange(w), indexing="ij")
+        per_view.append((base + (y // 8) * (8 * w) + 8 * x + y % 8).ravel())
+        base += w * ((h + 7) // 8 * 8)
+        w //= 2
+        h //= 2
+    one = np.concatenate(per_view)
+    return np.concatenate([one + v * base for v in range(n_views)])
+
+
 def run_gpu(rast, scene, params: dict, grads=None, dropout=None, capacity=None):
     import torch
     from vet_b200.render import scene_to_device
@@ -39,12 +53,26 @@ def run_gpu(rast, scene, params: dict, grads=None, dropout=None, capacity=None):
                        want_depth=True)
     F, longest = rast.fragment_count()
     groups = rast._saved["groups"]
-    counts = torch.cat([g[2].counts for g in groups]).cpu().numpy()
-    ends = [g[2].ends.cpu().numpy().astype(np.int64) for g in groups]
-    keys_parts = []
-    for g, e in zip(groups, ends):
+    # the library keeps its pixel space in bands of eight rows (column by column inside a band, last band padded); the
+    # oracle's arrays are row-major: bring counts and the concatenated lists into row-major pixel order
+    w0, h0 = scene.views[0].w, scene.views[0].h
+    Ln = params.get("num_layers", 4)
+    counts_parts, keys_parts = [], []
+    for (b0, b1, lists, _) in groups:
+        c = lists.counts.cpu().numpy()
+        e = lists.ends.cpu().numpy().astype(np.int64)
         n = int(e[-1]) if e.size and params.get("render_mode", 1) != 0 else 0
-        keys_parts.append(g[2].frags[:n, 0].cpu().numpy().view(np.uint64))  # first 8 bytes of a record = key
+        k = lists.frags[:n, 0].cpu().numpy().view(np.uint64)  # first 8 bytes of a record = key
+        order = row_major_order(w0, h0, Ln, b1 - b0)
+        c_rm = c[order]
+        counts_parts.append(c_rm)
+        if params.get("render_mode", 1) != 0:
+            starts = (e - c)[order]
+            total = int(c_rm.sum())
+            seg_first = np.cumsum(c_rm) - c_rm
+            idx = np.repeat(starts - seg_first, c_rm) + np.arange(total)
+            keys_parts.append(k[idx])
+    counts = np.concatenate(counts_parts)
     keys = np.concatenate(keys_parts) if keys_parts else np.zeros(0, np.uint64)
     out = dict(fwd={k: (None if v is None else [t.cpu().numpy() for t in v]) for k, v in fwd.items()}, counts=counts,
                keys=keys, F=F, longest=longest)

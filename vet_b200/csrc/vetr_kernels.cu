@@ -37,6 +37,7 @@
 #include <string.h>
 
 #include <new>
+#include <vector>
 
 #include "../../include/vetr.h"
 #include "vetr_math.cuh"
@@ -92,9 +93,11 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
     float depth_accept;
     int ghost;
     int lw[VETR_MAX_LAYERS], lh[VETR_MAX_LAYERS];
-    float inv_lw[VETR_MAX_LAYERS];
-    long long lbase[VETR_MAX_LAYERS];
-    long long P, PT;
+    float inv_lw[VETR_MAX_LAYERS], inv_band[VETR_MAX_LAYERS];  // 1 / w and 1 / (8 w) of a level
+    long long lbase[VETR_MAX_LAYERS];  // first pixel of a level in the pixel space of one view (banded order, see pixel_offset)
+    long long rbase[VETR_MAX_LAYERS];  // the same in plain row-major order (the interleaved image copies)
+    long long P, PT;                   // pixels of one view / of all views in the pixel space (levels padded to 8 rows)
+    long long Prm;                     // row-major pixels of one view (sum of w * h)
     ViewDev views[VETR_MAX_VIEWS];
     const float4* position;
     const int* index;
@@ -115,6 +118,14 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
     float4* img4;               // [PT] forward image, channels interleaved, indexed like counts[] (backward scratch)
     float4* grad4;              // [PT] its incoming gradient
 };
+
+// Order of the pixels of a level in the pixel space: bands of eight rows, column by column inside a band,
+//     offset(x, y) = (y / 8) * 8 w + 8 x + y % 8,
+// so that 8 x 8 (and 8-row x k-column) patches of the image are contiguous.  Points arrive in Morton order: the
+// fragments of neighbouring points then land in a few nearby runs of the fragment buffer instead of one run per image
+// row, and a work item (a run of consecutive pixels) covers a compact patch.  The last band of a level is padded to
+// eight rows; padded pixels have no fragments and are skipped wherever pixels are visited.
+__device__ __forceinline__ int pixel_offset(int w, int x, int y) { return (y >> 3) * (w << 3) + (x << 3) + (y & 7); }
 
 // Mode 3 keeps the bilinear corner of a fragment in the two top bits of the record's descriptor index.
 constexpr int kCornerShift = 30;
@@ -219,7 +230,7 @@ __global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_cons
                 {
                     const int lw = f.lw[l], lh = f.lh[l];
                     const int x = round_half_even(ip.x), y = round_half_even(ip.y);
-                    if ((unsigned)x < (unsigned)lw && (unsigned)y < (unsigned)lh) g[it][l] = vbase + (int)f.lbase[l] + y * lw + x;
+                    if ((unsigned)x < (unsigned)lw && (unsigned)y < (unsigned)lh) g[it][l] = vbase + (int)f.lbase[l] + pixel_offset(lw, x, y);
                 }
                 radius *= 0.5f, ip.x *= 0.5f, ip.y *= 0.5f;
             }
@@ -314,7 +325,7 @@ __global__ void __launch_bounds__(kProjThreads) project_kernel(const __grid_cons
                 const int x = bx + (cidx & 1), y = by + (cidx >> 1);
                 slot[cidx]  = -1;
                 if ((unsigned)x >= (unsigned)lw || (unsigned)y >= (unsigned)lh) continue;
-                const int g = gbase + y * lw + x;
+                const int g = gbase + pixel_offset(lw, x, y);
                 if (!kCollect)
                     atomicAdd(f.counts + g, 1);
                 else
@@ -479,7 +490,8 @@ struct PixInfo  // decoded pixel of the global pixel space, 8 bytes
 {
     short x, y;
     unsigned char level, view;
-    unsigned short interior;  // ImageView::distanceFromEdge > 2: the pixel takes part in the position gradient
+    unsigned char interior;  // ImageView::distanceFromEdge > 2: the pixel takes part in the position gradient
+    unsigned char valid;     // 0: padding row of the level's last band
 };
 
 // View, level and offset inside the level of pixel g, without divisions (a run of comparisons each).
@@ -504,16 +516,23 @@ __device__ __forceinline__ PixInfo decode_pixel(const Frame& f, unsigned g)
     int view, l;
     unsigned q;
     locate_pixel(f, g, view, l, q);
-    const unsigned w = (unsigned)f.lw[l];
-    // row = q / w: float estimate, then one correction step either way (exact: the estimate is off by at most one)
-    unsigned y = (unsigned)__float2int_rz(__fmul_rn((float)q, f.inv_lw[l]));
-    int x      = (int)(q - y * w);
-    if (x < 0) x += (int)w, --y;
-    if (x >= (int)w) x -= (int)w, ++y;
+    const int w = f.lw[l], h = f.lh[l], bw = w << 3;
+    // band = q / (8 w): float estimate, then one correction step either way (exact: the estimate is off by at most one)
+    int band = __float2int_rz(__fmul_rn((float)q, f.inv_band[l]));
+    int rem  = (int)q - band * bw;
+    if (rem < 0) rem += bw, --band;
+    if (rem >= bw) rem -= bw, ++band;
+    const int x = rem >> 3, y = (band << 3) + (rem & 7);
     r.x = (short)x, r.y = (short)y, r.level = (unsigned char)l, r.view = (unsigned char)view;
-    const int h = f.lh[l];
-    r.interior  = min(min((int)r.x, (int)w - 1 - r.x), min((int)r.y, h - 1 - r.y)) > 2;
+    r.valid    = y < h;
+    r.interior = min(min(x, w - 1 - x), min(y, h - 1 - y)) > 2;
     return r;
+}
+
+// Index of a pixel in the row-major image copies (img4 / grad4).
+__device__ __forceinline__ int row_major_index(const Frame& f, const PixInfo& px)
+{
+    return px.view * (int)f.Prm + (int)f.rbase[px.level] + px.y * f.lw[px.level] + px.x;
 }
 
 __device__ __forceinline__ int list_end(const Frame& f, int g) { return g < 0 ? 0 : f.ends[g]; }
@@ -638,15 +657,14 @@ struct OutPtrs
     float* depth[VETR_MAX_LAYERS];
 };
 
-// Outputs of pixel g of the global pixel space (planar [view, channel, y, x] tensors per level: the offset inside the
-// level is the row-major pixel offset, so rows and columns are not needed).
+// Outputs of pixel g of the global pixel space (planar [view, channel, y, x] tensors per level).
 __device__ __forceinline__ void write_pixel(const Frame& f, const OutPtrs& out, unsigned g, const float c[4], float T, float depth)
 {
-    int view, level;
-    unsigned o;
-    locate_pixel(f, g, view, level, o);
-    const int hw = f.lw[level] * f.lh[level];
-    float* col   = out.color[level] + (size_t)(view * f.C) * hw + o;
+    const PixInfo px = decode_pixel(f, g);
+    if (!px.valid) return;
+    const int level = px.level, view = px.view;
+    const int w = f.lw[level], hw = w * f.lh[level], o = px.y * w + px.x;
+    float* col = out.color[level] + (size_t)(view * f.C) * hw + o;
     col[0] = c[0], col[hw] = c[1], col[2 * hw] = c[2];
     if (f.C > 3) col[3 * hw] = c[3];
     const size_t po = (size_t)view * hw + o;
@@ -1194,15 +1212,25 @@ __device__ __forceinline__ float4 load_grad(const Frame& f, int g) { return __ld
 // tensors are planar [view, channel, y, x] per level).
 __global__ void __launch_bounds__(256) pack_images_kernel(const __grid_constant__ Frame f, const __grid_constant__ BackPtrs bp)
 {
-    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (g >= f.PT) return;
-    const PixInfo px = decode_pixel(f, (unsigned)g);
-    const int w = f.lw[px.level], hw = w * f.lh[px.level];
-    const int o = (px.view * f.C) * hw + px.y * w + px.x;
-    const float* I = bp.out_color[px.level] + o;
-    const float* G = bp.grad_color[px.level] + o;
-    f.img4[g]  = make_float4(__ldg(I), __ldg(I + hw), __ldg(I + 2 * hw), f.C > 3 ? __ldg(I + 3 * hw) : 0.f);
-    f.grad4[g] = make_float4(__ldg(G), __ldg(G + hw), __ldg(G + 2 * hw), f.C > 3 ? __ldg(G + 3 * hw) : 0.f);
+    // one thread per pixel in plain row-major order (view, level, y, x): coalesced reads of the planar tensors
+    const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= f.Prm * f.n_views) return;
+    const int Prm  = (int)f.Prm;
+    int view = 0;
+#pragma unroll
+    for (int i = 1; i < VETR_MAX_VIEWS; ++i)
+        if (i < f.n_views && r >= (long long)i * Prm) view = i;
+    const int q = (int)(r - (long long)view * Prm);
+    int l = 0;
+#pragma unroll
+    for (int i = 1; i < VETR_MAX_LAYERS; ++i)
+        if (i < f.L && q >= (int)f.rbase[i]) l = i;
+    const int o  = q - (int)f.rbase[l];  // y * w + x
+    const int hw = f.lw[l] * f.lh[l];
+    const float* I = bp.out_color[l] + (size_t)(view * f.C) * hw + o;
+    const float* G = bp.grad_color[l] + (size_t)(view * f.C) * hw + o;
+    f.img4[r]  = make_float4(__ldg(I), __ldg(I + hw), __ldg(I + 2 * hw), f.C > 3 ? __ldg(I + 3 * hw) : 0.f);
+    f.grad4[r] = make_float4(__ldg(G), __ldg(G + hw), __ldg(G + 2 * hw), f.C > 3 ? __ldg(G + 3 * hw) : 0.f);
 }
 
 __device__ __forceinline__ float dot4(float4 a, float4 b, int C)
@@ -1238,7 +1266,7 @@ __device__ __forceinline__ void fragment_stage_a(const Frame& f, BackSmem& s, in
     if (!kBilinear && f.need_point_grad)
     {
         float2 dR = make_float2(__int_as_float(kNoGradientBits), 0.f);
-        if (blended && px.interior) dR = neighbour_gradient(f, g, f.lw[px.level], d);
+        if (blended && px.interior) dR = neighbour_gradient(f, row_major_index(f, px), f.lw[px.level], d);
         f.point_grad[((size_t)px.view * f.L + px.level) * f.n + pid] = dR;
     }
 }
@@ -1458,7 +1486,7 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
                 s.seg_end[tid + 1] = se;
                 const PixInfo px   = decode_pixel(f, (unsigned)(lo + tid));
                 s.pix[tid]         = px;
-                s.grad[tid]        = load_grad(f, lo + tid);
+                s.grad[tid]        = px.valid ? load_grad(f, row_major_index(f, px)) : make_float4(0.f, 0.f, 0.f, 0.f);
                 seg_fill(s.seg, parity, tid, ss, se);
             }
             if (tid == 0) s.seg_end[0] = 0;
@@ -1479,7 +1507,7 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
             }
             __syncthreads();
             PHASE_MARK(2);
-            if (tid < np)
+            if (tid < np && s.pix[tid].valid)
             {
                 if constexpr (kFuzzy)
                     sweep_list_fuzzy(f, s.alpha, s.dot, s.trans, s.desc, s.depth, s.gv, s.gfirst, s.seg_end[tid], s.seg_end[tid + 1],
@@ -1530,7 +1558,7 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
         const int n  = f.ends[lo] - e0;
         const PixInfo px = decode_pixel(f, (unsigned)lo);
         __syncthreads();
-        const float4 G = load_grad(f, lo);
+        const float4 G = load_grad(f, row_major_index(f, px));
         int cnt = n;
         if (f.dbg_max_len > 0) cnt = min(cnt, f.dbg_max_len);
         cnt = min(cnt, 256 * kCap);
@@ -1660,7 +1688,7 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
             continue;
         }
         const PixInfo px = decode_pixel(f, (unsigned)lo);
-        const float4 G = load_grad(f, lo);
+        const float4 G = load_grad(f, row_major_index(f, px));
         __syncthreads();  // every warp has left the previous list
         const bool spatial = px.interior;
         for (int i = tid; i < n; i += kThreads)
@@ -1672,7 +1700,8 @@ __global__ void __launch_bounds__(kThreads) backward_fuzzy_long_kernel(const __g
             const bool blended = f.dbg_max_len <= 0 || i < f.dbg_max_len;
             if (f.need_point_grad)
                 f.point_grad[((size_t)px.view * f.L + px.level) * f.n + (int)h.x] =
-                    spatial && blended ? neighbour_gradient(f, lo, f.lw[px.level], d) : make_float2(__int_as_float(kNoGradientBits), 0.f);
+                    spatial && blended ? neighbour_gradient(f, row_major_index(f, px), f.lw[px.level], d)
+                                       : make_float2(__int_as_float(kNoGradientBits), 0.f);
         }
         __syncthreads();
         if (tid == 0) sweep_list_fuzzy(f, s.alpha, s.dot, s.trans, s.desc, s.depth, s.gv, s.gfirst, 0, n, G, bgc, bg_acc);
@@ -1909,7 +1938,7 @@ __global__ void __launch_bounds__(kProjThreads) fuzzy_dt_point_kernel(const __gr
         const int lw = f.lw[l], lh = f.lh[l];
         const int x = round_half_even(ip.x), y = round_half_even(ip.y);
         if ((unsigned)x >= (unsigned)lw || (unsigned)y >= (unsigned)lh) continue;
-        const int g = vbase + (int)f.lbase[l] + y * lw + x;
+        const int g = vbase + (int)f.lbase[l] + pixel_offset(lw, x, y);
         if (kPass == 0)
             atomicMin(f.ends + g, __float_as_int(pr.z));  // z > 0: integer order = float order
         else
@@ -1966,7 +1995,9 @@ __global__ void __launch_bounds__(256) fuzzy_dt_background_kernel(const __grid_c
     for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < f.PT; g += (long long)gridDim.x * blockDim.x)
         if (f.counts[g] == 0)
         {
-            const float4 G = load_grad_planar(f, bp, decode_pixel(f, (unsigned)g));
+            const PixInfo px = decode_pixel(f, (unsigned)g);
+            if (!px.valid) continue;
+            const float4 G = load_grad_planar(f, bp, px);
             v[0] += G.x, v[1] += G.y, v[2] += G.z, v[3] += G.w;
         }
     for (int k = 0; k < 4; ++k)
@@ -2016,12 +2047,12 @@ __global__ void __launch_bounds__(kProjThreads) fuzzy_dt_backward_kernel(const _
                 const int lw = f.lw[l], lh = f.lh[l];
                 const int x = round_half_even(ip.x), y = round_half_even(ip.y);
                 if ((unsigned)x >= (unsigned)lw || (unsigned)y >= (unsigned)lh) continue;
-                const int g   = vbase + (int)f.lbase[l] + y * lw + x;
+                const int g   = vbase + (int)f.lbase[l] + pixel_offset(lw, x, y);
                 const float w = (float)f.counts[g];
                 if (w == 0.f) continue;
                 if (pr.z > __int_as_float(f.ends[g]) * (f.depth_accept + 1)) continue;
                 PixInfo px;
-                px.x = (short)x, px.y = (short)y, px.level = (unsigned char)l, px.view = (unsigned char)b;
+                px.x = (short)x, px.y = (short)y, px.level = (unsigned char)l, px.view = (unsigned char)b, px.valid = 1;
                 px.interior = min(min(x, f.lw[l] - 1 - x), min(y, f.lh[l] - 1 - y)) > 2;
                 if (!drop_out)
                 {
@@ -2598,16 +2629,22 @@ static int __float_as_int_host(float v)
     return i;
 }
 
-static int64_t pyramid(int w, int h, int L, int* lw, int* lh, long long* lbase)
+// Pixel space of one view: every level's height is padded to a multiple of eight rows (the banded order of pixel_offset).
+// rbase / *row_major: the same levels in plain row-major order without padding.
+static int64_t pyramid(int w, int h, int L, int* lw, int* lh, long long* lbase, long long* rbase = nullptr,
+                       long long* row_major = nullptr)
 {
-    long long base = 0;
+    long long base = 0, rm = 0;
     for (int l = 0; l < L; ++l)
     {
         if (lw) lw[l] = w, lh[l] = h, lbase[l] = base;
-        base += (long long)w * h;
+        if (rbase) rbase[l] = rm;
+        base += (long long)w * ((h + 7) / 8 * 8);
+        rm += (long long)w * h;
         w /= 2;
         h /= 2;
     }
+    if (row_major) *row_major = rm;
     return base;
 }
 
@@ -2802,10 +2839,10 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     f.stability_cutoff = p->stability_cutoff_value, f.k_grad_factor = p->K_gradient_factor;
     f.dist_grad_factor = p->distortion_gradient_factor, f.mask_value = p->output_background_mask_value;
     f.accept_blend = p->depth_accept_blend, f.depth_accept = p->depth_accept, f.ghost = p->ghost_gradients;
-    f.P  = pyramid(f.w, f.h, f.L, f.lw, f.lh, f.lbase);
+    f.P  = pyramid(f.w, f.h, f.L, f.lw, f.lh, f.lbase, f.rbase, &f.Prm);
     f.PT = f.P * n_views;
     if (f.lw[f.L - 1] < 1 || f.lh[f.L - 1] < 1) return VETR_E_INVALID_ARG;  // the reference asserts w > 0 && h > 0 per level
-    for (int l = 0; l < f.L; ++l) f.inv_lw[l] = 1.f / (float)f.lw[l];
+    for (int l = 0; l < f.L; ++l) f.inv_lw[l] = 1.f / (float)f.lw[l], f.inv_band[l] = 1.f / (float)(8 * f.lw[l]);
     if (f.PT > 0x7fffffffLL || (long long)f.lw[0] * f.lh[0] * f.C * n_views > 0x7fffffffLL) return VETR_E_TOO_LARGE;
     f.position = (const float4*)cloud->position, f.index = cloud->index;
     f.texture = tex->texture, f.confidence = tex->confidence, f.background = tex->background;
@@ -2969,7 +3006,7 @@ extern "C" int vetr_backward_phase(vetr_ctx* ctx, const vetr_params* params, con
     {
         PassScope t(ctx, VETR_T_BACKWARD, 3);
         cudaStream_t st = ctx->stream;
-        pack_images_kernel<<<(unsigned)((f.PT + 255) / 256), 256, 0, st>>>(f, bp);
+        pack_images_kernel<<<(unsigned)((f.Prm * n_views + 255) / 256), 256, 0, st>>>(f, bp);
         if (f.mode == VETR_MODE_FUZZY_BLEND)
         {
             const int grid = ctx->sm_count * ctx->fuzzy_ctas_per_sm;
@@ -3222,24 +3259,9 @@ extern "C" int vetr_scan_counts_static(int device, void* cuda_stream, const int3
     return cudaGetLastError() == cudaSuccess ? VETR_OK : VETR_E_CUDA;
 }
 
-namespace vetr
-{
-__global__ void unpack_lists_kernel(const uint4* recs, long long first, long long n, int* out)
-{
-    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    uint4 h    = recs[2 * (first + i)];
-    out[i]     = (int)h.y;
-    out[n + i] = (int)h.x;
-}
-__global__ void local_offsets_kernel(const int* ends, const int* counts, long long g0, long long npix, long long first, int* out)
-{
-    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= npix) return;
-    out[i] = (int)((long long)ends[g0 + i] - counts[g0 + i] - first);
-}
-}  // namespace vetr
-
+// Parity / debugging: the lists of one (view, level) in the reference's layout.  The reference keeps its lists in
+// row-major pixel order; here they are stored in the banded order of the pixel space, so the level is brought to the
+// host, reordered there and copied back (a debugging call: it synchronises and is not meant for large scenes).
 extern "C" int vetr_get_lists(vetr_ctx* ctx, const vetr_lists* lists, int w, int h, int num_layers, int n_views, int view,
                               int layer, int32_t* out_collections, int32_t* out_scanned_counting, int64_t* n_fragments)
 {
@@ -3248,30 +3270,52 @@ extern "C" int vetr_get_lists(vetr_ctx* ctx, const vetr_lists* lists, int w, int
         return VETR_E_INVALID_ARG;
     int lw[VETR_MAX_LAYERS], lh[VETR_MAX_LAYERS];
     long long lbase[VETR_MAX_LAYERS];
-    long long P    = pyramid(w, h, num_layers, lw, lh, lbase);
-    long long g0   = (long long)view * P + lbase[layer];
-    long long npix = (long long)lw[layer] * lh[layer];
-    if (npix == 0)
+    const long long P    = pyramid(w, h, num_layers, lw, lh, lbase);
+    const long long g0   = (long long)view * P + lbase[layer];
+    const int W = lw[layer], H = lh[layer];
+    const long long npad = (long long)W * ((H + 7) / 8 * 8);  // pixels of the level in the pixel space
+    if ((long long)W * H == 0)
     {
         if (n_fragments) *n_fragments = 0;
         return VETR_OK;
     }
     VETR_CUDA(ctx, cudaSetDevice(ctx->device));
-    int first_end, first_cnt, last_end;
-    VETR_CUDA(ctx, cudaMemcpyAsync(&first_end, lists->ends + g0, 4, cudaMemcpyDeviceToHost, ctx->stream));
-    VETR_CUDA(ctx, cudaMemcpyAsync(&first_cnt, lists->counts + g0, 4, cudaMemcpyDeviceToHost, ctx->stream));
-    VETR_CUDA(ctx, cudaMemcpyAsync(&last_end, lists->ends + g0 + npix - 1, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    std::vector<int> counts((size_t)npad), ends((size_t)npad);
+    VETR_CUDA(ctx, cudaMemcpyAsync(counts.data(), lists->counts + g0, npad * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VETR_CUDA(ctx, cudaMemcpyAsync(ends.data(), lists->ends + g0, npad * 4, cudaMemcpyDeviceToHost, ctx->stream));
     VETR_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    long long first = (long long)first_end - first_cnt;
-    long long n     = (long long)last_end - first;
+    const long long first = (long long)ends[0] - counts[0];
+    const long long n     = (long long)ends[(size_t)npad - 1] - first;
     if (n_fragments) *n_fragments = n;
+    if (!out_collections && !out_scanned_counting) return VETR_OK;
+    std::vector<uint4> recs;
     if (out_collections && n > 0)
-        unpack_lists_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>((const uint4*)lists->frags, first, n,
-                                                                                   out_collections);
+    {
+        recs.resize((size_t)(2 * n));
+        VETR_CUDA(ctx, cudaMemcpyAsync(recs.data(), (const uint4*)lists->frags + 2 * first, (size_t)n * 32, cudaMemcpyDeviceToHost,
+                                       ctx->stream));
+        VETR_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    std::vector<int> scanned((size_t)W * H), coll(out_collections ? (size_t)(2 * n) : 0);
+    long long run = 0;
+    for (int y = 0; y < H; ++y)
+        for (int x = 0; x < W; ++x)
+        {
+            const size_t k = (size_t)(y >> 3) * ((size_t)W << 3) + ((size_t)x << 3) + (y & 7);  // pixel_offset
+            scanned[(size_t)y * W + x] = (int)run;
+            if (out_collections)
+                for (int j = 0; j < counts[k]; ++j)
+                {
+                    const uint4 r = recs[(size_t)(2 * ((long long)ends[k] - counts[k] - first + j))];
+                    coll[(size_t)(run + j)]     = (int)r.y;  // row 0: depth bits
+                    coll[(size_t)(n + run + j)] = (int)r.x;  // row 1: point index
+                }
+            run += counts[k];
+        }
+    if (out_collections && n > 0)
+        VETR_CUDA(ctx, cudaMemcpyAsync(out_collections, coll.data(), (size_t)(2 * n) * 4, cudaMemcpyHostToDevice, ctx->stream));
     if (out_scanned_counting)
-        local_offsets_kernel<<<(unsigned)((npix + 255) / 256), 256, 0, ctx->stream>>>(lists->ends, lists->counts, g0, npix, first,
-                                                                                      out_scanned_counting);
-    VETR_CUDA(ctx, cudaGetLastError());
+        VETR_CUDA(ctx, cudaMemcpyAsync(out_scanned_counting, scanned.data(), (size_t)W * H * 4, cudaMemcpyHostToDevice, ctx->stream));
     VETR_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return VETR_OK;
 }
