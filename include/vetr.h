@@ -154,10 +154,13 @@ const char* vetr_strerror(int status);
 int vetr_last_cuda_error(const vetr_ctx* ctx);
 
 /* Size of the pixel space of one w x h view with num_layers levels (successive integer halving, PointRenderer.cu:351-381):
- * the sum over the levels of w_l * (h_l rounded up to a multiple of 8).  The pixel space orders the pixels of a level in
- * bands of eight rows, column by column inside a band (offset = (y / 8) * 8 w_l + 8 x + y % 8), so that the fragments
- * of neighbouring points land near each other in the fragment buffer; the rows that pad the last band hold no fragments.
- * counts / ends of vetr_lists are indexed like this; the images stay plain [view, channel, y, x] tensors. */
+ * the sum over the levels of w_l * (h_l rounded up to a multiple of VETR_PIXEL_BAND).  The pixel space orders the pixels
+ * of a level in bands of VETR_PIXEL_BAND rows, column by column inside a band,
+ *     offset(x, y) = (y / BAND) * BAND * w_l + BAND * x + y % BAND,
+ * so that a run of consecutive pixels is a compact patch of the image and the fragments of neighbouring points land
+ * near each other in the fragment buffer; the rows that pad the last band hold no fragments.  counts / ends of
+ * vetr_lists are indexed like this; the images stay plain [view, channel, y, x] tensors. */
+#define VETR_PIXEL_BAND 4
 int64_t vetr_pyramid_pixels(int w, int h, int num_layers);
 
 /* Entries the work-item table of vetr_lists needs for a fragment buffer of `capacity` records over `n_pixels_total` pixels. */

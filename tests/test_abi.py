@@ -28,9 +28,10 @@ def test_every_declared_symbol_is_exported():
 
 def test_host_only_entry_points():
     lib = L.lib()
-    # every level's height is padded to a multiple of eight rows in the pixel space
-    assert lib.vetr_pyramid_pixels(1920, 1080, 4) == 1920 * 1080 + 960 * 544 + 480 * 272 + 240 * 136
-    assert lib.vetr_pyramid_pixels(5, 3, 2) == 5 * 8 + 2 * 8
+    # every level's height is padded to a multiple of VETR_PIXEL_BAND (4) rows in the pixel space
+    assert L.PIXEL_BAND == 4
+    assert lib.vetr_pyramid_pixels(1920, 1080, 4) == 1920 * 1080 + 960 * 540 + 480 * 272 + 240 * 136
+    assert lib.vetr_pyramid_pixels(5, 3, 2) == 5 * 4 + 2 * 4
     assert lib.vetr_pyramid_pixels(0, 3, 2) == -1 and lib.vetr_pyramid_pixels(4, 4, 6) == -1
     p = L.Params(render_mode=1, num_layers=4)
     assert lib.vetr_max_fragments(1000, 3, C.byref(p)) == 12000

@@ -30,12 +30,14 @@ def run_oracle(scene, params: dict, grads=None, dropout=None, quadratic=False):
 
 def row_major_order(w: int, h: int, levels: int, n_views: int) -> np.ndarray:
     """Pixel-space index of every (view, level, y, x) in row-major order: level l starts after the padded levels before
-    it, and inside a level offset(x, y) = (y // 8) * 8 w + 8 x + y % 8 (vetr_kernels.cu: pixel_offset)."""
+    it, and inside a level offset(x, y) = (y // B) * B w + B x + y % B with B = VETR_PIXEL_BAND (include/vetr.h)."""
+    from vet_b200._lib import PIXEL_BAND as B
+
     per_view, base = [], 0
     for _ in range(levels):
         y, x = np.meshgrid(np.arange(h), np.arange(w), indexing="ij")
-        per_view.append((base + (y // 8) * (8 * w) + 8 * x + y % 8).ravel())
-        base += w * ((h + 7) // 8 * 8)
+        per_view.append((base + (y // B) * (B * w) + B * x + y % B).ravel())
+        base += w * ((h + B - 1) // B * B)
         w //= 2
         h //= 2
     one = np.concatenate(per_view)
@@ -53,7 +55,7 @@ def run_gpu(rast, scene, params: dict, grads=None, dropout=None, capacity=None):
                        want_depth=True)
     F, longest = rast.fragment_count()
     groups = rast._saved["groups"]
-    # the library keeps its pixel space in bands of eight rows (column by column inside a band, last band padded); the
+    # the library keeps its pixel space in bands of a few rows (column by column inside a band, last band padded); the
     # oracle's arrays are row-major: bring counts and the concatenated lists into row-major pixel order
     w0, h0 = scene.views[0].w, scene.views[0].h
     Ln = params.get("num_layers", 4)

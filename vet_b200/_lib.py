@@ -55,6 +55,7 @@ class Lists(C.Structure):
 
 
 MAX_RANKS = 16
+PIXEL_BAND = 4  # VETR_PIXEL_BAND: rows per band of the pixel space
 
 
 class Exchange(C.Structure):

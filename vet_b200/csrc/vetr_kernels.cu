@@ -93,10 +93,10 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
     float depth_accept;
     int ghost;
     int lw[VETR_MAX_LAYERS], lh[VETR_MAX_LAYERS];
-    float inv_lw[VETR_MAX_LAYERS], inv_band[VETR_MAX_LAYERS];  // 1 / w and 1 / (8 w) of a level
+    float inv_lw[VETR_MAX_LAYERS], inv_band[VETR_MAX_LAYERS];  // 1 / w and 1 / (kBand w) of a level
     long long lbase[VETR_MAX_LAYERS];  // first pixel of a level in the pixel space of one view (banded order, see pixel_offset)
     long long rbase[VETR_MAX_LAYERS];  // the same in plain row-major order (the interleaved image copies)
-    long long P, PT;                   // pixels of one view / of all views in the pixel space (levels padded to 8 rows)
+    long long P, PT;                   // pixels of one view / of all views in the pixel space (levels padded to whole bands)
     long long Prm;                     // row-major pixels of one view (sum of w * h)
     ViewDev views[VETR_MAX_VIEWS];
     const float4* position;
@@ -119,13 +119,16 @@ struct Frame  // kernel parameter block (travels by value; no global or __consta
     float4* grad4;              // [PT] its incoming gradient
 };
 
-// Order of the pixels of a level in the pixel space: bands of eight rows, column by column inside a band,
-//     offset(x, y) = (y / 8) * 8 w + 8 x + y % 8,
-// so that 8 x 8 (and 8-row x k-column) patches of the image are contiguous.  Points arrive in Morton order: the
+// Order of the pixels of a level in the pixel space: bands of kBand = 4 rows, column by column inside a band,
+//     offset(x, y) = (y / 4) * 4 w + 4 x + y % 4,
+// so that 4-row x k-column patches of the image are contiguous.  Points arrive in Morton order: the
 // fragments of neighbouring points then land in a few nearby runs of the fragment buffer instead of one run per image
 // row, and a work item (a run of consecutive pixels) covers a compact patch.  The last band of a level is padded to
-// eight rows; padded pixels have no fragments and are skipped wherever pixels are visited.
-__device__ __forceinline__ int pixel_offset(int w, int x, int y) { return (y >> 3) * (w << 3) + (x << 3) + (y & 7); }
+// full height; padded pixels have no fragments and are skipped wherever pixels are visited.
+constexpr int kBand = VETR_PIXEL_BAND;  // rows per band (a power of two); 4 measured best among 1, 2, 4, 8, 16
+constexpr int kBandShift = kBand == 1 ? 0 : kBand == 2 ? 1 : kBand == 4 ? 2 : kBand == 8 ? 3 : 4;
+static_assert((1 << kBandShift) == kBand, "VETR_PIXEL_BAND must be 1, 2, 4, 8 or 16");
+__device__ __forceinline__ int pixel_offset(int w, int x, int y) { return (y >> kBandShift) * (w << kBandShift) + (x << kBandShift) + (y & (kBand - 1)); }
 
 // Mode 3 keeps the bilinear corner of a fragment in the two top bits of the record's descriptor index.
 constexpr int kCornerShift = 30;
@@ -516,13 +519,13 @@ __device__ __forceinline__ PixInfo decode_pixel(const Frame& f, unsigned g)
     int view, l;
     unsigned q;
     locate_pixel(f, g, view, l, q);
-    const int w = f.lw[l], h = f.lh[l], bw = w << 3;
-    // band = q / (8 w): float estimate, then one correction step either way (exact: the estimate is off by at most one)
+    const int w = f.lw[l], h = f.lh[l], bw = w << kBandShift;
+    // band = q / (kBand w): float estimate, then one correction step either way (exact: the estimate is off by at most one)
     int band = __float2int_rz(__fmul_rn((float)q, f.inv_band[l]));
     int rem  = (int)q - band * bw;
     if (rem < 0) rem += bw, --band;
     if (rem >= bw) rem -= bw, ++band;
-    const int x = rem >> 3, y = (band << 3) + (rem & 7);
+    const int x = rem >> kBandShift, y = (band << kBandShift) + (rem & (kBand - 1));
     r.x = (short)x, r.y = (short)y, r.level = (unsigned char)l, r.view = (unsigned char)view;
     r.valid    = y < h;
     r.interior = min(min(x, w - 1 - x), min(y, h - 1 - y)) > 2;
@@ -2629,7 +2632,7 @@ static int __float_as_int_host(float v)
     return i;
 }
 
-// Pixel space of one view: every level's height is padded to a multiple of eight rows (the banded order of pixel_offset).
+// Pixel space of one view: every level's height is padded to a multiple of kBand rows (the banded order of pixel_offset).
 // rbase / *row_major: the same levels in plain row-major order without padding.
 static int64_t pyramid(int w, int h, int L, int* lw, int* lh, long long* lbase, long long* rbase = nullptr,
                        long long* row_major = nullptr)
@@ -2639,7 +2642,7 @@ static int64_t pyramid(int w, int h, int L, int* lw, int* lh, long long* lbase, 
     {
         if (lw) lw[l] = w, lh[l] = h, lbase[l] = base;
         if (rbase) rbase[l] = rm;
-        base += (long long)w * ((h + 7) / 8 * 8);
+        base += (long long)w * ((h + kBand - 1) / kBand * kBand);
         rm += (long long)w * h;
         w /= 2;
         h /= 2;
@@ -2842,7 +2845,7 @@ static int fill_frame(vetr_ctx* ctx, Frame& f, const vetr_params* p, const vetr_
     f.P  = pyramid(f.w, f.h, f.L, f.lw, f.lh, f.lbase, f.rbase, &f.Prm);
     f.PT = f.P * n_views;
     if (f.lw[f.L - 1] < 1 || f.lh[f.L - 1] < 1) return VETR_E_INVALID_ARG;  // the reference asserts w > 0 && h > 0 per level
-    for (int l = 0; l < f.L; ++l) f.inv_lw[l] = 1.f / (float)f.lw[l], f.inv_band[l] = 1.f / (float)(8 * f.lw[l]);
+    for (int l = 0; l < f.L; ++l) f.inv_lw[l] = 1.f / (float)f.lw[l], f.inv_band[l] = 1.f / (float)(kBand * f.lw[l]);
     if (f.PT > 0x7fffffffLL || (long long)f.lw[0] * f.lh[0] * f.C * n_views > 0x7fffffffLL) return VETR_E_TOO_LARGE;
     f.position = (const float4*)cloud->position, f.index = cloud->index;
     f.texture = tex->texture, f.confidence = tex->confidence, f.background = tex->background;
@@ -3273,7 +3276,7 @@ extern "C" int vetr_get_lists(vetr_ctx* ctx, const vetr_lists* lists, int w, int
     const long long P    = pyramid(w, h, num_layers, lw, lh, lbase);
     const long long g0   = (long long)view * P + lbase[layer];
     const int W = lw[layer], H = lh[layer];
-    const long long npad = (long long)W * ((H + 7) / 8 * 8);  // pixels of the level in the pixel space
+    const long long npad = (long long)W * ((H + kBand - 1) / kBand * kBand);  // pixels of the level in the pixel space
     if ((long long)W * H == 0)
     {
         if (n_fragments) *n_fragments = 0;
@@ -3301,7 +3304,7 @@ extern "C" int vetr_get_lists(vetr_ctx* ctx, const vetr_lists* lists, int w, int
     for (int y = 0; y < H; ++y)
         for (int x = 0; x < W; ++x)
         {
-            const size_t k = (size_t)(y >> 3) * ((size_t)W << 3) + ((size_t)x << 3) + (y & 7);  // pixel_offset
+            const size_t k = (size_t)(y >> kBandShift) * ((size_t)W << kBandShift) + ((size_t)x << kBandShift) + (y & (kBand - 1));  // pixel_offset
             scanned[(size_t)y * W + x] = (int)run;
             if (out_collections)
                 for (int j = 0; j < counts[k]; ++j)
