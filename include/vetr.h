@@ -275,6 +275,50 @@ int vetr_grid_loss(vetr_ctx* ctx, const vetr_cameras* cameras, const vetr_view* 
                    const float* cell_bb_min, const float* cell_bb_len, const float* loss_img, int channels,
                    float* cell_value, int32_t* cell_access_count);
 
+/* Texture environment map: EnvironmentMapImpl::Sample2 (rendering/EnvironmentMap.cu:378-485) with its kernels
+ * BuildSphericalRayList (:201-287, pinhole branch) and CreateSampleUVMapAllSpheres (:587-684) and the libtorch operators
+ * of forward_mps5 (:692-758: two 3-D grid_sample calls, sigmoid, one multiply-add chain per sphere), as ONE kernel over
+ * all views, levels and pixels; the backward call replaces what autograd records for forward_mps5.
+ * The map is n_spheres concentric spheres around the origin (the last one at infinity), each an equirectangular
+ * resolution x resolution texture of a density and `channels` colours.  For a pixel of level l, the ray through it is
+ * intersected with every sphere from the inside, the hit direction gives (u, v) = (lon / pi, 2 lat / pi), the sphere gives
+ * z = 2 s / (n_spheres - 1) - 1, and the textures are sampled at (u, v, z) exactly as
+ * grid_sample(mode = bilinear, padding_mode = zeros, align_corners = true) does on the 5-D parameters.  Front to back,
+ *     env[c] += T * alpha_s * color_s[c];  T *= 1 - alpha_s;   alpha_s = hit_s * sigmoid(density_s), 1 on the last sphere,
+ * starting from T = the rasterizer's final transmittance of the pixel (LayerCuda::weight, RenderModule.cpp:130-141).
+ * A sphere the ray misses (possible only from outside it) contributes nothing; the reference's value there is NaN. */
+typedef struct vetr_envmap
+{
+    const float* density;  /* [n_spheres, resolution, resolution]            (EnvironmentMapImpl::density, [1,1,S,R,R]) */
+    const float* color;    /* [channels, n_spheres, resolution, resolution]  (EnvironmentMapImpl::color, [1,C,S,R,R]) */
+    float        radii[8]; /* inner_radius * radius_factor^s (EnvironmentMap.cu:109-113); the last sphere's is unused */
+    int32_t      n_spheres, resolution, channels; /* n_spheres 1..8 (MAX_NUM_SPHERES), channels 1..4 */
+    int32_t      up_axis;             /* 0, 1 or 2: the axis the latitude is measured from (EnvironmentMap.cu:543-563) */
+    int32_t      non_subzero_texture; /* 1: |color| is sampled (EnvironmentMap.cu:728) */
+} vetr_envmap;
+#define VETR_ENV_ADD 1            /* out += env instead of out = env: `images[i] + env_maps[i]`, RenderModule.cpp:188-203 */
+#define VETR_ENV_NOT_AT_POINTS 2  /* no_envmap_at_points: env counts as 0 where weight > 0.001 (RenderModule.cpp:190-201) */
+#define VETR_ENV_DEPTH_TEST_WEIGHT 4 /* mode 0 (FUZZY_DT), where weight is a hit count: T starts at (weight > 0.5 ? 0 : 1);
+                                        with VETR_ENV_ADD, out is also zeroed where weight <= 0.5 (RenderModule.cpp:143-155) */
+#define VETR_ENV_NO_DISTORTION_CHECK 8 /* the caller vouches that the views' cameras have zero distortion coefficients: the
+                                          call then does not read the intrinsics back (no synchronisation; capturable) */
+/*   weight   num_layers device pointers [n_views,1,h_l,w_l] (out_weight of vetr_forward)
+ *   out      num_layers device pointers [n_views,channels,h_l,w_l]
+ * All views share views[0].w x views[0].h; level sizes halve with integer division (EnvironmentMap.cu:398-436).
+ * Pinhole cameras only; non-zero distortion coefficients return VETR_E_UNSUPPORTED (the reference inverts the
+ * distortion with an iteration whose source is not part of its tree); checking that copies the intrinsics to the host
+ * and synchronises the stream unless VETR_ENV_NO_DISTORTION_CHECK is given. */
+int vetr_envmap_forward(vetr_ctx* ctx, const vetr_cameras* cameras, const vetr_view* views, int n_views, int num_layers,
+                        const vetr_envmap* env, const float* const* weight, float* const* out, int flags);
+/* Gradients of the map's parameters for the incoming gradient of `out` (same shapes), ADDED to
+ *   g_density [n_spheres, resolution, resolution],  g_color [channels, n_spheres, resolution, resolution].
+ * Nothing else receives a gradient in the reference either: the rays come from a raw kernel and the transmittance is a
+ * detached copy (RenderModule.cpp:140).  flags as in the forward call (VETR_ENV_ADD is ignored).  fp32 sums in no fixed
+ * order; lanes of a warp that hit the same texel are summed before the one atomic per texel and value. */
+int vetr_envmap_backward(vetr_ctx* ctx, const vetr_cameras* cameras, const vetr_view* views, int n_views, int num_layers,
+                         const vetr_envmap* env, const float* const* weight, const float* const* grad_out, int flags,
+                         float* g_density, float* g_color);
+
 /* L1 loss of an output pyramid against a target pyramid and its gradient, one launch for all levels:
  *   loss = sum_l mean |image_l - target_l| (written to the device scalar `loss`), grad_l = sign(image_l - target_l) / numel_l.
  * No counterpart in the reference's rasterizer: its training loop forms this term with libtorch element-wise operators
@@ -327,6 +371,7 @@ enum
     VETR_T_FINALIZE,     /* transpose + normalisation kernels */
     VETR_T_POINT_BACKWARD, /* per-point pass of the backward step (modes 1 and 2) */
     VETR_T_EXCHANGE,     /* vetr_exchange_finalize */
+    VETR_T_ENVMAP,       /* vetr_envmap_forward / vetr_envmap_backward */
     VETR_T_N
 };
 int vetr_set_timing(vetr_ctx* ctx, int enable);

@@ -190,3 +190,72 @@ def grid_loss(scene, view, bb_min, bb_len, loss_img, dist_cutoff: float = 20.0):
     if rc != 0:
         raise ValueError("oracle: invalid arguments")
     return value, count
+
+
+ENV_ADD, ENV_NOT_AT_POINTS, ENV_DEPTH_TEST_WEIGHT = 1, 2, 4
+
+
+class EnvMap:
+    """EnvironmentMapImpl's parameters (rendering/EnvironmentMap.h:286-301) as numpy arrays."""
+
+    def __init__(self, density, color, inner_radius=20.0, radius_factor=5.0, up_axis=0, non_subzero=False):
+        self.density = np.ascontiguousarray(density, np.float32)   # [S,R,R]
+        self.color = np.ascontiguousarray(color, np.float32)       # [C,S,R,R]
+        self.n_spheres, self.resolution = self.density.shape[0], self.density.shape[1]
+        self.channels = self.color.shape[0]
+        # radii.push_back(inner_radius * pow(radius_factor, i)) into a std::vector<float>, EnvironmentMap.cu:109-113
+        self.radii = np.array([np.float32(inner_radius * radius_factor ** i) for i in range(self.n_spheres)], np.float32)
+        self.up_axis, self.non_subzero = int(up_axis), bool(non_subzero)
+
+
+def _oviews(views):
+    return (OView * len(views))(*[OView(v.w, v.h, v.image_index, v.camera_index, v.camera_model,
+                                        (C.c_float * 5)(*v.crop), (C.c_float * 4)(*v.rot)) for v in views])
+
+
+def _env_args(env):
+    return (_ptr(env.density), _ptr(env.color), _ptr(env.radii), C.c_int(env.n_spheres), C.c_int(env.resolution),
+            C.c_int(env.channels), C.c_int(env.up_axis), C.c_int(int(env.non_subzero)))
+
+
+def envmap_forward(scene, views, num_layers, env, weight, flags=0, out=None):
+    """EnvironmentMapImpl::Sample2 on the CPU.  weight: per level [n_views,1,h_l,w_l]; returns per level [n_views,C,h_l,w_l]
+    (`out`, when given, is updated in place: the starting images of ENV_ADD)."""
+    weight = [np.ascontiguousarray(w, np.float32) for w in weight]
+    if out is None:
+        out = [np.zeros((len(views), env.channels) + w.shape[-2:], np.float32) for w in weight]
+    f = lib().vo_envmap_forward
+    f.restype = C.c_int
+    rc = f(_ptr(scene.poses), _ptr(scene.intrinsics), _oviews(views), C.c_int(len(views)), C.c_int(num_layers),
+           *_env_args(env), _ptr_array(weight), _ptr_array(out), C.c_int(flags))
+    if rc != 0:
+        raise ValueError("oracle: invalid arguments")
+    return out
+
+
+def envmap_uvz(scene, view, level, env):
+    """Sample coordinates [S, h_l*w_l, 3] and hit mask [S, h_l*w_l] of one view and level."""
+    w, h = view.w >> level, view.h >> level
+    uvz = np.zeros((env.n_spheres, h * w, 3), np.float32)
+    hit = np.zeros((env.n_spheres, h * w), np.float32)
+    f = lib().vo_envmap_uvz
+    f.restype = C.c_int
+    f(_ptr(scene.poses), _ptr(scene.intrinsics), C.byref(_oviews([view])[0]), C.c_int(level), _ptr(env.radii),
+      C.c_int(env.n_spheres), C.c_int(env.resolution), C.c_int(env.up_axis), _ptr(uvz), _ptr(hit))
+    return uvz, hit
+
+
+def envmap_backward(scene, views, num_layers, env, weight, grad_out, flags=0):
+    """Returns (g_density [S,R,R], g_color [C,S,R,R], mag_density, mag_color); the mag arrays are the sums of the
+    absolute addends of every element."""
+    weight = [np.ascontiguousarray(w, np.float32) for w in weight]
+    grad_out = [np.ascontiguousarray(g, np.float32) for g in grad_out]
+    gd, gc = np.zeros_like(env.density), np.zeros_like(env.color)
+    md, mc = np.zeros_like(env.density), np.zeros_like(env.color)
+    f = lib().vo_envmap_backward
+    f.restype = C.c_int
+    rc = f(_ptr(scene.poses), _ptr(scene.intrinsics), _oviews(views), C.c_int(len(views)), C.c_int(num_layers),
+           *_env_args(env), _ptr_array(weight), _ptr_array(grad_out), C.c_int(flags), _ptr(gd), _ptr(gc), _ptr(md), _ptr(mc))
+    if rc != 0:
+        raise ValueError("oracle: invalid arguments")
+    return gd, gc, md, mc

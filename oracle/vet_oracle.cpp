@@ -22,6 +22,8 @@
 //   projection backward   src/lib/rendering/PointRendererHelper.h:317-372
 //   normalisation         src/lib/rendering/PointRenderer.cu:1072-1109,1251-1308
 //   tangent application   src/lib/rendering/PointRenderer.cu:1325-1349
+//   error grid            src/lib/rendering/RenderForward.cu:639-791
+//   environment map       src/lib/rendering/EnvironmentMap.cu:201-287, 378-485, 587-758
 //
 // PARITY UNPINNED for the camera arithmetic: the reference takes TransformPoint, DivideByZ,
 // distortNormalizedPoint, IntrinsicsPinhole::normalizedToImage/scale, ImageView::distanceFromEdge and
@@ -1205,6 +1207,316 @@ int vo_grid_loss(const double* poses, const float* intrinsics, const OView* view
         cell_value[c] += (float)sum;
         cell_count[c] += hits;
     }
+    return 0;
+}
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Texture environment map: EnvironmentMapImpl::Sample2 / forward_mps5 (EnvironmentMap.cu:378-485, 692-758).
+// The ray of a pixel (BuildSphericalRayList, :201-287, pinhole branch), the sample coordinates on every sphere
+// (CreateSampleUVMapAllSpheres, :587-684) and the trilinear fetch of libtorch's grid_sample (bilinear, zero padding,
+// align_corners) are restated; tests compare the fetch and the composition with torch's own operators on the CPU.
+// saiga's IntrinsicsPinhole::unproject2 and Sophus' SE3::inverse are restated from their published definitions
+// (parity unpinned, as for the projection above).
+
+namespace
+{
+struct EnvRay
+{
+    V3 o, d;
+};
+
+inline V2 k_unproject2(const float* K, V2 ip)  // IntrinsicsPinhole::unproject2: the inverse of normalizedToImage
+{
+    float y = (ip.y - K[3]) / K[1];
+    float x = (ip.x - K[2] - K[4] * y) / K[0];
+    return {x, y};
+}
+
+inline EnvRay env_ray(const Pose& V, const float* intr, const OView& cam, int lw, int lh, float scale, int gx, int gy)
+{
+    // inverse crop rotation about the level's centre (integer division), Eigen's 2x2 inverse
+    const float det = cam.rot[0] * cam.rot[3] - cam.rot[2] * cam.rot[1];
+    const float inv = 1.f / det;
+    const float r00 = cam.rot[3] * inv, r01 = -cam.rot[1] * inv, r10 = -cam.rot[2] * inv, r11 = cam.rot[0] * inv;
+    const float cx = (float)(lw / 2), cy = (float)(lh / 2);
+    float dx = (float)gx - cx, dy = (float)gy - cy;
+    V2 ip{r00 * dx + r01 * dy, r10 * dx + r11 * dy};
+    ip = {ip.x + cx, ip.y + cy};
+    float crop[5];
+    for (int k = 0; k < 5; ++k) crop[k] = cam.crop[k] * scale;  // IntrinsicsPinhole::scale
+    V2 np = k_unproject2(intr, k_unproject2(crop, ip));          // zero distortion: the undistortion is the identity
+    // Sophus SE3::inverse: (q^-1, q^-1 * (-t))
+    Pose Vi;
+    Vi.q[0] = -V.q[0], Vi.q[1] = -V.q[1], Vi.q[2] = -V.q[2], Vi.q[3] = V.q[3];
+    V3 ti = rotate(Vi, {-V.t[0], -V.t[1], -V.t[2]});
+    V3 r  = rotate(Vi, {np.x, np.y, 1.f});
+    V3 wp{r.x + ti.x, r.y + ti.y, r.z + ti.z};
+    V3 d{wp.x - ti.x, wp.y - ti.y, wp.z - ti.z};
+    float n2 = d.x * d.x + d.y * d.y + d.z * d.z;
+    if (n2 > 0.f)
+    {
+        float n = std::sqrt(n2);
+        d = {d.x / n, d.y / n, d.z / n};
+    }
+    return {wp, d};
+}
+
+struct EnvTap  // one sphere's sample: trilinear base texel and weights, or a miss
+{
+    bool hit;
+    float u, v, z;
+    int x0, y0, z0;
+    float wx[2], wy[2], wz[2];
+};
+
+inline float env_unnormalize(float c, int size) { return ((c + 1.f) / 2.f) * (float)(size - 1); }
+
+inline EnvTap env_tap(const EnvRay& ray, float q2a, float qb, float f, int s, int S, int R, const float* radii, int up_axis)
+{
+    EnvTap t;
+    std::memset(&t, 0, sizeof(t));
+    V3 sv = ray.d;
+    t.hit = true;
+    if (s != S - 1)
+    {
+        const float r   = radii[s];
+        const float det = f + 2.f * q2a * (r * r);
+        t.hit           = det >= 0.f;
+        if (!t.hit) return t;
+        const float res = (-qb + std::sqrt(det)) / q2a;
+        V3 p{ray.o.x + res * ray.d.x, ray.o.y + res * ray.d.y, ray.o.z + res * ray.d.z};
+        const float len = std::sqrt(p.x * p.x + p.y * p.y + p.z * p.z);
+        sv = {p.x / len, p.y / len, p.z / len};
+    }
+    const float pi = 3.14159265358979323846f;
+    float a, b, c;  // lat = asin(a), lon = atan2(b, c)
+    if (up_axis == 0) a = sv.x, b = sv.y, c = sv.z;
+    else if (up_axis == 1) a = sv.y, b = sv.x, c = sv.z;
+    else a = sv.z, b = sv.x, c = sv.y;
+    a = std::fmin(std::fmax(a, -1.f), 1.f);  // a unit vector's component may round to 1 + 1 ulp
+    const float lat = std::asin(a), lon = std::atan2(b, c);
+    t.u = 2.f * (lon / 2.f / pi);
+    t.v = 2.f * (lat / pi);
+    t.z = S == 1 ? 0.f : (float)s / (float)(S - 1) * 2.f - 1.f;
+    const float ix = env_unnormalize(t.u, R), iy = env_unnormalize(t.v, R), iz = env_unnormalize(t.z, S);
+    const float fx = std::floor(ix), fy = std::floor(iy), fz = std::floor(iz);
+    t.x0 = (int)fx, t.y0 = (int)fy, t.z0 = (int)fz;
+    t.wx[1] = ix - fx, t.wx[0] = (fx + 1.f) - ix;
+    t.wy[1] = iy - fy, t.wy[0] = (fy + 1.f) - iy;
+    t.wz[1] = iz - fz, t.wz[0] = (fz + 1.f) - iz;
+    return t;
+}
+
+// grid_sample's trilinear fetch of one plane: corners in the order z, y, x; out-of-range corners read zero
+inline float env_fetch(const float* plane /*[S,R,R]*/, const EnvTap& t, int S, int R)
+{
+    float acc = 0.f;
+    for (int k = 0; k < 2; ++k)
+        for (int j = 0; j < 2; ++j)
+            for (int i = 0; i < 2; ++i)
+            {
+                const int x = t.x0 + i, y = t.y0 + j, z = t.z0 + k;
+                if (x < 0 || x >= R || y < 0 || y >= R || z < 0 || z >= S) continue;
+                const float w = t.wx[i] * t.wy[j] * t.wz[k];
+                acc += plane[((int64_t)z * R + y) * R + x] * w;
+            }
+    return acc;
+}
+
+struct EnvPixel
+{
+    EnvTap tap[8];
+    float alpha[8];    // hit * sigmoid(density), 1 on the last sphere
+    float sig[8];      // sigmoid(density)
+    float col[8][4];   // sampled colour (|.| when non_subzero)
+    float raw[8][4];   // before the abs
+    float T[9];        // transmittance in front of sphere s
+};
+
+constexpr int kEnvAdd = 1, kEnvNotAtPoints = 2, kEnvDepthTestWeight = 4;
+
+inline void env_pixel(const Pose& V, const float* intr, const OView& cam, int lw, int lh, float scale, int gx, int gy,
+                      const float* density, const float* color, const float* radii, int S, int R, int C, int up_axis,
+                      int non_subzero, float T0, EnvPixel& px)
+{
+    const EnvRay ray = env_ray(V, intr, cam, lw, lh, scale, gx, gy);
+    const float q2a = 2.f * (ray.d.x * ray.d.x) + 2.f * (ray.d.y * ray.d.y) + 2.f * (ray.d.z * ray.d.z);
+    const float qb  = 2.f * (ray.o.x * ray.d.x) + 2.f * (ray.o.y * ray.d.y) + 2.f * (ray.o.z * ray.d.z);
+    const float f   = qb * qb - 2.f * q2a * (ray.o.x * ray.o.x + ray.o.y * ray.o.y + ray.o.z * ray.o.z);
+    px.T[0] = T0;
+    for (int s = 0; s < S; ++s)
+    {
+        px.tap[s] = env_tap(ray, q2a, qb, f, s, S, R, radii, up_axis);
+        const EnvTap& t = px.tap[s];
+        px.sig[s] = 0.f, px.alpha[s] = 0.f;
+        for (int c = 0; c < 4; ++c) px.col[s][c] = px.raw[s][c] = 0.f;
+        if (t.hit)
+        {
+            if (s == S - 1)
+                px.alpha[s] = 1.f;
+            else
+            {
+                const float dv = env_fetch(density, t, S, R);
+                px.sig[s]      = 1.f / (1.f + std::exp(-dv));
+                px.alpha[s]    = px.sig[s];
+            }
+            for (int c = 0; c < C; ++c)
+            {
+                px.raw[s][c] = env_fetch(color + (int64_t)c * S * R * R, t, S, R);
+                px.col[s][c] = non_subzero ? std::fabs(px.raw[s][c]) : px.raw[s][c];
+            }
+        }
+        px.T[s + 1] = (1.f - px.alpha[s]) * px.T[s];
+    }
+}
+
+inline float env_start_T(float weight, int flags) { return (flags & kEnvDepthTestWeight) ? (weight > 0.5f ? 0.f : 1.f) : weight; }
+}  // namespace
+
+extern "C" {
+int vo_envmap_forward(const double* poses, const float* intrinsics, const OView* views, int n_views, int L,
+                      const float* density, const float* color, const float* radii, int S, int R, int C, int up_axis,
+                      int non_subzero, const float* const* weight, float* const* out, int flags)
+{
+    if (!poses || !intrinsics || !views || n_views < 1 || L < 1 || L > kMaxLayers || S < 1 || S > 8 || C < 1 || C > 4 || R < 1)
+        return -1;
+    int lw = views[0].w, lh = views[0].h;
+    float scale = 1.f;
+    for (int l = 0; l < L; ++l, lw /= 2, lh /= 2, scale *= 0.5f)
+        for (int b = 0; b < n_views; ++b)
+        {
+            const Pose V      = load_pose(poses + 8 * (int64_t)views[b].image_index);
+            const float* intr = intrinsics + 13 * (int64_t)views[b].camera_index;
+#pragma omp parallel for schedule(static)
+            for (int y = 0; y < lh; ++y)
+                for (int x = 0; x < lw; ++x)
+                {
+                    const int64_t pix = ((int64_t)b * lh + y) * lw + x;
+                    const float wgt   = weight[l][pix];
+                    EnvPixel px;
+                    env_pixel(V, intr, views[b], lw, lh, scale, x, y, density, color, radii, S, R, C, up_axis, non_subzero,
+                              env_start_T(wgt, flags), px);
+                    const bool masked = (flags & kEnvNotAtPoints) && wgt > 0.001f;
+                    for (int c = 0; c < C; ++c)
+                    {
+                        float acc = 0.f;
+                        for (int s = 0; s < S; ++s) acc = px.T[s] * px.alpha[s] * px.col[s][c] + acc;
+                        if (masked) acc = 0.f;
+                        float& o = out[l][(((int64_t)b * C + c) * lh + y) * lw + x];
+                        if (flags & kEnvAdd)
+                        {
+                            float base = o;
+                            if ((flags & kEnvDepthTestWeight) && !(wgt > 0.5f)) base = 0.f;
+                            o = base + acc;
+                        }
+                        else
+                            o = acc;
+                    }
+                }
+        }
+    return 0;
+}
+
+// Sample coordinates of one view and level, for the tests that run libtorch's own grid_sample on them:
+// uvz [S, h_l*w_l, 3], hit [S, h_l*w_l].
+int vo_envmap_uvz(const double* poses, const float* intrinsics, const OView* view, int level, const float* radii, int S,
+                  int R, int up_axis, float* uvz, float* hit)
+{
+    int lw = view->w, lh = view->h;
+    float scale = 1.f;
+    for (int l = 0; l < level; ++l) lw /= 2, lh /= 2, scale *= 0.5f;
+    const Pose V      = load_pose(poses + 8 * (int64_t)view->image_index);
+    const float* intr = intrinsics + 13 * (int64_t)view->camera_index;
+    for (int y = 0; y < lh; ++y)
+        for (int x = 0; x < lw; ++x)
+        {
+            const EnvRay ray = env_ray(V, intr, *view, lw, lh, scale, x, y);
+            const float q2a = 2.f * (ray.d.x * ray.d.x) + 2.f * (ray.d.y * ray.d.y) + 2.f * (ray.d.z * ray.d.z);
+            const float qb  = 2.f * (ray.o.x * ray.d.x) + 2.f * (ray.o.y * ray.d.y) + 2.f * (ray.o.z * ray.d.z);
+            const float f   = qb * qb - 2.f * q2a * (ray.o.x * ray.o.x + ray.o.y * ray.o.y + ray.o.z * ray.o.z);
+            for (int s = 0; s < S; ++s)
+            {
+                const EnvTap t  = env_tap(ray, q2a, qb, f, s, S, R, radii, up_axis);
+                const int64_t i = (int64_t)s * lw * lh + (int64_t)y * lw + x;
+                uvz[3 * i] = t.u, uvz[3 * i + 1] = t.v, uvz[3 * i + 2] = t.z;
+                hit[i] = t.hit ? 1.f : 0.f;
+            }
+        }
+    return 0;
+}
+
+// Gradients of density [S,R,R] and color [C,S,R,R], added to g_density / g_color; sums are formed in double.
+// mag_density / mag_color (optional): the sums of the absolute addends, for the tests' tolerance.
+int vo_envmap_backward(const double* poses, const float* intrinsics, const OView* views, int n_views, int L,
+                       const float* density, const float* color, const float* radii, int S, int R, int C, int up_axis,
+                       int non_subzero, const float* const* weight, const float* const* grad_out, int flags,
+                       float* g_density, float* g_color, float* mag_density, float* mag_color)
+{
+    if (!poses || !intrinsics || !views || n_views < 1 || L < 1 || L > kMaxLayers || S < 1 || S > 8 || C < 1 || C > 4 || R < 1)
+        return -1;
+    const int64_t plane = (int64_t)S * R * R;
+    std::vector<double> gd(plane, 0.0), gc(plane * C, 0.0), md(plane, 0.0), mc(plane * C, 0.0);
+    int lw = views[0].w, lh = views[0].h;
+    float scale = 1.f;
+    for (int l = 0; l < L; ++l, lw /= 2, lh /= 2, scale *= 0.5f)
+        for (int b = 0; b < n_views; ++b)
+        {
+            const Pose V      = load_pose(poses + 8 * (int64_t)views[b].image_index);
+            const float* intr = intrinsics + 13 * (int64_t)views[b].camera_index;
+            for (int y = 0; y < lh; ++y)
+                for (int x = 0; x < lw; ++x)
+                {
+                    const int64_t pix = ((int64_t)b * lh + y) * lw + x;
+                    const float wgt   = weight[l][pix];
+                    if ((flags & kEnvNotAtPoints) && wgt > 0.001f) continue;
+                    EnvPixel px;
+                    env_pixel(V, intr, views[b], lw, lh, scale, x, y, density, color, radii, S, R, C, up_axis, non_subzero,
+                              env_start_T(wgt, flags), px);
+                    float G[4] = {0, 0, 0, 0};
+                    for (int c = 0; c < C; ++c) G[c] = grad_out[l][(((int64_t)b * C + c) * lh + y) * lw + x];
+                    // rest[s] = d(sum of the spheres behind s, per unit of transmittance behind s) . G
+                    float rest = 0.f;
+                    for (int s = S - 1; s >= 0; --s)
+                    {
+                        float dot = 0.f;
+                        for (int c = 0; c < C; ++c) dot += px.col[s][c] * G[c];
+                        const float g_alpha = px.T[s] * (dot - rest);
+                        rest                = px.alpha[s] * dot + (1.f - px.alpha[s]) * rest;
+                        const EnvTap& t     = px.tap[s];
+                        if (!t.hit) continue;
+                        const float g_dens = s == S - 1 ? 0.f : g_alpha * (px.sig[s] * (1.f - px.sig[s]));
+                        float g_col[4];
+                        for (int c = 0; c < C; ++c)
+                        {
+                            g_col[c] = px.T[s] * px.alpha[s] * G[c];
+                            if (non_subzero) g_col[c] = px.raw[s][c] > 0.f ? g_col[c] : (px.raw[s][c] < 0.f ? -g_col[c] : 0.f);
+                        }
+                        for (int k = 0; k < 2; ++k)
+                            for (int j = 0; j < 2; ++j)
+                                for (int i = 0; i < 2; ++i)
+                                {
+                                    const int tx = t.x0 + i, ty = t.y0 + j, tz = t.z0 + k;
+                                    if (tx < 0 || tx >= R || ty < 0 || ty >= R || tz < 0 || tz >= S) continue;
+                                    const float w   = t.wx[i] * t.wy[j] * t.wz[k];
+                                    const int64_t a = ((int64_t)tz * R + ty) * R + tx;
+                                    gd[a] += (double)(w * g_dens);
+                                    md[a] += std::fabs((double)(w * g_dens));
+                                    for (int c = 0; c < C; ++c)
+                                    {
+                                        gc[c * plane + a] += (double)(w * g_col[c]);
+                                        mc[c * plane + a] += std::fabs((double)(w * g_col[c]));
+                                    }
+                                }
+                    }
+                }
+        }
+    for (int64_t i = 0; i < plane; ++i) g_density[i] += (float)gd[i];
+    for (int64_t i = 0; i < plane * C; ++i) g_color[i] += (float)gc[i];
+    if (mag_density)
+        for (int64_t i = 0; i < plane; ++i) mag_density[i] = (float)md[i];
+    if (mag_color)
+        for (int64_t i = 0; i < plane * C; ++i) mag_color[i] = (float)mc[i];
     return 0;
 }
 }  // extern "C"

@@ -1,0 +1,278 @@
+"""Texture environment map (EnvironmentMapImpl::Sample2 / forward_mps5, rendering/EnvironmentMap.cu:378-485, 692-758).
+
+CPU part: the restatement in oracle/ against (1) rays and sphere hits computed independently in float64 and (2) the
+libtorch operators the reference itself calls on the sample coordinates: grid_sample on the 5-D parameters, sigmoid,
+the per-sphere multiply-add chain, and autograd for the parameter gradients.
+GPU part: the CUDA kernels, through the C ABI, against the restatement.
+"""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import oracle as O
+from vet_b200 import scenes
+
+
+def _scene(n_views=2, w=80, h=56, f=60.0, seed=3):
+    sc = scenes.tiny_scene(n=16, w=w, h=h, n_views=n_views, seed=seed)
+    intr = scenes.pinhole_intrinsics(f, f * 1.1, w / 2 - 0.5, h / 2 + 0.25)
+    sc.intrinsics = np.repeat(intr[None].astype(np.float32), sc.intrinsics.shape[0], 0)
+    return sc
+
+
+def _env(rng, S=4, R=48, C=4, up_axis=0, non_subzero=False, inner_radius=20.0):
+    density = rng.normal(0.0, 2.0, size=(S, R, R)).astype(np.float32)
+    color = rng.normal(0.3, 1.0, size=(C, S, R, R)).astype(np.float32)
+    return O.EnvMap(density, color, inner_radius=inner_radius, up_axis=up_axis, non_subzero=non_subzero)
+
+
+def _weights(rng, sc, L):
+    out = []
+    for l in range(L):
+        w = rng.uniform(0.0, 1.0, size=(len(sc.views), 1, sc.views[0].h >> l, sc.views[0].w >> l)).astype(np.float32)
+        w[w < 0.2] = 0.0  # fully covered pixels
+        out.append(w)
+    return out
+
+
+def _rays_f64(sc, view, level):
+    """World-space ray of every pixel of a level: origin = the pixel's point on the z = 1 plane, direction from the eye."""
+    w, h = view.w >> level, view.h >> level
+    q = sc.poses[view.image_index, :4]
+    t = sc.poses[view.image_index, 4:7]
+    x, y, z, s = q
+    Rm = np.array([[1 - 2 * (y * y + z * z), 2 * (x * y - z * s), 2 * (x * z + y * s)],
+                   [2 * (x * y + z * s), 1 - 2 * (x * x + z * z), 2 * (y * z - x * s)],
+                   [2 * (x * z - y * s), 2 * (y * z + x * s), 1 - 2 * (x * x + y * y)]])
+    K = sc.intrinsics[view.camera_index].astype(np.float64)
+    crop = np.array(view.crop, np.float64) * 0.5 ** level
+    rot = np.array(view.rot, np.float64).reshape(2, 2)
+    gy, gx = np.mgrid[0:h, 0:w].astype(np.float64)
+    c = np.array([w // 2, h // 2], np.float64)
+    ip = np.stack([gx, gy], -1) - c
+    ip = ip @ np.linalg.inv(rot).T + c
+    py = (ip[..., 1] - crop[3]) / crop[1]
+    px = (ip[..., 0] - crop[2] - crop[4] * py) / crop[0]
+    ny = (py - K[3]) / K[1]
+    nx = (px - K[2] - K[4] * ny) / K[0]
+    cam = np.stack([nx, ny, np.ones_like(nx)], -1)
+    eye = -Rm.T @ t
+    wp = cam @ Rm + eye  # R^T cam + eye
+    d = wp - eye
+    d /= np.linalg.norm(d, axis=-1, keepdims=True)
+    return wp.reshape(-1, 3), d.reshape(-1, 3)
+
+
+def test_sample_coordinates_against_float64():
+    sc = _scene()
+    rng = np.random.default_rng(0)
+    for up_axis in (0, 1, 2):
+        env = _env(rng, S=4, up_axis=up_axis, inner_radius=3.0)  # the orbit cameras sit outside the first sphere
+        for level in (0, 1):
+            uvz, hit = O.envmap_uvz(sc, sc.views[1], level, env)
+            o, d = _rays_f64(sc, sc.views[1], level)
+            for s in range(env.n_spheres):
+                if s == env.n_spheres - 1:
+                    p, ok = d, np.ones(len(d), bool)
+                else:
+                    # |o + k d| = r, the far root
+                    b = (o * d).sum(-1)
+                    disc = b * b - ((o * o).sum(-1) - float(env.radii[s]) ** 2)
+                    ok = disc >= 0
+                    k = -b + np.sqrt(np.where(ok, disc, 0))
+                    p = o + k[:, None] * d
+                    p /= np.linalg.norm(p, axis=-1, keepdims=True)
+                a = [(0, 1, 2), (1, 0, 2), (2, 0, 1)][up_axis]
+                lat, lon = np.arcsin(p[:, a[0]]), np.arctan2(p[:, a[1]], p[:, a[2]])
+                sure = np.abs(disc) > 1e-4 if s != env.n_spheres - 1 else ok
+                assert np.array_equal(hit[s][sure] > 0, ok[sure])
+                m = ok & sure
+                assert m.sum() > 0
+                du = np.abs(uvz[s, m, 0] - lon[m] / np.pi)
+                du = np.minimum(du, 2 - du)  # the seam
+                assert du.max() < 5e-6
+                assert np.abs(uvz[s, m, 1] - 2 * lat[m] / np.pi).max() < 5e-6
+                assert np.allclose(uvz[s, :, 2][m], 2 * s / (env.n_spheres - 1) - 1, atol=1e-6)
+
+
+def _torch_forward_mps5(env, uvz, hit, T0, density_t, color_t):
+    """forward_mps5 (EnvironmentMap.cu:692-758) with libtorch's operators on given sample coordinates."""
+    S, n = uvz.shape[0], uvz.shape[1]
+    grid = torch.from_numpy(uvz).reshape(1, S * n, 1, 1, 3)
+    dens = F.grid_sample(density_t, grid, mode="bilinear", padding_mode="zeros", align_corners=True).reshape(1, S, n)
+    alpha_all = torch.sigmoid(dens.permute(1, 0, 2))
+    col = F.grid_sample(color_t, grid, mode="bilinear", padding_mode="zeros", align_corners=True)
+    col = col.reshape(env.channels, S, n).permute(1, 0, 2)
+    if env.non_subzero:
+        col = torch.abs(col)
+    final = torch.zeros(env.channels, n)
+    T = torch.from_numpy(T0).reshape(n, 1)
+    for s in range(S):
+        alpha = alpha_all[s]
+        if s == S - 1:
+            alpha = torch.ones_like(alpha)
+        alpha = alpha * torch.from_numpy(hit[s]).unsqueeze(0)
+        final = T.squeeze().unsqueeze(0) * alpha * col[s] + final
+        T = ((1 - alpha.squeeze()) * T.squeeze()).unsqueeze(1)
+    return final
+
+
+@pytest.mark.parametrize("non_subzero,S", [(False, 4), (True, 3), (False, 1)])
+def test_forward_and_backward_against_libtorch_operators(non_subzero, S):
+    sc = _scene()
+    rng = np.random.default_rng(5)
+    env = _env(rng, S=S, non_subzero=non_subzero)
+    L = 2
+    weight = _weights(rng, sc, L)
+    out = O.envmap_forward(sc, sc.views, L, env, weight)
+    grad_out = [rng.standard_normal(o.shape).astype(np.float32) for o in out]
+    gd, gc, md, mc = O.envmap_backward(sc, sc.views, L, env, weight, grad_out)
+
+    density_t = torch.from_numpy(env.density)[None, None].clone().requires_grad_(True)
+    color_t = torch.from_numpy(env.color)[None].clone().requires_grad_(True)
+    loss = 0
+    for l in range(L):
+        for b, view in enumerate(sc.views):
+            uvz, hit = O.envmap_uvz(sc, view, l, env)
+            assert hit.min() == 1.0  # cameras inside the first sphere: every ray hits every sphere
+            ref = _torch_forward_mps5(env, uvz, hit, weight[l][b].reshape(-1), density_t, color_t)
+            ref = ref.reshape(env.channels, view.h >> l, view.w >> l)
+            # same operators, same order: only the rounding of exp() and of fused multiply-adds can differ
+            np.testing.assert_allclose(out[l][b], ref.detach().numpy(), rtol=2e-6, atol=2e-6)
+            loss = loss + (ref * torch.from_numpy(grad_out[l][b])).sum()
+    loss.backward()
+    tgc = color_t.grad[0].numpy()
+    tgd = density_t.grad[0, 0].numpy() if S > 1 else np.zeros_like(env.density)  # one sphere: its alpha is the constant 1
+    assert np.abs(tgd).max() > 0 or S == 1
+    assert np.all(np.abs(gd - tgd) <= 1e-5 * md + 1e-7)
+    assert np.all(np.abs(gc - tgc) <= 1e-5 * mc + 1e-7)
+
+
+def test_flags():
+    sc = _scene()
+    rng = np.random.default_rng(9)
+    env = _env(rng)
+    L = 2
+    weight = _weights(rng, sc, L)
+    plain = O.envmap_forward(sc, sc.views, L, env, weight)
+    start = [rng.standard_normal(o.shape).astype(np.float32) for o in plain]
+    added = O.envmap_forward(sc, sc.views, L, env, weight, flags=O.ENV_ADD, out=[s.copy() for s in start])
+    for a, s, p in zip(added, start, plain):
+        assert np.array_equal(a, s + p)
+    masked = O.envmap_forward(sc, sc.views, L, env, weight, flags=O.ENV_NOT_AT_POINTS)
+    for m, p, w in zip(masked, plain, weight):
+        keep = np.broadcast_to(w <= 0.001, p.shape)
+        assert np.array_equal(m[keep], p[keep]) and np.all(m[~keep] == 0)
+    # mode 0: the weight is a hit count
+    counts = [np.floor(w * 3) for w in weight]
+    dt = O.envmap_forward(sc, sc.views, L, env, counts, flags=O.ENV_DEPTH_TEST_WEIGHT | O.ENV_ADD, out=[s.copy() for s in start])
+    full = O.envmap_forward(sc, sc.views, L, env, [np.ones_like(w) for w in weight])
+    for d, s, fl, c in zip(dt, start, full, counts):
+        hitp = np.broadcast_to(c > 0.5, s.shape)
+        assert np.array_equal(d[hitp], s[hitp]) and np.array_equal(d[~hitp], fl[~hitp])
+    # masked pixels send no gradient
+    g = [np.ones_like(p) for p in plain]
+    gd0, gc0, _, _ = O.envmap_backward(sc, sc.views, L, env, [np.ones_like(w) for w in weight], g, flags=O.ENV_NOT_AT_POINTS)
+    assert not gd0.any() and not gc0.any()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CUDA kernels against the restatement
+
+
+def _gpu_run(sc, env, L, weight, flags, grad_out=None, start=None):
+    from vet_b200.render import Rasterizer
+
+    dev = torch.device("cuda:0")
+    rast = Rasterizer(dev)
+    poses, intr = torch.from_numpy(sc.poses).to(dev), torch.from_numpy(sc.intrinsics).to(dev)
+    density, color = torch.from_numpy(env.density).to(dev), torch.from_numpy(env.color).to(dev)
+    kw = dict(up_axis=env.up_axis, non_subzero=env.non_subzero, flags=flags)
+    w_t = [torch.from_numpy(w).to(dev) for w in weight]
+    out_t = [torch.from_numpy(s).to(dev) for s in start] if start is not None else None
+    out_t = rast.envmap_forward(poses, intr, sc.views, L, density, color, env.radii, w_t, out=out_t, **kw)
+    res = [o.cpu().numpy() for o in out_t]
+    if grad_out is None:
+        return res
+    g_t = [torch.from_numpy(g).to(dev) for g in grad_out]
+    gd, gc = rast.envmap_backward(poses, intr, sc.views, L, density, color, env.radii, w_t, g_t, **kw)
+    return res, gd.cpu().numpy(), gc.cpu().numpy()
+
+
+def _sample_tolerance(env):
+    """A coordinate that differs by e texels changes a bilinear sample by at most e x the largest texel difference; the
+    device's asinf / atan2f / expf differ from the host's by a few ulp of a coordinate of size resolution."""
+    e = 8 * np.finfo(np.float32).eps * env.resolution
+    step = max(np.abs(np.diff(env.color, axis=-1)).max(), np.abs(np.diff(env.color, axis=-2)).max())
+    return float(e * step * 2 + 1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("up_axis,non_subzero,S,flags", [(0, False, 4, 0), (1, True, 3, O.ENV_NOT_AT_POINTS), (2, False, 1, 0),
+                                                         (0, False, 8, 0)])
+def test_gpu_envmap_matches_oracle(up_axis, non_subzero, S, flags):
+    sc = _scene(n_views=3, w=200, h=120, f=150.0)
+    rng = np.random.default_rng(11)
+    env = _env(rng, S=S, R=64, up_axis=up_axis, non_subzero=non_subzero)
+    # smooth textures: the comparison is of the arithmetic, not of how a 1e-6 texel shift samples noise
+    k = torch.ones(1, 1, 5, 5) / 25
+    env.color = F.conv2d(torch.from_numpy(env.color).reshape(-1, 1, 64, 64), k, padding=2).reshape(env.color.shape).numpy()
+    env.density = F.conv2d(torch.from_numpy(env.density).reshape(-1, 1, 64, 64), k, padding=2).reshape(env.density.shape).numpy()
+    L = 3
+    weight = _weights(rng, sc, L)
+    ref = O.envmap_forward(sc, sc.views, L, env, weight, flags=flags)
+    grad_out = [rng.standard_normal(o.shape).astype(np.float32) for o in ref]
+    rgd, rgc, md, mc = O.envmap_backward(sc, sc.views, L, env, weight, grad_out, flags=flags)
+    out, gd, gc = _gpu_run(sc, env, L, weight, flags, grad_out)
+    tol = _sample_tolerance(env)
+    for o, r in zip(out, ref):
+        assert np.abs(o - r).max() <= tol
+    assert np.abs(rgc).max() > 0
+    # gradient sums: 1e-5 of the summed magnitudes, plus the texel-weight shift of the coordinates
+    e = 8 * np.finfo(np.float32).eps * env.resolution
+    assert np.all(np.abs(gd - rgd) <= (1e-5 + 4 * e) * md + 1e-6)
+    assert np.all(np.abs(gc - rgc) <= (1e-5 + 4 * e) * mc + 1e-6)
+
+
+@pytest.mark.gpu
+def test_gpu_envmap_add_and_depth_test_flags():
+    sc = _scene(n_views=2, w=96, h=64, f=80.0)
+    rng = np.random.default_rng(13)
+    env = _env(rng, S=4, R=32)
+    L = 2
+    weight = [np.floor(w * 3) for w in _weights(rng, sc, L)]
+    flags = O.ENV_ADD | O.ENV_DEPTH_TEST_WEIGHT
+    start = [rng.standard_normal((2, 4, 64 >> l, 96 >> l)).astype(np.float32) for l in range(L)]
+    ref = O.envmap_forward(sc, sc.views, L, env, weight, flags=flags, out=[s.copy() for s in start])
+    out = _gpu_run(sc, env, L, weight, flags, start=start)
+    tol = _sample_tolerance(env)
+    for o, r in zip(out, ref):
+        assert np.abs(o - r).max() <= tol
+
+
+@pytest.mark.gpu
+def test_gpu_envmap_rejects_distortion_and_bad_arguments():
+    from vet_b200 import _lib
+    from vet_b200.render import Rasterizer
+
+    sc = _scene()
+    rng = np.random.default_rng(1)
+    env = _env(rng, R=16)
+    dev = torch.device("cuda:0")
+    rast = Rasterizer(dev)
+    poses = torch.from_numpy(sc.poses).to(dev)
+    density, color = torch.from_numpy(env.density).to(dev), torch.from_numpy(env.color).to(dev)
+    w_t = [torch.ones(2, 1, 56, 80, device=dev)]
+    distorted = sc.intrinsics.copy()
+    distorted[:, 5] = 0.1
+    with pytest.raises(_lib.VetrError) as ei:
+        rast.envmap_forward(poses, torch.from_numpy(distorted).to(dev), sc.views, 1, density, color, env.radii, w_t)
+    assert ei.value.status == _lib.E_UNSUPPORTED
+    intr = torch.from_numpy(sc.intrinsics).to(dev)
+    with pytest.raises(_lib.VetrError) as ei:
+        rast.envmap_forward(poses, intr, sc.views, 1, density, color, env.radii, w_t, up_axis=3)
+    assert ei.value.status == _lib.E_INVALID_ARG
+    with pytest.raises(_lib.VetrError) as ei:
+        rast.envmap_forward(poses, intr, sc.views, 1, density, color, env.radii, w_t, flags=64)
+    assert ei.value.status == _lib.E_INVALID_ARG

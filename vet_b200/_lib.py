@@ -58,6 +58,11 @@ MAX_RANKS = 16
 PIXEL_BAND = 4  # VETR_PIXEL_BAND: rows per band of the pixel space
 
 
+class EnvMap(C.Structure):
+    _fields_ = [("density", C.c_void_p), ("color", C.c_void_p), ("radii", C.c_float * 8), ("n_spheres", C.c_int32),
+                ("resolution", C.c_int32), ("channels", C.c_int32), ("up_axis", C.c_int32), ("non_subzero_texture", C.c_int32)]
+
+
 class Exchange(C.Structure):
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("raw", C.c_void_p * MAX_RANKS), ("out", C.c_void_p * MAX_RANKS),
                 ("raw_multicast", C.c_void_p), ("out_multicast", C.c_void_p)]
@@ -69,10 +74,12 @@ EXPORTS = [
     "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists", "vetr_set_timing", "vetr_get_timings",
     "vetr_launch_count", "vetr_scan_counts_static", "vetr_exchange_raw_floats", "vetr_exchange_out_floats",
     "vetr_exchange_finalize", "vetr_grid_loss", "vetr_l1_loss_grad", "vetr_backward_phase", "vetr_exchange_finalize_part",
+    "vetr_envmap_forward", "vetr_envmap_backward",
 ]
+ENV_ADD, ENV_NOT_AT_POINTS, ENV_DEPTH_TEST_WEIGHT, ENV_NO_DISTORTION_CHECK = 1, 2, 4, 8
 BACKWARD_FRAGMENTS, BACKWARD_POINTS = 1, 2
 SEG_DESC, SEG_POINTS, SEG_CONF = 1, 2, 4
-TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize", "point_backward", "exchange"]
+TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize", "point_backward", "exchange", "envmap"]
 
 _lib = None
 
@@ -129,5 +136,8 @@ def lib():
         L.vetr_exchange_finalize_part.argtypes = [vp, C.POINTER(Exchange), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
         L.vetr_l1_loss_grad.argtypes = [vp, C.c_int, vp, vp, vp, C.POINTER(C.c_int64), vp]
         L.vetr_grid_loss.argtypes = [vp, C.POINTER(Cameras), C.POINTER(View), C.c_float, C.c_int, vp, vp, vp, C.c_int, vp, vp]
+        L.vetr_envmap_forward.argtypes = [vp, C.POINTER(Cameras), C.POINTER(View), C.c_int, C.c_int, C.POINTER(EnvMap), vp, vp, C.c_int]
+        L.vetr_envmap_backward.argtypes = [vp, C.POINTER(Cameras), C.POINTER(View), C.c_int, C.c_int, C.POINTER(EnvMap), vp, vp,
+                                           C.c_int, vp, vp]
         _lib = L
     return _lib

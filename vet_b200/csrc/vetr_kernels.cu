@@ -2572,6 +2572,8 @@ __global__ void __launch_bounds__(256) l1_loss_grad_kernel(const __grid_constant
 
 }  // namespace vetr
 
+#include "vetr_envmap.cuh"
+
 // =========================================================================================================
 // C ABI
 
@@ -3162,6 +3164,119 @@ extern "C" int vetr_grid_loss(vetr_ctx* ctx, const vetr_cameras* cams, const vet
         const int ctas = min((n_cells + kGridWarps - 1) / kGridWarps, ctx->sm_count * 16);
         grid_loss_kernel<<<ctas, 32 * kGridWarps, 0, ctx->stream>>>(f, a, ctx->grid_queue, ctx->grid_queue_count);
         grid_loss_chunk_kernel<<<ctx->sm_count * 16, 32 * kGridWarps, 0, ctx->stream>>>(f, a, ctx->grid_queue, ctx->grid_queue_count);
+    }
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+// Shared argument checks and parameter block of the two environment map calls, for views [v0, v0 + nv).
+static int envmap_args(const vetr_cameras* cams, const vetr_view* views, int n_views, int num_layers, const vetr_envmap* env,
+                       const float* const* weight, int flags, int v0, int nv, EnvArgs& a)
+{
+    if (!cams || !views || !env || !weight || !cams->poses_se3 || !cams->intrinsics || !env->density || !env->color)
+        return VETR_E_INVALID_ARG;
+    if (n_views < 1 || num_layers < 1 || num_layers > VETR_MAX_LAYERS) return VETR_E_INVALID_ARG;
+    if (env->n_spheres < 1 || env->n_spheres > kEnvMaxSpheres || env->channels < 1 || env->channels > 4 || env->resolution < 1 ||
+        env->up_axis < 0 || env->up_axis > 2 || (flags & ~15) != 0)
+        return VETR_E_INVALID_ARG;
+    if ((long long)env->n_spheres * env->resolution * env->resolution > 0x7fffffffLL) return VETR_E_TOO_LARGE;
+    const int w = views[0].w, h = views[0].h;
+    if (w <= 0 || h <= 0 || (w >> (num_layers - 1)) < 1 || (h >> (num_layers - 1)) < 1) return VETR_E_INVALID_ARG;
+    memset(&a, 0, sizeof(a));
+    a.n_views = nv, a.L = num_layers, a.S = env->n_spheres, a.R = env->resolution, a.C = env->channels;
+    a.up_axis = env->up_axis, a.non_subzero = env->non_subzero_texture, a.flags = flags;
+    memcpy(a.radii, env->radii, sizeof(a.radii));
+    a.poses = cams->poses_se3, a.intr = cams->intrinsics, a.density = env->density, a.color = env->color;
+    for (int b = 0; b < nv; ++b)
+    {
+        const vetr_view& v = views[v0 + b];
+        if (v.w != w || v.h != h) return VETR_E_INVALID_ARG;
+        if (v.camera_model != 0) return VETR_E_UNSUPPORTED;
+        if (v.image_index < 0 || v.image_index >= cams->n_img || v.camera_index < 0 || v.camera_index >= cams->n_cam)
+            return VETR_E_INVALID_ARG;
+        a.views[b].image_index = v.image_index, a.views[b].camera_index = v.camera_index;
+        memcpy(a.views[b].crop, v.crop, sizeof(v.crop));
+        memcpy(a.views[b].rot, v.rot, sizeof(v.rot));
+    }
+    long long run = 0;
+    int lw = w, lh = h;
+    float scale = 1.f;
+    for (int l = 0; l < num_layers; ++l, lw /= 2, lh /= 2, scale *= 0.5f)
+    {
+        if (!weight[l]) return VETR_E_INVALID_ARG;
+        if ((long long)n_views * 4 * lw * lh > 0x7fffffffLL) return VETR_E_TOO_LARGE;
+        a.lw[l] = lw, a.lh[l] = lh, a.scale[l] = scale;
+        run += (long long)nv * lw * lh;
+        a.lend[l]   = run;
+        a.weight[l] = weight[l] + (long long)v0 * lw * lh;
+    }
+    return VETR_OK;
+}
+
+// The cameras' distortion coefficients must all be zero: read back once per call (a few hundred bytes; synchronises).
+static int envmap_check_distortion(vetr_ctx* ctx, const vetr_cameras* cams, const vetr_view* views, int n_views)
+{
+    std::vector<float> k((size_t)cams->n_cam * 13);
+    VETR_CUDA(ctx, cudaMemcpyAsync(k.data(), cams->intrinsics, k.size() * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    VETR_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int b = 0; b < n_views; ++b)
+    {
+        if (views[b].camera_index < 0 || views[b].camera_index >= cams->n_cam) return VETR_E_INVALID_ARG;
+        for (int i = 5; i < 13; ++i)
+            if (k[(size_t)views[b].camera_index * 13 + i] != 0.f) return VETR_E_UNSUPPORTED;
+    }
+    return VETR_OK;
+}
+
+extern "C" int vetr_envmap_forward(vetr_ctx* ctx, const vetr_cameras* cams, const vetr_view* views, int n_views, int num_layers,
+                                   const vetr_envmap* env, const float* const* weight, float* const* out, int flags)
+{
+    if (!ctx || !out) return VETR_E_INVALID_ARG;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    PassScope scope(ctx, VETR_T_ENVMAP, 0);
+    for (int v0 = 0; v0 < n_views || v0 == 0; v0 += VETR_MAX_VIEWS)
+    {
+        const int nv = std::min(VETR_MAX_VIEWS, n_views - v0);
+        EnvArgs a;
+        int rc = envmap_args(cams, views, n_views, num_layers, env, weight, flags, v0, nv, a);
+        if (rc != VETR_OK) return rc;
+        if (v0 == 0 && !(flags & VETR_ENV_NO_DISTORTION_CHECK) && (rc = envmap_check_distortion(ctx, cams, views, n_views)) != VETR_OK) return rc;
+        for (int l = 0; l < num_layers; ++l)
+        {
+            if (!out[l]) return VETR_E_INVALID_ARG;
+            a.out[l] = out[l] + (long long)v0 * env->channels * a.lw[l] * a.lh[l];
+        }
+        const long long blocks = (a.lend[num_layers - 1] + kEnvThreads - 1) / kEnvThreads;
+        ctx->launches += 1;
+        envmap_forward_kernel<<<(int)std::min<long long>(blocks, (long long)ctx->sm_count * 32), kEnvThreads, 0, ctx->stream>>>(a);
+    }
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+extern "C" int vetr_envmap_backward(vetr_ctx* ctx, const vetr_cameras* cams, const vetr_view* views, int n_views, int num_layers,
+                                    const vetr_envmap* env, const float* const* weight, const float* const* grad_out, int flags,
+                                    float* g_density, float* g_color)
+{
+    if (!ctx || !grad_out || !g_density || !g_color) return VETR_E_INVALID_ARG;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    PassScope scope(ctx, VETR_T_ENVMAP, 0);
+    for (int v0 = 0; v0 < n_views || v0 == 0; v0 += VETR_MAX_VIEWS)
+    {
+        const int nv = std::min(VETR_MAX_VIEWS, n_views - v0);
+        EnvArgs a;
+        int rc = envmap_args(cams, views, n_views, num_layers, env, weight, flags, v0, nv, a);
+        if (rc != VETR_OK) return rc;
+        if (v0 == 0 && !(flags & VETR_ENV_NO_DISTORTION_CHECK) && (rc = envmap_check_distortion(ctx, cams, views, n_views)) != VETR_OK) return rc;
+        for (int l = 0; l < num_layers; ++l)
+        {
+            if (!grad_out[l]) return VETR_E_INVALID_ARG;
+            a.grad[l] = grad_out[l] + (long long)v0 * env->channels * a.lw[l] * a.lh[l];
+        }
+        a.g_density = g_density, a.g_color = g_color;
+        const long long blocks = (a.lend[num_layers - 1] + kEnvThreads - 1) / kEnvThreads;
+        ctx->launches += 1;
+        envmap_backward_kernel<<<(int)std::min<long long>(blocks, (long long)ctx->sm_count * 32), kEnvThreads, 0, ctx->stream>>>(a);
     }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;

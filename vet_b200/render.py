@@ -290,6 +290,49 @@ class Rasterizer:
                                     _ptr(cell_access_count))
         self._check(rc, "vetr_grid_loss")
 
+    def _envmap(self, density, color, radii, up_axis, non_subzero):
+        assert density.dtype == torch.float32 and color.dtype == torch.float32 and density.is_contiguous() and color.is_contiguous()
+        n_spheres, res = density.shape[-3], density.shape[-1]
+        channels = color.shape[-4]
+        assert density.shape[-2] == res and tuple(color.shape[-3:]) == (n_spheres, res, res) and len(radii) == n_spheres
+        r = (C.c_float * 8)(*([float(x) for x in radii] + [0.0] * (8 - n_spheres)))
+        return L.EnvMap(density.data_ptr(), color.data_ptr(), r, n_spheres, res, channels, int(up_axis), int(bool(non_subzero)))
+
+    def envmap_forward(self, poses, intrinsics, views, num_layers, density, color, radii, weight, up_axis=0, non_subzero=False,
+                       flags=0, out=None):
+        """EnvironmentMapImpl::Sample2 (EnvironmentMap.cu:378-485): samples the sphere textures density [S,R,R] (or
+        [1,1,S,R,R]) and color [C,S,R,R] along every pixel's ray, front to back, starting from the transmittance planes
+        `weight` (per level [n_views,1,h_l,w_l]).  Returns per level [n_views,C,h_l,w_l]; with ENV_ADD in `flags` the result
+        is added to the images given as `out`."""
+        self._sync_stream()
+        env = self._envmap(density, color, radii, up_axis, non_subzero)
+        h, w = views[0].h, views[0].w
+        if out is None:
+            out = [torch.empty((len(views), env.channels, h >> l, w >> l), dtype=torch.float32, device=density.device)
+                   for l in range(num_layers)]
+        assert all(t.is_contiguous() and t.dtype == torch.float32 for t in list(weight) + list(out))
+        cams = L.Cameras(poses.data_ptr(), intrinsics.data_ptr(), poses.shape[0], intrinsics.shape[0])
+        rc = L.lib().vetr_envmap_forward(self._ctx, C.byref(cams), self._views(views), len(views), num_layers, C.byref(env),
+                                         _ptr_array(weight), _ptr_array(out), flags)
+        self._check(rc, "vetr_envmap_forward")
+        return out
+
+    def envmap_backward(self, poses, intrinsics, views, num_layers, density, color, radii, weight, grad_out, up_axis=0,
+                        non_subzero=False, flags=0, g_density=None, g_color=None):
+        """Adds the gradients of the map's parameters to g_density / g_color (zero-filled when not given) and returns them."""
+        self._sync_stream()
+        env = self._envmap(density, color, radii, up_axis, non_subzero)
+        if g_density is None:
+            g_density = torch.zeros_like(density)
+        if g_color is None:
+            g_color = torch.zeros_like(color)
+        assert all(t.is_contiguous() and t.dtype == torch.float32 for t in list(weight) + list(grad_out) + [g_density, g_color])
+        cams = L.Cameras(poses.data_ptr(), intrinsics.data_ptr(), poses.shape[0], intrinsics.shape[0])
+        rc = L.lib().vetr_envmap_backward(self._ctx, C.byref(cams), self._views(views), len(views), num_layers, C.byref(env),
+                                          _ptr_array(weight), _ptr_array(grad_out), flags, _ptr(g_density), _ptr(g_color))
+        self._check(rc, "vetr_envmap_backward")
+        return g_density, g_color
+
     def l1_loss_grad(self, images, targets, grads, loss):
         """loss (device scalar) = sum over levels of mean |image - target|; grads[l] = sign(image - target) / numel, one launch."""
         self._sync_stream()
