@@ -1301,7 +1301,9 @@ inline EnvTap env_tap(const EnvRay& ray, float q2a, float qb, float f, int s, in
     t.z = S == 1 ? 0.f : (float)s / (float)(S - 1) * 2.f - 1.f;
     const float ix = env_unnormalize(t.u, R), iy = env_unnormalize(t.v, R), iz = env_unnormalize(t.z, S);
     const float fx = std::floor(ix), fy = std::floor(iy), fz = std::floor(iz);
-    t.x0 = (int)fx, t.y0 = (int)fy, t.z0 = (int)fz;
+    // kept inside [-2, size]: defined int conversion for every float; out there everything reads zero either way
+    t.x0 = (int)std::fmin(std::fmax(fx, -2.f), (float)R), t.y0 = (int)std::fmin(std::fmax(fy, -2.f), (float)R);
+    t.z0 = (int)std::fmin(std::fmax(fz, -2.f), (float)S);
     t.wx[1] = ix - fx, t.wx[0] = (fx + 1.f) - ix;
     t.wy[1] = iy - fy, t.wy[0] = (fy + 1.f) - iy;
     t.wz[1] = iz - fz, t.wz[0] = (fz + 1.f) - iz;

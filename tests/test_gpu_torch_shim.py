@@ -127,3 +127,36 @@ def test_fill_scene_grid_with_loss(ops):
     assert ref_c.sum() > 1000
     np.testing.assert_array_equal(count.cpu().numpy()[:, 0].astype(np.int64), ref_c)
     np.testing.assert_allclose(value.cpu().numpy()[:, 0], ref_v, rtol=1e-5)
+
+
+def test_environment_map_sample2(ops):
+    """EnvironmentMap::Sample2 through the libtorch surface and autograd, against the CPU restatement."""
+    import torch
+
+    from oracle import oracle as O
+    from tests import test_envmap as E
+
+    dev = torch.device("cuda", 0)
+    sc = E._scene(n_views=2, w=128, h=96, f=100.0)
+    rng = np.random.default_rng(21)
+    env = E._env(rng, S=4, R=32)
+    L = 3
+    weight = E._weights(rng, sc, L)
+    ref = O.envmap_forward(sc, sc.views, L, env, weight)
+    grads = [rng.standard_normal(r.shape).astype(np.float32) for r in ref]
+    rgd, rgc, md, mc = O.envmap_backward(sc, sc.views, L, env, weight, grads)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    density = t(env.density[None, None]).requires_grad_(True)
+    color = t(env.color[None]).requires_grad_(True)
+    vi, vf = _views(sc, dev)
+    out = ops.environment_map_sample2(density, color, 20.0, 5.0, env.up_axis, env.non_subzero, t(sc.poses), t(sc.intrinsics),
+                                      vi, vf, L, [t(w) for w in weight])
+    assert len(out) == L
+    tol = E._sample_tolerance(env)
+    for o, r in zip(out, ref):
+        assert tuple(o.shape) == r.shape
+        assert np.abs(o.detach().cpu().numpy() - r).max() <= tol
+    sum((o * t(g)).sum() for o, g in zip(out, grads)).backward()
+    e = 8 * np.finfo(np.float32).eps * env.resolution
+    assert np.all(np.abs(density.grad.cpu().numpy()[0, 0] - rgd) <= (1e-5 + 4 * e) * md + 1e-6)
+    assert np.all(np.abs(color.grad.cpu().numpy()[0] - rgc) <= (1e-5 + 4 * e) * mc + 1e-6)

@@ -165,7 +165,10 @@ __device__ __forceinline__ EnvTap env_tap(const EnvArgs& a, const EnvRay& ray, i
     const float z = a.S == 1 ? 0.f : (float)s / (float)(a.S - 1) * 2.f - 1.f;
     const float ix = env_unnormalize(u, a.R), iy = env_unnormalize(v, a.R), iz = env_unnormalize(z, a.S);
     const float fx = floorf(ix), fy = floorf(iy), fz = floorf(iz);
-    t.x0 = (int)fx, t.y0 = (int)fy, t.z0 = (int)fz;
+    // the base texel, kept inside [-2, size] so that the int conversion and the + 1 of the far corners are defined for
+    // every float (anything out there is outside the texture and reads zero either way)
+    t.x0 = (int)fminf(fmaxf(fx, -2.f), (float)a.R), t.y0 = (int)fminf(fmaxf(fy, -2.f), (float)a.R);
+    t.z0 = (int)fminf(fmaxf(fz, -2.f), (float)a.S);
     t.wx[1] = ix - fx, t.wx[0] = (fx + 1.f) - ix;
     t.wy[1] = iy - fy, t.wy[0] = (fy + 1.f) - iy;
     t.wz[1] = iz - fz, t.wz[0] = (fz + 1.f) - iz;

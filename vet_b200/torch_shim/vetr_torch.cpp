@@ -342,6 +342,133 @@ variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_out
 }  // namespace torch::autograd
 
 // ---------------------------------------------------------------------------------------------------------
+// Environment map
+
+namespace vetr_torch
+{
+EnvironmentMapImpl::EnvironmentMapImpl(int channels, int h, int w, bool /*log_texture*/, int axis, int num_images, float inner_radius,
+                                       float radius_factor, bool non_subzero_texture)
+    : up_axis(axis), channels(channels), non_subzero_texture(non_subzero_texture)
+{
+    TORCH_CHECK(num_images >= 1 && num_images <= 8, "currently not more spheres are supported");  // EnvironmentMap.cu:97
+    const int resolution = std::max(h, w);
+    const auto opt = torch::TensorOptions(torch::kCUDA);
+    density = register_parameter("density", torch::full({1, 1, num_images, resolution, resolution}, 1.f, opt));
+    color   = register_parameter("color", torch::full({1, channels, num_images, resolution, resolution}, 1.f, opt));
+    for (int i = 0; i < num_images; ++i) radii.push_back(inner_radius * std::pow(radius_factor, i));  // EnvironmentMap.cu:109-113
+}
+
+namespace
+{
+void fill_env(const EnvironmentSampleState& st, const torch::Tensor& density, const torch::Tensor& color, vetr_envmap& env)
+{
+    env = vetr_envmap{};
+    env.density = density.data_ptr<float>(), env.color = color.data_ptr<float>();
+    env.n_spheres = (int)density.size(2), env.resolution = (int)density.size(4), env.channels = (int)color.size(1);
+    env.up_axis = st.up_axis, env.non_subzero_texture = st.non_subzero_texture;
+    for (int i = 0; i < 8; ++i) env.radii[i] = st.radii[i];
+}
+
+std::vector<vetr_view> to_views(const std::vector<ReducedImageInfo>& images)
+{
+    std::vector<vetr_view> views(images.size());
+    for (size_t b = 0; b < images.size(); ++b)
+    {
+        const ReducedImageInfo& im = images[b];
+        vetr_view& v = views[b];
+        v = vetr_view{};
+        v.w = im.w, v.h = im.h, v.image_index = im.image_index, v.camera_index = im.camera_index, v.camera_model = im.camera_model_type;
+        for (int i = 0; i < 5; ++i) v.crop[i] = im.crop_transform[i];
+        for (int i = 0; i < 4; ++i) v.rot[i] = im.crop_rotation[i];
+    }
+    return views;
+}
+}  // namespace
+
+std::vector<torch::Tensor> EnvironmentMapImpl::Sample2(torch::Tensor poses, torch::Tensor intrinsics,
+                                                       const std::vector<ReducedImageInfo>& info_batch, int num_layers,
+                                                       const std::vector<std::vector<torch::Tensor>>& layers_cuda)
+{
+    TORCH_CHECK((int)layers_cuda.size() >= num_layers && !info_batch.empty(), "Sample2: one weight list per layer");
+    auto st = torch::make_intrusive<EnvironmentSampleState>();
+    st->poses = poses.contiguous(), st->intrinsics = intrinsics.contiguous();
+    st->images = info_batch, st->num_layers = num_layers;
+    for (int l = 0; l < num_layers; ++l)
+    {
+        TORCH_CHECK(layers_cuda[l].size() == info_batch.size(), "Sample2: one weight tensor per image and layer");
+        // the reference copies every [1,1,h,w] plane into its ray list (EnvironmentMap.cu:423); here into one [B,1,h,w] tensor
+        st->weight.push_back(torch::cat(layers_cuda[l], 0).detach().to(torch::kFloat32).contiguous());
+    }
+    for (size_t i = 0; i < radii.size(); ++i) st->radii[i] = radii[i];
+    st->up_axis = up_axis, st->non_subzero_texture = non_subzero_texture, st->cache = &cache_;
+    return torch::autograd::EnvironmentSample::apply(density, color, torch::IValue(st));
+}
+}  // namespace vetr_torch
+
+namespace torch::autograd
+{
+variable_list EnvironmentSample::forward(AutogradContext* ctx, Variable density, Variable color, IValue state)
+{
+    using namespace vetr_torch;
+    auto st = state.toCustomClass<EnvironmentSampleState>();
+    TORCH_CHECK(density.dim() == 5 && color.dim() == 5 && density.is_cuda() && color.is_cuda(), "density / color must be 5-D CUDA tensors");
+    c10::cuda::CUDAGuard guard(density.device());
+    vetr_ctx* vc = st->cache->context(density.device().index());
+    torch::Tensor d = density.detach().contiguous(), c = color.detach().contiguous();
+    vetr_envmap env;
+    fill_env(*st, d, c, env);
+    std::vector<vetr_view> views = to_views(st->images);
+    const int B = (int)views.size();
+    variable_list out;
+    std::vector<const float*> wp;
+    std::vector<float*> op;
+    int h = views[0].h, w = views[0].w;
+    for (int l = 0; l < st->num_layers; ++l, h /= 2, w /= 2)
+    {
+        TORCH_CHECK(st->weight[l].numel() == (int64_t)B * h * w, "Sample2: weight of layer ", l, " has the wrong size");
+        out.push_back(torch::empty({B, env.channels, h, w}, d.options()));
+        wp.push_back(st->weight[l].data_ptr<float>());
+        op.push_back(out.back().data_ptr<float>());
+    }
+    vetr_cameras cams{st->poses.data_ptr<double>(), st->intrinsics.data_ptr<float>(), (int)st->poses.size(0), (int)st->intrinsics.size(0)};
+    int rc = vetr_envmap_forward(vc, &cams, views.data(), B, st->num_layers, &env, wp.data(), op.data(), st->flags);
+    if (rc != VETR_OK) throw std::runtime_error(std::string("vetr_envmap_forward: ") + vetr_strerror(rc));
+    ctx->save_for_backward({density, color});
+    ctx->saved_data["state"] = state;
+    return out;
+}
+
+variable_list EnvironmentSample::backward(AutogradContext* ctx, variable_list grad_output)
+{
+    using namespace vetr_torch;
+    auto st    = ctx->saved_data["state"].toCustomClass<EnvironmentSampleState>();
+    auto saved = ctx->get_saved_variables();
+    torch::Tensor d = saved[0].detach().contiguous(), c = saved[1].detach().contiguous();
+    c10::cuda::CUDAGuard guard(d.device());
+    vetr_ctx* vc = st->cache->context(d.device().index());
+    vetr_envmap env;
+    fill_env(*st, d, c, env);
+    std::vector<vetr_view> views = to_views(st->images);
+    const int B = (int)views.size();
+    std::vector<torch::Tensor> g(st->num_layers);
+    std::vector<const float*> wp, gp;
+    int h = views[0].h, w = views[0].w;
+    for (int l = 0; l < st->num_layers; ++l, h /= 2, w /= 2)
+    {
+        g[l] = grad_output[l].defined() ? grad_output[l].to(torch::kFloat32).contiguous() : torch::zeros({B, env.channels, h, w}, d.options());
+        wp.push_back(st->weight[l].data_ptr<float>());
+        gp.push_back(g[l].data_ptr<float>());
+    }
+    torch::Tensor g_density = torch::zeros_like(d), g_color = torch::zeros_like(c);
+    vetr_cameras cams{st->poses.data_ptr<double>(), st->intrinsics.data_ptr<float>(), (int)st->poses.size(0), (int)st->intrinsics.size(0)};
+    int rc = vetr_envmap_backward(vc, &cams, views.data(), B, st->num_layers, &env, wp.data(), gp.data(),
+                                  st->flags | VETR_ENV_NO_DISTORTION_CHECK, g_density.data_ptr<float>(), g_color.data_ptr<float>());
+    if (rc != VETR_OK) throw std::runtime_error(std::string("vetr_envmap_backward: ") + vetr_strerror(rc));
+    return {g_density, g_color, Variable()};
+}
+}  // namespace torch::autograd
+
+// ---------------------------------------------------------------------------------------------------------
 // Python-visible entry for tests: builds a NeuralRenderInfo from plain arguments and calls BlendPointCloud.
 namespace
 {
@@ -412,11 +539,46 @@ void fill_scene_grid_with_loss_op(torch::Tensor poses_se3, torch::Tensor intrins
     for (int i = 0; i < 4; ++i) im.crop_rotation[i] = pf[5 + i];
     cache.FillSceneGridWithLoss(0, scene, {im}, loss_img);
 }
+
+// EnvironmentMap::Sample2 with the caller's parameter tensors (density [1,1,S,R,R], color [1,C,S,R,R]) and one
+// transmittance tensor [B,1,h_l,w_l] per layer; views as in blend_point_cloud.
+std::vector<torch::Tensor> environment_map_sample2_op(torch::Tensor density, torch::Tensor color, double inner_radius,
+                                                      double radius_factor, int64_t up_axis, bool non_subzero_texture,
+                                                      torch::Tensor poses_se3, torch::Tensor intrinsics, torch::Tensor views_i,
+                                                      torch::Tensor views_f, int64_t num_layers, std::vector<torch::Tensor> weights)
+{
+    // the module outlives the autograd graph of the call (its cache owns the context the backward node uses)
+    static std::vector<EnvironmentMap> keep;
+    EnvironmentMap env((int)color.size(1), 1, 1, false, (int)up_axis, (int)density.size(2), (float)inner_radius, (float)radius_factor,
+                       non_subzero_texture);
+    keep.push_back(env);
+    if (keep.size() > 8) keep.erase(keep.begin());
+    env->density = density, env->color = color;
+    auto vi = views_i.cpu().contiguous();
+    auto vf = views_f.cpu().contiguous();
+    std::vector<ReducedImageInfo> images;
+    for (int64_t b = 0; b < vi.size(0); ++b)
+    {
+        ReducedImageInfo im;
+        const int* pi   = vi.data_ptr<int>() + 5 * b;
+        const float* pf = vf.data_ptr<float>() + 9 * b;
+        im.w = pi[0], im.h = pi[1], im.image_index = pi[2], im.camera_index = pi[3], im.camera_model_type = pi[4];
+        for (int i = 0; i < 5; ++i) im.crop_transform[i] = pf[i];
+        for (int i = 0; i < 4; ++i) im.crop_rotation[i] = pf[5 + i];
+        images.push_back(im);
+    }
+    std::vector<std::vector<torch::Tensor>> layers(num_layers);
+    for (int64_t l = 0; l < num_layers; ++l)
+        for (int64_t b = 0; b < vi.size(0); ++b) layers[l].push_back(weights[l].slice(0, b, b + 1));
+    return env->Sample2(poses_se3, intrinsics, images, (int)num_layers, layers);
+}
 }  // namespace
 
 TORCH_LIBRARY(vetr, m)
 {
     m.def("fill_scene_grid_with_loss", &fill_scene_grid_with_loss_op);
+    m.class_<vetr_torch::EnvironmentSampleState>("EnvironmentSampleState").def(torch::init());
+    m.def("environment_map_sample2", &environment_map_sample2_op);
     m.class_<vetr_torch::NeuralRenderInfo>("NeuralRenderInfo").def(torch::init());
     m.def("blend_point_cloud", &blend_point_cloud_op);
     m.def("apply_tangent_to_pose", &vetr_torch::ApplyTangentToPose);

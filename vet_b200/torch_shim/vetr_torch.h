@@ -7,6 +7,8 @@
 //   ApplyTangentToPose(tangent, pose)     rendering/PointRenderer.h:64,   rendering/PointRenderer.cu:1343-1349
 //   PointRendererCache / LayerCuda        rendering/PointRenderer.h:66-248 (the members outside code reads:
 //                                         layers_cuda[i].weight / .depth, num_batches, render_mode)
+//   PointRendererCache::FillSceneGridWithLoss   rendering/PointRenderer.h:152, RenderForward.cu:761-791
+//   EnvironmentMapImpl (constructor, density, color, Sample2)   rendering/EnvironmentMap.h:252-301
 // The reference's NeuralScene / RenderParams / ReducedImageInfo come from parts of VET that need the saiga library;
 // the structs below carry exactly the fields the render operator reads from them, under the same names, so that the
 // reference's call site (models/Pipeline.cpp:133 via RenderModule.cpp:45-245) maps onto them one to one.
@@ -129,6 +131,46 @@ class NeuralRenderInfo : public torch::CustomClassHolder
 std::vector<torch::Tensor> BlendPointCloud(NeuralRenderInfo* info);
 
 void ApplyTangentToPose(torch::Tensor tangent, torch::Tensor pose);
+
+// What one Sample2 call hands to its autograd node.
+struct EnvironmentSampleState : public torch::CustomClassHolder
+{
+    torch::Tensor poses, intrinsics;
+    std::vector<ReducedImageInfo> images;
+    std::vector<torch::Tensor> weight;  // per layer [B,1,h,w]
+    int num_layers = 0, flags = 0;
+    float radii[8] = {};
+    int up_axis = 0;
+    bool non_subzero_texture = false;
+    PointRendererCache* cache = nullptr;
+};
+
+// rendering/EnvironmentMap.h:252-301.  Same constructor arguments, parameters and Sample2 result; `scene` (only read
+// for OCam cameras) and the timer are not taken.  density / color receive gradients through autograd as in the
+// reference, where forward_mps5 is built from differentiable libtorch operators.
+class EnvironmentMapImpl : public torch::nn::Module
+{
+   public:
+    EnvironmentMapImpl(int channels, int h, int w, bool log_texture, int axis = 0, int num_images = 4, float inner_radius = 20.f,
+                       float radius_factor = 5.f, bool non_subzero_texture = false);
+
+    // layers_cuda[layer][batch]: the rasterizer's transmittance of that image and layer, [1,1,h_l,w_l]
+    // (RenderModule.cpp:133-141).  Returns per layer [B,channels,h_l,w_l].
+    std::vector<torch::Tensor> Sample2(torch::Tensor poses, torch::Tensor intrinsics, const std::vector<ReducedImageInfo>& info_batch,
+                                       int num_layers, const std::vector<std::vector<torch::Tensor>>& layers_cuda);
+
+    torch::Tensor density;  // [1, 1, num_images, resolution, resolution]
+    torch::Tensor color;    // [1, channels, num_images, resolution, resolution]
+    int NumImages() { return (int)density.size(2); }
+
+   private:
+    std::vector<float> radii;
+    int up_axis;
+    int channels;
+    bool non_subzero_texture;
+    PointRendererCache cache_;  // owns the C-ABI context
+};
+TORCH_MODULE(EnvironmentMap);
 }  // namespace vetr_torch
 
 namespace torch::autograd
@@ -138,6 +180,12 @@ struct PointRender : public Function<PointRender>
     static variable_list forward(AutogradContext* ctx, Variable texture, Variable background_color, Variable points,
                                  Variable pose_tangents, Variable intrinsics, Variable confidence,
                                  Variable dynamic_refinement, IValue info);
+    static variable_list backward(AutogradContext* ctx, variable_list grad_output);
+};
+
+struct EnvironmentSample : public Function<EnvironmentSample>
+{
+    static variable_list forward(AutogradContext* ctx, Variable density, Variable color, IValue state);
     static variable_list backward(AutogradContext* ctx, variable_list grad_output);
 };
 }  // namespace torch::autograd
