@@ -31,7 +31,9 @@ def _weights(rng, sc, L):
     out = []
     for l in range(L):
         w = rng.uniform(0.0, 1.0, size=(len(sc.views), 1, sc.views[0].h >> l, sc.views[0].w >> l)).astype(np.float32)
-        w[w < 0.2] = 0.0  # fully covered pixels
+        thin = (w >= 0.1) & (w < 0.2)
+        w[thin] = (w[thin] - 0.1) * 0.009  # nearly covered pixels: below the 0.001 threshold of no_envmap_at_points
+        w[(w < 0.1) & ~thin] = 0.0         # fully covered pixels
         out.append(w)
     return out
 
@@ -185,7 +187,7 @@ def _gpu_run(sc, env, L, weight, flags, grad_out=None, start=None):
     from vet_b200.render import Rasterizer
 
     dev = torch.device("cuda:0")
-    rast = Rasterizer(dev)
+    rast = Rasterizer(0)
     poses, intr = torch.from_numpy(sc.poses).to(dev), torch.from_numpy(sc.intrinsics).to(dev)
     density, color = torch.from_numpy(env.density).to(dev), torch.from_numpy(env.color).to(dev)
     kw = dict(up_axis=env.up_axis, non_subzero=env.non_subzero, flags=flags)
@@ -208,6 +210,17 @@ def _sample_tolerance(env):
     return float(e * step * 2 + 1e-5)
 
 
+def _grad_tolerance(mag, env):
+    """Bound of |device sum - host sum| per texel.  mag: the summed magnitudes of a texel's addends.  1e-5 of them for the
+    order of the fp32 sums; and a sample coordinate that differs by e texels (asinf / atan2f differ by a few ulp between
+    device and host) moves the fraction e of an addend between neighbouring texels, so a texel can gain or lose e times
+    what its 3 x 3 neighbourhood receives."""
+    e = 8 * np.finfo(np.float32).eps * env.resolution
+    m = torch.from_numpy(mag).reshape(-1, 1, env.resolution, env.resolution)
+    near = (F.avg_pool2d(m, 3, stride=1, padding=1, count_include_pad=True) * 9).reshape(mag.shape).numpy()
+    return 1e-5 * mag + 4 * e * near + 1e-6
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("up_axis,non_subzero,S,flags", [(0, False, 4, 0), (1, True, 3, O.ENV_NOT_AT_POINTS), (2, False, 1, 0),
                                                          (0, False, 8, 0)])
@@ -219,6 +232,9 @@ def test_gpu_envmap_matches_oracle(up_axis, non_subzero, S, flags):
     k = torch.ones(1, 1, 5, 5) / 25
     env.color = F.conv2d(torch.from_numpy(env.color).reshape(-1, 1, 64, 64), k, padding=2).reshape(env.color.shape).numpy()
     env.density = F.conv2d(torch.from_numpy(env.density).reshape(-1, 1, 64, 64), k, padding=2).reshape(env.density.shape).numpy()
+    if non_subzero:  # |.| has no gradient at 0: keep the samples away from it, with both signs present
+        sign = np.where(np.arange(env.channels) % 2 == 0, -1.0, 1.0).astype(np.float32)[:, None, None, None]
+        env.color = sign * (np.abs(env.color) + 0.1)
     L = 3
     weight = _weights(rng, sc, L)
     ref = O.envmap_forward(sc, sc.views, L, env, weight, flags=flags)
@@ -229,10 +245,8 @@ def test_gpu_envmap_matches_oracle(up_axis, non_subzero, S, flags):
     for o, r in zip(out, ref):
         assert np.abs(o - r).max() <= tol
     assert np.abs(rgc).max() > 0
-    # gradient sums: 1e-5 of the summed magnitudes, plus the texel-weight shift of the coordinates
-    e = 8 * np.finfo(np.float32).eps * env.resolution
-    assert np.all(np.abs(gd - rgd) <= (1e-5 + 4 * e) * md + 1e-6)
-    assert np.all(np.abs(gc - rgc) <= (1e-5 + 4 * e) * mc + 1e-6)
+    assert np.all(np.abs(gd - rgd) <= _grad_tolerance(md, env))
+    assert np.all(np.abs(gc - rgc) <= _grad_tolerance(mc, env))
 
 
 @pytest.mark.gpu
@@ -260,7 +274,7 @@ def test_gpu_envmap_rejects_distortion_and_bad_arguments():
     rng = np.random.default_rng(1)
     env = _env(rng, R=16)
     dev = torch.device("cuda:0")
-    rast = Rasterizer(dev)
+    rast = Rasterizer(0)
     poses = torch.from_numpy(sc.poses).to(dev)
     density, color = torch.from_numpy(env.density).to(dev), torch.from_numpy(env.color).to(dev)
     w_t = [torch.ones(2, 1, 56, 80, device=dev)]

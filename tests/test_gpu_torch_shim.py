@@ -157,6 +157,5 @@ def test_environment_map_sample2(ops):
         assert tuple(o.shape) == r.shape
         assert np.abs(o.detach().cpu().numpy() - r).max() <= tol
     sum((o * t(g)).sum() for o, g in zip(out, grads)).backward()
-    e = 8 * np.finfo(np.float32).eps * env.resolution
-    assert np.all(np.abs(density.grad.cpu().numpy()[0, 0] - rgd) <= (1e-5 + 4 * e) * md + 1e-6)
-    assert np.all(np.abs(color.grad.cpu().numpy()[0] - rgc) <= (1e-5 + 4 * e) * mc + 1e-6)
+    assert np.all(np.abs(density.grad.cpu().numpy()[0, 0] - rgd) <= E._grad_tolerance(md, env))
+    assert np.all(np.abs(color.grad.cpu().numpy()[0] - rgc) <= E._grad_tolerance(mc, env))
