@@ -179,6 +179,32 @@ def test_flags():
     assert not gd0.any() and not gc0.any()
 
 
+def _fixture():
+    import os
+
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_tiny.npz"))
+    sc = scenes.tiny_scene(n=4, w=40, h=28, n_views=2, seed=79, crop=True)  # the scene tests/golden/make_golden.py used
+    env = O.EnvMap(g["env_density"], g["env_color"], up_axis=1)
+    assert np.array_equal(env.radii, g["env_radii"])
+    return g, sc, env, 2
+
+
+def test_fixture_restatement_and_libtorch_values():
+    """The committed fixture holds the restatement's output and, beside it, forward_mps5 evaluated with libtorch's own
+    grid_sample / sigmoid / autograd when the fixture was made: the restatement reproduces the first bit for bit and
+    agrees with the second."""
+    g, sc, env, L = _fixture()
+    weight = [g[f"env_weight_l{l}"] for l in range(L)]
+    out = O.envmap_forward(sc, sc.views, L, env, weight)
+    gd, gc, md, mc = O.envmap_backward(sc, sc.views, L, env, weight, [g[f"env_gout_l{l}"] for l in range(L)])
+    for l in range(L):
+        assert np.array_equal(out[l], g[f"env_out_l{l}"])
+        np.testing.assert_allclose(out[l], g[f"env_torch_l{l}"], rtol=2e-6, atol=2e-6)
+    assert np.array_equal(gd, g["env_g_density"]) and np.array_equal(gc, g["env_g_color"])
+    assert np.all(np.abs(gd - g["env_torch_g_density"]) <= 1e-5 * md + 1e-7)
+    assert np.all(np.abs(gc - g["env_torch_g_color"]) <= 1e-5 * mc + 1e-7)
+
+
 # ---------------------------------------------------------------------------------------------------------
 # CUDA kernels against the restatement
 
@@ -290,3 +316,19 @@ def test_gpu_envmap_rejects_distortion_and_bad_arguments():
     with pytest.raises(_lib.VetrError) as ei:
         rast.envmap_forward(poses, intr, sc.views, 1, density, color, env.radii, w_t, flags=64)
     assert ei.value.status == _lib.E_INVALID_ARG
+
+
+@pytest.mark.gpu
+def test_gpu_envmap_against_fixture():
+    """The kernels against the committed fixture: the restatement's values and those of libtorch's operators."""
+    g, sc, env, L = _fixture()
+    weight = [g[f"env_weight_l{l}"] for l in range(L)]
+    gout = [g[f"env_gout_l{l}"] for l in range(L)]
+    out, gd, gc = _gpu_run(sc, env, L, weight, 0, gout)
+    tol = _sample_tolerance(env)
+    for l in range(L):
+        assert np.abs(out[l] - g[f"env_out_l{l}"]).max() <= tol
+        assert np.abs(out[l] - g[f"env_torch_l{l}"]).max() <= tol
+    for mine, ref, mag in ((gd, g["env_torch_g_density"], g["env_mag_density"]), (gc, g["env_torch_g_color"], g["env_mag_color"]),
+                           (gd, g["env_g_density"], g["env_mag_density"]), (gc, g["env_g_color"], g["env_mag_color"])):
+        assert np.all(np.abs(mine - ref) <= _grad_tolerance(mag, env))
