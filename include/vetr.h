@@ -319,6 +319,20 @@ int vetr_envmap_backward(vetr_ctx* ctx, const vetr_cameras* cameras, const vetr_
                          const vetr_envmap* env, const float* const* weight, const float* const* grad_out, int flags,
                          float* g_density, float* g_color);
 
+/* Drop-out radius of every point: SceneData::ComputeRadius (data/SceneData.cpp:554-597), which the reference runs on the
+ * host (a KD-tree over the whole cloud, one (k+1)-nearest query per point) when a scene is prepared and again whenever
+ * points are added (NeuralScene.cpp:511, 1079; SceneData.cpp:756, 812).  radius[i] = |p_i - p_j| for the k-th nearest other point j, i.e. the
+ * (k+1)-th smallest distance from p_i to the points of the cloud, itself included; with fewer than k+1 points, the distance
+ * to the farthest one.  The value does not depend on how equal distances are ordered, and the squared distance is formed
+ * as (dx dx + dy dy) + dz dz in fp32 without contraction, so results are bit-equal to an all-pairs evaluation.
+ *   position  n points, `position_stride` floats apart (4 for t_position [N,4]); finite coordinates
+ *   radius    written at radius[i * radius_stride] (position + 3 with stride 4 writes t_position's radius column in place)
+ *   k         1..16 (the reference uses 4)
+ * The call bins the points into a uniform grid whose cell size it picks from the cloud (a few host round trips of a few
+ * bytes each), so it synchronises the context's stream; its scratch (16 bytes per point and 8 bytes per grid cell, at
+ * most 64 Mi cells) is allocated inside the context and reused by later calls. */
+int vetr_knn_radius(vetr_ctx* ctx, const float* position, int position_stride, int n, int k, float* radius, int radius_stride);
+
 /* L1 loss of an output pyramid against a target pyramid and its gradient, one launch for all levels:
  *   loss = sum_l mean |image_l - target_l| (written to the device scalar `loss`), grad_l = sign(image_l - target_l) / numel_l.
  * No counterpart in the reference's rasterizer: its training loop forms this term with libtorch element-wise operators
@@ -372,6 +386,7 @@ enum
     VETR_T_POINT_BACKWARD, /* per-point pass of the backward step (modes 1 and 2) */
     VETR_T_EXCHANGE,     /* vetr_exchange_finalize */
     VETR_T_ENVMAP,       /* vetr_envmap_forward / vetr_envmap_backward */
+    VETR_T_KNN,          /* vetr_knn_radius */
     VETR_T_N
 };
 int vetr_set_timing(vetr_ctx* ctx, int enable);

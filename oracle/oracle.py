@@ -259,3 +259,15 @@ def envmap_backward(scene, views, num_layers, env, weight, grad_out, flags=0):
     if rc != 0:
         raise ValueError("oracle: invalid arguments")
     return gd, gc, md, mc
+
+
+def knn_radius(xyz, k: int = 4):
+    """SceneData::ComputeRadius on the CPU, all pairs: distance of every point to its k-th nearest other point."""
+    xyz = np.ascontiguousarray(xyz, np.float32)
+    n, stride = xyz.shape
+    out = np.zeros(n, np.float32)
+    f = lib().vo_knn_radius
+    f.restype = C.c_int
+    if f(_ptr(xyz), C.c_int(stride), C.c_int(n), C.c_int(k), _ptr(out)) != 0:
+        raise ValueError("oracle: invalid arguments")
+    return out

@@ -24,6 +24,7 @@
 //   tangent application   src/lib/rendering/PointRenderer.cu:1325-1349
 //   error grid            src/lib/rendering/RenderForward.cu:639-791
 //   environment map       src/lib/rendering/EnvironmentMap.cu:201-287, 378-485, 587-758
+//   drop-out radius       src/lib/data/SceneData.cpp:554-597 (ComputeRadius)
 //
 // PARITY UNPINNED for the camera arithmetic: the reference takes TransformPoint, DivideByZ,
 // distortNormalizedPoint, IntrinsicsPinhole::normalizedToImage/scale, ImageView::distanceFromEdge and
@@ -1522,3 +1523,33 @@ int vo_envmap_backward(const double* poses, const float* intrinsics, const OView
     return 0;
 }
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// SceneData::ComputeRadius (data/SceneData.cpp:554-597): data[i](0) = the distance from point i to the last of its
+// n + 1 nearest points, itself included (a KD-tree query in the reference; here every pair is visited).  The value
+// is the (n + 1)-th smallest of the distances |p_i - p_j| over all j, which does not depend on how ties are
+// ordered.  With fewer than n + 1 points it is the distance to the farthest one.
+extern "C" int vo_knn_radius(const float* position, int stride, int n_points, int k, float* radius)
+{
+    if (!position || !radius || n_points < 0 || k < 1 || stride < 3) return -1;
+#pragma omp parallel
+    {
+        std::vector<float> d2((size_t)n_points);
+#pragma omp for schedule(static)
+        for (int i = 0; i < n_points; ++i)
+        {
+            const float* a = position + (int64_t)i * stride;
+            for (int j = 0; j < n_points; ++j)
+            {
+                const float* b = position + (int64_t)j * stride;
+                const float dx = a[0] - b[0], dy = a[1] - b[1], dz = a[2] - b[2];
+                d2[j] = dx * dx + dy * dy + dz * dz;
+            }
+            const int kth = std::min(k, n_points - 1);
+            std::nth_element(d2.begin(), d2.begin() + kth, d2.end());
+            radius[i] = std::sqrt(d2[kth]);
+        }
+    }
+    return 0;
+}
+

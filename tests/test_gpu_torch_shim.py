@@ -159,3 +159,14 @@ def test_environment_map_sample2(ops):
     sum((o * t(g)).sum() for o, g in zip(out, grads)).backward()
     assert np.all(np.abs(density.grad.cpu().numpy()[0, 0] - rgd) <= E._grad_tolerance(md, env))
     assert np.all(np.abs(color.grad.cpu().numpy()[0] - rgc) <= E._grad_tolerance(mc, env))
+
+
+def test_compute_radius(ops):
+    """SceneData::ComputeRadius through the libtorch surface, against the all-pairs restatement."""
+    import torch
+
+    from oracle import oracle as O
+
+    sc = scenes.config_planar(6000, 64, 64, 50.0, seed=12)
+    r = ops.compute_radius(torch.from_numpy(sc.position).cuda(), 4)
+    np.testing.assert_array_equal(r.cpu().numpy(), O.knn_radius(sc.position[:, :3], 4))

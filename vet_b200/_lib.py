@@ -74,12 +74,12 @@ EXPORTS = [
     "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists", "vetr_set_timing", "vetr_get_timings",
     "vetr_launch_count", "vetr_scan_counts_static", "vetr_exchange_raw_floats", "vetr_exchange_out_floats",
     "vetr_exchange_finalize", "vetr_grid_loss", "vetr_l1_loss_grad", "vetr_backward_phase", "vetr_exchange_finalize_part",
-    "vetr_envmap_forward", "vetr_envmap_backward",
+    "vetr_envmap_forward", "vetr_envmap_backward", "vetr_knn_radius",
 ]
 ENV_ADD, ENV_NOT_AT_POINTS, ENV_DEPTH_TEST_WEIGHT, ENV_NO_DISTORTION_CHECK = 1, 2, 4, 8
 BACKWARD_FRAGMENTS, BACKWARD_POINTS = 1, 2
 SEG_DESC, SEG_POINTS, SEG_CONF = 1, 2, 4
-TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize", "point_backward", "exchange", "envmap"]
+TIMING_NAMES = ["count", "scan", "collect", "sort_blend", "backward", "finalize", "point_backward", "exchange", "envmap", "knn"]
 
 _lib = None
 
@@ -139,5 +139,6 @@ def lib():
         L.vetr_envmap_forward.argtypes = [vp, C.POINTER(Cameras), C.POINTER(View), C.c_int, C.c_int, C.POINTER(EnvMap), vp, vp, C.c_int]
         L.vetr_envmap_backward.argtypes = [vp, C.POINTER(Cameras), C.POINTER(View), C.c_int, C.c_int, C.POINTER(EnvMap), vp, vp,
                                            C.c_int, vp, vp]
+        L.vetr_knn_radius.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, vp, C.c_int]
         _lib = L
     return _lib

@@ -2573,6 +2573,7 @@ __global__ void __launch_bounds__(256) l1_loss_grad_kernel(const __grid_constant
 }  // namespace vetr
 
 #include "vetr_envmap.cuh"
+#include "vetr_knn.cuh"
 
 // =========================================================================================================
 // C ABI
@@ -2589,6 +2590,15 @@ struct vetr_ctx
     long long tile_cap   = 0;
     int2* grid_queue     = nullptr;  // (cell, chunk) queue of vetr_grid_loss, allocated by its first call
     int* grid_queue_count = nullptr;
+    // scratch of vetr_knn_radius, grown on demand: per point (sorted copy, cell, queue) and per cell (starts, ends)
+    float4* knn_sorted   = nullptr;
+    int* knn_point_cell  = nullptr;
+    int* knn_queue       = nullptr;
+    long long knn_cap_points = 0;
+    int* knn_starts      = nullptr;
+    int* knn_ends        = nullptr;
+    long long knn_cap_cells = 0;
+    int* knn_tile_sums   = nullptr;  // 16384 tile sums, then 16 words: bounds[6], occupied (64 bit), queue count
     int blend_ctas_per_sm = 1, back_ctas_per_sm = 1, fuzzy_ctas_per_sm = 1, bilinear_ctas_per_sm = 1;
     long long launches   = 0;
     bool timing          = false;
@@ -2753,6 +2763,8 @@ extern "C" void vetr_destroy(vetr_ctx* ctx)
     cudaSetDevice(ctx->device);
     if (ctx->tile_sums) cudaFree(ctx->tile_sums);
     if (ctx->grid_queue) cudaFree(ctx->grid_queue);
+    cudaFree(ctx->knn_sorted), cudaFree(ctx->knn_point_cell), cudaFree(ctx->knn_queue);
+    cudaFree(ctx->knn_starts), cudaFree(ctx->knn_ends), cudaFree(ctx->knn_tile_sums);
     for (int i = 0; i < VETR_T_N; ++i)
         for (int k = 0; k < 2; ++k)
             if (ctx->ev[i][k]) cudaEventDestroy(ctx->ev[i][k]);
@@ -3278,6 +3290,134 @@ extern "C" int vetr_envmap_backward(vetr_ctx* ctx, const vetr_cameras* cams, con
         ctx->launches += 1;
         envmap_backward_kernel<<<(int)std::min<long long>(blocks, (long long)ctx->sm_count * 32), kEnvThreads, 0, ctx->stream>>>(a);
     }
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+template <int KMAX>
+static void knn_launch_search(vetr_ctx* ctx, const KnnSearch& a)
+{
+    knn_near_kernel<KMAX><<<(a.n + 127) / 128, 128, 0, ctx->stream>>>(a);
+    knn_far_kernel<KMAX><<<ctx->sm_count * 8, 128, 0, ctx->stream>>>(a);
+}
+
+extern "C" int vetr_knn_radius(vetr_ctx* ctx, const float* position, int position_stride, int n, int k, float* radius, int radius_stride)
+{
+    if (!ctx || n < 0 || k < 1 || k > kKnnMaxK || position_stride < 3 || radius_stride < 1) return VETR_E_INVALID_ARG;
+    if (n == 0) return VETR_OK;
+    if (!position || !radius) return VETR_E_INVALID_ARG;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    PassScope scope(ctx, VETR_T_KNN, 0);
+    cudaStream_t st = ctx->stream;
+    if (n > ctx->knn_cap_points)
+    {
+        cudaFree(ctx->knn_sorted), cudaFree(ctx->knn_point_cell), cudaFree(ctx->knn_queue);
+        ctx->knn_sorted = nullptr, ctx->knn_point_cell = nullptr, ctx->knn_queue = nullptr, ctx->knn_cap_points = 0;
+        VETR_CUDA(ctx, cudaMalloc(&ctx->knn_sorted, (size_t)n * sizeof(float4)));
+        VETR_CUDA(ctx, cudaMalloc(&ctx->knn_point_cell, (size_t)n * sizeof(int)));
+        VETR_CUDA(ctx, cudaMalloc(&ctx->knn_queue, (size_t)n * sizeof(int)));
+        ctx->knn_cap_points = n;
+    }
+    if (!ctx->knn_tile_sums) VETR_CUDA(ctx, cudaMalloc(&ctx->knn_tile_sums, (16384 + 16) * sizeof(int)));
+    unsigned* d_bounds          = reinterpret_cast<unsigned*>(ctx->knn_tile_sums + 16384);
+    unsigned long long* d_occ   = reinterpret_cast<unsigned long long*>(ctx->knn_tile_sums + 16384 + 8);
+    int* d_queue_count          = ctx->knn_tile_sums + 16384 + 10;
+
+    // bounding box
+    const unsigned init[6] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0u, 0u, 0u};
+    unsigned keys[6];
+    VETR_CUDA(ctx, cudaMemcpyAsync(d_bounds, init, sizeof(init), cudaMemcpyHostToDevice, st));
+    const int sweep = std::min((n + 255) / 256, ctx->sm_count * 8);
+    knn_bounds_kernel<<<sweep, 256, 0, st>>>(position, position_stride, n, d_bounds);
+    VETR_CUDA(ctx, cudaMemcpyAsync(keys, d_bounds, sizeof(keys), cudaMemcpyDeviceToHost, st));
+    VETR_CUDA(ctx, cudaStreamSynchronize(st));
+    float lo[3], hi[3], ext = 0.f, maxabs = 0.f;
+    for (int a = 0; a < 3; ++a)
+    {
+        lo[a] = knn_unkey(keys[a]), hi[a] = knn_unkey(keys[3 + a]);
+        if (!(lo[a] <= hi[a]) || std::isinf(lo[a]) || std::isinf(hi[a])) return VETR_E_INVALID_ARG;  // NaN or infinite coordinates
+        ext    = std::max(ext, hi[a] - lo[a]);
+        maxabs = std::max(maxabs, std::max(std::fabs(lo[a]), std::fabs(hi[a])));
+    }
+
+    // cell size: halve from 1/32 of the longest extent until an occupied cell holds 8 points or fewer on average
+    KnnGrid g;
+    g.ox = lo[0], g.oy = lo[1], g.oz = lo[2];
+    auto dims_for = [&](float cell, int d[3]) -> long long
+    {
+        long long cells = 1;
+        for (int a = 0; a < 3; ++a)
+        {
+            const double c = std::floor((double)(hi[a] - lo[a]) / cell) + 1.0;
+            d[a] = (int)std::min(c, 1.0e9);
+            cells = cells > (1ll << 40) ? cells : cells * d[a];
+        }
+        return cells;
+    };
+    float cell = ext > 0.f ? ext / 32.f : 1.f;
+    int d[3];
+    long long cells = dims_for(cell, d);
+    for (int iter = 0; iter < 24 && ext > 0.f; ++iter)
+    {
+        if (cells > ctx->knn_cap_cells)
+        {
+            cudaFree(ctx->knn_starts), cudaFree(ctx->knn_ends);
+            ctx->knn_starts = nullptr, ctx->knn_ends = nullptr, ctx->knn_cap_cells = 0;
+            const long long cap = std::min(kKnnMaxCells, std::max(cells * 8, 1ll << 20));
+            VETR_CUDA(ctx, cudaMalloc(&ctx->knn_starts, (size_t)cap * sizeof(int)));
+            VETR_CUDA(ctx, cudaMalloc(&ctx->knn_ends, (size_t)cap * sizeof(int)));
+            ctx->knn_cap_cells = cap;
+        }
+        g.cell = cell, g.inv_cell = 1.f / cell, g.nx = d[0], g.ny = d[1], g.nz = d[2];
+        VETR_CUDA(ctx, cudaMemsetAsync(ctx->knn_starts, 0, (size_t)cells * sizeof(int), st));
+        VETR_CUDA(ctx, cudaMemsetAsync(d_occ, 0, sizeof(unsigned long long), st));
+        knn_count_kernel<<<sweep, 256, 0, st>>>(position, position_stride, n, g, ctx->knn_starts, nullptr);
+        knn_occupied_kernel<<<(int)std::min<long long>((cells + 255) / 256, ctx->sm_count * 16), 256, 0, st>>>(ctx->knn_starts, cells, d_occ);
+        unsigned long long occupied = 0;
+        VETR_CUDA(ctx, cudaMemcpyAsync(&occupied, d_occ, sizeof(occupied), cudaMemcpyDeviceToHost, st));
+        VETR_CUDA(ctx, cudaStreamSynchronize(st));
+        ctx->launches += 2;
+        if (occupied == 0 || (double)n / (double)occupied <= 8.0) break;
+        int d2[3];
+        const long long finer = dims_for(cell * 0.5f, d2);
+        if (finer > kKnnMaxCells) break;
+        cell *= 0.5f, cells = finer;
+        d[0] = d2[0], d[1] = d2[1], d[2] = d2[2];
+    }
+    if (cells > ctx->knn_cap_cells)  // only when all points coincide (no iteration ran)
+    {
+        cudaFree(ctx->knn_starts), cudaFree(ctx->knn_ends);
+        ctx->knn_starts = nullptr, ctx->knn_ends = nullptr, ctx->knn_cap_cells = 0;
+        VETR_CUDA(ctx, cudaMalloc(&ctx->knn_starts, (size_t)(1ll << 20) * sizeof(int)));
+        VETR_CUDA(ctx, cudaMalloc(&ctx->knn_ends, (size_t)(1ll << 20) * sizeof(int)));
+        ctx->knn_cap_cells = 1ll << 20;
+    }
+    g.cell = cell, g.inv_cell = 1.f / cell, g.nx = d[0], g.ny = d[1], g.nz = d[2];
+
+    // counting sort into the chosen grid
+    const int n_tiles = (int)((cells + kKnnScanTile - 1) / kKnnScanTile);
+    VETR_CUDA(ctx, cudaMemsetAsync(ctx->knn_starts, 0, (size_t)cells * sizeof(int), st));
+    VETR_CUDA(ctx, cudaMemsetAsync(d_queue_count, 0, sizeof(int), st));
+    knn_count_kernel<<<sweep, 256, 0, st>>>(position, position_stride, n, g, ctx->knn_starts, ctx->knn_point_cell);
+    knn_tile_sums_kernel<<<n_tiles, 256, 0, st>>>(ctx->knn_starts, cells, ctx->knn_tile_sums);
+    knn_spine_kernel<<<1, 1024, 0, st>>>(ctx->knn_tile_sums, n_tiles);
+    knn_apply_kernel<<<n_tiles, 256, 0, st>>>(ctx->knn_starts, cells, ctx->knn_tile_sums, ctx->knn_starts);
+    VETR_CUDA(ctx, cudaMemcpyAsync(ctx->knn_ends, ctx->knn_starts, (size_t)cells * sizeof(int), cudaMemcpyDeviceToDevice, st));
+    knn_scatter_kernel<<<sweep, 256, 0, st>>>(position, position_stride, n, ctx->knn_point_cell, ctx->knn_ends, ctx->knn_sorted);
+
+    // search
+    KnnSearch a;
+    a.g = g, a.sorted = ctx->knn_sorted, a.starts = ctx->knn_starts, a.ends = ctx->knn_ends, a.n = n;
+    const int k1 = std::min(k, n - 1) + 1;  // list entries that count: the point itself and its k nearest
+    a.slack = 1e-3f * cell + 4e-6f * (maxabs + ext);
+    a.radius = radius, a.radius_stride = radius_stride, a.queue = ctx->knn_queue, a.queue_count = d_queue_count;
+    if (k1 <= 5)
+        a.dummies = 5 - k1, knn_launch_search<5>(ctx, a);
+    else if (k1 <= 9)
+        a.dummies = 9 - k1, knn_launch_search<9>(ctx, a);
+    else
+        a.dummies = 17 - k1, knn_launch_search<17>(ctx, a);
+    ctx->launches += 8;
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }

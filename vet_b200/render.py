@@ -333,6 +333,24 @@ class Rasterizer:
         self._check(rc, "vetr_envmap_backward")
         return g_density, g_color
 
+    def knn_radius(self, position, k: int = 4, out=None):
+        """SceneData::ComputeRadius (data/SceneData.cpp:554-597): distance of every point to its k-th nearest other point.
+        position: CUDA float32 [n,3] or [n,4].  out: None (a new [n] tensor is returned), or the string "w" to write the
+        radius column of a [n,4] position tensor in place (t_position's layout).  Synchronises the stream."""
+        assert position.dtype == torch.float32 and position.is_contiguous() and position.dim() == 2 and position.shape[1] in (3, 4)
+        self._sync_stream()
+        n, stride = position.shape
+        if isinstance(out, str):
+            assert out == "w" and stride == 4
+            rc = L.lib().vetr_knn_radius(self._ctx, position.data_ptr(), 4, n, k, position.data_ptr() + 12, 4)
+            self._check(rc, "vetr_knn_radius")
+            return position
+        if out is None:
+            out = torch.empty(n, dtype=torch.float32, device=position.device)
+        rc = L.lib().vetr_knn_radius(self._ctx, position.data_ptr(), stride, n, k, out.data_ptr(), 1)
+        self._check(rc, "vetr_knn_radius")
+        return out
+
     def l1_loss_grad(self, images, targets, grads, loss):
         """loss (device scalar) = sum over levels of mean |image - target|; grads[l] = sign(image - target) / numel, one launch."""
         self._sync_stream()

@@ -342,6 +342,26 @@ variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_out
 }  // namespace torch::autograd
 
 // ---------------------------------------------------------------------------------------------------------
+// Drop-out radius
+
+namespace vetr_torch
+{
+torch::Tensor ComputeRadius(torch::Tensor position, int n)
+{
+    TORCH_CHECK(position.is_cuda() && position.dtype() == torch::kFloat32 && position.dim() == 2 &&
+                    (position.size(1) == 3 || position.size(1) == 4),
+                "ComputeRadius: position must be a CUDA float tensor [N,3] or [N,4]");
+    static PointRendererCache cache;  // owns the context and its grid scratch
+    c10::cuda::CUDAGuard guard(position.device());
+    vetr_ctx* vc = cache.context(position.device().index());
+    torch::Tensor p = position.contiguous();
+    torch::Tensor r = torch::empty({p.size(0)}, p.options());
+    check(vetr_knn_radius(vc, p.data_ptr<float>(), (int)p.size(1), (int)p.size(0), n, r.data_ptr<float>(), 1), "vetr_knn_radius");
+    return r;
+}
+}  // namespace vetr_torch
+
+// ---------------------------------------------------------------------------------------------------------
 // Environment map
 
 namespace vetr_torch
@@ -579,6 +599,7 @@ TORCH_LIBRARY(vetr, m)
     m.def("fill_scene_grid_with_loss", &fill_scene_grid_with_loss_op);
     m.class_<vetr_torch::EnvironmentSampleState>("EnvironmentSampleState").def(torch::init());
     m.def("environment_map_sample2", &environment_map_sample2_op);
+    m.def("compute_radius", [](torch::Tensor position, int64_t n) { return vetr_torch::ComputeRadius(position, (int)n); });
     m.class_<vetr_torch::NeuralRenderInfo>("NeuralRenderInfo").def(torch::init());
     m.def("blend_point_cloud", &blend_point_cloud_op);
     m.def("apply_tangent_to_pose", &vetr_torch::ApplyTangentToPose);

@@ -9,6 +9,7 @@
 //                                         layers_cuda[i].weight / .depth, num_batches, render_mode)
 //   PointRendererCache::FillSceneGridWithLoss   rendering/PointRenderer.h:152, RenderForward.cu:761-791
 //   EnvironmentMapImpl (constructor, density, color, Sample2)   rendering/EnvironmentMap.h:252-301
+//   SceneData::ComputeRadius(point_cloud, n)   data/SceneData.h:396
 // The reference's NeuralScene / RenderParams / ReducedImageInfo come from parts of VET that need the saiga library;
 // the structs below carry exactly the fields the render operator reads from them, under the same names, so that the
 // reference's call site (models/Pipeline.cpp:133 via RenderModule.cpp:45-245) maps onto them one to one.
@@ -131,6 +132,10 @@ class NeuralRenderInfo : public torch::CustomClassHolder
 std::vector<torch::Tensor> BlendPointCloud(NeuralRenderInfo* info);
 
 void ApplyTangentToPose(torch::Tensor tangent, torch::Tensor pose);
+
+// SceneData::ComputeRadius (data/SceneData.h:396, SceneData.cpp:554-597) for a cloud that already lives on the GPU:
+// position [N,3] or [N,4] float CUDA tensor -> [N] distances to the n-th nearest other point (the reference's data[i](0)).
+torch::Tensor ComputeRadius(torch::Tensor position, int n = 4);
 
 // What one Sample2 call hands to its autograd node.
 struct EnvironmentSampleState : public torch::CustomClassHolder
