@@ -302,8 +302,8 @@ __global__ void __launch_bounds__(128) knn_near_kernel(const __grid_constant__ K
         a.queue[atomicAdd(a.queue_count, 1)] = i;
 }
 
-// Second pass: one warp per queued point.  Ring r adds the shell of the cube [c - r, c + r]^3; the (2r+1)^2 rows
-// (y, z) of the cube are dealt to the lanes: a row on the shell's y or z face contributes all its cells (contiguous slots),
+// Second pass: one warp per queued point.  Ring r adds the shell of the cube [c - r, c + r]^3; the rows (y, z) of the
+// cube that lie inside the grid are dealt to the lanes: a row on the shell's y or z face contributes all its cells (contiguous slots),
 // any other row its two end cells.  After each ring the lanes' lists are merged into the k+1 smallest overall.
 template <int KMAX>
 __global__ void __launch_bounds__(128) knn_far_kernel(const __grid_constant__ KnnSearch a)
@@ -321,15 +321,15 @@ __global__ void __launch_bounds__(128) knn_far_kernel(const __grid_constant__ Kn
         const int r_max = max(max(max(cx, a.g.nx - 1 - cx), max(cy, a.g.ny - 1 - cy)), max(cz, a.g.nz - 1 - cz));
         for (int r = 1;; ++r)
         {
-            const int side = 2 * r + 1;
-            for (int t = lane; t < side * side; t += 32)
+            // rows (y, z) of the cube that lie inside the grid
+            const int ylo = max(cy - r, 0), yhi = min(cy + r, a.g.ny - 1), zlo = max(cz - r, 0), zhi = min(cz + r, a.g.nz - 1);
+            const int wz = zhi - zlo + 1, rows = (yhi - ylo + 1) * wz;  // <= ny nz <= 2^26
+            const int x0 = cx - r, x1 = cx + r;
+            for (int t = lane; t < rows; t += 32)
             {
-                const int dy = t / side - r, dz = t % side - r;
-                const int y = cy + dy, z = cz + dz;
-                if (y < 0 || y >= a.g.ny || z < 0 || z >= a.g.nz) continue;
+                const int y = ylo + t / wz, z = zlo + t % wz;
                 const int row = (z * a.g.ny + y) * a.g.nx;
-                const int x0 = cx - r, x1 = cx + r;
-                if (r == 1 || abs(dy) == r || abs(dz) == r)  // the first cube is taken whole
+                if (r == 1 || abs(y - cy) == r || abs(z - cz) == r)  // the first cube is taken whole
                     knn_scan_slots<KMAX>(a, a.starts[row + max(x0, 0)], a.ends[row + min(x1, a.g.nx - 1)], p.x, p.y, p.z, best);
                 else
                 {
