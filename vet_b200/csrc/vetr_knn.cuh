@@ -4,7 +4,7 @@
 // the cells around its own in growing cubes until the k-th nearest distance found so far is smaller than the distance to
 // the cube's faces, beyond which nothing has been looked at.  Most points end after the first cube of 3 x 3 x 3 cells,
 // with one thread per point; the rest (isolated points, whose cubes grow to tens of cells a side) go to a queue and are
-// finished by one warp per point, whose lanes split the shell of each cube.
+// finished by one warp per point, whose lanes split the rows of a cube that grows by half from stage to stage.
 //
 // The result is the (k+1)-th smallest of a multiset of fp32 squared distances, each formed as (dx dx + dy dy) + dz dz
 // without contraction, so it does not depend on the order in which candidates are met and is bit-equal to an all-pairs
@@ -302,9 +302,11 @@ __global__ void __launch_bounds__(128) knn_near_kernel(const __grid_constant__ K
         a.queue[atomicAdd(a.queue_count, 1)] = i;
 }
 
-// Second pass: one warp per queued point.  Ring r adds the shell of the cube [c - r, c + r]^3; the rows (y, z) of the
-// cube that lie inside the grid are dealt to the lanes: a row on the shell's y or z face contributes all its cells (contiguous slots),
-// any other row its two end cells.  After each ring the lanes' lists are merged into the k+1 smallest overall.
+// Second pass: one warp per queued point.  The cube [c - R, c + R]^3 grows its half-width R by half from stage to stage.  The
+// rows (y, z) of the cube that lie inside the grid are dealt to the lanes; the cells of a row are consecutive in the sorted
+// array, so a row costs one or two range look-ups whatever its length: the whole row if it lies outside the previous
+// cube, else the two pieces left and right of it.  After each stage the lanes' lists are merged into the k+1 smallest
+// overall and the stopping rule is applied to the cube's faces.
 template <int KMAX>
 __global__ void __launch_bounds__(128) knn_far_kernel(const __grid_constant__ KnnSearch a)
 {
@@ -319,22 +321,23 @@ __global__ void __launch_bounds__(128) knn_far_kernel(const __grid_constant__ Kn
 #pragma unroll
         for (int j = 0; j < KMAX; ++j) best[j] = (lane == 0 && j < a.dummies) ? -CUDART_INF_F : CUDART_INF_F;
         const int r_max = max(max(max(cx, a.g.nx - 1 - cx), max(cy, a.g.ny - 1 - cy)), max(cz, a.g.nz - 1 - cz));
-        for (int r = 1;; ++r)
+        int r_prev = -1;  // half-width of the cube already visited (-1: nothing yet)
+        for (int r = 1;; r = min(r + max(r / 2, 1), max(r_max, 1)))  // 1, 2, 3, 4, 6, 9, 13, ...
         {
-            // rows (y, z) of the cube that lie inside the grid
             const int ylo = max(cy - r, 0), yhi = min(cy + r, a.g.ny - 1), zlo = max(cz - r, 0), zhi = min(cz + r, a.g.nz - 1);
             const int wz = zhi - zlo + 1, rows = (yhi - ylo + 1) * wz;  // <= ny nz <= 2^26
-            const int x0 = cx - r, x1 = cx + r;
+            const int x0 = max(cx - r, 0), x1 = min(cx + r, a.g.nx - 1);
             for (int t = lane; t < rows; t += 32)
             {
                 const int y = ylo + t / wz, z = zlo + t % wz;
                 const int row = (z * a.g.ny + y) * a.g.nx;
-                if (r == 1 || abs(y - cy) == r || abs(z - cz) == r)  // the first cube is taken whole
-                    knn_scan_slots<KMAX>(a, a.starts[row + max(x0, 0)], a.ends[row + min(x1, a.g.nx - 1)], p.x, p.y, p.z, best);
+                if (abs(y - cy) > r_prev || abs(z - cz) > r_prev)
+                    knn_scan_slots<KMAX>(a, a.starts[row + x0], a.ends[row + x1], p.x, p.y, p.z, best);
                 else
                 {
-                    if (x0 >= 0) knn_scan_slots<KMAX>(a, a.starts[row + x0], a.ends[row + x0], p.x, p.y, p.z, best);
-                    if (x1 < a.g.nx) knn_scan_slots<KMAX>(a, a.starts[row + x1], a.ends[row + x1], p.x, p.y, p.z, best);
+                    const int left = cx - r_prev - 1, right = cx + r_prev + 1;  // the cells next to the visited piece
+                    if (left >= x0) knn_scan_slots<KMAX>(a, a.starts[row + x0], a.ends[row + left], p.x, p.y, p.z, best);
+                    if (right <= x1) knn_scan_slots<KMAX>(a, a.starts[row + right], a.ends[row + x1], p.x, p.y, p.z, best);
                 }
             }
             // merge: KMAX times, take the smallest head of all lanes
@@ -361,6 +364,7 @@ __global__ void __launch_bounds__(128) knn_far_kernel(const __grid_constant__ Kn
                 if (lane == 0) a.radius[(size_t)__float_as_int(p.w) * a.radius_stride] = sqrtf(kth);
                 break;
             }
+            r_prev = r;
         }
     }
 }
