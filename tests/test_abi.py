@@ -50,6 +50,8 @@ def test_struct_sizes_match_the_header():
     assert C.sizeof(L.View) == 56
     assert C.sizeof(L.Cloud) == 24 and C.sizeof(L.Texture) == 32 and C.sizeof(L.Cameras) == 24
     assert C.sizeof(L.Lists) == 80
+    assert C.sizeof(L.EnvMap) == 72  # two pointers, eight radii, five ints, padded to the pointer size
+    assert C.sizeof(L.Exchange) == 8 + 2 * 8 * L.MAX_RANKS + 16
 
 
 def test_create_without_gpu_reports_cuda_error():
