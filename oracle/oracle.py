@@ -245,6 +245,17 @@ def envmap_uvz(scene, view, level, env):
     return uvz, hit
 
 
+def envmap_rays(scene, view, level):
+    """World-space ray origin and direction [h_l*w_l, 3] of every pixel of one view and level."""
+    w, h = view.w >> level, view.h >> level
+    o = np.zeros((h * w, 3), np.float32)
+    d = np.zeros((h * w, 3), np.float32)
+    f = lib().vo_envmap_rays
+    f.restype = C.c_int
+    f(_ptr(scene.poses), _ptr(scene.intrinsics), C.byref(_oviews([view])[0]), C.c_int(level), _ptr(o), _ptr(d))
+    return o, d
+
+
 def envmap_backward(scene, views, num_layers, env, weight, grad_out, flags=0):
     """Returns (g_density [S,R,R], g_color [C,S,R,R], mag_density, mag_color); the mag arrays are the sums of the
     absolute addends of every element."""

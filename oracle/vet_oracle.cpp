@@ -1449,6 +1449,26 @@ int vo_envmap_uvz(const double* poses, const float* intrinsics, const OView* vie
     return 0;
 }
 
+// World-space rays of one view and level (BuildSphericalRayList): origin, direction [h_l*w_l, 3].  For the test that
+// ties the ray construction to the rasterizer's projection: a point on the ray of a pixel must be drawn into that pixel.
+int vo_envmap_rays(const double* poses, const float* intrinsics, const OView* view, int level, float* origin, float* direction)
+{
+    int lw = view->w, lh = view->h;
+    float scale = 1.f;
+    for (int l = 0; l < level; ++l) lw /= 2, lh /= 2, scale *= 0.5f;
+    const Pose V      = load_pose(poses + 8 * (int64_t)view->image_index);
+    const float* intr = intrinsics + 13 * (int64_t)view->camera_index;
+    for (int y = 0; y < lh; ++y)
+        for (int x = 0; x < lw; ++x)
+        {
+            const EnvRay ray = env_ray(V, intr, *view, lw, lh, scale, x, y);
+            const int64_t i  = (int64_t)y * lw + x;
+            origin[3 * i] = ray.o.x, origin[3 * i + 1] = ray.o.y, origin[3 * i + 2] = ray.o.z;
+            direction[3 * i] = ray.d.x, direction[3 * i + 1] = ray.d.y, direction[3 * i + 2] = ray.d.z;
+        }
+    return 0;
+}
+
 // Gradients of density [S,R,R] and color [C,S,R,R], added to g_density / g_color; sums are formed in double.
 // mag_density / mag_color (optional): the sums of the absolute addends, for the tests' tolerance.
 int vo_envmap_backward(const double* poses, const float* intrinsics, const OView* views, int n_views, int L,

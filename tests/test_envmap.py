@@ -98,6 +98,31 @@ def test_sample_coordinates_against_float64():
                 assert np.allclose(uvz[s, :, 2][m], 2 * s / (env.n_spheres - 1) - 1, atol=1e-6)
 
 
+def test_rays_invert_the_rasterizer_projection():
+    """The two halves of a VET image must register: a point placed on the environment-map ray of pixel (x, y) of level l
+    is drawn by the rasterizer into exactly that pixel of that level.  Ties the restated unproject2 / SE3 inverse / inverse
+    crop rotation to the restated projection, with crop transform, crop rotation and skew-free intrinsics."""
+    sc = scenes.tiny_scene(n=4, w=64, h=48, n_views=2, seed=31, crop=True)
+    rng = np.random.default_rng(4)
+    L = 3
+    for b, view in enumerate(sc.views):
+        for level in range(L):
+            w, h = view.w >> level, view.h >> level
+            o, d = O.envmap_rays(sc, view, level)
+            pick = rng.choice(w * h, size=25, replace=False)
+            t = rng.uniform(2.0, 6.0, size=(25, 1)).astype(np.float32)
+            pts = o[pick] + t * d[pick]
+            cloud = scenes.Scene(position=np.concatenate([pts, np.full((25, 1), 10.0, np.float32)], 1).astype(np.float32),
+                                 index=np.arange(25, dtype=np.int32), texture=np.ones((4, 25), np.float32),
+                                 confidence=np.full(25, 0.5, np.float32), background=np.zeros(4, np.float32),
+                                 poses=sc.poses, intrinsics=sc.intrinsics, views=sc.views)
+            res = O.Oracle().forward(cloud, O.default_params(num_layers=L), views=[view])
+            drawn = res["depth"][level][0, 0] < 1000.0  # 100000 where nothing was drawn
+            ys, xs = pick // w, pick % w
+            assert drawn[ys, xs].all(), (b, level, int((~drawn[ys, xs]).sum()))
+            assert drawn.sum() == 25  # and nowhere else on that level
+
+
 def _torch_forward_mps5(env, uvz, hit, T0, density_t, color_t):
     """forward_mps5 (EnvironmentMap.cu:692-758) with libtorch's operators on given sample coordinates."""
     S, n = uvz.shape[0], uvz.shape[1]
