@@ -333,6 +333,24 @@ int vetr_envmap_backward(vetr_ctx* ctx, const vetr_cameras* cameras, const vetr_
  * most 64 Mi cells) is allocated inside the context and reused by later calls. */
 int vetr_knn_radius(vetr_ctx* ctx, const float* position, int position_stride, int n, int k, float* radius, int radius_stride);
 
+/* Removing points: NeuralScene::RemovePoints (data/NeuralScene.cpp:1156-1239) without the host round trip.  The reference
+ * sorts the indices to remove, forms the complementary keep list in a host loop, rebuilds the cloud through a CPU mesh and
+ * index_selects every per-point tensor with the keep list (texture and confidence, NeuralTexture.cpp:160-173; the Adam
+ * moments, my_adam.cpp:107-135).  Here the plan call flags the removed points and scans the flags, and one gather call per
+ * group of tensors copies the survivors in their old order: dst[r, new_index[i], :] = src[r, i, :].
+ *   remove     m device int64 indices (the reference's index dtype), duplicates allowed; an index outside [0, n) returns
+ *              VETR_E_INVALID_ARG
+ *   new_index  [n] device int32, written: the index of point i after the removal, or -1
+ *   n_kept     host int, written (the call synchronises the stream to read it): the caller sizes the destinations with it */
+int vetr_remove_points_plan(vetr_ctx* ctx, int n, const int64_t* remove, int m, int32_t* new_index, int* n_kept);
+typedef struct vetr_point_array
+{
+    const void* src; /* [rows, n, width] elements of four bytes (float or int32) */
+    void*       dst; /* [rows, n_kept, width]; must not overlap src */
+    int32_t     rows, width; /* t_position [N,4]: rows 1, width 4 (16-byte aligned); texture [C,N]: rows C, width 1 */
+} vetr_point_array;
+int vetr_gather_points(vetr_ctx* ctx, int n, int n_kept, const int32_t* new_index, const vetr_point_array* arrays, int n_arrays);
+
 /* L1 loss of an output pyramid against a target pyramid and its gradient, one launch for all levels:
  *   loss = sum_l mean |image_l - target_l| (written to the device scalar `loss`), grad_l = sign(image_l - target_l) / numel_l.
  * No counterpart in the reference's rasterizer: its training loop forms this term with libtorch element-wise operators

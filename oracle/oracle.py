@@ -282,3 +282,23 @@ def knn_radius(xyz, k: int = 4):
     if f(_ptr(xyz), C.c_int(stride), C.c_int(n), C.c_int(k), _ptr(out)) != 0:
         raise ValueError("oracle: invalid arguments")
     return out
+
+
+def remove_points(n: int, remove, point_last=(), point_first=()):
+    """NeuralScene::RemovePoints (data/NeuralScene.cpp:1156-1239) as the reference does it on the host: sort the indices,
+    walk the points once to list the ones to keep (:1169-1181), index_select every per-point tensor with that list
+    (NeuralTexture.cpp:160-173, my_adam.cpp:107-135).  Returns (new_index [n] int32, shrunken point_last, point_first)."""
+    indices = sorted(int(i) for i in remove)
+    keep, it = [], 0
+    for i in range(n):
+        while it < len(indices) and indices[it] < i:   # duplicates and indices already passed
+            it += 1
+        if it < len(indices) and indices[it] == i:
+            it += 1
+        else:
+            keep.append(i)
+    keep = np.asarray(keep, np.int64)
+    new_index = np.full(n, -1, np.int32)
+    new_index[keep] = np.arange(len(keep), dtype=np.int32)
+    return (new_index, [np.ascontiguousarray(np.take(a, keep, axis=-1)) for a in point_last],
+            [np.ascontiguousarray(np.take(a, keep, axis=0)) for a in point_first])

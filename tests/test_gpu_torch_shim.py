@@ -170,3 +170,22 @@ def test_compute_radius(ops):
     sc = scenes.config_planar(6000, 64, 64, 50.0, seed=12)
     r = ops.compute_radius(torch.from_numpy(sc.position).cuda(), 4)
     np.testing.assert_array_equal(r.cpu().numpy(), O.knn_radius(sc.position[:, :3], 4))
+
+
+def test_remove_points_in_place(ops):
+    """NeuralScene::RemovePoints through the libtorch surface: the scene's tensors and the optimizer moments shrink in place."""
+    import torch
+
+    from oracle import oracle as O
+    from tests.test_remove_points import _case
+
+    n = 3000
+    remove, (texture, conf, moments), (position, index) = _case(np.random.default_rng(5), n, 400)
+    _, ref_last, ref_first = O.remove_points(n, remove, [texture, conf, moments], [position])
+    t = lambda a: torch.from_numpy(a).cuda()
+    g_tex, g_conf, g_pos, g_idx, g_mom = t(texture), t(conf), t(position), t(index), t(moments)
+    kept = ops.remove_points(g_tex, g_conf, g_pos, g_idx, torch.from_numpy(remove), [g_mom])
+    assert kept == ref_first[0].shape[0] and tuple(g_tex.shape) == (4, kept) and tuple(g_mom.shape) == (2, 4, kept)
+    for g, r in zip((g_tex, g_conf, g_mom, g_pos), ref_last + ref_first):
+        np.testing.assert_array_equal(g.cpu().numpy(), r)
+    np.testing.assert_array_equal(g_idx.cpu().numpy()[:, 0], np.arange(kept))

@@ -58,6 +58,10 @@ MAX_RANKS = 16
 PIXEL_BAND = 4  # VETR_PIXEL_BAND: rows per band of the pixel space
 
 
+class PointArray(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("dst", C.c_void_p), ("rows", C.c_int32), ("width", C.c_int32)]
+
+
 class EnvMap(C.Structure):
     _fields_ = [("density", C.c_void_p), ("color", C.c_void_p), ("radii", C.c_float * 8), ("n_spheres", C.c_int32),
                 ("resolution", C.c_int32), ("channels", C.c_int32), ("up_axis", C.c_int32), ("non_subzero_texture", C.c_int32)]
@@ -74,7 +78,7 @@ EXPORTS = [
     "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists", "vetr_set_timing", "vetr_get_timings",
     "vetr_launch_count", "vetr_scan_counts_static", "vetr_exchange_raw_floats", "vetr_exchange_out_floats",
     "vetr_exchange_finalize", "vetr_grid_loss", "vetr_l1_loss_grad", "vetr_backward_phase", "vetr_exchange_finalize_part",
-    "vetr_envmap_forward", "vetr_envmap_backward", "vetr_knn_radius",
+    "vetr_envmap_forward", "vetr_envmap_backward", "vetr_knn_radius", "vetr_remove_points_plan", "vetr_gather_points",
 ]
 ENV_ADD, ENV_NOT_AT_POINTS, ENV_DEPTH_TEST_WEIGHT, ENV_NO_DISTORTION_CHECK = 1, 2, 4, 8
 BACKWARD_FRAGMENTS, BACKWARD_POINTS = 1, 2
@@ -140,5 +144,7 @@ def lib():
         L.vetr_envmap_backward.argtypes = [vp, C.POINTER(Cameras), C.POINTER(View), C.c_int, C.c_int, C.POINTER(EnvMap), vp, vp,
                                            C.c_int, vp, vp]
         L.vetr_knn_radius.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, vp, C.c_int]
+        L.vetr_remove_points_plan.argtypes = [vp, C.c_int, vp, C.c_int, vp, C.POINTER(C.c_int)]
+        L.vetr_gather_points.argtypes = [vp, C.c_int, C.c_int, vp, C.POINTER(PointArray), C.c_int]
         _lib = L
     return _lib

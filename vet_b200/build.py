@@ -14,7 +14,7 @@ import sys
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libvetr.so")
 SOURCES = [os.path.join(_HERE, "csrc", "vetr_kernels.cu")]
-HEADERS = [os.path.join(_HERE, "csrc", "vetr_math.cuh"), os.path.join(_HERE, "csrc", "vetr_envmap.cuh"), os.path.join(_HERE, "csrc", "vetr_knn.cuh"), os.path.join(_HERE, "..", "include", "vetr.h")]
+HEADERS = [os.path.join(_HERE, "csrc", "vetr_math.cuh"), os.path.join(_HERE, "csrc", "vetr_envmap.cuh"), os.path.join(_HERE, "csrc", "vetr_knn.cuh"), os.path.join(_HERE, "csrc", "vetr_points.cuh"), os.path.join(_HERE, "..", "include", "vetr.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
          "-Xcompiler", "-fPIC", "-shared", "-ccbin", "/usr/bin/g++"]

@@ -2574,6 +2574,7 @@ __global__ void __launch_bounds__(256) l1_loss_grad_kernel(const __grid_constant
 
 #include "vetr_envmap.cuh"
 #include "vetr_knn.cuh"
+#include "vetr_points.cuh"
 
 // =========================================================================================================
 // C ABI
@@ -2598,7 +2599,9 @@ struct vetr_ctx
     int* knn_starts      = nullptr;
     int* knn_ends        = nullptr;
     long long knn_cap_cells = 0;
-    int* knn_tile_sums   = nullptr;  // 16384 tile sums, then 16 words: bounds[6], occupied (64 bit), queue count
+    int* knn_tile_sums   = nullptr;  // 16384 tile sums, then 16 words: bounds[6], occupied (64 bit), queue count, 2 of the point removal
+    int* points_flags    = nullptr;  // keep flags of vetr_remove_points_plan
+    long long points_cap = 0;
     int blend_ctas_per_sm = 1, back_ctas_per_sm = 1, fuzzy_ctas_per_sm = 1, bilinear_ctas_per_sm = 1;
     long long launches   = 0;
     bool timing          = false;
@@ -2764,7 +2767,7 @@ extern "C" void vetr_destroy(vetr_ctx* ctx)
     if (ctx->tile_sums) cudaFree(ctx->tile_sums);
     if (ctx->grid_queue) cudaFree(ctx->grid_queue);
     cudaFree(ctx->knn_sorted), cudaFree(ctx->knn_point_cell), cudaFree(ctx->knn_queue);
-    cudaFree(ctx->knn_starts), cudaFree(ctx->knn_ends), cudaFree(ctx->knn_tile_sums);
+    cudaFree(ctx->knn_starts), cudaFree(ctx->knn_ends), cudaFree(ctx->knn_tile_sums), cudaFree(ctx->points_flags);
     for (int i = 0; i < VETR_T_N; ++i)
         for (int k = 0; k < 2; ++k)
             if (ctx->ev[i][k]) cudaEventDestroy(ctx->ev[i][k]);
@@ -3418,6 +3421,65 @@ extern "C" int vetr_knn_radius(vetr_ctx* ctx, const float* position, int positio
     else
         a.dummies = 17 - k1, knn_launch_search<17>(ctx, a);
     ctx->launches += 8;
+    VETR_CUDA(ctx, cudaGetLastError());
+    return VETR_OK;
+}
+
+extern "C" int vetr_remove_points_plan(vetr_ctx* ctx, int n, const int64_t* remove, int m, int32_t* new_index, int* n_kept)
+{
+    if (!ctx || n < 0 || m < 0 || !n_kept || (n > 0 && !new_index) || (m > 0 && !remove)) return VETR_E_INVALID_ARG;
+    if ((long long)n > kKnnMaxCells) return VETR_E_TOO_LARGE;  // one spine block scans 16384 tiles of 4096 flags
+    *n_kept = 0;
+    if (n == 0) return m == 0 ? VETR_OK : VETR_E_INVALID_ARG;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t st = ctx->stream;
+    if (n > ctx->points_cap)
+    {
+        cudaFree(ctx->points_flags);
+        ctx->points_flags = nullptr, ctx->points_cap = 0;
+        VETR_CUDA(ctx, cudaMalloc(&ctx->points_flags, (size_t)n * sizeof(int) + 16));
+        ctx->points_cap = n;
+    }
+    if (!ctx->knn_tile_sums) VETR_CUDA(ctx, cudaMalloc(&ctx->knn_tile_sums, (16384 + 16) * sizeof(int)));
+    int* d_small = ctx->knn_tile_sums + 16384 + 12;  // {bad index flag, survivors}
+    VETR_CUDA(ctx, cudaMemsetAsync(d_small, 0, 2 * sizeof(int), st));
+    const int sweep = std::min((n + 255) / 256, ctx->sm_count * 8);
+    const int n_tiles = (n + kKnnScanTile - 1) / kKnnScanTile;
+    points_fill_kernel<<<sweep, 256, 0, st>>>(ctx->points_flags, n, 1);
+    if (m > 0) points_mark_removed_kernel<<<std::min((m + 255) / 256, ctx->sm_count * 8), 256, 0, st>>>((const long long*)remove, m, n, ctx->points_flags, d_small);
+    knn_tile_sums_kernel<<<n_tiles, 256, 0, st>>>(ctx->points_flags, n, ctx->knn_tile_sums);
+    knn_spine_kernel<<<1, 1024, 0, st>>>(ctx->knn_tile_sums, n_tiles);
+    knn_apply_kernel<<<n_tiles, 256, 0, st>>>(ctx->points_flags, n, ctx->knn_tile_sums, new_index);
+    points_new_index_kernel<<<sweep, 256, 0, st>>>(ctx->points_flags, n, new_index, d_small + 1);
+    ctx->launches += 6;
+    int host[2] = {0, 0};
+    VETR_CUDA(ctx, cudaMemcpyAsync(host, d_small, sizeof(host), cudaMemcpyDeviceToHost, st));
+    VETR_CUDA(ctx, cudaStreamSynchronize(st));
+    if (host[0]) return VETR_E_INVALID_ARG;
+    *n_kept = host[1];
+    return VETR_OK;
+}
+
+extern "C" int vetr_gather_points(vetr_ctx* ctx, int n, int n_kept, const int32_t* new_index, const vetr_point_array* arrays, int n_arrays)
+{
+    if (!ctx || n < 0 || n_kept < 0 || n_kept > n || n_arrays < 0 || (n_arrays > 0 && !arrays) || (n > 0 && !new_index))
+        return VETR_E_INVALID_ARG;
+    for (int k = 0; k < n_arrays; ++k)
+    {
+        const vetr_point_array& a = arrays[k];
+        if (a.rows < 1 || a.width < 1 || (n > 0 && !a.src) || (n_kept > 0 && !a.dst)) return VETR_E_INVALID_ARG;
+        if (a.width == 4 && ((((uintptr_t)a.src | (uintptr_t)a.dst) & 15) != 0)) return VETR_E_INVALID_ARG;
+    }
+    if (n == 0 || n_kept == 0) return VETR_OK;
+    VETR_CUDA(ctx, cudaSetDevice(ctx->device));
+    for (int k = 0; k < n_arrays; ++k)
+    {
+        const vetr_point_array& a = arrays[k];
+        const long long total = (long long)a.rows * n;
+        const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 16);
+        points_gather_kernel<<<blocks, 256, 0, ctx->stream>>>((const uint32_t*)a.src, (uint32_t*)a.dst, new_index, n, n_kept, a.rows, a.width);
+        ctx->launches += 1;
+    }
     VETR_CUDA(ctx, cudaGetLastError());
     return VETR_OK;
 }

@@ -351,6 +351,36 @@ class Rasterizer:
         self._check(rc, "vetr_knn_radius")
         return out
 
+    def remove_points(self, n: int, remove, point_last=(), point_first=()):
+        """NeuralScene::RemovePoints (data/NeuralScene.cpp:1156-1239) on the device.  remove: CUDA int64 indices.
+        point_last: tensors [..., n] (texture [C,N], confidence [1,N], optimizer moments); point_first: tensors [n, w]
+        (t_position [N,4], t_index [N,1]).  Returns (new_index [n] int32: position after the removal or -1,
+        the shrunken point_last tensors, the shrunken point_first tensors).  Synchronises the stream once."""
+        assert remove.dtype == torch.int64 and remove.is_contiguous() and remove.is_cuda
+        self._sync_stream()
+        new_index = torch.empty(max(n, 1), dtype=torch.int32, device=self.device)
+        kept = C.c_int(0)
+        rc = L.lib().vetr_remove_points_plan(self._ctx, n, _ptr(remove) if remove.numel() else None, remove.numel(),
+                                             _ptr(new_index), C.byref(kept))
+        self._check(rc, "vetr_remove_points_plan")
+        k = kept.value
+        arrays, outs_last, outs_first = [], [], []
+        for t in point_last:
+            assert t.is_contiguous() and t.element_size() == 4 and t.shape[-1] == n
+            o = torch.empty(tuple(t.shape[:-1]) + (k,), dtype=t.dtype, device=t.device)
+            rows = t.numel() // n if n else 1
+            arrays.append(L.PointArray(t.data_ptr(), o.data_ptr(), max(rows, 1), 1))
+            outs_last.append(o)
+        for t in point_first:
+            assert t.is_contiguous() and t.element_size() == 4 and t.shape[0] == n and t.dim() == 2
+            o = torch.empty((k, t.shape[1]), dtype=t.dtype, device=t.device)
+            arrays.append(L.PointArray(t.data_ptr(), o.data_ptr(), 1, t.shape[1]))
+            outs_first.append(o)
+        if arrays:
+            arr = (L.PointArray * len(arrays))(*arrays)
+            self._check(L.lib().vetr_gather_points(self._ctx, n, k, _ptr(new_index), arr, len(arrays)), "vetr_gather_points")
+        return new_index[:n], outs_last, outs_first
+
     def l1_loss_grad(self, images, targets, grads, loss):
         """loss (device scalar) = sum over levels of mean |image - target|; grads[l] = sign(image - target) / numel, one launch."""
         self._sync_stream()

@@ -362,6 +362,53 @@ torch::Tensor ComputeRadius(torch::Tensor position, int n)
 }  // namespace vetr_torch
 
 // ---------------------------------------------------------------------------------------------------------
+// Point removal
+
+namespace vetr_torch
+{
+int64_t RemovePoints(RenderScene& s, torch::Tensor indices_to_remove, std::vector<torch::Tensor> per_point_state)
+{
+    TORCH_CHECK(s.t_position.defined() && s.t_position.is_cuda() && s.t_position.dim() == 2 && s.t_position.size(1) == 4,
+                "RemovePoints: t_position must be a CUDA tensor [N,4]");
+    static PointRendererCache cache;
+    const auto dev = s.t_position.device();
+    c10::cuda::CUDAGuard guard(dev);
+    vetr_ctx* vc = cache.context(dev.index());
+    torch::NoGradGuard ngg;
+    const int n = (int)s.t_position.size(0);
+    torch::Tensor remove = indices_to_remove.to(dev, torch::kLong).reshape({-1}).contiguous();
+    torch::Tensor new_index = torch::empty({std::max(n, 1)}, torch::TensorOptions().dtype(torch::kInt32).device(dev));
+    int kept = 0;
+    check(vetr_remove_points_plan(vc, n, remove.numel() ? remove.data_ptr<int64_t>() : nullptr, (int)remove.numel(),
+                                  new_index.data_ptr<int>(), &kept),
+          "vetr_remove_points_plan");
+    std::vector<torch::Tensor*> last = {&s.texture, &s.confidence_value_of_point};
+    for (auto& t : per_point_state) last.push_back(&t);
+    std::vector<torch::Tensor> src, dst;
+    std::vector<vetr_point_array> arrays;
+    for (torch::Tensor* t : last)
+    {
+        if (!t->defined()) continue;
+        TORCH_CHECK(t->size(-1) == n && t->element_size() == 4, "RemovePoints: per-point tensors end in the point dimension");
+        src.push_back(t->contiguous());
+        auto sizes = t->sizes().vec();
+        sizes.back() = kept;
+        dst.push_back(torch::empty(sizes, t->options()));
+        arrays.push_back({src.back().data_ptr(), dst.back().data_ptr(), (int32_t)std::max<int64_t>(src.back().numel() / std::max(n, 1), 1), 1});
+    }
+    torch::Tensor pos_src = s.t_position.contiguous(), pos_dst = torch::empty({kept, 4}, s.t_position.options());
+    arrays.push_back({pos_src.data_ptr(), pos_dst.data_ptr(), 1, 4});
+    check(vetr_gather_points(vc, n, kept, new_index.data_ptr<int>(), arrays.data(), (int)arrays.size()), "vetr_gather_points");
+    size_t k = 0;
+    for (torch::Tensor* t : last)
+        if (t->defined()) t->set_(dst[k++]);
+    s.t_position.set_(pos_dst);
+    if (s.t_index.defined()) s.t_index.set_(torch::arange(kept, s.t_index.options()).reshape({kept, 1}));
+    return kept;
+}
+}  // namespace vetr_torch
+
+// ---------------------------------------------------------------------------------------------------------
 // Environment map
 
 namespace vetr_torch
@@ -599,6 +646,12 @@ TORCH_LIBRARY(vetr, m)
     m.def("fill_scene_grid_with_loss", &fill_scene_grid_with_loss_op);
     m.class_<vetr_torch::EnvironmentSampleState>("EnvironmentSampleState").def(torch::init());
     m.def("environment_map_sample2", &environment_map_sample2_op);
+    m.def("remove_points", [](torch::Tensor texture, torch::Tensor confidence, torch::Tensor position, torch::Tensor index,
+                              torch::Tensor indices_to_remove, std::vector<torch::Tensor> state) {
+        vetr_torch::RenderScene scene;
+        scene.texture = texture, scene.confidence_value_of_point = confidence, scene.t_position = position, scene.t_index = index;
+        return vetr_torch::RemovePoints(scene, indices_to_remove, state);  // the tensors shrink in place
+    });
     m.def("compute_radius", [](torch::Tensor position, int64_t n) { return vetr_torch::ComputeRadius(position, (int)n); });
     m.class_<vetr_torch::NeuralRenderInfo>("NeuralRenderInfo").def(torch::init());
     m.def("blend_point_cloud", &blend_point_cloud_op);

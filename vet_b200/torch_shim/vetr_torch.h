@@ -10,6 +10,7 @@
 //   PointRendererCache::FillSceneGridWithLoss   rendering/PointRenderer.h:152, RenderForward.cu:761-791
 //   EnvironmentMapImpl (constructor, density, color, Sample2)   rendering/EnvironmentMap.h:252-301
 //   SceneData::ComputeRadius(point_cloud, n)   data/SceneData.h:396
+//   NeuralScene::RemovePoints(indices_to_remove)   data/NeuralScene.h (device part)
 // The reference's NeuralScene / RenderParams / ReducedImageInfo come from parts of VET that need the saiga library;
 // the structs below carry exactly the fields the render operator reads from them, under the same names, so that the
 // reference's call site (models/Pipeline.cpp:133 via RenderModule.cpp:45-245) maps onto them one to one.
@@ -136,6 +137,13 @@ void ApplyTangentToPose(torch::Tensor tangent, torch::Tensor pose);
 // SceneData::ComputeRadius (data/SceneData.h:396, SceneData.cpp:554-597) for a cloud that already lives on the GPU:
 // position [N,3] or [N,4] float CUDA tensor -> [N] distances to the n-th nearest other point (the reference's data[i](0)).
 torch::Tensor ComputeRadius(torch::Tensor position, int n = 4);
+
+// NeuralScene::RemovePoints (data/NeuralScene.cpp:1156-1239) for the tensors the render operator reads, without the host
+// round trip: t_position and t_index (rebuilt as the identity, as the reference's cloud constructor does), texture and
+// confidence_value_of_point shrink in place (Tensor::set_, as RemoveAndFlatten does, so parameters keep their identity),
+// and so does every tensor of `per_point_state` whose last dimension is the point count (the optimizer's exp_avg /
+// exp_avg_sq, my_adam.cpp:107-135).  indices_to_remove: int64, any device.  Returns the number of points left.
+int64_t RemovePoints(RenderScene& scene, torch::Tensor indices_to_remove, std::vector<torch::Tensor> per_point_state = {});
 
 // What one Sample2 call hands to its autograd node.
 struct EnvironmentSampleState : public torch::CustomClassHolder
