@@ -303,7 +303,10 @@ __global__ void __launch_bounds__(kEnvThreads) envmap_forward_kernel(const __gri
 // crosses a few hundred texels), so before the atomics the lanes of a warp that share a base texel, in runs of
 // consecutive lanes, are summed with a segmented shuffle reduction and the run's first lane issues one atomic per
 // corner and value.
-__global__ void __launch_bounds__(kEnvThreads) envmap_backward_kernel(const __grid_constant__ EnvArgs a)
+#ifndef VETR_ENV_BACK_CTAS
+#    define VETR_ENV_BACK_CTAS 3  // 80 registers with a few spills: 5.3 -> 4.1 ms on the benchmark row (2: 118 registers, 4: 64 registers, 4.5 ms)
+#endif
+__global__ void __launch_bounds__(kEnvThreads, VETR_ENV_BACK_CTAS) envmap_backward_kernel(const __grid_constant__ EnvArgs a)
 {
     __shared__ EnvCam s_cam[VETR_MAX_VIEWS];
     if (threadIdx.x < a.n_views) s_cam[threadIdx.x] = load_env_cam(a, threadIdx.x);
@@ -430,6 +433,7 @@ __global__ void __launch_bounds__(kEnvThreads) envmap_backward_kernel(const __gr
                     if (v > a.C) continue;
                     if (v == 0 && s == a.S - 1) continue;  // the last sphere's alpha is the constant 1
                     float x = c.off[q] >= 0 ? c.w[q] * gv[v] : 0.f;
+#ifndef VETR_ENV_NO_PRESUM
 #pragma unroll
                     for (int k = 0; k < 5; ++k)
                     {
@@ -437,6 +441,9 @@ __global__ void __launch_bounds__(kEnvThreads) envmap_backward_kernel(const __gr
                         if (same >> k & 1) x += y;
                     }
                     if (head && c.off[q] >= 0 && x != 0.f)
+#else
+                    if (c.off[q] >= 0 && x != 0.f)
+#endif
                         atomicAdd((v == 0 ? a.g_density : a.g_color + (v - 1) * plane) + c.off[q], x);
                 }
             }
