@@ -302,3 +302,16 @@ def remove_points(n: int, remove, point_last=(), point_first=()):
     new_index[keep] = np.arange(len(keep), dtype=np.int32)
     return (new_index, [np.ascontiguousarray(np.take(a, keep, axis=-1)) for a in point_last],
             [np.ascontiguousarray(np.take(a, keep, axis=0)) for a in point_first])
+
+
+def project_with_backward(pos4, pose8, intr13, view, level_scale, grad2, dist_cutoff=20.0):
+    """(image position at the level + z [3], gradients [22] = point 3, pose tangent 6, K 5, distortion 8) of one point, or
+    None for the gradients when the point is behind the camera."""
+    pos4, intr13 = np.ascontiguousarray(pos4, np.float32), np.ascontiguousarray(intr13, np.float32)
+    pose8, grad2 = np.ascontiguousarray(pose8, np.float64), np.ascontiguousarray(grad2, np.float32)
+    out, g = np.zeros(3, np.float32), np.zeros(22, np.float32)
+    f = lib().vo_project_with_backward
+    f.restype = C.c_int
+    rc = f(_ptr(pos4), _ptr(pose8), _ptr(intr13), C.byref(_oviews([view])[0]), C.c_float(level_scale), _ptr(grad2),
+           C.c_float(dist_cutoff), _ptr(out), _ptr(g))
+    return out, (g if rc == 0 else None)

@@ -1071,6 +1071,26 @@ float vo_blend(float T, float a, float c, float dst, int fused) { return fused ?
 float vo_new_T(float T, float a) { return new_T(T, a); }
 void vo_blending_fac(float u, float v, float* w4, float* J8) { blending_fac({u, v}, w4, J8); }
 
+// One point through the restated projection and its backward function, for the test that compares the chain of
+// transposed Jacobians with automatic differentiation of the same projection in float64.
+//   out[0..1] image position at the level, out[2] z; g[0..2] point, g[3..8] pose tangent, g[9..13] K, g[14..21] distortion
+int vo_project_with_backward(const float* pos4, const double* pose8, const float* intr13, const OView* view, float level_scale,
+                             const float* grad2, float dist_cutoff, float* out, float* g)
+{
+    const Pose V = load_pose(pose8);
+    const Projected pr = project(pos4, V, intr13, *view, dist_cutoff);
+    out[0] = pr.ip.x * level_scale, out[1] = pr.ip.y * level_scale, out[2] = pr.z;
+    float crop2[5];
+    for (int k = 0; k < 5; ++k) crop2[k] = view->crop[k] * level_scale;  // IntrinsicsPinhole::scale
+    BackOut bo;
+    if (!project_backward(pos4, {grad2[0], grad2[1]}, V, intr13, crop2, view->rot, dist_cutoff, bo)) return 1;
+    for (int k = 0; k < 3; ++k) g[k] = bo.g_point[k];
+    for (int k = 0; k < 6; ++k) g[3 + k] = bo.g_pose[k];
+    for (int k = 0; k < 5; ++k) g[9 + k] = bo.g_k[k];
+    for (int k = 0; k < 8; ++k) g[14 + k] = bo.g_dis[k];
+    return 0;
+}
+
 // Magnitude shadow: with `on`, vo_backward accumulates |addend| instead of addend into every gradient sum (counts
 // are unchanged).  The result bounds the rounding noise an fp32 sum of the same addends can carry in any order.
 void vo_set_abs_mode(void* h, int on) { ((Oracle*)h)->abs_mode = on != 0; }

@@ -257,3 +257,61 @@ def test_golden_fixture():
         count += gc
     np.testing.assert_array_equal(count, data["grid_count"])
     np.testing.assert_allclose(value, data["grid_value"], rtol=1e-12)
+
+
+def _projection_f64(p, xi, q, t, K, dist, crop, rot, centre, scale):
+    """The projection (PointRendererHelper.h:184-218 + crop transform, crop rotation and level scale) in float64 torch, as
+    a function of the point, a left pose perturbation xi = (translation, rotation) at zero, K and the distortion."""
+    x, y, z, w = q
+    R = torch.stack([torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - z * w), 2 * (x * z + y * w)]),
+                     torch.stack([2 * (x * y + z * w), 1 - 2 * (x * x + z * z), 2 * (y * z - x * w)]),
+                     torch.stack([2 * (x * z - y * w), 2 * (y * z + x * w), 1 - 2 * (x * x + y * y)])])
+    v = R @ p + t
+    v = v + xi[:3] + torch.linalg.cross(xi[3:], v)       # exp(xi) V p to first order: d/dxi = [I | -skew(v)]
+    n = v[:2] / v[2]
+    r2 = (n * n).sum()
+    k1, k2, k3, k4, k5, k6, p1, p2 = dist
+    radial = (1 + k1 * r2 + k2 * r2 ** 2 + k3 * r2 ** 3) / (1 + k4 * r2 + k5 * r2 ** 2 + k6 * r2 ** 3)
+    dx = n[0] * radial + 2 * p1 * n[0] * n[1] + p2 * (r2 + 2 * n[0] ** 2)
+    dy = n[1] * radial + 2 * p2 * n[0] * n[1] + p1 * (r2 + 2 * n[1] ** 2)
+    ix = K[0] * dx + K[4] * dy + K[2]
+    iy = K[1] * dy + K[3]
+    cx = crop[0] * ix + crop[4] * iy + crop[2]
+    cy = crop[1] * iy + crop[3]
+    d = torch.stack([cx, cy]) - centre
+    return (rot @ d + centre) * scale
+
+
+def test_projection_backward_is_the_transposed_jacobian():
+    """ProjectPointPinholeBackward (PointRendererHelper.h:317-372) chains the transposed Jacobians of TransformPoint,
+    DivideByZ, distortNormalizedPoint and normalizedToImage.  The restatement's chain against automatic differentiation
+    of the restated projection in float64: point, pose tangent, intrinsics and all eight distortion coefficients, with
+    crop transform, crop rotation and a level scale."""
+    rng = np.random.default_rng(12)
+    sc = scenes.tiny_scene(n=40, w=64, h=48, n_views=3, seed=5, crop=True)
+    sc.intrinsics[:, 4] = 0.7                                          # shear
+    sc.intrinsics[:, 5:] = rng.uniform(-0.05, 0.05, size=(sc.intrinsics.shape[0], 8)).astype(np.float32)
+    checked = 0
+    for view in sc.views:
+        for level, scale in ((0, 1.0), (2, 0.25)):
+            for i in range(sc.n):
+                grad = rng.standard_normal(2).astype(np.float32)
+                out, g = O.project_with_backward(sc.position[i], sc.poses[view.image_index], sc.intrinsics[view.camera_index],
+                                                 view, scale, grad)
+                if g is None:
+                    continue
+                t64 = lambda a: torch.tensor(np.asarray(a, np.float64))
+                p = t64(sc.position[i, :3]).requires_grad_(True)
+                xi = torch.zeros(6, dtype=torch.float64, requires_grad=True)
+                K = t64(sc.intrinsics[view.camera_index, :5]).requires_grad_(True)
+                dist = t64(sc.intrinsics[view.camera_index, 5:]).requires_grad_(True)
+                pose = sc.poses[view.image_index]
+                ip = _projection_f64(p, xi, t64(np.float32(pose[:4])), t64(np.float32(pose[4:7])), K, dist, t64(view.crop),
+                                     t64(view.rot).reshape(2, 2), t64([view.w // 2, view.h // 2]), scale)
+                np.testing.assert_allclose(out[:2], ip.detach().numpy(), rtol=2e-5, atol=2e-4)
+                (ip * t64(grad)).sum().backward()
+                ref = np.concatenate([p.grad.numpy(), xi.grad.numpy(), K.grad.numpy(), dist.grad.numpy()])
+                scale_of = np.abs(ref).max()
+                np.testing.assert_allclose(g, ref, rtol=2e-4, atol=2e-5 * scale_of)
+                checked += 1
+    assert checked > 100
