@@ -237,7 +237,14 @@ __device__ __forceinline__ float env_start_T(float weight, int flags)
     return (flags & VETR_ENV_DEPTH_TEST_WEIGHT) ? (weight > 0.5f ? 0.f : 1.f) : weight;
 }
 
+#ifndef VETR_ENV_FWD_CTAS
+#    define VETR_ENV_FWD_CTAS 0  // resident thread blocks per SM the forward kernel is compiled for (0: the compiler's choice, 64 registers)
+#endif
+#if VETR_ENV_FWD_CTAS > 0
+__global__ void __launch_bounds__(kEnvThreads, VETR_ENV_FWD_CTAS) envmap_forward_kernel(const __grid_constant__ EnvArgs a)
+#else
 __global__ void __launch_bounds__(kEnvThreads) envmap_forward_kernel(const __grid_constant__ EnvArgs a)
+#endif
 {
     __shared__ EnvCam s_cam[VETR_MAX_VIEWS];
     if (threadIdx.x < a.n_views) s_cam[threadIdx.x] = load_env_cam(a, threadIdx.x);
