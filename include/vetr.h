@@ -329,7 +329,7 @@ int vetr_envmap_backward(vetr_ctx* ctx, const vetr_cameras* cameras, const vetr_
  *   radius    written at radius[i * radius_stride] (position + 3 with stride 4 writes t_position's radius column in place)
  *   k         1..16 (the reference uses 4)
  * The call bins the points into a uniform grid whose cell size it picks from the cloud (a few host round trips of a few
- * bytes each), so it synchronises the context's stream; its scratch (16 bytes per point and 8 bytes per grid cell, at
+ * bytes each), so it synchronises the context's stream; its scratch (24 bytes per point and 8 bytes per grid cell, at
  * most 64 Mi cells) is allocated inside the context and reused by later calls. */
 int vetr_knn_radius(vetr_ctx* ctx, const float* position, int position_stride, int n, int k, float* radius, int radius_stride);
 
