@@ -108,7 +108,8 @@ typedef struct vetr_cameras
  * Per-pixel fragment lists of one forward call: what the reference keeps in LayerCuda::counting /
  * scanned_counting / per_image_atomic_counters and in collections[b][l] (PointRenderer.h:66-110,
  * PointRenderer.cu:796-822).  All views and levels live in ONE pixel space of n_views * P entries
- * (P = pyramid pixels of a view; view-major, then level, then row-major) and ONE fragment buffer.
+ * (P = pyramid pixels of a view; view-major, then level, then the banded order of VETR_PIXEL_BAND below) and ONE
+ * fragment buffer.
  * Caller-owned device memory.
  */
 typedef struct vetr_lists
