@@ -621,114 +621,119 @@ def run_ours(args):
     # 128^3 grid around the scene (FillSceneGridWithLoss; one launch per training image at the end of an epoch)
     next_rows = None
     if rank == 0 and world == 1 and not args.no_next_rows:
-        cells = 128
-        ax = torch.linspace(-10.0, 10.0, cells + 1, device=dev)[:-1]
-        gx, gy, gz = torch.meshgrid(ax, ax, ax, indexing="ij")
-        bb_min = torch.stack([gx, gy, gz], dim=-1).reshape(-1, 3).contiguous()
-        bb_len = torch.full_like(bb_min, 20.0 / cells)
-        loss_img = torch.rand(3, H, W, device=dev)
-        cell_value = torch.zeros(bb_min.shape[0], device=dev)
-        cell_count = torch.zeros(bb_min.shape[0], dtype=torch.int32, device=dev)
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for it in range(4):
-            if it == 1:
-                g0.record(stream)
-            rast.grid_loss(poses, intrinsics, my_views[0], bb_min, bb_len, loss_img, cell_value, cell_count)
-        g1.record(stream)
-        torch.cuda.synchronize(dev)
-        next_rows = {"grid_loss": {"ms": g0.elapsed_time(g1) / 3, "cells": int(bb_min.shape[0]),
-                                   "covered_pixels_per_launch": int(cell_count.sum().item()) // 4,
-                                   "workload": f"{cells}^3 cells over a 20-unit box, one {W}x{H} view, 3-channel loss image"}}
-        del bb_min, bb_len, loss_img, cell_value, cell_count
-
-        # texture environment map (EnvironmentMapImpl::Sample2 and its gradient): four spheres of 1024 x 1024 texels, four
-        # colour channels, sampled for every pixel of the step's views and levels from a random transmittance
-        S_env, R_env = 4, 1024
-        density = torch.randn(S_env, R_env, R_env, device=dev)
-        color = torch.rand(CHANNELS, S_env, R_env, R_env, device=dev)
-        radii = [20.0 * 5.0 ** i for i in range(S_env)]
-        weight_env = [torch.rand(V, 1, H >> l, W >> l, device=dev) for l in range(LAYERS)]
-        grad_env = [torch.randn(V, CHANNELS, H >> l, W >> l, device=dev) for l in range(LAYERS)]
-        g_density, g_color = torch.zeros_like(density), torch.zeros_like(color)
-        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        env_flags = 8  # zero distortion vouched for: no read-back inside the timed loop
-        for it in range(4):
-            if it == 1:
-                e0.record(stream)
-            env_out = rast.envmap_forward(poses, intrinsics, my_views, LAYERS, density, color, radii, weight_env, flags=env_flags)
-        e1.record(stream)
-        for it in range(3):
-            rast.envmap_backward(poses, intrinsics, my_views, LAYERS, density, color, radii, weight_env, grad_env, flags=env_flags,
-                                 g_density=g_density, g_color=g_color)
-        e2.record(stream)
-        torch.cuda.synchronize(dev)
-        env_px = sum(V * (H >> l) * (W >> l) for l in range(LAYERS))
-        fwd_ms, bwd_ms = e0.elapsed_time(e1) / 3, e1.elapsed_time(e2) / 3
-        next_rows["envmap"] = {"forward_ms": fwd_ms, "backward_ms": bwd_ms, "pixels": env_px,
-                               "forward_GBps": env_px * 4 * (1 + CHANNELS) / (fwd_ms * 1e-3) / 1e9,
-                               "workload": f"{S_env} spheres of {R_env}^2 texels, {CHANNELS} channels, {V} views x {LAYERS} levels"}
-        # the reference's formulation of the same work (libtorch operators + autograd), timed beside it; also a check of the
-        # fused kernels against it on the full-size workload
+        # informative rows: a failure here is reported in the line and never costs the headline measurement
+        next_rows = {}
         try:
-            g_density.zero_(), g_color.zero_()
-            rast.envmap_backward(poses, intrinsics, my_views, LAYERS, density, color, radii, weight_env, grad_env, flags=env_flags,
-                                 g_density=g_density, g_color=g_color)
-            lt_f, lt_b, lt_out, lt_gd, lt_gc = envmap_libtorch(torch, density, color, radii, poses, intrinsics, my_views, LAYERS,
-                                                               weight_env, grad_env)
-            mine = torch.cat([env_out[l][b].reshape(CHANNELS, -1) for l in range(LAYERS) for b in range(V)], 1)
-            next_rows["envmap"]["libtorch_operators"] = {
-                "forward_ms": lt_f, "backward_ms": lt_b,
-                "max_abs_difference_forward": float((mine - lt_out).abs().max().item()),
-                "relative_difference_g_color": float(((g_color - lt_gc).norm() / lt_gc.norm()).item()),
-                "relative_difference_g_density": float(((g_density - lt_gd).norm() / lt_gd.norm()).item()),
-                "note": "forward_mps5 as the reference writes it (grid_sample x2, sigmoid, per-sphere chain; autograd backward) on "
-                        "precomputed sample coordinates, same GPU; coordinates from torch operators, so samples differ by the "
-                        "rounding of the coordinates"}
-            del lt_out, lt_gd, lt_gc, mine
-        except Exception as e:  # the comparison is informative; the row's own numbers stand without it
-            next_rows["envmap"]["libtorch_operators"] = {"error": repr(e)[:200]}
-        del density, color, weight_env, grad_env, g_density, g_color, env_out
-        torch.cuda.empty_cache()
-
-        # drop-out radius of the benchmark cloud (SceneData::ComputeRadius: distance to the 4th nearest other point), one call
-        # including its host round trips, after one warm-up call that allocates the grid scratch
-        rad = rast.knn_radius(position, 4)
-        torch.cuda.synchronize(dev)
-        k0 = time.perf_counter()
-        rad = rast.knn_radius(position, 4, out=rad)
-        torch.cuda.synchronize(dev)
-        next_rows["knn_radius"] = {"ms": (time.perf_counter() - k0) * 1e3, "points": int(position.shape[0]), "k": 4,
-                                   "mean_radius": float(rad.mean().item()),
-                                   "workload": "the benchmark cloud; wall time of one call (binning, cell-size search, both passes)"}
-        del rad
-
-        # the same step in mode 3 (bilinear splats: four fragments per point and level; the mode the reference's shipped
-        # configuration trains with), a few launches without graph replay, reported beside the headline
-        if args.mode == 1:
-            p3 = default_params(render_mode=3, num_layers=LAYERS, num_channels=CHANNELS)
-            rast._lists_cache.clear()
-            torch.cuda.empty_cache()
-            m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps3 = 3
-            for it in range(reps3 + 1):
+            cells = 128
+            ax = torch.linspace(-10.0, 10.0, cells + 1, device=dev)[:-1]
+            gx, gy, gz = torch.meshgrid(ax, ax, ax, indexing="ij")
+            bb_min = torch.stack([gx, gy, gz], dim=-1).reshape(-1, 3).contiguous()
+            bb_len = torch.full_like(bb_min, 20.0 / cells)
+            loss_img = torch.rand(3, H, W, device=dev)
+            cell_value = torch.zeros(bb_min.shape[0], device=dev)
+            cell_count = torch.zeros(bb_min.shape[0], dtype=torch.int32, device=dev)
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for it in range(4):
                 if it == 1:
-                    m0.record(stream)
-                out3 = rast.forward(position, index, texture, confidence, background, poses, intrinsics, my_views, p3,
-                                    want_weight=True)
-                rast.l1_loss_grad(out3["color"], targets_dev, grad_bufs, loss_buf)
-                flat.zero_()
-                g3 = rast.backward_raw(grad_bufs, want_intrinsics=False, accum=grad_views())
-                rast.finalize(g3)
-            m1.record(stream)
+                    g0.record(stream)
+                rast.grid_loss(poses, intrinsics, my_views[0], bb_min, bb_len, loss_img, cell_value, cell_count)
+            g1.record(stream)
             torch.cuda.synchronize(dev)
-            F3, longest3 = rast.fragment_count()
-            ms3 = m0.elapsed_time(m1) / reps3
-            next_rows["mode3"] = {"ms_per_step": ms3, "frames_per_s": V / (ms3 * 1e-3), "fragments": F3,
-                                  "longest_list": longest3, "workload": "the headline step in render mode 3"}
-            del out3, g3
-            rast._lists_cache.clear()
-            rast._saved = None
+            next_rows.update({"grid_loss": {"ms": g0.elapsed_time(g1) / 3, "cells": int(bb_min.shape[0]),
+                                       "covered_pixels_per_launch": int(cell_count.sum().item()) // 4,
+                                       "workload": f"{cells}^3 cells over a 20-unit box, one {W}x{H} view, 3-channel loss image"}})
+            del bb_min, bb_len, loss_img, cell_value, cell_count
+
+            # texture environment map (EnvironmentMapImpl::Sample2 and its gradient): four spheres of 1024 x 1024 texels, four
+            # colour channels, sampled for every pixel of the step's views and levels from a random transmittance
+            S_env, R_env = 4, 1024
+            density = torch.randn(S_env, R_env, R_env, device=dev)
+            color = torch.rand(CHANNELS, S_env, R_env, R_env, device=dev)
+            radii = [20.0 * 5.0 ** i for i in range(S_env)]
+            weight_env = [torch.rand(V, 1, H >> l, W >> l, device=dev) for l in range(LAYERS)]
+            grad_env = [torch.randn(V, CHANNELS, H >> l, W >> l, device=dev) for l in range(LAYERS)]
+            g_density, g_color = torch.zeros_like(density), torch.zeros_like(color)
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            env_flags = 8  # zero distortion vouched for: no read-back inside the timed loop
+            for it in range(4):
+                if it == 1:
+                    e0.record(stream)
+                env_out = rast.envmap_forward(poses, intrinsics, my_views, LAYERS, density, color, radii, weight_env, flags=env_flags)
+            e1.record(stream)
+            for it in range(3):
+                rast.envmap_backward(poses, intrinsics, my_views, LAYERS, density, color, radii, weight_env, grad_env, flags=env_flags,
+                                     g_density=g_density, g_color=g_color)
+            e2.record(stream)
+            torch.cuda.synchronize(dev)
+            env_px = sum(V * (H >> l) * (W >> l) for l in range(LAYERS))
+            fwd_ms, bwd_ms = e0.elapsed_time(e1) / 3, e1.elapsed_time(e2) / 3
+            next_rows["envmap"] = {"forward_ms": fwd_ms, "backward_ms": bwd_ms, "pixels": env_px,
+                                   "forward_GBps": env_px * 4 * (1 + CHANNELS) / (fwd_ms * 1e-3) / 1e9,
+                                   "workload": f"{S_env} spheres of {R_env}^2 texels, {CHANNELS} channels, {V} views x {LAYERS} levels"}
+            # the reference's formulation of the same work (libtorch operators + autograd), timed beside it; also a check of the
+            # fused kernels against it on the full-size workload
+            try:
+                g_density.zero_(), g_color.zero_()
+                rast.envmap_backward(poses, intrinsics, my_views, LAYERS, density, color, radii, weight_env, grad_env, flags=env_flags,
+                                     g_density=g_density, g_color=g_color)
+                lt_f, lt_b, lt_out, lt_gd, lt_gc = envmap_libtorch(torch, density, color, radii, poses, intrinsics, my_views, LAYERS,
+                                                                   weight_env, grad_env)
+                mine = torch.cat([env_out[l][b].reshape(CHANNELS, -1) for l in range(LAYERS) for b in range(V)], 1)
+                next_rows["envmap"]["libtorch_operators"] = {
+                    "forward_ms": lt_f, "backward_ms": lt_b,
+                    "max_abs_difference_forward": float((mine - lt_out).abs().max().item()),
+                    "relative_difference_g_color": float(((g_color - lt_gc).norm() / lt_gc.norm()).item()),
+                    "relative_difference_g_density": float(((g_density - lt_gd).norm() / lt_gd.norm()).item()),
+                    "note": "forward_mps5 as the reference writes it (grid_sample x2, sigmoid, per-sphere chain; autograd backward) on "
+                            "precomputed sample coordinates, same GPU; coordinates from torch operators, so samples differ by the "
+                            "rounding of the coordinates"}
+                del lt_out, lt_gd, lt_gc, mine
+            except Exception as e:  # the comparison is informative; the row's own numbers stand without it
+                next_rows["envmap"]["libtorch_operators"] = {"error": repr(e)[:200]}
+            del density, color, weight_env, grad_env, g_density, g_color, env_out
             torch.cuda.empty_cache()
+
+            # drop-out radius of the benchmark cloud (SceneData::ComputeRadius: distance to the 4th nearest other point), one call
+            # including its host round trips, after one warm-up call that allocates the grid scratch
+            rad = rast.knn_radius(position, 4)
+            torch.cuda.synchronize(dev)
+            k0 = time.perf_counter()
+            rad = rast.knn_radius(position, 4, out=rad)
+            torch.cuda.synchronize(dev)
+            next_rows["knn_radius"] = {"ms": (time.perf_counter() - k0) * 1e3, "points": int(position.shape[0]), "k": 4,
+                                       "mean_radius": float(rad.mean().item()),
+                                       "workload": "the benchmark cloud; wall time of one call (binning, cell-size search, both passes)"}
+            del rad
+
+            # the same step in mode 3 (bilinear splats: four fragments per point and level; the mode the reference's shipped
+            # configuration trains with), a few launches without graph replay, reported beside the headline
+            if args.mode == 1:
+                p3 = default_params(render_mode=3, num_layers=LAYERS, num_channels=CHANNELS)
+                rast._lists_cache.clear()
+                torch.cuda.empty_cache()
+                m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps3 = 3
+                for it in range(reps3 + 1):
+                    if it == 1:
+                        m0.record(stream)
+                    out3 = rast.forward(position, index, texture, confidence, background, poses, intrinsics, my_views, p3,
+                                        want_weight=True)
+                    rast.l1_loss_grad(out3["color"], targets_dev, grad_bufs, loss_buf)
+                    flat.zero_()
+                    g3 = rast.backward_raw(grad_bufs, want_intrinsics=False, accum=grad_views())
+                    rast.finalize(g3)
+                m1.record(stream)
+                torch.cuda.synchronize(dev)
+                F3, longest3 = rast.fragment_count()
+                ms3 = m0.elapsed_time(m1) / reps3
+                next_rows["mode3"] = {"ms_per_step": ms3, "frames_per_s": V / (ms3 * 1e-3), "fragments": F3,
+                                      "longest_list": longest3, "workload": "the headline step in render mode 3"}
+                del out3, g3
+                rast._lists_cache.clear()
+                rast._saved = None
+                torch.cuda.empty_cache()
+        except Exception as e:
+            next_rows["error"] = repr(e)[:300]
 
     # ---- CPU baseline on the host cores (rank 0, N = 1 only)
     cpu = None
