@@ -703,6 +703,22 @@ def run_ours(args):
             next_rows["knn_radius"] = {"ms": (time.perf_counter() - k0) * 1e3, "points": int(position.shape[0]), "k": 4,
                                        "mean_radius": float(rad.mean().item()),
                                        "workload": "the benchmark cloud; wall time of one call (binning, cell-size search, both passes)"}
+            if not args.no_cpu_baseline:
+                # CPU baseline of this row (part of the cpu_baseline leg): the oracle's grid search on the host cores, same
+                # cloud, and a comparison of all values (the kernel's are bit-equal to it by construction)
+                try:
+                    from oracle import oracle as O
+
+                    xyz_host = np.ascontiguousarray(scene.position[:, :3])
+                    c0 = time.perf_counter()
+                    rad_cpu = O.knn_radius(xyz_host, 4, grid=True)
+                    cpu_s = time.perf_counter() - c0
+                    next_rows["knn_radius"]["cpu_baseline"] = {
+                        "seconds": cpu_s, "cores": O.threads(), "kind": "port",
+                        "values_that_differ": int((rad.cpu().numpy() != rad_cpu).sum()),
+                        "sample": "the whole cloud, one call of the oracle's uniform-grid search (OpenMP)"}
+                except Exception as e:
+                    next_rows["knn_radius"]["cpu_baseline"] = {"error": repr(e)[:200]}
             del rad
 
             # the same step in mode 3 (bilinear splats: four fragments per point and level; the mode the reference's shipped

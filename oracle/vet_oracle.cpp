@@ -1593,3 +1593,116 @@ extern "C" int vo_knn_radius(const float* position, int stride, int n_points, in
     return 0;
 }
 
+// The same query with a uniform grid instead of all pairs (what a host implementation would do, as the reference's
+// KD-tree does, in O(n) cells): bit-equal to vo_knn_radius, and fast enough to be timed on the benchmark cloud as
+// the CPU baseline of this row.  Cell size: halved from 1/32 of the longest extent until an occupied cell holds at
+// most 8 points on average; rings of cells around the point's cell until the k-th nearest distance found is smaller
+// than the distance to the faces of the visited cube.
+extern "C" int vo_knn_radius_grid(const float* position, int stride, int n_points, int k, float* radius)
+{
+    if (!position || !radius || n_points < 0 || k < 1 || stride < 3) return -1;
+    const int n = n_points;
+    if (n == 0) return 0;
+    float lo[3] = {INFINITY, INFINITY, INFINITY}, hi[3] = {-INFINITY, -INFINITY, -INFINITY};
+    for (int i = 0; i < n; ++i)
+        for (int a = 0; a < 3; ++a)
+        {
+            const float v = position[(int64_t)i * stride + a];
+            if (!std::isfinite(v)) return -1;
+            lo[a] = std::min(lo[a], v), hi[a] = std::max(hi[a], v);
+        }
+    float ext = 0.f, maxabs = 0.f;
+    for (int a = 0; a < 3; ++a)
+    {
+        ext    = std::max(ext, hi[a] - lo[a]);
+        maxabs = std::max(maxabs, std::max(std::fabs(lo[a]), std::fabs(hi[a])));
+    }
+    float cell = ext > 0.f ? ext / 32.f : 1.f;
+    int d[3];
+    std::vector<int> cell_of((size_t)n), start;
+    auto dims_for = [&](float c, int* dd)
+    {
+        int64_t cells = 1;
+        for (int a = 0; a < 3; ++a)
+        {
+            dd[a] = (int)std::min(std::floor((double)(hi[a] - lo[a]) / c) + 1.0, 1.0e9);
+            cells = cells > ((int64_t)1 << 40) ? cells : cells * dd[a];
+        }
+        return cells;
+    };
+    auto coord = [&](float p, int a, float inv) { return (int)std::fmin(std::fmax(std::floor((p - lo[a]) * inv), 0.f), (float)(d[a] - 1)); };
+    int64_t cells = dims_for(cell, d);
+    for (int iter = 0; iter < 24; ++iter)
+    {
+        const float inv = 1.f / cell;
+        start.assign((size_t)cells + 1, 0);
+        for (int i = 0; i < n; ++i)
+        {
+            const float* p = position + (int64_t)i * stride;
+            cell_of[i]     = (coord(p[2], 2, inv) * d[1] + coord(p[1], 1, inv)) * d[0] + coord(p[0], 0, inv);
+            ++start[(size_t)cell_of[i] + 1];
+        }
+        int64_t occupied = 0;
+        for (int64_t c = 0; c < cells; ++c) occupied += start[(size_t)c + 1] > 0;
+        int d2[3];
+        if (ext <= 0.f || (double)n / (double)occupied <= 8.0 || dims_for(cell * 0.5f, d2) > ((int64_t)1 << 26)) break;
+        cell *= 0.5f;
+        cells = dims_for(cell, d);
+    }
+    for (int64_t c = 0; c < cells; ++c) start[(size_t)c + 1] += start[(size_t)c];
+    std::vector<int> cursor(start.begin(), start.end() - 1), order((size_t)n);
+    for (int i = 0; i < n; ++i) order[(size_t)cursor[(size_t)cell_of[i]]++] = i;
+    const float inv = 1.f / cell, slack = 1e-3f * cell + 4e-6f * (maxabs + ext);
+    const int k1 = std::min(k, n - 1) + 1;
+#pragma omp parallel for schedule(dynamic, 1024)
+    for (int s = 0; s < n; ++s)
+    {
+        const int i    = order[(size_t)s];
+        const float* p = position + (int64_t)i * stride;
+        const int c[3] = {coord(p[0], 0, inv), coord(p[1], 1, inv), coord(p[2], 2, inv)};
+        std::vector<float> best((size_t)k1, INFINITY);  // ascending
+        const int r_max = std::max(std::max(std::max(c[0], d[0] - 1 - c[0]), std::max(c[1], d[1] - 1 - c[1])), std::max(c[2], d[2] - 1 - c[2]));
+        for (int r = 0;; ++r)
+        {
+            for (int z = std::max(c[2] - r, 0); z <= std::min(c[2] + r, d[2] - 1); ++z)
+                for (int y = std::max(c[1] - r, 0); y <= std::min(c[1] + r, d[1] - 1); ++y)
+                {
+                    const bool face = std::abs(z - c[2]) == r || std::abs(y - c[1]) == r;
+                    auto visit = [&](int x)
+                    {
+                        const int64_t ci = ((int64_t)z * d[1] + y) * d[0] + x;
+                        for (int j = start[(size_t)ci]; j < start[(size_t)ci + 1]; ++j)
+                        {
+                            const float* q = position + (int64_t)order[(size_t)j] * stride;
+                            const float dx = p[0] - q[0], dy = p[1] - q[1], dz = p[2] - q[2];
+                            const float dd = dx * dx + dy * dy + dz * dz;
+                            if (dd < best[(size_t)k1 - 1])
+                            {
+                                int at = k1 - 1;
+                                while (at > 0 && best[(size_t)at - 1] > dd) best[(size_t)at] = best[(size_t)at - 1], --at;
+                                best[(size_t)at] = dd;
+                            }
+                        }
+                    };
+                    if (face)  // a row on the shell's y or z face: all its cells
+                        for (int x = std::max(c[0] - r, 0); x <= std::min(c[0] + r, d[0] - 1); ++x) visit(x);
+                    else  // an inner row: its two end cells
+                    {
+                        if (c[0] - r >= 0) visit(c[0] - r);
+                        if (c[0] + r < d[0]) visit(c[0] + r);
+                    }
+                }
+            float m = INFINITY;
+            for (int a = 0; a < 3; ++a)
+            {
+                if (c[a] - r > 0) m = std::min(m, p[a] - (lo[a] + (float)(c[a] - r) * cell));
+                if (c[a] + r < d[a] - 1) m = std::min(m, (lo[a] + (float)(c[a] + r + 1) * cell) - p[a]);
+            }
+            m -= slack;
+            if (r >= r_max || (m > 0.f && best[(size_t)k1 - 1] <= m * m)) break;
+        }
+        radius[i] = std::sqrt(best[(size_t)k1 - 1]);
+    }
+    return 0;
+}
+

@@ -70,6 +70,17 @@ def _clouds():
     yield "offset far from the origin", (rng.uniform(0, 1, size=(5000, 3)) + 4096.0).astype(np.float32)
 
 
+def test_grid_search_equals_all_pairs():
+    """The restatement's uniform-grid search (the timed CPU baseline of this row) against all pairs, bit for bit."""
+    for name, xyz in _clouds():
+        for k in (1, 4, 16):
+            assert np.array_equal(O.knn_radius(xyz, k, grid=True), O.knn_radius(xyz, k)), (name, k)
+    p = np.array([[0, 0, 0], [3, 0, 0], [0, 4, 0]], np.float32)
+    assert np.array_equal(O.knn_radius(p, 4, grid=True), np.array([4, 5, 5], np.float32))
+    assert np.array_equal(O.knn_radius(np.repeat(p[1:2], 9, 0), 4, grid=True), np.zeros(9, np.float32))
+    assert O.knn_radius(np.zeros((0, 3), np.float32), 4, grid=True).shape == (0,)
+
+
 @pytest.mark.gpu
 def test_gpu_matches_all_pairs_bit_for_bit():
     for name, xyz in _clouds():
