@@ -690,6 +690,24 @@ def run_ours(args):
                 del lt_out, lt_gd, lt_gc, mine
             except Exception as e:  # the comparison is informative; the row's own numbers stand without it
                 next_rows["envmap"]["libtorch_operators"] = {"error": repr(e)[:200]}
+            if not args.no_cpu_baseline:
+                # CPU baseline of this row (part of the cpu_baseline leg): the oracle's forward pass of ONE view on the host
+                # cores, same textures and transmittance, and its largest difference from the kernel's result for that view
+                try:
+                    from oracle import oracle as O
+
+                    env_cpu = O.EnvMap(density.cpu().numpy(), color.cpu().numpy(), inner_radius=20.0, radius_factor=5.0)
+                    w_cpu = [w[:1].cpu().numpy() for w in weight_env]
+                    c0 = time.perf_counter()
+                    ref_env = O.envmap_forward(scene, my_views[:1], LAYERS, env_cpu, w_cpu)
+                    cpu_s = time.perf_counter() - c0
+                    next_rows["envmap"]["cpu_baseline"] = {
+                        "forward_seconds_per_view": cpu_s, "cores": O.threads(), "kind": "port",
+                        "max_abs_difference": max(float(np.abs(env_out[l][:1].cpu().numpy() - ref_env[l]).max()) for l in range(LAYERS)),
+                        "sample": "forward pass of one view (4 levels) with the oracle (OpenMP)"}
+                    del env_cpu, w_cpu, ref_env
+                except Exception as e:
+                    next_rows["envmap"]["cpu_baseline"] = {"error": repr(e)[:200]}
             del density, color, weight_env, grad_env, g_density, g_color, env_out
             torch.cuda.empty_cache()
 
