@@ -50,6 +50,11 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-next-rows", action="store_true", help="skip the measurements reported beside the headline (grid loss, mode 3)")
+    ap.add_argument("--no-configs", action="store_true",
+                    help="skip the blocks for the other benchmark configurations (viewer frame, training step, scene in shells; "
+                         "N = 1 only) and the 20 M-point batch of 32 distinct views sharded over the GPUs (every N)")
+    ap.add_argument("--min-seconds", type=float, default=1.0,
+                    help="the timed region repeats the K steps until it has run at least this long (K steps at a time)")
     ap.add_argument("--prewarm", type=float, default=1.0, help="seconds of untimed load before the warm-up steps")
     ap.add_argument("--views-mode", choices=["same", "distinct"], default="same",
                     help="N > 1: every rank renders the same V camera poses (identical per-GPU work), or V poses of its own")
@@ -73,7 +78,7 @@ def measured_peak():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     except Exception:
-        return HBM_FALLBACK_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+        return HBM_FALLBACK_GBS, "fallback (6.65 TB/s: MEASURED_PEAKS.json is absent)"
 
 
 def make_scene(n_points: int, n_views_total: int):
@@ -149,27 +154,50 @@ class ClockSampler:
 # reference arm / CPU baseline: the oracle on the host cores
 
 
-def cpu_oracle_run(scene, params, steps: int, warmup: int):
-    """Times forward + backward of ONE view per step with the CPU oracle.  Returns (seconds per step, threads)."""
+def cpu_oracle_run(scene, params, steps: int, warmup: int, backward: bool = True):
+    """Times forward (+ backward) of ONE view per step with the CPU oracle on all host threads.  Returns (seconds per
+    step, threads)."""
     from oracle import oracle as O
 
+    threads = O.use_all_host_threads()  # a process launcher may have pinned OMP_NUM_THREADS to 1
     o = O.Oracle()
-    p = O.default_params(render_mode=params["render_mode"], num_layers=LAYERS)
+    p = O.default_params(**{k: v for k, v in params.items() if k in O.default_params()})
     times = []
     for it in range(warmup + steps):
         view = [scene.views[it % len(scene.views)]]
         t0 = time.perf_counter()
         fwd = o.forward(scene, p, views=view)
         t1 = time.perf_counter()
-        rng = np.random.default_rng(it)  # seeded L1 target: input preparation, not timed
-        grads = [(np.sign(c - rng.uniform(0.0, 1.0, size=c.shape).astype(np.float32)) / c.size).astype(np.float32)
-                 for c in fwd["color"]]
-        t2 = time.perf_counter()
-        o.backward(grads)
-        t3 = time.perf_counter()
+        t2 = t3 = 0.0
+        if backward:
+            rng = np.random.default_rng(it)  # seeded L1 target: input preparation, not timed
+            grads = [(np.sign(c - rng.uniform(0.0, 1.0, size=c.shape).astype(np.float32)) / c.size).astype(np.float32)
+                     for c in fwd["color"]]
+            t2 = time.perf_counter()
+            o.backward(grads)
+            t3 = time.perf_counter()
         if it >= warmup:
             times.append((t1 - t0) + (t3 - t2))
-    return float(np.mean(times)), O.threads()
+    return float(np.mean(times)), threads
+
+
+def parity_against_oracle(rast, scene, params, view_index: int = 0, backward: bool = True) -> dict:
+    """One view of `scene` through the CUDA library and through the CPU oracle on the same inputs, compared: fragment
+    total, per-pixel counts and sorted keys (exact), images (largest absolute difference), raw gradient sums (largest
+    error in units of the bound 1e-5 x sum|addends| of the element).  The oracle is the checker here, never the thing
+    measured; a difference is reported, not raised."""
+    import copy
+
+    from tests import util
+
+    one = copy.copy(scene)
+    one.views = [scene.views[view_index]]
+    ora = util.run_oracle(one, params)
+    grads = util.l1_grads(ora["fwd"]["color"], seed=5) if backward else None
+    if backward:
+        ora = util.run_oracle(one, params, grads=grads)
+    gpu = util.run_gpu(rast, one, params, grads=grads)
+    return util.parity_report(gpu, ora, scene.channels)
 
 
 def envmap_libtorch(torch, density, color, radii, poses, intrinsics, views, layers, weight, grad_out, reps=2):
@@ -477,13 +505,21 @@ def run_ours(args):
     launches0 = rast.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    # the timed region: K steps, repeated (K at a time) until it has run for --min-seconds, so that a small K still gives
+    # the clock sampler and the end-to-end leg a region of about a second.  The repeat count is agreed between the ranks
+    # from the prewarm step time, before the region starts.
+    repeats = 1
+    if args.min_seconds > 0 and args.prewarm > 0:
+        repeats = int(min(1000, max(1, np.ceil(args.min_seconds / max(float(one.item()) * args.steps, 1e-6)))))
+    timed_steps = repeats * args.steps
     t_begin = time.perf_counter()
     step_events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     e0.record(stream)
     step_events[0].record(stream)
-    for i in range(args.steps):
+    for i in range(timed_steps):
         loss, fin = step(static_targets)
-        step_events[i + 1].record(stream)
+        if i < args.steps:
+            step_events[i + 1].record(stream)
     e1.record(stream)
     barrier()
     t_end = time.perf_counter()
@@ -493,13 +529,13 @@ def run_ours(args):
     if graph_info["used"]:
         l0 = rast.launch_count()
         eager_step(static_targets)
-        launches = (rast.launch_count() - l0) * args.steps  # the graph replays exactly the launches of one eager step
+        launches = (rast.launch_count() - l0) * timed_steps  # the graph replays exactly the launches of one eager step
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
-    frames = world * V * args.steps
+    frames = world * V * timed_steps
     value = frames / (ms_total * 1e-3)
     # per-rank load (the step time is the max over the ranks): fragments of the rank's views, ms of its compute graph
     per_rank = None
@@ -518,6 +554,47 @@ def run_ours(args):
         allr = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(allr, mine)
         per_rank = [{"fragments": int(t[0].item()), "compute_ms": round(float(t[1].item()), 3)} for t in allr]
+
+    # ---- N > 1: one untimed step whose exchanged result (the kernel over peer memory, plain or through the NVSwitch
+    # multicast object) is compared with an NCCL all-reduce of the same raw buffers followed by the epilogue kernels, and
+    # whose bits are compared between the ranks
+    exchange_check = None
+    if world > 1 and peer is not None:
+        try:
+            _, g_c = compute(static_targets)
+            if overlap:  # compute() then stops after the per-fragment kernels: add the per-point pass
+                rast.backward_raw(grad_bufs, want_intrinsics=False, accum=g_c, phases=2)
+            torch.cuda.synchronize(dev)
+            raw_copy = flat.clone()
+            pose_copy, pose_count_copy = g_c["pose"].clone(), g_c["pose_count"].clone()
+            fin_x = peer.run(g_c)
+            torch.cuda.synchronize(dev)
+            got = {k: fin_x[k].clone() for k in ("texture", "points", "confidence")}
+            dist.all_reduce(raw_copy)
+            dist.all_reduce(pose_copy)
+            dist.all_reduce(pose_count_copy)
+            ref = rast.finalize(dict(desc=raw_copy[:4 * n_tex].view(n_tex, 4), points=raw_copy[4 * n_tex:4 * n_tex + 4 * n].view(n, 4),
+                                     conf=raw_copy[4 * n_tex + 4 * n:], background=torch.zeros(CHANNELS, device=dev),
+                                     pose=pose_copy, pose_count=pose_count_copy))
+            diffs, scale = {}, {}
+            for k in got:
+                a, b = got[k].reshape(-1), ref[k].reshape(-1)
+                diffs[k] = float((a - b).abs().max().item())
+                scale[k] = float(b.abs().max().item())
+            diffs["pose"] = float((fin_x["pose"] - ref["pose"]).abs().max().item())
+            # the same bits on every rank: a 64-bit sum of the results' bit patterns, gathered and compared
+            word = torch.stack([got[k].reshape(-1).view(torch.int32).to(torch.int64).sum() for k in ("texture", "points", "confidence")])
+            words = [torch.zeros_like(word) for _ in range(world)]
+            dist.all_gather(words, word)
+            worst = torch.tensor([max(diffs[k] / max(scale.get(k, 1.0), 1e-30) for k in got)], dtype=torch.float64, device=dev)
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            exchange_check = {"kind": exchange_kind, "max_abs_diff": diffs, "max_abs_value": scale,
+                              "max_diff_relative_to_largest_value_over_ranks": float(worst.item()),
+                              "identical_on_all_ranks": bool(all(torch.equal(w, words[0]) for w in words)),
+                              "compared_with": "NCCL all-reduce of the same raw buffers + vetr_finalize_gradients"}
+            del raw_copy, got, ref
+        except Exception as e:  # noqa: BLE001
+            exchange_check = {"error": repr(e)[:300]}
 
     # ---- e2e: per-step targets arrive from pinned host memory (prefetched on a copy stream), loss read back
     e2e = None
@@ -558,7 +635,7 @@ def run_ours(args):
         barrier()
         t0 = time.perf_counter()
         e0.record(stream)
-        e2e_run(args.steps)
+        e2e_run(timed_steps)
         e1.record(stream)
         barrier()
         wall = (time.perf_counter() - t0) * 1e3
@@ -566,7 +643,7 @@ def run_ours(args):
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e = {"value": frames / (float(t[0].item()) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
-               "d2h_bytes_per_step": 4, "wall_ms_per_step": float(t[1].item()) / args.steps,
+               "d2h_bytes_per_step": 4, "wall_ms_per_step": float(t[1].item()) / timed_steps,
                "note": "the views' 8-bit target images copied from pinned host memory every step (double-buffered on a copy "
                        "stream), target pyramid built on the device, loss scalar read back every step"}
 
@@ -612,8 +689,8 @@ def run_ours(args):
                             if dominant in TRAFFIC_OVER_ALGORITHMIC else None),
                 "peak_source": peak_src, "kernels": kernels,
                 "whole_step": {"algorithmic_bytes": whole_bytes,
-                               "achieved_gbs": whole_bytes * args.steps / (ms_total * 1e-3) / 1e9,
-                               "frac": whole_bytes * args.steps / (ms_total * 1e-3) / 1e9 / peak},
+                               "achieved_gbs": whole_bytes * timed_steps / (ms_total * 1e-3) / 1e9,
+                               "frac": whole_bytes * timed_steps / (ms_total * 1e-3) / 1e9 / peak},
                 "counts": {"N": N, "N_touched": touched, "F": F, "pixels": PT, "views_per_launch": V,
                            "longest_list": longest}}
 
@@ -777,10 +854,29 @@ def run_ours(args):
                "sample": "2 timed steps after 1 warm-up; each step = forward+backward of ONE 1920x1080 view of the same "
                          f"{N}-point cloud with the CPU oracle (OpenMP, all host threads)"}
 
+    # ---- parity at the benchmark's own size: view 0 of the cloud that was timed, CUDA library against the CPU oracle
+    parity_headline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            parity_headline = parity_against_oracle(rast, scene, params)
+        except Exception as e:  # noqa: BLE001
+            parity_headline = {"error": repr(e)[:300]}
+
+    # ---- the other benchmark configurations
+    configs = None
+    if not args.no_configs:
+        rast._lists_cache.clear()
+        rast._saved = None
+        torch.cuda.empty_cache()
+        try:
+            configs = run_configs(args, torch, dist, rast, dev, rank, world, peak)
+        except Exception as e:  # noqa: BLE001
+            configs = {"error": repr(e)[:300]}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_total / timed_steps, "timed_steps": timed_steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"headline: {N} planar-scene points replicated, {V} views {W}x{H} f={FOCAL:g} per GPU and "
                                    f"step, {LAYERS} levels, mode {args.mode}, fwd+bwd, L1 vs seeded target"
@@ -789,10 +885,264 @@ def run_ours(args):
                                                               "pyramids; gradient buffer 288 MB rewritten every step)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
             "loss": float(loss.item()), "step_ms": [round(x, 3) for x in step_ms], "cuda_graph": graph_info, "exchange": exchange_kind + ("+overlap" if overlap else ""), "per_rank": per_rank, "next_rows": next_rows,
+            "parity_headline": parity_headline, "exchange_check": exchange_check, "configs": configs,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# -------------------------------------------------------------------------------------------------------------
+# the other benchmark configurations, reported as blocks beside the headline
+
+
+def algorithmic_bytes_per_launch(N, F, P_total, touched, n_views, backward):
+    """Per launch of n_views views: forward 20 N per view + 36 F + 28 P; backward 32 P + 44 F + 40 N (the zero fill, once)
+    + 80 N_t (one read + one write per touched gradient element)."""
+    b = 20 * N * n_views + 36 * F + 28 * P_total
+    if backward:
+        b += 32 * P_total + 44 * F + 40 * N + 80 * touched
+    return b
+
+
+class ConfigRun:
+    """One configuration: the scene on the device, seeded random L1 targets, and a step = forward (+ L1 gradient +
+    backward into one gradient buffer + epilogue) over `views` in launches of at most `chunk` views."""
+
+    def __init__(self, torch, rast, dev, scene, params, backward=True, want_intrinsics=True, chunk=4, flat=None):
+        from vet_b200.render import level_sizes, scene_to_device
+
+        self.torch, self.rast, self.dev, self.scene, self.params = torch, rast, dev, scene, params
+        self.backward, self.want_intrinsics, self.chunk = backward, want_intrinsics, chunk
+        self.tensors = scene_to_device(scene, dev)
+        self.n, self.n_tex = scene.n, scene.texture.shape[1]
+        w, h = scene.views[0].w, scene.views[0].h
+        self.sizes = level_sizes(w, h, LAYERS)
+        self.P = sum(a * b for a, b in self.sizes)
+        gen = torch.Generator(device=dev).manual_seed(99)
+        self.targets = [torch.rand(chunk, CHANNELS, hh, ww, device=dev, generator=gen) for (ww, hh) in self.sizes]
+        self.grads = [torch.empty(chunk, CHANNELS, hh, ww, device=dev) for (ww, hh) in self.sizes]
+        self.loss = torch.zeros((), device=dev)
+        n, n_tex = self.n, self.n_tex
+        self.flat = flat if flat is not None else torch.zeros(4 * n_tex + 4 * n + n_tex, dtype=torch.float32, device=dev)
+        self.fragments = {}  # view index -> fragments of the launch it was part of / views in that launch
+
+    def accum(self):
+        torch, n, n_tex, flat = self.torch, self.n, self.n_tex, self.flat
+        g = dict(desc=flat[:4 * n_tex].view(n_tex, 4), points=flat[4 * n_tex:4 * n_tex + 4 * n].view(n, 4),
+                 conf=flat[4 * n_tex + 4 * n:4 * n_tex + 4 * n + n_tex], background=torch.zeros(CHANNELS, device=self.dev),
+                 pose=torch.zeros(self.scene.poses.shape[0], 6, dtype=torch.float64, device=self.dev),
+                 pose_count=torch.zeros(self.scene.poses.shape[0], device=self.dev))
+        if self.want_intrinsics:
+            g["intrinsics"] = torch.zeros(self.scene.intrinsics.shape[0], 13, device=self.dev)
+            g["intrinsics_count"] = torch.zeros(self.scene.intrinsics.shape[0], device=self.dev)
+        return g
+
+    def local_step(self, view_ids, read_counts=False):
+        """Forward (+ backward) of the given views; returns the raw gradient dict (or None)."""
+        rast = self.rast
+        g = None
+        if self.backward:
+            self.flat.zero_()
+            g = self.accum()
+        for c0 in range(0, len(view_ids), self.chunk):
+            ids = view_ids[c0:c0 + self.chunk]
+            views = [self.scene.views[i] for i in ids]
+            out = rast.forward(*self.tensors, views, self.params, want_weight=True)
+            if read_counts:
+                F, longest = rast.fragment_count()
+                for i in ids:
+                    self.fragments[i] = (F / len(ids), longest)
+            if self.backward:
+                k = len(ids)
+                rast.l1_loss_grad(out["color"], [t[:k] for t in self.targets], [t[:k] for t in self.grads], self.loss)
+                rast.backward_raw([t[:k] for t in self.grads], want_intrinsics=self.want_intrinsics, accum=g)
+        return g
+
+    def time_local(self, view_ids, reps=5, warmup=2, finalize=True):
+        torch = self.torch
+        st = torch.cuda.current_stream(self.dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for it in range(warmup + reps):
+            if it == warmup:
+                e0.record(st)
+            g = self.local_step(view_ids)
+            if g is not None and finalize:
+                fin = self.rast.finalize(g)
+        e1.record(st)
+        torch.cuda.synchronize(self.dev)
+        return e0.elapsed_time(e1) / reps
+
+
+def config_block(torch, rast, dev, scene, params, peak, workload, backward=True, want_intrinsics=True, cpu=True, parity=True):
+    """frames/s, fraction of the HBM roofline, CPU frames/s and parity (view 0) of one single-GPU configuration."""
+    run = ConfigRun(torch, rast, dev, scene, params, backward=backward, want_intrinsics=want_intrinsics)
+    ids = list(range(len(scene.views)))
+    g = run.local_step(ids, read_counts=True)
+    F = sum(run.fragments[i][0] for i in ids)
+    longest = max(run.fragments[i][1] for i in ids)
+    touched = int(torch.count_nonzero(g["points"][:, 3]).item()) if g is not None else 0
+    ms = run.time_local(ids)
+    V = len(ids)
+    launches = [ids[c0:c0 + run.chunk] for c0 in range(0, V, run.chunk)]
+    bytes_step = sum(algorithmic_bytes_per_launch(scene.n, F * len(l) / V, run.P * len(l), touched if k == 0 else 0, len(l), backward)
+                     for k, l in enumerate(launches))
+    gbs = bytes_step / (ms * 1e-3) / 1e9
+    block = {"workload": workload, "ms_per_step": ms, "frames_per_s": V / (ms * 1e-3), "views_per_step": V,
+             "counts": {"N": scene.n, "F": int(F), "pixels": run.P * V, "N_touched": touched, "longest_list": int(longest)},
+             "roofline": {"bound": "hbm", "algorithmic_bytes": int(bytes_step), "achieved": gbs, "peak": peak, "unit": "GB/s",
+                          "frac": gbs / peak}}
+    del run
+    rast._lists_cache.clear()
+    rast._saved = None
+    torch.cuda.empty_cache()
+    if cpu:
+        sec, threads = cpu_oracle_run(scene, params, steps=1, warmup=0, backward=backward)
+        block["cpu_baseline"] = {"value": 1.0 / sec, "unit": UNIT, "cores": threads, "kind": "port",
+                                 "sample": "one view of this configuration, forward" + (" + backward" if backward else "")}
+    if parity:
+        try:
+            block["parity"] = parity_against_oracle(rast, scene, params, backward=backward)
+        except Exception as e:  # noqa: BLE001
+            block["parity"] = {"error": repr(e)[:300]}
+        rast._lists_cache.clear()
+        rast._saved = None
+        torch.cuda.empty_cache()
+    return block
+
+
+def balanced_assignment(costs, world):
+    """Views -> ranks, longest processing time first: the next most expensive view goes to the least loaded rank."""
+    load, mine = [0.0] * world, [[] for _ in range(world)]
+    for v in sorted(range(len(costs)), key=lambda i: -costs[i]):
+        r = min(range(world), key=lambda k: (load[k], k))
+        load[r] += costs[v]
+        mine[r].append(v)
+    return [sorted(m) for m in mine], load
+
+
+def run_configs(args, torch, dist, rast, dev, rank, world, peak):
+    from vet_b200 import scenes
+    from vet_b200.render import default_params
+
+    out = {}
+    p1 = default_params(render_mode=1, num_layers=LAYERS, num_channels=CHANNELS)
+    if world == 1 and rank == 0:
+        sc = scenes.config_planar(3_000_000, W, H, FOCAL, n_views=1, seed=2002, channels=CHANNELS)
+        out["config2_viewer_frame"] = config_block(
+            torch, rast, dev, sc, dict(p1, keep_sorted_lists=0), peak,
+            "3 M planar-scene points, one 1920x1080 view (f = 1200), 4 levels, forward only", backward=False)
+        sc = scenes.config_planar(8_000_000, 1024, 768, 900.0, n_views=4, seed=2002, channels=CHANNELS)
+        out["config3_training_step"] = config_block(
+            torch, rast, dev, sc, p1, peak,
+            "8 M planar-scene points, 4 views 1024x768 (f = 900), forward + backward with gradients to descriptors, "
+            "confidences, positions, pose and intrinsics")
+        sc = scenes.config_shells()
+        out["config4_scene_in_shells"] = config_block(
+            torch, rast, dev, sc, p1, peak,
+            "5 M planar-scene points + 4 shells of 1 M points (radii 10/20/40/80), one 1920x1080 view from the scene "
+            "centre, forward + backward")
+        del sc
+
+    # configuration 5: ONE fixed batch of 32 distinct 1920x1080 views of a 20 M-point cloud, sharded over the ranks
+    # (strong scaling of the batch: N = 1 renders all 32), gradients of 9 floats per point summed over the ranks.
+    n5, views5 = 20_000_000, 32
+    sc = scenes.config_planar(n5, W, H, FOCAL, n_views=views5, seed=5005, channels=CHANNELS)
+    peer = None
+    if world > 1 and args.exchange != "nccl":
+        try:
+            from vet_b200.dist import PeerExchange
+
+            peer = PeerExchange(rast, sc.n, sc.texture.shape[1], CHANNELS, dev,
+                                multicast=None if args.exchange == "auto" else args.exchange == "multicast")
+            peer.ctas_per_sm = args.exchange_ctas
+        except Exception:  # noqa: BLE001
+            peer = None
+        ok = torch.tensor([0.0 if peer is None else 1.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() < 1.0:
+            peer = None
+    run = ConfigRun(torch, rast, dev, sc, p1, want_intrinsics=False, flat=None if peer is None else peer.raw)
+    st = torch.cuda.current_stream(dev)
+
+    def sharded_step(mine):
+        g = run.local_step(mine)
+        if peer is not None:
+            return peer.run(g)
+        if world > 1:
+            dist.all_reduce(run.flat)
+            dist.all_reduce(g["pose"])
+            dist.all_reduce(g["pose_count"])
+        return rast.finalize(g)
+
+    def time_sharded(assignment, reps=3, warmup=1):
+        mine = assignment[rank]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(warmup):
+            sharded_step(mine)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        e0.record(st)
+        for _ in range(reps):
+            sharded_step(mine)
+        e1.record(st)
+        torch.cuda.synchronize(dev)
+        c0.record(st)  # this rank's own work without the exchange: how unequal the shards are
+        run.local_step(mine)
+        c1.record(st)
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([e0.elapsed_time(e1) / reps, c0.elapsed_time(c1)], dtype=torch.float64, device=dev)
+        per = [torch.zeros_like(t) for _ in range(world)]
+        if world > 1:
+            dist.all_gather(per, t)
+        else:
+            per = [t]
+        step_ms = max(float(x[0].item()) for x in per)
+        local = [float(x[1].item()) for x in per]
+        return step_ms, local
+
+    # per-view fragment counts (what a training loop has from the previous step): one launch per view, round robin
+    round_robin = [[v for v in range(views5) if v % world == r] for r in range(world)]
+    run.chunk = 1
+    run.backward, keep = False, run.backward
+    run.local_step(round_robin[rank], read_counts=True)
+    run.chunk, run.backward = 4, keep
+    frag = torch.zeros(views5, dtype=torch.float64, device=dev)
+    for v, (F, _) in run.fragments.items():
+        frag[v] = F
+    if world > 1:
+        dist.all_reduce(frag)
+    frag = [float(x) for x in frag.tolist()]
+    costs = [f + 4.0 * run.P for f in frag]  # work units of a view: one per fragment, four per pixel
+    balanced, load = balanced_assignment(costs, world)
+    rr_ms, rr_local = time_sharded(round_robin)
+    bal_ms, bal_local = (rr_ms, rr_local) if world == 1 else time_sharded(balanced)
+    F5 = sum(frag)
+    touched = 0
+    block = {"workload": f"{n5} planar-scene points replicated, one batch of {views5} distinct 1920x1080 views sharded over "
+                         f"{world} GPU(s), forward + backward, 9 gradient floats per point summed over the ranks"
+                         + (f" ({'multicast' if peer is not None and peer.multicast else 'peer' if peer is not None else 'nccl'})" if world > 1 else ""),
+             "scaling": "strong", "n_gpus": world, "views_per_step": views5,
+             "round_robin": {"ms_per_step": rr_ms, "frames_per_s": views5 / (rr_ms * 1e-3), "local_ms_per_rank": [round(x, 3) for x in rr_local],
+                             "slowest_over_fastest_rank": max(rr_local) / max(min(rr_local), 1e-9)},
+             "balanced_by_fragments": {"ms_per_step": bal_ms, "frames_per_s": views5 / (bal_ms * 1e-3),
+                                       "local_ms_per_rank": [round(x, 3) for x in bal_local],
+                                       "slowest_over_fastest_rank": max(bal_local) / max(min(bal_local), 1e-9),
+                                       "views_per_rank": [len(m) for m in balanced]},
+             "fragments_per_view": {"min": min(frag), "max": max(frag), "total": F5},
+             "exchange_bytes_per_rank": 36 * n5}
+    best = min(rr_ms, bal_ms)
+    bytes_step = sum(algorithmic_bytes_per_launch(n5, F5 * 4 / views5, run.P * 4, 0, 4, True) for _ in range(views5 // 4)) + 80 * n5
+    block["roofline"] = {"bound": "hbm", "algorithmic_bytes": int(bytes_step), "achieved": bytes_step / world / (best * 1e-3) / 1e9,
+                         "peak": peak, "unit": "GB/s per GPU", "frac": bytes_step / world / (best * 1e-3) / 1e9 / peak}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sec, threads = cpu_oracle_run(sc, p1, steps=1, warmup=0)
+        block["cpu_baseline"] = {"value": 1.0 / sec, "unit": UNIT, "cores": threads, "kind": "port",
+                                 "sample": "one view of this configuration, forward + backward"}
+    out["config5_sharded_batch"] = block
+    return out
 
 
 # DRAM traffic of each kernel relative to its algorithmic bytes, from the ncu captures summarised under profiles/

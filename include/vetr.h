@@ -170,6 +170,12 @@ int64_t vetr_item_table_entries(int64_t capacity, int64_t n_pixels_total);
 /* Upper bound of the number of fragments: n * num_layers * n_views (x4 in bilinear mode). */
 int64_t vetr_max_fragments(int n_points, int n_views, const vetr_params* params);
 
+/* Records the fragment buffer of vetr_lists must hold so that a call of n_views w x h views can never overflow: the
+ * bound above in modes 1-3 (the reference sizes collections[b][l] after reading the counts back, PointRenderer.cu:796-822;
+ * here nothing is read back); in mode 0, which keeps one accumulator record per pixel instead of lists, the size of the
+ * pixel space, n_views * vetr_pyramid_pixels. */
+int64_t vetr_list_capacity(int n_points, int n_views, int w, int h, const vetr_params* params);
+
 /* Forward pass: CountingPrepassMulti + exclusive_scan + CollectMulti + SortMulti + BlendMulti / BlendMultiBilinear +
  * CreateMask for all views and levels (BlendPointCloudForward, PointRenderer.cu:657-1069).
  *   dropout    [n_views, n] float device array, 1 = point dropped (PointRenderer.cu:461-468), or NULL
@@ -384,7 +390,8 @@ int vetr_get_lists(vetr_ctx* ctx, const vetr_lists* lists, int w, int h, int num
  *               advances its copy to the list ends); status [4] = {total, overflow flag, longest list, work items};
  *               items [items_capacity >= vetr_item_table_entries(capacity, n_pixels)]
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and should therefore come before
- * any stream capture on that device; it is not safe to make that first call from two threads at once.  All calls share
+ * any stream capture on that device; it is not safe to make that first call from two threads at once.  The kernels are
+ * launched on `device`; the caller's current device is the same after the call as before it.  All calls share
  * the one array: it is fully rewritten by every call (nothing needs clearing), the status words are zeroed by the call,
  * and two calls whose kernels overlap on the GPU (different streams, same device) race.  Calls no cudaMalloc / cudaFree. */
 int vetr_scan_counts_static(int device, void* cuda_stream, const int32_t* counts, int64_t n_pixels, int64_t capacity,

@@ -172,6 +172,19 @@ def threads() -> int:
     return int(lib().vo_threads())
 
 
+def use_all_host_threads() -> int:
+    """Lets the oracle use every core this process may run on, whatever OMP_NUM_THREADS says (process launchers such as
+    torchrun set it to 1 for their workers).  Returns the thread count now in use."""
+    import os
+
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().vo_set_threads(C.c_int(max(1, n)))
+    return threads()
+
+
 def grid_loss(scene, view, bb_min, bb_len, loss_img, dist_cutoff: float = 20.0):
     """FillSceneGridWithLossRasterize on the CPU: returns (value [n_cells] f32, access count [n_cells] i32)."""
     bb_min = np.ascontiguousarray(bb_min, np.float32)

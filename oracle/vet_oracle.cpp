@@ -410,6 +410,13 @@ int vo_threads()
     return 1;
 #endif
 }
+// Number of OpenMP threads of the following calls (a launcher may have set OMP_NUM_THREADS=1 for the process).
+void vo_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#endif
+}
 
 // Forward.  out_color[l] is [B,C,h_l,w_l]; out_weight[l], out_mask[l] (nullable), out_depth[l] (nullable) are
 // [B,1,h_l,w_l].  Returns the number of fragments F, or a negative value on invalid arguments.
@@ -700,6 +707,7 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
         double v_ = o.abs_mode ? std::fabs((double)(v)) : (double)(v);           \
         _Pragma("omp atomic") (dst) += v_;                                       \
     } while (0)
+#define ACCL(dst, v) (dst) += (o.abs_mode ? std::fabs((double)(v)) : (double)(v))  /* a thread's own accumulator */
     const int C = o.C, B = o.B;
     const bool bilinear = prm.render_mode == 3;
     const int n_tex     = o.n_tex;
@@ -822,9 +830,15 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
             const float* K   = o.intr + 13 * cam.camera_index;
             float crop2[5];
             for (int k = 0; k < 5; ++k) crop2[k] = cam.crop[k] * level_scale;  // IntrinsicsPinhole::scale
-            // Rows in parallel; the shared fp64 accumulators are updated atomically (their summation order then
-            // varies from run to run at the 1e-16 level, far below what is compared).
-#pragma omp parallel for schedule(dynamic, 4)
+            // Rows in parallel; the per-point fp64 accumulators are updated atomically (their summation order then
+            // varies from run to run at the 1e-16 level, far below what is compared).  The sums that every pixel of a
+            // view adds to (camera, background, descriptor 0's confidence term of the background entry) are kept per
+            // thread and added once per thread: atomics on those few addresses would serialise the threads.
+#pragma omp parallel
+            {
+            double t_bg[4] = {0, 0, 0, 0}, t_conf0 = 0, t_pose[6] = {0, 0, 0, 0, 0, 0}, t_pose_count = 0, t_intr[13], t_intr_count = 0;
+            for (int k = 0; k < 13; ++k) t_intr[k] = 0;
+#pragma omp for schedule(dynamic, 4) nowait
             for (int y = 0; y < lv.h; ++y)
                 for (int x = 0; x < lv.w; ++x)
                 {
@@ -877,7 +891,7 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                                     if (fg)
                                         ACC(g_texture[(int64_t)ci * n_tex + tex_of(t)], g_colors[ci] * inv_w);
                                     else
-                                        ACC(g_background[ci], g_colors[ci] * inv_w);
+                                        ACCL(t_bg[ci], g_colors[ci] * inv_w);
                                 }
                                 if (fg)
                                 {
@@ -940,13 +954,16 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                                 if (fg)
                                     ACC(g_texture[(int64_t)ci * n_tex + tex], g_col);
                                 else
-                                    ACC(g_background[ci], g_col);
+                                    ACCL(t_bg[ci], g_col);
                                 g_alpha += col[ci] * gin[ci];
                             }
                             g_alpha *= T;
                             if (!bilinear)
                             {
-                                if (fg || prm.background_alpha_to_point0) ACC(g_confidence[tex], g_alpha);
+                                if (fg)
+                                    ACC(g_confidence[tex], g_alpha);
+                                else if (prm.background_alpha_to_point0)
+                                    ACCL(t_conf0, g_alpha);  // the background entry's texture index stays 0
                             }
                             else if (fg)
                                 galpha[s + i] += o.abs_mode ? std::fabs(g_alpha) : g_alpha;
@@ -1043,24 +1060,40 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                         }
                         if (g_pose)
                         {
-                            for (int k = 0; k < 6; ++k) ACC(g_pose[6 * cam.image_index + k], bo.g_pose[k]);
-                            _Pragma("omp atomic") g_pose_count[cam.image_index] += bilinear ? 1.0 : (double)(1.f / 1024.f);
+                            for (int k = 0; k < 6; ++k) ACCL(t_pose[k], bo.g_pose[k]);
+                            t_pose_count += bilinear ? 1.0 : (double)(1.f / 1024.f);
                         }
                         if (g_intr)
                         {
                             bo.g_k[4] *= 0;
-                            for (int k = 0; k < 5; ++k) ACC(g_intr[13 * cam.camera_index + k], prm.K_gradient_factor * bo.g_k[k]);
+                            for (int k = 0; k < 5; ++k) ACCL(t_intr[k], prm.K_gradient_factor * bo.g_k[k]);
                             bo.g_dis[2] *= 0.25f;
                             for (int k = 3; k < 8; ++k) bo.g_dis[k] *= 0.1f;
-                            for (int k = 0; k < 8; ++k)
-                                ACC(g_intr[13 * cam.camera_index + 5 + k], prm.distortion_gradient_factor * bo.g_dis[k]);
-                            _Pragma("omp atomic") g_intr_count[cam.camera_index] += (double)(1.f / 1024.f);
+                            for (int k = 0; k < 8; ++k) ACCL(t_intr[5 + k], prm.distortion_gradient_factor * bo.g_dis[k]);
+                            t_intr_count += (double)(1.f / 1024.f);
                         }
                     }
                 }
+#pragma omp critical
+            {
+                for (int ci = 0; ci < C; ++ci) g_background[ci] += t_bg[ci];
+                g_confidence[0] += t_conf0;
+                if (g_pose)
+                {
+                    for (int k = 0; k < 6; ++k) g_pose[6 * cam.image_index + k] += t_pose[k];
+                    g_pose_count[cam.image_index] += t_pose_count;
+                }
+                if (g_intr)
+                {
+                    for (int k = 0; k < 13; ++k) g_intr[13 * cam.camera_index + k] += t_intr[k];
+                    g_intr_count[cam.camera_index] += t_intr_count;
+                }
+            }
+            }
         }
     }
 #undef ACC
+#undef ACCL
     return 0;
 }
 

@@ -37,6 +37,10 @@ def test_host_only_entry_points():
     assert lib.vetr_max_fragments(1000, 3, C.byref(p)) == 12000
     p.render_mode = 3
     assert lib.vetr_max_fragments(1000, 3, C.byref(p)) == 48000
+    # the buffer bound: fragments in modes 1-3, one accumulator record per pixel of the pixel space in mode 0
+    assert lib.vetr_list_capacity(1000, 3, 64, 48, C.byref(p)) == 48000
+    p.render_mode = 0
+    assert lib.vetr_list_capacity(500, 2, 256, 256, C.byref(p)) == 2 * lib.vetr_pyramid_pixels(256, 256, 4)
     assert lib.vetr_item_table_entries(0, 0) >= 2
     assert lib.vetr_item_table_entries(10**6, 10**6) > (10**6 + 4 * 10**6) // 1024
     assert lib.vetr_strerror(0) == b"ok"

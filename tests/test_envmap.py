@@ -11,31 +11,8 @@ import torch
 import torch.nn.functional as F
 
 from oracle import oracle as O
+from tests import util
 from vet_b200 import scenes
-
-
-def _scene(n_views=2, w=80, h=56, f=60.0, seed=3):
-    sc = scenes.tiny_scene(n=16, w=w, h=h, n_views=n_views, seed=seed)
-    intr = scenes.pinhole_intrinsics(f, f * 1.1, w / 2 - 0.5, h / 2 + 0.25)
-    sc.intrinsics = np.repeat(intr[None].astype(np.float32), sc.intrinsics.shape[0], 0)
-    return sc
-
-
-def _env(rng, S=4, R=48, C=4, up_axis=0, non_subzero=False, inner_radius=20.0):
-    density = rng.normal(0.0, 2.0, size=(S, R, R)).astype(np.float32)
-    color = rng.normal(0.3, 1.0, size=(C, S, R, R)).astype(np.float32)
-    return O.EnvMap(density, color, inner_radius=inner_radius, up_axis=up_axis, non_subzero=non_subzero)
-
-
-def _weights(rng, sc, L):
-    out = []
-    for l in range(L):
-        w = rng.uniform(0.0, 1.0, size=(len(sc.views), 1, sc.views[0].h >> l, sc.views[0].w >> l)).astype(np.float32)
-        thin = (w >= 0.1) & (w < 0.2)
-        w[thin] = (w[thin] - 0.1) * 0.009  # nearly covered pixels: below the 0.001 threshold of no_envmap_at_points
-        w[(w < 0.1) & ~thin] = 0.0         # fully covered pixels
-        out.append(w)
-    return out
 
 
 def _rays_f64(sc, view, level):
@@ -67,10 +44,10 @@ def _rays_f64(sc, view, level):
 
 
 def test_sample_coordinates_against_float64():
-    sc = _scene()
+    sc = util.env_scene()
     rng = np.random.default_rng(0)
     for up_axis in (0, 1, 2):
-        env = _env(rng, S=4, up_axis=up_axis, inner_radius=3.0)  # the orbit cameras sit outside the first sphere
+        env = util.env_map(rng, S=4, up_axis=up_axis, inner_radius=3.0)  # the orbit cameras sit outside the first sphere
         for level in (0, 1):
             uvz, hit = O.envmap_uvz(sc, sc.views[1], level, env)
             o, d = _rays_f64(sc, sc.views[1], level)
@@ -147,11 +124,11 @@ def _torch_forward_mps5(env, uvz, hit, T0, density_t, color_t):
 
 @pytest.mark.parametrize("non_subzero,S", [(False, 4), (True, 3), (False, 1)])
 def test_forward_and_backward_against_libtorch_operators(non_subzero, S):
-    sc = _scene()
+    sc = util.env_scene()
     rng = np.random.default_rng(5)
-    env = _env(rng, S=S, non_subzero=non_subzero)
+    env = util.env_map(rng, S=S, non_subzero=non_subzero)
     L = 2
-    weight = _weights(rng, sc, L)
+    weight = util.env_weights(rng, sc, L)
     out = O.envmap_forward(sc, sc.views, L, env, weight)
     grad_out = [rng.standard_normal(o.shape).astype(np.float32) for o in out]
     gd, gc, md, mc = O.envmap_backward(sc, sc.views, L, env, weight, grad_out)
@@ -177,11 +154,11 @@ def test_forward_and_backward_against_libtorch_operators(non_subzero, S):
 
 
 def test_flags():
-    sc = _scene()
+    sc = util.env_scene()
     rng = np.random.default_rng(9)
-    env = _env(rng)
+    env = util.env_map(rng)
     L = 2
-    weight = _weights(rng, sc, L)
+    weight = util.env_weights(rng, sc, L)
     plain = O.envmap_forward(sc, sc.views, L, env, weight)
     start = [rng.standard_normal(o.shape).astype(np.float32) for o in plain]
     added = O.envmap_forward(sc, sc.views, L, env, weight, flags=O.ENV_ADD, out=[s.copy() for s in start])
@@ -234,51 +211,13 @@ def test_fixture_restatement_and_libtorch_values():
 # CUDA kernels against the restatement
 
 
-def _gpu_run(sc, env, L, weight, flags, grad_out=None, start=None):
-    from vet_b200.render import Rasterizer
-
-    dev = torch.device("cuda:0")
-    rast = Rasterizer(0)
-    poses, intr = torch.from_numpy(sc.poses).to(dev), torch.from_numpy(sc.intrinsics).to(dev)
-    density, color = torch.from_numpy(env.density).to(dev), torch.from_numpy(env.color).to(dev)
-    kw = dict(up_axis=env.up_axis, non_subzero=env.non_subzero, flags=flags)
-    w_t = [torch.from_numpy(w).to(dev) for w in weight]
-    out_t = [torch.from_numpy(s).to(dev) for s in start] if start is not None else None
-    out_t = rast.envmap_forward(poses, intr, sc.views, L, density, color, env.radii, w_t, out=out_t, **kw)
-    res = [o.cpu().numpy() for o in out_t]
-    if grad_out is None:
-        return res
-    g_t = [torch.from_numpy(g).to(dev) for g in grad_out]
-    gd, gc = rast.envmap_backward(poses, intr, sc.views, L, density, color, env.radii, w_t, g_t, **kw)
-    return res, gd.cpu().numpy(), gc.cpu().numpy()
-
-
-def _sample_tolerance(env):
-    """A coordinate that differs by e texels changes a bilinear sample by at most e x the largest texel difference; the
-    device's asinf / atan2f / expf differ from the host's by a few ulp of a coordinate of size resolution."""
-    e = 8 * np.finfo(np.float32).eps * env.resolution
-    step = max(np.abs(np.diff(env.color, axis=-1)).max(), np.abs(np.diff(env.color, axis=-2)).max())
-    return float(e * step * 2 + 1e-5)
-
-
-def _grad_tolerance(mag, env):
-    """Bound of |device sum - host sum| per texel.  mag: the summed magnitudes of a texel's addends.  1e-5 of them for the
-    order of the fp32 sums; and a sample coordinate that differs by e texels (asinf / atan2f differ by a few ulp between
-    device and host) moves the fraction e of an addend between neighbouring texels, so a texel can gain or lose e times
-    what its 3 x 3 neighbourhood receives."""
-    e = 8 * np.finfo(np.float32).eps * env.resolution
-    m = torch.from_numpy(mag).reshape(-1, 1, env.resolution, env.resolution)
-    near = (F.avg_pool2d(m, 3, stride=1, padding=1, count_include_pad=True) * 9).reshape(mag.shape).numpy()
-    return 1e-5 * mag + 4 * e * near + 1e-6
-
-
 @pytest.mark.gpu
 @pytest.mark.parametrize("up_axis,non_subzero,S,flags", [(0, False, 4, 0), (1, True, 3, O.ENV_NOT_AT_POINTS), (2, False, 1, 0),
                                                          (0, False, 8, 0)])
 def test_gpu_envmap_matches_oracle(up_axis, non_subzero, S, flags):
-    sc = _scene(n_views=3, w=200, h=120, f=150.0)
+    sc = util.env_scene(n_views=3, w=200, h=120, f=150.0)
     rng = np.random.default_rng(11)
-    env = _env(rng, S=S, R=64, up_axis=up_axis, non_subzero=non_subzero)
+    env = util.env_map(rng, S=S, R=64, up_axis=up_axis, non_subzero=non_subzero)
     # smooth textures: the comparison is of the arithmetic, not of how a 1e-6 texel shift samples noise
     k = torch.ones(1, 1, 5, 5) / 25
     env.color = F.conv2d(torch.from_numpy(env.color).reshape(-1, 1, 64, 64), k, padding=2).reshape(env.color.shape).numpy()
@@ -287,31 +226,31 @@ def test_gpu_envmap_matches_oracle(up_axis, non_subzero, S, flags):
         sign = np.where(np.arange(env.channels) % 2 == 0, -1.0, 1.0).astype(np.float32)[:, None, None, None]
         env.color = sign * (np.abs(env.color) + 0.1)
     L = 3
-    weight = _weights(rng, sc, L)
+    weight = util.env_weights(rng, sc, L)
     ref = O.envmap_forward(sc, sc.views, L, env, weight, flags=flags)
     grad_out = [rng.standard_normal(o.shape).astype(np.float32) for o in ref]
     rgd, rgc, md, mc = O.envmap_backward(sc, sc.views, L, env, weight, grad_out, flags=flags)
-    out, gd, gc = _gpu_run(sc, env, L, weight, flags, grad_out)
-    tol = _sample_tolerance(env)
+    out, gd, gc = util.env_gpu_run(sc, env, L, weight, flags, grad_out)
+    tol = util.env_sample_tolerance(env)
     for o, r in zip(out, ref):
         assert np.abs(o - r).max() <= tol
     assert np.abs(rgc).max() > 0
-    assert np.all(np.abs(gd - rgd) <= _grad_tolerance(md, env))
-    assert np.all(np.abs(gc - rgc) <= _grad_tolerance(mc, env))
+    assert np.all(np.abs(gd - rgd) <= util.env_grad_tolerance(md, env))
+    assert np.all(np.abs(gc - rgc) <= util.env_grad_tolerance(mc, env))
 
 
 @pytest.mark.gpu
 def test_gpu_envmap_add_and_depth_test_flags():
-    sc = _scene(n_views=2, w=96, h=64, f=80.0)
+    sc = util.env_scene(n_views=2, w=96, h=64, f=80.0)
     rng = np.random.default_rng(13)
-    env = _env(rng, S=4, R=32)
+    env = util.env_map(rng, S=4, R=32)
     L = 2
-    weight = [np.floor(w * 3) for w in _weights(rng, sc, L)]
+    weight = [np.floor(w * 3) for w in util.env_weights(rng, sc, L)]
     flags = O.ENV_ADD | O.ENV_DEPTH_TEST_WEIGHT
     start = [rng.standard_normal((2, 4, 64 >> l, 96 >> l)).astype(np.float32) for l in range(L)]
     ref = O.envmap_forward(sc, sc.views, L, env, weight, flags=flags, out=[s.copy() for s in start])
-    out = _gpu_run(sc, env, L, weight, flags, start=start)
-    tol = _sample_tolerance(env)
+    out = util.env_gpu_run(sc, env, L, weight, flags, start=start)
+    tol = util.env_sample_tolerance(env)
     for o, r in zip(out, ref):
         assert np.abs(o - r).max() <= tol
 
@@ -321,9 +260,9 @@ def test_gpu_envmap_rejects_distortion_and_bad_arguments():
     from vet_b200 import _lib
     from vet_b200.render import Rasterizer
 
-    sc = _scene()
+    sc = util.env_scene()
     rng = np.random.default_rng(1)
-    env = _env(rng, R=16)
+    env = util.env_map(rng, R=16)
     dev = torch.device("cuda:0")
     rast = Rasterizer(0)
     poses = torch.from_numpy(sc.poses).to(dev)
@@ -349,11 +288,11 @@ def test_gpu_envmap_against_fixture():
     g, sc, env, L = _fixture()
     weight = [g[f"env_weight_l{l}"] for l in range(L)]
     gout = [g[f"env_gout_l{l}"] for l in range(L)]
-    out, gd, gc = _gpu_run(sc, env, L, weight, 0, gout)
-    tol = _sample_tolerance(env)
+    out, gd, gc = util.env_gpu_run(sc, env, L, weight, 0, gout)
+    tol = util.env_sample_tolerance(env)
     for l in range(L):
         assert np.abs(out[l] - g[f"env_out_l{l}"]).max() <= tol
         assert np.abs(out[l] - g[f"env_torch_l{l}"]).max() <= tol
     for mine, ref, mag in ((gd, g["env_torch_g_density"], g["env_mag_density"]), (gc, g["env_torch_g_color"], g["env_mag_color"]),
                            (gd, g["env_g_density"], g["env_mag_density"]), (gc, g["env_g_color"], g["env_mag_color"])):
-        assert np.all(np.abs(mine - ref) <= _grad_tolerance(mag, env))
+        assert np.all(np.abs(mine - ref) <= util.env_grad_tolerance(mag, env))

@@ -185,6 +185,31 @@ def test_plumbing_config_l1(rasterizer):
     _roundtrip(rasterizer, sc, default_params(render_mode=3), grads="l1")
 
 
+@pytest.mark.parametrize("mode", [1, 3])
+def test_benchmark_configs_2_3_4(rasterizer, mode):
+    """The generators of benchmark configurations 2, 3 and 4 at a size the oracle finishes in seconds (the full sizes are
+    compared inside bench.py): the viewer frame (forward only, 1920x1080), the training step (four 1024x768 views, gradients
+    to descriptors, confidences, positions, pose and intrinsics) and the scene inside four concentric point shells."""
+    params = default_params(render_mode=mode)
+    sc = scenes.config_planar(300_000, 1920, 1080, 1200.0, n_views=1, seed=2002)
+    ora = util.run_oracle(sc, params)
+    gpu = util.run_gpu(rasterizer, sc, params)
+    util.compare_forward(gpu, ora, exact_images=True)
+    sc = scenes.config_planar(300_000, 1024, 768, 900.0, n_views=4, seed=3003)
+    gpu, _ = _roundtrip(rasterizer, sc, params, grads="l1")
+    assert np.abs(gpu["bwd_raw"]["pose"]).sum() > 0 and np.abs(gpu["bwd_raw"]["intrinsics"]).sum() > 0
+    sc = scenes.config_shells(n_scene=180_000, n_shell=40_000)
+    gpu, _ = _roundtrip(rasterizer, sc, params, grads="l1")
+    assert gpu["F"] > 100_000
+
+
+def test_mode0_sparse_cloud_on_a_large_image(rasterizer):
+    """Mode 0 keeps one accumulator record per pixel: with fewer points than pixels the buffer is sized by the pixel space
+    (vetr_list_capacity), not by the fragment bound."""
+    sc = scenes.tiny_scene(n=500, w=256, h=256, n_views=2, seed=91)
+    _mode0_roundtrip(rasterizer, sc, default_params(render_mode=0))
+
+
 def test_key_buffer_overflow_is_reported(rasterizer):
     from vet_b200 import _lib as L
 

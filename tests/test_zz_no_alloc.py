@@ -1,7 +1,7 @@
 """vetr_scan_counts_static: the forward pass's scan as a stand-alone call that allocates no device memory (for hosts that
-must not allocate while rendering: its scratch is a fixed array inside the library).  Checked against what the regular
-entry point, vetr_forward, leaves in its list buffers for the same per-pixel counts, on two calls in a row with different
-inputs (the second call reuses the shared scratch array and must not see the first call's contents)."""
+must not allocate while rendering: its scratch is a fixed array inside the library).  Checked against a numpy prefix sum
+of the same counts and against what the regular entry point, vetr_forward, leaves in its list buffers, on two calls in a
+row with different inputs (the second call reuses the shared scratch array and must not see the first call's contents)."""
 import ctypes as C
 
 import numpy as np
@@ -12,6 +12,8 @@ from vet_b200 import scenes
 from vet_b200.render import default_params, scene_to_device
 
 pytestmark = pytest.mark.gpu
+
+ITEM_UNITS, ITEM_PIXELS = 512, 128  # work units of one item (1 per fragment, 4 per pixel) and the pixels that allows
 
 
 def _forward_lists(rast, scene, params):
@@ -37,6 +39,19 @@ def _check(rast, scene, params):
                                          C.c_void_p(status.data_ptr()), C.c_void_p(items.data_ptr()), items.numel())
     assert rc == L.OK
     torch.cuda.synchronize()
+    # independent of the library: the offsets are the exclusive prefix sum of the counts, the status words hold the total
+    # and the longest list, and the work-item table is ascending, starts at pixel 0 and ends at the pixel count
+    c = counts.cpu().numpy().astype(np.int64)
+    np.testing.assert_array_equal(ends.cpu().numpy(), np.cumsum(c) - c)
+    st = status.cpu().numpy()
+    assert st[0] == c.sum() and st[1] == 0 and st[2] == c.max()
+    table = items[:int(st[3]) + 1].cpu().numpy()
+    assert table[0] == 0 and table[-1] == n and np.all(np.diff(table) >= 0)
+    # every item holds at most ITEM_PIXELS pixels, and fewer than ITEM_UNITS fragments beyond its first pixel's list
+    first = np.minimum(table[:-1], n - 1)
+    frag_end = np.concatenate([np.cumsum(c), [c.sum()]])
+    beyond_first = frag_end[np.maximum(table[1:], 1) - 1] - frag_end[first]
+    assert np.all(np.diff(table) <= ITEM_PIXELS) and np.all(beyond_first < ITEM_UNITS)
     # vetr_forward's collection pass has advanced its offsets from list starts to list ends: ends = starts + counts
     np.testing.assert_array_equal((ends + counts).cpu().numpy(), lists.ends.cpu().numpy())
     st, st_ref = status.cpu().numpy(), lists.status.cpu().numpy()

@@ -165,3 +165,102 @@ def compare_backward(gpu_raw, ora, channels, rtol=1e-5, floor_rel=0.0):
     if "intrinsics" in gpu_raw and "intrinsics" in b:
         assert_sum_close("g_intrinsics", gpu_raw["intrinsics"], b["intrinsics"], m["intrinsics"], rtol)
         assert_sum_close("g_intrinsics_count", gpu_raw["intrinsics_count"], b["intrinsics_count"], m["intrinsics_count"], rtol)
+
+
+def parity_report(gpu, ora, channels, rtol=1e-5) -> dict:
+    """The comparisons of compare_forward / compare_backward as numbers instead of assertions (for bench.py, which
+    reports parity at sizes the tests do not run)."""
+    rep = dict(F=int(gpu["F"]), F_equal=bool(gpu["F"] == ora["F"]),
+               counts_equal=bool(np.array_equal(gpu["counts"], ora["counts"])),
+               keys_equal=bool(np.array_equal(gpu["keys"], ora["keys"])))
+    rep["image_max_abs"] = max(float(np.abs(a.astype(np.float64) - b).max()) for name in ("color", "weight", "depth")
+                               for a, b in zip(gpu["fwd"][name], ora["fwd"][name]))
+    rep["images_bit_equal"] = all(np.array_equal(a, b) for name in ("color", "weight", "mask", "depth")
+                                  for a, b in zip(gpu["fwd"][name], ora["fwd"][name]))
+    if "bwd_raw" in gpu and "bwd" in ora:
+        g, b, m = gpu["bwd_raw"], ora["bwd"], ora["bwd_mag"]
+        pairs = [(g["desc"][:, :channels].T, "texture"), (g["conf"], "confidence"), (g["background"], "background")]
+        if "points" in g and "points" in b:
+            pairs.append((g["points"][:, :3], "points"))
+            rep["hit_counts_equal"] = bool(np.array_equal(g["points"][:, 3], b["points_count"]))
+        for key in ("pose", "intrinsics"):
+            if key in g and key in b:
+                pairs.append((g[key], key))
+        worst = {}
+        for got, key in pairs:
+            want, mag = np.asarray(b[key], np.float64), np.asarray(m[key], np.float64)
+            bound = rtol * np.maximum(mag, np.abs(want)) + 1e-30
+            worst[key] = float((np.abs(np.asarray(got, np.float64) - want) / bound).max()) if want.size else 0.0
+        rep["grad_worst_over_bound"] = max(worst.values())
+        rep["grad_worst_over_bound_by_tensor"] = {k: round(v, 4) for k, v in worst.items()}
+    return rep
+
+
+# ---- environment map cases (shared by tests/test_envmap.py and the smoke check)
+
+def env_scene(n_views=2, w=80, h=56, f=60.0, seed=3):
+    from vet_b200 import scenes
+
+    sc = scenes.tiny_scene(n=16, w=w, h=h, n_views=n_views, seed=seed)
+    intr = scenes.pinhole_intrinsics(f, f * 1.1, w / 2 - 0.5, h / 2 + 0.25)
+    sc.intrinsics = np.repeat(intr[None].astype(np.float32), sc.intrinsics.shape[0], 0)
+    return sc
+
+
+def env_map(rng, S=4, R=48, C=4, up_axis=0, non_subzero=False, inner_radius=20.0):
+    density = rng.normal(0.0, 2.0, size=(S, R, R)).astype(np.float32)
+    color = rng.normal(0.3, 1.0, size=(C, S, R, R)).astype(np.float32)
+    return O.EnvMap(density, color, inner_radius=inner_radius, up_axis=up_axis, non_subzero=non_subzero)
+
+
+def env_weights(rng, sc, L):
+    out = []
+    for l in range(L):
+        w = rng.uniform(0.0, 1.0, size=(len(sc.views), 1, sc.views[0].h >> l, sc.views[0].w >> l)).astype(np.float32)
+        thin = (w >= 0.1) & (w < 0.2)
+        w[thin] = (w[thin] - 0.1) * 0.009  # nearly covered pixels: below the 0.001 threshold of no_envmap_at_points
+        w[(w < 0.1) & ~thin] = 0.0         # fully covered pixels
+        out.append(w)
+    return out
+
+
+def env_gpu_run(sc, env, L, weight, flags, grad_out=None, start=None):
+    import torch
+    from vet_b200.render import Rasterizer
+
+    dev = torch.device("cuda:0")
+    rast = Rasterizer(0)
+    poses, intr = torch.from_numpy(sc.poses).to(dev), torch.from_numpy(sc.intrinsics).to(dev)
+    density, color = torch.from_numpy(env.density).to(dev), torch.from_numpy(env.color).to(dev)
+    kw = dict(up_axis=env.up_axis, non_subzero=env.non_subzero, flags=flags)
+    w_t = [torch.from_numpy(w).to(dev) for w in weight]
+    out_t = [torch.from_numpy(s).to(dev) for s in start] if start is not None else None
+    out_t = rast.envmap_forward(poses, intr, sc.views, L, density, color, env.radii, w_t, out=out_t, **kw)
+    res = [o.cpu().numpy() for o in out_t]
+    if grad_out is None:
+        return res
+    g_t = [torch.from_numpy(g).to(dev) for g in grad_out]
+    gd, gc = rast.envmap_backward(poses, intr, sc.views, L, density, color, env.radii, w_t, g_t, **kw)
+    return res, gd.cpu().numpy(), gc.cpu().numpy()
+
+
+def env_sample_tolerance(env):
+    """A coordinate that differs by e texels changes a bilinear sample by at most e x the largest texel difference; the
+    device's asinf / atan2f / expf differ from the host's by a few ulp of a coordinate of size resolution."""
+    e = 8 * np.finfo(np.float32).eps * env.resolution
+    step = max(np.abs(np.diff(env.color, axis=-1)).max(), np.abs(np.diff(env.color, axis=-2)).max())
+    return float(e * step * 2 + 1e-5)
+
+
+def env_grad_tolerance(mag, env):
+    """Bound of |device sum - host sum| per texel.  mag: the summed magnitudes of a texel's addends.  1e-5 of them for the
+    order of the fp32 sums; and a sample coordinate that differs by e texels (asinf / atan2f differ by a few ulp between
+    device and host) moves the fraction e of an addend between neighbouring texels, so a texel can gain or lose e times
+    what its 3 x 3 neighbourhood receives."""
+    import torch
+    import torch.nn.functional as F
+
+    e = 8 * np.finfo(np.float32).eps * env.resolution
+    m = torch.from_numpy(mag).reshape(-1, 1, env.resolution, env.resolution)
+    near = (F.avg_pool2d(m, 3, stride=1, padding=1, count_include_pad=True) * 9).reshape(mag.shape).numpy()
+    return 1e-5 * mag + 4 * e * near + 1e-6

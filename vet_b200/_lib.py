@@ -74,7 +74,7 @@ class Exchange(C.Structure):
 
 EXPORTS = [
     "vetr_create", "vetr_destroy", "vetr_set_stream", "vetr_strerror", "vetr_last_cuda_error", "vetr_pyramid_pixels",
-    "vetr_item_table_entries", "vetr_max_fragments", "vetr_forward", "vetr_backward", "vetr_finalize_gradients",
+    "vetr_item_table_entries", "vetr_max_fragments", "vetr_list_capacity", "vetr_forward", "vetr_backward", "vetr_finalize_gradients",
     "vetr_apply_tangent", "vetr_read_status", "vetr_get_lists", "vetr_set_timing", "vetr_get_timings",
     "vetr_launch_count", "vetr_scan_counts_static", "vetr_exchange_raw_floats", "vetr_exchange_out_floats",
     "vetr_exchange_finalize", "vetr_grid_loss", "vetr_l1_loss_grad", "vetr_backward_phase", "vetr_exchange_finalize_part",
@@ -115,6 +115,8 @@ def lib():
         L.vetr_item_table_entries.restype = C.c_int64
         L.vetr_max_fragments.argtypes = [C.c_int, C.c_int, C.POINTER(Params)]
         L.vetr_max_fragments.restype = C.c_int64
+        L.vetr_list_capacity.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(Params)]
+        L.vetr_list_capacity.restype = C.c_int64
         vp = C.c_void_p
         L.vetr_forward.argtypes = [vp, C.POINTER(Params), C.POINTER(Cloud), C.POINTER(Texture), C.POINTER(Cameras),
                                    C.POINTER(View), C.c_int, vp, C.POINTER(Lists), vp, vp, vp, vp]

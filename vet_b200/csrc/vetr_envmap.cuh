@@ -440,7 +440,7 @@ __global__ void __launch_bounds__(kEnvThreads, VETR_ENV_BACK_CTAS) envmap_backwa
                     if (v > a.C) continue;
                     if (v == 0 && s == a.S - 1) continue;  // the last sphere's alpha is the constant 1
                     float x = c.off[q] >= 0 ? c.w[q] * gv[v] : 0.f;
-#ifndef VETR_ENV_NO_PRESUM  // (building with it issues one atomic per lane instead: measured 3 % slower)
+                    // (one atomic per lane without this pre-sum was measured 3 % slower)
 #pragma unroll
                     for (int k = 0; k < 5; ++k)
                     {
@@ -448,9 +448,6 @@ __global__ void __launch_bounds__(kEnvThreads, VETR_ENV_BACK_CTAS) envmap_backwa
                         if (same >> k & 1) x += y;
                     }
                     if (head && c.off[q] >= 0 && x != 0.f)
-#else
-                    if (c.off[q] >= 0 && x != 0.f)
-#endif
                         atomicAdd((v == 0 ? a.g_density : a.g_color + (v - 1) * plane) + c.off[q], x);
                 }
             }

@@ -3,7 +3,8 @@
 //
 // Data layout in HBM
 //   pixel space : all views and all pyramid levels of a call form ONE array of PT = n_views * P pixels
-//                 (view-major, then level, then row-major).  counts[PT], ends[PT] (int32).
+//                 (view-major, then level, then bands of VETR_PIXEL_BAND rows, column by column inside a band; see
+//                 pixel_offset).  counts[PT], ends[PT] (int32).
 //   records     : one 32-byte record per fragment = one DRAM sector: 64-bit key (depth bits << 32 | point index),
 //                 alpha, descriptor index, descriptor.  The list of pixel g is recs[ends[g] - counts[g] .. ends[g]).
 //                 Lists of consecutive pixels are contiguous, so a CTA that owns a run of pixels streams its fragments
@@ -747,23 +748,6 @@ struct FuzzyFold
     }
 };
 
-// Optional instrumentation: cycles one thread of every CTA spends between the marks of an item kernel.
-#ifdef VETR_PHASE_TIMING
-__device__ unsigned long long g_phase_cycles[16];
-#    define PHASE_MARK(k)                                                                 \
-        do                                                                                \
-        {                                                                                 \
-            if (threadIdx.x == 0)                                                         \
-            {                                                                             \
-                long long now_ = clock64();                                               \
-                atomicAdd(&g_phase_cycles[k], (unsigned long long)(now_ - t_phase_));     \
-                t_phase_ = now_;                                                          \
-            }                                                                             \
-        } while (0)
-#else
-#    define PHASE_MARK(k)
-#endif
-
 // ---------------------------------------------------------------------------------------------------------
 // Pass 4: sort + blend.
 
@@ -789,9 +773,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
     const float bg[4]   = {f.background[0], f.background[1], f.background[2], f.C > 3 ? f.background[3] : 0.f};
     if (tid == 0) s.seg.n_long[0] = s.seg.n_long[1] = 0;
     int parity = 0;
-#ifdef VETR_PHASE_TIMING
-    long long t_phase_ = clock64();
-#endif
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x)
     {
@@ -801,7 +782,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
         lo += long_prefix(f, lo);
         if (lo >= hi) continue;
         __syncthreads();  // every warp has left the previous item
-        PHASE_MARK(8);
         parity ^= 1;
         if (tid == 0) s.seg.n_long[parity ^ 1] = 0;
         const int f0 = list_end(f, lo - 1);
@@ -829,7 +809,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
             s.tex[i]      = (int)h.w;
         }
         __syncthreads();
-        PHASE_MARK(9);
         // rank sort inside each list; keys are unique (distinct point indices), so ranks are a permutation
         for (int i = tid; i < nf; i += kThreads)
         {
@@ -841,7 +820,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
             s.perm[ss + rank] = (unsigned short)i;
         }
         __syncthreads();
-        PHASE_MARK(10);
         // write the sorted lists back for the backward pass
         if (f.keep_sorted)
             for (int r = tid; r < nf; r += kThreads)
@@ -849,7 +827,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
                 const int u = s.perm[r];
                 store_record(f, f0 + r, s.key[u], s.alpha[u], s.tex[u], s.desc[u]);
             }
-        PHASE_MARK(11);
         // fold: one thread per pixel
         if (tid < np)
         {
@@ -883,7 +860,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) sort_blend_kernel(const __
             float depth = se > ss ? __uint_as_float((unsigned)(s.key[s.perm[ss]] >> 32)) : kMaxDepth;
             write_pixel(f, out, (unsigned)(lo + tid), fold.c, fold.T, depth);
         }
-        PHASE_MARK(12);
     }
 }
 
@@ -1465,9 +1441,6 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
     float p0_acc    = 0.f;
     if (tid == 0) s.seg.n_long[0] = s.seg.n_long[1] = 0;
     int parity = 0;
-#ifdef VETR_PHASE_TIMING
-    long long t_phase_ = clock64();
-#endif
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x)
     {
@@ -1478,7 +1451,6 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
         if (lo >= hi) continue;
         {
             __syncthreads();  // every warp has left the previous item
-            PHASE_MARK(0);
             parity ^= 1;
             if (tid == 0) s.seg.n_long[parity ^ 1] = 0;
             const int f0 = list_end(f, lo - 1);
@@ -1494,7 +1466,6 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
             }
             if (tid == 0) s.seg_end[0] = 0;
             __syncthreads();
-            PHASE_MARK(1);
             const int nf = s.seg_end[np];
             for (int i = tid; i < nf; i += kThreads)
             {
@@ -1509,7 +1480,6 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
                     fragment_stage_a<kBilinear>(f, s, lo + a, s.pix[a], s.grad[a], i, h, d, blended);
             }
             __syncthreads();
-            PHASE_MARK(2);
             if (tid < np && s.pix[tid].valid)
             {
                 if constexpr (kFuzzy)
@@ -1519,7 +1489,6 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
                     sweep_list(f, s, s.seg_end[tid], s.seg_end[tid + 1], s.grad[tid], bgc, bg_acc, p0_acc);
             }
             __syncthreads();
-            PHASE_MARK(3);
             for (int i = tid; i < nf; i += kThreads)
             {
                 const float Ti     = s.trans[i];
@@ -1528,7 +1497,6 @@ __global__ void __launch_bounds__(kThreads, kFuzzy ? 1 : kMinCtas) backward_kern
                 const int a = seg_lookup(s.seg, parity, s.seg_end, i);
                 fragment_stage_b<kBilinear>(f, bp, s.pix[a], s.grad[a], s.pid[i], s.tex[i], Ti, s.dot[i], blended);
             }
-            PHASE_MARK(4);
         }
     }
     reduce_background(f, bp, s, bg_acc, p0_acc);
@@ -2687,6 +2655,20 @@ extern "C" int64_t vetr_max_fragments(int n_points, int n_views, const vetr_para
     return f;
 }
 
+extern "C" int64_t vetr_list_capacity(int n_points, int n_views, int w, int h, const vetr_params* p)
+{
+    if (!p) return -1;
+    int64_t f = vetr_max_fragments(n_points, n_views, p);
+    if (p->render_mode == VETR_MODE_FUZZY_DT)
+    {
+        // mode 0 keeps no lists: the buffer holds one accumulator record per pixel of the pixel space instead
+        const int64_t px = vetr_pyramid_pixels(w, h, p->num_layers);
+        if (px < 0) return -1;
+        f = px * n_views;
+    }
+    return f;
+}
+
 extern "C" const char* vetr_strerror(int status)
 {
     switch (status)
@@ -2800,20 +2782,6 @@ extern "C" int vetr_get_timings(vetr_ctx* ctx, float* out_ms)
 }
 
 extern "C" int64_t vetr_launch_count(const vetr_ctx* ctx) { return ctx ? ctx->launches : 0; }
-
-#ifdef VETR_PHASE_TIMING
-extern "C" int vetr_debug_phase_cycles(unsigned long long* out, int reset)
-{
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(g_phase_cycles));
-    if (reset)
-    {
-        unsigned long long z[16] = {};
-        cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z));
-    }
-    return 0;
-}
-#endif
 
 extern "C" int vetr_set_stream(vetr_ctx* ctx, void* cuda_stream)
 {
@@ -3561,7 +3529,18 @@ extern "C" int vetr_scan_counts_static(int device, void* cuda_stream, const int3
     const long long n_tiles = (n_pixels + kScanTile - 1) / kScanTile;
     if (n_tiles > kStaticScanTiles) return VETR_E_TOO_LARGE;  // more pixels than the fixed scratch covers
     if (items_capacity < vetr_item_table_entries(capacity, n_pixels)) return VETR_E_INVALID_ARG;
-    if (cudaSetDevice(device) != cudaSuccess) return VETR_E_CUDA;
+    // the launches below go to `device`; the caller's current device is put back before returning
+    int caller_device = device;
+    if (cudaGetDevice(&caller_device) != cudaSuccess) return VETR_E_CUDA;
+    struct RestoreDevice
+    {
+        int to, from;
+        ~RestoreDevice()
+        {
+            if (to != from) cudaSetDevice(to);
+        }
+    } restore{caller_device, device};
+    if (caller_device != device && cudaSetDevice(device) != cudaSuccess) return VETR_E_CUDA;
     if (!g_static_tile_ptr[device])
     {
         // The array's name is only a handle on the host; kernels need its address on THIS device.

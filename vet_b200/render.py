@@ -170,7 +170,7 @@ class Rasterizer:
         for gi, b0 in enumerate(range(0, B, L.MAX_VIEWS)):
             b1 = min(B, b0 + L.MAX_VIEWS)
             nb = b1 - b0
-            cap = capacity if capacity is not None else int(lib.vetr_max_fragments(position.shape[0], nb, C.byref(prm)))
+            cap = capacity if capacity is not None else int(lib.vetr_list_capacity(position.shape[0], nb, w, h, C.byref(prm)))
             lists = self._lists(gi, P * nb, cap, exact=capacity is not None)
             if prm.render_mode == 3 or (prm.render_mode in (1, 2) and prm.need_point_gradient):
                 lists.ensure_level_mask(nb * position.shape[0])

@@ -239,7 +239,7 @@ variable_list PointRender::forward(AutogradContext* ctx, Variable texture, Varia
         const bool point_pass = prm.render_mode == VETR_MODE_BILINEAR_BLEND ||
                                 ((prm.render_mode == VETR_MODE_FULL_BLEND || prm.render_mode == VETR_MODE_FUZZY_BLEND) &&
                                  prm.need_point_gradient);
-        GroupLists g = alloc_lists(P * nb, vetr_max_fragments(in.cloud.n, nb, &prm),
+        GroupLists g = alloc_lists(P * nb, vetr_list_capacity(in.cloud.n, nb, info->images.front().w, info->images.front().h, &prm),
                                    point_pass ? (int64_t)nb * in.cloud.n : 0, dev);
         auto views   = make_views(*info, b0, b1);
         auto pc = level_ptrs(color, b0), pw = level_ptrs(weight, b0), pd = level_ptrs(depth, b0), pm = level_ptrs(mask, b0);
