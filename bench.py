@@ -1002,7 +1002,8 @@ def config_block(torch, rast, dev, scene, params, peak, workload, backward=True,
                                  "sample": "one view of this configuration, forward" + (" + backward" if backward else "")}
     if parity:
         try:
-            block["parity"] = parity_against_oracle(rast, scene, params, backward=backward)
+            # (the sorted lists are compared too: keep them even where the timed configuration does not)
+            block["parity"] = parity_against_oracle(rast, scene, dict(params, keep_sorted_lists=1), backward=backward)
         except Exception as e:  # noqa: BLE001
             block["parity"] = {"error": repr(e)[:300]}
         rast._lists_cache.clear()

@@ -134,14 +134,13 @@ def test_environment_map_sample2(ops):
     import torch
 
     from oracle import oracle as O
-    from tests import test_envmap as E
 
     dev = torch.device("cuda", 0)
-    sc = E._scene(n_views=2, w=128, h=96, f=100.0)
+    sc = util.env_scene(n_views=2, w=128, h=96, f=100.0)
     rng = np.random.default_rng(21)
-    env = E._env(rng, S=4, R=32)
+    env = util.env_map(rng, S=4, R=32)
     L = 3
-    weight = E._weights(rng, sc, L)
+    weight = util.env_weights(rng, sc, L)
     ref = O.envmap_forward(sc, sc.views, L, env, weight)
     grads = [rng.standard_normal(r.shape).astype(np.float32) for r in ref]
     rgd, rgc, md, mc = O.envmap_backward(sc, sc.views, L, env, weight, grads)
@@ -152,13 +151,13 @@ def test_environment_map_sample2(ops):
     out = ops.environment_map_sample2(density, color, 20.0, 5.0, env.up_axis, env.non_subzero, t(sc.poses), t(sc.intrinsics),
                                       vi, vf, L, [t(w) for w in weight])
     assert len(out) == L
-    tol = E._sample_tolerance(env)
+    tol = util.env_sample_tolerance(env)
     for o, r in zip(out, ref):
         assert tuple(o.shape) == r.shape
         assert np.abs(o.detach().cpu().numpy() - r).max() <= tol
     sum((o * t(g)).sum() for o, g in zip(out, grads)).backward()
-    assert np.all(np.abs(density.grad.cpu().numpy()[0, 0] - rgd) <= E._grad_tolerance(md, env))
-    assert np.all(np.abs(color.grad.cpu().numpy()[0] - rgc) <= E._grad_tolerance(mc, env))
+    assert np.all(np.abs(density.grad.cpu().numpy()[0, 0] - rgd) <= util.env_grad_tolerance(md, env))
+    assert np.all(np.abs(color.grad.cpu().numpy()[0] - rgc) <= util.env_grad_tolerance(mc, env))
 
 
 def test_compute_radius(ops):
