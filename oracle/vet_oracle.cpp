@@ -1074,19 +1074,19 @@ int vo_backward(void* h, const float* const* grad_color, double* g_texture, doub
                         }
                     }
                 }
-#pragma omp critical
+            // (atomic: other threads may still be adding to descriptor 0's confidence gradient from their pixels)
             {
-                for (int ci = 0; ci < C; ++ci) g_background[ci] += t_bg[ci];
-                g_confidence[0] += t_conf0;
+                for (int ci = 0; ci < C; ++ci) _Pragma("omp atomic") g_background[ci] += t_bg[ci];
+                _Pragma("omp atomic") g_confidence[0] += t_conf0;
                 if (g_pose)
                 {
-                    for (int k = 0; k < 6; ++k) g_pose[6 * cam.image_index + k] += t_pose[k];
-                    g_pose_count[cam.image_index] += t_pose_count;
+                    for (int k = 0; k < 6; ++k) _Pragma("omp atomic") g_pose[6 * cam.image_index + k] += t_pose[k];
+                    _Pragma("omp atomic") g_pose_count[cam.image_index] += t_pose_count;
                 }
                 if (g_intr)
                 {
-                    for (int k = 0; k < 13; ++k) g_intr[13 * cam.camera_index + k] += t_intr[k];
-                    g_intr_count[cam.camera_index] += t_intr_count;
+                    for (int k = 0; k < 13; ++k) _Pragma("omp atomic") g_intr[13 * cam.camera_index + k] += t_intr[k];
+                    _Pragma("omp atomic") g_intr_count[cam.camera_index] += t_intr_count;
                 }
             }
             }

@@ -66,13 +66,17 @@ def test_mode2_dense_and_long_lists(rasterizer):
     sc = scenes.tiny_scene(n=12000, w=16, h=12, n_views=1, seed=5)  # lists of 300 .. 1600: whole-list kernel
     gpu, _ = _roundtrip(rasterizer, sc, default_params(render_mode=2, drop_out_points_by_radius=0, num_layers=3))
     assert 256 < gpu["longest"] <= 3072
-    # beyond 3072 fragments in one list the mode-2 backward pass skips the pixel and says so
+    # up to 4096 fragments in one list (what the reference sorts of a list) the backward pass handles the list
     sc = scenes.tiny_scene(n=30000, w=16, h=12, n_views=1, seed=5)
     params = default_params(render_mode=2, drop_out_points_by_radius=0, num_layers=3)
+    gpu, _ = _roundtrip(rasterizer, sc, params)
+    assert 3072 < gpu["longest"] <= 4096
+    # beyond that it skips the pixel and says so
+    sc = scenes.tiny_scene(n=45000, w=16, h=12, n_views=1, seed=5)
     ora = util.run_oracle(sc, params)
     gpu = util.run_gpu(rasterizer, sc, params, grads=util.random_grads(ora["fwd"]["color"]))
     util.compare_forward(gpu, ora)  # the forward pass has no such limit
-    assert gpu["longest"] > 3072
+    assert gpu["longest"] > 4096
     with pytest.raises(L.VetrError) as e:
         rasterizer.fragment_count()
     assert e.value.status == L.E_TOO_LARGE

@@ -1621,8 +1621,8 @@ __global__ void __launch_bounds__(kThreads) backward_long_kernel(const __grid_co
 
 // Mode 2, lists longer than kLongList: one CTA per list with the whole list staged (the group structure does not split
 // into blocks).  Lists beyond kFuzzyLongMax are skipped and flagged in the status word (the reference itself sorts only
-// the first 4096 fragments of a list, AlphaListSort.cu:289-290, so its result for such lists is not defined either).
-constexpr int kFuzzyLongMax = 3072;
+// the first 4096 fragments of a list, AlphaListSort.cu:289-290, so its result for longer lists is not defined either).
+constexpr int kFuzzyLongMax = 4096;  // what the reference sorts of a list (AlphaListSort.cu:289-290)
 struct FuzzyLongSmem
 {
     float4 desc[kFuzzyLongMax];
