@@ -69,6 +69,9 @@ def parse_args():
                          "segments (measured no faster at N = 2: the extra collective and launches cost what the overlap saves)")
     ap.add_argument("--torch-loss", action="store_true", help="form the L1 loss and its gradient with torch element-wise kernels")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
+    ap.add_argument("--no-graph-step", action="store_true",
+                    help="N > 1: keep the collectives and the exchange kernel outside the CUDA graph (by default the whole step, "
+                         "NCCL calls and side stream included, is one graph when every rank can capture it)")
     return ap.parse_args()
 
 
@@ -478,6 +481,31 @@ def run_ours(args):
             graph_info["error"] = repr(e)[:200]
             step = eager_step
             torch.cuda.synchronize(dev)
+        # N > 1: the whole step as ONE graph - compute, the ordering collectives, the exchange kernel(s) and the side
+        # stream of --overlap - so that no host launch sits between the compute part and the exchange.  Used only if every
+        # rank captured it (agreed with a collective outside the capture); otherwise the two-graph form above stays.
+        if graph_info["used"] and peer is not None and not args.no_graph_step:
+            captured = 1.0
+            try:
+                graph_step = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph_step, capture_error_mode="thread_local"):
+                    loss_whole, fin_whole = eager_step(static_targets)
+            except Exception as e:  # noqa: BLE001
+                captured = 0.0
+                graph_info["whole_step_error"] = repr(e)[:200]
+            torch.cuda.synchronize(dev)
+            agreed = torch.tensor([captured], device=dev)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if agreed.item() >= 1.0:
+                def step(targets):  # noqa: F811
+                    if targets is not static_targets:
+                        for dst, src in zip(static_targets, targets):
+                            if dst.data_ptr() != src.data_ptr():
+                                dst.copy_(src, non_blocking=True)
+                    graph_step.replay()
+                    return loss_whole, fin_whole
+
+            graph_info["whole_step"] = bool(agreed.item() >= 1.0)
 
     # ---- value: inputs resident in HBM
     sampler = ClockSampler(local_rank)
@@ -646,6 +674,69 @@ def run_ours(args):
                "d2h_bytes_per_step": 4, "wall_ms_per_step": float(t[1].item()) / timed_steps,
                "note": "the views' 8-bit target images copied from pinned host memory every step (double-buffered on a copy "
                        "stream), target pyramid built on the device, loss scalar read back every step"}
+
+    # ---- the same step through the C++/libtorch operator surface (torch.ops.vetr.blend_point_cloud: the PointRender
+    # autograd node of vet_b200/torch_shim, what the reference's pipeline calls) with torch's own L1 loss and
+    # loss.backward(), inputs and loss crossing the host boundary as in the e2e leg.  Rank 0 at N = 1.
+    e2e_shim = None
+    if not args.no_e2e and world == 1 and args.mode == 1:
+        try:
+            shim = os.path.join(ROOT, "vet_b200", "libvetr_torch.so")
+            torch.ops.load_library(shim)
+            leaf = lambda t: t.detach().clone().requires_grad_(True)
+            sh_tex, sh_bg, sh_pos, sh_conf = leaf(texture), leaf(background), leaf(position), leaf(confidence[None])
+            sh_tan = torch.zeros(poses.shape[0], 6, dtype=torch.float64, device=dev, requires_grad=True)
+            vi = torch.tensor([[v.w, v.h, v.image_index, v.camera_index, v.camera_model] for v in my_views], dtype=torch.int32)
+            vf = torch.tensor([list(v.crop) + list(v.rot) for v in my_views], dtype=torch.float32)
+            leaves = (sh_tex, sh_bg, sh_pos, sh_conf, sh_tan)
+            cs2 = torch.cuda.Stream(dev)
+            bufs2 = [torch.empty_like(targets_host, device=dev) for _ in range(2)]
+            ready2, used2 = [torch.cuda.Event() for _ in range(2)], [torch.cuda.Event() for _ in range(2)]
+            loss_host2 = torch.zeros(1).pin_memory()
+
+            def shim_steps(k):
+                for ev in used2:
+                    ev.record(stream)
+                for i in range(k):
+                    with torch.cuda.stream(cs2):
+                        cs2.wait_event(used2[i % 2])
+                        bufs2[i % 2].copy_(targets_host, non_blocking=True)
+                        ready2[i % 2].record(cs2)
+                    stream.wait_event(ready2[i % 2])
+                    build_targets(bufs2[i % 2], static_targets)
+                    used2[i % 2].record(stream)
+                    for t in leaves:
+                        t.grad = None
+                    outs = torch.ops.vetr.blend_point_cloud(sh_tex, sh_bg, sh_pos, index[:, None], poses, sh_tan, intrinsics, sh_conf,
+                                                            vi, vf, LAYERS, 1, False, False, True, False, True)
+                    l1 = sum((o - t).abs().mean() for o, t in zip(outs[:LAYERS], static_targets))
+                    l1.backward()
+                    loss_host2.copy_(l1.detach().reshape(1), non_blocking=True)
+                torch.cuda.synchronize(dev)
+
+            shim_steps(3)
+            base_alloc = torch.cuda.memory_allocated(dev)
+            torch.cuda.reset_peak_memory_stats(dev)
+            k_shim = max(5, min(timed_steps, 50))
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            s0.record(stream)
+            shim_steps(k_shim)
+            s1.record(stream)
+            torch.cuda.synchronize(dev)
+            wall = (time.perf_counter() - t0) * 1e3
+            peak_extra = torch.cuda.max_memory_allocated(dev) - base_alloc
+            e2e_shim = {"value": V * k_shim / (s0.elapsed_time(s1) * 1e-3), "unit": UNIT, "steps": k_shim,
+                        "wall_ms_per_step": wall / k_shim, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
+                        "peak_extra_device_bytes": int(peak_extra), "fragment_records_bytes": int(F_total) * 32,
+                        "loss": float(loss_host2.item()),
+                        "note": "torch.ops.vetr.blend_point_cloud + torch L1 loss + loss.backward(); the fragment buffer is sized "
+                                "from the totals of earlier calls; peak_extra = device memory above the resident tensors while a "
+                                "step runs (lists, scratch, images, gradients, autograd's saved tensors)"}
+            del leaves, sh_tex, sh_bg, sh_pos, sh_conf, sh_tan, bufs2
+            torch.cuda.empty_cache()
+        except Exception as e:  # noqa: BLE001
+            e2e_shim = {"error": repr(e)[:300]}
 
     # ---- per-kernel timing (CUDA events on the launching stream, outside the timed region) and roofline
     rast.set_timing(True)
@@ -883,7 +974,7 @@ def run_ours(args):
                                    + (f", gradients of 9 floats per point summed over the ranks ({exchange_kind})" if world > 1 else ""),
                        "views_per_gpu": V, "views_mode": args.views_mode if world > 1 else None, "points": N, "l2": "inputs larger than L2 (cloud 128 MB + descriptors 160 MB + "
                                                               "pyramids; gradient buffer 288 MB rewritten every step)"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
+            "clocks": clocks, "e2e": e2e, "e2e_shim": e2e_shim, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
             "loss": float(loss.item()), "step_ms": [round(x, 3) for x in step_ms], "cuda_graph": graph_info, "exchange": exchange_kind + ("+overlap" if overlap else ""), "per_rank": per_rank, "next_rows": next_rows,
             "parity_headline": parity_headline, "exchange_check": exchange_check, "configs": configs,
         }
@@ -1104,19 +1195,27 @@ def run_configs(args, torch, dist, rast, dev, rank, world, peak):
         local = [float(x[1].item()) for x in per]
         return step_ms, local
 
-    # per-view fragment counts (what a training loop has from the previous step): one launch per view, round robin
+    # per-view cost (what a training loop knows from the previous epoch): every rank renders its round-robin share one
+    # view per launch, forward + backward, and times each view on the device; fragments are counted on the way
     round_robin = [[v for v in range(views5) if v % world == r] for r in range(world)]
     run.chunk = 1
-    run.backward, keep = False, run.backward
-    run.local_step(round_robin[rank], read_counts=True)
-    run.chunk, run.backward = 4, keep
+    cost = torch.zeros(views5, dtype=torch.float64, device=dev)
     frag = torch.zeros(views5, dtype=torch.float64, device=dev)
-    for v, (F, _) in run.fragments.items():
-        frag[v] = F
+    v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for v in round_robin[rank]:
+        run.local_step([v], read_counts=True)  # untimed: sizes the scratch of a one-view launch, reads the fragment count
+        v0.record(st)
+        run.local_step([v])
+        v1.record(st)
+        torch.cuda.synchronize(dev)
+        cost[v] = v0.elapsed_time(v1)
+        frag[v] = run.fragments[v][0]
+    run.chunk = 4
     if world > 1:
+        dist.all_reduce(cost)
         dist.all_reduce(frag)
     frag = [float(x) for x in frag.tolist()]
-    costs = [f + 4.0 * run.P for f in frag]  # work units of a view: one per fragment, four per pixel
+    costs = [float(x) for x in cost.tolist()]
     balanced, load = balanced_assignment(costs, world)
     rr_ms, rr_local = time_sharded(round_robin)
     bal_ms, bal_local = (rr_ms, rr_local) if world == 1 else time_sharded(balanced)
@@ -1128,11 +1227,12 @@ def run_configs(args, torch, dist, rast, dev, rank, world, peak):
              "scaling": "strong", "n_gpus": world, "views_per_step": views5,
              "round_robin": {"ms_per_step": rr_ms, "frames_per_s": views5 / (rr_ms * 1e-3), "local_ms_per_rank": [round(x, 3) for x in rr_local],
                              "slowest_over_fastest_rank": max(rr_local) / max(min(rr_local), 1e-9)},
-             "balanced_by_fragments": {"ms_per_step": bal_ms, "frames_per_s": views5 / (bal_ms * 1e-3),
+             "balanced_by_view_cost": {"ms_per_step": bal_ms, "frames_per_s": views5 / (bal_ms * 1e-3),
                                        "local_ms_per_rank": [round(x, 3) for x in bal_local],
                                        "slowest_over_fastest_rank": max(bal_local) / max(min(bal_local), 1e-9),
                                        "views_per_rank": [len(m) for m in balanced]},
              "fragments_per_view": {"min": min(frag), "max": max(frag), "total": F5},
+             "ms_per_view_alone": {"min": min(costs), "max": max(costs)},
              "exchange_bytes_per_rank": 36 * n5}
     best = min(rr_ms, bal_ms)
     bytes_step = sum(algorithmic_bytes_per_launch(n5, F5 * 4 / views5, run.P * 4, 0, 4, True) for _ in range(views5 // 4)) + 80 * n5

@@ -86,6 +86,55 @@ def test_undefined_gradients_for_inputs_without_grad(ops):
     assert texture.grad is not None and position.grad is None and tangent.grad is None and intr.grad is None
 
 
+def _render(ops, sc, mode=1, layers=4, drop_by_radius=True, backward=True):
+    import torch
+
+    dev = torch.device("cuda", 0)
+    t = lambda a, rg=False: torch.from_numpy(a).to(dev).requires_grad_(rg)
+    texture = t(sc.texture, True)
+    tangent = torch.zeros(sc.poses.shape[0], 6, dtype=torch.float64, device=dev)
+    vi, vf = _views(sc, dev)
+    out = ops.blend_point_cloud(texture, t(sc.background), t(sc.position), t(sc.index[:, None]), t(sc.poses), tangent,
+                                t(sc.intrinsics), t(sc.confidence[None]), vi, vf, layers, mode, False, False, drop_by_radius, False, False)
+    if backward:
+        sum(o.sum() for o in out).backward()
+    torch.cuda.synchronize()
+    return out, texture
+
+
+def test_fragment_buffer_follows_what_was_seen(ops):
+    """The shim sizes the fragment buffer from the totals of earlier calls (1.5 x the largest seen per view of the same cloud
+    and pyramid) instead of the worst case; a view that needs more than that is reported at the next entry into the
+    operator, and the call after that is sized safely again."""
+    import copy
+
+    sc = scenes.tiny_scene(n=20010, w=96, h=64, n_views=1, seed=33)
+    far = copy.deepcopy(sc)
+    far.position[500:, 0] += 1000.0  # all but 500 points leave the frustum: a handful of fragments, same tensor shapes
+    params = default_params(drop_out_points_by_radius=0)
+    ora, ora_far = util.run_oracle(sc, params), util.run_oracle(far, params)
+    assert ora_far["F"] * 1.5 + 4096 < ora["F"]
+    out, _ = _render(ops, far, drop_by_radius=False)      # first call of this shape: the bound that cannot overflow
+    np.testing.assert_array_equal(out[0].detach().cpu().numpy(), ora_far["fwd"]["color"][0])
+    out, _ = _render(ops, far, drop_by_radius=False)      # sized from the first call's total
+    np.testing.assert_array_equal(out[0].detach().cpu().numpy(), ora_far["fwd"]["color"][0])
+    with pytest.raises(RuntimeError, match="overflowed"):
+        _render(ops, sc, drop_by_radius=False)            # the dense view exceeds it: reported before its gradients form
+    for _ in range(3):                                    # the call after that is safe again, and so are the following ones
+        out, _ = _render(ops, sc, drop_by_radius=False)
+        np.testing.assert_array_equal(out[0].detach().cpu().numpy(), ora["fwd"]["color"][0])
+
+
+def test_mode2_skipped_list_is_reported(ops):
+    """Mode 2's backward pass skips lists of more than 4096 fragments; through the shim that surfaces as an error at the
+    next call instead of silently missing gradients."""
+    sc = scenes.tiny_scene(n=45000, w=16, h=12, n_views=1, seed=5)
+    _render(ops, sc, mode=2, layers=3, drop_by_radius=False)
+    with pytest.raises(RuntimeError, match="4096"):
+        _render(ops, sc, mode=2, layers=3, drop_by_radius=False, backward=False)
+    _render(ops, sc, mode=2, layers=3, drop_by_radius=False, backward=False)  # a forward-only call has nothing to report
+
+
 def test_apply_tangent_to_pose(ops):
     import torch
     from oracle import oracle as O

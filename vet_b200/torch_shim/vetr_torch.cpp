@@ -4,6 +4,7 @@
 
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime.h>
 
 #include <stdexcept>
 #include <string>
@@ -101,7 +102,7 @@ GroupLists alloc_lists(int64_t n_pixels, int64_t capacity, int64_t mask_entries,
     g.items  = torch::empty({n_items}, i32);
     g.level_mask = torch::empty({std::max<int64_t>(mask_entries, 1)}, i32.dtype(torch::kUInt8));
     g.c = {g.counts.data_ptr<int>(), g.ends.data_ptr<int>(), g.frags.data_ptr(), capacity, g.status.data_ptr<int>(),
-           g.items.data_ptr<int>(), n_items, g.level_mask.data_ptr<uint8_t>(), nullptr, nullptr};
+           g.items.data_ptr<int>(), n_items, mask_entries > 0 ? g.level_mask.data_ptr<uint8_t>() : nullptr, nullptr, nullptr};
     return g;
 }
 
@@ -116,6 +117,11 @@ std::vector<float*> level_ptrs(const std::vector<torch::Tensor>& t, int b0)
 PointRendererCache::~PointRendererCache()
 {
     if (ctx_) vetr_destroy(ctx_);
+    if (status_host_)
+    {
+        cudaFreeHost(status_host_);
+        for (auto& e : status_event_) cudaEventDestroy(e);
+    }
 }
 
 vetr_ctx* PointRendererCache::context(int device)
@@ -129,6 +135,62 @@ vetr_ctx* PointRendererCache::context(int device)
     }
     check(vetr_set_stream(ctx_, stream), "vetr_set_stream");
     return ctx_;
+}
+
+int64_t PointRendererCache::FragmentCapacity(int64_t safe_bound, int n_views, int n_points, int num_layers, int w, int h, int mode)
+{
+    const int64_t shape[5] = {n_points, num_layers, w, h, mode};
+    if (!std::equal(shape, shape + 5, shape_))  // another cloud, pyramid or mode: what was seen says nothing about it
+    {
+        std::copy(shape, shape + 5, shape_);
+        high_water_per_view_ = 0;
+    }
+    int64_t cap = safe_bound;
+    if (high_water_per_view_ > 0 && mode != VETR_MODE_FUZZY_DT)  // (mode 0 keeps one record per pixel, not lists)
+        cap = std::min<int64_t>(safe_bound, (int64_t)(kFragmentHeadroom * (double)high_water_per_view_ * n_views) + 4096);
+    last_fragment_capacity = cap;
+    return cap;
+}
+
+void PointRendererCache::NoteStatus(const torch::Tensor& status_dev, int64_t capacity, int n_views, bool after_backward)
+{
+    if (pending_.size() >= kStatusSlots) CheckEarlierCalls();
+    if (!status_host_)
+    {
+        // plain runtime objects, not tensors: a cache may live in static storage and be destroyed after libtorch's own
+        // allocators, and the runtime's calls fail harmlessly then
+        TORCH_CHECK(cudaMallocHost((void**)&status_host_, kStatusSlots * 4 * sizeof(int)) == cudaSuccess, "vetr: no pinned memory");
+        for (auto& e : status_event_) TORCH_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess);
+    }
+    const int slot = (int)pending_.size();
+    cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
+    TORCH_CHECK(cudaMemcpyAsync(status_host_ + 4 * slot, status_dev.data_ptr<int>(), 4 * sizeof(int), cudaMemcpyDeviceToHost, st) ==
+                cudaSuccess);
+    TORCH_CHECK(cudaEventRecord(status_event_[slot], st) == cudaSuccess);
+    pending_.push_back({slot, capacity, n_views, after_backward});
+}
+
+void PointRendererCache::CheckEarlierCalls()
+{
+    std::string problem;
+    for (auto& p : pending_)
+    {
+        cudaEventSynchronize(status_event_[p.slot]);  // recorded one call ago: already complete
+        const int* w = status_host_ + 4 * p.slot;
+        if (!p.after_backward && render_mode != FUZZY_DT)
+            high_water_per_view_ = std::max<int64_t>(high_water_per_view_, ((int64_t)w[0] + p.n_views - 1) / std::max(p.n_views, 1));
+        if (w[1] & 1)
+        {
+            high_water_per_view_ = 0;  // the next call is sized by the bound that cannot overflow
+            problem = "vetr: the fragment buffer of the previous render call overflowed (" + std::to_string(w[0]) + " fragments, room for " +
+                      std::to_string(p.capacity) + "); its images are incomplete.  The next call is sized safely: run the step again";
+        }
+        else if ((w[1] & 2) && p.after_backward)
+            problem = "vetr: the mode-2 backward pass skipped at least one list of more than 4096 fragments (longest list " +
+                      std::to_string(w[2]) + "); its gradients are incomplete";
+    }
+    pending_.clear();
+    if (!problem.empty()) throw std::runtime_error(problem);
 }
 
 void PointRendererCache::FillSceneGridWithLoss(int batch, RenderScene& s, const std::vector<ReducedImageInfo>& images,
@@ -201,6 +263,7 @@ variable_list PointRender::forward(AutogradContext* ctx, Variable texture, Varia
 
     const int B = (int)info->images.size(), L = info->num_layers, C = info->params.num_texture_channels;
     TORCH_CHECK(B > 0);
+    cache.CheckEarlierCalls();
     cache.num_batches = B;
     cache.render_mode = (PointRendererCache::RenderMode)info->params.render_mode;
     const vetr_params prm = make_params(*info);
@@ -239,16 +302,22 @@ variable_list PointRender::forward(AutogradContext* ctx, Variable texture, Varia
         const bool point_pass = prm.render_mode == VETR_MODE_BILINEAR_BLEND ||
                                 ((prm.render_mode == VETR_MODE_FULL_BLEND || prm.render_mode == VETR_MODE_FUZZY_BLEND) &&
                                  prm.need_point_gradient);
-        GroupLists g = alloc_lists(P * nb, vetr_list_capacity(in.cloud.n, nb, info->images.front().w, info->images.front().h, &prm),
-                                   point_pass ? (int64_t)nb * in.cloud.n : 0, dev);
+        const int w0 = info->images.front().w, h0 = info->images.front().h;
+        const int64_t capacity = cache.FragmentCapacity(vetr_list_capacity(in.cloud.n, nb, w0, h0, &prm), nb, in.cloud.n, L, w0, h0,
+                                                        prm.render_mode);
+        GroupLists g = alloc_lists(P * nb, capacity, point_pass ? (int64_t)nb * in.cloud.n : 0, dev);
         auto views   = make_views(*info, b0, b1);
         auto pc = level_ptrs(color, b0), pw = level_ptrs(weight, b0), pd = level_ptrs(depth, b0), pm = level_ptrs(mask, b0);
         check(vetr_forward(vc, &prm, &in.cloud, &in.tex, &in.cams, views.data(), nb,
                            dropout.defined() ? dropout.data_ptr<float>() + (int64_t)b0 * dropout.stride(0) : nullptr, &g.c,
                            pc.data(), pw.data(), mask.empty() ? nullptr : pm.data(), pd.data()),
               "vetr_forward");
+        cache.NoteStatus(g.status, capacity, nb, false);
         for (auto& t : {g.counts, g.ends, g.frags, g.status, g.items, g.level_mask}) saved.push_back(t);
     }
+    // the drop-out mask belongs to this call (PointRenderer.cu:1056, 1194 save it with the node): a second forward through
+    // the same cache before this call's backward must not replace it
+    saved.push_back(dropout.defined() ? dropout : torch::empty({0}, f32));
     ctx->saved_data["n_groups"] = n_groups;
     ctx->save_for_backward(saved);
 
@@ -272,7 +341,9 @@ variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_out
     Inputs in             = make_inputs(s);
     auto saved            = ctx->get_saved_variables();
     const int n_groups    = (int)ctx->saved_data["n_groups"].toInt();
-    TORCH_CHECK((int)saved.size() == 5 + L + 6 * n_groups);
+    TORCH_CHECK((int)saved.size() == 5 + L + 6 * n_groups + 1);
+    cache.CheckEarlierCalls();  // an overflow of this call's forward pass is reported before gradients are formed from it
+    const torch::Tensor dropout = saved.back();
 
     std::vector<torch::Tensor> color(saved.begin() + 5, saved.begin() + 5 + L), gcolor;
     for (int l = 0; l < L; ++l)
@@ -314,9 +385,9 @@ variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_out
         auto views = make_views(*info, b0, b1);
         auto pc = level_ptrs(color, b0), pg = level_ptrs(gcolor, b0);
         std::vector<const float*> cpc(pc.begin(), pc.end()), cpg(pg.begin(), pg.end());
-        const bool has_dropout = cache.dropout_points.defined() && info->params.dropout > 0 && info->train;
+        const bool has_dropout = dropout.numel() > 0;
         check(vetr_backward(vc, &prm, &in.cloud, &in.tex, &in.cams, views.data(), nb,
-                            has_dropout ? cache.dropout_points.data_ptr<float>() + (int64_t)b0 * cache.dropout_points.stride(0) : nullptr,
+                            has_dropout ? dropout.data_ptr<float>() + (int64_t)b0 * dropout.stride(0) : nullptr,
                             &lists, cpc.data(), cpg.data(),
                             g_desc.data_ptr<float>(), g_conf.data_ptr<float>(),
                             g_points.defined() ? g_points.data_ptr<float>() : nullptr, g_background.data_ptr<float>(),
@@ -325,6 +396,8 @@ variable_list PointRender::backward(AutogradContext* ctx, variable_list grad_out
                             g_intr.defined() ? g_intr.data_ptr<float>() : nullptr,
                             g_intr.defined() ? g_intr_count.data_ptr<float>() : nullptr),
               "vetr_backward");
+        // mode 2 flags lists it had to skip in the status words: looked at when the next call starts
+        if (prm.render_mode == VETR_MODE_FUZZY_BLEND) cache.NoteStatus(t[3], t[2].size(0), nb, true);
     }
     torch::Tensor g_texture = torch::empty_like(s.texture);
     check(vetr_finalize_gradients(vc, C, (int)n_tex, g_desc.data_ptr<float>(), g_texture.data_ptr<float>(), (int)n,

@@ -104,6 +104,19 @@ class PointRendererCache
 
     vetr_ctx* context(int device);  // one C-ABI context per cache, created on first use on the current stream
 
+    // Fragment buffer sizing.  The reference reads the list sizes back (two blocking .item() per view and level,
+    // PointRenderer.cu:796-822) and allocates exactly; here nothing is read back inside a call.  The first call for a
+    // scene shape uses the bound that cannot overflow (vetr_list_capacity: every point on every level); every call copies
+    // its status words (fragment total, overflow flag) to pinned host memory behind its kernels, and later calls size the
+    // buffer as kFragmentHeadroom x the largest total per view seen so far.  The words of earlier calls are looked at when
+    // the next call starts and again before a backward pass (long after the copy finished, so nothing stalls): an overflow
+    // or a list the mode-2 backward pass had to skip raises an error there, and the next call is sized by the safe bound.
+    static constexpr double kFragmentHeadroom = 1.5;
+    int64_t FragmentCapacity(int64_t safe_bound, int n_views, int n_points, int num_layers, int w, int h, int mode);
+    void NoteStatus(const torch::Tensor& status_dev, int64_t capacity, int n_views, bool after_backward);
+    void CheckEarlierCalls();  // throws std::runtime_error
+    int64_t last_fragment_capacity = 0;  // records the buffer of the most recent forward group held (for reporting)
+
     // PointRendererCache::FillSceneGridWithLoss (RenderForward.cu:761-791, called from train.cpp:1077): adds the loss image
     // of images[batch] ([C,h,w]) to the grid cells of `scene` that its camera sees.  Enqueued on the current stream; the
     // reference synchronises the device afterwards, this does not.
@@ -113,6 +126,19 @@ class PointRendererCache
    private:
     vetr_ctx* ctx_ = nullptr;
     int device_    = -1;
+    struct Pending
+    {
+        int slot;  // of status_host_ / status_event_
+        int64_t capacity;
+        int n_views;
+        bool after_backward;
+    };
+    static constexpr size_t kStatusSlots = 16;
+    std::vector<Pending> pending_;
+    int* status_host_ = nullptr;  // [kStatusSlots][4] pinned: {fragment total, flags, longest list, work items} of a call
+    CUevent_st* status_event_[kStatusSlots] = {};  // cudaEvent_t recorded behind the copy into the slot
+    int64_t high_water_per_view_ = 0;  // largest fragment total per view seen for shape_
+    int64_t shape_[5]            = {-1, -1, -1, -1, -1};
 };
 
 class NeuralRenderInfo : public torch::CustomClassHolder
