@@ -69,9 +69,10 @@ def parse_args():
                          "segments (measured no faster at N = 2: the extra collective and launches cost what the overlap saves)")
     ap.add_argument("--torch-loss", action="store_true", help="form the L1 loss and its gradient with torch element-wise kernels")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
-    ap.add_argument("--no-graph-step", action="store_true",
-                    help="N > 1: keep the collectives and the exchange kernel outside the CUDA graph (by default the whole step, "
-                         "NCCL calls and side stream included, is one graph when every rank can capture it)")
+    ap.add_argument("--graph-step", action="store_true",
+                    help="N > 1: capture the whole step - NCCL calls, exchange kernel(s) and the side stream of --overlap "
+                         "included - as one CUDA graph when every rank can (measured at N = 8: no gain without --overlap, "
+                         "2 % with it); by default the collectives and the exchange stay outside the graphs")
     return ap.parse_args()
 
 
@@ -484,7 +485,7 @@ def run_ours(args):
         # N > 1: the whole step as ONE graph - compute, the ordering collectives, the exchange kernel(s) and the side
         # stream of --overlap - so that no host launch sits between the compute part and the exchange.  Used only if every
         # rank captured it (agreed with a collective outside the capture); otherwise the two-graph form above stays.
-        if graph_info["used"] and peer is not None and not args.no_graph_step:
+        if graph_info["used"] and peer is not None and args.graph_step:
             captured = 1.0
             try:
                 graph_step = torch.cuda.CUDAGraph()
@@ -980,7 +981,20 @@ def run_ours(args):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        # Every rank is idle here (all work synchronised, the line printed).  Releasing graphs that hold NCCL kernels and
+        # tearing the process group down has been seen not to return; the result must not depend on that, so a watchdog
+        # ends the process if the teardown has not finished after a while.
+        import threading
+
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        watchdog = threading.Timer(20.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
         dist.destroy_process_group()
+        watchdog.cancel()
 
 
 # -------------------------------------------------------------------------------------------------------------
