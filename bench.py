@@ -931,6 +931,37 @@ def run_ours(args):
                 ms3 = m0.elapsed_time(m1) / reps3
                 next_rows["mode3"] = {"ms_per_step": ms3, "frames_per_s": V / (ms3 * 1e-3), "fragments": F3,
                                       "longest_list": longest3, "workload": "the headline step in render mode 3"}
+                # per-kernel table and roofline of the mode-3 step (one more step with the passes bracketed by events): the
+                # algorithmic bytes are those of mode 1 with mode 3's own F, plus 16 F for the (u, v, corner) side data the
+                # reference writes once and reads once per fragment
+                try:
+                    rast.set_timing(True)
+                    out3 = rast.forward(position, index, texture, confidence, background, poses, intrinsics, my_views, p3,
+                                        want_weight=True)
+                    rast.l1_loss_grad(out3["color"], targets_dev, grad_bufs, loss_buf)
+                    flat.zero_()
+                    g3 = rast.backward_raw(grad_bufs, want_intrinsics=False, accum=grad_views())
+                    touched3 = int(torch.count_nonzero(g3["points"][:, 3]).item())
+                    rast.finalize(g3)
+                    t3 = rast.timings()
+                    rast.set_timing(False)
+                    bytes3 = {"count": 16 * N * V + 4 * PT, "scan": 12 * PT, "collect": 16 * N * V + 8 * F3,
+                              "sort_blend": 36 * F3 + 4 * PT + (4 * CHANNELS + 4) * PT,
+                              "backward": 28 * F3 + 4 * PT + 8 * CHANNELS * PT + 2 * 20 * touched3,
+                              "point_backward": 16 * F3 + 2 * 16 * touched3, "finalize": 32 * n_tex + 32 * N}
+                    k3 = {k: {"ms": t3.get(k, 0.0), "bytes": b, "gbs": (b / (t3[k] * 1e-3) / 1e9) if t3.get(k, 0.0) > 0 else None}
+                          for k, b in bytes3.items()}
+                    whole3 = sum(bytes3.values()) + 16 * F3 + 4 * flat.numel()
+                    dom3 = max(k3, key=lambda k: k3[k]["ms"])
+                    next_rows["mode3"]["roofline"] = {
+                        "bound": "hbm", "kernel": dom3, "achieved": k3[dom3]["gbs"], "peak": peak, "unit": "GB/s",
+                        "frac": (k3[dom3]["gbs"] or 0.0) / peak, "traffic": None, "kernels": k3,
+                        "whole_step": {"algorithmic_bytes": whole3, "achieved_gbs": whole3 / (ms3 * 1e-3) / 1e9,
+                                       "frac": whole3 / (ms3 * 1e-3) / 1e9 / peak},
+                        "counts": {"N": N, "N_touched": touched3, "F": F3, "pixels": PT, "longest_list": longest3}}
+                except Exception as e:  # noqa: BLE001
+                    rast.set_timing(False)
+                    next_rows["mode3"]["roofline"] = {"error": repr(e)[:200]}
                 del out3, g3
                 rast._lists_cache.clear()
                 rast._saved = None

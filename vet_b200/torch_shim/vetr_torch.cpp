@@ -482,6 +482,136 @@ int64_t RemovePoints(RenderScene& s, torch::Tensor indices_to_remove, std::vecto
 }  // namespace vetr_torch
 
 // ---------------------------------------------------------------------------------------------------------
+// Adding points, ordering a cloud
+
+namespace vetr_torch
+{
+namespace
+{
+// t <- cat(t, fill) along the last (point) dimension, in place
+void append_columns(torch::Tensor& t, int64_t m, const torch::Tensor& fill_like_values)
+{
+    if (!t.defined() || m == 0) return;
+    t.set_(torch::cat({t.detach(), fill_like_values.to(t.options())}, -1));
+}
+}  // namespace
+
+int64_t AddNewPoints(RenderScene& s, torch::Tensor new_positions, std::vector<torch::Tensor> per_point_state, bool random_init,
+                     torch::Tensor u, torch::Tensor distance)
+{
+    TORCH_CHECK(s.t_position.defined() && s.t_position.dim() == 2 && s.t_position.size(1) == 4, "AddNewPoints: t_position must be [N,4]");
+    TORCH_CHECK(new_positions.dim() == 2 && new_positions.size(1) == 3 && new_positions.dtype() == torch::kFloat32,
+                "AddNewPoints: new positions must be [m,3] float");
+    torch::NoGradGuard ngg;
+    const auto dev  = s.t_position.device();
+    const int64_t n = s.t_position.size(0), m = new_positions.size(0), total = n + m;
+    auto column_fill = [&](const torch::Tensor& t, double value) {
+        auto sizes   = t.sizes().vec();
+        sizes.back() = m;
+        return torch::full(sizes, value, t.options());
+    };
+    if (s.texture.defined())
+    {
+        TORCH_CHECK(s.texture.size(-1) == n, "AddNewPoints: texture does not match the cloud");
+        torch::Tensor fill = column_fill(s.texture, 0.5);
+        if (random_init) fill = torch::rand_like(fill) * 2 - fill * 2;  // NeuralTexture.cpp:135-138
+        append_columns(s.texture, m, fill);
+    }
+    if (s.confidence_value_of_point.defined()) append_columns(s.confidence_value_of_point, m, column_fill(s.confidence_value_of_point, 0.0));
+    for (auto& t : per_point_state)
+    {
+        if (!t.defined()) continue;
+        TORCH_CHECK(t.size(-1) == n, "AddNewPoints: per-point state tensors end in the point dimension");
+        append_columns(t, m, column_fill(t, 0.0));
+    }
+    // positions: appended, then the drop-out radius of the whole cloud as SceneData::ComputeRadius leaves it
+    torch::Tensor xyz = torch::cat({s.t_position.detach().slice(1, 0, 3), new_positions.to(dev)}, 0).contiguous();
+    if (!distance.defined()) distance = total > 0 ? ComputeRadius(xyz, 4) : torch::empty({0}, xyz.options());
+    TORCH_CHECK(distance.numel() == total, "AddNewPoints: one neighbour distance per point");
+    if (!u.defined()) u = torch::rand({total}, xyz.options()).clamp_min(1e-12);
+    TORCH_CHECK(u.numel() == total, "AddNewPoints: one uniform sample per point");
+    const torch::Tensor factor = torch::sqrt(1.0 / u.to(dev, torch::kFloat64)).to(torch::kFloat32);  // d[2] = sqrt(1 / sample)
+    const torch::Tensor radius = distance.to(dev, torch::kFloat32).reshape({-1}) * factor.reshape({-1});  // d[3] = d[0] * d[2]
+    s.t_position.set_(torch::cat({xyz, radius.reshape({total, 1})}, 1).contiguous());
+    if (s.t_index.defined()) s.t_index.set_(torch::arange(total, s.t_index.options()).reshape({total, 1}));
+    return total;
+}
+
+namespace
+{
+// spreads the low 21 bits of v so that two zero bits follow every bit
+torch::Tensor part1by2(torch::Tensor v)
+{
+    auto m = [](uint64_t x) { return torch::Scalar((int64_t)x); };
+    v = v.bitwise_and(m(0x1FFFFF));
+    v = v.bitwise_or(v.bitwise_left_shift(32)).bitwise_and(m(0x1F00000000FFFFull));
+    v = v.bitwise_or(v.bitwise_left_shift(16)).bitwise_and(m(0x1F0000FF0000FFull));
+    v = v.bitwise_or(v.bitwise_left_shift(8)).bitwise_and(m(0x100F00F00F00F00Full));
+    v = v.bitwise_or(v.bitwise_left_shift(4)).bitwise_and(m(0x10C30C30C30C30C3ull));
+    v = v.bitwise_or(v.bitwise_left_shift(2)).bitwise_and(m(0x1249249249249249ull));
+    return v;
+}
+}  // namespace
+
+torch::Tensor MortonOrder(torch::Tensor position)
+{
+    TORCH_CHECK(position.dim() == 2 && position.size(1) >= 3, "MortonOrder: positions must be [N,3] or [N,4]");
+    torch::NoGradGuard ngg;
+    if (position.size(0) == 0) return torch::empty({0}, torch::TensorOptions().dtype(torch::kLong).device(position.device()));
+    const torch::Tensor xyz  = position.detach().slice(1, 0, 3).to(torch::kFloat64);
+    const torch::Tensor lo   = std::get<0>(xyz.min(0));
+    const torch::Tensor span = (std::get<0>(xyz.max(0)) - lo).clamp_min(1e-12);
+    const torch::Tensor q = ((xyz - lo) / span * (double)((1 << 21) - 1)).to(torch::kLong).clamp(0, (1 << 21) - 1);
+    const torch::Tensor code = part1by2(q.select(1, 0))
+                                   .bitwise_or(part1by2(q.select(1, 1)).bitwise_left_shift(1))
+                                   .bitwise_or(part1by2(q.select(1, 2)).bitwise_left_shift(2));
+    return std::get<1>(code.sort(/*stable=*/true, 0, false));
+}
+
+torch::Tensor RandomBlockShuffle(int64_t n, int64_t block, torch::Tensor block_perm, torch::Device device)
+{
+    TORCH_CHECK(n >= 0 && block >= 1, "RandomBlockShuffle: bad sizes");
+    const int64_t nb = (n + block - 1) / block;
+    const auto i64   = torch::TensorOptions().dtype(torch::kLong).device(device);
+    if (!block_perm.defined()) block_perm = torch::randperm(nb, i64);
+    TORCH_CHECK(block_perm.numel() == nb, "RandomBlockShuffle: one entry per block");
+    const torch::Tensor idx = (block_perm.to(device, torch::kLong).reshape({nb, 1}) * block + torch::arange(block, i64).reshape({1, block})).reshape({-1});
+    return idx.masked_select(idx < n);
+}
+
+torch::Tensor SortBlocksByRadius(torch::Tensor radius, int64_t block)
+{
+    TORCH_CHECK(radius.dim() == 1 && block >= 1, "SortBlocksByRadius: radius must be [N]");
+    torch::NoGradGuard ngg;
+    const int64_t n = radius.size(0), nb = n / block;  // the reference sorts full blocks only
+    const auto i64  = torch::TensorOptions().dtype(torch::kLong).device(radius.device());
+    torch::Tensor perm = torch::arange(n, i64);
+    if (nb == 0) return perm;
+    const torch::Tensor in_block = std::get<1>(radius.detach().slice(0, 0, nb * block).reshape({nb, block}).sort(/*stable=*/true, 1, false));
+    perm.slice(0, 0, nb * block).copy_((in_block + torch::arange(nb, i64).reshape({nb, 1}) * block).reshape({-1}));
+    return perm;
+}
+
+void ApplyPointOrder(RenderScene& s, torch::Tensor perm, std::vector<torch::Tensor> per_point_state)
+{
+    TORCH_CHECK(s.t_position.defined() && perm.dim() == 1 && perm.size(0) == s.t_position.size(0), "ApplyPointOrder: one index per point");
+    torch::NoGradGuard ngg;
+    const int64_t n = perm.size(0);
+    perm = perm.to(s.t_position.device(), torch::kLong);
+    s.t_position.set_(s.t_position.detach().index_select(0, perm));
+    std::vector<torch::Tensor*> last = {&s.texture, &s.confidence_value_of_point};
+    for (auto& t : per_point_state) last.push_back(&t);
+    for (torch::Tensor* t : last)
+    {
+        if (!t->defined()) continue;
+        TORCH_CHECK(t->size(-1) == n, "ApplyPointOrder: per-point tensors end in the point dimension");
+        t->set_(t->detach().index_select(t->dim() - 1, perm.to(t->device())));
+    }
+    if (s.t_index.defined()) s.t_index.set_(torch::arange(n, s.t_index.options()).reshape({n, 1}));
+}
+}  // namespace vetr_torch
+
+// ---------------------------------------------------------------------------------------------------------
 // Environment map
 
 namespace vetr_torch
@@ -726,6 +856,26 @@ TORCH_LIBRARY(vetr, m)
         return vetr_torch::RemovePoints(scene, indices_to_remove, state);  // the tensors shrink in place
     });
     m.def("compute_radius", [](torch::Tensor position, int64_t n) { return vetr_torch::ComputeRadius(position, (int)n); });
+    m.def("add_new_points", [](torch::Tensor texture, torch::Tensor confidence, torch::Tensor position, torch::Tensor index,
+                               torch::Tensor new_positions, std::vector<torch::Tensor> state, bool random_init,
+                               c10::optional<torch::Tensor> u, c10::optional<torch::Tensor> distance) {
+        vetr_torch::RenderScene scene;
+        scene.texture = texture, scene.confidence_value_of_point = confidence, scene.t_position = position, scene.t_index = index;
+        return vetr_torch::AddNewPoints(scene, new_positions, state, random_init, u.value_or(torch::Tensor()),
+                                        distance.value_or(torch::Tensor()));  // the tensors grow in place
+    });
+    m.def("morton_order", &vetr_torch::MortonOrder);
+    m.def("random_block_shuffle", [](int64_t n, int64_t block, c10::optional<torch::Tensor> block_perm) {
+        const torch::Tensor bp = block_perm.value_or(torch::Tensor());
+        return vetr_torch::RandomBlockShuffle(n, block, bp, bp.defined() ? bp.device() : torch::Device(torch::kCPU));
+    });
+    m.def("sort_blocks_by_radius", &vetr_torch::SortBlocksByRadius);
+    m.def("apply_point_order", [](torch::Tensor texture, torch::Tensor confidence, torch::Tensor position, torch::Tensor index,
+                                  torch::Tensor perm, std::vector<torch::Tensor> state) {
+        vetr_torch::RenderScene scene;
+        scene.texture = texture, scene.confidence_value_of_point = confidence, scene.t_position = position, scene.t_index = index;
+        vetr_torch::ApplyPointOrder(scene, perm, state);  // the tensors are reordered in place
+    });
     m.class_<vetr_torch::NeuralRenderInfo>("NeuralRenderInfo").def(torch::init());
     m.def("blend_point_cloud", &blend_point_cloud_op);
     m.def("apply_tangent_to_pose", &vetr_torch::ApplyTangentToPose);

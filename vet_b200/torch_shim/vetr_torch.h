@@ -11,6 +11,8 @@
 //   EnvironmentMapImpl (constructor, density, color, Sample2)   rendering/EnvironmentMap.h:252-301
 //   SceneData::ComputeRadius(point_cloud, n)   data/SceneData.h:396
 //   NeuralScene::RemovePoints(indices_to_remove)   data/NeuralScene.h (device part)
+//   NeuralScene::AddNewPoints(positions)           data/NeuralScene.cpp:1013-1074 (device part)
+//   ReorderMorton64 / RandomBlockShuffle / SortBlocksByRadius   data/SceneData.cpp:105-108
 // The reference's NeuralScene / RenderParams / ReducedImageInfo come from parts of VET that need the saiga library;
 // the structs below carry exactly the fields the render operator reads from them, under the same names, so that the
 // reference's call site (models/Pipeline.cpp:133 via RenderModule.cpp:45-245) maps onto them one to one.
@@ -170,6 +172,36 @@ torch::Tensor ComputeRadius(torch::Tensor position, int n = 4);
 // and so does every tensor of `per_point_state` whose last dimension is the point count (the optimizer's exp_avg /
 // exp_avg_sq, my_adam.cpp:107-135).  indices_to_remove: int64, any device.  Returns the number of points left.
 int64_t RemovePoints(RenderScene& scene, torch::Tensor indices_to_remove, std::vector<torch::Tensor> per_point_state = {});
+
+// NeuralScene::AddNewPoints (data/NeuralScene.cpp:1013-1074) for the tensors the render operator reads, on whatever device
+// they live: the new positions are appended behind the existing ones (SceneData::AddPoints, SceneData.cpp:669-691),
+// t_index is rebuilt as the identity, texture gets columns of 0.5 - or of U(-1, 1) with `random_init` - and
+// confidence_value_of_point columns of 0 (NeuralPointTextureImpl::EnlargeTexture / ResizeAndFill, NeuralTexture.h:94-103,
+// NeuralTexture.cpp:118-158), every tensor of `per_point_state` (the optimizer's exp_avg / exp_avg_sq,
+// MyAdam::appendToInternalState, my_adam.cpp:137-170) columns of 0; all in place (Tensor::set_), so parameters keep
+// their identity.  The reference then recomputes the drop-out radius of the WHOLE cloud (ComputeRadius inside AddPoints):
+// column 3 of t_position becomes distance to the 4th nearest other point x sqrt(1 / u).  `u`: [N + m] uniform samples in
+// (0, 1] (drawn with torch::rand when undefined; the reference draws them from its own generator).  `distance`: the
+// neighbour distances [N + m] if the caller has them; otherwise they come from ComputeRadius (CUDA tensors).
+// Returns the new number of points.
+int64_t AddNewPoints(RenderScene& scene, torch::Tensor new_positions, std::vector<torch::Tensor> per_point_state = {},
+                     bool random_init = false, torch::Tensor u = {}, torch::Tensor distance = {});
+
+// The ordering the reference gives a cloud when a scene is prepared (data/SceneData.cpp:105-108: ReorderMorton64,
+// RandomBlockShuffle(256), ComputeRadius, SortBlocksByRadius(256)), as permutations computed with libtorch operators on
+// the tensors' own device (torch's sort is a device radix sort on CUDA tensors), so that texture and optimizer state can
+// follow the positions.  Each function returns int64 indices: element i of the new order is element perm[i] of the old.
+//   MortonOrder          stable ascending order of the 63-bit Morton code of the positions (21 bits per axis over the
+//                        bounding box, x in the lowest bit of every triple)
+//   RandomBlockShuffle   whole blocks of `block` consecutive points in the order `block_perm` (a permutation of the
+//                        ceil(n / block) block indices; torch::randperm when undefined); a shorter last block moves as it is
+//   SortBlocksByRadius   inside every full block, ascending by radius (SceneData.cpp:1005-1018; the tail stays)
+//   ApplyPointOrder      reorders t_position, texture, confidence_value_of_point and `per_point_state` in place and
+//                        rebuilds t_index as the identity
+torch::Tensor MortonOrder(torch::Tensor position);
+torch::Tensor RandomBlockShuffle(int64_t n, int64_t block, torch::Tensor block_perm, torch::Device device);
+torch::Tensor SortBlocksByRadius(torch::Tensor radius, int64_t block);
+void ApplyPointOrder(RenderScene& scene, torch::Tensor perm, std::vector<torch::Tensor> per_point_state = {});
 
 // What one Sample2 call hands to its autograd node.
 struct EnvironmentSampleState : public torch::CustomClassHolder
