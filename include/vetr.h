@@ -34,7 +34,7 @@ typedef enum vetr_status
     VETR_E_UNSUPPORTED    = -3, /* camera model / option the library does not implement */
     VETR_E_LIST_OVERFLOW  = -4, /* more fragments than the fragment buffer holds (reported by vetr_read_status) */
     VETR_E_TOO_LARGE      = -5  /* a size exceeds a fixed limit of the entry point (vetr_read_status: a list longer than
-                                   3072 fragments met the mode-2 backward pass, which skipped that pixel) */
+                                   4096 fragments met the mode-2 backward pass, which skipped that pixel) */
 } vetr_status;
 
 /* Render modes: PointRendererCache::RenderMode, PointRenderer.h. */
