@@ -83,3 +83,32 @@ def test_two_ranks_equal_one_process(tmp_path):
     np.testing.assert_allclose(got["background"], b["background"], atol=scale(b["background"]))
     np.testing.assert_allclose(got["pose"], b["pose"], rtol=1e-9, atol=1e-9)
     np.testing.assert_allclose(got["pose_count"], b["pose_count"], rtol=1e-6)
+
+
+def test_views_to_ranks_by_cost():
+    """bench.py's assignment of a batch's views to ranks for benchmark configuration 5: longest view first to the least
+    loaded rank.  Every view is assigned once, the loads add up, and no rank exceeds the greedy bound (mean + largest)."""
+    import bench
+
+    rng = np.random.default_rng(4)
+    for world in (1, 2, 4, 8):
+        costs = rng.uniform(1.8, 4.6, size=32).tolist()
+        mine, load = bench.balanced_assignment(costs, world)
+        assert sorted(v for m in mine for v in m) == list(range(32))
+        assert abs(sum(load) - sum(costs)) < 1e-9
+        for m, l in zip(mine, load):
+            assert abs(sum(costs[v] for v in m) - l) < 1e-9
+        assert max(load) <= sum(costs) / world + max(costs) + 1e-9
+    # equal costs: equal shares
+    mine, load = bench.balanced_assignment([1.0] * 32, 8)
+    assert [len(m) for m in mine] == [4] * 8
+
+
+def test_algorithmic_bytes_of_a_launch():
+    """The per-launch byte count bench.py divides by the measured time: forward 20 N per view + 36 F + 28 P, backward
+    32 P + 44 F + 40 N + 80 N_t."""
+    import bench
+
+    N, F, P, Nt = 1000, 5000, 300, 700
+    assert bench.algorithmic_bytes_per_launch(N, F, P, Nt, 1, False) == 20 * N + 36 * F + 28 * P
+    assert bench.algorithmic_bytes_per_launch(N, F, 4 * P, Nt, 4, True) == 20 * N * 4 + 36 * F + 28 * 4 * P + 32 * 4 * P + 44 * F + 40 * N + 80 * Nt
